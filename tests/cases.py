@@ -1,0 +1,226 @@
+"""Seeded input generators shared by the golden-vector script and the parity tests.
+
+Every tensor is drawn on the CPU in float32 from its own ``torch.Generator`` (seed derived from
+the case name and the tensor name) and then cast, so the golden script (run where the reference
+can be imported), the CPU oracle and the CUDA path all see bit-identical inputs.  The golden files
+store checksums of these inputs, so a drift of the generator is detected rather than silently
+compared against stale outputs.
+"""
+from __future__ import annotations
+
+import dataclasses
+import math
+import zlib
+from typing import Dict, Optional
+
+import torch
+
+
+@dataclasses.dataclass(frozen=True)
+class Case:
+  name: str
+  kind: str            # "blockdiag" | "conv1d" | "rglru" | "rnn_scan" | "block"
+  dtype: str           # "float32" | "bfloat16"
+  batch: int
+  seq: int
+  lru_width: int
+  heads: int = 1
+  width: int = 0       # block (model) width; 0 -> lru_width
+  temporal_width: int = 4
+  pos: str = "half"    # segment_pos pattern, see make_segment_pos
+  with_h0: bool = False
+  decode_steps: int = 2
+
+  @property
+  def torch_dtype(self) -> torch.dtype:
+    return {"float32": torch.float32, "bfloat16": torch.bfloat16}[self.dtype]
+
+  @property
+  def model_width(self) -> int:
+    return self.width or self.lru_width
+
+
+def _seed(case_name: str, tensor_name: str) -> int:
+  return zlib.crc32(f"{case_name}/{tensor_name}".encode()) & 0x7FFFFFFF
+
+
+def normal(case: str, name: str, shape, std: float = 1.0, dtype=torch.float32) -> torch.Tensor:
+  g = torch.Generator(device="cpu").manual_seed(_seed(case, name))
+  return (torch.randn(shape, generator=g, dtype=torch.float32) * std).to(dtype)
+
+
+def uniform(case: str, name: str, shape, lo: float, hi: float) -> torch.Tensor:
+  g = torch.Generator(device="cpu").manual_seed(_seed(case, name))
+  return torch.rand(shape, generator=g, dtype=torch.float32) * (hi - lo) + lo
+
+
+def make_a_param(case: str, width: int, dtype=torch.float32) -> torch.Tensor:
+  """softplus^-1(-0.5 ln u), u ~ U(0.9^2, 0.999^2): the RG-LRU's ring init (layers.py:194-213)."""
+  u = uniform(case, "a_param", (width,), 0.9 ** 2 + 1e-8, 0.999 ** 2 + 1e-8).double()
+  a_real = -0.5 * torch.log(u)
+  return torch.log(torch.expm1(a_real)).float().to(dtype)
+
+
+def make_segment_pos(pattern: str, batch: int, seq: int, case: str = "") -> torch.Tensor:
+  """int64 [batch, seq] positions; a zero marks the first token of a document."""
+  ar = torch.arange(seq, dtype=torch.int64)
+  if pattern == "arange":
+    pos = ar.repeat(batch, 1)
+  elif pattern == "half":
+    # The reference tests' pattern (torch/test_utils.py:74-75): two documents per row.
+    first = seq // 2
+    pos = torch.cat([torch.arange(first), torch.arange(seq - first)]).repeat(batch, 1)
+  elif pattern == "padded":
+    # Left padding as the sampler produces it (torch/sampler.py:235-238): padded slots hold -1,
+    # the first real token holds 0.  Row b is padded by (3*b + 1) % seq slots.
+    rows = []
+    for b in range(batch):
+      pad = (3 * b + 1) % max(seq, 1)
+      rows.append(torch.clamp(ar - pad, min=-1))
+    pos = torch.stack(rows)
+  elif pattern == "multi":
+    # Random document lengths, including one-token documents (consecutive zeros) and a
+    # document start in each of the last three slots of some row.
+    g = torch.Generator(device="cpu").manual_seed(_seed(case, "segment_pos"))
+    rows = []
+    for b in range(batch):
+      starts = torch.rand(seq, generator=g) < 0.12
+      starts[0] = True
+      if seq >= 3:
+        starts[seq - 1 - (b % 3)] = True
+      if seq >= 8:
+        starts[5] = True
+        starts[6] = True
+      p = torch.zeros(seq, dtype=torch.int64)
+      c = 0
+      for t in range(seq):
+        c = 0 if bool(starts[t]) else c + 1
+        p[t] = c
+      rows.append(p)
+    pos = torch.stack(rows)
+  elif pattern == "noreset":
+    # No document start at all (continuation of an earlier chunk): positions begin at 1.
+    pos = (ar + 1).repeat(batch, 1)
+  else:
+    raise ValueError(pattern)
+  return pos.contiguous()
+
+
+def geometric_segment_pos(batch: int, seq: int, mean_len: float, seed: int) -> torch.Tensor:
+  """Documents with Geometric(1/mean_len) lengths (support >= 1); t = 0 starts a document."""
+  g = torch.Generator(device="cpu").manual_seed(seed)
+  starts = torch.rand((batch, seq), generator=g) < (1.0 / mean_len)
+  starts[:, 0] = True
+  idx = torch.arange(seq, dtype=torch.int64).repeat(batch, 1)
+  last_start = torch.where(starts, idx, torch.zeros_like(idx)).cummax(dim=1).values
+  return (idx - last_start).contiguous()
+
+
+def make_params(case: Case) -> Dict[str, torch.Tensor]:
+  """Parameters named as in the reference state_dict of RecurrentBlock (modules.py:531-560)."""
+  dt = case.torch_dtype
+  e, h, d, w = case.lru_width, case.heads, case.model_width, case.temporal_width
+  bw = e // h
+  n = case.name
+  p = {
+      "rg_lru.a_param": make_a_param(n, e, dt),
+      "rg_lru.input_gate.w": normal(n, "gate_x_w", (h, bw, bw), math.sqrt(1.0 / bw), dt),
+      "rg_lru.input_gate.b": normal(n, "gate_x_b", (h, bw), 0.3, dt),
+      "rg_lru.a_gate.w": normal(n, "gate_a_w", (h, bw, bw), math.sqrt(1.0 / bw), dt),
+      "rg_lru.a_gate.b": normal(n, "gate_a_b", (h, bw), 0.3, dt),
+      "conv_1d.w": normal(n, "conv_w", (w, e), math.sqrt(1.0 / w), dt),
+      "conv_1d.b": normal(n, "conv_b", (e,), 0.2, dt),
+  }
+  if case.kind == "block":
+    p.update({
+        "linear_y.weight": normal(n, "linear_y_w", (e, d), math.sqrt(1.0 / d), dt),
+        "linear_y.bias": normal(n, "linear_y_b", (e,), 0.1, dt),
+        "linear_x.weight": normal(n, "linear_x_w", (e, d), math.sqrt(1.0 / d), dt),
+        "linear_x.bias": normal(n, "linear_x_b", (e,), 0.1, dt),
+        "linear_out.weight": normal(n, "linear_out_w", (d, e), math.sqrt(1.0 / e), dt),
+        "linear_out.bias": normal(n, "linear_out_b", (d,), 0.1, dt),
+    })
+  return p
+
+
+def make_inputs(case: Case) -> Dict[str, Optional[torch.Tensor]]:
+  """Activations, positions, optional initial state and the decode-step tokens of a case."""
+  dt = case.torch_dtype
+  n = case.name
+  in_width = case.model_width if case.kind == "block" else case.lru_width
+  out: Dict[str, Optional[torch.Tensor]] = {
+      "x": normal(n, "x", (case.batch, case.seq, in_width), 1.0, dt),
+      "segment_pos": make_segment_pos(case.pos, case.batch, case.seq, n),
+      "h0": normal(n, "h0", (case.batch, case.lru_width), 0.5) if case.with_h0 else None,
+  }
+  if case.kind == "rnn_scan":
+    a = uniform(n, "a", (case.batch, case.seq, case.lru_width), 0.5, 0.999).to(dt)
+    out["a"] = a
+  for i in range(case.decode_steps):
+    out[f"x_step{i}"] = normal(n, f"x_step{i}", (case.batch, 1, in_width), 1.0, dt)
+  return out
+
+
+def decode_positions(case: Case, segment_pos: torch.Tensor, step: int) -> torch.Tensor:
+  """Positions fed to decode step `step`: they continue from the last prefill position."""
+  return (segment_pos[:, -1:] + 1 + step).contiguous()
+
+
+def checksum(tensors: Dict[str, Optional[torch.Tensor]]) -> float:
+  s = 0.0
+  for k in sorted(tensors):
+    t = tensors[k]
+    if t is None:
+      continue
+    s += float(t.double().abs().sum()) + 0.5 * float(t.double().sum())
+  return s
+
+
+def _c(name, kind, dtype, b, t, e, h=1, **kw) -> Case:
+  return Case(name=name, kind=kind, dtype=dtype, batch=b, seq=t, lru_width=e, heads=h, **kw)
+
+
+def golden_cases():
+  """The cases whose reference outputs are committed under tests/golden/.
+
+  Shapes follow the reference's own parameterised tests (torch/layers_test.py:96-172,
+  torch/modules_test.py:119-159) shrunk where that keeps the fixture small, plus ragged lengths
+  and position patterns those tests do not reach.
+  """
+  cases = []
+  for dt in ("float32", "bfloat16"):
+    s = "f32" if dt == "float32" else "bf16"
+    cases += [
+        _c(f"bdl_{s}_128x1", "blockdiag", dt, 2, 8, 128, 1, decode_steps=0),
+        _c(f"bdl_{s}_1024x16", "blockdiag", dt, 2, 8, 1024, 16, decode_steps=0),
+        _c(f"bdl_{s}_512x2", "blockdiag", dt, 2, 8, 512, 2, decode_steps=0),
+        _c(f"conv_{s}_128_w4", "conv1d", dt, 2, 32, 128),
+        _c(f"conv_{s}_256_w4_multi", "conv1d", dt, 3, 37, 256, pos="multi"),
+        _c(f"conv_{s}_128_w8", "conv1d", dt, 2, 32, 128, temporal_width=8),
+        _c(f"conv_{s}_128_w4_t1", "conv1d", dt, 2, 1, 128, pos="arange"),
+        _c(f"conv_{s}_128_w4_t2", "conv1d", dt, 2, 2, 128, pos="multi"),
+        _c(f"conv_{s}_128_w4_t3", "conv1d", dt, 3, 3, 128, pos="multi"),
+        _c(f"conv_{s}_128_w4_pad", "conv1d", dt, 3, 9, 128, pos="padded"),
+        _c(f"scan_{s}_128", "rnn_scan", dt, 2, 40, 128, pos="multi", with_h0=True, decode_steps=0),
+        _c(f"scan_{s}_128_t1", "rnn_scan", dt, 2, 1, 128, pos="noreset", with_h0=True,
+           decode_steps=0),
+        _c(f"scan_{s}_128_t1_noh0", "rnn_scan", dt, 2, 1, 128, pos="noreset", decode_steps=0),
+        _c(f"rglru_{s}_128x1_t32", "rglru", dt, 2, 32, 128, 1),
+        _c(f"rglru_{s}_256x1_t128", "rglru", dt, 2, 128, 256, 1),
+        _c(f"rglru_{s}_1024x16_t32", "rglru", dt, 2, 32, 1024, 16),
+        _c(f"rglru_{s}_512x2_t131_multi_h0", "rglru", dt, 2, 131, 512, 2, pos="multi",
+           with_h0=True),
+        _c(f"rglru_{s}_256x1_t7_pad", "rglru", dt, 3, 7, 256, 1, pos="padded"),
+        _c(f"block_{s}_128_h1_l128", "block", dt, 2, 64, 128, 1, width=128),
+        _c(f"block_{s}_128_h1_l256_multi", "block", dt, 2, 67, 256, 1, width=128, pos="multi"),
+        _c(f"block_{s}_256_h8_l256", "block", dt, 2, 64, 256, 8, width=256),
+        _c(f"block_{s}_128_h2_l512_pad", "block", dt, 3, 21, 512, 2, width=128, pos="padded"),
+    ]
+  return cases
+
+
+def case_by_name(name: str) -> Case:
+  for c in golden_cases():
+    if c.name == name:
+      return c
+  raise KeyError(name)

@@ -1,0 +1,111 @@
+"""Generates tests/golden/*.npz by running the reference torch implementation on seeded inputs.
+
+Run where the reference checkout is available (it is imported, never copied):
+
+    python tests/golden/make_golden.py --reference /path/to/recurrentgemma-checkout
+
+`recurrentgemma/__init__.py` imports the JAX half of the package, which needs flax; registering an
+empty parent package first lets `recurrentgemma.torch` import on a torch-only machine.
+
+Each file holds the reference outputs of one case of tests/cases.py (prefill, then the decode
+steps fed with the returned cache) and a checksum of the generated inputs and parameters.
+bfloat16 tensors are stored widened to float32, which is exact.
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import sys
+import types
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+
+from tests import cases as C  # noqa: E402
+
+
+def import_reference(path: str):
+  pkg = types.ModuleType("recurrentgemma")
+  pkg.__path__ = [os.path.join(path, "recurrentgemma")]
+  sys.modules["recurrentgemma"] = pkg
+  import recurrentgemma.torch as rg  # pylint: disable=import-outside-toplevel
+  from recurrentgemma.torch import layers, modules  # pylint: disable=import-outside-toplevel
+  return rg, layers, modules
+
+
+def _np(t):
+  return t.detach().to(torch.float32).numpy()
+
+
+def run_case(case: C.Case, layers, modules) -> dict:
+  dt = case.torch_dtype
+  p = C.make_params(case)
+  inp = C.make_inputs(case)
+  pos = inp["segment_pos"]
+  out = {"input_checksum": np.float64(C.checksum({**p, **inp}))}
+
+  with torch.no_grad():
+    if case.kind == "blockdiag":
+      m = layers.BlockDiagonalLinear(case.lru_width, case.heads, dtype=dt)
+      m.load_state_dict({"w": p["rg_lru.input_gate.w"], "b": p["rg_lru.input_gate.b"]})
+      out["out"] = _np(m(inp["x"]))
+
+    elif case.kind == "conv1d":
+      m = layers.Conv1D(case.lru_width, case.temporal_width, dtype=dt)
+      m.load_state_dict({"w": p["conv_1d.w"], "b": p["conv_1d.b"]})
+      y, cache = m(inp["x"].clone(), pos)   # the reference masks its input in place
+      out["out"], out["cache"] = _np(y), _np(cache)
+      for i in range(case.decode_steps):
+        y, cache = m(inp[f"x_step{i}"].clone(), C.decode_positions(case, pos, i), cache)
+        out[f"out_step{i}"], out[f"cache_step{i}"] = _np(y), _np(cache)
+
+    elif case.kind == "rnn_scan":
+      y, h = layers.rnn_scan(inp["x"], inp["a"], pos == 0, inp["h0"])
+      out["out"], out["h"] = _np(y), _np(h)
+
+    elif case.kind == "rglru":
+      m = layers.RGLRU(case.lru_width, case.heads, dtype=dt)
+      m.load_state_dict({k[len("rg_lru."):]: v for k, v in p.items() if k.startswith("rg_lru.")})
+      y, h = m(inp["x"], pos, inp["h0"])
+      out["out"], out["h"] = _np(y), _np(h)
+      assert h.dtype == torch.float32
+      for i in range(case.decode_steps):
+        y, h = m(inp[f"x_step{i}"], C.decode_positions(case, pos, i), h)
+        out[f"out_step{i}"], out[f"h_step{i}"] = _np(y), _np(h)
+
+    elif case.kind == "block":
+      m = modules.RecurrentBlock(case.model_width, case.heads, case.lru_width,
+                                 case.temporal_width, dtype=dt)
+      m.load_state_dict(p)
+      y, cache = m(inp["x"], pos)
+      out["out"], out["h"], out["cache"] = _np(y), _np(cache.rg_lru_state), _np(cache.conv1d_state)
+      for i in range(case.decode_steps):
+        y, cache = m(inp[f"x_step{i}"], C.decode_positions(case, pos, i), cache)
+        out[f"out_step{i}"] = _np(y)
+        out[f"h_step{i}"] = _np(cache.rg_lru_state)
+        out[f"cache_step{i}"] = _np(cache.conv1d_state)
+    else:
+      raise ValueError(case.kind)
+  return out
+
+
+def main():
+  ap = argparse.ArgumentParser()
+  ap.add_argument("--reference", default="/root/reference")
+  args = ap.parse_args()
+  _, layers, modules = import_reference(args.reference)
+  total = 0
+  for case in C.golden_cases():
+    res = run_case(case, layers, modules)
+    path = os.path.join(HERE, case.name + ".npz")
+    np.savez_compressed(path, **res)
+    total += os.path.getsize(path)
+    print(f"{case.name:44s} {os.path.getsize(path)/1024:8.1f} KiB")
+  print(f"total {total/1024:.1f} KiB")
+
+
+if __name__ == "__main__":
+  main()

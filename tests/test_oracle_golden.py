@@ -1,0 +1,87 @@
+"""Pins the CPU oracle against outputs of the reference torch implementation (tests/golden/).
+
+The fixtures were produced by tests/golden/make_golden.py importing the reference itself.  The
+float32 oracle must reproduce them to 2e-6 (it differs from ATen only in summation order and in
+libm vs vectorised transcendental rounding); the bfloat16 oracle, which re-creates every
+intermediate rounding, to 1e-2 with at most a few elements off by one bfloat16 step.
+"""
+import pytest
+import torch
+
+from tests import cases as C
+from tests.util import assert_close, as_f32, load_golden
+
+CASES = C.golden_cases()
+ORACLE_TOL = {"float32": 2e-6, "bfloat16": 1e-2}
+
+
+def _frac_mismatch(out, ref) -> float:
+  o, r = as_f32(out), as_f32(ref)
+  return float((o != r).float().mean())
+
+
+@pytest.mark.parametrize("case", CASES, ids=[c.name for c in CASES])
+def test_oracle_matches_reference(case, oracle):
+  g = load_golden(case.name)
+  p = C.make_params(case)
+  inp = C.make_inputs(case)
+  assert abs(C.checksum({**p, **inp}) - float(g["input_checksum"])) <= 1e-6 * abs(
+      float(g["input_checksum"])), "seeded inputs differ from those the fixture was made with"
+  tol = ORACLE_TOL[case.dtype]
+  pos = inp["segment_pos"]
+  mism = []
+
+  def chk(out, key):
+    assert_close(out, g[key], tol, f"{case.name}:{key}")
+    mism.append(_frac_mismatch(out, g[key]))
+
+  if case.kind == "blockdiag":
+    chk(oracle.blockdiag_linear(inp["x"], p["rg_lru.input_gate.w"], p["rg_lru.input_gate.b"]),
+        "out")
+  elif case.kind == "conv1d":
+    y, cache = oracle.conv1d(inp["x"], pos, p["conv_1d.w"], p["conv_1d.b"])
+    chk(y, "out"); chk(cache, "cache")
+    for i in range(case.decode_steps):
+      y, cache = oracle.conv1d(inp[f"x_step{i}"], C.decode_positions(case, pos, i), p["conv_1d.w"],
+                               p["conv_1d.b"], cache)
+      chk(y, f"out_step{i}"); chk(cache, f"cache_step{i}")
+  elif case.kind == "rnn_scan":
+    y, h = oracle.rnn_scan(inp["x"], inp["a"], pos == 0, inp["h0"])
+    chk(y, "out"); chk(h, "h")
+  elif case.kind == "rglru":
+    args = (p["rg_lru.a_param"], p["rg_lru.input_gate.w"], p["rg_lru.input_gate.b"],
+            p["rg_lru.a_gate.w"], p["rg_lru.a_gate.b"])
+    y, h = oracle.rglru(inp["x"], pos, *args, inp["h0"])
+    chk(y, "out"); chk(h, "h")
+    for i in range(case.decode_steps):
+      y, h = oracle.rglru(inp[f"x_step{i}"], C.decode_positions(case, pos, i), *args, h)
+      chk(y, f"out_step{i}"); chk(h, f"h_step{i}")
+  elif case.kind == "block":
+    op = oracle.params_of(p)
+    y, h, cache = oracle.recurrent_block(inp["x"], pos, op)
+    chk(y, "out"); chk(h, "h"); chk(cache, "cache")
+    for i in range(case.decode_steps):
+      y, h, cache = oracle.recurrent_block(inp[f"x_step{i}"], C.decode_positions(case, pos, i), op,
+                                           h, cache)
+      chk(y, f"out_step{i}"); chk(h, f"h_step{i}"); chk(cache, f"cache_step{i}")
+  # bfloat16: the rounding model must hold almost everywhere, not merely within tolerance.
+  if case.dtype == "bfloat16":
+    assert max(mism) < 0.03, f"{case.name}: {max(mism):.3%} of elements differ from the reference"
+
+
+def test_prefill_state_equals_decode_state(oracle):
+  """prefill(T) == prefill(T-1) followed by one decode step (the sampler's contract,
+  torch/sampler_test.py:150-230), checked on the oracle itself."""
+  case = C.case_by_name("block_f32_128_h1_l256_multi")
+  p = oracle.params_of(C.make_params(case))
+  inp = C.make_inputs(case)
+  x, pos = inp["x"], inp["segment_pos"]
+  y_full, h_full, c_full = oracle.recurrent_block(x, pos, p)
+  _, h_a, c_a = oracle.recurrent_block(x[:, :-1].contiguous(), pos[:, :-1].contiguous(), p)
+  # the final position of this case starts no document, as in a decode continuation
+  keep = (pos[:, -1] != 0)
+  y_b, h_b, c_b = oracle.recurrent_block(x[:, -1:].contiguous(), pos[:, -1:].contiguous(), p, h_a,
+                                         c_a)
+  assert keep.any()
+  assert_close(h_b[keep], h_full[keep], 1e-6, "state")
+  assert_close(y_b[keep], y_full[keep][:, -1:], 1e-6, "last output")
