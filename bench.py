@@ -1,0 +1,377 @@
+"""Benchmark of the RG-LRU + Conv1D path at the 2B-dims prefill workload.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload ("cfg1"): the RG-LRU + Conv1D sub-path of RecurrentBlock prefill at RecurrentGemma-2B
+dimensions - batch 8, 4096 tokens, lru_width 2560, 10 heads, conv width 4, bfloat16 activations and
+parameters, float32 scan state, single segment per row.  A step is one pass of
+out = RGLRU(Conv1D(xb)) * gelu(yb) over that batch (xb, yb = the outputs of linear_x / linear_y,
+synthetic N(0,1)); `value` is tokens/s with inputs resident in HBM, `e2e` the same through the
+public API with pinned host buffers (host->device and device->host copies inside the timed
+region).  With N > 1 (torchrun, one process per GPU) every rank runs the whole workload on its own
+GPU - the path shards by batch without any collective - and `value` is the sum (weak scaling).
+
+`--impl reference` times the CPU restatement of the reference's own implementation of the same
+sub-path (oracle/, OpenMP over the host cores) on a bounded sample of the workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+  sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+METRIC = "rglru_conv1d_prefill_tokens_per_s"
+UNIT = "tokens/s"
+CFG1 = dict(batch=8, seq=4096, lru_width=2560, heads=10, conv_width=4)
+
+
+def _peaks():
+  path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+  if os.path.exists(path):
+    with open(path) as f:
+      d = json.load(f)
+    return float(d["hbm_gbs"]), float(d.get("bf16_tflops", 1590.0)), "measured"
+  return 6650.0, 1590.0, "fallback"
+
+
+def _workload_name(cfg):
+  return (f"cfg1: RG-LRU+Conv1D sub-path of RecurrentBlock prefill, B{cfg['batch']} T{cfg['seq']} "
+          f"E{cfg['lru_width']} H{cfg['heads']} W{cfg['conv_width']} bf16 (fp32 scan state)")
+
+
+# ------------------------------------------------------------------------------------------------
+# synthetic inputs (seeded; shapes and distributions of the workload)
+# ------------------------------------------------------------------------------------------------
+def make_params(cfg, device, seed):
+  import math
+  g = torch.Generator(device="cpu").manual_seed(seed)
+  e, h, w = cfg["lru_width"], cfg["heads"], cfg["conv_width"]
+  bw = e // h
+  dt = torch.bfloat16
+
+  def n(shape, std):
+    return (torch.randn(shape, generator=g) * std).to(dt).to(device)
+
+  u = torch.rand((e,), generator=g).double() * (0.999 ** 2 - 0.9 ** 2) + 0.9 ** 2
+  a_param = torch.log(torch.expm1(-0.5 * torch.log(u))).float().to(dt).to(device)
+  return {
+      "conv_1d.w": n((w, e), math.sqrt(1.0 / w)), "conv_1d.b": torch.zeros(e, dtype=dt, device=device),
+      "rg_lru.a_param": a_param,
+      "rg_lru.input_gate.w": n((h, bw, bw), math.sqrt(1.0 / bw)),
+      "rg_lru.input_gate.b": torch.zeros((h, bw), dtype=dt, device=device),
+      "rg_lru.a_gate.w": n((h, bw, bw), math.sqrt(1.0 / bw)),
+      "rg_lru.a_gate.b": torch.zeros((h, bw), dtype=dt, device=device),
+  }
+
+
+def make_activations(cfg, device, seed, batch=None):
+  b = batch or cfg["batch"]
+  g = torch.Generator(device="cpu").manual_seed(seed + 1)
+  shape = (b, cfg["seq"], cfg["lru_width"])
+  xb = torch.randn(shape, generator=g).to(torch.bfloat16)
+  yb = torch.randn(shape, generator=g).to(torch.bfloat16)
+  pos = torch.arange(cfg["seq"], dtype=torch.int64).repeat(b, 1)
+  if device != "cpu":
+    return xb.pin_memory(), yb.pin_memory(), pos.to(device)
+  return xb, yb, pos
+
+
+# ------------------------------------------------------------------------------------------------
+# clocks
+# ------------------------------------------------------------------------------------------------
+class ClockSampler:
+  FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+            "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+            "clocks_event_reasons.sw_power_cap")
+
+  def __init__(self, index: int):
+    self.index = index
+    self.proc = None
+    self.path = f"/tmp/rgk_clocks_{os.getpid()}.csv"
+
+  def start(self):
+    try:
+      self.out = open(self.path, "w")
+      self.proc = subprocess.Popen(
+          ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms",
+           "50", "-i", str(self.index)], stdout=self.out, stderr=subprocess.DEVNULL)
+    except OSError:
+      self.proc = None
+
+  def stop(self):
+    res = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+    if self.proc is None:
+      return res
+    time.sleep(0.12)
+    self.proc.terminate()
+    try:
+      self.proc.wait(timeout=5)
+    except subprocess.TimeoutExpired:
+      self.proc.kill()
+    self.out.close()
+    sm, mx, reasons = [], [], set()
+    names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+    try:
+      with open(self.path) as f:
+        for line in f:
+          parts = [p.strip() for p in line.split(",")]
+          if len(parts) < 7:
+            continue
+          try:
+            sm.append(float(parts[0])); mx.append(float(parts[1]))
+          except ValueError:
+            continue
+          for nme, val in zip(names, parts[3:7]):
+            if val == "Active":
+              reasons.add(nme)
+      os.remove(self.path)
+    except OSError:
+      pass
+    if sm:
+      res.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons),
+                 samples=len(sm))
+    return res
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU legs (the oracle: the reference's algorithm restated in C, OpenMP over the host cores)
+# ------------------------------------------------------------------------------------------------
+def cpu_leg(cfg, steps, warmup, sample_batch=1):
+  from oracle import oracle
+  oracle.lib()
+  p = make_params(cfg, "cpu", 1)
+  op = oracle.params_of(p)
+  xb, yb, pos = make_activations(cfg, "cpu", 1, batch=sample_batch)
+  times = []
+  for i in range(warmup + steps):
+    t0 = time.perf_counter()
+    oracle.recurrent_path(xb, yb, pos, op)
+    if i >= warmup:
+      times.append(time.perf_counter() - t0)
+  tokens = sample_batch * cfg["seq"]
+  best = min(times)
+  mean = sum(times) / len(times)
+  return {
+      "value": tokens / mean, "best": tokens / best, "unit": UNIT, "cores": os.cpu_count(),
+      "kind": "port",
+      "sample": (f"oracle/rglru_oracle.c recurrent_path (OpenMP, {os.cpu_count()} threads) on "
+                 f"{sample_batch} of {cfg['batch']} batch rows x {cfg['seq']} tokens x "
+                 f"{cfg['lru_width']} channels, mean of {steps} after {warmup} warm-up"),
+      "seconds_per_sample": mean,
+  }
+
+
+def run_reference(args, cfg):
+  rank = int(os.environ.get("RANK", "0"))
+  if rank != 0:
+    return
+  steps = max(1, min(args.steps, 5))
+  warmup = max(1, min(args.warmup, 1))
+  leg = cpu_leg(cfg, steps, warmup)
+  line = {
+      "impl": "reference", "metric": METRIC, "value": leg["value"], "unit": UNIT,
+      "n_gpus": args.gpus, "steps": steps, "warmup": warmup,
+      "ms_per_step": leg["seconds_per_sample"] * 1e3, "higher_is_better": True, "scaling": "weak",
+      "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+      "config": {"workload": _workload_name(cfg), "step": leg["sample"]},
+      "cpu_baseline": {k: leg[k] for k in ("value", "unit", "cores", "kind", "sample")},
+      "e2e": {"value": leg["value"], "unit": UNIT, "h2d_bytes_per_step": 0,
+              "d2h_bytes_per_step": 0},
+  }
+  print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------------
+def _time_loop(fn, steps, stream):
+  ev0 = torch.cuda.Event(enable_timing=True)
+  ev1 = torch.cuda.Event(enable_timing=True)
+  ev0.record(stream)
+  for _ in range(steps):
+    fn()
+  ev1.record(stream)
+  ev1.synchronize()
+  return ev0.elapsed_time(ev1) / steps  # ms per call
+
+
+def run_gpu(args, cfg):
+  import torch.distributed as dist
+  import recurrentgemma_b200 as rg
+  from recurrentgemma_b200 import _lib
+
+  rank = int(os.environ.get("RANK", "0"))
+  world = int(os.environ.get("WORLD_SIZE", "1"))
+  local = int(os.environ.get("LOCAL_RANK", "0"))
+  if world != args.gpus:
+    if world == 1 and args.gpus > 1:
+      raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run, one rank per GPU")
+  torch.cuda.set_device(local)
+  dev = torch.device("cuda", local)
+  if world > 1:
+    dist.init_process_group("nccl", device_id=dev)
+  lib = _lib.load()
+  _lib.check(lib.rgk_device_check())
+
+  b, t, e, h = cfg["batch"], cfg["seq"], cfg["lru_width"], cfg["heads"]
+  dt = torch.bfloat16
+  p = make_params(cfg, dev, 1 + rank)
+  conv = rg.Conv1D(e, 4, device=dev, dtype=dt)
+  conv.load_state_dict({"w": p["conv_1d.w"], "b": p["conv_1d.b"]})
+  lru = rg.RGLRU(e, h, device=dev, dtype=dt)
+  lru.load_state_dict({k[len("rg_lru."):]: v for k, v in p.items() if k.startswith("rg_lru.")})
+  xb_h, yb_h, pos = make_activations(cfg, dev, 1 + rank)
+  xb, yb = xb_h.to(dev), yb_h.to(dev)
+  out = torch.empty_like(xb)
+  out_h = torch.empty_like(xb_h).pin_memory()
+  stream = torch.cuda.current_stream(dev)
+
+  def step():
+    rg.recurrent_path(xb, yb, pos, conv, lru, out=out)
+
+  def step_e2e():
+    xd = xb_h.to(dev, non_blocking=True)
+    yd = yb_h.to(dev, non_blocking=True)
+    o, cache = rg.recurrent_path(xd, yd, pos, conv, lru)
+    out_h.copy_(o, non_blocking=True)
+    cache.rg_lru_state.cpu()   # the step's state read back: also orders the step on the host
+
+  for _ in range(max(args.warmup, 3)):
+    step()
+  torch.cuda.synchronize()
+  _lib.workspace_status(_lib.workspace(dev, 1))
+
+  clocks = ClockSampler(local)
+  if rank == 0:
+    clocks.start()
+  if world > 1:
+    dist.barrier()
+  torch.cuda.synchronize()
+  ms = _time_loop(step, args.steps, stream)
+  torch.cuda.synchronize()
+  if world > 1:
+    tmax = torch.tensor([ms], device=dev)
+    dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+    dist.barrier()
+    ms = float(tmax.item())
+  clk = clocks.stop() if rank == 0 else None
+
+  # end to end through the public API, host buffers
+  e2e_ms = None
+  if not args.no_e2e:
+    e2e_steps = max(2, min(args.steps, 10))
+    for _ in range(2):
+      step_e2e()
+    torch.cuda.synchronize()
+    if world > 1:
+      dist.barrier()
+    t0 = time.perf_counter()
+    ev_ms = _time_loop(step_e2e, e2e_steps, stream)
+    torch.cuda.synchronize()
+    wall_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+    e2e_ms = max(ev_ms, wall_ms)
+    if world > 1:
+      tmax = torch.tensor([e2e_ms], device=dev)
+      dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+      e2e_ms = float(tmax.item())
+
+  # per-kernel device times, each through its own entry point (CUDA events on the launch stream)
+  kernels = {}
+  if rank == 0:
+    n_el = b * t * e
+    es = 2
+    c = torch.empty_like(xb)
+    ksteps = max(3, min(args.steps, 20))
+    kernels["conv1d_prefill"] = {
+        "ms": _time_loop(lambda: conv(xb, pos), ksteps, stream), "bytes": 2 * n_el * es,
+        "flops": 8 * n_el}
+    c, _ = conv(xb, pos)
+    gw = p["rg_lru.input_gate.w"].numel() * es
+    a_t = torch.rand_like(c.float()).mul_(0.4).add_(0.6).to(dt)
+    kernels["scan_gelu"] = {
+        "ms": _time_loop(lambda: rg.rnn_scan(c, a_t, pos == -1, None, y_mul=yb), ksteps, stream),
+        "bytes": 4 * n_el * es, "flops": 12 * n_el}
+    # the gate projections + gate arithmetic are timed as (RGLRU forward) - (scan without join)
+    t_lru = _time_loop(lambda: lru(c, pos), ksteps, stream)
+    t_scan_plain = _time_loop(lambda: rg.rnn_scan(c, a_t, pos == -1, None), ksteps, stream)
+    kernels["gates"] = {"ms": max(t_lru - t_scan_plain, 1e-6), "bytes": 3 * n_el * es + 2 * gw,
+                        "flops": 2 * 2 * b * t * e * (e // h)}
+    del a_t, c
+
+  if rank != 0:
+    if world > 1:
+      dist.destroy_process_group()
+    return
+
+  hbm_gbs, bf16_tf, which = _peaks()
+  tokens = b * t
+  value = world * tokens / (ms * 1e-3)
+  for k in kernels.values():
+    k["gbs"] = k["bytes"] / (k["ms"] * 1e-3) / 1e9
+    k["tflops"] = k["flops"] / (k["ms"] * 1e-3) / 1e12
+  dom_name = max(kernels, key=lambda k: kernels[k]["ms"])
+  dom = kernels[dom_name]
+  path_bytes = 3 * b * t * e * 2 + 2 * p["rg_lru.input_gate.w"].numel() * 2
+  roofline = {
+      "bound": "hbm", "kernel": dom_name, "achieved": dom["gbs"], "peak": hbm_gbs, "unit": "GB/s",
+      "frac": dom["gbs"] / hbm_gbs, "peak_source": which, "traffic": None,
+      "path": {"algorithmic_bytes": path_bytes, "achieved": path_bytes / (ms * 1e-3) / 1e9,
+               "frac": path_bytes / (ms * 1e-3) / 1e9 / hbm_gbs,
+               "frac_of_nominal_8TBs": path_bytes / (ms * 1e-3) / 1e9 / 8000.0},
+      "kernels": {k: {"ms": round(v["ms"], 4), "GB/s": round(v["gbs"], 1),
+                      "TFLOP/s": round(v["tflops"], 2)} for k, v in kernels.items()},
+  }
+  cpu = None if args.no_cpu else cpu_leg(cfg, 2, 1)
+  line = {
+      "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+      "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+      "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+      "config": {"workload": _workload_name(cfg), "per_gpu_batch": b, "seq_len": t,
+                 "parallelism": f"batch-sharded x{world}, no collective",
+                 "cache": "inputs (336 MB) larger than L2 (126 MB); no flush"},
+      "roofline": roofline,
+      "cpu_baseline": None if cpu is None else {k: cpu[k] for k in
+                                                ("value", "unit", "cores", "kind", "sample")},
+      "clocks": clk,
+      "gpu_launches": 3 * args.steps,
+  }
+  if e2e_ms is not None:
+    line["e2e"] = {"value": world * tokens / (e2e_ms * 1e-3), "unit": UNIT,
+                   "h2d_bytes_per_step": 2 * b * t * e * 2, "d2h_bytes_per_step": b * t * e * 2 + b * e * 4,
+                   "ms_per_step": e2e_ms}
+  print(json.dumps(line), flush=True)
+  if world > 1:
+    dist.destroy_process_group()
+
+
+def main():
+  ap = argparse.ArgumentParser()
+  ap.add_argument("--gpus", type=int, default=1)
+  ap.add_argument("--steps", type=int, default=20)
+  ap.add_argument("--warmup", type=int, default=3)
+  ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+  ap.add_argument("--batch", type=int, default=None, help="override the per-GPU batch (profiling)")
+  ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+  ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg")
+  args = ap.parse_args()
+  cfg = dict(CFG1)
+  if args.batch:
+    cfg["batch"] = args.batch
+  if args.impl == "reference":
+    run_reference(args, cfg)
+  else:
+    run_gpu(args, cfg)
+
+
+if __name__ == "__main__":
+  main()

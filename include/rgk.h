@@ -1,0 +1,170 @@
+/*
+ * rgk.h - C ABI of librgk.so: the RG-LRU + Conv1D path of recurrentgemma's torch implementation
+ * as hand-written CUDA for sm_100a (NVIDIA B200).
+ *
+ * The reference is pure Python and has no FFI; the interface each entry point replaces is the
+ * Python method cited beside it (paths inside the recurrentgemma checkout).  All pointers are
+ * DEVICE pointers unless stated otherwise; tensors are dense, row-major and contiguous; nothing is
+ * allocated, freed or retained by the library (scratch comes from the caller, see
+ * rgk_workspace_bytes).  Every call only enqueues work on `stream` (a cudaStream_t) and returns
+ * 0 or a negative rgk_status; it never synchronises, throws or exits.  There is no CPU path: on a
+ * device that is not compute capability 10.x every call returns RGK_EARCH.
+ *
+ * dtype: activations and parameters are either all float32 or all bfloat16 (RGK_F32 / RGK_BF16).
+ * In RGK_BF16 the kernels round after every tensor-level operation of the reference, as torch
+ * does for bfloat16 tensors.  The recurrence state is float32 in both (torch/layers.py:146, 376).
+ * segment_pos is int32 or int64 (RGK_I32 / RGK_I64); a value of 0 marks the first token of a
+ * document (torch/layers.py:335), negative values (left padding, torch/sampler.py:235-238) are
+ * ordinary non-zero positions.
+ */
+#ifndef RGK_H_
+#define RGK_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RGK_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define RGK_API __attribute__((visibility("default")))
+#else
+#define RGK_API
+#endif
+
+typedef enum rgk_status {
+  RGK_OK = 0,
+  RGK_EINVAL = -1,     /* null pointer, negative size, unknown enum */
+  RGK_ESHAPE = -2,     /* shape the kernels do not cover (message says which) */
+  RGK_EALIGN = -3,     /* pointer not 16-byte aligned */
+  RGK_EARCH = -4,      /* current device is not sm_100 */
+  RGK_ECUDA = -5,      /* a CUDA runtime call failed (message holds cudaGetErrorString) */
+  RGK_EWORKSPACE = -6, /* workspace missing or too small */
+  RGK_ETIMEOUT = -7    /* a bounded device-side wait expired (reported by rgk_workspace_status) */
+} rgk_status;
+
+enum { RGK_F32 = 0, RGK_BF16 = 1 };
+enum { RGK_I32 = 0, RGK_I64 = 1 };
+
+/* Which kernels a composed call may use for the block-diagonal gate projections. */
+enum {
+  RGK_GATES_AUTO = 0,   /* tcgen05 kernel when dtype is bf16 and the head width is 256 */
+  RGK_GATES_SIMT = 1,   /* CUDA-core kernel (any head width that is a multiple of 16; float32) */
+  RGK_GATES_TCGEN05 = 2 /* tensor-core kernel; RGK_ESHAPE if the shape is not covered */
+};
+
+RGK_API int rgk_abi_version(void);
+
+/* Thread-local text of the last failure on the calling host thread ("" if none). */
+RGK_API const char* rgk_last_error(void);
+
+/* RGK_OK if the current CUDA device can run this library, else RGK_EARCH / RGK_ECUDA. */
+RGK_API int rgk_device_check(void);
+
+/* ------------------------------------------------------------------------------------------------
+ * Conv1D.forward, prefill form (cache is None)                    torch/layers.py:447-529
+ *   x [B,T,E], segment_pos [B,T], w [W,E], b [E]  ->  out [B,T,E], cache_out [B,W-1,E] or NULL
+ * Causal depthwise convolution whose taps do not cross a document start; cache_out receives the
+ * last W-1 input rows as the reference leaves them (masked by later document starts, zero where
+ * T < W-1).  W must be 4.  x is not modified.
+ * ---------------------------------------------------------------------------------------------- */
+RGK_API int rgk_conv1d_prefill(const void* x, const void* segment_pos, int pos_dtype, const void* w,
+                       const void* b, int64_t B, int64_t T, int64_t E, int W, int dtype, void* out,
+                       void* cache_out, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Conv1D.forward, decode form (cache given, T == 1)               torch/layers.py:469-474, 531-550
+ *   x [B,E], cache_in [B,W-1,E]  ->  out [B,E], cache_out [B,W-1,E] (may alias cache_in) or NULL
+ * No document masking in this form.  W must be 4.
+ * ---------------------------------------------------------------------------------------------- */
+RGK_API int rgk_conv1d_decode(const void* x, const void* cache_in, const void* w, const void* b, int64_t B,
+                      int64_t E, int W, int dtype, void* out, void* cache_out, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * BlockDiagonalLinear.forward                                      torch/layers.py:127-137
+ *   x [M, H*bw], w [H, bw(in), bw(out)], b [H, bw]  ->  out [M, H*bw]
+ * ---------------------------------------------------------------------------------------------- */
+RGK_API int rgk_blockdiag_linear(const void* x, const void* w, const void* b, int64_t M, int H, int bw,
+                         int dtype, void* out, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * rnn_scan                                                         torch/layers.py:140-191
+ *   x, a [B,T,E] (dtype), reset [B,T] uint8 (non-zero = reset), h0 [B,E] float32 or NULL
+ *   ->  y [B,T,E] (dtype), h_last [B,E] float32 or NULL
+ * h_t = (a_t * !reset_t) * h_{t-1} + x_t in float32; with T == 1 and h0 == NULL the output is x
+ * (torch/layers.py:172-173).  y_mul (optional, [B,T,E]) fuses RecurrentBlock's join
+ * (torch/modules.py:627-628, 646): y <- y * gelu_tanh(y_mul).
+ * workspace: rgk_workspace_bytes(B, T, E, dtype) bytes, 256-byte aligned; reused freely between
+ * calls that do not overlap on the device.
+ * ---------------------------------------------------------------------------------------------- */
+RGK_API int rgk_linear_scan(const void* x, const void* a, const uint8_t* reset, const float* h0,
+                    const void* y_mul, int64_t B, int64_t T, int64_t E, int dtype, void* y,
+                    float* h_last, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Parameters of one recurrent block's RG-LRU + Conv1D, as the reference state_dict holds them
+ * (torch/layers.py:105-112, 262-278, 409-412).
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct rgk_params {
+  const void* conv_w;    /* conv_1d.w            [W, E]            */
+  const void* conv_b;    /* conv_1d.b            [E]               */
+  const void* a_param;   /* rg_lru.a_param       [E]               */
+  const void* gate_x_w;  /* rg_lru.input_gate.w  [H, E/H, E/H] (in, out) */
+  const void* gate_x_b;  /* rg_lru.input_gate.b  [H, E/H]          */
+  const void* gate_a_w;  /* rg_lru.a_gate.w      [H, E/H, E/H]     */
+  const void* gate_a_b;  /* rg_lru.a_gate.b      [H, E/H]          */
+} rgk_params;
+
+/* ------------------------------------------------------------------------------------------------
+ * RGLRU.forward                                                    torch/layers.py:313-365
+ *   x [B,T,E], segment_pos [B,T], h0 [B,E] float32 or NULL
+ *   ->  y [B,T,E], h_last [B,E] float32 or NULL
+ * Uses a_param and the two gate projections of `p` (conv_w / conv_b are ignored).  Any T >= 1;
+ * T == 1 follows the sampling branch of rnn_scan (new state = unrounded float32).
+ * ---------------------------------------------------------------------------------------------- */
+RGK_API int rgk_rglru_forward(const void* x, const void* segment_pos, int pos_dtype, const rgk_params* p,
+                      const float* h0, int64_t B, int64_t T, int64_t E, int H, int dtype,
+                      int gates_impl, void* y, float* h_last, void* workspace,
+                      size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * The RG-LRU + Conv1D sub-path of RecurrentBlock.forward           torch/modules.py:631-646
+ *   prefill:  out = RGLRU(Conv1D(xb)) * gelu_tanh(yb)     (yb NULL: no join, out = RGLRU(Conv1D(xb)))
+ *   xb, yb [B,T,E] = linear_x(x), linear_y(x);  h0 [B,E] float32 or NULL
+ *   ->  out [B,T,E], h_last [B,E] float32 or NULL, conv_cache_out [B,W-1,E] or NULL
+ * ---------------------------------------------------------------------------------------------- */
+RGK_API int rgk_recurrent_path_prefill(const void* xb, const void* yb, const void* segment_pos,
+                               int pos_dtype, const rgk_params* p, const float* h0, int64_t B,
+                               int64_t T, int64_t E, int H, int W, int dtype, int gates_impl,
+                               void* out, float* h_last, void* conv_cache_out, void* workspace,
+                               size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * The same sub-path for one decode step (T == 1 with caches)       torch/modules.py:631-646,
+ *   xb, yb [B,E]; conv_cache_in [B,W-1,E]; h_in [B,E] float32     torch/layers.py:170-177, 469-474
+ *   ->  out [B,E], h_out [B,E] float32, conv_cache_out [B,W-1,E]
+ * h_out may alias h_in and conv_cache_out may alias conv_cache_in (in-place state update).
+ * segment_pos [B] still selects the reset behaviour of the RG-LRU (a position of 0 drops h_in).
+ * ---------------------------------------------------------------------------------------------- */
+RGK_API int rgk_recurrent_path_decode(const void* xb, const void* yb, const void* segment_pos,
+                              int pos_dtype, const rgk_params* p, const float* h_in,
+                              const void* conv_cache_in, int64_t B, int64_t E, int H, int W,
+                              int dtype, int gates_impl, void* out, float* h_out,
+                              void* conv_cache_out, void* workspace, size_t workspace_bytes,
+                              void* stream);
+
+/* Scratch needed by the calls above for a problem of this size (an upper bound over the entry
+ * points, so one buffer serves all of them).  Returns 0 on invalid arguments. */
+RGK_API size_t rgk_workspace_bytes(int64_t B, int64_t T, int64_t E, int dtype);
+
+/* Copies the status word the kernels of the last call on `workspace` left behind to the host
+ * (synchronises `stream`).  RGK_OK, or RGK_ETIMEOUT if a bounded device-side wait gave up. */
+RGK_API int rgk_workspace_status(const void* workspace, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RGK_H_ */

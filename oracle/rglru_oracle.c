@@ -75,23 +75,31 @@ RGO_API int rgo_version(void) { return 1; }
 RGO_API void rgo_blockdiag_linear(const float* x, const float* w, const float* b, int64_t M,
                                   int H, int bw, int dt, float* out) {
   const int64_t E = (int64_t)H * bw;
+  enum { RB = 8 }; /* rows that share one pass over a head's weights */
+  const int64_t n_rb = (M + RB - 1) / RB;
 #pragma omp parallel for collapse(2) schedule(static)
-  for (int64_t m = 0; m < M; ++m) {
+  for (int64_t rb = 0; rb < n_rb; ++rb) {
     for (int h = 0; h < H; ++h) {
-      float acc[1024];
-      float* accp = bw <= 1024 ? acc : (float*)malloc(sizeof(float) * (size_t)bw);
-      for (int j = 0; j < bw; ++j) accp[j] = 0.0f;
-      const float* xr = x + m * E + (int64_t)h * bw;
+      const int64_t m0 = rb * RB;
+      const int rows = (int)((M - m0) < RB ? (M - m0) : RB);
+      float* acc = (float*)malloc(sizeof(float) * (size_t)RB * (size_t)bw);
+      for (int i = 0; i < RB * bw; ++i) acc[i] = 0.0f;
       const float* wh = w + (int64_t)h * bw * bw;
       for (int i = 0; i < bw; ++i) {
-        const float xi = xr[i];
         const float* wr = wh + (int64_t)i * bw;
-        for (int j = 0; j < bw; ++j) accp[j] += xi * wr[j];
+        for (int r = 0; r < rows; ++r) {
+          const float xi = x[(m0 + r) * E + (int64_t)h * bw + i];
+          float* ar = acc + (size_t)r * bw;
+          for (int j = 0; j < bw; ++j) ar[j] += xi * wr[j];
+        }
       }
-      float* o = out + m * E + (int64_t)h * bw;
       const float* bh = b + (int64_t)h * bw;
-      for (int j = 0; j < bw; ++j) o[j] = rnd(rnd(accp[j], dt) + bh[j], dt);
-      if (accp != acc) free(accp);
+      for (int r = 0; r < rows; ++r) {
+        float* o = out + (m0 + r) * E + (int64_t)h * bw;
+        const float* ar = acc + (size_t)r * bw;
+        for (int j = 0; j < bw; ++j) o[j] = rnd(rnd(ar[j], dt) + bh[j], dt);
+      }
+      free(acc);
     }
   }
 }

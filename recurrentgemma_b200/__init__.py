@@ -1,0 +1,13 @@
+"""B200-native (sm_100a) RG-LRU + Conv1D path for recurrentgemma's torch models.
+
+The public names mirror `recurrentgemma.torch` for the modules on that path; `dropin` swaps them
+into a reference `Griffin`.  Importing the package does not load the CUDA library; the first
+forward does, and raises if it has not been built.
+"""
+from recurrentgemma_b200.layers import BlockDiagonalLinear, Conv1D, RGLRU, rnn_scan
+from recurrentgemma_b200.modules import RecurrentBlock, RecurrentBlockCache, recurrent_path
+
+__all__ = [
+    "BlockDiagonalLinear", "Conv1D", "RGLRU", "rnn_scan", "RecurrentBlock", "RecurrentBlockCache",
+    "recurrent_path",
+]

@@ -1,0 +1,338 @@
+// extern "C" surface of librgk (include/rgk.h): argument validation, error text, workspace carving
+// and the composition of the kernels into the calls the reference's Python methods map to.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "../../include/rgk.h"
+#include "rgk_common.cuh"
+#include "rgk_internal.h"
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+  return fail(RGK_ECUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+size_t up256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
+
+int elem_size(int dtype) { return dtype == RGK_BF16 ? 2 : 4; }
+
+// Compute capability of each device, looked up once (immutable afterwards).
+int device_ok() {
+  static int cached[64];  // 0 unknown, 1 ok, -1 wrong arch
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+  if (dev >= 0 && dev < 64 && cached[dev] == 1) return RGK_OK;
+  int major = 0;
+  e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute");
+  if (major != 10) {
+    return fail(RGK_EARCH, "device %d has compute capability %d.x; librgk is built for sm_100a only",
+                dev, major);
+  }
+  if (dev >= 0 && dev < 64) cached[dev] = 1;
+  return RGK_OK;
+}
+
+#define RGK_REQUIRE(cond, code, ...) \
+  do {                               \
+    if (!(cond)) return fail(code, __VA_ARGS__); \
+  } while (0)
+
+#define RGK_CHECK_DEVICE()          \
+  do {                              \
+    int rc_ = device_ok();          \
+    if (rc_ != RGK_OK) return rc_;  \
+  } while (0)
+
+#define RGK_CUDA(expr, what)                              \
+  do {                                                    \
+    cudaError_t e_ = (expr);                              \
+    if (e_ != cudaSuccess) return cuda_fail(e_, what);    \
+  } while (0)
+
+int check_common(int64_t B, int64_t T, int64_t E, int dtype) {
+  RGK_REQUIRE(dtype == RGK_F32 || dtype == RGK_BF16, RGK_EINVAL, "unknown dtype %d", dtype);
+  RGK_REQUIRE(B >= 0 && T >= 0 && E >= 0, RGK_EINVAL, "negative size (B=%lld T=%lld E=%lld)",
+              (long long)B, (long long)T, (long long)E);
+  const int pack = dtype == RGK_BF16 ? 8 : 4;
+  RGK_REQUIRE(E % pack == 0, RGK_ESHAPE, "width %lld is not a multiple of %d (16-byte channel packs)",
+              (long long)E, pack);
+  RGK_REQUIRE(B <= 65535, RGK_ESHAPE, "batch %lld exceeds 65535", (long long)B);
+  RGK_REQUIRE(T <= (1 << 21), RGK_ESHAPE, "sequence length %lld exceeds 2^21", (long long)T);
+  RGK_REQUIRE(E <= (1 << 20), RGK_ESHAPE, "width %lld exceeds 2^20", (long long)E);
+  return RGK_OK;
+}
+
+int check_heads(int64_t E, int H) {
+  RGK_REQUIRE(H >= 1 && E % H == 0, RGK_ESHAPE, "width %lld is not divisible by %d heads",
+              (long long)E, H);
+  RGK_REQUIRE((E / H) % 16 == 0, RGK_ESHAPE, "head width %lld is not a multiple of 16",
+              (long long)(E / H));
+  return RGK_OK;
+}
+
+int check_params(const rgk_params* p, bool need_conv) {
+  RGK_REQUIRE(p != nullptr, RGK_EINVAL, "params is NULL");
+  RGK_REQUIRE(p->a_param && p->gate_x_w && p->gate_x_b && p->gate_a_w && p->gate_a_b, RGK_EINVAL,
+              "a gate parameter pointer is NULL");
+  RGK_REQUIRE(!need_conv || (p->conv_w && p->conv_b), RGK_EINVAL, "conv parameter pointer is NULL");
+  RGK_REQUIRE(aligned16(p->a_param) && aligned16(p->gate_x_w) && aligned16(p->gate_x_b) &&
+                  aligned16(p->gate_a_w) && aligned16(p->gate_a_b) &&
+                  (!need_conv || (aligned16(p->conv_w) && aligned16(p->conv_b))),
+              RGK_EALIGN, "parameter pointers must be 16-byte aligned");
+  return RGK_OK;
+}
+
+// Carves the workspace of the composed calls: [scan scratch | c | a | xn].
+struct PathWs {
+  void* scan;
+  void* c;
+  void* a;
+  void* xn;
+  size_t total;
+};
+
+PathWs carve(void* ws, int64_t B, int64_t T, int64_t E, int dtype) {
+  PathWs w;
+  const size_t scan_bytes = rgk::scan_workspace_bytes(B, T, E, dtype);
+  const size_t act = up256(static_cast<size_t>(B) * T * E * elem_size(dtype));
+  char* base = static_cast<char*>(ws);
+  w.scan = base;
+  w.c = base ? base + scan_bytes : nullptr;
+  w.a = base ? base + scan_bytes + act : nullptr;
+  w.xn = base ? base + scan_bytes + 2 * act : nullptr;
+  w.total = scan_bytes + 3 * act;
+  return w;
+}
+
+}  // namespace
+
+extern "C" {
+
+int rgk_abi_version(void) { return RGK_ABI_VERSION; }
+
+const char* rgk_last_error(void) { return g_err; }
+
+int rgk_device_check(void) { return device_ok(); }
+
+size_t rgk_workspace_bytes(int64_t B, int64_t T, int64_t E, int dtype) {
+  if (B < 0 || T < 0 || E < 0 || (dtype != RGK_F32 && dtype != RGK_BF16)) return 0;
+  if (T < 1) T = 1;
+  return carve(nullptr, B, T, E, dtype).total;
+}
+
+int rgk_workspace_status(const void* workspace, void* stream) {
+  RGK_REQUIRE(workspace != nullptr, RGK_EINVAL, "workspace is NULL");
+  int status = 0;
+  RGK_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)), "cudaStreamSynchronize");
+  RGK_CUDA(cudaMemcpy(&status, workspace, sizeof(int), cudaMemcpyDeviceToHost), "cudaMemcpy");
+  if (status == rgk::kStatusTimeout)
+    return fail(RGK_ETIMEOUT, "a bounded device-side wait expired; results of that call are invalid");
+  return RGK_OK;
+}
+
+int rgk_conv1d_prefill(const void* x, const void* segment_pos, int pos_dtype, const void* w,
+                       const void* b, int64_t B, int64_t T, int64_t E, int W, int dtype, void* out,
+                       void* cache_out, void* stream) {
+  int rc = check_common(B, T, E, dtype);
+  if (rc) return rc;
+  RGK_REQUIRE(W == 4, RGK_ESHAPE, "temporal width %d is not supported (only 4)", W);
+  RGK_REQUIRE(pos_dtype == RGK_I32 || pos_dtype == RGK_I64, RGK_EINVAL, "unknown index dtype");
+  RGK_REQUIRE(x && segment_pos && w && b && out, RGK_EINVAL, "NULL pointer argument");
+  RGK_REQUIRE(aligned16(x) && aligned16(w) && aligned16(b) && aligned16(out) && aligned16(cache_out),
+              RGK_EALIGN, "pointers must be 16-byte aligned");
+  RGK_CHECK_DEVICE();
+  RGK_CUDA(rgk::launch_conv1d_prefill(x, segment_pos, pos_dtype, w, b, B, T, E, dtype, out,
+                                      cache_out, static_cast<cudaStream_t>(stream)),
+           "conv1d_prefill launch");
+  if (T == 0 && cache_out && B * E > 0)
+    RGK_CUDA(cudaMemsetAsync(cache_out, 0, (size_t)B * 3 * E * elem_size(dtype),
+                             static_cast<cudaStream_t>(stream)), "cudaMemsetAsync");
+  return RGK_OK;
+}
+
+int rgk_conv1d_decode(const void* x, const void* cache_in, const void* w, const void* b, int64_t B,
+                      int64_t E, int W, int dtype, void* out, void* cache_out, void* stream) {
+  int rc = check_common(B, 1, E, dtype);
+  if (rc) return rc;
+  RGK_REQUIRE(W == 4, RGK_ESHAPE, "temporal width %d is not supported (only 4)", W);
+  RGK_REQUIRE(x && cache_in && w && b && out, RGK_EINVAL, "NULL pointer argument");
+  RGK_REQUIRE(aligned16(x) && aligned16(cache_in) && aligned16(w) && aligned16(b) &&
+                  aligned16(out) && aligned16(cache_out),
+              RGK_EALIGN, "pointers must be 16-byte aligned");
+  RGK_CHECK_DEVICE();
+  RGK_CUDA(rgk::launch_conv1d_decode(x, cache_in, w, b, B, E, dtype, out, cache_out,
+                                     static_cast<cudaStream_t>(stream)),
+           "conv1d_decode launch");
+  return RGK_OK;
+}
+
+int rgk_blockdiag_linear(const void* x, const void* w, const void* b, int64_t M, int H, int bw,
+                         int dtype, void* out, void* stream) {
+  RGK_REQUIRE(dtype == RGK_F32 || dtype == RGK_BF16, RGK_EINVAL, "unknown dtype %d", dtype);
+  RGK_REQUIRE(M >= 0 && H >= 1 && bw >= 1, RGK_EINVAL, "bad size (M=%lld H=%d bw=%d)", (long long)M,
+              H, bw);
+  RGK_REQUIRE(bw % 16 == 0, RGK_ESHAPE, "head width %d is not a multiple of 16", bw);
+  RGK_REQUIRE(M <= (int64_t)0x7fffffff * 64, RGK_ESHAPE, "too many rows");
+  RGK_REQUIRE(x && w && b && out, RGK_EINVAL, "NULL pointer argument");
+  RGK_CHECK_DEVICE();
+  RGK_CUDA(rgk::launch_blockdiag_linear_simt(x, w, b, M, H, bw, dtype, out,
+                                             static_cast<cudaStream_t>(stream)),
+           "blockdiag_linear launch");
+  return RGK_OK;
+}
+
+int rgk_linear_scan(const void* x, const void* a, const uint8_t* reset, const float* h0,
+                    const void* y_mul, int64_t B, int64_t T, int64_t E, int dtype, void* y,
+                    float* h_last, void* workspace, size_t workspace_bytes, void* stream) {
+  int rc = check_common(B, T, E, dtype);
+  if (rc) return rc;
+  RGK_REQUIRE(x && a && y, RGK_EINVAL, "NULL pointer argument");
+  RGK_REQUIRE(aligned16(x) && aligned16(a) && aligned16(y) && aligned16(y_mul) && aligned16(h0) &&
+                  aligned16(h_last),
+              RGK_EALIGN, "pointers must be 16-byte aligned");
+  if (B * T * E == 0) return RGK_OK;
+  const size_t need = rgk::scan_workspace_bytes(B, T, E, dtype);
+  RGK_REQUIRE(workspace != nullptr && workspace_bytes >= need, RGK_EWORKSPACE,
+              "workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+  RGK_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255u) == 0, RGK_EALIGN,
+              "workspace must be 256-byte aligned");
+  RGK_CHECK_DEVICE();
+  RGK_CUDA(rgk::launch_scan(x, a, reset, nullptr, 0, h0, y_mul, B, T, E, dtype, y, h_last,
+                            workspace, static_cast<cudaStream_t>(stream)),
+           "scan launch");
+  return RGK_OK;
+}
+
+int rgk_rglru_forward(const void* x, const void* segment_pos, int pos_dtype, const rgk_params* p,
+                      const float* h0, int64_t B, int64_t T, int64_t E, int H, int dtype,
+                      int gates_impl, void* y, float* h_last, void* workspace,
+                      size_t workspace_bytes, void* stream) {
+  int rc = check_common(B, T, E, dtype);
+  if (rc) return rc;
+  if ((rc = check_heads(E, H))) return rc;
+  if ((rc = check_params(p, false))) return rc;
+  RGK_REQUIRE(pos_dtype == RGK_I32 || pos_dtype == RGK_I64, RGK_EINVAL, "unknown index dtype");
+  RGK_REQUIRE(gates_impl >= RGK_GATES_AUTO && gates_impl <= RGK_GATES_TCGEN05, RGK_EINVAL,
+              "unknown gates_impl %d", gates_impl);
+  RGK_REQUIRE(x && segment_pos && y, RGK_EINVAL, "NULL pointer argument");
+  RGK_REQUIRE(aligned16(x) && aligned16(y) && aligned16(h0) && aligned16(h_last), RGK_EALIGN,
+              "pointers must be 16-byte aligned");
+  if (B * T * E == 0) return RGK_OK;
+  const PathWs w = carve(workspace, B, T, E, dtype);
+  RGK_REQUIRE(workspace != nullptr && workspace_bytes >= w.total, RGK_EWORKSPACE,
+              "workspace of %zu bytes needed, %zu given", w.total, workspace_bytes);
+  RGK_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255u) == 0, RGK_EALIGN,
+              "workspace must be 256-byte aligned");
+  RGK_REQUIRE(gates_impl != RGK_GATES_TCGEN05, RGK_ESHAPE,
+              "the tcgen05 gate kernel is not available for this call");
+  RGK_CHECK_DEVICE();
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int bw = (int)(E / H);
+  RGK_CUDA(rgk::launch_gates_simt(x, segment_pos, pos_dtype, p->a_param, p->gate_x_w, p->gate_x_b,
+                                  p->gate_a_w, p->gate_a_b, B * T, H, bw, dtype, w.a, w.xn, s),
+           "gates launch");
+  RGK_CUDA(rgk::launch_scan(w.xn, w.a, nullptr, nullptr, 0, h0, nullptr, B, T, E, dtype, y, h_last,
+                            w.scan, s),
+           "scan launch");
+  return RGK_OK;
+}
+
+int rgk_recurrent_path_prefill(const void* xb, const void* yb, const void* segment_pos,
+                               int pos_dtype, const rgk_params* p, const float* h0, int64_t B,
+                               int64_t T, int64_t E, int H, int W, int dtype, int gates_impl,
+                               void* out, float* h_last, void* conv_cache_out, void* workspace,
+                               size_t workspace_bytes, void* stream) {
+  int rc = check_common(B, T, E, dtype);
+  if (rc) return rc;
+  if ((rc = check_heads(E, H))) return rc;
+  if ((rc = check_params(p, true))) return rc;
+  RGK_REQUIRE(W == 4, RGK_ESHAPE, "temporal width %d is not supported (only 4)", W);
+  RGK_REQUIRE(pos_dtype == RGK_I32 || pos_dtype == RGK_I64, RGK_EINVAL, "unknown index dtype");
+  RGK_REQUIRE(gates_impl >= RGK_GATES_AUTO && gates_impl <= RGK_GATES_TCGEN05, RGK_EINVAL,
+              "unknown gates_impl %d", gates_impl);
+  RGK_REQUIRE(xb && segment_pos && out, RGK_EINVAL, "NULL pointer argument");
+  RGK_REQUIRE(aligned16(xb) && aligned16(yb) && aligned16(out) && aligned16(h0) &&
+                  aligned16(h_last) && aligned16(conv_cache_out),
+              RGK_EALIGN, "pointers must be 16-byte aligned");
+  RGK_REQUIRE(T >= 1 || B * E == 0, RGK_ESHAPE, "prefill needs at least one token");
+  if (B * T * E == 0) return RGK_OK;
+  const PathWs w = carve(workspace, B, T, E, dtype);
+  RGK_REQUIRE(workspace != nullptr && workspace_bytes >= w.total, RGK_EWORKSPACE,
+              "workspace of %zu bytes needed, %zu given", w.total, workspace_bytes);
+  RGK_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255u) == 0, RGK_EALIGN,
+              "workspace must be 256-byte aligned");
+  RGK_REQUIRE(gates_impl != RGK_GATES_TCGEN05, RGK_ESHAPE,
+              "the tcgen05 gate kernel is not available for this call");
+  RGK_CHECK_DEVICE();
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int bw = (int)(E / H);
+  RGK_CUDA(rgk::launch_conv1d_prefill(xb, segment_pos, pos_dtype, p->conv_w, p->conv_b, B, T, E,
+                                      dtype, w.c, conv_cache_out, s),
+           "conv1d_prefill launch");
+  RGK_CUDA(rgk::launch_gates_simt(w.c, segment_pos, pos_dtype, p->a_param, p->gate_x_w,
+                                  p->gate_x_b, p->gate_a_w, p->gate_a_b, B * T, H, bw, dtype, w.a,
+                                  w.xn, s),
+           "gates launch");
+  RGK_CUDA(rgk::launch_scan(w.xn, w.a, nullptr, nullptr, 0, h0, yb, B, T, E, dtype, out, h_last,
+                            w.scan, s),
+           "scan launch");
+  return RGK_OK;
+}
+
+int rgk_recurrent_path_decode(const void* xb, const void* yb, const void* segment_pos,
+                              int pos_dtype, const rgk_params* p, const float* h_in,
+                              const void* conv_cache_in, int64_t B, int64_t E, int H, int W,
+                              int dtype, int gates_impl, void* out, float* h_out,
+                              void* conv_cache_out, void* workspace, size_t workspace_bytes,
+                              void* stream) {
+  int rc = check_common(B, 1, E, dtype);
+  if (rc) return rc;
+  if ((rc = check_heads(E, H))) return rc;
+  if ((rc = check_params(p, true))) return rc;
+  RGK_REQUIRE(W == 4, RGK_ESHAPE, "temporal width %d is not supported (only 4)", W);
+  RGK_REQUIRE(pos_dtype == RGK_I32 || pos_dtype == RGK_I64, RGK_EINVAL, "unknown index dtype");
+  RGK_REQUIRE(gates_impl >= RGK_GATES_AUTO && gates_impl <= RGK_GATES_TCGEN05, RGK_EINVAL,
+              "unknown gates_impl %d", gates_impl);
+  RGK_REQUIRE(xb && segment_pos && h_in && conv_cache_in && out && h_out, RGK_EINVAL,
+              "NULL pointer argument");
+  RGK_REQUIRE(aligned16(xb) && aligned16(yb) && aligned16(out) && aligned16(h_in) &&
+                  aligned16(h_out) && aligned16(conv_cache_in) && aligned16(conv_cache_out),
+              RGK_EALIGN, "pointers must be 16-byte aligned");
+  if (B * E == 0) return RGK_OK;
+  const PathWs w = carve(workspace, B, 1, E, dtype);
+  RGK_REQUIRE(workspace != nullptr && workspace_bytes >= w.total, RGK_EWORKSPACE,
+              "workspace of %zu bytes needed, %zu given", w.total, workspace_bytes);
+  RGK_REQUIRE(gates_impl != RGK_GATES_TCGEN05, RGK_ESHAPE,
+              "the tcgen05 gate kernel is not available for this call");
+  RGK_CHECK_DEVICE();
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int bw = (int)(E / H);
+  RGK_CUDA(rgk::launch_conv1d_decode(xb, conv_cache_in, p->conv_w, p->conv_b, B, E, dtype, w.c,
+                                     conv_cache_out, s),
+           "conv1d_decode launch");
+  RGK_CUDA(rgk::launch_gates_simt(w.c, segment_pos, pos_dtype, p->a_param, p->gate_x_w,
+                                  p->gate_x_b, p->gate_a_w, p->gate_a_b, B, H, bw, dtype, w.a, w.xn,
+                                  s),
+           "gates launch");
+  RGK_CUDA(rgk::launch_decode_update(w.a, w.xn, h_in, yb, B, E, dtype, out, h_out, s),
+           "decode_update launch");
+  return RGK_OK;
+}
+
+}  // extern "C"

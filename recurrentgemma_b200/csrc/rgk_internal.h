@@ -1,0 +1,41 @@
+// Launchers implemented by the .cu files of librgk; called only from api.cu, which validates
+// arguments first.  Each returns the cudaError_t of its last launch.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace rgk {
+
+// conv1d.cu
+cudaError_t launch_conv1d_prefill(const void* x, const void* pos, int pos64, const void* w,
+                                  const void* b, int64_t B, int64_t T, int64_t E, int dtype,
+                                  void* out, void* cache_out, cudaStream_t s);
+cudaError_t launch_conv1d_decode(const void* x, const void* cache_in, const void* w, const void* b,
+                                 int64_t B, int64_t E, int dtype, void* out, void* cache_out,
+                                 cudaStream_t s);
+
+// blockdiag_simt.cu
+cudaError_t launch_blockdiag_linear_simt(const void* x, const void* w, const void* b, int64_t M,
+                                         int H, int bw, int dtype, void* out, cudaStream_t s);
+// Gate projections + gate arithmetic: writes a (reset-masked) and the normalised input.
+cudaError_t launch_gates_simt(const void* c, const void* pos, int pos64, const void* a_param,
+                              const void* wx, const void* bx, const void* wa, const void* ba,
+                              int64_t M, int H, int bw, int dtype, void* a_out, void* xn_out,
+                              cudaStream_t s);
+
+// scan.cu
+size_t scan_workspace_bytes(int64_t B, int64_t T, int64_t E, int dtype);
+cudaError_t launch_scan(const void* x, const void* a, const uint8_t* reset, const void* pos,
+                        int pos64, const float* h0, const void* y_mul, int64_t B, int64_t T,
+                        int64_t E, int dtype, void* y, float* h_last, void* ws, cudaStream_t s);
+
+// decode.cu
+// One recurrence step from precomputed a / normalised x: h_out = a h_in + xn (float32, unrounded),
+// out = round(h_out) [* gelu_tanh(yb)].
+cudaError_t launch_decode_update(const void* a, const void* xn, const float* h_in, const void* yb,
+                                 int64_t B, int64_t E, int dtype, void* out, float* h_out,
+                                 cudaStream_t s);
+
+}  // namespace rgk

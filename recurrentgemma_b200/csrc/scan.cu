@@ -1,0 +1,313 @@
+// The linear recurrence of the RG-LRU, h_t = a_t h_{t-1} + x_t with a float32 state
+// (recurrentgemma torch/layers.py:140-191), as a single-pass chunked parallel scan.
+//
+// Decomposition.  The [B, T, E] problem is cut into tiles of kRows time steps x 64 channels.
+// Inside a tile every thread owns 8 consecutive time steps of one 16-byte pack of channels and
+// runs them sequentially in registers: pass 1 reduces its steps to the pair (P, H) of the affine
+// map h -> P h + H, the pairs of the tile's sub-chunks are chained through shared memory, and
+// pass 2 replays the same steps from registers starting from the now known incoming state.
+// Tiles of one sequence are linked by a decoupled look-back: each tile publishes its own (P, H)
+// as soon as it has it, then walks back over its predecessors' records (a warp reads up to 32
+// flags at a time) until it meets one that already holds the inclusive state.  Tile numbers are
+// handed out by an atomic ticket in time-major order, so a predecessor has always started before
+// its successor and no tile can wait on one that is not running.  All waits are bounded; a wait
+// that expires sets WsHeader::status and the tile continues with a zero carry.
+//
+// Every input element is read from HBM exactly once and every output written once; the
+// optional join with the block's other branch (y * gelu_tanh(y_mul), torch/modules.py:627-628,
+// 646) is fused into pass 2.
+#include "rgk_common.cuh"
+#include "rgk_internal.h"
+
+namespace rgk {
+namespace {
+
+constexpr int kThreads = 128;
+constexpr int kChan = 64;        // channels per tile
+constexpr int kRowsPerThread = 8;
+constexpr unsigned kSpinLimit = 1u << 21;
+
+template <typename T> struct ScanCfg {
+  static constexpr int kPack = Traits<T>::kPack;
+  static constexpr int kLanesPerRow = kChan / kPack;          // 8 (bf16) or 16 (f32)
+  static constexpr int kSubs = kThreads / kLanesPerRow;       // 16 or 8 sub-chunks
+  static constexpr int kRows = kSubs * kRowsPerThread;        // 128 or 64 time steps per tile
+};
+
+__device__ __forceinline__ unsigned ld_acquire(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release(unsigned* p, unsigned v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ float4 ld_cg_f4(const void* p) {
+  float4 v;
+  asm volatile("ld.global.cg.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ float2 ld_cg_f2(const void* p) {
+  float2 v;
+  asm volatile("ld.global.cg.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "l"(p) : "memory");
+  return v;
+}
+
+template <typename T, bool kMul>
+__global__ void __launch_bounds__(kThreads, 3)
+scan_kernel(const T* __restrict__ x, const T* __restrict__ a, const uint8_t* __restrict__ reset,
+            const void* __restrict__ pos, int pos64, const float* __restrict__ h0,
+            const T* __restrict__ y_mul, int B, int T_, int E, int tiles_t, int groups,
+            T* __restrict__ y, float* __restrict__ h_last, WsHeader* hdr, unsigned* flags,
+            float2* agg, float* incl) {
+  using Cfg = ScanCfg<T>;
+  constexpr int kPack = Cfg::kPack;
+  constexpr bool kBf16 = Traits<T>::kBf16;
+  constexpr int kSubs = Cfg::kSubs;
+
+  __shared__ float2 s_sub[kSubs][kChan];   // (P, H) of every sub-chunk
+  __shared__ float s_subin[kSubs][kChan];  // state entering every sub-chunk
+  __shared__ float2 s_tile[kChan];         // (P, H) of the whole tile
+  __shared__ float s_hin[kChan];           // state entering the tile
+  __shared__ unsigned s_ticket;
+
+  const int tid = threadIdx.x;
+  if (tid == 0) s_ticket = atomicAdd(&hdr->ticket, 1u);
+  __syncthreads();
+  const unsigned tile = s_ticket;
+  const int nseq = B * groups;
+  const int tt = tile / nseq;
+  const int seq = tile - tt * nseq;
+  const int b = seq / groups;
+  const int g = seq - b * groups;
+  if (tt >= tiles_t) return;  // cannot happen with the launch grid; keeps indices in range
+
+  const int lane_in_row = tid % Cfg::kLanesPerRow;
+  const int sub = tid / Cfg::kLanesPerRow;
+  const int e0 = g * kChan + lane_in_row * kPack;
+  const bool chan_ok = e0 < E;
+  const int t0 = tt * Cfg::kRows + sub * kRowsPerThread;
+  const int64_t row0 = (int64_t)b * T_;
+
+  // ---- loads: everything this thread will ever need, issued back to back -------------------------
+  uint4 araw[kRowsPerThread], xraw[kRowsPerThread], mraw[kRowsPerThread];
+  unsigned valid = 0, rst = 0;
+#pragma unroll
+  for (int r = 0; r < kRowsPerThread; ++r) {
+    const int t = t0 + r;
+    if (chan_ok && t < T_) {
+      valid |= 1u << r;
+      const int64_t off = (row0 + t) * E + e0;
+      araw[r] = ld_stream(a + off);
+      xraw[r] = ld_stream(x + off);
+      if constexpr (kMul) mraw[r] = ld_stream(y_mul + off);
+      bool rs = false;
+      if (reset != nullptr) rs = reset[row0 + t] != 0;
+      else if (pos != nullptr) rs = pos_is_zero(pos, pos64, row0 + t);
+      if (rs) rst |= 1u << r;
+    }
+  }
+
+  // ---- pass 1: this thread's 8 steps as an affine map --------------------------------------------
+  {
+    float P[kPack], Hh[kPack];
+#pragma unroll
+    for (int i = 0; i < kPack; ++i) { P[i] = 1.0f; Hh[i] = 0.0f; }
+#pragma unroll
+    for (int r = 0; r < kRowsPerThread; ++r) {
+      if (valid & (1u << r)) {
+        float av[kPack], xv[kPack];
+        unpack<T>(araw[r], av);
+        unpack<T>(xraw[r], xv);
+        const float keep = (rst & (1u << r)) ? 0.0f : 1.0f;
+#pragma unroll
+        for (int i = 0; i < kPack; ++i) {
+          const float ae = av[i] * keep;
+          Hh[i] = fmaf(ae, Hh[i], xv[i]);
+          P[i] *= ae;
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < kPack; ++i) s_sub[sub][lane_in_row * kPack + i] = make_float2(P[i], Hh[i]);
+  }
+  __syncthreads();
+
+  // ---- tile aggregate, published before anything is waited for -----------------------------------
+  const int64_t rec = (int64_t)tile;  // record index = ticket = tt * nseq + seq
+  if (tid < kChan) {
+    float P = 1.0f, Hh = 0.0f;
+#pragma unroll
+    for (int s = 0; s < kSubs; ++s) {
+      const float2 ph = s_sub[s][tid];
+      Hh = fmaf(ph.x, Hh, ph.y);
+      P *= ph.x;
+    }
+    s_tile[tid] = make_float2(P, Hh);
+    if (tt == 0) {
+      const int e = g * kChan + tid;
+      const float hin = (h0 != nullptr && e < E) ? h0[(int64_t)b * E + e] : 0.0f;
+      s_hin[tid] = hin;
+      incl[rec * kChan + tid] = fmaf(P, hin, Hh);
+    } else {
+      agg[rec * kChan + tid] = make_float2(P, Hh);
+    }
+    __threadfence();
+  }
+  __syncthreads();
+  if (tid == 0) st_release(&flags[rec], tt == 0 ? 2u : 1u);
+
+  // ---- decoupled look-back by warp 0 (lane owns channels 2*lane, 2*lane+1) -----------------------
+  if (tt > 0 && tid < 32) {
+    const int lane = tid;
+    float Pc0 = 1.0f, Hc0 = 0.0f, Pc1 = 1.0f, Hc1 = 0.0f;
+    float hin0 = 0.0f, hin1 = 0.0f;
+    int base = tt - 1;
+    bool done = false, timed_out = false;
+    while (!done) {
+      const int pred = base - lane;
+      unsigned f = 2u;
+      int L = 32;
+      unsigned spins = 0;
+      while (true) {
+        if (pred >= 0) f = ld_acquire(&flags[(int64_t)pred * nseq + seq]);
+        const unsigned incl_mask = __ballot_sync(0xffffffffu, f == 2u);
+        L = incl_mask ? (__ffs(incl_mask) - 1) : 32;
+        const unsigned need = (L >= 31) ? 0xffffffffu : ((2u << L) - 1u);
+        const unsigned zero = __ballot_sync(0xffffffffu, f == 0u) & need;
+        if (zero == 0u) break;
+        if (++spins > kSpinLimit) { timed_out = true; break; }
+        __nanosleep(64);
+      }
+      if (timed_out) break;
+      const int n_agg = L < 32 ? L : 32;  // lanes 0 .. n_agg-1 hold plain aggregates
+      for (int j = 0; j < n_agg; ++j) {
+        const int64_t r2 = (int64_t)(base - j) * nseq + seq;
+        const float4 v = ld_cg_f4(reinterpret_cast<const float4*>(agg + r2 * kChan) + lane);
+        Hc0 = fmaf(Pc0, v.y, Hc0); Pc0 *= v.x;
+        Hc1 = fmaf(Pc1, v.w, Hc1); Pc1 *= v.z;
+      }
+      if (L < 32) {
+        const int64_t r2 = (int64_t)(base - L) * nseq + seq;
+        const float2 v = ld_cg_f2(reinterpret_cast<const float2*>(incl + r2 * kChan) + lane);
+        hin0 = fmaf(Pc0, v.x, Hc0);
+        hin1 = fmaf(Pc1, v.y, Hc1);
+        done = true;
+      } else {
+        base -= 32;
+      }
+    }
+    if (timed_out) {
+      if (lane == 0) atomicExch(&hdr->status, kStatusTimeout);
+      hin0 = hin1 = 0.0f;
+    }
+    s_hin[2 * lane] = hin0;
+    s_hin[2 * lane + 1] = hin1;
+    const float2 t0v = s_tile[2 * lane], t1v = s_tile[2 * lane + 1];
+    float2 inc;
+    inc.x = fmaf(t0v.x, hin0, t0v.y);
+    inc.y = fmaf(t1v.x, hin1, t1v.y);
+    *(reinterpret_cast<float2*>(incl + rec * kChan) + lane) = inc;
+    __threadfence();
+    __syncwarp();
+    if (lane == 0) st_release(&flags[rec], 2u);
+  }
+  __syncthreads();
+
+  // ---- state entering each sub-chunk; the last tile of a sequence also writes h_last -------------
+  if (tid < kChan) {
+    float h = s_hin[tid];
+#pragma unroll
+    for (int s = 0; s < kSubs; ++s) {
+      s_subin[s][tid] = h;
+      const float2 ph = s_sub[s][tid];
+      h = fmaf(ph.x, h, ph.y);
+    }
+    const int e = g * kChan + tid;
+    if (h_last != nullptr && tt == tiles_t - 1 && e < E) h_last[(int64_t)b * E + e] = h;
+  }
+  __syncthreads();
+
+  // ---- pass 2: replay from registers with the true incoming state --------------------------------
+  float h[kPack];
+#pragma unroll
+  for (int i = 0; i < kPack; ++i) h[i] = s_subin[sub][lane_in_row * kPack + i];
+#pragma unroll
+  for (int r = 0; r < kRowsPerThread; ++r) {
+    if (valid & (1u << r)) {
+      float av[kPack], xv[kPack], out[kPack];
+      unpack<T>(araw[r], av);
+      unpack<T>(xraw[r], xv);
+      const float keep = (rst & (1u << r)) ? 0.0f : 1.0f;
+#pragma unroll
+      for (int i = 0; i < kPack; ++i) {
+        h[i] = __fadd_rn(__fmul_rn(av[i] * keep, h[i]), xv[i]);
+        out[i] = rnd<kBf16>(h[i]);
+      }
+      if constexpr (kMul) {
+        float mv[kPack];
+        unpack<T>(mraw[r], mv);
+#pragma unroll
+        for (int i = 0; i < kPack; ++i)
+          out[i] = rnd<kBf16>(out[i] * rnd<kBf16>(gelu_tanh_<kBf16>(mv[i])));
+      }
+      st_stream(y + (row0 + t0 + r) * E + e0, pack<T>(out));
+    }
+  }
+}
+
+struct ScanLayout {
+  int tiles_t, groups;
+  int64_t ntiles;
+  size_t flags_off, agg_off, incl_off, total;
+};
+
+ScanLayout scan_layout(int64_t B, int64_t T, int64_t E, int dtype) {
+  ScanLayout L;
+  const int rows = dtype ? ScanCfg<__nv_bfloat16>::kRows : ScanCfg<float>::kRows;
+  L.tiles_t = (int)((T + rows - 1) / rows);
+  L.groups = (int)((E + kChan - 1) / kChan);
+  L.ntiles = (int64_t)L.tiles_t * B * L.groups;
+  auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
+  L.flags_off = sizeof(WsHeader);
+  L.agg_off = up(L.flags_off + (size_t)L.ntiles * sizeof(unsigned));
+  L.incl_off = up(L.agg_off + (size_t)L.ntiles * kChan * sizeof(float2));
+  L.total = up(L.incl_off + (size_t)L.ntiles * kChan * sizeof(float));
+  return L;
+}
+
+}  // namespace
+
+size_t scan_workspace_bytes(int64_t B, int64_t T, int64_t E, int dtype) {
+  return scan_layout(B, T, E, dtype).total;
+}
+
+cudaError_t launch_scan(const void* x, const void* a, const uint8_t* reset, const void* pos,
+                        int pos64, const float* h0, const void* y_mul, int64_t B, int64_t T,
+                        int64_t E, int dtype, void* y, float* h_last, void* ws, cudaStream_t s) {
+  if (B == 0 || T == 0 || E == 0) return cudaSuccess;
+  const ScanLayout L = scan_layout(B, T, E, dtype);
+  char* base = static_cast<char*>(ws);
+  // Header (status, ticket) and flags start every launch at zero.
+  cudaError_t err = cudaMemsetAsync(base, 0, L.agg_off, s);
+  if (err != cudaSuccess) return err;
+  WsHeader* hdr = reinterpret_cast<WsHeader*>(base);
+  unsigned* flags = reinterpret_cast<unsigned*>(base + L.flags_off);
+  float2* agg = reinterpret_cast<float2*>(base + L.agg_off);
+  float* incl = reinterpret_cast<float*>(base + L.incl_off);
+  const unsigned grid = (unsigned)L.ntiles;
+#define RGK_SCAN_LAUNCH(TYPE, MUL)                                                              \
+  scan_kernel<TYPE, MUL><<<grid, kThreads, 0, s>>>(                                             \
+      (const TYPE*)x, (const TYPE*)a, reset, pos, pos64, h0, (const TYPE*)y_mul, (int)B, (int)T, \
+      (int)E, L.tiles_t, L.groups, (TYPE*)y, h_last, hdr, flags, agg, incl)
+  if (dtype) {
+    if (y_mul) RGK_SCAN_LAUNCH(__nv_bfloat16, true); else RGK_SCAN_LAUNCH(__nv_bfloat16, false);
+  } else {
+    if (y_mul) RGK_SCAN_LAUNCH(float, true); else RGK_SCAN_LAUNCH(float, false);
+  }
+#undef RGK_SCAN_LAUNCH
+  return cudaGetLastError();
+}
+
+}  // namespace rgk

@@ -1,0 +1,143 @@
+"""Drop-in counterpart of recurrentgemma.torch.modules.RecurrentBlock (modules.py:496-680).
+
+Same constructor, parameter names (`linear_y`, `linear_x`, `linear_out`, `conv_1d`, `rg_lru`),
+forward signature and cache type as the reference, so it slots into the reference `Griffin` model
+and `Sampler` unchanged.  The RG-LRU + Conv1D sub-path between the projections runs as one
+composed call into librgk.so; the three dense projections are plain library GEMMs.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import NamedTuple, Optional, Tuple
+
+import torch
+from torch import nn
+
+from recurrentgemma_b200 import _lib
+from recurrentgemma_b200 import layers
+
+
+class RecurrentBlockCache(NamedTuple):
+  """Field order and dtypes of recurrentgemma/torch/modules.py:32-37."""
+  rg_lru_state: torch.Tensor   # [B, lru_width] float32
+  conv1d_state: torch.Tensor   # [B, conv1d_temporal_width - 1, lru_width] activation dtype
+
+
+def recurrent_path(
+    xb: torch.Tensor, yb: Optional[torch.Tensor], segment_pos: torch.Tensor,
+    conv_1d: layers.Conv1D, rg_lru: layers.RGLRU,
+    cache: Optional[RecurrentBlockCache] = None, return_cache: bool = True,
+    out: Optional[torch.Tensor] = None,
+) -> Tuple[torch.Tensor, Optional[RecurrentBlockCache]]:
+  """RGLRU(Conv1D(xb)) * gelu_tanh(yb): the sub-path of RecurrentBlock.forward between the
+  input projections and `linear_out` (recurrentgemma/torch/modules.py:631-646)."""
+  bs, l, e = xb.shape
+  dev = _lib.require_cuda(xb, yb, segment_pos, conv_1d.w, rg_lru.a_param)
+  layers._same_dtype(xb, conv_1d.w, conv_1d.b, rg_lru.a_param, rg_lru.input_gate.w,
+                     rg_lru.input_gate.b, rg_lru.a_gate.w, rg_lru.a_gate.b)
+  if yb is not None:
+    assert yb.shape == xb.shape and yb.dtype == xb.dtype
+  if conv_1d.temporal_width != 4:
+    raise NotImplementedError("the CUDA Conv1D covers temporal_width == 4 only")
+  pos = layers._pos(segment_pos, bs, l)
+  lib = _lib.load()
+  dt = _lib.dtype_code(xb.dtype)
+  xc = xb.contiguous()
+  yc = None if yb is None else yb.contiguous()
+  if out is None:
+    out = torch.empty_like(xc)
+  p = rg_lru._params(conv_1d)
+  with torch.cuda.device(dev):
+    ws = _lib.workspace(dev, _lib.workspace_bytes(bs, l, e, xb.dtype))
+    if cache is None:
+      h_last = torch.empty((bs, e), dtype=torch.float32, device=dev) if return_cache else None
+      conv_state = torch.empty((bs, 3, e), dtype=xb.dtype, device=dev) if return_cache else None
+      _lib.check(lib.rgk_recurrent_path_prefill(
+          xc.data_ptr(), _lib.ptr(yc), pos.data_ptr(), _lib.pos_code(pos), ctypes.byref(p), None,
+          bs, l, e, rg_lru.num_heads, 4, dt, rg_lru.gates_impl, out.data_ptr(), _lib.ptr(h_last),
+          _lib.ptr(conv_state), ws.data_ptr(), ws.numel(), _lib.stream_ptr(dev)))
+    else:
+      # Conv1D decoding takes one token at a time (recurrentgemma/torch/layers.py:548-549).
+      assert l == 1, "with a cache the recurrent block takes one token at a time"
+      assert cache.rg_lru_state.dtype == torch.float32
+      assert cache.rg_lru_state.shape == (bs, e) and cache.conv1d_state.shape == (bs, 3, e)
+      h_in = cache.rg_lru_state.contiguous()
+      conv_in = cache.conv1d_state.to(xb.dtype).contiguous()
+      h_last = torch.empty_like(h_in)
+      conv_state = torch.empty_like(conv_in)
+      _lib.check(lib.rgk_recurrent_path_decode(
+          xc.data_ptr(), _lib.ptr(yc), pos.data_ptr(), _lib.pos_code(pos), ctypes.byref(p),
+          h_in.data_ptr(), conv_in.data_ptr(), bs, e, rg_lru.num_heads, 4, dt, rg_lru.gates_impl,
+          out.data_ptr(), h_last.data_ptr(), conv_state.data_ptr(), ws.data_ptr(), ws.numel(),
+          _lib.stream_ptr(dev)))
+      if conv_state.dtype != cache.conv1d_state.dtype:
+        conv_state = conv_state.to(cache.conv1d_state.dtype)
+  if not return_cache:
+    return out, None
+  return out, RecurrentBlockCache(rg_lru_state=h_last, conv1d_state=conv_state)
+
+
+class RecurrentBlock(nn.Module):
+  """Griffin and Hawk's recurrent block."""
+
+  def __init__(self, width: int, num_heads: int, lru_width: Optional[int] = None,
+               conv1d_temporal_width: int = 4, final_w_init_variance_scale: float = 1.0,
+               device=None, dtype=None):
+    super().__init__()
+    self.width = width
+    self.num_heads = num_heads
+    self.lru_width = lru_width or width
+    self.conv1d_temporal_width = conv1d_temporal_width
+    self.final_w_init_variance_scale = final_w_init_variance_scale
+
+    self.linear_y = nn.Linear(self.width, self.lru_width, device=device, dtype=dtype)
+    self.linear_x = nn.Linear(self.width, self.lru_width, device=device, dtype=dtype)
+    self.linear_out = nn.Linear(self.lru_width, self.width, device=device, dtype=dtype)
+    self.conv_1d = layers.Conv1D(width=self.lru_width, temporal_width=self.conv1d_temporal_width,
+                                 device=device, dtype=dtype)
+    self.rg_lru = layers.RGLRU(width=self.lru_width, num_heads=self.num_heads, device=device,
+                               dtype=dtype)
+    self.reset_parameters()
+
+  def reset_parameters(self) -> None:
+    self.w_init_(self.linear_x.weight)
+    torch.nn.init.zeros_(self.linear_x.bias)
+    self.w_init_(self.linear_y.weight)
+    torch.nn.init.zeros_(self.linear_y.bias)
+    self.out_w_init_(self.linear_out.weight)
+    torch.nn.init.zeros_(self.linear_out.bias)
+    self.conv_1d.reset_parameters()
+    self.rg_lru.reset_parameters()
+
+  def w_init_(self, w: torch.Tensor) -> None:
+    torch.nn.init.normal_(w, mean=0.0, std=math.sqrt(1.0 / self.width))
+
+  def out_w_init_(self, w: torch.Tensor) -> None:
+    torch.nn.init.normal_(w, mean=0.0,
+                          std=math.sqrt(self.final_w_init_variance_scale / self.lru_width))
+
+  @torch.no_grad()
+  def forward(
+      self, x: torch.Tensor, segment_pos: torch.Tensor,
+      cache: Optional[RecurrentBlockCache] = None, return_cache: bool = True,
+  ) -> Tuple[torch.Tensor, Optional[RecurrentBlockCache]]:
+    """Returns (block output [B,T,width], updated cache or None)."""
+    _lib.require_cuda(x, segment_pos, self.linear_x.weight)
+    yb = self.linear_y(x)
+    xb = self.linear_x(x)
+    z, new_cache = recurrent_path(xb, yb, segment_pos, self.conv_1d, self.rg_lru, cache,
+                                  return_cache)
+    return self.linear_out(z), new_cache
+
+  @classmethod
+  def init_cache(cls, batch_size: int, lru_width: int, dtype: torch.dtype,
+                 conv1d_temporal_width: int = 4, device=None) -> RecurrentBlockCache:
+    """Empty cache (recurrentgemma/torch/modules.py:657-680)."""
+    return RecurrentBlockCache(
+        rg_lru_state=layers.RGLRU.init_cache(batch_size=batch_size, width=lru_width,
+                                             device=device),
+        conv1d_state=layers.Conv1D.init_cache(batch_size=batch_size, width=lru_width, dtype=dtype,
+                                              conv1d_temporal_width=conv1d_temporal_width,
+                                              device=device),
+    )

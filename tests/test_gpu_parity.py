@@ -1,0 +1,199 @@
+"""Parity of the CUDA path (through the drop-in modules, hence through the C ABI of librgk.so)
+with the reference-generated golden vectors and with the CPU oracle.  Needs a B200."""
+import pytest
+import torch
+
+from tests import cases as C
+from tests.util import TOL, assert_close, load_golden
+
+pytestmark = pytest.mark.gpu
+
+CASES = C.golden_cases()
+DEV = "cuda:0"
+
+
+def _cuda(d):
+  return {k: (None if v is None else v.to(DEV)) for k, v in d.items()}
+
+
+@pytest.fixture(scope="module")
+def rg():
+  import recurrentgemma_b200 as m
+  from recurrentgemma_b200 import _lib
+  _lib.load()
+  return m
+
+
+def _block(rg, case, p):
+  m = rg.RecurrentBlock(case.model_width, case.heads, case.lru_width, case.temporal_width,
+                        device=DEV, dtype=case.torch_dtype)
+  m.load_state_dict(p)
+  return m
+
+
+@pytest.mark.parametrize("case", CASES, ids=[c.name for c in CASES])
+def test_golden(case, rg, oracle):
+  g = load_golden(case.name)
+  p = C.make_params(case)
+  inp = C.make_inputs(case)
+  assert abs(C.checksum({**p, **inp}) - float(g["input_checksum"])) <= 1e-6 * abs(
+      float(g["input_checksum"]))
+  tol = TOL[case.torch_dtype]
+  pc, ic = _cuda(p), _cuda(inp)
+  pos = ic["segment_pos"]
+
+  def chk(out, key):
+    assert_close(out, g[key], tol, f"{case.name}:{key}")
+
+  if case.kind == "blockdiag":
+    m = rg.BlockDiagonalLinear(case.lru_width, case.heads, device=DEV, dtype=case.torch_dtype)
+    m.load_state_dict({"w": p["rg_lru.input_gate.w"], "b": p["rg_lru.input_gate.b"]})
+    chk(m(ic["x"]), "out")
+
+  elif case.kind == "conv1d":
+    m = rg.Conv1D(case.lru_width, case.temporal_width, device=DEV, dtype=case.torch_dtype)
+    m.load_state_dict({"w": p["conv_1d.w"], "b": p["conv_1d.b"]})
+    if case.temporal_width != 4:
+      with pytest.raises(NotImplementedError):
+        m(ic["x"], pos)
+      return
+    x_before = ic["x"].clone()
+    y, cache = m(ic["x"], pos)
+    assert torch.equal(ic["x"], x_before), "the input must not be modified"
+    chk(y, "out"); chk(cache, "cache")
+    assert cache.dtype == case.torch_dtype and cache.shape == (case.batch, 3, case.lru_width)
+    for i in range(case.decode_steps):
+      y, cache = m(ic[f"x_step{i}"], C.decode_positions(case, inp["segment_pos"], i).to(DEV), cache)
+      chk(y, f"out_step{i}"); chk(cache, f"cache_step{i}")
+
+  elif case.kind == "rnn_scan":
+    y, h = rg.rnn_scan(ic["x"], ic["a"], pos == 0, ic["h0"])
+    chk(y, "out"); chk(h, "h")
+    assert h.dtype == torch.float32
+
+  elif case.kind == "rglru":
+    m = rg.RGLRU(case.lru_width, case.heads, device=DEV, dtype=case.torch_dtype)
+    m.load_state_dict({k[len("rg_lru."):]: v for k, v in p.items() if k.startswith("rg_lru.")})
+    y, h = m(ic["x"], pos, ic["h0"])
+    chk(y, "out"); chk(h, "h")
+    assert h.dtype == torch.float32
+    for i in range(case.decode_steps):
+      y, h = m(ic[f"x_step{i}"], C.decode_positions(case, inp["segment_pos"], i).to(DEV), h)
+      chk(y, f"out_step{i}"); chk(h, f"h_step{i}")
+    y2, none = m(ic["x"], pos, ic["h0"], return_cache=False)
+    assert none is None
+    assert_close(y2, g["out"], tol, "return_cache=False")
+
+  elif case.kind == "block":
+    m = _block(rg, case, p)
+    y, cache = m(ic["x"], pos)
+    assert isinstance(cache, rg.RecurrentBlockCache)
+    assert cache._fields == ("rg_lru_state", "conv1d_state")
+    chk(y, "out"); chk(cache.rg_lru_state, "h"); chk(cache.conv1d_state, "cache")
+    for i in range(case.decode_steps):
+      y, cache = m(ic[f"x_step{i}"], C.decode_positions(case, inp["segment_pos"], i).to(DEV), cache)
+      chk(y, f"out_step{i}"); chk(cache.rg_lru_state, f"h_step{i}")
+      chk(cache.conv1d_state, f"cache_step{i}")
+    y3, none = m(ic["x"], pos, return_cache=False)
+    assert none is None
+    assert_close(y3, g["out"], tol, "return_cache=False")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("shape", [(2, 1031, 320), (1, 9000, 64), (3, 257, 72), (1, 5, 8),
+                                   (2, 128, 64), (2, 129, 64)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_scan_vs_oracle(rg, oracle, dtype, shape):
+  """rnn_scan over many tiles (look-back windows of several tiles), ragged T and E, resets, an
+  initial state and the fused gelu join, against the oracle."""
+  b, t, e = shape
+  name = f"scan_{b}_{t}_{e}_{dtype}"
+  x = C.normal(name, "x", shape, 1.0, dtype)
+  a = C.uniform(name, "a", shape, 0.6, 1.0).to(dtype)
+  ym = C.normal(name, "ym", shape, 1.0, dtype)
+  h0 = C.normal(name, "h0", (b, e), 0.5)
+  reset = C.uniform(name, "reset", (b, t), 0.0, 1.0) < 0.01
+  tol = TOL[dtype]
+  y_ref, h_ref = oracle.rnn_scan(x, a, reset, h0)
+  y, h = rg.rnn_scan(x.to(DEV), a.to(DEV), reset.to(DEV), h0.to(DEV))
+  assert_close(y, y_ref, tol, "y"); assert_close(h, h_ref, TOL[torch.float32] * 3, "h")
+  y2, _ = rg.rnn_scan(x.to(DEV), a.to(DEV), reset.to(DEV), None, y_mul=ym.to(DEV))
+  y_ref2, _ = oracle.rnn_scan(x, a, reset, None)
+  assert_close(y2, oracle.gelu_mul(y_ref2, ym), tol, "y*gelu")
+
+
+@pytest.mark.parametrize("name", ["block_f32_128_h1_l256_multi", "block_bf16_256_h8_l256"])
+def test_prefill_state_equals_decode_state(rg, name):
+  """State after prefill(T) == state after prefill(T-1) + one decode step (what the sampler relies
+  on, recurrentgemma/torch/sampler_test.py:150-230)."""
+  case = C.case_by_name(name)
+  p = C.make_params(case)
+  inp = _cuda(C.make_inputs(case))
+  m = _block(rg, case, p)
+  x, pos = inp["x"], inp["segment_pos"]
+  tol = TOL[case.torch_dtype]
+  y_full, c_full = m(x, pos)
+  _, c_a = m(x[:, :-1].contiguous(), pos[:, :-1].contiguous())
+  y_b, c_b = m(x[:, -1:].contiguous(), pos[:, -1:].contiguous(), c_a)
+  keep = (pos[:, -1] != 0).cpu()   # a decode step never starts a document in the sampler
+  assert keep.any()
+  assert_close(c_b.rg_lru_state.cpu()[keep], c_full.rg_lru_state.cpu()[keep], tol, "state")
+  assert_close(y_b.cpu()[keep], y_full[:, -1:].cpu()[keep], tol, "last output")
+  assert_close(c_b.conv1d_state.cpu()[keep][:, -1], c_full.conv1d_state.cpu()[keep][:, -1], tol,
+               "newest conv row")
+
+
+def test_full_size_slice_vs_oracle(rg, oracle):
+  """The 2B-dims prefill workload (batch 8, 4096 tokens, 2560 channels, 10 heads, bfloat16) at
+  full size; channels of different heads and different batch rows never mix, so the oracle checks
+  one (row, head) slice of the full-size result."""
+  torch.manual_seed(0)
+  b, t, e, h = 8, 4096, 2560, 10
+  dt = torch.bfloat16
+  case = C.Case("full_cfg1", "rglru", "bfloat16", b, t, e, h)
+  p = C.make_params(case)
+  g = torch.Generator(device="cpu").manual_seed(1234)
+  xb = torch.randn((b, t, e), generator=g, dtype=torch.float32).to(dt)
+  yb = torch.randn((b, t, e), generator=g, dtype=torch.float32).to(dt)
+  pos = C.geometric_segment_pos(b, t, 1024.0, 7)
+  conv = rg.Conv1D(e, 4, device=DEV, dtype=dt)
+  conv.load_state_dict({"w": p["conv_1d.w"], "b": p["conv_1d.b"]})
+  lru = rg.RGLRU(e, h, device=DEV, dtype=dt)
+  lru.load_state_dict({k[len("rg_lru."):]: v for k, v in p.items() if k.startswith("rg_lru.")})
+  out, cache = rg.recurrent_path(xb.to(DEV), yb.to(DEV), pos.to(DEV), conv, lru)
+  from recurrentgemma_b200 import _lib
+  _lib.workspace_status(_lib.workspace(torch.device(DEV), 1))
+  row, head, bw = 5, 7, 256
+  sl = slice(head * bw, (head + 1) * bw)
+  op = {
+      "conv_w": p["conv_1d.w"][:, sl], "conv_b": p["conv_1d.b"][sl],
+      "a_param": p["rg_lru.a_param"][sl],
+      "gate_x_w": p["rg_lru.input_gate.w"][head:head + 1],
+      "gate_x_b": p["rg_lru.input_gate.b"][head:head + 1],
+      "gate_a_w": p["rg_lru.a_gate.w"][head:head + 1],
+      "gate_a_b": p["rg_lru.a_gate.b"][head:head + 1],
+  }
+  o_ref, h_ref, c_ref = oracle.recurrent_path(xb[row:row + 1, :, sl].contiguous(),
+                                              yb[row:row + 1, :, sl].contiguous(),
+                                              pos[row:row + 1], op)
+  assert_close(out[row:row + 1, :, sl], o_ref, TOL[dt], "out slice")
+  assert_close(cache.rg_lru_state[row:row + 1, sl], h_ref, TOL[dt], "state slice")
+  assert_close(cache.conv1d_state[row:row + 1, :, sl], c_ref, TOL[dt], "conv state slice")
+
+
+def test_errors(rg):
+  """Error behaviour: no CPU path, shape / dtype mismatches raise instead of computing."""
+  from recurrentgemma_b200 import _lib
+  conv = rg.Conv1D(128, 4, device=DEV, dtype=torch.float32)
+  with pytest.raises(RuntimeError):
+    conv(torch.zeros(1, 4, 128), torch.zeros(1, 4, dtype=torch.int64))          # CPU tensors
+  with pytest.raises(TypeError):
+    conv(torch.zeros(1, 4, 128, device=DEV, dtype=torch.bfloat16),
+         torch.zeros(1, 4, dtype=torch.int64, device=DEV))                       # dtype mismatch
+  with pytest.raises(AssertionError):
+    conv(torch.zeros(1, 2, 128, device=DEV), torch.zeros(1, 2, dtype=torch.int64, device=DEV),
+         torch.zeros(1, 3, 128, device=DEV))                                     # decode needs T == 1
+  lib = _lib.load()
+  assert lib.rgk_conv1d_prefill(None, None, 0, None, None, 1, 1, 128, 4, 0, None, None, None) == -1
+  assert b"NULL" in lib.rgk_last_error()
+  assert lib.rgk_conv1d_prefill(1, 1, 0, 1, 1, 1, 1, 130, 4, 0, 1, None, None) == -2
