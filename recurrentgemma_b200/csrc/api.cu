@@ -98,12 +98,33 @@ int check_params(const rgk_params* p, bool need_conv) {
   return RGK_OK;
 }
 
-// Carves the workspace of the composed calls: [scan scratch | c | a | xn].
+// Gate projections + gate arithmetic with the kernel `gates_impl` selects.
+int run_gates(const void* c, const void* pos, int pos64, const rgk_params* p, int64_t M, int H,
+              int bw, int dtype, int gates_impl, void* wpack, void* a, void* xn, void* ws_header,
+              cudaStream_t s) {
+  const bool tc_ok = rgk::gates_tc_supported(dtype, bw, M);
+  if (gates_impl == RGK_GATES_TCGEN05 && !tc_ok)
+    return fail(RGK_ESHAPE, "the tcgen05 gate kernel covers bfloat16 with head width 256 only "
+                            "(dtype %d, head width %d)", dtype, bw);
+  if (tc_ok && gates_impl != RGK_GATES_SIMT) {
+    cudaError_t e = rgk::launch_gates_tc(c, pos, pos64, p->a_param, p->gate_x_w, p->gate_x_b,
+                                         p->gate_a_w, p->gate_a_b, M, H, wpack, a, xn, ws_header, s);
+    if (e != cudaSuccess) return cuda_fail(e, "tcgen05 gates launch");
+    return RGK_OK;
+  }
+  cudaError_t e = rgk::launch_gates_simt(c, pos, pos64, p->a_param, p->gate_x_w, p->gate_x_b,
+                                         p->gate_a_w, p->gate_a_b, M, H, bw, dtype, a, xn, s);
+  if (e != cudaSuccess) return cuda_fail(e, "gates launch");
+  return RGK_OK;
+}
+
+// Carves the workspace of the composed calls: [scan scratch | c | a | xn | packed gate weights].
 struct PathWs {
   void* scan;
   void* c;
   void* a;
   void* xn;
+  void* wpack;
   size_t total;
 };
 
@@ -116,7 +137,9 @@ PathWs carve(void* ws, int64_t B, int64_t T, int64_t E, int dtype) {
   w.c = base ? base + scan_bytes : nullptr;
   w.a = base ? base + scan_bytes + act : nullptr;
   w.xn = base ? base + scan_bytes + 2 * act : nullptr;
-  w.total = scan_bytes + 3 * act;
+  w.wpack = base ? base + scan_bytes + 3 * act : nullptr;
+  // K-major copy of both gate weights for the tensor-core kernel: 2 * E * 256 bfloat16.
+  w.total = scan_bytes + 3 * act + up256(static_cast<size_t>(E) * 1024);
   return w;
 }
 
@@ -213,6 +236,8 @@ int rgk_linear_scan(const void* x, const void* a, const uint8_t* reset, const fl
   RGK_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255u) == 0, RGK_EALIGN,
               "workspace must be 256-byte aligned");
   RGK_CHECK_DEVICE();
+  RGK_CUDA(cudaMemsetAsync(workspace, 0, sizeof(int), static_cast<cudaStream_t>(stream)),
+           "cudaMemsetAsync");
   RGK_CUDA(rgk::launch_scan(x, a, reset, nullptr, 0, h0, y_mul, B, T, E, dtype, y, h_last,
                             workspace, static_cast<cudaStream_t>(stream)),
            "scan launch");
@@ -239,14 +264,13 @@ int rgk_rglru_forward(const void* x, const void* segment_pos, int pos_dtype, con
               "workspace of %zu bytes needed, %zu given", w.total, workspace_bytes);
   RGK_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255u) == 0, RGK_EALIGN,
               "workspace must be 256-byte aligned");
-  RGK_REQUIRE(gates_impl != RGK_GATES_TCGEN05, RGK_ESHAPE,
-              "the tcgen05 gate kernel is not available for this call");
   RGK_CHECK_DEVICE();
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int bw = (int)(E / H);
-  RGK_CUDA(rgk::launch_gates_simt(x, segment_pos, pos_dtype, p->a_param, p->gate_x_w, p->gate_x_b,
-                                  p->gate_a_w, p->gate_a_b, B * T, H, bw, dtype, w.a, w.xn, s),
-           "gates launch");
+  RGK_CUDA(cudaMemsetAsync(workspace, 0, sizeof(int), s), "cudaMemsetAsync");
+  if ((rc = run_gates(x, segment_pos, pos_dtype, p, B * T, H, bw, dtype, gates_impl, w.wpack, w.a,
+                      w.xn, workspace, s)))
+    return rc;
   RGK_CUDA(rgk::launch_scan(w.xn, w.a, nullptr, nullptr, 0, h0, nullptr, B, T, E, dtype, y, h_last,
                             w.scan, s),
            "scan launch");
@@ -277,18 +301,16 @@ int rgk_recurrent_path_prefill(const void* xb, const void* yb, const void* segme
               "workspace of %zu bytes needed, %zu given", w.total, workspace_bytes);
   RGK_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255u) == 0, RGK_EALIGN,
               "workspace must be 256-byte aligned");
-  RGK_REQUIRE(gates_impl != RGK_GATES_TCGEN05, RGK_ESHAPE,
-              "the tcgen05 gate kernel is not available for this call");
   RGK_CHECK_DEVICE();
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int bw = (int)(E / H);
+  RGK_CUDA(cudaMemsetAsync(workspace, 0, sizeof(int), s), "cudaMemsetAsync");
   RGK_CUDA(rgk::launch_conv1d_prefill(xb, segment_pos, pos_dtype, p->conv_w, p->conv_b, B, T, E,
                                       dtype, w.c, conv_cache_out, s),
            "conv1d_prefill launch");
-  RGK_CUDA(rgk::launch_gates_simt(w.c, segment_pos, pos_dtype, p->a_param, p->gate_x_w,
-                                  p->gate_x_b, p->gate_a_w, p->gate_a_b, B * T, H, bw, dtype, w.a,
-                                  w.xn, s),
-           "gates launch");
+  if ((rc = run_gates(w.c, segment_pos, pos_dtype, p, B * T, H, bw, dtype, gates_impl, w.wpack, w.a,
+                      w.xn, workspace, s)))
+    return rc;
   RGK_CUDA(rgk::launch_scan(w.xn, w.a, nullptr, nullptr, 0, h0, yb, B, T, E, dtype, out, h_last,
                             w.scan, s),
            "scan launch");
@@ -318,18 +340,16 @@ int rgk_recurrent_path_decode(const void* xb, const void* yb, const void* segmen
   const PathWs w = carve(workspace, B, 1, E, dtype);
   RGK_REQUIRE(workspace != nullptr && workspace_bytes >= w.total, RGK_EWORKSPACE,
               "workspace of %zu bytes needed, %zu given", w.total, workspace_bytes);
-  RGK_REQUIRE(gates_impl != RGK_GATES_TCGEN05, RGK_ESHAPE,
-              "the tcgen05 gate kernel is not available for this call");
   RGK_CHECK_DEVICE();
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int bw = (int)(E / H);
+  RGK_CUDA(cudaMemsetAsync(workspace, 0, sizeof(int), s), "cudaMemsetAsync");
   RGK_CUDA(rgk::launch_conv1d_decode(xb, conv_cache_in, p->conv_w, p->conv_b, B, E, dtype, w.c,
                                      conv_cache_out, s),
            "conv1d_decode launch");
-  RGK_CUDA(rgk::launch_gates_simt(w.c, segment_pos, pos_dtype, p->a_param, p->gate_x_w,
-                                  p->gate_x_b, p->gate_a_w, p->gate_a_b, B, H, bw, dtype, w.a, w.xn,
-                                  s),
-           "gates launch");
+  if ((rc = run_gates(w.c, segment_pos, pos_dtype, p, B, H, bw, dtype, gates_impl, w.wpack, w.a,
+                      w.xn, workspace, s)))
+    return rc;
   RGK_CUDA(rgk::launch_decode_update(w.a, w.xn, h_in, yb, B, E, dtype, out, h_out, s),
            "decode_update launch");
   return RGK_OK;

@@ -1,0 +1,472 @@
+// Block-diagonal gate projections of the RG-LRU on the 5th-generation tensor cores, fused with the
+// gate arithmetic (recurrentgemma torch/layers.py:127-137, 338-353), for bfloat16 and heads of
+// width 256.
+//
+//   z_x = c_h W_x[h] + b_x[h],  z_a = c_h W_a[h] + b_a[h]          (tcgen05.mma, fp32 in TMEM)
+//   a, xn = gate arithmetic(c, z_x, z_a, softplus(a_param), reset)   (epilogue, from TMEM)
+//
+// Work decomposition.  A "group" is one head and one half of its channels: the 128 x-gate and the
+// 128 a-gate output columns of those channels form one N = 256 accumulator, so that an epilogue
+// thread finds both gates of a channel in its own TMEM lane.  A persistent CTA serves one group:
+// the group's weights, pre-packed K-major as [256 (n), 256 (k)] bfloat16 = 128 KiB, are brought in
+// once by TMA and stay in shared memory; the CTA then walks its share of the 128-token tiles.
+// Per tile the A operand (128 tokens x the head's 256 channels, 64 KiB) arrives by TMA in four
+// K-slices of 64 channels (128-byte swizzle), each slice is consumed by four
+// tcgen05.mma.cta_group::1.kind::f16 instructions (M 128, N 256, K 16) and released for the next
+// tile's slice by tcgen05.commit.  The accumulator is double buffered in TMEM (2 x 256 columns), so
+// the tensor pipe works on tile i+1 while the epilogue warps drain tile i.
+//
+// Warp roles (320 threads): warps 0-3 / 4-7 epilogue for even / odd tiles (warp w reads TMEM lanes
+// 32 (w % 4) ..), warp 8 TMA producer, warp 9 TMEM allocation and MMA issue.
+//
+// Every mbarrier wait is bounded; when one expires the CTA raises WsHeader::status, all roles leave
+// their loops, TMEM is released and the kernel returns.
+#include <cuda.h>
+
+#include "rgk_common.cuh"
+#include "rgk_internal.h"
+
+namespace rgk {
+namespace {
+
+constexpr int kHeadWidth = 256;       // K of the contraction = channels per head
+constexpr int kTileM = 128;           // tokens per tile
+constexpr int kTileN = 256;           // accumulator columns: 128 x-gate + 128 a-gate
+constexpr int kHalf = 128;            // channels per group
+constexpr int kKSlice = 64;           // channels per TMA slice (128 bytes)
+constexpr int kNumSlices = kHeadWidth / kKSlice;
+constexpr int kASliceBytes = kTileM * kKSlice * 2;   // 16 KiB
+constexpr int kBSliceBytes = kTileN * kKSlice * 2;   // 32 KiB
+constexpr int kEpiWarps = 8;
+constexpr int kThreadsTc = (kEpiWarps + 2) * 32;
+
+// shared memory map (offsets from a 1024-byte aligned base)
+constexpr int kOffB = 0;
+constexpr int kOffA = kOffB + kNumSlices * kBSliceBytes;            // 131072
+constexpr int kOffConst = kOffA + kNumSlices * kASliceBytes;        // 196608
+constexpr int kConstBytes = 3 * (kHalf / 2) * 4;                    // bias_x, bias_a, -8 softplus (bf16x2)
+constexpr int kOffBar = kOffConst + kConstBytes;                    // 8-byte aligned
+constexpr int kNumBars = 2 * kNumSlices + 1 + 4;                    // a_full[4] a_empty[4] b_full acc_full[2] acc_empty[2]
+constexpr int kOffTmemPtr = kOffBar + kNumBars * 8;
+constexpr int kOffAbort = kOffTmemPtr + 4;
+constexpr int kSmemBytes = kOffAbort + 4 + 1024;                    // + slack for the alignment
+
+constexpr unsigned kWaitLimit = 1u << 20;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false (and raises the CTA's abort flag) when the limit is hit or another
+// role has already aborted.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  for (unsigned i = 0; i < kWaitLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      :: "r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+               :: "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                            uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      :: "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld_32x32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+        "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+        "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
+        "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+        "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major operand slice stored with the 128-byte swizzle:
+// rows of 128 bytes, groups of 8 rows 1024 bytes apart (stride byte offset), descriptor version 1.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((addr & 0x3ffffu) >> 4);        // start address, bits [0,14)
+  d |= static_cast<uint64_t>(1) << 16;                       // leading byte offset (unused with swizzle)
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;               // stride byte offset, bits [32,46)
+  d |= static_cast<uint64_t>(1) << 46;                       // version
+  d |= static_cast<uint64_t>(2) << 61;                       // SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor: D float32, A and B bfloat16, both K-major, M 128, N 256.
+constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((kTileN >> 3) << 17) |
+                            ((kTileM >> 4) << 24);
+
+// packed bfloat16x2 arithmetic, each lane rounded to nearest even (what torch does per element)
+__device__ __forceinline__ uint32_t bmul2(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ uint32_t badd2(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ uint32_t bsub2(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ float ex2f(float v) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
+  return r;
+}
+__device__ __forceinline__ float rcpf(float v) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
+  return r;
+}
+__device__ __forceinline__ float sqrtf_approx(float v) {
+  float r;
+  asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
+  return r;
+}
+
+// Gate arithmetic for two neighbouring channels (torch/layers.py:338-353), every tensor-level
+// result rounded to bfloat16 where torch rounds it.
+//   zx, za   float32 accumulators;  bx2, ba2 packed biases;  m8sp2 = packed -8 softplus(a_param)
+//   c2       packed conv outputs;  returns packed a (reset-masked) and packed normalised input.
+__device__ __forceinline__ void gate_pair(float zx0, float zx1, float za0, float za1, uint32_t bx2,
+                                          uint32_t ba2, uint32_t m8sp2, uint32_t c2, bool is_reset,
+                                          uint32_t& a2, uint32_t& xn2) {
+  constexpr float kLog2e = 1.4426950408889634f;
+  const uint32_t zx2 = badd2(pack_bf16x2(zx0, zx1), bx2);
+  const uint32_t za2 = badd2(pack_bf16x2(za0, za1), ba2);
+  // sigmoid(z) = 1 / (1 + 2^(-z log2 e)); the two gates of a channel share one reciprocal.
+  // Arguments are clamped so that the product of the two denominators stays finite.
+  const float ex0 = ex2f(fminf(-bf16_lo(zx2) * kLog2e, 60.0f));
+  const float ex1 = ex2f(fminf(-bf16_hi(zx2) * kLog2e, 60.0f));
+  const float ea0 = ex2f(fminf(-bf16_lo(za2) * kLog2e, 60.0f));
+  const float ea1 = ex2f(fminf(-bf16_hi(za2) * kLog2e, 60.0f));
+  const float dx0 = 1.0f + ex0, da0 = 1.0f + ea0, dx1 = 1.0f + ex1, da1 = 1.0f + ea1;
+  const float r0 = rcpf(dx0 * da0), r1 = rcpf(dx1 * da1);
+  const uint32_t gx2 = pack_bf16x2(r0 * da0, r1 * da1);
+  const uint32_t ga2 = pack_bf16x2(r0 * dx0, r1 * dx1);
+  // log_a = (-8 gate_a) softplus(a_param): the factor -8 is exact in bfloat16, so it is folded
+  // into the per-channel constant.
+  const uint32_t la2 = bmul2(ga2, m8sp2);
+  const float e0 = ex2f(bf16_lo(la2) * kLog2e), e1 = ex2f(bf16_hi(la2) * kLog2e);
+  a2 = pack_bf16x2(e0, e1);
+  const uint32_t asq2 = pack_bf16x2(e0 * e0, e1 * e1);      // exp(2 log_a)
+  const uint32_t om2 = bsub2(0x3f803f80u, asq2);            // 1 - a^2
+  uint32_t mult2 = pack_bf16x2(sqrtf_approx(bf16_lo(om2)), sqrtf_approx(bf16_hi(om2)));
+  if (is_reset) {
+    mult2 = 0x3f803f80u;
+    a2 = 0u;
+  }
+  xn2 = bmul2(bmul2(c2, gx2), mult2);
+}
+
+__global__ void __launch_bounds__(kThreadsTc, 1)
+gates_tc_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_w,
+                const __nv_bfloat16* __restrict__ c, const void* __restrict__ pos, int pos64,
+                const __nv_bfloat16* __restrict__ a_param, const __nv_bfloat16* __restrict__ bias_x,
+                const __nv_bfloat16* __restrict__ bias_a, int64_t M, int E, int tiles,
+                int ctas_per_group, __nv_bfloat16* __restrict__ a_out,
+                __nv_bfloat16* __restrict__ xn_out, WsHeader* hdr) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  const uint32_t s_base = smem_u32(smem);
+  const uint32_t s_b = s_base + kOffB, s_a = s_base + kOffA;
+  uint32_t* s_const = reinterpret_cast<uint32_t*>(smem + kOffConst);   // [3][64] packed pairs
+  const uint32_t bar0 = s_base + kOffBar;
+  auto bar_a_full = [&](int k) { return bar0 + 8u * k; };
+  auto bar_a_empty = [&](int k) { return bar0 + 8u * (kNumSlices + k); };
+  const uint32_t bar_b_full = bar0 + 8u * (2 * kNumSlices);
+  auto bar_acc_full = [&](int s) { return bar0 + 8u * (2 * kNumSlices + 1 + s); };
+  auto bar_acc_empty = [&](int s) { return bar0 + 8u * (2 * kNumSlices + 3 + s); };
+  volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(smem + kOffTmemPtr);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(smem + kOffAbort);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int group = blockIdx.x / ctas_per_group;          // (head, half)
+  const int slot = blockIdx.x % ctas_per_group;
+  const int head = group >> 1, half = group & 1;
+  const int chan0 = head * kHeadWidth + half * kHalf;     // first channel of the group
+  // tiles slot, slot + ctas_per_group, ... of this group
+  const int n_my = (tiles - slot + ctas_per_group - 1) / ctas_per_group;
+
+  if (threadIdx.x == 0) {
+    *s_abort = 0;
+    for (int k = 0; k < kNumSlices; ++k) { mbar_init(bar_a_full(k), 1); mbar_init(bar_a_empty(k), 1); }
+    mbar_init(bar_b_full, 1);
+    for (int s = 0; s < 2; ++s) { mbar_init(bar_acc_full(s), 1); mbar_init(bar_acc_empty(s), 4); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 9) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 :: "r"(s_base + kOffTmemPtr), "r"(512) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  if (threadIdx.x < 3 * (kHalf / 2)) {
+    // per-channel constants as packed pairs: bias_x, bias_a, -8 softplus(a_param)
+    const int which = threadIdx.x / (kHalf / 2), pair = threadIdx.x % (kHalf / 2);
+    const int e = chan0 + 2 * pair;
+    uint32_t v;
+    if (which == 0) v = *reinterpret_cast<const uint32_t*>(bias_x + e);
+    else if (which == 1) v = *reinterpret_cast<const uint32_t*>(bias_a + e);
+    else {
+      const float s0 = round_bf16(softplus_(__bfloat162float(a_param[e])));
+      const float s1 = round_bf16(softplus_(__bfloat162float(a_param[e + 1])));
+      v = pack_bf16x2(-8.0f * s0, -8.0f * s1);
+    }
+    s_const[which * (kHalf / 2) + pair] = v;
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *s_tmem;
+
+  if (warp == 8) {
+    // ------------------------------ TMA producer --------------------------------------------------
+    if (lane == 0) {
+      mbar_expect_tx(bar_b_full, kNumSlices * kBSliceBytes);
+      for (int k = 0; k < kNumSlices; ++k)
+        tma_load_2d(s_b + k * kBSliceBytes, &map_w, k * kKSlice, group * kTileN, bar_b_full);
+      bool ok = true;
+      for (int it = 0; it < n_my && ok; ++it) {
+        const int tile = slot + it * ctas_per_group;
+        for (int k = 0; k < kNumSlices; ++k) {
+          ok = mbar_wait(bar_a_empty(k), (it & 1) ^ 1, s_abort);
+          if (!ok) break;
+          mbar_expect_tx(bar_a_full(k), kASliceBytes);
+          tma_load_2d(s_a + k * kASliceBytes, &map_c, head * kHeadWidth + k * kKSlice,
+                      tile * kTileM, bar_a_full(k));
+        }
+      }
+    }
+  } else if (warp == 9) {
+    // ------------------------------ MMA issue -----------------------------------------------------
+    if (lane == 0) {
+      bool ok = mbar_wait(bar_b_full, 0, s_abort);
+      for (int it = 0; it < n_my && ok; ++it) {
+        const int s = it & 1;
+        ok = mbar_wait(bar_acc_empty(s), ((it >> 1) & 1) ^ 1, s_abort);
+        if (!ok) break;
+        tc_fence_after();
+        for (int k = 0; k < kNumSlices && ok; ++k) {
+          ok = mbar_wait(bar_a_full(k), it & 1, s_abort);
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll
+          for (int ks = 0; ks < kKSlice / 16; ++ks) {
+            const uint64_t da = smem_desc_sw128(s_a + k * kASliceBytes + ks * 32);
+            const uint64_t db = smem_desc_sw128(s_b + k * kBSliceBytes + ks * 32);
+            tc_mma_bf16(tmem_base + s * kTileN, da, db, kIdesc, (k | ks) != 0 ? 1u : 0u);
+          }
+          tc_commit(bar_a_empty(k));     // slice k may be overwritten once these MMAs are done
+        }
+        if (ok) tc_commit(bar_acc_full(s));
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ------------------------------------------------------
+    const int s = warp >> 2;                 // accumulator stage = tile parity
+    const int lane_base = (warp & 3) * 32;   // TMEM lanes this warp may read
+    bool ok = true;
+    for (int it = s; it < n_my && ok; it += 2) {
+      const int tile = slot + it * ctas_per_group;
+      const int64_t row = (int64_t)tile * kTileM + lane_base + lane;
+      const bool row_ok = row < M;
+      const bool is_reset = row_ok && pos_is_zero(pos, pos64, row);
+      ok = mbar_wait(bar_acc_full(s), (it >> 1) & 1, s_abort);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lane_base) << 16) + s * kTileN;
+      const __nv_bfloat16* c_row = c + row * E + chan0;
+      __nv_bfloat16* a_row = a_out + row * E + chan0;
+      __nv_bfloat16* xn_row = xn_out + row * E + chan0;
+#pragma unroll 1
+      for (int cc = 0; cc < kHalf / 32; ++cc) {
+        uint32_t zx[32], za[32];
+        tc_ld_32x32(t_row + cc * 32, zx);
+        tc_ld_32x32(t_row + kHalf + cc * 32, za);
+        uint4 cv[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          cv[j] = row_ok ? *reinterpret_cast<const uint4*>(c_row + cc * 32 + j * 8)
+                         : make_uint4(0u, 0u, 0u, 0u);
+        tc_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {            // 8 channels per 16-byte store
+          const uint32_t cw[4] = {cv[j].x, cv[j].y, cv[j].z, cv[j].w};
+          uint32_t av[4], xv[4];
+#pragma unroll
+          for (int p = 0; p < 4; ++p) {
+            const int n = j * 8 + p * 2;                 // channel inside this 32-column chunk
+            const int pair = (cc * 32 + n) >> 1;
+            gate_pair(__uint_as_float(zx[n]), __uint_as_float(zx[n + 1]), __uint_as_float(za[n]),
+                      __uint_as_float(za[n + 1]), s_const[pair], s_const[kHalf / 2 + pair],
+                      s_const[kHalf + pair], cw[p], is_reset, av[p], xv[p]);
+          }
+          if (row_ok) {
+            *reinterpret_cast<uint4*>(a_row + cc * 32 + j * 8) = make_uint4(av[0], av[1], av[2], av[3]);
+            *reinterpret_cast<uint4*>(xn_row + cc * 32 + j * 8) = make_uint4(xv[0], xv[1], xv[2], xv[3]);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_acc_empty(s));
+    }
+  }
+
+  // ------------------------------ teardown --------------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *s_abort) atomicExch(&hdr->status, kStatusTimeout);
+  if (warp == 9) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"(512)
+                 : "memory");
+  }
+}
+
+// Packs the two gate weights [H, 256 (k), 256 (n)] into K-major groups [H, 2, 256 (n'), 256 (k)]:
+// rows 0-127 of a group are the x-gate columns of its 128 channels, rows 128-255 the a-gate ones.
+__global__ void pack_gate_weights_kernel(const __nv_bfloat16* __restrict__ wx,
+                                         const __nv_bfloat16* __restrict__ wa, int H,
+                                         __nv_bfloat16* __restrict__ packed) {
+  __shared__ __nv_bfloat16 tile[32][33];
+  // grid: (k tiles = 8, n' tiles = 8, groups = 2H); block 32 x 8
+  const int group = blockIdx.z, head = group >> 1, half = group & 1;
+  const int k0 = blockIdx.x * 32, n0 = blockIdx.y * 32;          // n' in [0, 256)
+  const __nv_bfloat16* src = (n0 < kHalf ? wx : wa) + (int64_t)head * kHeadWidth * kHeadWidth;
+  const int chan = half * kHalf + (n0 % kHalf);                    // source column of n' = n0
+  for (int r = threadIdx.y; r < 32; r += 8)                        // r walks k, x walks n
+    tile[r][threadIdx.x] = src[(int64_t)(k0 + r) * kHeadWidth + chan + threadIdx.x];
+  __syncthreads();
+  __nv_bfloat16* dst = packed + (int64_t)group * kTileN * kHeadWidth;
+  for (int r = threadIdx.y; r < 32; r += 8)                        // r walks n', x walks k
+    dst[(int64_t)(n0 + r) * kHeadWidth + k0 + threadIdx.x] = tile[threadIdx.x][r];
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// 2-D bfloat16 row-major tensor [rows, cols]; box = box_rows x 64 columns, 128-byte swizzle.
+bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return false;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols * 2};
+  const cuuint32_t box[2] = {kKSlice, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+            estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+size_t gates_tc_packed_bytes(int H) { return (size_t)H * 2 * kTileN * kHeadWidth * 2; }
+
+bool gates_tc_supported(int dtype, int bw, int64_t M) {
+  return dtype == 1 && bw == kHeadWidth && M >= 1 && M < ((int64_t)1 << 31);
+}
+
+cudaError_t launch_gates_tc(const void* c, const void* pos, int pos64, const void* a_param,
+                            const void* wx, const void* bx, const void* wa, const void* ba,
+                            int64_t M, int H, void* packed_w, void* a_out, void* xn_out,
+                            void* ws_header, cudaStream_t s) {
+  if (M == 0) return cudaSuccess;
+  using T_ = __nv_bfloat16;
+  const int E = H * kHeadWidth;
+  pack_gate_weights_kernel<<<dim3(kHeadWidth / 32, kTileN / 32, 2 * H), dim3(32, 8), 0, s>>>(
+      (const T_*)wx, (const T_*)wa, H, (T_*)packed_w);
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return err;
+
+  CUtensorMap map_c, map_w;
+  if (!make_map(&map_c, c, (uint64_t)M, (uint64_t)E, kTileM) ||
+      !make_map(&map_w, packed_w, (uint64_t)H * 2 * kTileN, kHeadWidth, kTileN))
+    return cudaErrorInvalidValue;
+
+  static int num_sms = 0;
+  if (num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaFuncSetAttribute(gates_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+  }
+  const int groups = 2 * H;
+  const int tiles = (int)((M + kTileM - 1) / kTileM);
+  int cpg = num_sms / groups;
+  if (cpg < 1) cpg = 1;
+  if (cpg > tiles) cpg = tiles;
+  gates_tc_kernel<<<groups * cpg, kThreadsTc, kSmemBytes, s>>>(
+      map_c, map_w, (const T_*)c, pos, pos64, (const T_*)a_param, (const T_*)bx, (const T_*)ba, M, E,
+      tiles, cpg, (T_*)a_out, (T_*)xn_out, reinterpret_cast<WsHeader*>(ws_header));
+  return cudaGetLastError();
+}
+
+}  // namespace rgk

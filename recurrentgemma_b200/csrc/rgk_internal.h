@@ -25,6 +25,15 @@ cudaError_t launch_gates_simt(const void* c, const void* pos, int pos64, const v
                               int64_t M, int H, int bw, int dtype, void* a_out, void* xn_out,
                               cudaStream_t s);
 
+// gates_tc.cu: the same as launch_gates_simt on tcgen05 tensor cores (bfloat16, head width 256).
+// packed_w: gates_tc_packed_bytes(H) bytes of scratch for the K-major copy of the weights.
+bool gates_tc_supported(int dtype, int bw, int64_t M);
+size_t gates_tc_packed_bytes(int H);
+cudaError_t launch_gates_tc(const void* c, const void* pos, int pos64, const void* a_param,
+                            const void* wx, const void* bx, const void* wa, const void* ba,
+                            int64_t M, int H, void* packed_w, void* a_out, void* xn_out,
+                            void* ws_header, cudaStream_t s);
+
 // scan.cu
 size_t scan_workspace_bytes(int64_t B, int64_t T, int64_t E, int dtype);
 cudaError_t launch_scan(const void* x, const void* a, const uint8_t* reset, const void* pos,

@@ -2,7 +2,7 @@
 // (recurrentgemma torch/layers.py:140-191), as a single-pass chunked parallel scan.
 //
 // Decomposition.  The [B, T, E] problem is cut into tiles of kRows time steps x 64 channels.
-// Inside a tile every thread owns 8 consecutive time steps of one 16-byte pack of channels and
+// Inside a tile every thread owns 4 consecutive time steps of one 16-byte pack of channels and
 // runs them sequentially in registers: pass 1 reduces its steps to the pair (P, H) of the affine
 // map h -> P h + H, the pairs of the tile's sub-chunks are chained through shared memory, and
 // pass 2 replays the same steps from registers starting from the now known incoming state.
@@ -22,15 +22,15 @@
 namespace rgk {
 namespace {
 
-constexpr int kThreads = 128;
+constexpr int kThreads = 256;
 constexpr int kChan = 64;        // channels per tile
-constexpr int kRowsPerThread = 8;
+constexpr int kRowsPerThread = 4;
 constexpr unsigned kSpinLimit = 1u << 21;
 
 template <typename T> struct ScanCfg {
   static constexpr int kPack = Traits<T>::kPack;
   static constexpr int kLanesPerRow = kChan / kPack;          // 8 (bf16) or 16 (f32)
-  static constexpr int kSubs = kThreads / kLanesPerRow;       // 16 or 8 sub-chunks
+  static constexpr int kSubs = kThreads / kLanesPerRow;       // 32 or 16 sub-chunks
   static constexpr int kRows = kSubs * kRowsPerThread;        // 128 or 64 time steps per tile
 };
 
@@ -52,6 +52,28 @@ __device__ __forceinline__ float2 ld_cg_f2(const void* p) {
   float2 v;
   asm volatile("ld.global.cg.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "l"(p) : "memory");
   return v;
+}
+
+
+// gelu_tanh(z) for the bfloat16 path: z * sigmoid(2u) with the constants pre-multiplied by
+// -log2(e), so that it costs 5 float operations and 2 SFU operations.
+__device__ __forceinline__ float gelu_fast(float z) {
+  constexpr float k0 = -1.5957691216057308f * 1.4426950408889634f;
+  constexpr float k1 = k0 * 0.044715f;
+  const float z2 = z * z;
+  const float w = z * fmaf(z2, k1, k0);
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(w));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(e + 1.0f));
+  return z * r;
+}
+
+// Product of two packed bfloat16 pairs, each lane rounded to nearest even: the same value torch
+// produces when it multiplies two bfloat16 tensors.
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
 }
 
 template <typename T, bool kMul>
@@ -91,25 +113,37 @@ scan_kernel(const T* __restrict__ x, const T* __restrict__ a, const uint8_t* __r
   const int64_t row0 = (int64_t)b * T_;
 
   // ---- loads: everything this thread will ever need, issued back to back -------------------------
+  // Rows past the end of the sequence (and packs past the last channel) load a clamped, valid
+  // address instead of branching, so that no load waits for an earlier one to return.
   uint4 araw[kRowsPerThread], xraw[kRowsPerThread], mraw[kRowsPerThread];
   unsigned valid = 0, rst = 0;
+  const int e_ld = chan_ok ? e0 : 0;
 #pragma unroll
   for (int r = 0; r < kRowsPerThread; ++r) {
     const int t = t0 + r;
-    if (chan_ok && t < T_) {
-      valid |= 1u << r;
-      const int64_t off = (row0 + t) * E + e0;
-      araw[r] = ld_stream(a + off);
-      xraw[r] = ld_stream(x + off);
-      if constexpr (kMul) mraw[r] = ld_stream(y_mul + off);
-      bool rs = false;
-      if (reset != nullptr) rs = reset[row0 + t] != 0;
-      else if (pos != nullptr) rs = pos_is_zero(pos, pos64, row0 + t);
-      if (rs) rst |= 1u << r;
+    if (chan_ok && t < T_) valid |= 1u << r;
+    const int64_t row = row0 + min(t, T_ - 1);
+    const int64_t off = row * E + e_ld;
+    araw[r] = ld_stream(a + off);
+    xraw[r] = ld_stream(x + off);
+    if constexpr (kMul) mraw[r] = ld_stream(y_mul + off);
+  }
+  if (reset != nullptr || pos != nullptr) {
+    bool rs[kRowsPerThread];
+#pragma unroll
+    for (int r = 0; r < kRowsPerThread; ++r) {
+      const int64_t row = row0 + min(t0 + r, T_ - 1);
+      rs[r] = (reset != nullptr) ? (reset[row] != 0) : pos_is_zero(pos, pos64, row);
     }
+#pragma unroll
+    for (int r = 0; r < kRowsPerThread; ++r) rst |= rs[r] ? (1u << r) : 0u;
+    // a_t * !reset_t (torch/layers.py:168), applied once to the packed registers.
+#pragma unroll
+    for (int r = 0; r < kRowsPerThread; ++r)
+      if (rst & (1u << r)) araw[r] = make_uint4(0u, 0u, 0u, 0u);
   }
 
-  // ---- pass 1: this thread's 8 steps as an affine map --------------------------------------------
+  // ---- pass 1: this thread's steps as an affine map --------------------------------------------
   {
     float P[kPack], Hh[kPack];
 #pragma unroll
@@ -120,12 +154,10 @@ scan_kernel(const T* __restrict__ x, const T* __restrict__ a, const uint8_t* __r
         float av[kPack], xv[kPack];
         unpack<T>(araw[r], av);
         unpack<T>(xraw[r], xv);
-        const float keep = (rst & (1u << r)) ? 0.0f : 1.0f;
 #pragma unroll
         for (int i = 0; i < kPack; ++i) {
-          const float ae = av[i] * keep;
-          Hh[i] = fmaf(ae, Hh[i], xv[i]);
-          P[i] *= ae;
+          Hh[i] = fmaf(av[i], Hh[i], xv[i]);
+          P[i] *= av[i];
         }
       }
     }
@@ -236,23 +268,37 @@ scan_kernel(const T* __restrict__ x, const T* __restrict__ a, const uint8_t* __r
 #pragma unroll
   for (int r = 0; r < kRowsPerThread; ++r) {
     if (valid & (1u << r)) {
-      float av[kPack], xv[kPack], out[kPack];
+      float av[kPack], xv[kPack];
       unpack<T>(araw[r], av);
       unpack<T>(xraw[r], xv);
-      const float keep = (rst & (1u << r)) ? 0.0f : 1.0f;
 #pragma unroll
-      for (int i = 0; i < kPack; ++i) {
-        h[i] = __fadd_rn(__fmul_rn(av[i] * keep, h[i]), xv[i]);
-        out[i] = rnd<kBf16>(h[i]);
-      }
-      if constexpr (kMul) {
-        float mv[kPack];
-        unpack<T>(mraw[r], mv);
+      for (int i = 0; i < kPack; ++i) h[i] = fmaf(av[i], h[i], xv[i]);
+      uint4 o;
+      if constexpr (kBf16) {
+        // y = bf16(h); the join multiplies it by bf16(gelu(y_mul)) and rounds once more.
+        uint32_t yp[4] = {pack_bf16x2(h[0], h[1]), pack_bf16x2(h[2], h[3]),
+                          pack_bf16x2(h[4], h[5]), pack_bf16x2(h[6], h[7])};
+        if constexpr (kMul) {
+          float mv[kPack];
+          unpack<T>(mraw[r], mv);
 #pragma unroll
-        for (int i = 0; i < kPack; ++i)
-          out[i] = rnd<kBf16>(out[i] * rnd<kBf16>(gelu_tanh_<kBf16>(mv[i])));
+          for (int j = 0; j < 4; ++j)
+            yp[j] = mul_bf16x2(yp[j], pack_bf16x2(gelu_fast(mv[2 * j]), gelu_fast(mv[2 * j + 1])));
+        }
+        o = make_uint4(yp[0], yp[1], yp[2], yp[3]);
+      } else {
+        float out[kPack];
+#pragma unroll
+        for (int i = 0; i < kPack; ++i) out[i] = h[i];
+        if constexpr (kMul) {
+          float mv[kPack];
+          unpack<T>(mraw[r], mv);
+#pragma unroll
+          for (int i = 0; i < kPack; ++i) out[i] = out[i] * gelu_tanh_<false>(mv[i]);
+        }
+        o = pack<T>(out);
       }
-      st_stream(y + (row0 + t0 + r) * E + e0, pack<T>(out));
+      st_stream(y + (row0 + t0 + r) * E + e0, o);
     }
   }
 }
@@ -289,8 +335,9 @@ cudaError_t launch_scan(const void* x, const void* a, const uint8_t* reset, cons
   if (B == 0 || T == 0 || E == 0) return cudaSuccess;
   const ScanLayout L = scan_layout(B, T, E, dtype);
   char* base = static_cast<char*>(ws);
-  // Header (status, ticket) and flags start every launch at zero.
-  cudaError_t err = cudaMemsetAsync(base, 0, L.agg_off, s);
+  // Ticket and flags start every launch at zero (the status word before them belongs to the
+  // caller, which clears it once per API call).
+  cudaError_t err = cudaMemsetAsync(base + sizeof(int), 0, L.agg_off - sizeof(int), s);
   if (err != cudaSuccess) return err;
   WsHeader* hdr = reinterpret_cast<WsHeader*>(base);
   unsigned* flags = reinterpret_cast<unsigned*>(base + L.flags_off);

@@ -197,3 +197,35 @@ def test_errors(rg):
   assert lib.rgk_conv1d_prefill(None, None, 0, None, None, 1, 1, 128, 4, 0, None, None, None) == -1
   assert b"NULL" in lib.rgk_last_error()
   assert lib.rgk_conv1d_prefill(1, 1, 0, 1, 1, 1, 1, 130, 4, 0, 1, None, None) == -2
+
+
+@pytest.mark.parametrize("shape", [(1, 133, 256, 1), (3, 700, 512, 2), (2, 2048, 2560, 10),
+                                   (256, 1, 2560, 10)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_gates_tcgen05_matches_simt_and_oracle(rg, oracle, shape):
+  """The tensor-core gate kernel against the CUDA-core one (both re-create the reference's
+  bfloat16 roundings, so they may differ only where an accumulation-order difference flips a
+  rounding) and, on the smaller shapes, against the oracle."""
+  from recurrentgemma_b200 import _lib
+  b, t, e, h = shape
+  case = C.Case(f"tc_{b}_{t}_{e}", "rglru", "bfloat16", b, t, e, h, pos="multi" if t > 8 else "noreset")
+  p = C.make_params(case)
+  inp = C.make_inputs(case)
+  m = rg.RGLRU(e, h, device=DEV, dtype=torch.bfloat16)
+  m.load_state_dict({k[len("rg_lru."):]: v for k, v in p.items() if k.startswith("rg_lru.")})
+  x, pos = inp["x"].to(DEV), inp["segment_pos"].to(DEV)
+  h0 = C.normal(case.name, "h0", (b, e), 0.5).to(DEV)
+  m.gates_impl = _lib.GATES_TCGEN05
+  y_tc, h_tc = m(x, pos, h0)
+  _lib.workspace_status(_lib.workspace(torch.device(DEV), 1))
+  m.gates_impl = _lib.GATES_SIMT
+  y_si, h_si = m(x, pos, h0)
+  assert_close(y_tc, y_si, 5e-3, "tcgen05 vs simt y")
+  assert_close(h_tc, h_si, 5e-3, "tcgen05 vs simt h")
+  assert float((y_tc != y_si).float().mean()) < 0.02
+  if b * t * e <= 3 * 700 * 512:
+    y_ref, h_ref = oracle.rglru(inp["x"], inp["segment_pos"], p["rg_lru.a_param"],
+                                p["rg_lru.input_gate.w"], p["rg_lru.input_gate.b"],
+                                p["rg_lru.a_gate.w"], p["rg_lru.a_gate.b"], h0.cpu())
+    assert_close(y_tc, y_ref, TOL[torch.bfloat16], "tcgen05 vs oracle y")
+    assert_close(h_tc, h_ref, TOL[torch.bfloat16], "tcgen05 vs oracle h")
