@@ -285,28 +285,54 @@ def run_gpu(args, cfg):
       dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
       e2e_ms = float(tmax.item())
 
-  # per-kernel device times, each through its own entry point (CUDA events on the launch stream)
+  # Per-kernel device times: each stage through its own C-ABI entry point on preallocated buffers,
+  # CUDA events on the launch stream (torch's current stream is the stream the library is given).
   kernels = {}
   if rank == 0:
+    import ctypes
     n_el = b * t * e
     es = 2
+    ksteps = max(5, min(args.steps, 20))
+    sp = stream.cuda_stream
+    dtc = _lib.RGK_BF16
     c = torch.empty_like(xb)
-    ksteps = max(3, min(args.steps, 20))
-    kernels["conv1d_prefill"] = {
-        "ms": _time_loop(lambda: conv(xb, pos), ksteps, stream), "bytes": 2 * n_el * es,
-        "flops": 8 * n_el}
-    c, _ = conv(xb, pos)
+    y2 = torch.empty_like(xb)
+    h_last = torch.empty((b, e), dtype=torch.float32, device=dev)
+    ws = _lib.workspace(dev, _lib.workspace_bytes(b, t, e, dt))
+    prm = lru._params(conv)
+    no_reset = torch.zeros((b, t), dtype=torch.uint8, device=dev)
+    a_t = torch.rand((b, t, e), device=dev).mul_(0.4).add_(0.6).to(dt)
+
+    def k_conv():
+      _lib.check(lib.rgk_conv1d_prefill(xb.data_ptr(), pos.data_ptr(), _lib.RGK_I64,
+                                        conv.w.data_ptr(), conv.b.data_ptr(), b, t, e, 4, dtc,
+                                        c.data_ptr(), None, sp))
+
+    def k_scan(mul):
+      _lib.check(lib.rgk_linear_scan(c.data_ptr(), a_t.data_ptr(), no_reset.data_ptr(), None,
+                                     yb.data_ptr() if mul else None, b, t, e, dtc, y2.data_ptr(),
+                                     h_last.data_ptr(), ws.data_ptr(), ws.numel(), sp))
+
+    def k_lru():
+      _lib.check(lib.rgk_rglru_forward(c.data_ptr(), pos.data_ptr(), _lib.RGK_I64,
+                                       ctypes.byref(prm), None, b, t, e, h, dtc, lru.gates_impl,
+                                       y2.data_ptr(), h_last.data_ptr(), ws.data_ptr(), ws.numel(),
+                                       sp))
+
+    for fn in (k_conv, lambda: k_scan(True), lambda: k_scan(False), k_lru):
+      fn()
+    torch.cuda.synchronize()
+    kernels["conv1d_prefill"] = {"ms": _time_loop(k_conv, ksteps, stream), "bytes": 2 * n_el * es,
+                                 "flops": 8 * n_el}
+    kernels["scan_gelu"] = {"ms": _time_loop(lambda: k_scan(True), ksteps, stream),
+                            "bytes": 4 * n_el * es, "flops": 12 * n_el}
+    # gate projections + gate arithmetic = (RGLRU forward) - (scan without the join)
+    t_lru = _time_loop(k_lru, ksteps, stream)
+    t_scan_plain = _time_loop(lambda: k_scan(False), ksteps, stream)
     gw = p["rg_lru.input_gate.w"].numel() * es
-    a_t = torch.rand_like(c.float()).mul_(0.4).add_(0.6).to(dt)
-    kernels["scan_gelu"] = {
-        "ms": _time_loop(lambda: rg.rnn_scan(c, a_t, pos == -1, None, y_mul=yb), ksteps, stream),
-        "bytes": 4 * n_el * es, "flops": 12 * n_el}
-    # the gate projections + gate arithmetic are timed as (RGLRU forward) - (scan without join)
-    t_lru = _time_loop(lambda: lru(c, pos), ksteps, stream)
-    t_scan_plain = _time_loop(lambda: rg.rnn_scan(c, a_t, pos == -1, None), ksteps, stream)
     kernels["gates"] = {"ms": max(t_lru - t_scan_plain, 1e-6), "bytes": 3 * n_el * es + 2 * gw,
                         "flops": 2 * 2 * b * t * e * (e // h)}
-    del a_t, c
+    del a_t, c, y2
 
   if rank != 0:
     if world > 1:

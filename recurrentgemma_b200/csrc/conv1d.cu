@@ -7,7 +7,7 @@
 namespace rgk {
 namespace {
 
-constexpr int kConvRows = 32;     // output rows per thread
+constexpr int kConvRows = 16;     // output rows per thread
 constexpr int kConvThreads = 128; // packs (of 16 bytes) per block
 
 // One tap: acc <- round(acc + round(x * w)); the first tap initialises acc (the reference starts
@@ -22,81 +22,119 @@ __device__ __forceinline__ void tap(float (&acc)[kPack], const float (&x)[kPack]
   }
 }
 
+// 16-byte packs with the arithmetic of the tensor dtype: float32 lanes, or bfloat16 pairs whose
+// products and sums are rounded to bfloat16 by the packed instructions themselves.
+__device__ __forceinline__ uint32_t bf2_mul(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ uint32_t bf2_add(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+template <typename T> struct PackOps;
+template <> struct PackOps<float> {
+  static __device__ __forceinline__ uint4 mul(const uint4& a, const uint4& b) {
+    return make_uint4(__float_as_uint(__fmul_rn(__uint_as_float(a.x), __uint_as_float(b.x))),
+                      __float_as_uint(__fmul_rn(__uint_as_float(a.y), __uint_as_float(b.y))),
+                      __float_as_uint(__fmul_rn(__uint_as_float(a.z), __uint_as_float(b.z))),
+                      __float_as_uint(__fmul_rn(__uint_as_float(a.w), __uint_as_float(b.w))));
+  }
+  static __device__ __forceinline__ uint4 add(const uint4& a, const uint4& b) {
+    return make_uint4(__float_as_uint(__fadd_rn(__uint_as_float(a.x), __uint_as_float(b.x))),
+                      __float_as_uint(__fadd_rn(__uint_as_float(a.y), __uint_as_float(b.y))),
+                      __float_as_uint(__fadd_rn(__uint_as_float(a.z), __uint_as_float(b.z))),
+                      __float_as_uint(__fadd_rn(__uint_as_float(a.w), __uint_as_float(b.w))));
+  }
+  // x * 0 keeps the sign of x, as the reference's in-place masking does
+  static __device__ __forceinline__ uint4 zero_like(const uint4& a) {
+    return make_uint4(a.x & 0x80000000u, a.y & 0x80000000u, a.z & 0x80000000u, a.w & 0x80000000u);
+  }
+};
+template <> struct PackOps<__nv_bfloat16> {
+  static __device__ __forceinline__ uint4 mul(const uint4& a, const uint4& b) {
+    return make_uint4(bf2_mul(a.x, b.x), bf2_mul(a.y, b.y), bf2_mul(a.z, b.z), bf2_mul(a.w, b.w));
+  }
+  static __device__ __forceinline__ uint4 add(const uint4& a, const uint4& b) {
+    return make_uint4(bf2_add(a.x, b.x), bf2_add(a.y, b.y), bf2_add(a.z, b.z), bf2_add(a.w, b.w));
+  }
+  static __device__ __forceinline__ uint4 zero_like(const uint4& a) {
+    return make_uint4(a.x & 0x80008000u, a.y & 0x80008000u, a.z & 0x80008000u, a.w & 0x80008000u);
+  }
+};
+
 template <typename T>
 __global__ void __launch_bounds__(kConvThreads)
 conv1d_prefill_kernel(const T* __restrict__ x, const void* __restrict__ pos, int pos64,
                       const T* __restrict__ w, const T* __restrict__ bias, int T_, int E,
                       T* __restrict__ out, T* __restrict__ cache_out) {
   constexpr int kPack = Traits<T>::kPack;
-  constexpr bool kBf16 = Traits<T>::kBf16;
+  using Ops = PackOps<T>;
   const int pack_idx = blockIdx.x * kConvThreads + threadIdx.x;
   const int e0 = pack_idx * kPack;
   if (e0 >= E) return;
   const int b = blockIdx.z;
   const int t_begin = blockIdx.y * kConvRows;
-  const int t_end = min(t_begin + kConvRows, T_);
   const int64_t row0 = (int64_t)b * T_;
 
-  float wv[4][kPack], bv[kPack];
+  // All rows this thread touches (3 halo rows + kConvRows), loaded back to back; rows outside the
+  // sequence read a clamped address and are never used.
+  uint4 xr[kConvRows + 3];
 #pragma unroll
-  for (int k = 0; k < 4; ++k) unpack<T>(*reinterpret_cast<const uint4*>(w + (int64_t)k * E + e0), wv[k]);
-  unpack<T>(*reinterpret_cast<const uint4*>(bias + e0), bv);
-
-  // Rolling window: xm1/xm2/xm3 = rows t-1, t-2, t-3; n1, n2 = "row t-1 / t-2 starts no document".
-  float xm1[kPack], xm2[kPack], xm3[kPack], xc[kPack];
-  bool n1 = true, n2 = true;
-#pragma unroll
-  for (int i = 0; i < kPack; ++i) xm1[i] = xm2[i] = xm3[i] = 0.0f;
-  if (t_begin >= 1) {
-    unpack<T>(ld_stream(x + (row0 + t_begin - 1) * E + e0), xm1);
-    n1 = !pos_is_zero(pos, pos64, row0 + t_begin - 1);
+  for (int i = 0; i < kConvRows + 3; ++i) {
+    const int t = min(max(t_begin - 3 + i, 0), T_ - 1);
+    xr[i] = ld_stream(x + (row0 + t) * E + e0);
   }
-  if (t_begin >= 2) {
-    unpack<T>(ld_stream(x + (row0 + t_begin - 2) * E + e0), xm2);
-    n2 = !pos_is_zero(pos, pos64, row0 + t_begin - 2);
+  // nz bit i: row t_begin - 3 + i starts no document (rows outside the sequence count as set).
+  unsigned nz = 0;
+#pragma unroll
+  for (int i = 0; i < kConvRows + 3; ++i) {
+    const int t = t_begin - 3 + i;
+    const bool inside = t >= 0 && t < T_;
+    const bool z = pos_is_zero(pos, pos64, row0 + min(max(t, 0), T_ - 1));
+    if (!(inside && z)) nz |= 1u << i;
   }
-  if (t_begin >= 3) unpack<T>(ld_stream(x + (row0 + t_begin - 3) * E + e0), xm3);
+  uint4 wv[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) wv[k] = *reinterpret_cast<const uint4*>(w + (int64_t)k * E + e0);
+  const uint4 bv = *reinterpret_cast<const uint4*>(bias + e0);
 
-  bool n0 = true;
-  for (int t = t_begin; t < t_end; ++t) {
-    unpack<T>(ld_stream(x + (row0 + t) * E + e0), xc);
-    n0 = !pos_is_zero(pos, pos64, row0 + t);
-    float acc[kPack];
-    tap<kBf16, kPack>(acc, xc, wv[3], true);
-    // Tap s reaches row t-s and survives while rows t-s+1 .. t start no document.  A masked or
-    // left-padded tap contributes round(acc + 0) = acc, so it is skipped.
-    if (t >= 1 && n0) tap<kBf16, kPack>(acc, xm1, wv[2], false);
-    if (t >= 2 && n0 && n1) tap<kBf16, kPack>(acc, xm2, wv[1], false);
-    if (t >= 3 && n0 && n1 && n2) tap<kBf16, kPack>(acc, xm3, wv[0], false);
 #pragma unroll
-    for (int i = 0; i < kPack; ++i) acc[i] = rnd<kBf16>(__fadd_rn(acc[i], bv[i]));
-    st_stream(out + (row0 + t) * E + e0, pack<T>(acc));
-    if (t + 1 < t_end) {
-#pragma unroll
-      for (int i = 0; i < kPack; ++i) { xm3[i] = xm2[i]; xm2[i] = xm1[i]; xm1[i] = xc[i]; }
-      n2 = n1; n1 = n0;
+  for (int r = 0; r < kConvRows; ++r) {
+    const int t = t_begin + r;
+    if (t < T_) {
+      const int i = r + 3;                       // index of row t inside xr
+      // Tap s reaches row t-s and survives while rows t-s+1 .. t start no document.  A masked or
+      // left-padded tap contributes round(acc + 0) = acc, so it is skipped
+      // (torch/layers.py:487-517, 575-607).
+      uint4 acc = Ops::mul(xr[i], wv[3]);
+      const bool n0 = (nz >> i) & 1u, n1 = (nz >> (i - 1)) & 1u, n2 = (nz >> (i - 2)) & 1u;
+      if (t >= 1 && n0) acc = Ops::add(acc, Ops::mul(xr[i - 1], wv[2]));
+      if (t >= 2 && n0 && n1) acc = Ops::add(acc, Ops::mul(xr[i - 2], wv[1]));
+      if (t >= 3 && n0 && n1 && n2) acc = Ops::add(acc, Ops::mul(xr[i - 3], wv[0]));
+      acc = Ops::add(acc, bv);
+      st_stream(out + (row0 + t) * E + e0, acc);
     }
   }
 
   // The block that owns the last row also writes the cache: rows T-3 .. T-1 of the input, each
   // multiplied by (0 or 1) for the document starts that follow it (torch/layers.py:497-508, 526).
-  if (cache_out != nullptr && t_end == T_ && t_begin < T_) {
-    // Here xc = row T-1, xm1 = row T-2, xm2 = row T-3; n0 = n[T-1], n1 = n[T-2].
-    float r[kPack];
+  if (cache_out != nullptr && t_begin < T_ && t_begin + kConvRows >= T_) {
+    const int il = T_ - 1 - t_begin + 3;         // index of row T-1 inside xr (>= 3)
     T* c = cache_out + (int64_t)b * 3 * E + e0;
-    {
-      const float k = (T_ >= 3) ? ((n0 && n1) ? 1.0f : 0.0f) : 0.0f;
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-      for (int i = 0; i < kPack; ++i) r[i] = (T_ >= 3) ? xm2[i] * k : 0.0f;
-      *reinterpret_cast<uint4*>(c) = pack<T>(r);
+    for (int r = 0; r < kConvRows; ++r) {
+      if (r + 3 == il) {
+        const bool n0 = (nz >> (r + 3)) & 1u, n1 = (nz >> (r + 2)) & 1u;
+        const uint4 x2 = xr[r + 1], x1 = xr[r + 2], x0 = xr[r + 3];   // rows T-3, T-2, T-1
+        *reinterpret_cast<uint4*>(c) = (T_ >= 3) ? ((n0 && n1) ? x2 : Ops::zero_like(x2)) : zero;
+        *reinterpret_cast<uint4*>(c + E) = (T_ >= 2) ? (n0 ? x1 : Ops::zero_like(x1)) : zero;
+        *reinterpret_cast<uint4*>(c + 2 * (int64_t)E) = x0;
+      }
     }
-    {
-      const float k = n0 ? 1.0f : 0.0f;
-#pragma unroll
-      for (int i = 0; i < kPack; ++i) r[i] = (T_ >= 2) ? xm1[i] * k : 0.0f;
-      *reinterpret_cast<uint4*>(c + E) = pack<T>(r);
-    }
-    *reinterpret_cast<uint4*>(c + 2 * (int64_t)E) = pack<T>(xc);
   }
 }
 

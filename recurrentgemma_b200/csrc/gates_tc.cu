@@ -16,8 +16,9 @@
 // tile's slice by tcgen05.commit.  The accumulator is double buffered in TMEM (2 x 256 columns), so
 // the tensor pipe works on tile i+1 while the epilogue warps drain tile i.
 //
-// Warp roles (320 threads): warps 0-3 / 4-7 epilogue for even / odd tiles (warp w reads TMEM lanes
-// 32 (w % 4) ..), warp 8 TMA producer, warp 9 TMEM allocation and MMA issue.
+// Warp roles (576 threads): warps 0-7 / 8-15 epilogue for even / odd tiles (warp w reads TMEM lanes
+// 32 (w % 4) .. and the channel half (w / 4) % 2 of the tile), warp 16 TMA producer, warp 17 TMEM
+// allocation and MMA issue.
 //
 // Every mbarrier wait is bounded; when one expires the CTA raises WsHeader::status, all roles leave
 // their loops, TMEM is released and the kernel returns.
@@ -37,7 +38,7 @@ constexpr int kKSlice = 64;           // channels per TMA slice (128 bytes)
 constexpr int kNumSlices = kHeadWidth / kKSlice;
 constexpr int kASliceBytes = kTileM * kKSlice * 2;   // 16 KiB
 constexpr int kBSliceBytes = kTileN * kKSlice * 2;   // 32 KiB
-constexpr int kEpiWarps = 8;
+constexpr int kEpiWarps = 16;
 constexpr int kThreadsTc = (kEpiWarps + 2) * 32;
 
 // shared memory map (offsets from a 1024-byte aligned base)
@@ -245,10 +246,10 @@ gates_tc_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_constant
     *s_abort = 0;
     for (int k = 0; k < kNumSlices; ++k) { mbar_init(bar_a_full(k), 1); mbar_init(bar_a_empty(k), 1); }
     mbar_init(bar_b_full, 1);
-    for (int s = 0; s < 2; ++s) { mbar_init(bar_acc_full(s), 1); mbar_init(bar_acc_empty(s), 4); }
+    for (int s = 0; s < 2; ++s) { mbar_init(bar_acc_full(s), 1); mbar_init(bar_acc_empty(s), kEpiWarps / 2); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 9) {
+  if (warp == kEpiWarps + 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                  :: "r"(s_base + kOffTmemPtr), "r"(512) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -272,7 +273,7 @@ gates_tc_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = *s_tmem;
 
-  if (warp == 8) {
+  if (warp == kEpiWarps) {
     // ------------------------------ TMA producer --------------------------------------------------
     if (lane == 0) {
       mbar_expect_tx(bar_b_full, kNumSlices * kBSliceBytes);
@@ -290,7 +291,7 @@ gates_tc_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_constant
         }
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == kEpiWarps + 1) {
     // ------------------------------ MMA issue -----------------------------------------------------
     if (lane == 0) {
       bool ok = mbar_wait(bar_b_full, 0, s_abort);
@@ -316,43 +317,52 @@ gates_tc_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_constant
     }
   } else {
     // ------------------------------ epilogue ------------------------------------------------------
-    const int s = warp >> 2;                 // accumulator stage = tile parity
+    const int s = warp >> 3;                 // accumulator stage = tile parity
     const int lane_base = (warp & 3) * 32;   // TMEM lanes this warp may read
+    const int col_half = (warp >> 2) & 1;    // which 64 of the tile's 128 channels
     bool ok = true;
     for (int it = s; it < n_my && ok; it += 2) {
       const int tile = slot + it * ctas_per_group;
       const int64_t row = (int64_t)tile * kTileM + lane_base + lane;
       const bool row_ok = row < M;
       const bool is_reset = row_ok && pos_is_zero(pos, pos64, row);
+      const int64_t row_ld = row_ok ? row : 0;   // rows past the end read row 0 and store nothing
+      const __nv_bfloat16* c_row = c + row_ld * E + chan0 + col_half * 64;
+      __nv_bfloat16* a_row = a_out + row_ld * E + chan0 + col_half * 64;
+      __nv_bfloat16* xn_row = xn_out + row_ld * E + chan0 + col_half * 64;
+      // conv outputs of the first 32 channels, in flight while the accumulator is awaited
+      uint4 cv[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) cv[j] = *reinterpret_cast<const uint4*>(c_row + j * 8);
       ok = mbar_wait(bar_acc_full(s), (it >> 1) & 1, s_abort);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lane_base) << 16) + s * kTileN;
-      const __nv_bfloat16* c_row = c + row * E + chan0;
-      __nv_bfloat16* a_row = a_out + row * E + chan0;
-      __nv_bfloat16* xn_row = xn_out + row * E + chan0;
-#pragma unroll 1
-      for (int cc = 0; cc < kHalf / 32; ++cc) {
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lane_base) << 16) + s * kTileN +
+                             col_half * 64;
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
         uint32_t zx[32], za[32];
         tc_ld_32x32(t_row + cc * 32, zx);
         tc_ld_32x32(t_row + kHalf + cc * 32, za);
-        uint4 cv[4];
+        uint4 cw[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-          cv[j] = row_ok ? *reinterpret_cast<const uint4*>(c_row + cc * 32 + j * 8)
-                         : make_uint4(0u, 0u, 0u, 0u);
+        for (int j = 0; j < 4; ++j) cw[j] = cv[j];
+        if (cc == 0) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) cv[j] = *reinterpret_cast<const uint4*>(c_row + 32 + j * 8);
+        }
         tc_wait_ld();
 #pragma unroll
         for (int j = 0; j < 4; ++j) {            // 8 channels per 16-byte store
-          const uint32_t cw[4] = {cv[j].x, cv[j].y, cv[j].z, cv[j].w};
+          const uint32_t cp[4] = {cw[j].x, cw[j].y, cw[j].z, cw[j].w};
           uint32_t av[4], xv[4];
 #pragma unroll
           for (int p = 0; p < 4; ++p) {
             const int n = j * 8 + p * 2;                 // channel inside this 32-column chunk
-            const int pair = (cc * 32 + n) >> 1;
+            const int pair = (col_half * 64 + cc * 32 + n) >> 1;
             gate_pair(__uint_as_float(zx[n]), __uint_as_float(zx[n + 1]), __uint_as_float(za[n]),
                       __uint_as_float(za[n + 1]), s_const[pair], s_const[kHalf / 2 + pair],
-                      s_const[kHalf + pair], cw[p], is_reset, av[p], xv[p]);
+                      s_const[kHalf + pair], cp[p], is_reset, av[p], xv[p]);
           }
           if (row_ok) {
             *reinterpret_cast<uint4*>(a_row + cc * 32 + j * 8) = make_uint4(av[0], av[1], av[2], av[3]);
@@ -370,7 +380,7 @@ gates_tc_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_constant
   tc_fence_before();
   __syncthreads();
   if (threadIdx.x == 0 && *s_abort) atomicExch(&hdr->status, kStatusTimeout);
-  if (warp == 9) {
+  if (warp == kEpiWarps + 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"(512)
                  : "memory");

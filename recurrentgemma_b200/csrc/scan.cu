@@ -185,8 +185,9 @@ scan_kernel(const T* __restrict__ x, const T* __restrict__ a, const uint8_t* __r
     } else {
       agg[rec * kChan + tid] = make_float2(P, Hh);
     }
-    __threadfence();
   }
+  // The barrier orders the 64 record stores before thread 0's release store, and a release is
+  // cumulative over that order: a tile that acquires the flag sees the whole record.
   __syncthreads();
   if (tid == 0) st_release(&flags[rec], tt == 0 ? 2u : 1u);
 
@@ -241,7 +242,6 @@ scan_kernel(const T* __restrict__ x, const T* __restrict__ a, const uint8_t* __r
     inc.x = fmaf(t0v.x, hin0, t0v.y);
     inc.y = fmaf(t1v.x, hin1, t1v.y);
     *(reinterpret_cast<float2*>(incl + rec * kChan) + lane) = inc;
-    __threadfence();
     __syncwarp();
     if (lane == 0) st_release(&flags[rec], 2u);
   }
