@@ -104,7 +104,7 @@ class ClockSampler:
       self.out = open(self.path, "w")
       self.proc = subprocess.Popen(
           ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms",
-           "50", "-i", str(self.index)], stdout=self.out, stderr=subprocess.DEVNULL)
+           "20", "-i", str(self.index)], stdout=self.out, stderr=subprocess.DEVNULL)
     except OSError:
       self.proc = None
 
@@ -369,7 +369,7 @@ def run_gpu(args, cfg):
       "cpu_baseline": None if cpu is None else {k: cpu[k] for k in
                                                 ("value", "unit", "cores", "kind", "sample")},
       "clocks": clk,
-      "gpu_launches": 3 * args.steps,
+      "gpu_launches": 4 * args.steps,
   }
   if e2e_ms is not None:
     line["e2e"] = {"value": world * tokens / (e2e_ms * 1e-3), "unit": UNIT,
@@ -383,7 +383,7 @@ def run_gpu(args, cfg):
 def main():
   ap = argparse.ArgumentParser()
   ap.add_argument("--gpus", type=int, default=1)
-  ap.add_argument("--steps", type=int, default=20)
+  ap.add_argument("--steps", type=int, default=200)
   ap.add_argument("--warmup", type=int, default=3)
   ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
   ap.add_argument("--batch", type=int, default=None, help="override the per-GPU batch (profiling)")

@@ -23,6 +23,7 @@
 // Every mbarrier wait is bounded; when one expires the CTA raises WsHeader::status, all roles leave
 // their loops, TMEM is released and the kernel returns.
 #include <cuda.h>
+#include <cstdlib>
 
 #include "rgk_common.cuh"
 #include "rgk_internal.h"
@@ -47,10 +48,13 @@ constexpr int kOffA = kOffB + kNumSlices * kBSliceBytes;            // 131072
 constexpr int kOffConst = kOffA + kNumSlices * kASliceBytes;        // 196608
 constexpr int kConstBytes = 3 * (kHalf / 2) * 4;                    // bias_x, bias_a, -8 softplus (bf16x2)
 constexpr int kOffBar = kOffConst + kConstBytes;                    // 8-byte aligned
-constexpr int kNumBars = 2 * kNumSlices + 1 + 4;                    // a_full[4] a_empty[4] b_full acc_full[2] acc_empty[2]
+constexpr int kNumBars = 3 * kNumSlices + 1 + 4;                    // a_full[2][4] a_empty[4] b_full acc_full[2] acc_empty[2]
 constexpr int kOffTmemPtr = kOffBar + kNumBars * 8;
 constexpr int kOffAbort = kOffTmemPtr + 4;
-constexpr int kSmemBytes = kOffAbort + 4 + 1024;                    // + slack for the alignment
+constexpr int kOffStage = (kOffAbort + 4 + 15) & ~15;               // per-warp store staging
+constexpr int kStageBytes = 32 * 64;                                // 32 rows x 32 channels
+constexpr int kSmemBytes = kOffStage + kEpiWarps * kStageBytes + 1024;  // + slack for the alignment
+static_assert(kSmemBytes <= 232448, "exceeds the 227 KiB of shared memory a CTA may use");
 
 constexpr unsigned kWaitLimit = 1u << 20;
 
@@ -212,6 +216,7 @@ __device__ __forceinline__ void gate_pair(float zx0, float zx1, float za0, float
   xn2 = bmul2(bmul2(c2, gx2), mult2);
 }
 
+template <int kDbg>
 __global__ void __launch_bounds__(kThreadsTc, 1)
 gates_tc_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_w,
                 const __nv_bfloat16* __restrict__ c, const void* __restrict__ pos, int pos64,
@@ -226,11 +231,14 @@ gates_tc_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_constant
   const uint32_t s_b = s_base + kOffB, s_a = s_base + kOffA;
   uint32_t* s_const = reinterpret_cast<uint32_t*>(smem + kOffConst);   // [3][64] packed pairs
   const uint32_t bar0 = s_base + kOffBar;
-  auto bar_a_full = [&](int k) { return bar0 + 8u * k; };
-  auto bar_a_empty = [&](int k) { return bar0 + 8u * (kNumSlices + k); };
-  const uint32_t bar_b_full = bar0 + 8u * (2 * kNumSlices);
-  auto bar_acc_full = [&](int s) { return bar0 + 8u * (2 * kNumSlices + 1 + s); };
-  auto bar_acc_empty = [&](int s) { return bar0 + 8u * (2 * kNumSlices + 3 + s); };
+  // "slice k is loaded" has one barrier per tile parity: its waiters (the MMA thread and the
+  // epilogue warps of that parity) then see every one of its phases, which a waiter that skips
+  // every other tile of a single barrier would not.
+  auto bar_a_full = [&](int k, int par) { return bar0 + 8u * (par * kNumSlices + k); };
+  auto bar_a_empty = [&](int k) { return bar0 + 8u * (2 * kNumSlices + k); };
+  const uint32_t bar_b_full = bar0 + 8u * (3 * kNumSlices);
+  auto bar_acc_full = [&](int s) { return bar0 + 8u * (3 * kNumSlices + 1 + s); };
+  auto bar_acc_empty = [&](int s) { return bar0 + 8u * (3 * kNumSlices + 3 + s); };
   volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(smem + kOffTmemPtr);
   volatile int* s_abort = reinterpret_cast<volatile int*>(smem + kOffAbort);
 
@@ -244,7 +252,13 @@ gates_tc_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_constant
 
   if (threadIdx.x == 0) {
     *s_abort = 0;
-    for (int k = 0; k < kNumSlices; ++k) { mbar_init(bar_a_full(k), 1); mbar_init(bar_a_empty(k), 1); }
+    // A slice is released by the MMA commit and, for the two slices that hold this group's own
+    // channels, by the four epilogue warps that copy their conv values out of it.
+    for (int k = 0; k < kNumSlices; ++k) {
+      mbar_init(bar_a_full(k, 0), 1);
+      mbar_init(bar_a_full(k, 1), 1);
+      mbar_init(bar_a_empty(k), (k >> 1) == half ? 5 : 1);
+    }
     mbar_init(bar_b_full, 1);
     for (int s = 0; s < 2; ++s) { mbar_init(bar_acc_full(s), 1); mbar_init(bar_acc_empty(s), kEpiWarps / 2); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -285,9 +299,9 @@ gates_tc_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_constant
         for (int k = 0; k < kNumSlices; ++k) {
           ok = mbar_wait(bar_a_empty(k), (it & 1) ^ 1, s_abort);
           if (!ok) break;
-          mbar_expect_tx(bar_a_full(k), kASliceBytes);
+          mbar_expect_tx(bar_a_full(k, it & 1), kASliceBytes);
           tma_load_2d(s_a + k * kASliceBytes, &map_c, head * kHeadWidth + k * kKSlice,
-                      tile * kTileM, bar_a_full(k));
+                      tile * kTileM, bar_a_full(k, it & 1));
         }
       }
     }
@@ -301,7 +315,7 @@ gates_tc_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_constant
         if (!ok) break;
         tc_fence_after();
         for (int k = 0; k < kNumSlices && ok; ++k) {
-          ok = mbar_wait(bar_a_full(k), it & 1, s_abort);
+          ok = mbar_wait(bar_a_full(k, it & 1), (it >> 1) & 1, s_abort);
           if (!ok) break;
           tc_fence_after();
 #pragma unroll
@@ -326,48 +340,80 @@ gates_tc_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_constant
       const int64_t row = (int64_t)tile * kTileM + lane_base + lane;
       const bool row_ok = row < M;
       const bool is_reset = row_ok && pos_is_zero(pos, pos64, row);
-      const int64_t row_ld = row_ok ? row : 0;   // rows past the end read row 0 and store nothing
-      const __nv_bfloat16* c_row = c + row_ld * E + chan0 + col_half * 64;
-      __nv_bfloat16* a_row = a_out + row_ld * E + chan0 + col_half * 64;
-      __nv_bfloat16* xn_row = xn_out + row_ld * E + chan0 + col_half * 64;
-      // conv outputs of the first 32 channels, in flight while the accumulator is awaited
-      uint4 cv[4];
+      // The conv outputs this thread gates are already on chip: the TMA slice half*2 + col_half of
+      // the A operand holds this group's 64 channels of every row.  Row r of a slice is 128 bytes
+      // at r * 128 with its 16-byte units XOR-ed by r % 8 (the 128-byte swizzle).
+      const int my_slice = half * 2 + col_half;
+      ok = mbar_wait(bar_a_full(my_slice, s), (it >> 1) & 1, s_abort);
+      if (!ok) break;
+      uint4 cv[8];
+      {
+        const int r = lane_base + lane;
+        const uint8_t* a_row_smem = smem + kOffA + my_slice * kASliceBytes + r * 128;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) cv[j] = *reinterpret_cast<const uint4*>(c_row + j * 8);
+        for (int u = 0; u < 8; ++u)
+          cv[u] = *reinterpret_cast<const uint4*>(a_row_smem + ((u ^ (r & 7)) << 4));
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_a_empty(my_slice));
       ok = mbar_wait(bar_acc_full(s), (it >> 1) & 1, s_abort);
       if (!ok) break;
       tc_fence_after();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lane_base) << 16) + s * kTileN +
                              col_half * 64;
 #pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
+      for (int cc = 0; cc < (kDbg == 4 ? 0 : 2); ++cc) {
         uint32_t zx[32], za[32];
         tc_ld_32x32(t_row + cc * 32, zx);
         tc_ld_32x32(t_row + kHalf + cc * 32, za);
         uint4 cw[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) cw[j] = cv[j];
-        if (cc == 0) {
-#pragma unroll
-          for (int j = 0; j < 4; ++j) cv[j] = *reinterpret_cast<const uint4*>(c_row + 32 + j * 8);
-        }
+        for (int j = 0; j < 4; ++j) cw[j] = cv[cc * 4 + j];
         tc_wait_ld();
+        uint4 av[4], xv[4];                      // 8 channels per 16-byte piece
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {            // 8 channels per 16-byte store
+        for (int j = 0; j < 4; ++j) {
           const uint32_t cp[4] = {cw[j].x, cw[j].y, cw[j].z, cw[j].w};
-          uint32_t av[4], xv[4];
+          uint32_t ap[4], xp[4];
 #pragma unroll
           for (int p = 0; p < 4; ++p) {
             const int n = j * 8 + p * 2;                 // channel inside this 32-column chunk
             const int pair = (col_half * 64 + cc * 32 + n) >> 1;
+            if constexpr (kDbg == 1 || kDbg >= 3) {
+              ap[p] = zx[n] ^ za[n + 1] ^ cp[p]; xp[p] = zx[n + 1] ^ za[n] ^ s_const[pair];
+            } else
             gate_pair(__uint_as_float(zx[n]), __uint_as_float(zx[n + 1]), __uint_as_float(za[n]),
                       __uint_as_float(za[n + 1]), s_const[pair], s_const[kHalf / 2 + pair],
-                      s_const[kHalf + pair], cp[p], is_reset, av[p], xv[p]);
+                      s_const[kHalf + pair], cp[p], is_reset, ap[p], xp[p]);
           }
-          if (row_ok) {
-            *reinterpret_cast<uint4*>(a_row + cc * 32 + j * 8) = make_uint4(av[0], av[1], av[2], av[3]);
-            *reinterpret_cast<uint4*>(xn_row + cc * 32 + j * 8) = make_uint4(xv[0], xv[1], xv[2], xv[3]);
+          av[j] = make_uint4(ap[0], ap[1], ap[2], ap[3]);
+          xv[j] = make_uint4(xp[0], xp[1], xp[2], xp[3]);
+        }
+        // A thread holds 64 bytes of its own row, so storing from here would touch 32 rows per
+        // instruction, half a sector each.  The warp's 32 x 32 block is transposed through a
+        // 2 KiB staging buffer (16-byte pieces XOR-swizzled by row pair: conflict free both ways)
+        // so that every store instruction writes 8 rows x 64 contiguous bytes.
+        uint8_t* stage = smem + kOffStage + warp * kStageBytes;
+        const int64_t tile_row0 = (int64_t)tile * kTileM + lane_base;
+        const int chan_chunk = chan0 + col_half * 64 + cc * 32;
+#pragma unroll
+        for (int which = 0; which < 2; ++which) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            *reinterpret_cast<uint4*>(stage + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) =
+                which == 0 ? av[j] : xv[j];
+          __syncwarp();
+          __nv_bfloat16* dst = which == 0 ? a_out : xn_out;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int r = (lane >> 2) + 8 * k, piece = lane & 3;
+            const uint4 v = *reinterpret_cast<const uint4*>(stage + r * 64 +
+                                                            ((piece ^ ((r >> 1) & 3)) << 4));
+            const int64_t grow = tile_row0 + r;
+            if (grow < M && kDbg < 2)
+              *reinterpret_cast<uint4*>(dst + grow * E + chan_chunk + piece * 8) = v;
           }
+          __syncwarp();
         }
       }
       tc_fence_before();
@@ -466,16 +512,23 @@ cudaError_t launch_gates_tc(const void* c, const void* pos, int pos64, const voi
     int dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
-    cudaFuncSetAttribute(gates_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    cudaFuncSetAttribute(gates_tc_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    cudaFuncSetAttribute(gates_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    cudaFuncSetAttribute(gates_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    cudaFuncSetAttribute(gates_tc_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    cudaFuncSetAttribute(gates_tc_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
   }
+  const char* dbg_env = getenv("RGK_GATES_DEBUG");
+  const int dbg = dbg_env ? atoi(dbg_env) : 0;
   const int groups = 2 * H;
   const int tiles = (int)((M + kTileM - 1) / kTileM);
   int cpg = num_sms / groups;
   if (cpg < 1) cpg = 1;
   if (cpg > tiles) cpg = tiles;
-  gates_tc_kernel<<<groups * cpg, kThreadsTc, kSmemBytes, s>>>(
-      map_c, map_w, (const T_*)c, pos, pos64, (const T_*)a_param, (const T_*)bx, (const T_*)ba, M, E,
-      tiles, cpg, (T_*)a_out, (T_*)xn_out, reinterpret_cast<WsHeader*>(ws_header));
+#define RGK_G(D) gates_tc_kernel<D><<<groups * cpg, kThreadsTc, kSmemBytes, s>>>( \
+      map_c, map_w, (const T_*)c, pos, pos64, (const T_*)a_param, (const T_*)bx, (const T_*)ba, M, E, \
+      tiles, cpg, (T_*)a_out, (T_*)xn_out, reinterpret_cast<WsHeader*>(ws_header))
+  if (dbg == 1) RGK_G(1); else if (dbg == 2) RGK_G(2); else if (dbg == 3) RGK_G(3); else if (dbg == 4) RGK_G(4); else RGK_G(0);
   return cudaGetLastError();
 }
 
