@@ -105,6 +105,33 @@ RGK_API int rgk_linear_scan(const void* x, const void* a, const uint8_t* reset, 
                     float* h_last, void* workspace, size_t workspace_bytes, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * rgk_linear_scan for callers that cannot allocate device memory.  (No counterpart in the
+ * reference: it exists for hosts such as a serving runtime that plans all device buffers up front
+ * and forbids allocation on its request path, or a process whose own arena already owns the whole
+ * device, so that a cudaMalloc made on the library's behalf would fail.)
+ *
+ * Same computation and arguments as rgk_linear_scan, minus the workspace: the scratch is an 8 MiB
+ * array built into the library's device image (held by every GPU that loads the library until the
+ * process exits).  Problems whose scan scratch exceeds 8 MiB - about 10,800 tiles of 128 x 64
+ * elements in bfloat16 (64 x 64 in float32); B8 T4096 E2560 bfloat16 fits - are rejected with
+ * RGK_ESHAPE.  The call allocates nothing: no cudaMalloc / cudaFree, only launches, memsets and
+ * one 4-byte device-to-device copy.
+ *
+ * The first call on each device looks up the array's device address (with that device current);
+ * make that first call outside any stream capture.  All calls on a device share the one array:
+ * two calls that overlap on the GPU (different streams, no ordering between them) race and give
+ * wrong results; calls on one stream, or otherwise ordered, are fine, and no state has to be
+ * cleared by the caller between them.
+ *
+ * status_out (optional, device pointer to one int): receives 0, or RGK_ETIMEOUT if a bounded
+ * device-side wait expired, once the call's work on `stream` has finished.
+ * ---------------------------------------------------------------------------------------------- */
+RGK_API int rgk_linear_scan_static(const void* x, const void* a, const uint8_t* reset,
+                                   const float* h0, const void* y_mul, int64_t B, int64_t T,
+                                   int64_t E, int dtype, void* y, float* h_last, int* status_out,
+                                   void* stream);
+
+/* ------------------------------------------------------------------------------------------------
  * Parameters of one recurrent block's RG-LRU + Conv1D, as the reference state_dict holds them
  * (torch/layers.py:105-112, 262-278, 409-412).
  * ---------------------------------------------------------------------------------------------- */

@@ -39,6 +39,8 @@ SIGNATURES = {
     "rgk_blockdiag_linear": (_int, [_vp, _vp, _vp, _i64, _int, _int, _int, _vp, _vp]),
     "rgk_linear_scan": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _vp, _vp, _sz,
                                _vp]),
+    "rgk_linear_scan_static": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _vp, _vp,
+                                      _vp]),
     "rgk_rglru_forward": (_int, [_vp, _vp, _int, ctypes.POINTER(RgkParams), _vp, _i64, _i64, _i64,
                                  _int, _int, _int, _vp, _vp, _vp, _sz, _vp]),
     "rgk_recurrent_path_prefill": (_int, [_vp, _vp, _vp, _int, ctypes.POINTER(RgkParams), _vp, _i64,

@@ -244,6 +244,37 @@ int rgk_linear_scan(const void* x, const void* a, const uint8_t* reset, const fl
   return RGK_OK;
 }
 
+int rgk_linear_scan_static(const void* x, const void* a, const uint8_t* reset, const float* h0,
+                           const void* y_mul, int64_t B, int64_t T, int64_t E, int dtype, void* y,
+                           float* h_last, int* status_out, void* stream) {
+  int rc = check_common(B, T, E, dtype);
+  if (rc) return rc;
+  RGK_REQUIRE(x && a && y, RGK_EINVAL, "NULL pointer argument");
+  RGK_REQUIRE(aligned16(x) && aligned16(a) && aligned16(y) && aligned16(y_mul) && aligned16(h0) &&
+                  aligned16(h_last),
+              RGK_EALIGN, "pointers must be 16-byte aligned");
+  if (B * T * E == 0) return RGK_OK;
+  const size_t need = rgk::scan_workspace_bytes(B, T, E, dtype);
+  const size_t have = rgk::scan_static_scratch_bytes();
+  RGK_REQUIRE(need <= have, RGK_ESHAPE,
+              "problem needs %zu bytes of scan scratch but the built-in scratch holds %zu; use "
+              "rgk_linear_scan with a caller workspace for sizes this large", need, have);
+  RGK_CHECK_DEVICE();
+  void* scratch = nullptr;
+  RGK_CUDA(rgk::scan_static_scratch(&scratch), "cudaGetSymbolAddress(built-in scan scratch)");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // The array keeps whatever the previous call left: the status word is cleared here, the ticket
+  // and the look-back flags by the launch below; records are rewritten before they are read.
+  RGK_CUDA(cudaMemsetAsync(scratch, 0, sizeof(int), s), "cudaMemsetAsync");
+  RGK_CUDA(rgk::launch_scan(x, a, reset, nullptr, 0, h0, y_mul, B, T, E, dtype, y, h_last, scratch,
+                            s),
+           "scan launch");
+  if (status_out != nullptr)
+    RGK_CUDA(cudaMemcpyAsync(status_out, scratch, sizeof(int), cudaMemcpyDeviceToDevice, s),
+             "cudaMemcpyAsync");
+  return RGK_OK;
+}
+
 int rgk_rglru_forward(const void* x, const void* segment_pos, int pos_dtype, const rgk_params* p,
                       const float* h0, int64_t B, int64_t T, int64_t E, int H, int dtype,
                       int gates_impl, void* y, float* h_last, void* workspace,

@@ -40,6 +40,11 @@ cudaError_t launch_scan(const void* x, const void* a, const uint8_t* reset, cons
                         int pos64, const float* h0, const void* y_mul, int64_t B, int64_t T,
                         int64_t E, int dtype, void* y, float* h_last, void* ws, cudaStream_t s);
 
+// The scan's built-in scratch (a __device__ array inside scan.cu): its size, and its address on the
+// current device (looked up with cudaGetSymbolAddress on first use per device).
+size_t scan_static_scratch_bytes();
+cudaError_t scan_static_scratch(void** ptr_out);
+
 // decode.cu
 // One recurrence step from precomputed a / normalised x: h_out = a h_in + xn (float32, unrounded),
 // out = round(h_out) [* gelu_tanh(yb)].

@@ -16,6 +16,8 @@
 // Every input element is read from HBM exactly once and every output written once; the
 // optional join with the block's other branch (y * gelu_tanh(y_mul), torch/modules.py:627-628,
 // 646) is fused into pass 2.
+#include <mutex>
+
 #include "rgk_common.cuh"
 #include "rgk_internal.h"
 
@@ -355,6 +357,44 @@ cudaError_t launch_scan(const void* x, const void* a, const uint8_t* reset, cons
   }
 #undef RGK_SCAN_LAUNCH
   return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------------
+// Built-in scratch for callers that may not allocate.
+//
+// Some hosts of this library own every byte of device memory themselves: a serving runtime that
+// plans its buffers once and forbids allocation on the request path, or a process that has handed
+// the whole device to its own arena so that a cudaMalloc from a plug-in would simply fail.  Such a
+// caller can still pass inputs and outputs, but it has no workspace to lend.  For it the scan can
+// run on this array instead, which lives in the library's device image: every GPU that loads
+// librgk.so holds these 8 MiB until the process exits.
+//
+// In host code `g_static_scratch` is only a handle for the symbol, never a device address; the
+// address is looked up with cudaGetSymbolAddress, once per device and with that device current.
+// ------------------------------------------------------------------------------------------------
+constexpr size_t kStaticScratchBytes = size_t(8) << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+size_t scan_static_scratch_bytes() { return kStaticScratchBytes; }
+
+cudaError_t scan_static_scratch(void** ptr_out) {
+  static std::mutex mu;
+  static void* device_ptr[64];
+  static int looked_up[64];
+  std::lock_guard<std::mutex> lock(mu);
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return err;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (!looked_up[dev]) {
+    void* p = nullptr;
+    err = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (err != cudaSuccess) return err;
+    device_ptr[dev] = p;
+    looked_up[dev] = 1;
+  }
+  *ptr_out = device_ptr[dev];
+  return cudaSuccess;
 }
 
 }  // namespace rgk
