@@ -2,10 +2,12 @@
 // (recurrentgemma torch/layers.py:140-191), as a single-pass chunked parallel scan.
 //
 // Decomposition.  The [B, T, E] problem is cut into tiles of kRows time steps x 64 channels.
-// Inside a tile every thread owns 4 consecutive time steps of one 16-byte pack of channels and
-// runs them sequentially in registers: pass 1 reduces its steps to the pair (P, H) of the affine
+// The x and a tiles are brought into shared memory by TMA (two cp.async.bulk.tensor copies per
+// tile, asked for by one thread), so a tile in flight costs no registers and four tiles per SM are
+// resident.  Inside a tile every thread owns 4 consecutive time steps of one 16-byte pack of
+// channels and runs them sequentially: pass 1 reduces its steps to the pair (P, H) of the affine
 // map h -> P h + H, the pairs of the tile's sub-chunks are chained through shared memory, and
-// pass 2 replays the same steps from registers starting from the now known incoming state.
+// pass 2 replays the same steps from shared memory starting from the now known incoming state.
 // Tiles of one sequence are linked by a decoupled look-back: each tile publishes its own (P, H)
 // as soon as it has it, then walks back over its predecessors' records (a warp reads up to 32
 // flags at a time) until it meets one that already holds the inclusive state.  Tile numbers are
@@ -14,12 +16,14 @@
 // that expires sets WsHeader::status and the tile continues with a zero carry.
 //
 // Every input element is read from HBM exactly once and every output written once; the
-// optional join with the block's other branch (y * gelu_tanh(y_mul), torch/modules.py:627-628,
+// other branch's tile (needed once) goes straight to registers.  The optional join with the block's other branch (y * gelu_tanh(y_mul), torch/modules.py:627-628,
 // 646) is fused into pass 2.
+#include <cstdlib>
 #include <mutex>
 
 #include "rgk_common.cuh"
 #include "rgk_internal.h"
+#include "tma.cuh"
 
 namespace rgk {
 namespace {
@@ -78,28 +82,51 @@ __device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
   return r;
 }
 
+// Shared memory of one tile (dynamic, 128-byte aligned): the x and a tiles as TMA delivers them
+// (row-major, kRows x 64 channels), the per-sub-chunk maps, and a few small arrays.
+template <typename T> struct ScanSmem {
+  static constexpr int kTileBytes = ScanCfg<T>::kRows * kChan * (int)sizeof(T);      // 16 KiB
+  static constexpr int kOffX = 0;
+  static constexpr int kOffA = kTileBytes;
+  static constexpr int kOffSub = 2 * kTileBytes;                                      // float2 [kSubs][64]
+  static constexpr int kOffTile = kOffSub + ScanCfg<T>::kSubs * kChan * 8;            // float2 [64]
+  static constexpr int kOffHin = kOffTile + kChan * 8;                                // float [64]
+  static constexpr int kOffBar = kOffHin + kChan * 4;                                 // mbarrier
+  static constexpr int kOffMisc = kOffBar + 8;                                        // ticket, load ok
+  static constexpr int kBytes = kOffMisc + 8 + 128;                                   // + alignment slack
+};
+
 template <typename T, bool kMul>
-__global__ void __launch_bounds__(kThreads, 3)
-scan_kernel(const T* __restrict__ x, const T* __restrict__ a, const uint8_t* __restrict__ reset,
-            const void* __restrict__ pos, int pos64, const float* __restrict__ h0,
-            const T* __restrict__ y_mul, int B, int T_, int E, int tiles_t, int groups,
-            T* __restrict__ y, float* __restrict__ h_last, WsHeader* hdr, unsigned* flags,
-            float2* agg, float* incl) {
+__global__ void __launch_bounds__(kThreads, 4)
+scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_a,
+            const uint8_t* __restrict__ reset, const void* __restrict__ pos, int pos64,
+            const float* __restrict__ h0, const T* __restrict__ y_mul, int B, int T_, int E,
+            int tiles_t, int groups, T* __restrict__ y, float* __restrict__ h_last, WsHeader* hdr,
+            unsigned* flags, float2* agg, float* incl, int dbg) {
   using Cfg = ScanCfg<T>;
+  using Sm = ScanSmem<T>;
   constexpr int kPack = Cfg::kPack;
   constexpr bool kBf16 = Traits<T>::kBf16;
   constexpr int kSubs = Cfg::kSubs;
+  constexpr int kRowBytes = kChan * (int)sizeof(T);
 
-  __shared__ float2 s_sub[kSubs][kChan];   // (P, H) of every sub-chunk
-  __shared__ float s_subin[kSubs][kChan];  // state entering every sub-chunk
-  __shared__ float2 s_tile[kChan];         // (P, H) of the whole tile
-  __shared__ float s_hin[kChan];           // state entering the tile
-  __shared__ unsigned s_ticket;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) &
+                                             ~static_cast<uintptr_t>(127));
+  float2 (*s_sub)[kChan] = reinterpret_cast<float2 (*)[kChan]>(smem + Sm::kOffSub);
+  float2* s_tile = reinterpret_cast<float2*>(smem + Sm::kOffTile);
+  float* s_hin = reinterpret_cast<float*>(smem + Sm::kOffHin);
+  volatile unsigned* s_misc = reinterpret_cast<volatile unsigned*>(smem + Sm::kOffMisc);
+  const uint32_t bar = smem_u32(smem + Sm::kOffBar);
 
   const int tid = threadIdx.x;
-  if (tid == 0) s_ticket = atomicAdd(&hdr->ticket, 1u);
+  if (tid == 0) {
+    s_misc[0] = atomicAdd(&hdr->ticket, 1u);
+    mbar_init(bar, 1);
+    mbar_fence_init();
+  }
   __syncthreads();
-  const unsigned tile = s_ticket;
+  const unsigned tile = s_misc[0];
   const int nseq = B * groups;
   const int tt = tile / nseq;
   const int seq = tile - tt * nseq;
@@ -107,29 +134,24 @@ scan_kernel(const T* __restrict__ x, const T* __restrict__ a, const uint8_t* __r
   const int g = seq - b * groups;
   if (tt >= tiles_t) return;  // cannot happen with the launch grid; keeps indices in range
 
+  // ---- the x and a tiles by TMA: one thread asks, the copy engine delivers both tiles ------------
+  // Rows past T and channels past E are zero-filled by the hardware and masked out below.
+  if (tid == 0) {
+    mbar_expect_tx(bar, 2 * Sm::kTileBytes);
+    tma_load_3d(smem_u32(smem + Sm::kOffX), &map_x, g * kChan, tt * Cfg::kRows, b, bar);
+    tma_load_3d(smem_u32(smem + Sm::kOffA), &map_a, g * kChan, tt * Cfg::kRows, b, bar);
+  }
+
   const int lane_in_row = tid % Cfg::kLanesPerRow;
   const int sub = tid / Cfg::kLanesPerRow;
   const int e0 = g * kChan + lane_in_row * kPack;
   const bool chan_ok = e0 < E;
   const int t0 = tt * Cfg::kRows + sub * kRowsPerThread;
   const int64_t row0 = (int64_t)b * T_;
-
-  // ---- loads: everything this thread will ever need, issued back to back -------------------------
-  // Rows past the end of the sequence (and packs past the last channel) load a clamped, valid
-  // address instead of branching, so that no load waits for an earlier one to return.
-  uint4 araw[kRowsPerThread], xraw[kRowsPerThread], mraw[kRowsPerThread];
   unsigned valid = 0, rst = 0;
-  const int e_ld = chan_ok ? e0 : 0;
 #pragma unroll
-  for (int r = 0; r < kRowsPerThread; ++r) {
-    const int t = t0 + r;
-    if (chan_ok && t < T_) valid |= 1u << r;
-    const int64_t row = row0 + min(t, T_ - 1);
-    const int64_t off = row * E + e_ld;
-    araw[r] = ld_stream(a + off);
-    xraw[r] = ld_stream(x + off);
-    if constexpr (kMul) mraw[r] = ld_stream(y_mul + off);
-  }
+  for (int r = 0; r < kRowsPerThread; ++r)
+    if (chan_ok && t0 + r < T_) valid |= 1u << r;
   if (reset != nullptr || pos != nullptr) {
     bool rs[kRowsPerThread];
 #pragma unroll
@@ -139,13 +161,25 @@ scan_kernel(const T* __restrict__ x, const T* __restrict__ a, const uint8_t* __r
     }
 #pragma unroll
     for (int r = 0; r < kRowsPerThread; ++r) rst |= rs[r] ? (1u << r) : 0u;
-    // a_t * !reset_t (torch/layers.py:168), applied once to the packed registers.
-#pragma unroll
-    for (int r = 0; r < kRowsPerThread; ++r)
-      if (rst & (1u << r)) araw[r] = make_uint4(0u, 0u, 0u, 0u);
   }
+  // a_t * !reset_t (torch/layers.py:168) and rows past the end (identity map) in one mask.
+  const unsigned live = valid & ~rst;
 
-  // ---- pass 1: this thread's steps as an affine map --------------------------------------------
+  // Bounded wait for the tiles.
+  {
+    bool ok = false;
+    for (unsigned i = 0; i < kSpinLimit; ++i) {
+      if (mbar_try_wait(bar, 0)) { ok = true; break; }
+    }
+    if (!ok) {
+      if (tid == 0) atomicExch(&hdr->status, kStatusTimeout);
+      valid = 0;   // compute nothing from a tile that never arrived; the carries still link up
+    }
+  }
+  const uint8_t* sx = smem + Sm::kOffX + (sub * kRowsPerThread) * kRowBytes + lane_in_row * 16;
+  const uint8_t* sa = smem + Sm::kOffA + (sub * kRowsPerThread) * kRowBytes + lane_in_row * 16;
+
+  // ---- pass 1: this thread's steps as an affine map ----------------------------------------------
   {
     float P[kPack], Hh[kPack];
 #pragma unroll
@@ -154,17 +188,31 @@ scan_kernel(const T* __restrict__ x, const T* __restrict__ a, const uint8_t* __r
     for (int r = 0; r < kRowsPerThread; ++r) {
       if (valid & (1u << r)) {
         float av[kPack], xv[kPack];
-        unpack<T>(araw[r], av);
-        unpack<T>(xraw[r], xv);
+        unpack<T>(*reinterpret_cast<const uint4*>(sx + r * kRowBytes), xv);
+        if (live & (1u << r)) {
+          unpack<T>(*reinterpret_cast<const uint4*>(sa + r * kRowBytes), av);
 #pragma unroll
-        for (int i = 0; i < kPack; ++i) {
-          Hh[i] = fmaf(av[i], Hh[i], xv[i]);
-          P[i] *= av[i];
+          for (int i = 0; i < kPack; ++i) {
+            Hh[i] = fmaf(av[i], Hh[i], xv[i]);
+            P[i] *= av[i];
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < kPack; ++i) { Hh[i] = xv[i]; P[i] = 0.0f; }
         }
       }
     }
 #pragma unroll
     for (int i = 0; i < kPack; ++i) s_sub[sub][lane_in_row * kPack + i] = make_float2(P[i], Hh[i]);
+  }
+  // The other branch's tile is needed once, in pass 2: it goes straight to registers, and its
+  // latency hides behind the carry resolution below.
+  uint4 mraw[kRowsPerThread];
+  if constexpr (kMul) {
+    const int e_ld = chan_ok ? e0 : 0;
+#pragma unroll
+    for (int r = 0; r < kRowsPerThread; ++r)
+      mraw[r] = ld_stream(y_mul + (row0 + min(t0 + r, T_ - 1)) * E + e_ld);
   }
   __syncthreads();
 
@@ -194,7 +242,7 @@ scan_kernel(const T* __restrict__ x, const T* __restrict__ a, const uint8_t* __r
   if (tid == 0) st_release(&flags[rec], tt == 0 ? 2u : 1u);
 
   // ---- decoupled look-back by warp 0 (lane owns channels 2*lane, 2*lane+1) -----------------------
-  if (tt > 0 && tid < 32) {
+  if (tt > 0 && tid < 32 && dbg != 1) {
     const int lane = tid;
     float Pc0 = 1.0f, Hc0 = 0.0f, Pc1 = 1.0f, Hc1 = 0.0f;
     float hin0 = 0.0f, hin1 = 0.0f;
@@ -213,7 +261,7 @@ scan_kernel(const T* __restrict__ x, const T* __restrict__ a, const uint8_t* __r
         const unsigned zero = __ballot_sync(0xffffffffu, f == 0u) & need;
         if (zero == 0u) break;
         if (++spins > kSpinLimit) { timed_out = true; break; }
-        __nanosleep(64);
+        __nanosleep(32);
       }
       if (timed_out) break;
       const int n_agg = L < 32 ? L : 32;  // lanes 0 .. n_agg-1 hold plain aggregates
@@ -249,13 +297,14 @@ scan_kernel(const T* __restrict__ x, const T* __restrict__ a, const uint8_t* __r
   }
   __syncthreads();
 
-  // ---- state entering each sub-chunk; the last tile of a sequence also writes h_last -------------
+  // ---- state entering each sub-chunk (kept in place of the sub-chunk's H); the last tile of a
+  // sequence also writes h_last -------------------------------------------------------------------
   if (tid < kChan) {
     float h = s_hin[tid];
 #pragma unroll
     for (int s = 0; s < kSubs; ++s) {
-      s_subin[s][tid] = h;
       const float2 ph = s_sub[s][tid];
+      s_sub[s][tid].y = h;
       h = fmaf(ph.x, h, ph.y);
     }
     const int e = g * kChan + tid;
@@ -263,18 +312,23 @@ scan_kernel(const T* __restrict__ x, const T* __restrict__ a, const uint8_t* __r
   }
   __syncthreads();
 
-  // ---- pass 2: replay from registers with the true incoming state --------------------------------
+  // ---- pass 2: replay the tile from shared memory with the true incoming state -------------------
   float h[kPack];
 #pragma unroll
-  for (int i = 0; i < kPack; ++i) h[i] = s_subin[sub][lane_in_row * kPack + i];
+  for (int i = 0; i < kPack; ++i) h[i] = s_sub[sub][lane_in_row * kPack + i].y;
 #pragma unroll
   for (int r = 0; r < kRowsPerThread; ++r) {
     if (valid & (1u << r)) {
       float av[kPack], xv[kPack];
-      unpack<T>(araw[r], av);
-      unpack<T>(xraw[r], xv);
+      unpack<T>(*reinterpret_cast<const uint4*>(sx + r * kRowBytes), xv);
+      if (live & (1u << r)) {
+        unpack<T>(*reinterpret_cast<const uint4*>(sa + r * kRowBytes), av);
 #pragma unroll
-      for (int i = 0; i < kPack; ++i) h[i] = fmaf(av[i], h[i], xv[i]);
+        for (int i = 0; i < kPack; ++i) h[i] = fmaf(av[i], h[i], xv[i]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < kPack; ++i) h[i] = xv[i];
+      }
       uint4 o;
       if constexpr (kBf16) {
         // y = bf16(h); the join multiplies it by bf16(gelu(y_mul)) and rounds once more.
@@ -303,6 +357,45 @@ scan_kernel(const T* __restrict__ x, const T* __restrict__ a, const uint8_t* __r
       st_stream(y + (row0 + t0 + r) * E + e0, o);
     }
   }
+}
+
+// 3-D tensor map over [B, T, E] with a box of kRows x 64 channels of one batch row.
+template <typename T>
+bool make_scan_map(CUtensorMap* map, const void* base, int64_t B, int64_t T_, int64_t E) {
+  EncodeTiledFn fn = tensor_map_encoder();
+  if (fn == nullptr) return false;
+  const cuuint64_t dims[3] = {(cuuint64_t)E, (cuuint64_t)T_, (cuuint64_t)B};
+  const cuuint64_t strides[2] = {(cuuint64_t)E * sizeof(T), (cuuint64_t)T_ * E * sizeof(T)};
+  const cuuint32_t box[3] = {kChan, (cuuint32_t)ScanCfg<T>::kRows, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUtensorMapDataType dt = sizeof(T) == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  return fn(map, dt, 3, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <typename T, bool kMul>
+cudaError_t launch_scan_typed(const void* x, const void* a, const uint8_t* reset, const void* pos,
+                              int pos64, const float* h0, const void* y_mul, int64_t B, int64_t T_,
+                              int64_t E, int tiles_t, int groups, unsigned grid, void* y,
+                              float* h_last, WsHeader* hdr, unsigned* flags, float2* agg, float* incl,
+                              cudaStream_t s) {
+  CUtensorMap map_x, map_a;
+  if (!make_scan_map<T>(&map_x, x, B, T_, E) || !make_scan_map<T>(&map_a, a, B, T_, E))
+    return cudaErrorInvalidValue;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(scan_kernel<T, kMul>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         ScanSmem<T>::kBytes);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  scan_kernel<T, kMul><<<grid, kThreads, ScanSmem<T>::kBytes, s>>>(
+      map_x, map_a, reset, pos, pos64, h0, (const T*)y_mul, (int)B, (int)T_, (int)E, tiles_t, groups,
+      (T*)y, h_last, hdr, flags, agg, incl, getenv("RGK_SCAN_DEBUG") ? atoi(getenv("RGK_SCAN_DEBUG")) : 0);
+  return cudaGetLastError();
 }
 
 struct ScanLayout {
@@ -346,17 +439,12 @@ cudaError_t launch_scan(const void* x, const void* a, const uint8_t* reset, cons
   float2* agg = reinterpret_cast<float2*>(base + L.agg_off);
   float* incl = reinterpret_cast<float*>(base + L.incl_off);
   const unsigned grid = (unsigned)L.ntiles;
-#define RGK_SCAN_LAUNCH(TYPE, MUL)                                                              \
-  scan_kernel<TYPE, MUL><<<grid, kThreads, 0, s>>>(                                             \
-      (const TYPE*)x, (const TYPE*)a, reset, pos, pos64, h0, (const TYPE*)y_mul, (int)B, (int)T, \
-      (int)E, L.tiles_t, L.groups, (TYPE*)y, h_last, hdr, flags, agg, incl)
-  if (dtype) {
-    if (y_mul) RGK_SCAN_LAUNCH(__nv_bfloat16, true); else RGK_SCAN_LAUNCH(__nv_bfloat16, false);
-  } else {
-    if (y_mul) RGK_SCAN_LAUNCH(float, true); else RGK_SCAN_LAUNCH(float, false);
-  }
+#define RGK_SCAN_LAUNCH(TYPE, MUL)                                                                \
+  launch_scan_typed<TYPE, MUL>(x, a, reset, pos, pos64, h0, y_mul, B, T, E, L.tiles_t, L.groups,  \
+                               grid, y, h_last, hdr, flags, agg, incl, s)
+  if (dtype) return y_mul ? RGK_SCAN_LAUNCH(__nv_bfloat16, true) : RGK_SCAN_LAUNCH(__nv_bfloat16, false);
+  return y_mul ? RGK_SCAN_LAUNCH(float, true) : RGK_SCAN_LAUNCH(float, false);
 #undef RGK_SCAN_LAUNCH
-  return cudaGetLastError();
 }
 
 // ------------------------------------------------------------------------------------------------
