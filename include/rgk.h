@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define RGK_ABI_VERSION 1
+#define RGK_ABI_VERSION 2
 
 #if defined(__GNUC__)
 #define RGK_API __attribute__((visibility("default")))
@@ -143,7 +143,20 @@ typedef struct rgk_params {
   const void* gate_x_b;  /* rg_lru.input_gate.b  [H, E/H]          */
   const void* gate_a_w;  /* rg_lru.a_gate.w      [H, E/H, E/H]     */
   const void* gate_a_b;  /* rg_lru.a_gate.b      [H, E/H]          */
+  const void* gates_packed; /* optional: output of rgk_pack_gate_weights for these gate weights;
+                               NULL makes the tensor-core kernels pack into the workspace per call */
 } rgk_params;
+
+/* ------------------------------------------------------------------------------------------------
+ * K-major copy of the two gate weights for the tcgen05 kernels (bfloat16, head width 256 only):
+ * rgk_gate_pack_bytes(H) bytes, written once per weight update and passed as
+ * rgk_params.gates_packed afterwards (saves a 2.6 MB repack per call; matters for decode steps).
+ * No reference counterpart: the reference keeps only the [H, in, out] layout
+ * (torch/layers.py:105-112).
+ * ---------------------------------------------------------------------------------------------- */
+RGK_API size_t rgk_gate_pack_bytes(int H);
+RGK_API int rgk_pack_gate_weights(const rgk_params* p, int H, int bw, int dtype, void* packed_out,
+                                  void* stream);
 
 /* ------------------------------------------------------------------------------------------------
  * RGLRU.forward                                                    torch/layers.py:313-365
@@ -173,7 +186,8 @@ RGK_API int rgk_recurrent_path_prefill(const void* xb, const void* yb, const voi
  * The same sub-path for one decode step (T == 1 with caches)       torch/modules.py:631-646,
  *   xb, yb [B,E]; conv_cache_in [B,W-1,E]; h_in [B,E] float32     torch/layers.py:170-177, 469-474
  *   ->  out [B,E], h_out [B,E] float32, conv_cache_out [B,W-1,E]
- * h_out may alias h_in and conv_cache_out may alias conv_cache_in (in-place state update).
+ * h_out may alias h_in and conv_cache_out may alias conv_cache_in (in-place state update; aliasing
+ * the conv cache selects a three-kernel path instead of the fused single-kernel step).
  * segment_pos [B] still selects the reset behaviour of the RG-LRU (a position of 0 drops h_in).
  * ---------------------------------------------------------------------------------------------- */
 RGK_API int rgk_recurrent_path_decode(const void* xb, const void* yb, const void* segment_pos,

@@ -25,7 +25,7 @@ _vp, _i64, _int, _sz = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_s
 class RgkParams(ctypes.Structure):
   """struct rgk_params of include/rgk.h."""
   _fields_ = [(n, _vp) for n in ("conv_w", "conv_b", "a_param", "gate_x_w", "gate_x_b", "gate_a_w",
-                                 "gate_a_b")]
+                                 "gate_a_b", "gates_packed")]
 
 
 # name -> (restype, argtypes); mirrors include/rgk.h declaration by declaration.
@@ -49,6 +49,8 @@ SIGNATURES = {
     "rgk_recurrent_path_decode": (_int, [_vp, _vp, _vp, _int, ctypes.POINTER(RgkParams), _vp, _vp,
                                          _i64, _i64, _int, _int, _int, _int, _vp, _vp, _vp, _vp,
                                          _sz, _vp]),
+    "rgk_gate_pack_bytes": (_sz, [_int]),
+    "rgk_pack_gate_weights": (_int, [ctypes.POINTER(RgkParams), _int, _int, _int, _vp, _vp]),
     "rgk_workspace_bytes": (_sz, [_i64, _i64, _i64, _int]),
     "rgk_workspace_status": (_int, [_vp, _vp]),
 }
@@ -80,7 +82,7 @@ def load() -> ctypes.CDLL:
       fn = getattr(lib, name)
       fn.restype = res
       fn.argtypes = args
-    if lib.rgk_abi_version() != 1:
+    if lib.rgk_abi_version() != 2:
       raise RuntimeError("librgk.so has a different ABI version; rebuild it")
     _lib = lib
     return lib

@@ -107,8 +107,10 @@ int run_gates(const void* c, const void* pos, int pos64, const rgk_params* p, in
     return fail(RGK_ESHAPE, "the tcgen05 gate kernel covers bfloat16 with head width 256 only "
                             "(dtype %d, head width %d)", dtype, bw);
   if (tc_ok && gates_impl != RGK_GATES_SIMT) {
-    cudaError_t e = rgk::launch_gates_tc(c, pos, pos64, p->a_param, p->gate_x_w, p->gate_x_b,
-                                         p->gate_a_w, p->gate_a_b, M, H, wpack, a, xn, ws_header, s);
+    cudaError_t e = rgk::launch_gates_tc(
+        c, pos, pos64, p->a_param, p->gate_x_w, p->gate_x_b, p->gate_a_w, p->gate_a_b, M, H,
+        p->gates_packed ? const_cast<void*>(p->gates_packed) : wpack, p->gates_packed != nullptr, a,
+        xn, ws_header, s);
     if (e != cudaSuccess) return cuda_fail(e, "tcgen05 gates launch");
     return RGK_OK;
   }
@@ -244,6 +246,23 @@ int rgk_linear_scan(const void* x, const void* a, const uint8_t* reset, const fl
   return RGK_OK;
 }
 
+size_t rgk_gate_pack_bytes(int H) { return H > 0 ? rgk::gates_tc_packed_bytes(H) : 0; }
+
+int rgk_pack_gate_weights(const rgk_params* p, int H, int bw, int dtype, void* packed_out,
+                          void* stream) {
+  int rc = check_params(p, false);
+  if (rc) return rc;
+  RGK_REQUIRE(H >= 1 && packed_out != nullptr && aligned16(packed_out), RGK_EINVAL,
+              "bad H or packed_out");
+  RGK_REQUIRE(rgk::gates_tc_supported(dtype, bw, 1), RGK_ESHAPE,
+              "packed gate weights exist for bfloat16 with head width 256 only");
+  RGK_CHECK_DEVICE();
+  RGK_CUDA(rgk::launch_pack_gate_weights(p->gate_x_w, p->gate_a_w, H, packed_out,
+                                         static_cast<cudaStream_t>(stream)),
+           "pack_gate_weights launch");
+  return RGK_OK;
+}
+
 int rgk_linear_scan_static(const void* x, const void* a, const uint8_t* reset, const float* h0,
                            const void* y_mul, int64_t B, int64_t T, int64_t E, int dtype, void* y,
                            float* h_last, int* status_out, void* stream) {
@@ -374,6 +393,23 @@ int rgk_recurrent_path_decode(const void* xb, const void* yb, const void* segmen
   RGK_CHECK_DEVICE();
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int bw = (int)(E / H);
+  RGK_CUDA(cudaMemsetAsync(workspace, 0, sizeof(int), s), "cudaMemsetAsync");
+  if (gates_impl != RGK_GATES_SIMT && rgk::gates_tc_supported(dtype, bw, B) &&
+      conv_cache_out != conv_cache_in) {
+    // the whole step in one kernel
+    const void* packed = p->gates_packed;
+    if (packed == nullptr) {
+      RGK_CUDA(rgk::launch_pack_gate_weights(p->gate_x_w, p->gate_a_w, H, w.wpack, s),
+               "pack_gate_weights launch");
+      packed = w.wpack;
+    }
+    RGK_CUDA(rgk::launch_path_decode_tc(xb, yb, segment_pos, pos_dtype, p->conv_w, p->conv_b,
+                                        p->a_param, p->gate_x_b, p->gate_a_b, packed, h_in,
+                                        conv_cache_in, B, H, out, h_out, conv_cache_out, workspace,
+                                        s),
+             "fused decode launch");
+    return RGK_OK;
+  }
   RGK_CUDA(cudaMemsetAsync(workspace, 0, sizeof(int), s), "cudaMemsetAsync");
   RGK_CUDA(rgk::launch_conv1d_decode(xb, conv_cache_in, p->conv_w, p->conv_b, B, E, dtype, w.c,
                                      conv_cache_out, s),

@@ -1,0 +1,290 @@
+// One decode step of the RG-LRU + Conv1D sub-path as a single kernel (bfloat16, heads of width
+// 256): recurrentgemma torch/layers.py:469-550 (Conv1D with a cache), 338-353 (gates), 170-177
+// (rnn_scan with one token) and the join of torch/modules.py:627-628, 646.
+//
+// The "tokens" of the contraction are the batch rows.  A CTA serves 128 rows x one quarter of a
+// head (64 channels): its 256 threads first build the A operand in shared memory - the conv output
+// of those rows for all 256 channels of the head, computed from the new token and the three cached
+// rows with the reference's bfloat16 roundings and written in the 128-byte-swizzled K-major layout
+// tcgen05 reads - while TMA brings the 64 x-gate and 64 a-gate weight rows (64 KiB, pre-packed
+// K-major).  Sixteen tcgen05.mma (M 128, N 128, K 16) leave both gates of every channel in TMEM;
+// the epilogue does the gate arithmetic, the state update h = a h + x in float32 (stored
+// unrounded), the join with gelu(y branch), and writes out / state / shifted conv cache.
+//
+// Both mbarrier waits are bounded; on expiry WsHeader::status is raised and the CTA leaves.
+#include <cuda.h>
+
+#include "rgk_common.cuh"
+#include "rgk_internal.h"
+#include "tc_common.cuh"
+
+namespace rgk {
+namespace {
+
+constexpr int kHeadW = 256;
+constexpr int kRowsM = 128;
+constexpr int kChanCta = 64;                     // channels per CTA
+constexpr int kN = 2 * kChanCta;                 // accumulator columns: 64 x-gate + 64 a-gate
+constexpr int kSlices = 4;                       // K slices of 64 channels
+constexpr int kASlice = kRowsM * 128;            // 16 KiB
+constexpr int kBSlice = kN * 128;                // 16 KiB
+constexpr int kOffB = 0;
+constexpr int kOffA = kSlices * kBSlice;                       // 65536
+constexpr int kOffConst = kOffA + kSlices * kASlice;           // 131072
+constexpr int kOffBar = kOffConst + 3 * (kChanCta / 2) * 4;    // two mbarriers
+constexpr int kOffTmem = kOffBar + 16;
+constexpr int kOffAbort = kOffTmem + 4;
+constexpr int kSmem = kOffAbort + 4 + 1024;
+constexpr int kThreadsDec = 256;
+constexpr uint32_t kIdescDec = tc_idesc_bf16(kRowsM, kN);
+
+__device__ __forceinline__ uint4 mul4(const uint4& a, const uint4& b) {
+  return make_uint4(bmul2(a.x, b.x), bmul2(a.y, b.y), bmul2(a.z, b.z), bmul2(a.w, b.w));
+}
+__device__ __forceinline__ uint4 add4(const uint4& a, const uint4& b) {
+  return make_uint4(badd2(a.x, b.x), badd2(a.y, b.y), badd2(a.z, b.z), badd2(a.w, b.w));
+}
+
+template <bool kMul>
+__global__ void __launch_bounds__(kThreadsDec, 1)
+decode_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __nv_bfloat16* __restrict__ xb,
+                 const __nv_bfloat16* __restrict__ yb, const void* __restrict__ pos, int pos64,
+                 const __nv_bfloat16* __restrict__ conv_w, const __nv_bfloat16* __restrict__ conv_b,
+                 const __nv_bfloat16* __restrict__ a_param, const __nv_bfloat16* __restrict__ bias_x,
+                 const __nv_bfloat16* __restrict__ bias_a, const float* __restrict__ h_in,
+                 const __nv_bfloat16* __restrict__ cache_in, int M, int E,
+                 __nv_bfloat16* __restrict__ out, float* __restrict__ h_out,
+                 __nv_bfloat16* __restrict__ cache_out, WsHeader* hdr) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  const uint32_t s_base = smem_u32(smem);
+  uint32_t* s_const = reinterpret_cast<uint32_t*>(smem + kOffConst);
+  const uint32_t bar_b = s_base + kOffBar, bar_mma = s_base + kOffBar + 8;
+  volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(smem + kOffTmem);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(smem + kOffAbort);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int head = blockIdx.x >> 2, quarter = blockIdx.x & 3;
+  const int tile = blockIdx.y;
+  const int chan0 = head * kHeadW + quarter * kChanCta;   // first channel this CTA produces
+
+  if (tid == 0) {
+    *s_abort = 0;
+    mbar_init(bar_b, 1);
+    mbar_init(bar_mma, 1);
+    mbar_fence_init();
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 :: "r"(s_base + kOffTmem), "r"(kN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  if (tid < 3 * (kChanCta / 2)) {
+    const int which = tid / (kChanCta / 2), pair = tid % (kChanCta / 2);
+    const int e = chan0 + 2 * pair;
+    uint32_t v;
+    if (which == 0) v = *reinterpret_cast<const uint32_t*>(bias_x + e);
+    else if (which == 1) v = *reinterpret_cast<const uint32_t*>(bias_a + e);
+    else {
+      const float s0 = round_bf16(softplus_(__bfloat162float(a_param[e])));
+      const float s1 = round_bf16(softplus_(__bfloat162float(a_param[e + 1])));
+      v = pack_bf16x2(-8.0f * s0, -8.0f * s1);
+    }
+    s_const[which * (kChanCta / 2) + pair] = v;
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *s_tmem;
+
+  // ---- weights: 64 x-gate rows and 64 a-gate rows of this quarter, per K slice -------------------
+  if (tid == 0) {
+    mbar_expect_tx(bar_b, kSlices * kBSlice);
+    const int group_row = (head * 2 + (quarter >> 1)) * 256 + (quarter & 1) * kChanCta;
+    for (int k = 0; k < kSlices; ++k) {
+      tma_load_2d(s_base + kOffB + k * kBSlice, &map_w, k * 64, group_row, bar_b);
+      tma_load_2d(s_base + kOffB + k * kBSlice + kChanCta * 128, &map_w, k * 64, group_row + 128,
+                  bar_b);
+    }
+  }
+
+  // ---- A operand: conv output of 128 rows x the head's 256 channels ------------------------------
+  {
+    const int pk = tid & 31;                      // 16-byte pack of the head's channels
+    const int e = head * kHeadW + pk * 8;
+    uint4 wv[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) wv[k] = *reinterpret_cast<const uint4*>(conv_w + (int64_t)k * E + e);
+    const uint4 bv = *reinterpret_cast<const uint4*>(conv_b + e);
+    const bool own = (pk >> 3) == quarter;        // this CTA also shifts the cache of its channels
+    uint8_t* a_slice = smem + kOffA + (pk >> 3) * kASlice;
+#pragma unroll 4
+    for (int r = warp; r < kRowsM; r += kThreadsDec / 32) {
+      const int64_t m = (int64_t)tile * kRowsM + r;
+      uint4 acc = make_uint4(0u, 0u, 0u, 0u);
+      if (m < M) {
+        const uint4 x3 = *reinterpret_cast<const uint4*>(xb + m * E + e);
+        const __nv_bfloat16* cr = cache_in + m * 3 * E + e;
+        const uint4 x0 = *reinterpret_cast<const uint4*>(cr);
+        const uint4 x1 = *reinterpret_cast<const uint4*>(cr + E);
+        const uint4 x2 = *reinterpret_cast<const uint4*>(cr + 2 * (int64_t)E);
+        // newest tap first (torch/layers.py:491-517 with prompt_len = 3), then the bias
+        acc = mul4(x3, wv[3]);
+        acc = add4(acc, mul4(x2, wv[2]));
+        acc = add4(acc, mul4(x1, wv[1]));
+        acc = add4(acc, mul4(x0, wv[0]));
+        acc = add4(acc, bv);
+        if (own && cache_out != nullptr) {
+          __nv_bfloat16* co = cache_out + m * 3 * E + e;
+          *reinterpret_cast<uint4*>(co) = x1;
+          *reinterpret_cast<uint4*>(co + E) = x2;
+          *reinterpret_cast<uint4*>(co + 2 * (int64_t)E) = x3;
+        }
+      }
+      *reinterpret_cast<uint4*>(a_slice + r * 128 + (((pk & 7) ^ (r & 7)) << 4)) = acc;
+    }
+  }
+  // make the generic-proxy writes of the A tile visible to the tensor core (async proxy)
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  __syncthreads();
+
+  // ---- MMA ------------------------------------------------------------------------------------------
+  if (tid == 0) {
+    if (mbar_wait(bar_b, 0, s_abort)) {
+      tc_fence_after();
+#pragma unroll
+      for (int k = 0; k < kSlices; ++k) {
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+          const uint64_t da = smem_desc_sw128(s_base + kOffA + k * kASlice + ks * 32);
+          const uint64_t db = smem_desc_sw128(s_base + kOffB + k * kBSlice + ks * 32);
+          tc_mma_bf16(tmem_base, da, db, kIdescDec, (k | ks) != 0 ? 1u : 0u);
+        }
+      }
+      tc_commit(bar_mma);
+    }
+  }
+
+  // ---- epilogue: 8 warps = 4 TMEM lane quarters x 2 halves of the 64 channels ---------------------
+  {
+    const int lane_base = (warp & 3) * 32, col_half = warp >> 2;
+    const int r = lane_base + lane;
+    const int64_t m = (int64_t)tile * kRowsM + r;
+    const bool row_ok = m < M;
+    const int64_t m_ld = row_ok ? m : 0;
+    const bool is_reset = row_ok && pos_is_zero(pos, pos64, m);
+    const int e = chan0 + col_half * 32;
+    // inputs of the state update and of the join, in flight while the MMA runs
+    float4 hv[8];
+    uint4 yv[4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) hv[j] = *reinterpret_cast<const float4*>(h_in + m_ld * E + e + 4 * j);
+    if constexpr (kMul) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) yv[j] = *reinterpret_cast<const uint4*>(yb + m_ld * E + e + 8 * j);
+    }
+    if (mbar_wait(bar_mma, 0, s_abort)) {
+      tc_fence_after();
+      uint32_t zx[32], za[32];
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lane_base) << 16) + col_half * 32;
+      tc_ld_32x32(t_row, zx);
+      tc_ld_32x32(t_row + kChanCta, za);
+      // conv outputs of these 32 channels: slice `quarter` of the A tile, units col_half*4 .. +3
+      uint4 cv[4];
+      const uint8_t* a_row = smem + kOffA + quarter * kASlice + r * 128;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        cv[j] = *reinterpret_cast<const uint4*>(a_row + (((col_half * 4 + j) ^ (r & 7)) << 4));
+      tc_wait_ld();
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t cp[4] = {cv[j].x, cv[j].y, cv[j].z, cv[j].w};
+        const uint32_t yp[4] = {yv[j].x, yv[j].y, yv[j].z, yv[j].w};
+        float hn[8];
+        uint32_t op[4];
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+          const int n = j * 8 + p * 2;
+          const int pair = (col_half * 32 + n) >> 1;
+          uint32_t a2, xn2;
+          gate_pair(__uint_as_float(zx[n]), __uint_as_float(zx[n + 1]), __uint_as_float(za[n]),
+                    __uint_as_float(za[n + 1]), s_const[pair], s_const[kChanCta / 2 + pair],
+                    s_const[kChanCta + pair], cp[p], is_reset, a2, xn2);
+          const float h0v = (p & 1) ? hv[2 * j + (p >> 1)].z : hv[2 * j + (p >> 1)].x;
+          const float h1v = (p & 1) ? hv[2 * j + (p >> 1)].w : hv[2 * j + (p >> 1)].y;
+          // h = a h + x in float32; the state keeps the unrounded value (torch/layers.py:176-177)
+          hn[2 * p] = fmaf(bf16_lo(a2), h0v, bf16_lo(xn2));
+          hn[2 * p + 1] = fmaf(bf16_hi(a2), h1v, bf16_hi(xn2));
+          op[p] = pack_bf16x2(hn[2 * p], hn[2 * p + 1]);
+          if constexpr (kMul) {
+            const float g0 = gelu_tanh_<true>(bf16_lo(yp[p])), g1 = gelu_tanh_<true>(bf16_hi(yp[p]));
+            op[p] = bmul2(op[p], pack_bf16x2(g0, g1));
+          }
+        }
+        if (row_ok) {
+          *reinterpret_cast<float4*>(h_out + m * E + e + 8 * j) = make_float4(hn[0], hn[1], hn[2], hn[3]);
+          *reinterpret_cast<float4*>(h_out + m * E + e + 8 * j + 4) = make_float4(hn[4], hn[5], hn[6], hn[7]);
+          *reinterpret_cast<uint4*>(out + m * E + e + 8 * j) = make_uint4(op[0], op[1], op[2], op[3]);
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (tid == 0 && *s_abort) atomicExch(&hdr->status, kStatusTimeout);
+  if (warp == 0) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"(kN)
+                 : "memory");
+  }
+}
+
+bool make_w_map(CUtensorMap* map, const void* packed, int H) {
+  EncodeTiledFn fn = tensor_map_encoder();
+  if (fn == nullptr) return false;
+  const cuuint64_t dims[2] = {256, (cuuint64_t)H * 2 * 256};
+  const cuuint64_t strides[1] = {512};
+  const cuuint32_t box[2] = {64, kChanCta};
+  const cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(packed), dims, strides, box,
+            estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+cudaError_t launch_path_decode_tc(const void* xb, const void* yb, const void* pos, int pos64,
+                                  const void* conv_w, const void* conv_b, const void* a_param,
+                                  const void* bx, const void* ba, const void* packed_w,
+                                  const float* h_in, const void* cache_in, int64_t B, int H,
+                                  void* out, float* h_out, void* cache_out, void* ws_header,
+                                  cudaStream_t s) {
+  if (B == 0) return cudaSuccess;
+  using T_ = __nv_bfloat16;
+  CUtensorMap map_w;
+  if (!make_w_map(&map_w, packed_w, H)) return cudaErrorInvalidValue;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(decode_tc_kernel<true>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(decode_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               kSmem);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  const dim3 grid((unsigned)(H * 4), (unsigned)((B + kRowsM - 1) / kRowsM));
+  const int E = H * kHeadW;
+#define RGK_DEC(MUL)                                                                               \
+  decode_tc_kernel<MUL><<<grid, kThreadsDec, kSmem, s>>>(                                          \
+      map_w, (const T_*)xb, (const T_*)yb, pos, pos64, (const T_*)conv_w, (const T_*)conv_b,       \
+      (const T_*)a_param, (const T_*)bx, (const T_*)ba, h_in, (const T_*)cache_in, (int)B, E,      \
+      (T_*)out, h_out, (T_*)cache_out, reinterpret_cast<WsHeader*>(ws_header))
+  if (yb) RGK_DEC(true); else RGK_DEC(false);
+#undef RGK_DEC
+  return cudaGetLastError();
+}
+
+}  // namespace rgk

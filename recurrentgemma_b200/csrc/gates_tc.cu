@@ -23,11 +23,10 @@
 // Every mbarrier wait is bounded; when one expires the CTA raises WsHeader::status, all roles leave
 // their loops, TMEM is released and the kernel returns.
 #include <cuda.h>
-#include <cstdlib>
 
 #include "rgk_common.cuh"
 #include "rgk_internal.h"
-#include "tma.cuh"
+#include "tc_common.cuh"
 
 namespace rgk {
 namespace {
@@ -57,137 +56,8 @@ constexpr int kStageBytes = 32 * 64;                                // 32 rows x
 constexpr int kSmemBytes = kOffStage + kEpiWarps * kStageBytes + 1024;  // + slack for the alignment
 static_assert(kSmemBytes <= 232448, "exceeds the 227 KiB of shared memory a CTA may use");
 
-constexpr unsigned kWaitLimit = 1u << 20;
+constexpr uint32_t kIdesc = tc_idesc_bf16(kTileM, kTileN);
 
-// Bounded wait.  Returns false (and raises the CTA's abort flag) when the limit is hit or another
-// role has already aborted.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  for (unsigned i = 0; i < kWaitLimit; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (*abort_flag) return false;
-  }
-  *abort_flag = 1;
-  return false;
-}
-
-__device__ __forceinline__ void tc_fence_before() {
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_after() {
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
-               :: "r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                            uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      :: "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tc_ld_32x32(uint32_t taddr, uint32_t (&v)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
-        "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
-        "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
-        "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
-        "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-      : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tc_wait_ld() {
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// Shared-memory matrix descriptor of a K-major operand slice stored with the 128-byte swizzle:
-// rows of 128 bytes, groups of 8 rows 1024 bytes apart (stride byte offset), descriptor version 1.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((addr & 0x3ffffu) >> 4);        // start address, bits [0,14)
-  d |= static_cast<uint64_t>(1) << 16;                       // leading byte offset (unused with swizzle)
-  d |= static_cast<uint64_t>(1024 >> 4) << 32;               // stride byte offset, bits [32,46)
-  d |= static_cast<uint64_t>(1) << 46;                       // version
-  d |= static_cast<uint64_t>(2) << 61;                       // SWIZZLE_128B
-  return d;
-}
-
-// Instruction descriptor: D float32, A and B bfloat16, both K-major, M 128, N 256.
-constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((kTileN >> 3) << 17) |
-                            ((kTileM >> 4) << 24);
-
-// packed bfloat16x2 arithmetic, each lane rounded to nearest even (what torch does per element)
-__device__ __forceinline__ uint32_t bmul2(uint32_t a, uint32_t b) {
-  uint32_t r;
-  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
-  return r;
-}
-__device__ __forceinline__ uint32_t badd2(uint32_t a, uint32_t b) {
-  uint32_t r;
-  asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
-  return r;
-}
-__device__ __forceinline__ uint32_t bsub2(uint32_t a, uint32_t b) {
-  uint32_t r;
-  asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
-  return r;
-}
-__device__ __forceinline__ float ex2f(float v) {
-  float r;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
-  return r;
-}
-__device__ __forceinline__ float rcpf(float v) {
-  float r;
-  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
-  return r;
-}
-__device__ __forceinline__ float sqrtf_approx(float v) {
-  float r;
-  asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
-  return r;
-}
-
-// Gate arithmetic for two neighbouring channels (torch/layers.py:338-353), every tensor-level
-// result rounded to bfloat16 where torch rounds it.
-//   zx, za   float32 accumulators;  bx2, ba2 packed biases;  m8sp2 = packed -8 softplus(a_param)
-//   c2       packed conv outputs;  returns packed a (reset-masked) and packed normalised input.
-__device__ __forceinline__ void gate_pair(float zx0, float zx1, float za0, float za1, uint32_t bx2,
-                                          uint32_t ba2, uint32_t m8sp2, uint32_t c2, bool is_reset,
-                                          uint32_t& a2, uint32_t& xn2) {
-  constexpr float kLog2e = 1.4426950408889634f;
-  const uint32_t zx2 = badd2(pack_bf16x2(zx0, zx1), bx2);
-  const uint32_t za2 = badd2(pack_bf16x2(za0, za1), ba2);
-  // sigmoid(z) = 1 / (1 + 2^(-z log2 e)); the two gates of a channel share one reciprocal.
-  // Arguments are clamped so that the product of the two denominators stays finite.
-  const float ex0 = ex2f(fminf(-bf16_lo(zx2) * kLog2e, 60.0f));
-  const float ex1 = ex2f(fminf(-bf16_hi(zx2) * kLog2e, 60.0f));
-  const float ea0 = ex2f(fminf(-bf16_lo(za2) * kLog2e, 60.0f));
-  const float ea1 = ex2f(fminf(-bf16_hi(za2) * kLog2e, 60.0f));
-  const float dx0 = 1.0f + ex0, da0 = 1.0f + ea0, dx1 = 1.0f + ex1, da1 = 1.0f + ea1;
-  const float r0 = rcpf(dx0 * da0), r1 = rcpf(dx1 * da1);
-  const uint32_t gx2 = pack_bf16x2(r0 * da0, r1 * da1);
-  const uint32_t ga2 = pack_bf16x2(r0 * dx0, r1 * dx1);
-  // log_a = (-8 gate_a) softplus(a_param): the factor -8 is exact in bfloat16, so it is folded
-  // into the per-channel constant.
-  const uint32_t la2 = bmul2(ga2, m8sp2);
-  const float e0 = ex2f(bf16_lo(la2) * kLog2e), e1 = ex2f(bf16_hi(la2) * kLog2e);
-  a2 = pack_bf16x2(e0, e1);
-  const uint32_t asq2 = pack_bf16x2(e0 * e0, e1 * e1);      // exp(2 log_a)
-  const uint32_t om2 = bsub2(0x3f803f80u, asq2);            // 1 - a^2
-  uint32_t mult2 = pack_bf16x2(sqrtf_approx(bf16_lo(om2)), sqrtf_approx(bf16_hi(om2)));
-  if (is_reset) {
-    mult2 = 0x3f803f80u;
-    a2 = 0u;
-  }
-  xn2 = bmul2(bmul2(c2, gx2), mult2);
-}
-
-template <int kDbg>
 __global__ void __launch_bounds__(kThreadsTc, 1)
 gates_tc_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_w,
                 const __nv_bfloat16* __restrict__ c, const void* __restrict__ pos, int pos64,
@@ -333,7 +203,7 @@ gates_tc_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_constant
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lane_base) << 16) + s * kTileN +
                              col_half * 64;
 #pragma unroll
-      for (int cc = 0; cc < (kDbg == 4 ? 0 : 2); ++cc) {
+      for (int cc = 0; cc < 2; ++cc) {
         uint32_t zx[32], za[32];
         tc_ld_32x32(t_row + cc * 32, zx);
         tc_ld_32x32(t_row + kHalf + cc * 32, za);
@@ -350,9 +220,6 @@ gates_tc_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_constant
           for (int p = 0; p < 4; ++p) {
             const int n = j * 8 + p * 2;                 // channel inside this 32-column chunk
             const int pair = (col_half * 64 + cc * 32 + n) >> 1;
-            if constexpr (kDbg == 1 || kDbg >= 3) {
-              ap[p] = zx[n] ^ za[n + 1] ^ cp[p]; xp[p] = zx[n + 1] ^ za[n] ^ s_const[pair];
-            } else
             gate_pair(__uint_as_float(zx[n]), __uint_as_float(zx[n + 1]), __uint_as_float(za[n]),
                       __uint_as_float(za[n + 1]), s_const[pair], s_const[kHalf / 2 + pair],
                       s_const[kHalf + pair], cp[p], is_reset, ap[p], xp[p]);
@@ -381,7 +248,7 @@ gates_tc_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_constant
             const uint4 v = *reinterpret_cast<const uint4*>(stage + r * 64 +
                                                             ((piece ^ ((r >> 1) & 3)) << 4));
             const int64_t grow = tile_row0 + r;
-            if (grow < M && kDbg < 2)
+            if (grow < M)
               *reinterpret_cast<uint4*>(dst + grow * E + chan_chunk + piece * 8) = v;
           }
           __syncwarp();
@@ -444,17 +311,25 @@ bool gates_tc_supported(int dtype, int bw, int64_t M) {
   return dtype == 1 && bw == kHeadWidth && M >= 1 && M < ((int64_t)1 << 31);
 }
 
+cudaError_t launch_pack_gate_weights(const void* wx, const void* wa, int H, void* packed_w,
+                                     cudaStream_t s) {
+  using T_ = __nv_bfloat16;
+  pack_gate_weights_kernel<<<dim3(kHeadWidth / 32, kTileN / 32, 2 * H), dim3(32, 8), 0, s>>>(
+      (const T_*)wx, (const T_*)wa, H, (T_*)packed_w);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_gates_tc(const void* c, const void* pos, int pos64, const void* a_param,
                             const void* wx, const void* bx, const void* wa, const void* ba,
-                            int64_t M, int H, void* packed_w, void* a_out, void* xn_out,
-                            void* ws_header, cudaStream_t s) {
+                            int64_t M, int H, void* packed_w, int packed_ready, void* a_out,
+                            void* xn_out, void* ws_header, cudaStream_t s) {
   if (M == 0) return cudaSuccess;
   using T_ = __nv_bfloat16;
   const int E = H * kHeadWidth;
-  pack_gate_weights_kernel<<<dim3(kHeadWidth / 32, kTileN / 32, 2 * H), dim3(32, 8), 0, s>>>(
-      (const T_*)wx, (const T_*)wa, H, (T_*)packed_w);
-  cudaError_t err = cudaGetLastError();
-  if (err != cudaSuccess) return err;
+  if (!packed_ready) {
+    cudaError_t err = launch_pack_gate_weights(wx, wa, H, packed_w, s);
+    if (err != cudaSuccess) return err;
+  }
 
   CUtensorMap map_c, map_w;
   if (!make_map(&map_c, c, (uint64_t)M, (uint64_t)E, kTileM) ||
@@ -466,23 +341,16 @@ cudaError_t launch_gates_tc(const void* c, const void* pos, int pos64, const voi
     int dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
-    cudaFuncSetAttribute(gates_tc_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-    cudaFuncSetAttribute(gates_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-    cudaFuncSetAttribute(gates_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-    cudaFuncSetAttribute(gates_tc_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-    cudaFuncSetAttribute(gates_tc_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    cudaFuncSetAttribute(gates_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
   }
-  const char* dbg_env = getenv("RGK_GATES_DEBUG");
-  const int dbg = dbg_env ? atoi(dbg_env) : 0;
   const int groups = 2 * H;
   const int tiles = (int)((M + kTileM - 1) / kTileM);
   int cpg = num_sms / groups;
   if (cpg < 1) cpg = 1;
   if (cpg > tiles) cpg = tiles;
-#define RGK_G(D) gates_tc_kernel<D><<<groups * cpg, kThreadsTc, kSmemBytes, s>>>( \
-      map_c, map_w, (const T_*)c, pos, pos64, (const T_*)a_param, (const T_*)bx, (const T_*)ba, M, E, \
-      tiles, cpg, (T_*)a_out, (T_*)xn_out, reinterpret_cast<WsHeader*>(ws_header))
-  if (dbg == 1) RGK_G(1); else if (dbg == 2) RGK_G(2); else if (dbg == 3) RGK_G(3); else if (dbg == 4) RGK_G(4); else RGK_G(0);
+gates_tc_kernel<<<groups * cpg, kThreadsTc, kSmemBytes, s>>>(
+      map_c, map_w, (const T_*)c, pos, pos64, (const T_*)a_param, (const T_*)bx, (const T_*)ba, M, E,
+      tiles, cpg, (T_*)a_out, (T_*)xn_out, reinterpret_cast<WsHeader*>(ws_header));
   return cudaGetLastError();
 }
 

@@ -31,8 +31,23 @@ bool gates_tc_supported(int dtype, int bw, int64_t M);
 size_t gates_tc_packed_bytes(int H);
 cudaError_t launch_gates_tc(const void* c, const void* pos, int pos64, const void* a_param,
                             const void* wx, const void* bx, const void* wa, const void* ba,
-                            int64_t M, int H, void* packed_w, void* a_out, void* xn_out,
-                            void* ws_header, cudaStream_t s);
+                            int64_t M, int H, void* packed_w, int packed_ready, void* a_out,
+                            void* xn_out, void* ws_header, cudaStream_t s);
+
+// Packs the gate weights only (the first step of launch_gates_tc), for callers that keep the
+// packed copy across calls; launch_gates_tc with packed_ready != 0 then skips its own packing.
+cudaError_t launch_pack_gate_weights(const void* wx, const void* wa, int H, void* packed_w,
+                                     cudaStream_t s);
+
+// decode_tc.cu: one decode step of the whole sub-path (conv step, gates on tcgen05, state update,
+// join) in a single kernel; bfloat16, head width 256.  packed_w as produced by
+// launch_pack_gate_weights.  cache_out must not alias cache_in.
+cudaError_t launch_path_decode_tc(const void* xb, const void* yb, const void* pos, int pos64,
+                                  const void* conv_w, const void* conv_b, const void* a_param,
+                                  const void* bx, const void* ba, const void* packed_w,
+                                  const float* h_in, const void* cache_in, int64_t B, int H,
+                                  void* out, float* h_out, void* cache_out, void* ws_header,
+                                  cudaStream_t s);
 
 // scan.cu
 size_t scan_workspace_bytes(int64_t B, int64_t T, int64_t E, int dtype);

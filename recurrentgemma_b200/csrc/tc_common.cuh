@@ -1,0 +1,142 @@
+// tcgen05 / TMEM wrappers, the shared-memory operand descriptor, and the RG-LRU gate arithmetic in
+// packed bfloat16 (recurrentgemma torch/layers.py:338-353), shared by the tensor-core kernels.
+#pragma once
+
+#include "rgk_common.cuh"
+#include "tma.cuh"
+
+namespace rgk {
+
+constexpr unsigned kWaitLimit = 1u << 20;
+
+// Bounded wait.  Returns false (and raises the CTA's abort flag) when the limit is hit or another
+// role has already aborted.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  for (unsigned i = 0; i < kWaitLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
+
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+               :: "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                            uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      :: "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld_32x32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+        "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+        "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
+        "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+        "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major operand slice stored with the 128-byte swizzle:
+// rows of 128 bytes, groups of 8 rows 1024 bytes apart (stride byte offset), descriptor version 1.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((addr & 0x3ffffu) >> 4);        // start address, bits [0,14)
+  d |= static_cast<uint64_t>(1) << 16;                       // leading byte offset (unused with swizzle)
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;               // stride byte offset, bits [32,46)
+  d |= static_cast<uint64_t>(1) << 46;                       // version
+  d |= static_cast<uint64_t>(2) << 61;                       // SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor of tcgen05.mma kind::f16: D float32, A and B bfloat16, both K-major.
+constexpr uint32_t tc_idesc_bf16(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+// packed bfloat16x2 arithmetic, each lane rounded to nearest even (what torch does per element)
+__device__ __forceinline__ uint32_t bmul2(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ uint32_t badd2(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ uint32_t bsub2(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ float ex2f(float v) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
+  return r;
+}
+__device__ __forceinline__ float rcpf(float v) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
+  return r;
+}
+__device__ __forceinline__ float sqrtf_approx(float v) {
+  float r;
+  asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
+  return r;
+}
+
+// Gate arithmetic for two neighbouring channels (torch/layers.py:338-353), every tensor-level
+// result rounded to bfloat16 where torch rounds it.
+//   zx, za   float32 accumulators;  bx2, ba2 packed biases;  m8sp2 = packed -8 softplus(a_param)
+//   c2       packed conv outputs;  returns packed a (reset-masked) and packed normalised input.
+__device__ __forceinline__ void gate_pair(float zx0, float zx1, float za0, float za1, uint32_t bx2,
+                                          uint32_t ba2, uint32_t m8sp2, uint32_t c2, bool is_reset,
+                                          uint32_t& a2, uint32_t& xn2) {
+  constexpr float kLog2e = 1.4426950408889634f;
+  const uint32_t zx2 = badd2(pack_bf16x2(zx0, zx1), bx2);
+  const uint32_t za2 = badd2(pack_bf16x2(za0, za1), ba2);
+  // sigmoid(z) = 1 / (1 + 2^(-z log2 e)); the two gates of a channel share one reciprocal.
+  // Arguments are clamped so that the product of the two denominators stays finite.
+  const float ex0 = ex2f(fminf(-bf16_lo(zx2) * kLog2e, 60.0f));
+  const float ex1 = ex2f(fminf(-bf16_hi(zx2) * kLog2e, 60.0f));
+  const float ea0 = ex2f(fminf(-bf16_lo(za2) * kLog2e, 60.0f));
+  const float ea1 = ex2f(fminf(-bf16_hi(za2) * kLog2e, 60.0f));
+  const float dx0 = 1.0f + ex0, da0 = 1.0f + ea0, dx1 = 1.0f + ex1, da1 = 1.0f + ea1;
+  const float r0 = rcpf(dx0 * da0), r1 = rcpf(dx1 * da1);
+  const uint32_t gx2 = pack_bf16x2(r0 * da0, r1 * da1);
+  const uint32_t ga2 = pack_bf16x2(r0 * dx0, r1 * dx1);
+  // log_a = (-8 gate_a) softplus(a_param): the factor -8 is exact in bfloat16, so it is folded
+  // into the per-channel constant.
+  const uint32_t la2 = bmul2(ga2, m8sp2);
+  const float e0 = ex2f(bf16_lo(la2) * kLog2e), e1 = ex2f(bf16_hi(la2) * kLog2e);
+  a2 = pack_bf16x2(e0, e1);
+  const uint32_t asq2 = pack_bf16x2(e0 * e0, e1 * e1);      // exp(2 log_a)
+  const uint32_t om2 = bsub2(0x3f803f80u, asq2);            // 1 - a^2
+  uint32_t mult2 = pack_bf16x2(sqrtf_approx(bf16_lo(om2)), sqrtf_approx(bf16_hi(om2)));
+  if (is_reset) {
+    mult2 = 0x3f803f80u;
+    a2 = 0u;
+  }
+  xn2 = bmul2(bmul2(c2, gx2), mult2);
+}
+
+
+}  // namespace rgk

@@ -153,8 +153,31 @@ class RGLRU(nn.Module):
   def a_param_init(self, w: torch.Tensor) -> torch.Tensor:
     return rnn_param_init(w, min_rad=0.9, max_rad=0.999)
 
+  def _packed_gates(self) -> Optional[int]:
+    """Device pointer of the K-major copy of the gate weights the tcgen05 kernels read, rebuilt
+    whenever either weight tensor is replaced or modified in place (a derived, non-persistent
+    buffer: it never enters the state_dict)."""
+    wx, wa = self.input_gate.w, self.a_gate.w
+    if (not wx.is_cuda or wx.dtype != torch.bfloat16 or self.width // self.num_heads != 256 or
+        self.gates_impl == _lib.GATES_SIMT):
+      return None
+    key = (wx.data_ptr(), wx._version, wa.data_ptr(), wa._version)
+    if getattr(self, "_pack_key", None) != key:
+      lib = _lib.load()
+      buf = torch.empty(lib.rgk_gate_pack_bytes(self.num_heads), dtype=torch.uint8,
+                        device=wx.device)
+      p = _lib.RgkParams(a_param=self.a_param.data_ptr(), gate_x_w=wx.data_ptr(),
+                         gate_x_b=self.input_gate.b.data_ptr(), gate_a_w=wa.data_ptr(),
+                         gate_a_b=self.a_gate.b.data_ptr())
+      with torch.cuda.device(wx.device):
+        _lib.check(lib.rgk_pack_gate_weights(ctypes.byref(p), self.num_heads, 256, _lib.RGK_BF16,
+                                             buf.data_ptr(), _lib.stream_ptr(wx.device)))
+      self._pack_buf, self._pack_key = buf, key
+    return self._pack_buf.data_ptr()
+
   def _params(self, conv: Optional["Conv1D"] = None) -> _lib.RgkParams:
     return _lib.RgkParams(
+        gates_packed=self._packed_gates(),
         conv_w=None if conv is None else conv.w.data_ptr(),
         conv_b=None if conv is None else conv.b.data_ptr(),
         a_param=self.a_param.data_ptr(),

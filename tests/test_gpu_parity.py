@@ -229,3 +229,49 @@ def test_gates_tcgen05_matches_simt_and_oracle(rg, oracle, shape):
                                 p["rg_lru.a_gate.w"], p["rg_lru.a_gate.b"], h0.cpu())
     assert_close(y_tc, y_ref, TOL[torch.bfloat16], "tcgen05 vs oracle y")
     assert_close(h_tc, h_ref, TOL[torch.bfloat16], "tcgen05 vs oracle h")
+
+
+@pytest.mark.parametrize("shape", [(256, 2560, 10), (5, 256, 1), (130, 512, 2)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_fused_decode_step_matches_unfused_and_oracle(rg, oracle, shape):
+  """The single-kernel decode step (conv step + tcgen05 gates + state update + join) against the
+  three-kernel CUDA-core path and against the oracle, including rows whose position is 0."""
+  from recurrentgemma_b200 import _lib
+  b, e, h = shape
+  case = C.Case(f"dec_{b}_{e}", "rglru", "bfloat16", b, 1, e, h)
+  p = C.make_params(case)
+  dt = torch.bfloat16
+  conv = rg.Conv1D(e, 4, device=DEV, dtype=dt)
+  conv.load_state_dict({"w": p["conv_1d.w"], "b": p["conv_1d.b"]})
+  lru = rg.RGLRU(e, h, device=DEV, dtype=dt)
+  lru.load_state_dict({k[len("rg_lru."):]: v for k, v in p.items() if k.startswith("rg_lru.")})
+  xb = C.normal(case.name, "xb", (b, 1, e), 1.0, dt)
+  yb = C.normal(case.name, "yb", (b, 1, e), 1.0, dt)
+  h0 = C.normal(case.name, "h0", (b, e), 0.5)
+  cc = C.normal(case.name, "cc", (b, 3, e), 1.0, dt)
+  pos = torch.randint(0, 3, (b, 1), generator=torch.Generator().manual_seed(3))
+  cache = rg.RecurrentBlockCache(rg_lru_state=h0.to(DEV), conv1d_state=cc.to(DEV))
+  lru.gates_impl = _lib.GATES_AUTO
+  o_f, c_f = rg.recurrent_path(xb.to(DEV), yb.to(DEV), pos.to(DEV), conv, lru, cache)
+  _lib.workspace_status(_lib.workspace(torch.device(DEV), 1))
+  lru.gates_impl = _lib.GATES_SIMT
+  o_u, c_u = rg.recurrent_path(xb.to(DEV), yb.to(DEV), pos.to(DEV), conv, lru, cache)
+  tol = TOL[dt]
+  assert_close(o_f, o_u, 5e-3, "fused vs unfused out")
+  assert_close(c_f.rg_lru_state, c_u.rg_lru_state, 5e-3, "fused vs unfused state")
+  assert torch.equal(c_f.conv1d_state, c_u.conv1d_state)
+  op = {"conv_w": p["conv_1d.w"], "conv_b": p["conv_1d.b"], "a_param": p["rg_lru.a_param"],
+        "gate_x_w": p["rg_lru.input_gate.w"], "gate_x_b": p["rg_lru.input_gate.b"],
+        "gate_a_w": p["rg_lru.a_gate.w"], "gate_a_b": p["rg_lru.a_gate.b"]}
+  o_r, h_r, c_r = oracle.recurrent_path(xb, yb, pos, op, h0, cc)
+  assert_close(o_f, o_r, tol, "fused vs oracle out")
+  assert_close(c_f.rg_lru_state, h_r, tol, "fused vs oracle state")
+  assert_close(c_f.conv1d_state, c_r, tol, "fused vs oracle conv cache")
+  # no y branch
+  lru.gates_impl = _lib.GATES_AUTO
+  o_n, _ = rg.recurrent_path(xb.to(DEV), None, pos.to(DEV), conv, lru, cache)
+  o_rn, _, _ = oracle.recurrent_path(xb, torch.zeros_like(yb), pos, op, h0, cc)
+  y_plain, _ = oracle.rglru(oracle.conv1d(xb, pos, op["conv_w"], op["conv_b"], cc)[0], pos,
+                            op["a_param"], op["gate_x_w"], op["gate_x_b"], op["gate_a_w"],
+                            op["gate_a_b"], h0)
+  assert_close(o_n, y_plain, tol, "fused, no join")
