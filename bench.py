@@ -380,8 +380,82 @@ def run_gpu(args, cfg):
     dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------------------------------------
+# cfg2: single-token decode step of the recurrent path through 26 layers (secondary workload)
+# ------------------------------------------------------------------------------------------------
+def run_decode(args):
+  """Per-step latency of 26 back-to-back RG-LRU + Conv1D decode steps at 2B dims (batch 256,
+  lru_width 2560, 10 heads, bf16, cached conv window and fp32 state), layer i feeding layer i+1,
+  replayed from a CUDA graph (one kernel per layer).  Prints one JSON line."""
+  import recurrentgemma_b200 as rg
+  from recurrentgemma_b200 import _lib, modules
+  dev = torch.device("cuda", 0)
+  torch.cuda.set_device(dev)
+  dt = torch.bfloat16
+  b, e, h, n_layers = 256, CFG1["lru_width"], CFG1["heads"], 26
+  layers = []
+  for i in range(n_layers):
+    p = make_params(CFG1, dev, 100 + i)
+    conv = rg.Conv1D(e, 4, device=dev, dtype=dt)
+    conv.load_state_dict({"w": p["conv_1d.w"], "b": p["conv_1d.b"]})
+    lru = rg.RGLRU(e, h, device=dev, dtype=dt)
+    lru.load_state_dict({k[len("rg_lru."):]: v for k, v in p.items() if k.startswith("rg_lru.")})
+    g = torch.Generator(device="cpu").manual_seed(500 + i)
+    cache = modules.RecurrentBlockCache(
+        rg_lru_state=(torch.randn((b, e), generator=g) * 0.5).to(dev),
+        conv1d_state=torch.randn((b, 3, e), generator=g).to(dt).to(dev))
+    yb = torch.randn((b, 1, e), generator=g).to(dt).to(dev)
+    layers.append((conv, lru, cache, yb))
+  g = torch.Generator(device="cpu").manual_seed(7)
+  x0 = torch.randn((b, 1, e), generator=g).to(dt).to(dev)
+  pos = torch.randint(1, 4097, (b, 1), generator=g).to(dev)
+
+  def step():
+    x = x0
+    for conv, lru, cache, yb in layers:
+      x, _ = rg.recurrent_path(x, yb, pos, conv, lru, cache)
+    return x
+
+  for _ in range(3):
+    step()
+  torch.cuda.synchronize()
+  t0 = time.perf_counter()
+  for _ in range(args.steps):
+    step()
+  torch.cuda.synchronize()
+  eager_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+  graph = torch.cuda.CUDAGraph()
+  side = torch.cuda.Stream()
+  with torch.cuda.stream(side):
+    step()
+    torch.cuda.synchronize()
+    with torch.cuda.graph(graph, stream=side):
+      step()
+  torch.cuda.synchronize()
+  for _ in range(3):
+    graph.replay()
+  torch.cuda.synchronize()
+  graph_ms = _time_loop(graph.replay, args.steps, torch.cuda.current_stream())
+  path_bytes = n_layers * (2 * b * e * 2 + b * e * 2 + 2 * b * 3 * e * 2 + 2 * b * e * 4 +
+                           2 * 256 * e * 2)
+  hbm, _, which = _peaks()
+  print(json.dumps({
+      "metric": "recurrent_path_decode_step_latency", "value": graph_ms, "unit": "ms",
+      "higher_is_better": False, "n_gpus": 1, "steps": args.steps, "dtype": "bf16",
+      "data": "synthetic",
+      "config": {"workload": "cfg2: RG-LRU+Conv1D decode step x26 layers, B256 E2560 H10 bf16, "
+                             "CUDA-graph replay, one fused kernel per layer"},
+      "eager_python_ms": eager_ms, "tokens_per_s": b / (graph_ms * 1e-3),
+      "roofline": {"bound": "hbm", "algorithmic_bytes": path_bytes,
+                   "achieved": path_bytes / (graph_ms * 1e-3) / 1e9, "peak": hbm, "unit": "GB/s",
+                   "frac": path_bytes / (graph_ms * 1e-3) / 1e9 / hbm, "peak_source": which},
+      "gpu_launches": n_layers * args.steps}), flush=True)
+
+
 def main():
   ap = argparse.ArgumentParser()
+  ap.add_argument("--workload", default="cfg1", choices=["cfg1", "cfg2"],
+                  help="cfg1 (default, the headline prefill workload) or cfg2 (decode step)")
   ap.add_argument("--gpus", type=int, default=1)
   ap.add_argument("--steps", type=int, default=200)
   ap.add_argument("--warmup", type=int, default=3)
@@ -393,7 +467,9 @@ def main():
   cfg = dict(CFG1)
   if args.batch:
     cfg["batch"] = args.batch
-  if args.impl == "reference":
+  if args.workload == "cfg2":
+    run_decode(args)
+  elif args.impl == "reference":
     run_reference(args, cfg)
   else:
     run_gpu(args, cfg)

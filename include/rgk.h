@@ -202,7 +202,10 @@ RGK_API int rgk_recurrent_path_decode(const void* xb, const void* yb, const void
 RGK_API size_t rgk_workspace_bytes(int64_t B, int64_t T, int64_t E, int dtype);
 
 /* Copies the status word the kernels of the last call on `workspace` left behind to the host
- * (synchronises `stream`).  RGK_OK, or RGK_ETIMEOUT if a bounded device-side wait gave up. */
+ * (synchronises `stream`).  RGK_OK, or RGK_ETIMEOUT if a bounded device-side wait gave up.
+ * Every call clears the word before its kernels run, except the single-kernel decode step, which
+ * only ever raises it: after a decode loop the word tells whether any step since the last
+ * clearing call timed out. */
 RGK_API int rgk_workspace_status(const void* workspace, void* stream);
 
 #ifdef __cplusplus

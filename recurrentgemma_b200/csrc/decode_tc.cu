@@ -119,30 +119,44 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __nv_bfloat16*
     const uint4 bv = *reinterpret_cast<const uint4*>(conv_b + e);
     const bool own = (pk >> 3) == quarter;        // this CTA also shifts the cache of its channels
     uint8_t* a_slice = smem + kOffA + (pk >> 3) * kASlice;
-#pragma unroll 4
-    for (int r = warp; r < kRowsM; r += kThreadsDec / 32) {
-      const int64_t m = (int64_t)tile * kRowsM + r;
-      uint4 acc = make_uint4(0u, 0u, 0u, 0u);
-      if (m < M) {
-        const uint4 x3 = *reinterpret_cast<const uint4*>(xb + m * E + e);
+    // 16 rows per thread, in two batches of 8 whose 32 loads are all issued before the first use:
+    // the step is latency bound, so bytes in flight are what counts.
+    constexpr int kBatch = 8;
+#pragma unroll 1
+    for (int r0 = warp; r0 < kRowsM; r0 += kBatch * (kThreadsDec / 32)) {
+      uint4 xv[kBatch][4];
+#pragma unroll
+      for (int i = 0; i < kBatch; ++i) {
+        const int r = r0 + i * (kThreadsDec / 32);
+        const int64_t m = min((int64_t)tile * kRowsM + r, (int64_t)M - 1);   // clamped: never out of range
         const __nv_bfloat16* cr = cache_in + m * 3 * E + e;
-        const uint4 x0 = *reinterpret_cast<const uint4*>(cr);
-        const uint4 x1 = *reinterpret_cast<const uint4*>(cr + E);
-        const uint4 x2 = *reinterpret_cast<const uint4*>(cr + 2 * (int64_t)E);
-        // newest tap first (torch/layers.py:491-517 with prompt_len = 3), then the bias
-        acc = mul4(x3, wv[3]);
-        acc = add4(acc, mul4(x2, wv[2]));
-        acc = add4(acc, mul4(x1, wv[1]));
-        acc = add4(acc, mul4(x0, wv[0]));
-        acc = add4(acc, bv);
-        if (own && cache_out != nullptr) {
-          __nv_bfloat16* co = cache_out + m * 3 * E + e;
-          *reinterpret_cast<uint4*>(co) = x1;
-          *reinterpret_cast<uint4*>(co + E) = x2;
-          *reinterpret_cast<uint4*>(co + 2 * (int64_t)E) = x3;
-        }
+        xv[i][0] = *reinterpret_cast<const uint4*>(cr);
+        xv[i][1] = *reinterpret_cast<const uint4*>(cr + E);
+        xv[i][2] = *reinterpret_cast<const uint4*>(cr + 2 * (int64_t)E);
+        xv[i][3] = *reinterpret_cast<const uint4*>(xb + m * E + e);
       }
-      *reinterpret_cast<uint4*>(a_slice + r * 128 + (((pk & 7) ^ (r & 7)) << 4)) = acc;
+#pragma unroll
+      for (int i = 0; i < kBatch; ++i) {
+        const int r = r0 + i * (kThreadsDec / 32);
+        const int64_t m = (int64_t)tile * kRowsM + r;
+        // newest tap first (torch/layers.py:491-517 with prompt_len = 3), then the bias
+        uint4 acc = mul4(xv[i][3], wv[3]);
+        acc = add4(acc, mul4(xv[i][2], wv[2]));
+        acc = add4(acc, mul4(xv[i][1], wv[1]));
+        acc = add4(acc, mul4(xv[i][0], wv[0]));
+        acc = add4(acc, bv);
+        if (m < M) {
+          if (own && cache_out != nullptr) {
+            __nv_bfloat16* co = cache_out + m * 3 * E + e;
+            *reinterpret_cast<uint4*>(co) = xv[i][1];
+            *reinterpret_cast<uint4*>(co + E) = xv[i][2];
+            *reinterpret_cast<uint4*>(co + 2 * (int64_t)E) = xv[i][3];
+          }
+        } else {
+          acc = make_uint4(0u, 0u, 0u, 0u);
+        }
+        *reinterpret_cast<uint4*>(a_slice + r * 128 + (((pk & 7) ^ (r & 7)) << 4)) = acc;
+      }
     }
   }
   // make the generic-proxy writes of the A tile visible to the tensor core (async proxy)
