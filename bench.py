@@ -452,10 +452,92 @@ def run_decode(args):
       "gpu_launches": n_layers * args.steps}), flush=True)
 
 
+# ------------------------------------------------------------------------------------------------
+# cfg3: long-sequence RG-LRU at 9B dims, channels sharded by whole heads (secondary workload)
+# ------------------------------------------------------------------------------------------------
+def run_long_scan(args):
+  """RG-LRU forward (gate projections + gate arithmetic + scan) at 9B dims: lru_width 4096, 16
+  heads, batch 4, 65536 tokens, bf16, documents of geometric length (mean 2048).  With N ranks
+  (torchrun) rank r owns heads [16 r / N, 16 (r+1) / N): strong scaling, no collective inside the
+  path; the timed region ends with the all_gather that reassembles the output when --gather is
+  given.  Prints one JSON line on rank 0."""
+  import torch.distributed as dist
+  import ctypes
+  import recurrentgemma_b200 as rg
+  from recurrentgemma_b200 import _lib, sharding
+  from tests import cases as C
+  rank = int(os.environ.get("RANK", "0"))
+  world = int(os.environ.get("WORLD_SIZE", "1"))
+  local = int(os.environ.get("LOCAL_RANK", "0"))
+  torch.cuda.set_device(local)
+  dev = torch.device("cuda", local)
+  if world > 1:
+    dist.init_process_group("nccl", device_id=dev)
+  b, t, e, h = 4, args.seq or 65536, 4096, 16
+  dt = torch.bfloat16
+  cfg = dict(batch=b, seq=t, lru_width=e, heads=h, conv_width=4)
+  p = make_params(cfg, "cpu", 3)
+  h0, h1 = sharding.head_range(h, world, rank)
+  e_loc = (h1 - h0) * (e // h)
+  pl = {k: v.to(dev) for k, v in sharding.shard_state_dict(p, e, h, world, rank).items()}
+  lru = rg.RGLRU(e_loc, h1 - h0, device=dev, dtype=dt)
+  lru.load_state_dict({k[len("rg_lru."):]: v for k, v in pl.items() if k.startswith("rg_lru.")})
+  gen = torch.Generator(device=dev).manual_seed(11 + rank)
+  x = torch.randn((b, t, e_loc), generator=gen, device=dev, dtype=torch.float32).to(dt)
+  pos = C.geometric_segment_pos(b, t, 2048.0, 5).to(dev)
+  y = torch.empty_like(x)
+  h_last = torch.empty((b, e_loc), dtype=torch.float32, device=dev)
+  lib = _lib.load()
+  ws = _lib.workspace(dev, _lib.workspace_bytes(b, t, e_loc, dt))
+  prm = lru._params()
+  stream = torch.cuda.current_stream(dev)
+
+  def step():
+    _lib.check(lib.rgk_rglru_forward(x.data_ptr(), pos.data_ptr(), _lib.RGK_I64, ctypes.byref(prm),
+                                     None, b, t, e_loc, h1 - h0, _lib.RGK_BF16, lru.gates_impl,
+                                     y.data_ptr(), h_last.data_ptr(), ws.data_ptr(), ws.numel(),
+                                     stream.cuda_stream))
+    if args.gather and world > 1:
+      sharding.gather_channels(y)
+
+  for _ in range(max(args.warmup, 3)):
+    step()
+  torch.cuda.synchronize()
+  _lib.workspace_status(ws)
+  if world > 1:
+    dist.barrier()
+  torch.cuda.synchronize()
+  ms = _time_loop(step, args.steps, stream)
+  torch.cuda.synchronize()
+  if world > 1:
+    tmax = torch.tensor([ms], device=dev)
+    dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+    ms = float(tmax.item())
+  if rank == 0:
+    hbm, _, which = _peaks()
+    alg = (2 * b * t * e * 2 + 2 * h * 256 * 256 * 2 + b * t * 8) / world   # per GPU
+    print(json.dumps({
+        "metric": "rglru_long_scan_tokens_per_s", "value": b * t / (ms * 1e-3), "unit": "tokens/s",
+        "n_gpus": world, "steps": args.steps, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "strong", "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"cfg3: RG-LRU forward B{b} T{t} E{e} H{h} bf16, geometric documents "
+                               f"(mean 2048), heads sharded x{world}",
+                   "gather_output": bool(args.gather)},
+        "roofline": {"bound": "hbm", "algorithmic_bytes_per_gpu": alg,
+                     "achieved": alg / (ms * 1e-3) / 1e9, "peak": hbm, "unit": "GB/s",
+                     "frac": alg / (ms * 1e-3) / 1e9 / hbm, "peak_source": which},
+        "gpu_launches": 3 * args.steps}), flush=True)
+  if world > 1:
+    dist.destroy_process_group()
+
+
 def main():
   ap = argparse.ArgumentParser()
-  ap.add_argument("--workload", default="cfg1", choices=["cfg1", "cfg2"],
-                  help="cfg1 (default, the headline prefill workload) or cfg2 (decode step)")
+  ap.add_argument("--workload", default="cfg1", choices=["cfg1", "cfg2", "cfg3"],
+                  help="cfg1 (default, the headline prefill workload), cfg2 (decode step) or cfg3 "
+                       "(long head-sharded scan)")
+  ap.add_argument("--seq", type=int, default=None, help="cfg3: sequence length (default 65536)")
+  ap.add_argument("--gather", action="store_true", help="cfg3: all_gather the output every step")
   ap.add_argument("--gpus", type=int, default=1)
   ap.add_argument("--steps", type=int, default=200)
   ap.add_argument("--warmup", type=int, default=3)
@@ -469,6 +551,8 @@ def main():
     cfg["batch"] = args.batch
   if args.workload == "cfg2":
     run_decode(args)
+  elif args.workload == "cfg3":
+    run_long_scan(args)
   elif args.impl == "reference":
     run_reference(args, cfg)
   else:
