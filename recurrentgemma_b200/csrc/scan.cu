@@ -294,6 +294,26 @@ scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
     __syncwarp();
     if (lane == 0) st_release(&flags[rec], 2u);
   }
+  // ---- the join's factor does not depend on the carry: every warp turns its y_mul rows into
+  // round(gelu_tanh(.)) now, so the seven warps that would otherwise sit at the barrier below while
+  // warp 0 resolves the carry do most of pass 2's arithmetic in that time ---------------------------
+  if constexpr (kMul) {
+#pragma unroll
+    for (int r = 0; r < kRowsPerThread; ++r) {
+      float mv[kPack];
+      unpack<T>(mraw[r], mv);
+      if constexpr (kBf16) {
+        mraw[r] = make_uint4(pack_bf16x2(gelu_fast(mv[0]), gelu_fast(mv[1])),
+                             pack_bf16x2(gelu_fast(mv[2]), gelu_fast(mv[3])),
+                             pack_bf16x2(gelu_fast(mv[4]), gelu_fast(mv[5])),
+                             pack_bf16x2(gelu_fast(mv[6]), gelu_fast(mv[7])));
+      } else {
+#pragma unroll
+        for (int i = 0; i < kPack; ++i) mv[i] = gelu_tanh_<false>(mv[i]);
+        mraw[r] = pack<T>(mv);
+      }
+    }
+  }
   __syncthreads();
 
   // ---- state entering each sub-chunk (kept in place of the sub-chunk's H); the last tile of a
@@ -334,11 +354,10 @@ scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
         uint32_t yp[4] = {pack_bf16x2(h[0], h[1]), pack_bf16x2(h[2], h[3]),
                           pack_bf16x2(h[4], h[5]), pack_bf16x2(h[6], h[7])};
         if constexpr (kMul) {
-          float mv[kPack];
-          unpack<T>(mraw[r], mv);
-#pragma unroll
-          for (int j = 0; j < 4; ++j)
-            yp[j] = mul_bf16x2(yp[j], pack_bf16x2(gelu_fast(mv[2 * j]), gelu_fast(mv[2 * j + 1])));
+          yp[0] = mul_bf16x2(yp[0], mraw[r].x);
+          yp[1] = mul_bf16x2(yp[1], mraw[r].y);
+          yp[2] = mul_bf16x2(yp[2], mraw[r].z);
+          yp[3] = mul_bf16x2(yp[3], mraw[r].w);
         }
         o = make_uint4(yp[0], yp[1], yp[2], yp[3]);
       } else {
@@ -349,7 +368,7 @@ scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
           float mv[kPack];
           unpack<T>(mraw[r], mv);
 #pragma unroll
-          for (int i = 0; i < kPack; ++i) out[i] = out[i] * gelu_tanh_<false>(mv[i]);
+          for (int i = 0; i < kPack; ++i) out[i] = out[i] * mv[i];
         }
         o = pack<T>(out);
       }
