@@ -197,6 +197,42 @@ RGK_API int rgk_recurrent_path_decode(const void* xb, const void* yb, const void
                               void* conv_cache_out, void* workspace, size_t workspace_bytes,
                               void* stream);
 
+/* ------------------------------------------------------------------------------------------------
+ * torch.nn.Linear as the block uses it                              torch/modules.py:531-548
+ *   x [M,K], weight [N,K] (out, in), bias [N] or NULL  ->  out [M,N] = x weight^T + bias
+ * tcgen05 tensor-core GEMM, bfloat16 only (float32 accumulation, one rounding); K and N multiples
+ * of 8.  act: RGK_ACT_NONE, or RGK_ACT_GELU_TANH to apply gelu(approximate="tanh") to the rounded
+ * result (torch/modules.py:289-291, 628).  status (optional device int) is raised to RGK_ETIMEOUT if
+ * a bounded device-side wait expires.
+ * ---------------------------------------------------------------------------------------------- */
+enum { RGK_ACT_NONE = 0, RGK_ACT_GELU_TANH = 1 };
+RGK_API int rgk_dense_linear(const void* x, const void* weight, const void* bias, int64_t M,
+                             int64_t K, int64_t N, int dtype, int act, void* out, int* status,
+                             void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * RecurrentBlock.forward, prefill form (cache is None)              torch/modules.py:605-655
+ *   x [B,T,D]  ->  out [B,T,D], h_last [B,E] float32 or NULL, conv_cache_out [B,W-1,E] or NULL
+ * linear_y (+gelu) and linear_x on tensor cores, the RG-LRU + Conv1D sub-path, linear_out.
+ * bfloat16 with head width 256 only (RGK_ESHAPE otherwise: compose the calls above instead).
+ * workspace: rgk_block_workspace_bytes(B, T, D, E, dtype) bytes, 256-byte aligned.
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct rgk_block_params {
+  rgk_params path;           /* conv_1d.*, rg_lru.*                         */
+  const void* linear_y_w;    /* linear_y.weight   [E, D]                    */
+  const void* linear_y_b;    /* linear_y.bias     [E]                       */
+  const void* linear_x_w;    /* linear_x.weight   [E, D]                    */
+  const void* linear_x_b;    /* linear_x.bias     [E]                       */
+  const void* linear_out_w;  /* linear_out.weight [D, E]                    */
+  const void* linear_out_b;  /* linear_out.bias   [D]                       */
+} rgk_block_params;
+RGK_API size_t rgk_block_workspace_bytes(int64_t B, int64_t T, int64_t D, int64_t E, int dtype);
+RGK_API int rgk_recurrent_block_prefill(const void* x, const void* segment_pos, int pos_dtype,
+                                        const rgk_block_params* p, int64_t B, int64_t T, int64_t D,
+                                        int64_t E, int H, int W, int dtype, void* out,
+                                        float* h_last, void* conv_cache_out, void* workspace,
+                                        size_t workspace_bytes, void* stream);
+
 /* Scratch needed by the calls above for a problem of this size (an upper bound over the entry
  * points, so one buffer serves all of them).  Returns 0 on invalid arguments. */
 RGK_API size_t rgk_workspace_bytes(int64_t B, int64_t T, int64_t E, int dtype);

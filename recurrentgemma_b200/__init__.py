@@ -5,9 +5,10 @@ into a reference `Griffin`.  Importing the package does not load the CUDA librar
 forward does, and raises if it has not been built.
 """
 from recurrentgemma_b200.layers import BlockDiagonalLinear, Conv1D, RGLRU, rnn_scan
-from recurrentgemma_b200.modules import RecurrentBlock, RecurrentBlockCache, recurrent_path
+from recurrentgemma_b200.modules import (RecurrentBlock, RecurrentBlockCache, dense_linear,
+                                         recurrent_path)
 
 __all__ = [
     "BlockDiagonalLinear", "Conv1D", "RGLRU", "rnn_scan", "RecurrentBlock", "RecurrentBlockCache",
-    "recurrent_path",
+    "recurrent_path", "dense_linear",
 ]

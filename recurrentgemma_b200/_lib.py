@@ -28,6 +28,12 @@ class RgkParams(ctypes.Structure):
                                  "gate_a_b", "gates_packed")]
 
 
+class RgkBlockParams(ctypes.Structure):
+  """struct rgk_block_params of include/rgk.h."""
+  _fields_ = [("path", RgkParams)] + [(n, _vp) for n in (
+      "linear_y_w", "linear_y_b", "linear_x_w", "linear_x_b", "linear_out_w", "linear_out_b")]
+
+
 # name -> (restype, argtypes); mirrors include/rgk.h declaration by declaration.
 SIGNATURES = {
     "rgk_abi_version": (_int, []),
@@ -51,6 +57,11 @@ SIGNATURES = {
                                          _sz, _vp]),
     "rgk_gate_pack_bytes": (_sz, [_int]),
     "rgk_pack_gate_weights": (_int, [ctypes.POINTER(RgkParams), _int, _int, _int, _vp, _vp]),
+    "rgk_dense_linear": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _vp, _vp, _vp]),
+    "rgk_block_workspace_bytes": (_sz, [_i64, _i64, _i64, _i64, _int]),
+    "rgk_recurrent_block_prefill": (_int, [_vp, _vp, _int, ctypes.POINTER(RgkBlockParams), _i64,
+                                           _i64, _i64, _i64, _int, _int, _int, _vp, _vp, _vp, _vp,
+                                           _sz, _vp]),
     "rgk_workspace_bytes": (_sz, [_i64, _i64, _i64, _int]),
     "rgk_workspace_status": (_int, [_vp, _vp]),
 }

@@ -240,7 +240,7 @@ int rgk_linear_scan(const void* x, const void* a, const uint8_t* reset, const fl
   RGK_CHECK_DEVICE();
   RGK_CUDA(cudaMemsetAsync(workspace, 0, sizeof(int), static_cast<cudaStream_t>(stream)),
            "cudaMemsetAsync");
-  RGK_CUDA(rgk::launch_scan(x, a, reset, nullptr, 0, h0, y_mul, B, T, E, dtype, y, h_last,
+  RGK_CUDA(rgk::launch_scan(x, a, reset, nullptr, 0, h0, y_mul, 0, B, T, E, dtype, y, h_last,
                             workspace, static_cast<cudaStream_t>(stream)),
            "scan launch");
   return RGK_OK;
@@ -285,7 +285,7 @@ int rgk_linear_scan_static(const void* x, const void* a, const uint8_t* reset, c
   // The array keeps whatever the previous call left: the status word is cleared here, the ticket
   // and the look-back flags by the launch below; records are rewritten before they are read.
   RGK_CUDA(cudaMemsetAsync(scratch, 0, sizeof(int), s), "cudaMemsetAsync");
-  RGK_CUDA(rgk::launch_scan(x, a, reset, nullptr, 0, h0, y_mul, B, T, E, dtype, y, h_last, scratch,
+  RGK_CUDA(rgk::launch_scan(x, a, reset, nullptr, 0, h0, y_mul, 0, B, T, E, dtype, y, h_last, scratch,
                             s),
            "scan launch");
   if (status_out != nullptr)
@@ -321,7 +321,7 @@ int rgk_rglru_forward(const void* x, const void* segment_pos, int pos_dtype, con
   if ((rc = run_gates(x, segment_pos, pos_dtype, p, B * T, H, bw, dtype, gates_impl, w.wpack, w.a,
                       w.xn, workspace, s)))
     return rc;
-  RGK_CUDA(rgk::launch_scan(w.xn, w.a, nullptr, nullptr, 0, h0, nullptr, B, T, E, dtype, y, h_last,
+  RGK_CUDA(rgk::launch_scan(w.xn, w.a, nullptr, nullptr, 0, h0, nullptr, 0, B, T, E, dtype, y, h_last,
                             w.scan, s),
            "scan launch");
   return RGK_OK;
@@ -361,9 +361,98 @@ int rgk_recurrent_path_prefill(const void* xb, const void* yb, const void* segme
   if ((rc = run_gates(w.c, segment_pos, pos_dtype, p, B * T, H, bw, dtype, gates_impl, w.wpack, w.a,
                       w.xn, workspace, s)))
     return rc;
-  RGK_CUDA(rgk::launch_scan(w.xn, w.a, nullptr, nullptr, 0, h0, yb, B, T, E, dtype, out, h_last,
+  RGK_CUDA(rgk::launch_scan(w.xn, w.a, nullptr, nullptr, 0, h0, yb, 0, B, T, E, dtype, out, h_last,
                             w.scan, s),
            "scan launch");
+  return RGK_OK;
+}
+
+int rgk_dense_linear(const void* x, const void* weight, const void* bias, int64_t M, int64_t K,
+                     int64_t N, int dtype, int act, void* out, int* status, void* stream) {
+  RGK_REQUIRE(dtype == RGK_F32 || dtype == RGK_BF16, RGK_EINVAL, "unknown dtype %d", dtype);
+  RGK_REQUIRE(act == RGK_ACT_NONE || act == RGK_ACT_GELU_TANH, RGK_EINVAL, "unknown act %d", act);
+  RGK_REQUIRE(M >= 0 && K >= 1 && N >= 1, RGK_EINVAL, "bad size (M=%lld K=%lld N=%lld)",
+              (long long)M, (long long)K, (long long)N);
+  RGK_REQUIRE(x && weight && out, RGK_EINVAL, "NULL pointer argument");
+  RGK_REQUIRE(aligned16(x) && aligned16(weight) && aligned16(out) && aligned16(bias), RGK_EALIGN,
+              "pointers must be 16-byte aligned");
+  RGK_REQUIRE(rgk::dense_tc_supported(dtype, M > 0 ? M : 1, K, N), RGK_ESHAPE,
+              "the tensor-core linear covers bfloat16 with K and N multiples of 8 "
+              "(dtype %d, K=%lld, N=%lld)", dtype, (long long)K, (long long)N);
+  if (M == 0) return RGK_OK;
+  RGK_CHECK_DEVICE();
+  RGK_CUDA(rgk::launch_dense_tc(x, weight, bias, M, (int)K, (int)N, act == RGK_ACT_GELU_TANH, out,
+                                status, static_cast<cudaStream_t>(stream)),
+           "dense linear launch");
+  return RGK_OK;
+}
+
+size_t rgk_block_workspace_bytes(int64_t B, int64_t T, int64_t D, int64_t E, int dtype) {
+  if (B < 0 || T < 0 || D < 0 || E < 0 || (dtype != RGK_F32 && dtype != RGK_BF16)) return 0;
+  if (T < 1) T = 1;
+  const size_t act = up256(static_cast<size_t>(B) * T * E * elem_size(dtype));
+  return carve(nullptr, B, T, E, dtype).total + 2 * act;
+}
+
+int rgk_recurrent_block_prefill(const void* x, const void* segment_pos, int pos_dtype,
+                                const rgk_block_params* p, int64_t B, int64_t T, int64_t D,
+                                int64_t E, int H, int W, int dtype, void* out, float* h_last,
+                                void* conv_cache_out, void* workspace, size_t workspace_bytes,
+                                void* stream) {
+  int rc = check_common(B, T, E, dtype);
+  if (rc) return rc;
+  if ((rc = check_heads(E, H))) return rc;
+  RGK_REQUIRE(p != nullptr, RGK_EINVAL, "params is NULL");
+  if ((rc = check_params(&p->path, true))) return rc;
+  RGK_REQUIRE(p->linear_y_w && p->linear_x_w && p->linear_out_w, RGK_EINVAL,
+              "a linear weight pointer is NULL");
+  RGK_REQUIRE(aligned16(p->linear_y_w) && aligned16(p->linear_x_w) && aligned16(p->linear_out_w) &&
+                  aligned16(p->linear_y_b) && aligned16(p->linear_x_b) && aligned16(p->linear_out_b),
+              RGK_EALIGN, "parameter pointers must be 16-byte aligned");
+  RGK_REQUIRE(W == 4, RGK_ESHAPE, "temporal width %d is not supported (only 4)", W);
+  RGK_REQUIRE(pos_dtype == RGK_I32 || pos_dtype == RGK_I64, RGK_EINVAL, "unknown index dtype");
+  RGK_REQUIRE(x && segment_pos && out, RGK_EINVAL, "NULL pointer argument");
+  RGK_REQUIRE(aligned16(x) && aligned16(out) && aligned16(h_last) && aligned16(conv_cache_out),
+              RGK_EALIGN, "pointers must be 16-byte aligned");
+  RGK_REQUIRE(D >= 8 && D % 8 == 0, RGK_ESHAPE, "block width %lld is not a multiple of 8",
+              (long long)D);
+  const int bw = (int)(E / H);
+  RGK_REQUIRE(rgk::gates_tc_supported(dtype, bw, B * T > 0 ? B * T : 1), RGK_ESHAPE,
+              "the fused block covers bfloat16 with head width 256 only (dtype %d, head width %d)",
+              dtype, bw);
+  if (B * T * E == 0) return RGK_OK;
+  const size_t need = rgk_block_workspace_bytes(B, T, D, E, dtype);
+  RGK_REQUIRE(workspace != nullptr && workspace_bytes >= need, RGK_EWORKSPACE,
+              "workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+  RGK_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255u) == 0, RGK_EALIGN,
+              "workspace must be 256-byte aligned");
+  RGK_CHECK_DEVICE();
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const PathWs w = carve(workspace, B, T, E, dtype);
+  const size_t act = up256(static_cast<size_t>(B) * T * E * elem_size(dtype));
+  char* xb = static_cast<char*>(workspace) + w.total;   // later reused for the joined output
+  char* yb = xb + act;
+  int* status = static_cast<int*>(workspace);
+  const int64_t M = B * T;
+  RGK_CUDA(cudaMemsetAsync(workspace, 0, sizeof(int), s), "cudaMemsetAsync");
+  // y branch with its gelu in the GEMM epilogue, x branch plain
+  RGK_CUDA(rgk::launch_dense_tc(x, p->linear_y_w, p->linear_y_b, M, (int)D, (int)E, 1, yb, status, s),
+           "linear_y launch");
+  RGK_CUDA(rgk::launch_dense_tc(x, p->linear_x_w, p->linear_x_b, M, (int)D, (int)E, 0, xb, status, s),
+           "linear_x launch");
+  RGK_CUDA(rgk::launch_conv1d_prefill(xb, segment_pos, pos_dtype, p->path.conv_w, p->path.conv_b, B,
+                                      T, E, dtype, w.c, conv_cache_out, s),
+           "conv1d_prefill launch");
+  if ((rc = run_gates(w.c, segment_pos, pos_dtype, &p->path, M, H, bw, dtype, RGK_GATES_AUTO,
+                      w.wpack, w.a, w.xn, workspace, s)))
+    return rc;
+  // the conv has consumed xb: its buffer now receives y * gelu(yb)
+  RGK_CUDA(rgk::launch_scan(w.xn, w.a, nullptr, nullptr, 0, nullptr, yb, 1, B, T, E, dtype, xb,
+                            h_last, w.scan, s),
+           "scan launch");
+  RGK_CUDA(rgk::launch_dense_tc(xb, p->linear_out_w, p->linear_out_b, M, (int)E, (int)D, 0, out,
+                                status, s),
+           "linear_out launch");
   return RGK_OK;
 }
 

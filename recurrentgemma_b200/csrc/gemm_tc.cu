@@ -1,0 +1,242 @@
+// Dense projection out = x W^T + b (torch.nn.Linear as RecurrentBlock uses it, recurrentgemma
+// torch/modules.py:531-548, 627-631, 647) on the 5th-generation tensor cores, bfloat16 in and out,
+// float32 accumulation, optional gelu_tanh epilogue (the y branch, torch/modules.py:628).
+//
+// x [M, K] and W [N, K] are both K-contiguous, i.e. K-major operands as they are: TMA brings
+// 128 x 64 (x) and 256 x 64 (W) boxes with the 128-byte swizzle into a 4-stage ring, a single
+// thread issues tcgen05.mma.cta_group::1.kind::f16 (M 128, N 256, K 16) into one of two TMEM
+// accumulators, and 16 epilogue warps drain the other: tcgen05.ld, + bias in float32, one rounding
+// to bfloat16 (then gelu and a second rounding if asked, as torch does for a separate gelu op),
+// a 32 x 32 transposition through shared memory and 64-byte-contiguous stores.  Persistent CTAs
+// walk the output tiles n-fastest so that the CTAs running together share x rows and all of W in L2.
+//
+// Every mbarrier wait is bounded; on expiry WsHeader::status (if given) is raised and the CTA leaves.
+#include <cuda.h>
+
+#include "rgk_common.cuh"
+#include "rgk_internal.h"
+#include "tc_common.cuh"
+
+namespace rgk {
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64, kStages = 4;
+constexpr int kABytes = BM * BK * 2;             // 16 KiB
+constexpr int kBBytes = BN * BK * 2;             // 32 KiB
+constexpr int kStageBytes = kABytes + kBBytes;   // 48 KiB
+constexpr int kEpi = 16;
+constexpr int kThreadsG = (kEpi + 2) * 32;
+constexpr int kOffRing = 0;
+constexpr int kOffStageOut = kStages * kStageBytes;              // 196608: per-warp 2 KiB staging
+constexpr int kOffBarG = kOffStageOut + kEpi * 2048;             // full[4] empty[4] acc_full[2] acc_empty[2]
+constexpr int kOffTmemG = kOffBarG + (2 * kStages + 4) * 8;
+constexpr int kOffAbortG = kOffTmemG + 4;
+constexpr int kSmemG = kOffAbortG + 4 + 1024;
+static_assert(kSmemG <= 232448, "exceeds the 227 KiB of shared memory a CTA may use");
+constexpr uint32_t kIdescG = tc_idesc_bf16(BM, BN);
+
+template <bool kGelu>
+__global__ void __launch_bounds__(kThreadsG, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+               const __nv_bfloat16* __restrict__ bias, int64_t M, int N, int K, int m_tiles,
+               int n_tiles, __nv_bfloat16* __restrict__ out, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  const uint32_t s_base = smem_u32(smem);
+  const uint32_t bar0 = s_base + kOffBarG;
+  auto bar_full = [&](int s) { return bar0 + 8u * s; };
+  auto bar_empty = [&](int s) { return bar0 + 8u * (kStages + s); };
+  auto bar_acc_full = [&](int s) { return bar0 + 8u * (2 * kStages + s); };
+  auto bar_acc_empty = [&](int s) { return bar0 + 8u * (2 * kStages + 2 + s); };
+  volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(smem + kOffTmemG);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(smem + kOffAbortG);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int k_blocks = (K + BK - 1) / BK;
+  const int total_tiles = m_tiles * n_tiles;
+  const int n_my = (total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+
+  if (threadIdx.x == 0) {
+    *s_abort = 0;
+    for (int s = 0; s < kStages; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(bar_acc_full(s), 1); mbar_init(bar_acc_empty(s), kEpi / 2); }
+    mbar_fence_init();
+  }
+  if (warp == kEpi + 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 :: "r"(s_base + kOffTmemG), "r"(512) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *s_tmem;
+
+  if (warp == kEpi) {
+    // ------------------------------ TMA producer --------------------------------------------------
+    if (lane == 0) {
+      unsigned it = 0;
+      bool ok = true;
+      for (int t = 0; t < n_my && ok; ++t) {
+        const int tile = blockIdx.x + t * gridDim.x;
+        const int m0 = (tile / n_tiles) * BM, n0 = (tile % n_tiles) * BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % kStages;
+          ok = mbar_wait(bar_empty(s), ((it / kStages) & 1) ^ 1, s_abort);
+          if (!ok) break;
+          mbar_expect_tx(bar_full(s), kStageBytes);
+          tma_load_2d(s_base + kOffRing + s * kStageBytes, &map_x, kb * BK, m0, bar_full(s));
+          tma_load_2d(s_base + kOffRing + s * kStageBytes + kABytes, &map_w, kb * BK, n0, bar_full(s));
+        }
+      }
+    }
+  } else if (warp == kEpi + 1) {
+    // ------------------------------ MMA issue -----------------------------------------------------
+    if (lane == 0) {
+      unsigned it = 0;
+      bool ok = true;
+      for (int t = 0; t < n_my && ok; ++t) {
+        const int as = t & 1;
+        ok = mbar_wait(bar_acc_empty(as), ((t >> 1) & 1) ^ 1, s_abort);
+        if (!ok) break;
+        tc_fence_after();
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % kStages;
+          ok = mbar_wait(bar_full(s), (it / kStages) & 1, s_abort);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a0 = s_base + kOffRing + s * kStageBytes, b0 = a0 + kABytes;
+#pragma unroll
+          for (int ks = 0; ks < BK / 16; ++ks)
+            tc_mma_bf16(tmem_base + as * BN, smem_desc_sw128(a0 + ks * 32),
+                        smem_desc_sw128(b0 + ks * 32), kIdescG, (kb | ks) != 0 ? 1u : 0u);
+          tc_commit(bar_empty(s));
+        }
+        if (ok) tc_commit(bar_acc_full(as));
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ------------------------------------------------------
+    const int as = warp >> 3;                // accumulator = tile parity
+    const int lane_base = (warp & 3) * 32;   // TMEM lanes this warp may read
+    const int col_half = (warp >> 2) & 1;    // which 128 of the tile's 256 columns
+    uint8_t* stage = smem + kOffStageOut + warp * 2048;
+    bool ok = true;
+    for (int t = as; t < n_my && ok; t += 2) {
+      const int tile = blockIdx.x + t * gridDim.x;
+      const int64_t m0 = (int64_t)(tile / n_tiles) * BM;
+      const int n0 = (tile % n_tiles) * BN + col_half * 128;
+      ok = mbar_wait(bar_acc_full(as), (t >> 1) & 1, s_abort);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lane_base) << 16) + as * BN +
+                             col_half * 128;
+#pragma unroll 1
+      for (int cc = 0; cc < 4; ++cc) {
+        uint32_t acc[32];
+        tc_ld_32x32(t_row + cc * 32, acc);
+        const int nc = n0 + cc * 32;         // first output column of this chunk
+        float bv[32];
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          uint32_t b2 = 0u;
+          if (bias != nullptr && nc + j < N) b2 = *reinterpret_cast<const uint32_t*>(bias + nc + j);
+          bv[j] = bf16_lo(b2); bv[j + 1] = bf16_hi(b2);
+        }
+        tc_wait_ld();
+        uint4 ov[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint32_t o[4];
+#pragma unroll
+          for (int p = 0; p < 4; ++p) {
+            const int n = j * 8 + p * 2;
+            float v0 = __uint_as_float(acc[n]) + bv[n], v1 = __uint_as_float(acc[n + 1]) + bv[n + 1];
+            uint32_t pk = pack_bf16x2(v0, v1);
+            if constexpr (kGelu) pk = pack_bf16x2(gelu_tanh_<true>(bf16_lo(pk)), gelu_tanh_<true>(bf16_hi(pk)));
+            o[p] = pk;
+          }
+          ov[j] = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+        // 32 x 32 transposition through the warp's staging buffer (see gates_tc.cu), then stores of
+        // 8 rows x 64 contiguous bytes per instruction.
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          *reinterpret_cast<uint4*>(stage + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) = ov[j];
+        __syncwarp();
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int r = (lane >> 2) + 8 * k, piece = lane & 3;
+          const uint4 v = *reinterpret_cast<const uint4*>(stage + r * 64 + ((piece ^ ((r >> 1) & 3)) << 4));
+          const int64_t grow = m0 + lane_base + r;
+          const int gcol = nc + piece * 8;
+          if (grow < M && gcol < N) *reinterpret_cast<uint4*>(out + grow * N + gcol) = v;
+        }
+        __syncwarp();
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_acc_empty(as));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *s_abort && status != nullptr) atomicExch(status, kStatusTimeout);
+  if (warp == kEpi + 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"(512)
+                 : "memory");
+  }
+}
+
+bool make_kmajor_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
+                     uint32_t box_rows) {
+  EncodeTiledFn fn = tensor_map_encoder();
+  if (fn == nullptr) return false;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols * 2};
+  const cuuint32_t box[2] = {BK, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+            estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+bool dense_tc_supported(int dtype, int64_t M, int64_t K, int64_t N) {
+  return dtype == 1 && M >= 1 && M < ((int64_t)1 << 31) && K >= 8 && K % 8 == 0 && N >= 8 &&
+         N % 8 == 0 && K < (1 << 24) && N < (1 << 24);
+}
+
+cudaError_t launch_dense_tc(const void* x, const void* w, const void* bias, int64_t M, int K, int N,
+                            int gelu, void* out, int* status, cudaStream_t s) {
+  if (M == 0) return cudaSuccess;
+  CUtensorMap map_x, map_w;
+  if (!make_kmajor_map(&map_x, x, (uint64_t)M, (uint64_t)K, BM) ||
+      !make_kmajor_map(&map_w, w, (uint64_t)N, (uint64_t)K, BN))
+    return cudaErrorInvalidValue;
+  static int num_sms = 0;
+  if (num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaFuncSetAttribute(gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemG);
+    cudaFuncSetAttribute(gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemG);
+  }
+  const int m_tiles = (int)((M + BM - 1) / BM), n_tiles = (N + BN - 1) / BN;
+  const int total = m_tiles * n_tiles;
+  const int grid = total < num_sms ? total : num_sms;
+  using T_ = __nv_bfloat16;
+  if (gelu)
+    gemm_tc_kernel<true><<<grid, kThreadsG, kSmemG, s>>>(map_x, map_w, (const T_*)bias, M, N, K,
+                                                        m_tiles, n_tiles, (T_*)out, status);
+  else
+    gemm_tc_kernel<false><<<grid, kThreadsG, kSmemG, s>>>(map_x, map_w, (const T_*)bias, M, N, K,
+                                                         m_tiles, n_tiles, (T_*)out, status);
+  return cudaGetLastError();
+}
+
+}  // namespace rgk

@@ -49,11 +49,21 @@ cudaError_t launch_path_decode_tc(const void* xb, const void* yb, const void* po
                                   void* out, float* h_out, void* cache_out, void* ws_header,
                                   cudaStream_t s);
 
+// gemm_tc.cu: out [M,N] = x [M,K] W[N,K]^T + bias (bfloat16, float32 accumulation) on tcgen05;
+// gelu != 0 applies gelu_tanh to the rounded result.  status: optional device int raised on a
+// bounded-wait timeout.
+bool dense_tc_supported(int dtype, int64_t M, int64_t K, int64_t N);
+cudaError_t launch_dense_tc(const void* x, const void* w, const void* bias, int64_t M, int K, int N,
+                            int gelu, void* out, int* status, cudaStream_t s);
+
 // scan.cu
 size_t scan_workspace_bytes(int64_t B, int64_t T, int64_t E, int dtype);
+// y_mul (optional): the join y * gelu_tanh(y_mul), or y * y_mul when y_activated != 0 (the factor
+// was already passed through gelu by whoever produced it).
 cudaError_t launch_scan(const void* x, const void* a, const uint8_t* reset, const void* pos,
-                        int pos64, const float* h0, const void* y_mul, int64_t B, int64_t T,
-                        int64_t E, int dtype, void* y, float* h_last, void* ws, cudaStream_t s);
+                        int pos64, const float* h0, const void* y_mul, int y_activated, int64_t B,
+                        int64_t T, int64_t E, int dtype, void* y, float* h_last, void* ws,
+                        cudaStream_t s);
 
 // The scan's built-in scratch (a __device__ array inside scan.cu): its size, and its address on the
 // current device (looked up with cudaGetSymbolAddress on first use per device).

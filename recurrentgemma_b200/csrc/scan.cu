@@ -95,7 +95,7 @@ template <typename T> struct ScanSmem {
   static constexpr int kBytes = kOffMisc + 8 + 128;                                   // + alignment slack
 };
 
-template <typename T, bool kMul>
+template <typename T, int kJoin>   // 0: no join, 1: y * gelu_tanh(y_mul), 2: y * y_mul
 __global__ void __launch_bounds__(kThreads, 4)
 scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_a,
             const uint8_t* __restrict__ reset, const void* __restrict__ pos, int pos64,
@@ -104,6 +104,7 @@ scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
             unsigned* flags, float2* agg, float* incl) {
   using Cfg = ScanCfg<T>;
   using Sm = ScanSmem<T>;
+  constexpr bool kMul = kJoin != 0;
   constexpr int kPack = Cfg::kPack;
   constexpr bool kBf16 = Traits<T>::kBf16;
   constexpr int kSubs = Cfg::kSubs;
@@ -297,7 +298,7 @@ scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
   // ---- the join's factor does not depend on the carry: every warp turns its y_mul rows into
   // round(gelu_tanh(.)) now, so the seven warps that would otherwise sit at the barrier below while
   // warp 0 resolves the carry do most of pass 2's arithmetic in that time ---------------------------
-  if constexpr (kMul) {
+  if constexpr (kJoin == 1) {
 #pragma unroll
     for (int r = 0; r < kRowsPerThread; ++r) {
       float mv[kPack];
@@ -393,7 +394,7 @@ bool make_scan_map(CUtensorMap* map, const void* base, int64_t B, int64_t T_, in
             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <typename T, bool kMul>
+template <typename T, int kJoin>
 cudaError_t launch_scan_typed(const void* x, const void* a, const uint8_t* reset, const void* pos,
                               int pos64, const float* h0, const void* y_mul, int64_t B, int64_t T_,
                               int64_t E, int tiles_t, int groups, unsigned grid, void* y,
@@ -404,13 +405,13 @@ cudaError_t launch_scan_typed(const void* x, const void* a, const uint8_t* reset
     return cudaErrorInvalidValue;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(scan_kernel<T, kMul>,
+    cudaError_t e = cudaFuncSetAttribute(scan_kernel<T, kJoin>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          ScanSmem<T>::kBytes);
     if (e != cudaSuccess) return e;
     attr_set = true;
   }
-  scan_kernel<T, kMul><<<grid, kThreads, ScanSmem<T>::kBytes, s>>>(
+  scan_kernel<T, kJoin><<<grid, kThreads, ScanSmem<T>::kBytes, s>>>(
       map_x, map_a, reset, pos, pos64, h0, (const T*)y_mul, (int)B, (int)T_, (int)E, tiles_t, groups,
       (T*)y, h_last, hdr, flags, agg, incl);
   return cudaGetLastError();
@@ -443,8 +444,9 @@ size_t scan_workspace_bytes(int64_t B, int64_t T, int64_t E, int dtype) {
 }
 
 cudaError_t launch_scan(const void* x, const void* a, const uint8_t* reset, const void* pos,
-                        int pos64, const float* h0, const void* y_mul, int64_t B, int64_t T,
-                        int64_t E, int dtype, void* y, float* h_last, void* ws, cudaStream_t s) {
+                        int pos64, const float* h0, const void* y_mul, int y_activated, int64_t B,
+                        int64_t T, int64_t E, int dtype, void* y, float* h_last, void* ws,
+                        cudaStream_t s) {
   if (B == 0 || T == 0 || E == 0) return cudaSuccess;
   const ScanLayout L = scan_layout(B, T, E, dtype);
   char* base = static_cast<char*>(ws);
@@ -457,11 +459,18 @@ cudaError_t launch_scan(const void* x, const void* a, const uint8_t* reset, cons
   float2* agg = reinterpret_cast<float2*>(base + L.agg_off);
   float* incl = reinterpret_cast<float*>(base + L.incl_off);
   const unsigned grid = (unsigned)L.ntiles;
-#define RGK_SCAN_LAUNCH(TYPE, MUL)                                                                \
-  launch_scan_typed<TYPE, MUL>(x, a, reset, pos, pos64, h0, y_mul, B, T, E, L.tiles_t, L.groups,  \
-                               grid, y, h_last, hdr, flags, agg, incl, s)
-  if (dtype) return y_mul ? RGK_SCAN_LAUNCH(__nv_bfloat16, true) : RGK_SCAN_LAUNCH(__nv_bfloat16, false);
-  return y_mul ? RGK_SCAN_LAUNCH(float, true) : RGK_SCAN_LAUNCH(float, false);
+#define RGK_SCAN_LAUNCH(TYPE, JOIN)                                                               \
+  launch_scan_typed<TYPE, JOIN>(x, a, reset, pos, pos64, h0, y_mul, B, T, E, L.tiles_t, L.groups, \
+                                grid, y, h_last, hdr, flags, agg, incl, s)
+  const int join = y_mul == nullptr ? 0 : (y_activated ? 2 : 1);
+  if (dtype) {
+    if (join == 0) return RGK_SCAN_LAUNCH(__nv_bfloat16, 0);
+    if (join == 1) return RGK_SCAN_LAUNCH(__nv_bfloat16, 1);
+    return RGK_SCAN_LAUNCH(__nv_bfloat16, 2);
+  }
+  if (join == 0) return RGK_SCAN_LAUNCH(float, 0);
+  if (join == 1) return RGK_SCAN_LAUNCH(float, 1);
+  return RGK_SCAN_LAUNCH(float, 2);
 #undef RGK_SCAN_LAUNCH
 }
 

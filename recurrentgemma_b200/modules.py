@@ -78,6 +78,26 @@ def recurrent_path(
   return out, RecurrentBlockCache(rg_lru_state=h_last, conv1d_state=conv_state)
 
 
+@torch.no_grad()
+def dense_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
+                 gelu: bool = False) -> torch.Tensor:
+  """x @ weight.T + bias on the tcgen05 GEMM of librgk (bfloat16), optionally followed by
+  gelu(approximate="tanh") on the rounded result: `nn.Linear` as the block uses it
+  (recurrentgemma/torch/modules.py:531-548, 627-631, 647)."""
+  dev = _lib.require_cuda(x, weight, bias)
+  layers._same_dtype(x, weight, *([bias] if bias is not None else []))
+  n, k = weight.shape
+  assert x.shape[-1] == k
+  xc, wc = x.contiguous(), weight.contiguous()
+  bc = None if bias is None else bias.contiguous()
+  out = torch.empty((*x.shape[:-1], n), dtype=x.dtype, device=dev)
+  with torch.cuda.device(dev):
+    _lib.check(_lib.load().rgk_dense_linear(
+        xc.data_ptr(), wc.data_ptr(), _lib.ptr(bc), xc.numel() // k, k, n, _lib.dtype_code(x.dtype),
+        1 if gelu else 0, out.data_ptr(), None, _lib.stream_ptr(dev)))
+  return out
+
+
 class RecurrentBlock(nn.Module):
   """Griffin and Hawk's recurrent block."""
 
@@ -123,12 +143,49 @@ class RecurrentBlock(nn.Module):
       cache: Optional[RecurrentBlockCache] = None, return_cache: bool = True,
   ) -> Tuple[torch.Tensor, Optional[RecurrentBlockCache]]:
     """Returns (block output [B,T,width], updated cache or None)."""
-    _lib.require_cuda(x, segment_pos, self.linear_x.weight)
+    dev = _lib.require_cuda(x, segment_pos, self.linear_x.weight)
+    if (cache is None and x.dtype == torch.bfloat16 and self.lru_width // self.num_heads == 256
+        and self.conv1d_temporal_width == 4 and self.width % 8 == 0
+        and self.rg_lru.gates_impl != _lib.GATES_SIMT):
+      return self._forward_fused(x, segment_pos, return_cache, dev)
     yb = self.linear_y(x)
     xb = self.linear_x(x)
     z, new_cache = recurrent_path(xb, yb, segment_pos, self.conv_1d, self.rg_lru, cache,
                                   return_cache)
     return self.linear_out(z), new_cache
+
+  def _forward_fused(self, x, segment_pos, return_cache, dev):
+    """Prefill of the whole block in one library call: the three projections on the tcgen05 GEMM
+    (gelu of the y branch in its epilogue), the RG-LRU + Conv1D sub-path in between."""
+    bs, l, d = x.shape
+    e = self.lru_width
+    params = [self.linear_y.weight, self.linear_y.bias, self.linear_x.weight, self.linear_x.bias,
+              self.linear_out.weight, self.linear_out.bias, self.conv_1d.w, self.conv_1d.b,
+              self.rg_lru.a_param, self.rg_lru.input_gate.w, self.rg_lru.input_gate.b,
+              self.rg_lru.a_gate.w, self.rg_lru.a_gate.b]
+    layers._same_dtype(x, *params)
+    pos = layers._pos(segment_pos, bs, l)
+    xc = x.contiguous()
+    out = torch.empty_like(xc)
+    h_last = torch.empty((bs, e), dtype=torch.float32, device=dev) if return_cache else None
+    conv_state = torch.empty((bs, 3, e), dtype=x.dtype, device=dev) if return_cache else None
+    lib = _lib.load()
+    p = _lib.RgkBlockParams(
+        path=self.rg_lru._params(self.conv_1d),
+        linear_y_w=self.linear_y.weight.data_ptr(), linear_y_b=self.linear_y.bias.data_ptr(),
+        linear_x_w=self.linear_x.weight.data_ptr(), linear_x_b=self.linear_x.bias.data_ptr(),
+        linear_out_w=self.linear_out.weight.data_ptr(),
+        linear_out_b=self.linear_out.bias.data_ptr())
+    with torch.cuda.device(dev):
+      dt = _lib.dtype_code(x.dtype)
+      ws = _lib.workspace(dev, int(lib.rgk_block_workspace_bytes(bs, l, d, e, dt)))
+      _lib.check(lib.rgk_recurrent_block_prefill(
+          xc.data_ptr(), pos.data_ptr(), _lib.pos_code(pos), ctypes.byref(p), bs, l, d, e,
+          self.num_heads, 4, dt, out.data_ptr(), _lib.ptr(h_last), _lib.ptr(conv_state),
+          ws.data_ptr(), ws.numel(), _lib.stream_ptr(dev)))
+    if not return_cache:
+      return out, None
+    return out, RecurrentBlockCache(rg_lru_state=h_last, conv1d_state=conv_state)
 
   @classmethod
   def init_cache(cls, batch_size: int, lru_width: int, dtype: torch.dtype,

@@ -275,3 +275,53 @@ def test_fused_decode_step_matches_unfused_and_oracle(rg, oracle, shape):
                             op["a_param"], op["gate_x_w"], op["gate_x_b"], op["gate_a_w"],
                             op["gate_a_b"], h0)
   assert_close(o_n, y_plain, tol, "fused, no join")
+
+
+@pytest.mark.parametrize("shape", [(300, 128, 256), (1000, 2560, 2560), (129, 72, 520), (4096, 2560, 2560)],
+                         ids=lambda s: "x".join(map(str, s)))
+@pytest.mark.parametrize("gelu", [False, True], ids=["plain", "gelu"])
+def test_dense_linear_tcgen05(rg, oracle, shape, gelu):
+  """The tensor-core nn.Linear (optionally + gelu) against a float32 evaluation of the same
+  bfloat16 inputs, and on the small shapes against the oracle (ragged M, K and N included)."""
+  m, k, n = shape
+  name = f"dense_{m}_{k}_{n}"
+  dt = torch.bfloat16
+  x = C.normal(name, "x", (m, k), 1.0, dt)
+  w = C.normal(name, "w", (n, k), (1.0 / k) ** 0.5, dt)
+  b = C.normal(name, "b", (n,), 0.2, dt)
+  out = rg.dense_linear(x.to(DEV), w.to(DEV), b.to(DEV), gelu=gelu)
+  ref = torch.nn.functional.linear(x.to(DEV).float(), w.to(DEV).float(), b.to(DEV).float())
+  ref = ref.to(dt).float()
+  if gelu:
+    ref = torch.nn.functional.gelu(ref, approximate="tanh")
+  assert_close(out, ref.to(dt), TOL[dt], "vs float32 torch")
+  assert float((out.float() - ref.to(dt).float()).abs().max()) <= 0.05
+  if m * k * n <= 300 * 128 * 256 * 4:
+    o_ref = oracle.linear(x, w, b)
+    if gelu:
+      o_ref = oracle.gelu_mul(torch.ones_like(o_ref), o_ref)
+    assert_close(out, o_ref, TOL[dt], "vs oracle")
+  out_nb = rg.dense_linear(x.to(DEV), w.to(DEV), None, gelu=gelu)
+  ref_nb = torch.nn.functional.linear(x.to(DEV).float(), w.to(DEV).float()).to(dt).float()
+  if gelu:
+    ref_nb = torch.nn.functional.gelu(ref_nb, approximate="tanh")
+  assert_close(out_nb, ref_nb.to(dt), TOL[dt], "no bias")
+
+
+def test_block_fused_matches_composed(rg):
+  """RecurrentBlock prefill through the single fused-block call (tcgen05 projections) against the
+  same module composed from torch linears + the sub-path call."""
+  from recurrentgemma_b200 import _lib
+  case = C.Case("blockfused", "block", "bfloat16", 2, 777, 2560, 10, width=2560, pos="multi")
+  p = C.make_params(case)
+  inp = _cuda(C.make_inputs(case))
+  m = _block(rg, case, p)
+  y_f, c_f = m(inp["x"], inp["segment_pos"])
+  _lib.workspace_status(_lib.workspace(torch.device(DEV), 1))
+  m.rg_lru.gates_impl = _lib.GATES_TCGEN05
+  yb = m.linear_y(inp["x"]); xb = m.linear_x(inp["x"])
+  z, c_c = rg.recurrent_path(xb, yb, inp["segment_pos"], m.conv_1d, m.rg_lru)
+  y_c = m.linear_out(z)
+  assert_close(y_f, y_c, TOL[torch.bfloat16], "fused vs composed out")
+  assert_close(c_f.rg_lru_state, c_c.rg_lru_state, TOL[torch.bfloat16], "state")
+  assert_close(c_f.conv1d_state, c_c.conv1d_state, TOL[torch.bfloat16], "conv state")
