@@ -239,12 +239,13 @@ def run_gpu(args, cfg):
   def step():
     rg.recurrent_path(xb, yb, pos, conv, lru, out=out)
 
+  from recurrentgemma_b200 import host
+  pipe = host.HostPipeline(conv, lru, t, rows_per_group=1, device=dev)
+
   def step_e2e():
-    xd = xb_h.to(dev, non_blocking=True)
-    yd = yb_h.to(dev, non_blocking=True)
-    o, cache = rg.recurrent_path(xd, yd, pos, conv, lru)
-    out_h.copy_(o, non_blocking=True)
-    cache.rg_lru_state.cpu()   # the step's state read back: also orders the step on the host
+    # public host-buffer API: batch rows streamed through copy-in / compute / copy-out streams
+    h_state, _ = pipe(xb_h, yb_h, pos, out_h)
+    h_state[:1, :1].cpu()      # the step's state read back
 
   for _ in range(max(args.warmup, 3)):
     step()
