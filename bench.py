@@ -335,12 +335,34 @@ def run_gpu(args, cfg):
                         "flops": 2 * 2 * b * t * e * (e // h)}
     del a_t, c, y2
 
+    # The whole RecurrentBlock (config 1 as BASELINE.json words it): the three projections on the
+    # tcgen05 GEMM around the sub-path, one library call.
+    import math
+    gb = torch.Generator(device="cpu").manual_seed(77)
+    blk = rg.RecurrentBlock(e, h, e, device=dev, dtype=dt)
+    sd = dict(p)
+    for nm in ("linear_y", "linear_x", "linear_out"):
+      sd[nm + ".weight"] = (torch.randn((e, e), generator=gb) * math.sqrt(1.0 / e)).to(dt).to(dev)
+      sd[nm + ".bias"] = torch.zeros(e, dtype=dt, device=dev)
+    blk.load_state_dict(sd)
+    x_in = torch.randn((b, t, e), generator=gb).to(dt).to(dev)
+    for _ in range(2):
+      blk(x_in, pos)
+    torch.cuda.synchronize()
+    t_blk = _time_loop(lambda: blk(x_in, pos), ksteps, stream)
+    t_lin = _time_loop(lambda: rg.dense_linear(x_in, sd["linear_x.weight"], sd["linear_x.bias"]),
+                       ksteps, stream)
+    block_info = {"ms": t_blk, "tokens_per_s": b * t / (t_blk * 1e-3),
+                  "linear_ms": t_lin, "linear_TFLOP/s": 2 * b * t * e * e / (t_lin * 1e-3) / 1e12,
+                  "what": "RecurrentBlock.forward prefill, same shapes, projections on the tcgen05 GEMM"}
+    del blk, x_in
   if rank != 0:
     if world > 1:
       dist.destroy_process_group()
     return
 
   hbm_gbs, bf16_tf, which = _peaks()
+  block_info["linear_frac_of_bf16_peak"] = block_info["linear_TFLOP/s"] / bf16_tf
   tokens = b * t
   value = world * tokens / (ms * 1e-3)
   for k in kernels.values():
@@ -369,6 +391,7 @@ def run_gpu(args, cfg):
       "roofline": roofline,
       "cpu_baseline": None if cpu is None else {k: cpu[k] for k in
                                                 ("value", "unit", "cores", "kind", "sample")},
+      "block_prefill": block_info,
       "clocks": clk,
       "gpu_launches": 4 * args.steps,
   }
