@@ -368,12 +368,17 @@ def run_gpu(args, cfg):
   for k in kernels.values():
     k["gbs"] = k["bytes"] / (k["ms"] * 1e-3) / 1e9
     k["tflops"] = k["flops"] / (k["ms"] * 1e-3) / 1e12
+  # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of each kernel at this
+  # workload, from the ncu capture summarised in profiles/ncu_full_cfg1_path_kernels.md.
+  ncu_traffic = {"conv1d_prefill": 288.3e6, "gates": 458.6e6, "scan_gelu": 644.5e6}
   dom_name = max(kernels, key=lambda k: kernels[k]["ms"])
   dom = kernels[dom_name]
   path_bytes = 3 * b * t * e * 2 + 2 * p["rg_lru.input_gate.w"].numel() * 2
   roofline = {
       "bound": "hbm", "kernel": dom_name, "achieved": dom["gbs"], "peak": hbm_gbs, "unit": "GB/s",
-      "frac": dom["gbs"] / hbm_gbs, "peak_source": which, "traffic": None,
+      "frac": dom["gbs"] / hbm_gbs, "peak_source": which,
+      "traffic": ncu_traffic.get(dom_name) if cfg["batch"] == CFG1["batch"] else None,
+      "algorithmic_bytes": dom["bytes"],
       "path": {"algorithmic_bytes": path_bytes, "achieved": path_bytes / (ms * 1e-3) / 1e9,
                "frac": path_bytes / (ms * 1e-3) / 1e9 / hbm_gbs,
                "frac_of_nominal_8TBs": path_bytes / (ms * 1e-3) / 1e9 / 8000.0},
