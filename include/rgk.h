@@ -51,9 +51,13 @@ enum { RGK_I32 = 0, RGK_I64 = 1 };
 
 /* Which kernels a composed call may use for the block-diagonal gate projections. */
 enum {
-  RGK_GATES_AUTO = 0,   /* tcgen05 kernel when dtype is bf16 and the head width is 256 */
-  RGK_GATES_SIMT = 1,   /* CUDA-core kernel (any head width that is a multiple of 16; float32) */
-  RGK_GATES_TCGEN05 = 2 /* tensor-core kernel; RGK_ESHAPE if the shape is not covered */
+  RGK_GATES_AUTO = 0,    /* the fastest kernel that covers the shape (see below) */
+  RGK_GATES_SIMT = 1,    /* CUDA-core gate kernel, then the scan kernel (any head width that is a
+                            multiple of 16; float32 or bfloat16) */
+  RGK_GATES_TCGEN05 = 2, /* tensor-core gate kernel, then the scan kernel (bfloat16, head width
+                            256); RGK_ESHAPE if the shape is not covered */
+  RGK_GATES_FUSED = 3    /* gates, gate arithmetic and scan in one tensor-core kernel (bfloat16,
+                            head width 256, T a multiple of 128); RGK_ESHAPE otherwise */
 };
 
 RGK_API int rgk_abi_version(void);

@@ -120,6 +120,40 @@ int run_gates(const void* c, const void* pos, int pos64, const rgk_params* p, in
   return RGK_OK;
 }
 
+// RG-LRU on a conv output c: fused kernel when asked for / possible, else gates then scan.
+int run_rglru(const void* c, const void* pos, int pos64, const rgk_params* p, const float* h0,
+              const void* yb, int y_activated, int64_t B, int64_t T, int64_t E, int H, int dtype,
+              int gates_impl, void* wpack, void* a_buf, void* xn_buf, void* scan_ws, void* out,
+              float* h_last, cudaStream_t s) {
+  const int bw = (int)(E / H);
+  const bool fused_ok = rgk::rglru_fused_supported(dtype, bw, B, T);
+  if (gates_impl == RGK_GATES_FUSED && !fused_ok)
+    return fail(RGK_ESHAPE, "the fused RG-LRU kernel covers bfloat16, head width 256 and sequence "
+                            "lengths that are multiples of 128 (dtype %d, head width %d, T %lld)",
+                dtype, bw, (long long)T);
+  if (fused_ok && (gates_impl == RGK_GATES_AUTO || gates_impl == RGK_GATES_FUSED)) {
+    const void* packed = p->gates_packed;
+    if (packed == nullptr) {
+      cudaError_t e = rgk::launch_pack_gate_weights(p->gate_x_w, p->gate_a_w, H, wpack, s);
+      if (e != cudaSuccess) return cuda_fail(e, "pack_gate_weights launch");
+      packed = wpack;
+    }
+    cudaError_t e = rgk::launch_rglru_fused(c, pos, pos64, p->a_param, p->gate_x_b, p->gate_a_b,
+                                            packed, h0, yb, y_activated, B, T, H, out, h_last,
+                                            scan_ws, s);
+    if (e != cudaSuccess) return cuda_fail(e, "fused RG-LRU launch");
+    return RGK_OK;
+  }
+  int rc = run_gates(c, pos, pos64, p, B * T, H, bw, dtype,
+                     gates_impl == RGK_GATES_FUSED ? RGK_GATES_AUTO : gates_impl, wpack, a_buf,
+                     xn_buf, scan_ws, s);
+  if (rc) return rc;
+  cudaError_t e = rgk::launch_scan(xn_buf, a_buf, nullptr, nullptr, 0, h0, yb, y_activated, B, T, E,
+                                   dtype, out, h_last, scan_ws, s);
+  if (e != cudaSuccess) return cuda_fail(e, "scan launch");
+  return RGK_OK;
+}
+
 // Carves the workspace of the composed calls: [scan scratch | c | a | xn | packed gate weights].
 struct PathWs {
   void* scan;
@@ -132,7 +166,9 @@ struct PathWs {
 
 PathWs carve(void* ws, int64_t B, int64_t T, int64_t E, int dtype) {
   PathWs w;
-  const size_t scan_bytes = rgk::scan_workspace_bytes(B, T, E, dtype);
+  size_t scan_bytes = rgk::scan_workspace_bytes(B, T, E, dtype);
+  const size_t fused_bytes = dtype == RGK_BF16 ? rgk::rglru_fused_workspace_bytes(B, T, E) : 0;
+  if (fused_bytes > scan_bytes) scan_bytes = fused_bytes;
   const size_t act = up256(static_cast<size_t>(B) * T * E * elem_size(dtype));
   char* base = static_cast<char*>(ws);
   w.scan = base;
@@ -303,7 +339,7 @@ int rgk_rglru_forward(const void* x, const void* segment_pos, int pos_dtype, con
   if ((rc = check_heads(E, H))) return rc;
   if ((rc = check_params(p, false))) return rc;
   RGK_REQUIRE(pos_dtype == RGK_I32 || pos_dtype == RGK_I64, RGK_EINVAL, "unknown index dtype");
-  RGK_REQUIRE(gates_impl >= RGK_GATES_AUTO && gates_impl <= RGK_GATES_TCGEN05, RGK_EINVAL,
+  RGK_REQUIRE(gates_impl >= RGK_GATES_AUTO && gates_impl <= RGK_GATES_FUSED, RGK_EINVAL,
               "unknown gates_impl %d", gates_impl);
   RGK_REQUIRE(x && segment_pos && y, RGK_EINVAL, "NULL pointer argument");
   RGK_REQUIRE(aligned16(x) && aligned16(y) && aligned16(h0) && aligned16(h_last), RGK_EALIGN,
@@ -318,13 +354,9 @@ int rgk_rglru_forward(const void* x, const void* segment_pos, int pos_dtype, con
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int bw = (int)(E / H);
   RGK_CUDA(cudaMemsetAsync(workspace, 0, sizeof(int), s), "cudaMemsetAsync");
-  if ((rc = run_gates(x, segment_pos, pos_dtype, p, B * T, H, bw, dtype, gates_impl, w.wpack, w.a,
-                      w.xn, workspace, s)))
-    return rc;
-  RGK_CUDA(rgk::launch_scan(w.xn, w.a, nullptr, nullptr, 0, h0, nullptr, 0, B, T, E, dtype, y, h_last,
-                            w.scan, s),
-           "scan launch");
-  return RGK_OK;
+  (void)bw;
+  return run_rglru(x, segment_pos, pos_dtype, p, h0, nullptr, 0, B, T, E, H, dtype, gates_impl,
+                   w.wpack, w.a, w.xn, w.scan, y, h_last, s);
 }
 
 int rgk_recurrent_path_prefill(const void* xb, const void* yb, const void* segment_pos,
@@ -338,7 +370,7 @@ int rgk_recurrent_path_prefill(const void* xb, const void* yb, const void* segme
   if ((rc = check_params(p, true))) return rc;
   RGK_REQUIRE(W == 4, RGK_ESHAPE, "temporal width %d is not supported (only 4)", W);
   RGK_REQUIRE(pos_dtype == RGK_I32 || pos_dtype == RGK_I64, RGK_EINVAL, "unknown index dtype");
-  RGK_REQUIRE(gates_impl >= RGK_GATES_AUTO && gates_impl <= RGK_GATES_TCGEN05, RGK_EINVAL,
+  RGK_REQUIRE(gates_impl >= RGK_GATES_AUTO && gates_impl <= RGK_GATES_FUSED, RGK_EINVAL,
               "unknown gates_impl %d", gates_impl);
   RGK_REQUIRE(xb && segment_pos && out, RGK_EINVAL, "NULL pointer argument");
   RGK_REQUIRE(aligned16(xb) && aligned16(yb) && aligned16(out) && aligned16(h0) &&
@@ -358,13 +390,9 @@ int rgk_recurrent_path_prefill(const void* xb, const void* yb, const void* segme
   RGK_CUDA(rgk::launch_conv1d_prefill(xb, segment_pos, pos_dtype, p->conv_w, p->conv_b, B, T, E,
                                       dtype, w.c, conv_cache_out, s),
            "conv1d_prefill launch");
-  if ((rc = run_gates(w.c, segment_pos, pos_dtype, p, B * T, H, bw, dtype, gates_impl, w.wpack, w.a,
-                      w.xn, workspace, s)))
-    return rc;
-  RGK_CUDA(rgk::launch_scan(w.xn, w.a, nullptr, nullptr, 0, h0, yb, 0, B, T, E, dtype, out, h_last,
-                            w.scan, s),
-           "scan launch");
-  return RGK_OK;
+  (void)bw;
+  return run_rglru(w.c, segment_pos, pos_dtype, p, h0, yb, 0, B, T, E, H, dtype, gates_impl,
+                   w.wpack, w.a, w.xn, w.scan, out, h_last, s);
 }
 
 int rgk_dense_linear(const void* x, const void* weight, const void* bias, int64_t M, int64_t K,
@@ -443,13 +471,10 @@ int rgk_recurrent_block_prefill(const void* x, const void* segment_pos, int pos_
   RGK_CUDA(rgk::launch_conv1d_prefill(xb, segment_pos, pos_dtype, p->path.conv_w, p->path.conv_b, B,
                                       T, E, dtype, w.c, conv_cache_out, s),
            "conv1d_prefill launch");
-  if ((rc = run_gates(w.c, segment_pos, pos_dtype, &p->path, M, H, bw, dtype, RGK_GATES_AUTO,
-                      w.wpack, w.a, w.xn, workspace, s)))
-    return rc;
   // the conv has consumed xb: its buffer now receives y * gelu(yb)
-  RGK_CUDA(rgk::launch_scan(w.xn, w.a, nullptr, nullptr, 0, nullptr, yb, 1, B, T, E, dtype, xb,
-                            h_last, w.scan, s),
-           "scan launch");
+  if ((rc = run_rglru(w.c, segment_pos, pos_dtype, &p->path, nullptr, yb, 1, B, T, E, H, dtype,
+                      RGK_GATES_AUTO, w.wpack, w.a, w.xn, w.scan, xb, h_last, s)))
+    return rc;
   RGK_CUDA(rgk::launch_dense_tc(xb, p->linear_out_w, p->linear_out_b, M, (int)E, (int)D, 0, out,
                                 status, s),
            "linear_out launch");
@@ -468,7 +493,7 @@ int rgk_recurrent_path_decode(const void* xb, const void* yb, const void* segmen
   if ((rc = check_params(p, true))) return rc;
   RGK_REQUIRE(W == 4, RGK_ESHAPE, "temporal width %d is not supported (only 4)", W);
   RGK_REQUIRE(pos_dtype == RGK_I32 || pos_dtype == RGK_I64, RGK_EINVAL, "unknown index dtype");
-  RGK_REQUIRE(gates_impl >= RGK_GATES_AUTO && gates_impl <= RGK_GATES_TCGEN05, RGK_EINVAL,
+  RGK_REQUIRE(gates_impl >= RGK_GATES_AUTO && gates_impl <= RGK_GATES_FUSED, RGK_EINVAL,
               "unknown gates_impl %d", gates_impl);
   RGK_REQUIRE(xb && segment_pos && h_in && conv_cache_in && out && h_out, RGK_EINVAL,
               "NULL pointer argument");

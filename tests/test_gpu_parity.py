@@ -325,3 +325,50 @@ def test_block_fused_matches_composed(rg):
   assert_close(y_f, y_c, TOL[torch.bfloat16], "fused vs composed out")
   assert_close(c_f.rg_lru_state, c_c.rg_lru_state, TOL[torch.bfloat16], "state")
   assert_close(c_f.conv1d_state, c_c.conv1d_state, TOL[torch.bfloat16], "conv state")
+
+
+@pytest.mark.parametrize("shape", [(1, 128, 256, 1), (2, 384, 512, 2), (1, 8192, 256, 1),
+                                   (3, 1024, 2560, 10), (8, 4096, 2560, 10)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_fused_rglru_kernel(rg, oracle, shape):
+  """Gates + gate arithmetic + scan (+ join) in one tensor-core kernel against the two-kernel
+  tensor-core route (same roundings; only the association of the carries differs) and, on the
+  smaller shapes, against the oracle.  Covers one unit per sequence, carries inside one round of
+  CTAs (B = 1, long T), and carries across rounds."""
+  from recurrentgemma_b200 import _lib
+  b, t, e, h = shape
+  case = C.Case(f"fused_{b}_{t}_{e}", "rglru", "bfloat16", b, t, e, h, pos="multi")
+  p = C.make_params(case)
+  inp = C.make_inputs(case)
+  dt = torch.bfloat16
+  m = rg.RGLRU(e, h, device=DEV, dtype=dt)
+  m.load_state_dict({k[len("rg_lru."):]: v for k, v in p.items() if k.startswith("rg_lru.")})
+  conv = rg.Conv1D(e, 4, device=DEV, dtype=dt)
+  conv.load_state_dict({"w": p["conv_1d.w"], "b": p["conv_1d.b"]})
+  x, pos = inp["x"].to(DEV), inp["segment_pos"].to(DEV)
+  h0 = C.normal(case.name, "h0", (b, e), 0.5).to(DEV)
+  yb = C.normal(case.name, "yb", (b, t, e), 1.0, dt).to(DEV)
+  ws = _lib.workspace(torch.device(DEV), 1)
+  m.gates_impl = _lib.GATES_FUSED
+  y_f, h_f = m(x, pos, h0)
+  _lib.workspace_status(ws)
+  o_f, c_f = rg.recurrent_path(x, yb, pos, conv, m)
+  _lib.workspace_status(ws)
+  m.gates_impl = _lib.GATES_TCGEN05
+  y_u, h_u = m(x, pos, h0)
+  o_u, c_u = rg.recurrent_path(x, yb, pos, conv, m)
+  tol = TOL[dt]
+  assert_close(y_f, y_u, 5e-3, "fused vs two-kernel y")
+  assert_close(h_f, h_u, 5e-3, "fused vs two-kernel h")
+  assert_close(o_f, o_u, 5e-3, "fused vs two-kernel path out")
+  assert_close(c_f.rg_lru_state, c_u.rg_lru_state, 5e-3, "fused vs two-kernel path state")
+  assert float((y_f != y_u).float().mean()) < 0.02
+  if b * t * e <= 2 * 384 * 512 * 8:
+    y_r, h_r = oracle.rglru(inp["x"], inp["segment_pos"], p["rg_lru.a_param"],
+                            p["rg_lru.input_gate.w"], p["rg_lru.input_gate.b"],
+                            p["rg_lru.a_gate.w"], p["rg_lru.a_gate.b"], h0.cpu())
+    assert_close(y_f, y_r, tol, "fused vs oracle y")
+    assert_close(h_f, h_r, tol, "fused vs oracle h")
+  with pytest.raises(_lib.RgkError):      # T not a multiple of 128
+    m.gates_impl = _lib.GATES_FUSED
+    m(x[:, :100].contiguous(), pos[:, :100].contiguous())
