@@ -314,25 +314,38 @@ def run_gpu(args, cfg):
                                      yb.data_ptr() if mul else None, b, t, e, dtc, y2.data_ptr(),
                                      h_last.data_ptr(), ws.data_ptr(), ws.numel(), sp))
 
-    def k_lru():
+    def k_lru(impl):
       _lib.check(lib.rgk_rglru_forward(c.data_ptr(), pos.data_ptr(), _lib.RGK_I64,
-                                       ctypes.byref(prm), None, b, t, e, h, dtc, lru.gates_impl,
+                                       ctypes.byref(prm), None, b, t, e, h, dtc, impl,
                                        y2.data_ptr(), h_last.data_ptr(), ws.data_ptr(), ws.numel(),
                                        sp))
 
-    for fn in (k_conv, lambda: k_scan(True), lambda: k_scan(False), k_lru):
+    def k_path():
+      _lib.check(lib.rgk_recurrent_path_prefill(
+          xb.data_ptr(), yb.data_ptr(), pos.data_ptr(), _lib.RGK_I64, ctypes.byref(prm), None, b, t,
+          e, h, 4, dtc, lru.gates_impl, y2.data_ptr(), h_last.data_ptr(), None, ws.data_ptr(),
+          ws.numel(), sp))
+
+    for fn in (k_conv, lambda: k_scan(True), lambda: k_scan(False),
+               lambda: k_lru(_lib.GATES_TCGEN05), k_path):
       fn()
     torch.cuda.synchronize()
-    kernels["conv1d_prefill"] = {"ms": _time_loop(k_conv, ksteps, stream), "bytes": 2 * n_el * es,
-                                 "flops": 8 * n_el}
-    kernels["scan_gelu"] = {"ms": _time_loop(lambda: k_scan(True), ksteps, stream),
-                            "bytes": 4 * n_el * es, "flops": 12 * n_el}
-    # gate projections + gate arithmetic = (RGLRU forward) - (scan without the join)
-    t_lru = _time_loop(k_lru, ksteps, stream)
-    t_scan_plain = _time_loop(lambda: k_scan(False), ksteps, stream)
     gw = p["rg_lru.input_gate.w"].numel() * es
-    kernels["gates"] = {"ms": max(t_lru - t_scan_plain, 1e-6), "bytes": 3 * n_el * es + 2 * gw,
-                        "flops": 2 * 2 * b * t * e * (e // h)}
+    gate_flops = 2 * 2 * b * t * e * (e // h)
+    t_conv = _time_loop(k_conv, ksteps, stream)
+    t_path = _time_loop(k_path, ksteps, stream)
+    kernels["conv1d_prefill"] = {"ms": t_conv, "bytes": 2 * n_el * es, "flops": 8 * n_el}
+    # The rest of the step is ONE kernel: gate projections (tcgen05) + gate arithmetic + scan + join.
+    # Its algorithmic bytes: conv output and y branch in, joined output out, gate weights.
+    kernels["rglru_fused"] = {"ms": max(t_path - t_conv, 1e-6), "bytes": 3 * n_el * es + 2 * gw,
+                              "flops": gate_flops + 20 * n_el}
+    # For comparison, the two-kernel route the library takes when T is not a multiple of 128.
+    t_scan = _time_loop(lambda: k_scan(True), ksteps, stream)
+    t_lru_tc = _time_loop(lambda: k_lru(_lib.GATES_TCGEN05), ksteps, stream)
+    t_scan_plain = _time_loop(lambda: k_scan(False), ksteps, stream)
+    two_kernel = {"gates_tc_ms": max(t_lru_tc - t_scan_plain, 1e-6), "scan_join_ms": t_scan,
+                  "gates_tc_GB/s": (3 * n_el * es + 2 * gw) / max(t_lru_tc - t_scan_plain, 1e-6) / 1e6,
+                  "scan_join_GB/s": 4 * n_el * es / t_scan / 1e6}
     del a_t, c, y2
 
     # The whole RecurrentBlock (config 1 as BASELINE.json words it): the three projections on the
@@ -370,7 +383,7 @@ def run_gpu(args, cfg):
     k["tflops"] = k["flops"] / (k["ms"] * 1e-3) / 1e12
   # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of each kernel at this
   # workload, from the ncu capture summarised in profiles/ncu_full_cfg1_path_kernels.md.
-  ncu_traffic = {"conv1d_prefill": 288.3e6, "gates": 458.6e6, "scan_gelu": 644.5e6}
+  ncu_traffic = {"conv1d_prefill": 288.3e6, "rglru_fused": 596.5e6}
   dom_name = max(kernels, key=lambda k: kernels[k]["ms"])
   dom = kernels[dom_name]
   path_bytes = 3 * b * t * e * 2 + 2 * p["rg_lru.input_gate.w"].numel() * 2
@@ -384,6 +397,10 @@ def run_gpu(args, cfg):
                "frac_of_nominal_8TBs": path_bytes / (ms * 1e-3) / 1e9 / 8000.0},
       "kernels": {k: {"ms": round(v["ms"], 4), "GB/s": round(v["gbs"], 1),
                       "TFLOP/s": round(v["tflops"], 2)} for k, v in kernels.items()},
+      "two_kernel_route": {k: round(v, 4) for k, v in two_kernel.items()},
+      "note": ("rglru_fused is bounded by the SFU and issue pipes (5 SFU operations and ~70 "
+               "instructions per element with the reference's bfloat16 roundings), not by HBM; "
+               "frac is its algorithmic bytes over its time against the measured copy bandwidth"),
   }
   cpu = None if args.no_cpu else cpu_leg(cfg, 2, 1)
   line = {
@@ -398,7 +415,7 @@ def run_gpu(args, cfg):
                                                 ("value", "unit", "cores", "kind", "sample")},
       "block_prefill": block_info,
       "clocks": clk,
-      "gpu_launches": 4 * args.steps,
+      "gpu_launches": 3 * args.steps,
   }
   if e2e_ms is not None:
     line["e2e"] = {"value": world * tokens / (e2e_ms * 1e-3), "unit": UNIT,
