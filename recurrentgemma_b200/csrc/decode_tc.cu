@@ -99,7 +99,9 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __nv_bfloat16*
   const uint32_t tmem_base = *s_tmem;
 
   // ---- weights: 64 x-gate rows and 64 a-gate rows of this quarter, per K slice -------------------
+  // (After the dependency wait: the packed copy may have been written by the kernel just before.)
   if (tid == 0) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     mbar_expect_tx(bar_b, kSlices * kBSlice);
     const int group_row = (head * 2 + (quarter >> 1)) * 256 + (quarter & 1) * kChanCta;
     for (int k = 0; k < kSlices; ++k) {
@@ -119,6 +121,12 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __nv_bfloat16*
     const uint4 bv = *reinterpret_cast<const uint4*>(conv_b + e);
     const bool own = (pk >> 3) == quarter;        // this CTA also shifts the cache of its channels
     uint8_t* a_slice = smem + kOffA + (pk >> 3) * kASlice;
+    // Everything above (barriers, TMEM, the per-channel constants) is independent of the kernel
+    // before this one on the stream, which in a decode loop is the previous layer: with
+    // programmatic dependent launch it overlaps that kernel's tail.  The activations below are its
+    // output, so wait for it here, then let the next layer's prologue start in turn.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     // 16 rows per thread, in two batches of 8 whose 32 loads are all issued before the first use:
     // the step is latency bound, so bytes in flight are what counts.
     constexpr int kBatch = 8;
@@ -291,12 +299,25 @@ cudaError_t launch_path_decode_tc(const void* xb, const void* yb, const void* po
   }
   const dim3 grid((unsigned)(H * 4), (unsigned)((B + kRowsM - 1) / kRowsM));
   const int E = H * kHeadW;
+  // Launched with programmatic stream serialization: the kernel may start while its predecessor
+  // on the stream is still draining; it orders itself with griddepcontrol.wait.
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kThreadsDec);
+  cfg.dynamicSmemBytes = kSmem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
 #define RGK_DEC(MUL)                                                                               \
-  decode_tc_kernel<MUL><<<grid, kThreadsDec, kSmem, s>>>(                                          \
-      map_w, (const T_*)xb, (const T_*)yb, pos, pos64, (const T_*)conv_w, (const T_*)conv_b,       \
-      (const T_*)a_param, (const T_*)bx, (const T_*)ba, h_in, (const T_*)cache_in, (int)B, E,      \
-      (T_*)out, h_out, (T_*)cache_out, reinterpret_cast<WsHeader*>(ws_header))
-  if (yb) RGK_DEC(true); else RGK_DEC(false);
+  cudaLaunchKernelEx(&cfg, decode_tc_kernel<MUL>, map_w, (const T_*)xb, (const T_*)yb, pos, pos64, \
+                     (const T_*)conv_w, (const T_*)conv_b, (const T_*)a_param, (const T_*)bx,      \
+                     (const T_*)ba, h_in, (const T_*)cache_in, (int)B, E, (T_*)out, h_out,         \
+                     (T_*)cache_out, reinterpret_cast<WsHeader*>(ws_header))
+  cudaError_t lerr = yb ? RGK_DEC(true) : RGK_DEC(false);
+  if (lerr != cudaSuccess) return lerr;
 #undef RGK_DEC
   return cudaGetLastError();
 }

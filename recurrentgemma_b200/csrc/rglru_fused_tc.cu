@@ -85,15 +85,6 @@ __device__ __forceinline__ float ld_cg_f32(const float* p) {
 __device__ __forceinline__ void named_bar_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" :: "r"(id), "r"(threads) : "memory");
 }
-__device__ __forceinline__ void tc_ld_32x16(uint32_t taddr, uint32_t (&v)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
-        "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
-        "=r"(v[14]), "=r"(v[15])
-      : "r"(taddr) : "memory");
-}
 __device__ __forceinline__ float gelu_fast_f(float z) {
   constexpr float k0 = -1.5957691216057308f * 1.4426950408889634f;
   constexpr float k1 = k0 * 0.044715f;
@@ -347,11 +338,24 @@ rglru_fused_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_const
                 if (timed_out) break;
                 __syncwarp();
                 const int n_agg = L < 32 ? L : 32;
-                for (int j = 0; j < n_agg; ++j) {
-                  const int64_t r2 = rec - (int64_t)(tt - (base - j)) * per_tt * 4;
-                  const float pj = ld_cg_f32(agg[r2].P + lane), hj = ld_cg_f32(agg[r2].H + lane);
-                  Hc = fmaf(Pc, hj, Hc);
-                  Pc *= pj;
+                // records are fetched eight at a time, all loads before the first use: the walk
+                // costs about one L2 round trip per eight predecessors instead of one each
+                for (int j0 = 0; j0 < n_agg; j0 += 8) {
+                  float pj[8], hj[8];
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) {
+                    const int j = min(j0 + i, n_agg - 1);
+                    const int64_t r2 = rec - (int64_t)(tt - (base - j)) * per_tt * 4;
+                    pj[i] = ld_cg_f32(agg[r2].P + lane);
+                    hj[i] = ld_cg_f32(agg[r2].H + lane);
+                  }
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) {
+                    if (j0 + i < n_agg) {
+                      Hc = fmaf(Pc, hj[i], Hc);
+                      Pc *= pj[i];
+                    }
+                  }
                 }
                 if (L < 32) {
                   const int64_t r2 = rec - (int64_t)(tt - (base - L)) * per_tt * 4;
