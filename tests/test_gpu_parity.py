@@ -372,3 +372,27 @@ def test_fused_rglru_kernel(rg, oracle, shape):
   with pytest.raises(_lib.RgkError):      # T not a multiple of 128
     m.gates_impl = _lib.GATES_FUSED
     m(x[:, :100].contiguous(), pos[:, :100].contiguous())
+
+
+def test_host_pipeline_matches_device_call(rg):
+  """The host-buffer pipeline (rows streamed through copy-in / compute / copy-out streams) returns
+  what the device-resident call returns."""
+  from recurrentgemma_b200 import host
+  case = C.Case("hostpipe", "rglru", "bfloat16", 4, 512, 512, 2, pos="multi")
+  p = C.make_params(case)
+  dt = torch.bfloat16
+  conv = rg.Conv1D(512, 4, device=DEV, dtype=dt)
+  conv.load_state_dict({"w": p["conv_1d.w"], "b": p["conv_1d.b"]})
+  lru = rg.RGLRU(512, 2, device=DEV, dtype=dt)
+  lru.load_state_dict({k[len("rg_lru."):]: v for k, v in p.items() if k.startswith("rg_lru.")})
+  xb = C.normal(case.name, "xb", (4, 512, 512), 1.0, dt).pin_memory()
+  yb = C.normal(case.name, "yb", (4, 512, 512), 1.0, dt).pin_memory()
+  pos = C.make_segment_pos("multi", 4, 512, case.name).to(DEV)
+  out_h = torch.empty_like(xb).pin_memory()
+  pipe = host.HostPipeline(conv, lru, 512, rows_per_group=1)
+  for _ in range(2):       # second call reuses the staging buffers
+    h_state, c_state = pipe(xb, yb, pos, out_h)
+  o_ref, cache = rg.recurrent_path(xb.to(DEV), yb.to(DEV), pos, conv, lru)
+  assert_close(out_h, o_ref, 1e-6, "out")
+  assert_close(h_state, cache.rg_lru_state, 1e-6, "state")
+  assert torch.equal(c_state, cache.conv1d_state)
