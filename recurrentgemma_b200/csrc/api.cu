@@ -126,7 +126,7 @@ int run_rglru(const void* c, const void* pos, int pos64, const rgk_params* p, co
               int gates_impl, void* wpack, void* a_buf, void* xn_buf, void* scan_ws, void* out,
               float* h_last, cudaStream_t s) {
   const int bw = (int)(E / H);
-  const bool fused_ok = rgk::rglru_fused_supported(dtype, bw, B, T);
+  const bool fused_ok = rgk::rglru_chan_supported(dtype, bw, B, T);
   if (gates_impl == RGK_GATES_FUSED && !fused_ok)
     return fail(RGK_ESHAPE, "the fused RG-LRU kernel covers bfloat16, head width 256 and sequence "
                             "lengths that are multiples of 128 (dtype %d, head width %d, T %lld)",
@@ -138,9 +138,9 @@ int run_rglru(const void* c, const void* pos, int pos64, const rgk_params* p, co
       if (e != cudaSuccess) return cuda_fail(e, "pack_gate_weights launch");
       packed = wpack;
     }
-    cudaError_t e = rgk::launch_rglru_fused(c, pos, pos64, p->a_param, p->gate_x_b, p->gate_a_b,
-                                            packed, h0, yb, y_activated, B, T, H, out, h_last,
-                                            scan_ws, s);
+    cudaError_t e = rgk::launch_rglru_chan(c, pos, pos64, p->a_param, p->gate_x_b, p->gate_a_b,
+                                           packed, h0, yb, y_activated, B, T, H, out, h_last,
+                                           scan_ws, s);
     if (e != cudaSuccess) return cuda_fail(e, "fused RG-LRU launch");
     return RGK_OK;
   }
@@ -167,7 +167,7 @@ struct PathWs {
 PathWs carve(void* ws, int64_t B, int64_t T, int64_t E, int dtype) {
   PathWs w;
   size_t scan_bytes = rgk::scan_workspace_bytes(B, T, E, dtype);
-  const size_t fused_bytes = dtype == RGK_BF16 ? rgk::rglru_fused_workspace_bytes(B, T, E) : 0;
+  const size_t fused_bytes = dtype == RGK_BF16 ? rgk::rglru_chan_workspace_bytes(B, T, E) : 0;
   if (fused_bytes > scan_bytes) scan_bytes = fused_bytes;
   const size_t act = up256(static_cast<size_t>(B) * T * E * elem_size(dtype));
   char* base = static_cast<char*>(ws);

@@ -56,8 +56,9 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __nv_bfloat16*
                  __nv_bfloat16* __restrict__ out, float* __restrict__ h_out,
                  __nv_bfloat16* __restrict__ cache_out, WsHeader* hdr) {
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                             ~static_cast<uintptr_t>(1023));
+  // aligned by an offset into the shared array, so that the address space stays known to the
+  // compiler (shared-memory load/store instructions instead of generic ones)
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   const uint32_t s_base = smem_u32(smem);
   uint32_t* s_const = reinterpret_cast<uint32_t*>(smem + kOffConst);
   const uint32_t bar_b = s_base + kOffBar, bar_mma = s_base + kOffBar + 8;

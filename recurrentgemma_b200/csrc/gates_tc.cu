@@ -66,8 +66,9 @@ gates_tc_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_constant
                 int ctas_per_group, __nv_bfloat16* __restrict__ a_out,
                 __nv_bfloat16* __restrict__ xn_out, WsHeader* hdr) {
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                             ~static_cast<uintptr_t>(1023));
+  // aligned by an offset into the shared array, so that the address space stays known to the
+  // compiler (shared-memory load/store instructions instead of generic ones)
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   const uint32_t s_base = smem_u32(smem);
   const uint32_t s_b = s_base + kOffB, s_a = s_base + kOffA;
   uint32_t* s_const = reinterpret_cast<uint32_t*>(smem + kOffConst);   // [3][64] packed pairs
@@ -195,6 +196,10 @@ gates_tc_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_constant
         for (int u = 0; u < 8; ++u)
           cv[u] = *reinterpret_cast<const uint4*>(a_row_smem + ((u ^ (r & 7)) << 4));
       }
+      // The slice is handed back to the copy engine below.  The values above are not used until
+      // after the accumulator wait, so nothing else keeps the loads ahead of the release: the fence
+      // makes every lane's loads complete before the warp-level barrier that precedes it.
+      __threadfence_block();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_a_empty(my_slice));
       ok = mbar_wait(bar_acc_full(s), (it >> 1) & 1, s_abort);

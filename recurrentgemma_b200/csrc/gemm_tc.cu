@@ -41,8 +41,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                const __nv_bfloat16* __restrict__ bias, int64_t M, int N, int K, int m_tiles,
                int n_tiles, __nv_bfloat16* __restrict__ out, int* status) {
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                             ~static_cast<uintptr_t>(1023));
+  // aligned by an offset into the shared array, so that the address space stays known to the
+  // compiler (shared-memory load/store instructions instead of generic ones)
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   const uint32_t s_base = smem_u32(smem);
   const uint32_t bar0 = s_base + kOffBarG;
   auto bar_full = [&](int s) { return bar0 + 8u * s; };

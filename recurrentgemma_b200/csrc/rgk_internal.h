@@ -49,16 +49,16 @@ cudaError_t launch_path_decode_tc(const void* xb, const void* yb, const void* po
                                   void* out, float* h_out, void* cache_out, void* ws_header,
                                   cudaStream_t s);
 
-// rglru_fused_tc.cu: gate projections + gate arithmetic + scan (+ join) in one kernel; bfloat16,
-// head width 256, T a multiple of 128.  ws: rglru_fused_workspace_bytes(B, T, E) bytes whose first
-// word is the caller's status word.
-bool rglru_fused_supported(int dtype, int bw, int64_t B, int64_t T);
-size_t rglru_fused_workspace_bytes(int64_t B, int64_t T, int64_t E);
-cudaError_t launch_rglru_fused(const void* c, const void* pos, int pos64, const void* a_param,
-                               const void* bx, const void* ba, const void* packed_w,
-                               const float* h0, const void* yb, int y_activated, int64_t B,
-                               int64_t T, int H, void* out, float* h_last, void* ws,
-                               cudaStream_t s);
+// rglru_chan_tc.cu: gate projections + gate arithmetic + scan (+ join) in one kernel with
+// channel-major accumulators (TMEM lane = channel), so that gate arithmetic, recurrence and join
+// run in registers in time order; bfloat16, head width 256, T a multiple of 128.
+// ws: rglru_chan_workspace_bytes(B, T, E) bytes whose first word is the caller's status word.
+bool rglru_chan_supported(int dtype, int bw, int64_t B, int64_t T);
+size_t rglru_chan_workspace_bytes(int64_t B, int64_t T, int64_t E);
+cudaError_t launch_rglru_chan(const void* c, const void* pos, int pos64, const void* a_param,
+                              const void* bx, const void* ba, const void* packed_w, const float* h0,
+                              const void* yb, int y_activated, int64_t B, int64_t T, int H,
+                              void* out, float* h_last, void* ws, cudaStream_t s);
 
 // gemm_tc.cu: out [M,N] = x [M,K] W[N,K]^T + bias (bfloat16, float32 accumulation) on tcgen05;
 // gelu != 0 applies gelu_tanh to the rounded result.  status: optional device int raised on a

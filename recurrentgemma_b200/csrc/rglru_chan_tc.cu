@@ -1,0 +1,636 @@
+// RG-LRU forward in ONE kernel with channel-major accumulators: the block-diagonal gate projections
+// run on tcgen05 as  D[channel, token] = W[channel, k] . C[token, k]^T,  so that a TMEM lane is a
+// channel and its columns are consecutive tokens.  An epilogue thread then owns one channel and a
+// run of 32 tokens: gate arithmetic, the linear recurrence and the join with the other branch all
+// happen in its registers, in time order, with no transposition (recurrentgemma torch/layers.py:
+// 127-137, 313-365, 140-191; join of torch/modules.py:627-628, 646).  The recurrence coefficients a
+// and the normalised input never reach HBM.  bfloat16, heads of width 256, sequence length a
+// multiple of 128.
+//
+// Units of work: 128 consecutive tokens of one sequence x one half of a head (128 channels).  Units
+// are numbered time-major and dealt out round-robin to persistent CTAs, one per SM, so the unit that
+// produces a carry has normally finished one round before the unit that consumes it starts.
+//
+// Roles in a CTA (18 warps):
+//   producer  one thread: per K-slice of 64 the conv-output tile (128 tokens x 64, operand B) and the
+//             packed gate weights (256 gate rows x 64, operand A) by TMA into a 3-stage ring;
+//   MMA       one thread: per K-step two tcgen05.mma M128 N128 (x-gate rows, a-gate rows) into one
+//             of two TMEM accumulator sets (2 x 128 columns each);
+//   epilogue  16 warps = 4 channel quarters (the warp's TMEM lane quarter) x 4 token quarters.
+//             A warp fetches its own 32 x 32 tiles of the conv output and of the other branch by
+//             TMA into 2 KiB buffers, and writes its outputs into the second buffer, which a TMA
+//             store sends to HBM: every global access of the kernel is a bulk tensor copy.
+// Per unit an epilogue thread: tcgen05.ld of 2 x 16 columns -> gate arithmetic on token pairs in
+// packed bfloat16 with the reference's roundings -> (a, x) kept packed in 32 registers while the
+// 32-token map (P, H): h -> P h + H is accumulated -> the four token quarters of a channel quarter
+// meet at a 128-thread named barrier; the last one publishes the tile's map, resolves the incoming
+// state (decoupled look-back over earlier time tiles, normally one already inclusive record) and
+// publishes the inclusive state -> second named barrier -> replay from registers with the true
+// incoming state, join, 2-byte stores into the output tile.
+// All waits (mbarriers, look-back flags) are bounded; on expiry WsHeader::status is raised, the
+// affected values are taken as zero and the kernel runs to completion.
+#include <cuda.h>
+
+#include "rgk_common.cuh"
+#include "rgk_internal.h"
+#include "tc_common.cuh"
+
+namespace rgk {
+namespace {
+
+constexpr int kHW = 256;                 // head width = K
+constexpr int kUT = 128;                 // tokens per unit (MMA N)
+constexpr int kUC = 128;                 // channels per unit (MMA M)
+constexpr int kKB = 64;                  // K per ring stage
+constexpr int kKBlocks = kHW / kKB;      // 4
+constexpr int kRing = 3;
+constexpr int kCBytes = kUT * kKB * 2;         // 16 KiB: conv-output slice (operand B)
+constexpr int kWBytes = 2 * kUC * kKB * 2;     // 32 KiB: x-gate rows then a-gate rows (operand A)
+constexpr int kStage = kCBytes + kWBytes;
+constexpr int kEpi = 16;
+constexpr int kThreads = (kEpi + 2) * 32;
+constexpr int kSub = 32;                 // a warp's tile: 32 tokens x 32 channels
+constexpr int kSubBytes = kSub * kSub * 2;
+constexpr int kOffRing = 0;
+constexpr int kOffTiles = kRing * kStage;                      // per warp: conv tile, then y/out tile
+constexpr int kOffQmap = kOffTiles + kEpi * 2 * kSubBytes;     // float2 [2 parity][4 chq][4 tq][32]
+constexpr int kOffHin = kOffQmap + 2 * 4 * 4 * 32 * 8;         // float  [2 parity][4 chq][32]
+constexpr int kOffKnown = kOffHin + 2 * 4 * 32 * 4;              // int    [2 parity][4 chq]
+constexpr int kOffBar = kOffKnown + 2 * 4 * 4;
+constexpr int kNumBar = 2 * kRing + 4 + 2 * kEpi;
+constexpr int kOffTmem = kOffBar + kNumBar * 8;
+constexpr int kOffAbort = kOffTmem + 4;
+constexpr int kSmem = kOffAbort + 4 + 1024;
+static_assert(kSmem <= 232448, "exceeds the 227 KiB of shared memory a CTA may use");
+constexpr uint32_t kIdesc = tc_idesc_bf16(kUC, kUT);
+constexpr unsigned kLookbackSpins = 1u << 20;
+
+// Look-back record of one (unit, channel quarter): 32 channels.
+struct QuarterRecord {
+  float P[kSub];
+  float H[kSub];
+};
+
+__device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_u32(unsigned* p, unsigned v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ float ld_cg_f32(const float* p) {
+  float v;
+  asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void named_bar_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" :: "r"(id), "r"(threads) : "memory");
+}
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y, uint32_t src) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+               :: "l"(map), "r"(x), "r"(y), "r"(src) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t bmax2(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("max.NaN.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ float gelu_fast_f(float z) {
+  constexpr float k0 = -1.5957691216057308f * 1.4426950408889634f;
+  constexpr float k1 = k0 * 0.044715f;
+  const float w = z * fmaf(z * z, k1, k0);
+  return z * rcpf(ex2f(w) + 1.0f);
+}
+
+// Gate arithmetic of ONE channel for two consecutive tokens (torch/layers.py:338-353), every
+// tensor-level result rounded to bfloat16 where torch rounds it.
+//   zx, za   float32 accumulators of the two tokens;  bx2, ba2, m8sp2: the channel's biases and
+//   -8 softplus(a_param), each duplicated into both halves.
+// Returns packed a, x-gate and input multiplier, resets not yet applied.
+__device__ __forceinline__ void gate_tokens(float zx0, float zx1, float za0, float za1, uint32_t bx2,
+                                            uint32_t ba2, uint32_t m8sp2, uint32_t& a2,
+                                            uint32_t& gx2, uint32_t& mult2) {
+  constexpr float kNegLog2e = -1.4426950408889634f;
+  constexpr uint32_t kFloor = 0xc226c226u;     // -41.5: keeps the product of two denominators finite
+  const uint32_t zx2 = bmax2(badd2(pack_bf16x2(zx0, zx1), bx2), kFloor);
+  const uint32_t za2 = bmax2(badd2(pack_bf16x2(za0, za1), ba2), kFloor);
+  // sigmoid(z) = 1 / (1 + 2^(-z log2 e)); the two gates of a token share one reciprocal
+  const float dx0 = 1.0f + ex2f(bf16_lo(zx2) * kNegLog2e), dx1 = 1.0f + ex2f(bf16_hi(zx2) * kNegLog2e);
+  const float da0 = 1.0f + ex2f(bf16_lo(za2) * kNegLog2e), da1 = 1.0f + ex2f(bf16_hi(za2) * kNegLog2e);
+  const float r0 = rcpf(dx0 * da0), r1 = rcpf(dx1 * da1);
+  gx2 = pack_bf16x2(r0 * da0, r1 * da1);
+  const uint32_t ga2 = pack_bf16x2(r0 * dx0, r1 * dx1);
+  // log_a = (-8 gate_a) softplus(a_param): -8 is exact in bfloat16 and folded into the constant
+  const uint32_t la2 = bmul2(ga2, m8sp2);
+  const float e0 = ex2f(bf16_lo(la2) * -kNegLog2e), e1 = ex2f(bf16_hi(la2) * -kNegLog2e);
+  a2 = pack_bf16x2(e0, e1);
+  const uint32_t om2 = bsub2(0x3f803f80u, pack_bf16x2(e0 * e0, e1 * e1));   // 1 - exp(2 log_a)
+  mult2 = pack_bf16x2(sqrtf_approx(bf16_lo(om2)), sqrtf_approx(bf16_hi(om2)));
+}
+
+// 16 tokens of one channel: gates from the accumulators, (a, x) packed per token pair, and the
+// running map (P, H) of the thread's tokens.  `ct` points at the thread's column of the warp's conv
+// tile (row stride 32 elements); `rs` holds the reset bits of the 16 tokens.
+template <bool kResets>
+__device__ __forceinline__ void gates_16(const uint32_t (&zx)[16], const uint32_t (&za)[16],
+                                         const uint16_t* ct, uint32_t bx2, uint32_t ba2,
+                                         uint32_t m8sp2, uint32_t rs, uint32_t* a_out,
+                                         uint32_t* x_out, float& P, float& H) {
+#pragma unroll
+  for (int jp = 0; jp < 8; ++jp) {
+    const uint32_t c2 = (uint32_t)ct[(2 * jp) * kSub] | ((uint32_t)ct[(2 * jp + 1) * kSub] << 16);
+    uint32_t a2, gx2, mult2;
+    gate_tokens(__uint_as_float(zx[2 * jp]), __uint_as_float(zx[2 * jp + 1]),
+                __uint_as_float(za[2 * jp]), __uint_as_float(za[2 * jp + 1]), bx2, ba2, m8sp2, a2, gx2,
+                mult2);
+    if constexpr (kResets) {
+      // a token that starts a document: a = 0, multiplier = 1 (torch/layers.py:343-350, 166)
+      const uint32_t keep = (((rs >> (2 * jp)) & 1u) ? 0u : 0x0000ffffu) |
+                            (((rs >> (2 * jp + 1)) & 1u) ? 0u : 0xffff0000u);
+      a2 &= keep;
+      mult2 = (mult2 & keep) | (0x3f803f80u & ~keep);
+    }
+    const uint32_t x2 = bmul2(bmul2(c2, gx2), mult2);
+    a_out[jp] = a2;
+    x_out[jp] = x2;
+    const float a0 = bf16_lo(a2), a1 = bf16_hi(a2);
+    // the pair as one map, then composed: keeps the dependent chain at one step per pair
+    const float p2 = a0 * a1, h2 = fmaf(a1, bf16_lo(x2), bf16_hi(x2));
+    H = fmaf(p2, H, h2);
+    P *= p2;
+  }
+}
+
+template <int kJoin>   // 0: out = y, 1: out = y * gelu_tanh(yb), 2: out = y * yb
+__global__ void __launch_bounds__(kThreads, 1)
+rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_w,
+                  const __grid_constant__ CUtensorMap map_ct, const __grid_constant__ CUtensorMap map_yt,
+                  const __grid_constant__ CUtensorMap map_ot, const void* __restrict__ pos, int pos64,
+                  const __nv_bfloat16* __restrict__ bias_x, const __nv_bfloat16* __restrict__ bias_a,
+                  const __nv_bfloat16* __restrict__ m8sp, const float* __restrict__ h0, int B, int T_,
+                  int E, int groups, int n_units, float* __restrict__ h_last, WsHeader* hdr,
+                  unsigned* flags, QuarterRecord* agg, float* incl) {
+  extern __shared__ uint8_t smem_raw[];
+  // aligned by an offset into the shared array, so that the address space stays known to the
+  // compiler (shared-memory load/store instructions instead of generic ones)
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  const uint32_t s_base = smem_u32(smem);
+  const uint32_t bar0 = s_base + kOffBar;
+  auto bar_full = [&](int s) { return bar0 + 8u * s; };
+  auto bar_empty = [&](int s) { return bar0 + 8u * (kRing + s); };
+  auto bar_acc_full = [&](int s) { return bar0 + 8u * (2 * kRing + s); };
+  auto bar_acc_empty = [&](int s) { return bar0 + 8u * (2 * kRing + 2 + s); };
+  auto bar_ct = [&](int w) { return bar0 + 8u * (2 * kRing + 4 + w); };
+  auto bar_yt = [&](int w) { return bar0 + 8u * (2 * kRing + 4 + kEpi + w); };
+  volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(smem + kOffTmem);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(smem + kOffAbort);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_t = T_ / kUT;
+  const int per_tt = B * groups;                         // units per time tile
+  const int n_my = (n_units - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+
+  if (threadIdx.x == 0) {
+    *s_abort = 0;
+    for (int s = 0; s < kRing; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(bar_acc_full(s), 1); mbar_init(bar_acc_empty(s), kEpi); }
+    for (int w = 0; w < kEpi; ++w) { mbar_init(bar_ct(w), 1); mbar_init(bar_yt(w), 1); }
+    mbar_fence_init();
+  }
+  if (warp == kEpi + 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 :: "r"(s_base + kOffTmem), "r"(512) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *s_tmem;
+
+  if (warp == kEpi) {
+    // ------------------------------ TMA producer of the MMA operands ------------------------------
+    if (lane == 0) {
+      unsigned it = 0;
+      bool ok = true;
+      for (int t = 0; t < n_my && ok; ++t) {
+        const int u = blockIdx.x + t * gridDim.x;
+        const int tt = u / per_tt, rem = u - tt * per_tt;
+        const int b = rem / groups, grp = rem - b * groups;
+        const int row0 = b * T_ + tt * kUT;
+        for (int kb = 0; kb < kKBlocks; ++kb, ++it) {
+          const int s = it % kRing;
+          ok = mbar_wait_relaxed(bar_empty(s), ((it / kRing) & 1) ^ 1, s_abort);
+          if (!ok) break;
+          mbar_expect_tx(bar_full(s), kStage);
+          tma_load_2d(s_base + kOffRing + s * kStage, &map_c, (grp >> 1) * kHW + kb * kKB, row0,
+                      bar_full(s));
+          tma_load_2d(s_base + kOffRing + s * kStage + kCBytes, &map_w, kb * kKB, grp * 2 * kUC,
+                      bar_full(s));
+        }
+      }
+    }
+  } else if (warp == kEpi + 1) {
+    // ------------------------------ MMA issue -----------------------------------------------------
+    if (lane == 0) {
+      unsigned it = 0;
+      bool ok = true;
+      for (int t = 0; t < n_my && ok; ++t) {
+        const int as = t & 1;
+        ok = mbar_wait_relaxed(bar_acc_empty(as), ((t >> 1) & 1) ^ 1, s_abort);
+        if (!ok) break;
+        tc_fence_after();
+        for (int kb = 0; kb < kKBlocks; ++kb, ++it) {
+          const int s = it % kRing;
+          ok = mbar_wait_relaxed(bar_full(s), (it / kRing) & 1, s_abort);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t c0 = s_base + kOffRing + s * kStage, w0 = c0 + kCBytes;
+#pragma unroll
+          for (int ks = 0; ks < kKB / 16; ++ks) {
+            const uint32_t acc = (kb | ks) != 0 ? 1u : 0u;
+            const uint64_t bdesc = smem_desc_sw128(c0 + ks * 32);
+            tc_mma_bf16(tmem_base + as * 2 * kUT, smem_desc_sw128(w0 + ks * 32), bdesc, kIdesc, acc);
+            tc_mma_bf16(tmem_base + as * 2 * kUT + kUT, smem_desc_sw128(w0 + kUC * 128 + ks * 32), bdesc,
+                        kIdesc, acc);
+          }
+          tc_commit(bar_empty(s));
+        }
+        if (ok) tc_commit(bar_acc_full(as));
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ------------------------------------------------------
+    const int chq = warp & 3;                // channel quarter = TMEM lane quarter of this warp
+    const int tq = warp >> 2;                // token quarter: tokens 32 tq .. 32 tq + 31 of the unit
+    const int set_id = 1 + chq;              // named barrier of the four token quarters
+    uint8_t* tile_c = smem + kOffTiles + warp * 2 * kSubBytes;
+    uint8_t* tile_y = tile_c + kSubBytes;
+    const uint16_t* ct = reinterpret_cast<const uint16_t*>(tile_c) + lane;
+    uint16_t* yt = reinterpret_cast<uint16_t*>(tile_y) + lane;
+    const uint32_t tile_c_s = smem_u32(tile_c), tile_y_s = smem_u32(tile_y);
+    bool ok = true;
+
+    auto unit_xy = [&](int t, int& x, int& y) {
+      const int u = blockIdx.x + t * gridDim.x;
+      const int tt = u / per_tt, rem = u - tt * per_tt;
+      const int b = rem / groups, grp = rem - b * groups;
+      x = (grp >> 1) * kHW + (grp & 1) * kUC + chq * kSub;
+      y = b * T_ + tt * kUT + tq * kSub;
+    };
+    if (lane == 0 && n_my > 0) {
+      int x, y;
+      unit_xy(0, x, y);
+      mbar_expect_tx(bar_ct(warp), kSubBytes);
+      tma_load_2d(tile_c_s, &map_ct, x, y, bar_ct(warp));
+    }
+
+    for (int t = 0; t < n_my; ++t) {
+      const int as = t & 1, par = t & 1;
+      const int u = blockIdx.x + t * gridDim.x;
+      const int tt = u / per_tt, rem = u - tt * per_tt;
+      const int b = rem / groups, grp = rem - b * groups;
+      const int e0 = (grp >> 1) * kHW + (grp & 1) * kUC + chq * kSub;     // first channel of the warp
+      const int row0 = b * T_ + tt * kUT + tq * kSub;                     // first token of the warp
+      const int64_t rec = (int64_t)u * 4 + chq;
+      float2* s_qmap = reinterpret_cast<float2*>(smem + kOffQmap) + ((par * 4 + chq) * 4) * 32;
+      float* s_hin = reinterpret_cast<float*>(smem + kOffHin) + (par * 4 + chq) * 32;
+      volatile int* s_known = reinterpret_cast<volatile int*>(smem + kOffKnown) + (par * 4 + chq);
+
+      const uint32_t resets = __ballot_sync(0xffffffffu, pos_is_zero(pos, pos64, (int64_t)row0 + lane));
+      const uint32_t bxv = __ldg(reinterpret_cast<const uint16_t*>(bias_x) + e0 + lane);
+      const uint32_t bav = __ldg(reinterpret_cast<const uint16_t*>(bias_a) + e0 + lane);
+      const uint32_t spv = __ldg(reinterpret_cast<const uint16_t*>(m8sp) + e0 + lane);
+      const uint32_t bx2 = bxv | (bxv << 16), ba2 = bav | (bav << 16), m8sp2 = spv | (spv << 16);
+
+      // the last token quarter looks at its predecessor's record early: normally inclusive already
+      float hin_pref = 0.0f;
+      bool have_hin = tt == 0;
+      if (tq == 3) {
+        if (tt == 0) {
+          hin_pref = h0 != nullptr ? h0[(int64_t)b * E + e0 + lane] : 0.0f;
+        } else {
+          const int64_t rp = rec - (int64_t)per_tt * 4;
+          unsigned f = 0;
+          if (lane == 0) f = ld_acquire_u32(&flags[rp]);
+          f = __shfl_sync(0xffffffffu, f, 0);
+          if (f == 2u) {
+            __syncwarp();
+            hin_pref = ld_cg_f32(incl + rp * kSub + lane);
+            have_hin = true;
+          }
+        }
+      }
+
+      // ---- gates of the thread's 32 tokens, 16 at a time ------------------------------------------
+      if (ok) ok = mbar_wait(bar_ct(warp), t & 1, s_abort);
+      if (ok) ok = mbar_wait(bar_acc_full(as), (t >> 1) & 1, s_abort);
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(chq * 32) << 16) + as * 2 * kUT + tq * kSub;
+      uint32_t a_pk[16], x_pk[16];
+      float P = 1.0f, H = 0.0f;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t zx[16], za[16];
+        if (ok) {
+          tc_ld_32x16(t_row + half * 16, zx);
+          tc_ld_32x16(t_row + kUT + half * 16, za);
+          tc_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) { zx[i] = 0u; za[i] = 0u; }
+        }
+        if (half == 1) {
+          // the accumulator set has been read: it may be overwritten
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0 && ok) mbar_arrive(bar_acc_empty(as));
+        }
+        const uint32_t rs = (resets >> (half * 16)) & 0xffffu;
+        if (rs == 0u)
+          gates_16<false>(zx, za, ct + half * 16 * kSub, bx2, ba2, m8sp2, rs, a_pk + half * 8,
+                          x_pk + half * 8, P, H);
+        else
+          gates_16<true>(zx, za, ct + half * 16 * kSub, bx2, ba2, m8sp2, rs, a_pk + half * 8,
+                         x_pk + half * 8, P, H);
+        if (half == 0) {
+          // the previous unit's output tile must have been read by its store before the buffer is
+          // written again; then the other branch's tile of this unit is fetched into it
+          if (lane == 0) {
+            bulk_wait_read();
+            if constexpr (kJoin != 0) {
+              mbar_expect_tx(bar_yt(warp), kSubBytes);
+              tma_load_2d(tile_y_s, &map_yt, e0, row0, bar_yt(warp));
+            }
+          }
+        }
+      }
+      __threadfence_block();                 // the tile's loads are complete before it is refilled
+      __syncwarp();
+      if (lane == 0 && t + 1 < n_my) {       // the conv tile is free: fetch the next unit's
+        int x, y;
+        unit_xy(t + 1, x, y);
+        mbar_expect_tx(bar_ct(warp), kSubBytes);
+        tma_load_2d(tile_c_s, &map_ct, x, y, bar_ct(warp));
+      }
+
+      // The incoming state is normally known before the tile's own map is (the predecessor's
+      // inclusive record was there at the start of the unit): then the quarters need one barrier,
+      // to see each other's maps, and nothing waits for the record of this tile to be published.
+      if (tq == 3) {
+        if (have_hin) s_hin[lane] = hin_pref;
+        if (lane == 0) *s_known = have_hin ? 1 : 0;
+      }
+      s_qmap[tq * 32 + lane] = make_float2(P, H);
+      named_bar_sync(set_id, 128);
+      const bool known = *s_known != 0;
+
+      // ---- the last token quarter: the tile's map, the incoming state, the records ---------------
+      bool publish_late = false;
+      if (tq == 3) {
+        float Pt = 1.0f, Ht = 0.0f;
+#pragma unroll
+        for (int qq = 0; qq < 4; ++qq) {
+          const float2 m = s_qmap[qq * 32 + lane];
+          Ht = fmaf(m.x, Ht, m.y);
+          Pt *= m.x;
+        }
+        float hin = hin_pref;
+        if (!known) {
+          agg[rec].P[lane] = Pt;
+          agg[rec].H[lane] = Ht;
+          __syncwarp();
+          if (lane == 0) st_release_u32(&flags[rec], 1u);
+          if (ok) {
+            // decoupled look-back: lane l polls the flag of the l-th earlier time tile
+            float Pc = 1.0f, Hc = 0.0f;
+            int base = tt - 1;
+            bool done = false, timed_out = false;
+            while (!done) {
+              const int pred = base - lane;
+              const int64_t rp = rec - (int64_t)(tt - pred) * per_tt * 4;
+              unsigned f = 2u;
+              int L = 32;
+              unsigned spins = 0;
+              while (true) {
+                if (pred >= 0) f = ld_acquire_u32(&flags[rp]);
+                const unsigned im = __ballot_sync(0xffffffffu, f == 2u);
+                L = im ? (__ffs(im) - 1) : 32;
+                const unsigned need = (L >= 31) ? 0xffffffffu : ((2u << L) - 1u);
+                if ((__ballot_sync(0xffffffffu, f == 0u) & need) == 0u) break;
+                if (++spins > kLookbackSpins) { timed_out = true; break; }
+                __nanosleep(32);
+              }
+              if (timed_out) break;
+              __syncwarp();
+              const int n_agg = L < 32 ? L : 32;
+              // records are fetched eight at a time, all loads before the first use
+              for (int j0 = 0; j0 < n_agg; j0 += 8) {
+                float pj[8], hj[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  const int j = min(j0 + i, n_agg - 1);
+                  const int64_t r2 = rec - (int64_t)(tt - (base - j)) * per_tt * 4;
+                  pj[i] = ld_cg_f32(agg[r2].P + lane);
+                  hj[i] = ld_cg_f32(agg[r2].H + lane);
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  if (j0 + i < n_agg) {
+                    Hc = fmaf(Pc, hj[i], Hc);
+                    Pc *= pj[i];
+                  }
+                }
+              }
+              if (L < 32) {
+                const int64_t r2 = rec - (int64_t)(tt - (base - L)) * per_tt * 4;
+                hin = fmaf(Pc, ld_cg_f32(incl + r2 * kSub + lane), Hc);
+                done = true;
+              } else {
+                base -= 32;
+              }
+            }
+            if (timed_out) {
+              if (lane == 0) atomicExch(&hdr->status, kStatusTimeout);
+              hin = 0.0f;
+            }
+          } else {
+            hin = 0.0f;
+          }
+          s_hin[lane] = hin;
+        }
+        const float h_end = fmaf(Pt, hin, Ht);
+        incl[rec * kSub + lane] = h_end;
+        if (h_last != nullptr && tt == tiles_t - 1) h_last[(int64_t)b * E + e0 + lane] = h_end;
+        if (!known) {
+          __syncwarp();
+          if (lane == 0) st_release_u32(&flags[rec], 2u);
+        } else {
+          // the release (which waits for the store above) is left to the end of the unit: its
+          // consumer is a full round of units away
+          publish_late = true;
+        }
+      }
+      if (!known) named_bar_sync(set_id, 128);
+
+      // ---- replay with the true incoming state, join, output tile ---------------------------------
+      float h = s_hin[lane];
+      for (int qq = 0; qq < tq; ++qq) {
+        const float2 m = s_qmap[qq * 32 + lane];
+        h = fmaf(m.x, h, m.y);
+      }
+      if constexpr (kJoin != 0) {
+        if (ok) ok = mbar_wait(bar_yt(warp), t & 1, s_abort);
+      }
+#pragma unroll
+      for (int jp = 0; jp < 16; ++jp) {
+        const uint32_t a2 = a_pk[jp], x2 = x_pk[jp];
+        h = fmaf(bf16_lo(a2), h, bf16_lo(x2));
+        const float y0 = h;
+        h = fmaf(bf16_hi(a2), h, bf16_hi(x2));
+        uint32_t y2 = pack_bf16x2(y0, h);
+        if constexpr (kJoin == 1) {
+          const float z0 = __uint_as_float((uint32_t)yt[(2 * jp) * kSub] << 16);
+          const float z1 = __uint_as_float((uint32_t)yt[(2 * jp + 1) * kSub] << 16);
+          y2 = bmul2(y2, pack_bf16x2(gelu_fast_f(z0), gelu_fast_f(z1)));
+        } else if constexpr (kJoin == 2) {
+          y2 = bmul2(y2, (uint32_t)yt[(2 * jp) * kSub] | ((uint32_t)yt[(2 * jp + 1) * kSub] << 16));
+        }
+        yt[(2 * jp) * kSub] = (uint16_t)(y2 & 0xffffu);
+        yt[(2 * jp + 1) * kSub] = (uint16_t)(y2 >> 16);
+      }
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_2d(&map_ot, e0, row0, tile_y_s);
+        bulk_commit();
+        if (publish_late) st_release_u32(&flags[rec], 2u);
+      }
+    }
+    if (lane == 0) bulk_wait_all();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *s_abort) atomicExch(&hdr->status, kStatusTimeout);
+  if (warp == kEpi + 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"(512)
+                 : "memory");
+  }
+}
+
+// -8 softplus(a_param), rounded as the reference rounds its factors, one value per channel.
+__global__ void m8sp_chan_kernel(const __nv_bfloat16* __restrict__ a_param, int E,
+                                 __nv_bfloat16* __restrict__ m8sp) {
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e < E) {
+    const float s = round_bf16(softplus_(__bfloat162float(a_param[e])));
+    m8sp[e] = __float2bfloat16_rn(-8.0f * s);
+  }
+}
+
+// Tensor map of a row-major bfloat16 matrix [rows, cols] with boxes of box_rows x box_cols.
+bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
+              uint32_t box_cols, bool swizzle128) {
+  EncodeTiledFn fn = tensor_map_encoder();
+  if (fn == nullptr) return false;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols * 2};
+  const cuuint32_t box[2] = {box_cols, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+            estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+            swizzle128 ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+struct ChanLayout {
+  int64_t n_units, n_rec;
+  size_t flags_off, m8sp_off, agg_off, incl_off, total;
+};
+
+ChanLayout chan_layout(int64_t B, int64_t T, int64_t E) {
+  ChanLayout L;
+  const int64_t groups = E / kUC;
+  L.n_units = (T / kUT) * B * groups;
+  L.n_rec = L.n_units * 4;
+  auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
+  L.flags_off = sizeof(WsHeader);
+  L.m8sp_off = up(L.flags_off + (size_t)L.n_rec * sizeof(unsigned));
+  L.agg_off = up(L.m8sp_off + (size_t)E * 2);
+  L.incl_off = up(L.agg_off + (size_t)L.n_rec * sizeof(QuarterRecord));
+  L.total = up(L.incl_off + (size_t)L.n_rec * kSub * sizeof(float));
+  return L;
+}
+
+}  // namespace
+
+bool rglru_chan_supported(int dtype, int bw, int64_t B, int64_t T) {
+  return dtype == 1 && bw == kHW && B >= 1 && T >= kUT && T % kUT == 0 &&
+         B * T < ((int64_t)1 << 31);
+}
+
+size_t rglru_chan_workspace_bytes(int64_t B, int64_t T, int64_t E) {
+  if (T < kUT || T % kUT != 0) return 0;
+  return chan_layout(B, T, E).total;
+}
+
+cudaError_t launch_rglru_chan(const void* c, const void* pos, int pos64, const void* a_param,
+                              const void* bx, const void* ba, const void* packed_w, const float* h0,
+                              const void* yb, int y_activated, int64_t B, int64_t T, int H,
+                              void* out, float* h_last, void* ws, cudaStream_t s) {
+  using T_ = __nv_bfloat16;
+  const int E = H * kHW;
+  const ChanLayout L = chan_layout(B, T, E);
+  char* base = static_cast<char*>(ws);
+  // flags start at zero (the status word before them belongs to the caller)
+  cudaError_t err = cudaMemsetAsync(base + sizeof(int), 0, L.m8sp_off - sizeof(int), s);
+  if (err != cudaSuccess) return err;
+  T_* m8sp = reinterpret_cast<T_*>(base + L.m8sp_off);
+  m8sp_chan_kernel<<<(E + 255) / 256, 256, 0, s>>>((const T_*)a_param, E, m8sp);
+  if ((err = cudaGetLastError()) != cudaSuccess) return err;
+
+  CUtensorMap map_c, map_w, map_ct, map_yt, map_ot;
+  const uint64_t rows = (uint64_t)(B * T);
+  if (!make_map(&map_c, c, rows, (uint64_t)E, kUT, kKB, true) ||
+      !make_map(&map_w, packed_w, (uint64_t)H * 4 * kUC, kHW, 2 * kUC, kKB, true) ||
+      !make_map(&map_ct, c, rows, (uint64_t)E, kSub, kSub, false) ||
+      !make_map(&map_ot, out, rows, (uint64_t)E, kSub, kSub, false) ||
+      !make_map(&map_yt, yb != nullptr ? yb : out, rows, (uint64_t)E, kSub, kSub, false))
+    return cudaErrorInvalidValue;
+  static int num_sms = 0;
+  if (num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaFuncSetAttribute(rglru_chan_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+    cudaFuncSetAttribute(rglru_chan_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+    cudaFuncSetAttribute(rglru_chan_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+  }
+  const int groups = 2 * H;
+  const int n_units = (int)L.n_units;
+  const int grid = n_units < num_sms ? n_units : num_sms;   // all CTAs resident: look-back may spin
+#define RGK_CHAN(J)                                                                              \
+  rglru_chan_kernel<J><<<grid, kThreads, kSmem, s>>>(                                            \
+      map_c, map_w, map_ct, map_yt, map_ot, pos, pos64, (const T_*)bx, (const T_*)ba, m8sp, h0,  \
+      (int)B, (int)T, E, groups, n_units, h_last, reinterpret_cast<WsHeader*>(base),             \
+      reinterpret_cast<unsigned*>(base + L.flags_off),                                           \
+      reinterpret_cast<QuarterRecord*>(base + L.agg_off),                                        \
+      reinterpret_cast<float*>(base + L.incl_off))
+  const int join = yb == nullptr ? 0 : (y_activated ? 2 : 1);
+  if (join == 0) RGK_CHAN(0); else if (join == 1) RGK_CHAN(1); else RGK_CHAN(2);
+#undef RGK_CHAN
+  return cudaGetLastError();
+}
+
+}  // namespace rgk

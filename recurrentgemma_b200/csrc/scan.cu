@@ -111,8 +111,9 @@ scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
   constexpr int kRowBytes = kChan * (int)sizeof(T);
 
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) &
-                                             ~static_cast<uintptr_t>(127));
+  // aligned by an offset into the shared array, so that the address space stays known to the
+  // compiler (shared-memory load/store instructions instead of generic ones)
+  uint8_t* smem = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);
   float2 (*s_sub)[kChan] = reinterpret_cast<float2 (*)[kChan]>(smem + Sm::kOffSub);
   float2* s_tile = reinterpret_cast<float2*>(smem + Sm::kOffTile);
   float* s_hin = reinterpret_cast<float*>(smem + Sm::kOffHin);

@@ -20,6 +20,21 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   return false;
 }
 
+// The same for a single-thread role whose waits are long (a producer waiting for a free stage, an
+// MMA issuer waiting for operands): the thread sleeps between attempts, so that its polling does not
+// take issue slots and shared-memory queue entries from the warps that do the arithmetic.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity,
+                                                  volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  for (unsigned i = 0; i < kWaitLimit; ++i) {
+    __nanosleep(200);
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
+
 __device__ __forceinline__ void tc_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 }

@@ -396,3 +396,27 @@ def test_host_pipeline_matches_device_call(rg):
   assert_close(out_h, o_ref, 1e-6, "out")
   assert_close(h_state, cache.rg_lru_state, 1e-6, "state")
   assert torch.equal(c_state, cache.conv1d_state)
+
+
+def test_gate_kernel_repeatable_at_full_size(rg):
+  """The tensor-core gate kernel hands each conv-output slice back to the copy engine as soon as
+  its epilogue warps have read their values from it; the reads must be complete by then.  Repeated
+  runs of the two-kernel route on the full-size workload agree with each other (a slice refilled
+  too early shows up as a handful of 16-byte pieces with errors of tens of percent)."""
+  from recurrentgemma_b200 import _lib
+  b, t, e, h = 8, 4096, 2560, 10
+  case = C.Case(f"fused_{b}_{t}_{e}", "rglru", "bfloat16", b, t, e, h, pos="multi")
+  p = C.make_params(case)
+  inp = C.make_inputs(case)
+  dt = torch.bfloat16
+  m = rg.RGLRU(e, h, device=DEV, dtype=dt)
+  m.load_state_dict({k[len("rg_lru."):]: v for k, v in p.items() if k.startswith("rg_lru.")})
+  x, pos = inp["x"].to(DEV), inp["segment_pos"].to(DEV)
+  for impl in (_lib.GATES_TCGEN05, _lib.GATES_FUSED):
+    m.gates_impl = impl
+    ys = []
+    for _ in range(6):
+      y, _h = m(x, pos)
+      ys.append(y.clone())
+    for y in ys[1:]:
+      assert_close(y, ys[0], 2e-3, f"run-to-run, gates_impl {impl}")
