@@ -71,72 +71,6 @@ struct QuarterRecord {
   float H[kSub];
 };
 
-__device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
-  unsigned v;
-  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_release_u32(unsigned* p, unsigned v) {
-  asm volatile("st.release.gpu.global.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ float ld_cg_f32(const float* p) {
-  float v;
-  asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void named_bar_sync(int id, int threads) {
-  asm volatile("bar.sync %0, %1;" :: "r"(id), "r"(threads) : "memory");
-}
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y, uint32_t src) {
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
-               :: "l"(map), "r"(x), "r"(y), "r"(src) : "memory");
-}
-__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_read() {
-  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-}
-__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-__device__ __forceinline__ void fence_proxy_async() {
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-__device__ __forceinline__ uint32_t bmax2(uint32_t a, uint32_t b) {
-  uint32_t r;
-  asm("max.NaN.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
-  return r;
-}
-__device__ __forceinline__ float gelu_fast_f(float z) {
-  constexpr float k0 = -1.5957691216057308f * 1.4426950408889634f;
-  constexpr float k1 = k0 * 0.044715f;
-  const float w = z * fmaf(z * z, k1, k0);
-  return z * rcpf(ex2f(w) + 1.0f);
-}
-
-// Gate arithmetic of ONE channel for two consecutive tokens (torch/layers.py:338-353), every
-// tensor-level result rounded to bfloat16 where torch rounds it.
-//   zx, za   float32 accumulators of the two tokens;  bx2, ba2, m8sp2: the channel's biases and
-//   -8 softplus(a_param), each duplicated into both halves.
-// Returns packed a, x-gate and input multiplier, resets not yet applied.
-__device__ __forceinline__ void gate_tokens(float zx0, float zx1, float za0, float za1, uint32_t bx2,
-                                            uint32_t ba2, uint32_t m8sp2, uint32_t& a2,
-                                            uint32_t& gx2, uint32_t& mult2) {
-  constexpr float kNegLog2e = -1.4426950408889634f;
-  constexpr uint32_t kFloor = 0xc226c226u;     // -41.5: keeps the product of two denominators finite
-  const uint32_t zx2 = bmax2(badd2(pack_bf16x2(zx0, zx1), bx2), kFloor);
-  const uint32_t za2 = bmax2(badd2(pack_bf16x2(za0, za1), ba2), kFloor);
-  // sigmoid(z) = 1 / (1 + 2^(-z log2 e)); the two gates of a token share one reciprocal
-  const float dx0 = 1.0f + ex2f(bf16_lo(zx2) * kNegLog2e), dx1 = 1.0f + ex2f(bf16_hi(zx2) * kNegLog2e);
-  const float da0 = 1.0f + ex2f(bf16_lo(za2) * kNegLog2e), da1 = 1.0f + ex2f(bf16_hi(za2) * kNegLog2e);
-  const float r0 = rcpf(dx0 * da0), r1 = rcpf(dx1 * da1);
-  gx2 = pack_bf16x2(r0 * da0, r1 * da1);
-  const uint32_t ga2 = pack_bf16x2(r0 * dx0, r1 * dx1);
-  // log_a = (-8 gate_a) softplus(a_param): -8 is exact in bfloat16 and folded into the constant
-  const uint32_t la2 = bmul2(ga2, m8sp2);
-  const float e0 = ex2f(bf16_lo(la2) * -kNegLog2e), e1 = ex2f(bf16_hi(la2) * -kNegLog2e);
-  a2 = pack_bf16x2(e0, e1);
-  const uint32_t om2 = bsub2(0x3f803f80u, pack_bf16x2(e0 * e0, e1 * e1));   // 1 - exp(2 log_a)
-  mult2 = pack_bf16x2(sqrtf_approx(bf16_lo(om2)), sqrtf_approx(bf16_hi(om2)));
-}
-
 // 16 tokens of one channel: gates from the accumulators, (a, x) packed per token pair, and the
 // running map (P, H) of the thread's tokens.  `ct` points at the thread's column of the warp's conv
 // tile (row stride 32 elements); `rs` holds the reset bits of the 16 tokens.

@@ -162,5 +162,162 @@ __device__ __forceinline__ void gate_pair(float zx0, float zx1, float za0, float
   xn2 = bmul2(bmul2(c2, gx2), mult2);
 }
 
+// ---- helpers shared by the fused RG-LRU kernels ------------------------------------------------
+
+__device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_u32(unsigned* p, unsigned v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ float ld_cg_f32(const float* p) {
+  float v;
+  asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void named_bar_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" :: "r"(id), "r"(threads) : "memory");
+}
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y, uint32_t src) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+               :: "l"(map), "r"(x), "r"(y), "r"(src) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t bmax2(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("max.NaN.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ float gelu_fast_f(float z) {
+  constexpr float k0 = -1.5957691216057308f * 1.4426950408889634f;
+  constexpr float k1 = k0 * 0.044715f;
+  const float w = z * fmaf(z * z, k1, k0);
+  return z * rcpf(ex2f(w) + 1.0f);
+}
+
+// Gate arithmetic of ONE channel for two consecutive tokens (torch/layers.py:338-353), every
+// tensor-level result rounded to bfloat16 where torch rounds it.
+//   zx, za   float32 accumulators of the two tokens;  bx2, ba2, m8sp2: the channel's biases and
+//   -8 softplus(a_param), each duplicated into both halves.
+// Returns packed a, x-gate and input multiplier, resets not yet applied.
+__device__ __forceinline__ void gate_tokens(float zx0, float zx1, float za0, float za1, uint32_t bx2,
+                                            uint32_t ba2, uint32_t m8sp2, uint32_t& a2,
+                                            uint32_t& gx2, uint32_t& mult2) {
+  constexpr float kNegLog2e = -1.4426950408889634f;
+  constexpr uint32_t kFloor = 0xc226c226u;     // -41.5: keeps the product of two denominators finite
+  const uint32_t zx2 = bmax2(badd2(pack_bf16x2(zx0, zx1), bx2), kFloor);
+  const uint32_t za2 = bmax2(badd2(pack_bf16x2(za0, za1), ba2), kFloor);
+  // sigmoid(z) = 1 / (1 + 2^(-z log2 e)); the two gates of a token share one reciprocal
+  const float dx0 = 1.0f + ex2f(bf16_lo(zx2) * kNegLog2e), dx1 = 1.0f + ex2f(bf16_hi(zx2) * kNegLog2e);
+  const float da0 = 1.0f + ex2f(bf16_lo(za2) * kNegLog2e), da1 = 1.0f + ex2f(bf16_hi(za2) * kNegLog2e);
+  const float r0 = rcpf(dx0 * da0), r1 = rcpf(dx1 * da1);
+  gx2 = pack_bf16x2(r0 * da0, r1 * da1);
+  const uint32_t ga2 = pack_bf16x2(r0 * dx0, r1 * dx1);
+  // log_a = (-8 gate_a) softplus(a_param): -8 is exact in bfloat16 and folded into the constant
+  const uint32_t la2 = bmul2(ga2, m8sp2);
+  const float e0 = ex2f(bf16_lo(la2) * -kNegLog2e), e1 = ex2f(bf16_hi(la2) * -kNegLog2e);
+  a2 = pack_bf16x2(e0, e1);
+  const uint32_t om2 = bsub2(0x3f803f80u, pack_bf16x2(e0 * e0, e1 * e1));   // 1 - exp(2 log_a)
+  mult2 = pack_bf16x2(sqrtf_approx(bf16_lo(om2)), sqrtf_approx(bf16_hi(om2)));
+}
+
+// gelu_tanh of 16 values in place, stage by stage (see gelu_fast_f).
+__device__ __forceinline__ void gelu_fast_x16(float (&z)[16]) {
+  constexpr float k0 = -1.5957691216057308f * 1.4426950408889634f;
+  constexpr float k1 = k0 * 0.044715f;
+  float w[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) w[i] = z[i] * z[i];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) w[i] = fmaf(w[i], k1, k0);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) w[i] *= z[i];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) w[i] = ex2f(w[i]);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) w[i] += 1.0f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) w[i] = rcpf(w[i]);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) z[i] *= w[i];
+}
+
+// The same arithmetic for 16 consecutive tokens of one channel (8 token pairs), written stage by
+// stage over all pairs: every instruction is followed by seven independent ones, so a warp that
+// runs alone on its scheduler still fills the pipelines.
+__device__ __forceinline__ void gate_tokens_x8(const uint32_t (&zx)[16], const uint32_t (&za)[16],
+                                               uint32_t bx2, uint32_t ba2, uint32_t m8sp2,
+                                               uint32_t (&a2)[8], uint32_t (&gx2)[8],
+                                               uint32_t (&mult2)[8]) {
+  constexpr float kNegLog2e = -1.4426950408889634f;
+  constexpr float kLog2e = 1.4426950408889634f;
+  constexpr uint32_t kFloor = 0xc226c226u;     // -41.5: keeps the product of two denominators finite
+  uint32_t zx2[8], za2[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    zx2[j] = pack_bf16x2(__uint_as_float(zx[2 * j]), __uint_as_float(zx[2 * j + 1]));
+    za2[j] = pack_bf16x2(__uint_as_float(za[2 * j]), __uint_as_float(za[2 * j + 1]));
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { zx2[j] = badd2(zx2[j], bx2); za2[j] = badd2(za2[j], ba2); }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { zx2[j] = bmax2(zx2[j], kFloor); za2[j] = bmax2(za2[j], kFloor); }
+  float dx[16], da[16];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    dx[2 * j] = bf16_lo(zx2[j]) * kNegLog2e;
+    dx[2 * j + 1] = bf16_hi(zx2[j]) * kNegLog2e;
+    da[2 * j] = bf16_lo(za2[j]) * kNegLog2e;
+    da[2 * j + 1] = bf16_hi(za2[j]) * kNegLog2e;
+  }
+#pragma unroll
+  for (int i = 0; i < 16; ++i) { dx[i] = ex2f(dx[i]); da[i] = ex2f(da[i]); }
+#pragma unroll
+  for (int i = 0; i < 16; ++i) { dx[i] += 1.0f; da[i] += 1.0f; }
+  float r[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) r[i] = dx[i] * da[i];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) r[i] = rcpf(r[i]);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) { da[i] *= r[i]; dx[i] *= r[i]; }   // da: x-gate, dx: a-gate
+  uint32_t la2[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    gx2[j] = pack_bf16x2(da[2 * j], da[2 * j + 1]);
+    la2[j] = pack_bf16x2(dx[2 * j], dx[2 * j + 1]);
+  }
+  // log_a = (-8 gate_a) softplus(a_param): -8 is exact in bfloat16 and folded into the constant
+#pragma unroll
+  for (int j = 0; j < 8; ++j) la2[j] = bmul2(la2[j], m8sp2);
+  float e[16];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    e[2 * j] = bf16_lo(la2[j]) * kLog2e;
+    e[2 * j + 1] = bf16_hi(la2[j]) * kLog2e;
+  }
+#pragma unroll
+  for (int i = 0; i < 16; ++i) e[i] = ex2f(e[i]);
+  uint32_t om2[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    a2[j] = pack_bf16x2(e[2 * j], e[2 * j + 1]);
+    om2[j] = pack_bf16x2(e[2 * j] * e[2 * j], e[2 * j + 1] * e[2 * j + 1]);   // exp(2 log_a)
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) om2[j] = bsub2(0x3f803f80u, om2[j]);             // 1 - a^2
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+    mult2[j] = pack_bf16x2(sqrtf_approx(bf16_lo(om2[j])), sqrtf_approx(bf16_hi(om2[j])));
+}
 
 }  // namespace rgk

@@ -328,13 +328,16 @@ def test_block_fused_matches_composed(rg):
 
 
 @pytest.mark.parametrize("shape", [(1, 128, 256, 1), (2, 384, 512, 2), (1, 8192, 256, 1),
-                                   (3, 1024, 2560, 10), (8, 4096, 2560, 10)],
+                                   (3, 1024, 2560, 10), (37, 384, 512, 2), (40, 256, 512, 2),
+                                   (8, 4096, 2560, 10)],
                          ids=lambda s: "x".join(map(str, s)))
 def test_fused_rglru_kernel(rg, oracle, shape):
   """Gates + gate arithmetic + scan (+ join) in one tensor-core kernel against the two-kernel
   tensor-core route (same roundings; only the association of the carries differs) and, on the
   smaller shapes, against the oracle.  Covers one unit per sequence, carries inside one round of
-  CTAs (B = 1, long T), and carries across rounds."""
+  CTAs (B = 1, long T), carries across rounds, and the one-pass kernel that takes over when there are
+  at least as many (sequence, half head) pairs as SMs (B = 37 and 40 with two heads: the state
+  comes from the same CTA's previous round, or from another CTA's)."""
   from recurrentgemma_b200 import _lib
   b, t, e, h = shape
   case = C.Case(f"fused_{b}_{t}_{e}", "rglru", "bfloat16", b, t, e, h, pos="multi")
@@ -363,7 +366,7 @@ def test_fused_rglru_kernel(rg, oracle, shape):
   assert_close(o_f, o_u, 5e-3, "fused vs two-kernel path out")
   assert_close(c_f.rg_lru_state, c_u.rg_lru_state, 5e-3, "fused vs two-kernel path state")
   assert float((y_f != y_u).float().mean()) < 0.02
-  if b * t * e <= 2 * 384 * 512 * 8:
+  if b * t * e <= 8 << 20:
     y_r, h_r = oracle.rglru(inp["x"], inp["segment_pos"], p["rg_lru.a_param"],
                             p["rg_lru.input_gate.w"], p["rg_lru.input_gate.b"],
                             p["rg_lru.a_gate.w"], p["rg_lru.a_gate.b"], h0.cpu())
