@@ -65,6 +65,18 @@ static_assert(kSmem <= 232448, "exceeds the 227 KiB of shared memory a CTA may u
 constexpr uint32_t kIdesc = tc_idesc_bf16(kUC, kUT);
 constexpr unsigned kLookbackSpins = 1u << 20;
 
+// An inclusive state travels as one 64-bit word per channel {h, token}: one store, one load, and a
+// reader that finds the token has the value, without a flag or a fence.
+constexpr unsigned long long kToken = 1ull << 32;
+__device__ __forceinline__ unsigned long long ld_relaxed_u64(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_relaxed_u64(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" :: "l"(p), "l"(v) : "memory");
+}
+
 // Look-back record of one (unit, channel quarter): 32 channels.
 struct QuarterRecord {
   float P[kSub];
@@ -112,7 +124,7 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
                   const __nv_bfloat16* __restrict__ bias_x, const __nv_bfloat16* __restrict__ bias_a,
                   const __nv_bfloat16* __restrict__ m8sp, const float* __restrict__ h0, int B, int T_,
                   int E, int groups, int n_units, float* __restrict__ h_last, WsHeader* hdr,
-                  unsigned* flags, QuarterRecord* agg, float* incl) {
+                  unsigned* flags, QuarterRecord* agg, unsigned long long* incl) {
   extern __shared__ uint8_t smem_raw[];
   // aligned by an offset into the shared array, so that the address space stays known to the
   // compiler (shared-memory load/store instructions instead of generic ones)
@@ -245,23 +257,14 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
       const uint32_t spv = __ldg(reinterpret_cast<const uint16_t*>(m8sp) + e0 + lane);
       const uint32_t bx2 = bxv | (bxv << 16), ba2 = bav | (bav << 16), m8sp2 = spv | (spv << 16);
 
-      // the last token quarter looks at its predecessor's record early: normally inclusive already
+      // the last token quarter asks for its predecessor's inclusive state now (normally published
+      // most of a round ago) and looks at the answer after the gate arithmetic
       float hin_pref = 0.0f;
       bool have_hin = tt == 0;
+      unsigned long long pre = 0ull;
       if (tq == 3) {
-        if (tt == 0) {
-          hin_pref = h0 != nullptr ? h0[(int64_t)b * E + e0 + lane] : 0.0f;
-        } else {
-          const int64_t rp = rec - (int64_t)per_tt * 4;
-          unsigned f = 0;
-          if (lane == 0) f = ld_acquire_u32(&flags[rp]);
-          f = __shfl_sync(0xffffffffu, f, 0);
-          if (f == 2u) {
-            __syncwarp();
-            hin_pref = ld_cg_f32(incl + rp * kSub + lane);
-            have_hin = true;
-          }
-        }
+        if (tt == 0) hin_pref = h0 != nullptr ? h0[(int64_t)b * E + e0 + lane] : 0.0f;
+        else pre = ld_relaxed_u64(incl + (rec - (int64_t)per_tt * 4) * kSub + lane);
       }
 
       // ---- gates of the thread's 32 tokens, 16 at a time ------------------------------------------
@@ -320,6 +323,10 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
       // inclusive record was there at the start of the unit): then the quarters need one barrier,
       // to see each other's maps, and nothing waits for the record of this tile to be published.
       if (tq == 3) {
+        if (tt > 0 && __all_sync(0xffffffffu, (pre >> 32) == 1ull)) {
+          hin_pref = __uint_as_float((uint32_t)pre);
+          have_hin = true;
+        }
         if (have_hin) s_hin[lane] = hin_pref;
         if (lane == 0) *s_known = have_hin ? 1 : 0;
       }
@@ -386,7 +393,7 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
               }
               if (L < 32) {
                 const int64_t r2 = rec - (int64_t)(tt - (base - L)) * per_tt * 4;
-                hin = fmaf(Pc, ld_cg_f32(incl + r2 * kSub + lane), Hc);
+                hin = fmaf(Pc, __uint_as_float((uint32_t)ld_relaxed_u64(incl + r2 * kSub + lane)), Hc);
                 done = true;
               } else {
                 base -= 32;
@@ -402,7 +409,7 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
           s_hin[lane] = hin;
         }
         const float h_end = fmaf(Pt, hin, Ht);
-        incl[rec * kSub + lane] = h_end;
+        st_relaxed_u64(incl + rec * kSub + lane, kToken | (unsigned long long)__float_as_uint(h_end));
         if (h_last != nullptr && tt == tiles_t - 1) h_last[(int64_t)b * E + e0 + lane] = h_end;
         if (!known) {
           __syncwarp();
@@ -500,10 +507,10 @@ ChanLayout chan_layout(int64_t B, int64_t T, int64_t E) {
   L.n_rec = L.n_units * 4;
   auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
   L.flags_off = sizeof(WsHeader);
-  L.m8sp_off = up(L.flags_off + (size_t)L.n_rec * sizeof(unsigned));
+  L.incl_off = up(L.flags_off + (size_t)L.n_rec * sizeof(unsigned));
+  L.m8sp_off = up(L.incl_off + (size_t)L.n_rec * kSub * sizeof(unsigned long long));
   L.agg_off = up(L.m8sp_off + (size_t)E * 2);
-  L.incl_off = up(L.agg_off + (size_t)L.n_rec * sizeof(QuarterRecord));
-  L.total = up(L.incl_off + (size_t)L.n_rec * kSub * sizeof(float));
+  L.total = up(L.agg_off + (size_t)L.n_rec * sizeof(QuarterRecord));
   return L;
 }
 
@@ -527,7 +534,7 @@ cudaError_t launch_rglru_chan(const void* c, const void* pos, int pos64, const v
   const int E = H * kHW;
   const ChanLayout L = chan_layout(B, T, E);
   char* base = static_cast<char*>(ws);
-  // flags start at zero (the status word before them belongs to the caller)
+  // flags and state words start at zero (the status word before them belongs to the caller)
   cudaError_t err = cudaMemsetAsync(base + sizeof(int), 0, L.m8sp_off - sizeof(int), s);
   if (err != cudaSuccess) return err;
   T_* m8sp = reinterpret_cast<T_*>(base + L.m8sp_off);
@@ -560,7 +567,7 @@ cudaError_t launch_rglru_chan(const void* c, const void* pos, int pos64, const v
       (int)B, (int)T, E, groups, n_units, h_last, reinterpret_cast<WsHeader*>(base),             \
       reinterpret_cast<unsigned*>(base + L.flags_off),                                           \
       reinterpret_cast<QuarterRecord*>(base + L.agg_off),                                        \
-      reinterpret_cast<float*>(base + L.incl_off))
+      reinterpret_cast<unsigned long long*>(base + L.incl_off))
   const int join = yb == nullptr ? 0 : (y_activated ? 2 : 1);
   if (join == 0) RGK_CHAN(0); else if (join == 1) RGK_CHAN(1); else RGK_CHAN(2);
 #undef RGK_CHAN
