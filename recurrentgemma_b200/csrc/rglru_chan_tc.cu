@@ -239,6 +239,14 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
       tma_load_2d(tile_c_s, &map_ct, x, y, bar_ct(warp));
     }
 
+    // whether this lane's token of the next unit starts a document: asked for a unit ahead
+    bool reset_next = false;
+    if (n_my > 0) {
+      int x, y;
+      unit_xy(0, x, y);
+      reset_next = pos_is_zero(pos, pos64, (int64_t)y + lane);
+    }
+
     for (int t = 0; t < n_my; ++t) {
       const int as = t & 1, par = t & 1;
       const int u = blockIdx.x + t * gridDim.x;
@@ -251,7 +259,7 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
       float* s_hin = reinterpret_cast<float*>(smem + kOffHin) + (par * 4 + chq) * 32;
       volatile int* s_known = reinterpret_cast<volatile int*>(smem + kOffKnown) + (par * 4 + chq);
 
-      const uint32_t resets = __ballot_sync(0xffffffffu, pos_is_zero(pos, pos64, (int64_t)row0 + lane));
+      const uint32_t resets = __ballot_sync(0xffffffffu, reset_next);
       const uint32_t bxv = __ldg(reinterpret_cast<const uint16_t*>(bias_x) + e0 + lane);
       const uint32_t bav = __ldg(reinterpret_cast<const uint16_t*>(bias_a) + e0 + lane);
       const uint32_t spv = __ldg(reinterpret_cast<const uint16_t*>(m8sp) + e0 + lane);
@@ -312,6 +320,11 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
       }
       __threadfence_block();                 // the tile's loads are complete before it is refilled
       __syncwarp();
+      if (t + 1 < n_my) {
+        int x, y;
+        unit_xy(t + 1, x, y);
+        reset_next = pos_is_zero(pos, pos64, (int64_t)y + lane);
+      }
       if (lane == 0 && t + 1 < n_my) {       // the conv tile is free: fetch the next unit's
         int x, y;
         unit_xy(t + 1, x, y);
@@ -335,7 +348,6 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
       const bool known = *s_known != 0;
 
       // ---- the last token quarter: the tile's map, the incoming state, the records ---------------
-      bool publish_late = false;
       if (tq == 3) {
         float Pt = 1.0f, Ht = 0.0f;
 #pragma unroll
@@ -362,7 +374,11 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
               int L = 32;
               unsigned spins = 0;
               while (true) {
-                if (pred >= 0) f = ld_acquire_u32(&flags[rp]);
+                if (pred >= 0) {
+                  // inclusive if the predecessor's first state word carries the token, else
+                  // whatever its flag says (1: its map is published)
+                  f = (ld_relaxed_u64(incl + rp * kSub) >> 32) == 1ull ? 2u : ld_acquire_u32(&flags[rp]);
+                }
                 const unsigned im = __ballot_sync(0xffffffffu, f == 2u);
                 L = im ? (__ffs(im) - 1) : 32;
                 const unsigned need = (L >= 31) ? 0xffffffffu : ((2u << L) - 1u);
@@ -393,7 +409,15 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
               }
               if (L < 32) {
                 const int64_t r2 = rec - (int64_t)(tt - (base - L)) * per_tt * 4;
-                hin = fmaf(Pc, __uint_as_float((uint32_t)ld_relaxed_u64(incl + r2 * kSub + lane)), Hc);
+                // the 32 state words were stored by one instruction but are 32 separate words: each
+                // lane waits for the token of its own
+                unsigned long long v = ld_relaxed_u64(incl + r2 * kSub + lane);
+                for (unsigned k = 0; (v >> 32) != 1ull && k < kLookbackSpins; ++k) {
+                  __nanosleep(32);
+                  v = ld_relaxed_u64(incl + r2 * kSub + lane);
+                }
+                if (!__all_sync(0xffffffffu, (v >> 32) == 1ull)) timed_out = true;
+                hin = fmaf(Pc, __uint_as_float((uint32_t)v), Hc);
                 done = true;
               } else {
                 base -= 32;
@@ -411,14 +435,6 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
         const float h_end = fmaf(Pt, hin, Ht);
         st_relaxed_u64(incl + rec * kSub + lane, kToken | (unsigned long long)__float_as_uint(h_end));
         if (h_last != nullptr && tt == tiles_t - 1) h_last[(int64_t)b * E + e0 + lane] = h_end;
-        if (!known) {
-          __syncwarp();
-          if (lane == 0) st_release_u32(&flags[rec], 2u);
-        } else {
-          // the release (which waits for the store above) is left to the end of the unit: its
-          // consumer is a full round of units away
-          publish_late = true;
-        }
       }
       if (!known) named_bar_sync(set_id, 128);
 
@@ -453,7 +469,6 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
       if (lane == 0) {
         tma_store_2d(&map_ot, e0, row0, tile_y_s);
         bulk_commit();
-        if (publish_late) st_release_u32(&flags[rec], 2u);
       }
     }
     if (lane == 0) bulk_wait_all();
