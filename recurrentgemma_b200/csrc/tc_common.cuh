@@ -7,13 +7,17 @@
 
 namespace rgk {
 
-constexpr unsigned kWaitLimit = 1u << 20;
+// Waits ask the hardware to suspend the thread for up to kWaitHintNs per attempt (it wakes when the
+// barrier's phase completes), so a waiting thread issues an instruction only every so often; the
+// number of attempts bounds the wait at about a second.
+constexpr unsigned kWaitHintNs = 20000;
+constexpr unsigned kWaitLimit = 1u << 16;
 
 // Bounded wait.  Returns false (and raises the CTA's abort flag) when the limit is hit or another
 // role has already aborted.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   for (unsigned i = 0; i < kWaitLimit; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait(bar, parity, kWaitHintNs)) return true;
     if (*abort_flag) return false;
   }
   *abort_flag = 1;
@@ -21,18 +25,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 }
 
 // The same for a single-thread role whose waits are long (a producer waiting for a free stage, an
-// MMA issuer waiting for operands): the thread sleeps between attempts, so that its polling does not
-// take issue slots and shared-memory queue entries from the warps that do the arithmetic.
+// MMA issuer waiting for operands).
 __device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity,
                                                   volatile int* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
-  for (unsigned i = 0; i < kWaitLimit; ++i) {
-    __nanosleep(200);
-    if (mbar_try_wait(bar, parity)) return true;
-    if (*abort_flag) return false;
-  }
-  *abort_flag = 1;
-  return false;
+  return mbar_wait(bar, parity, abort_flag);
 }
 
 __device__ __forceinline__ void tc_fence_before() {
