@@ -336,9 +336,17 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
       // inclusive record was there at the start of the unit): then the quarters need one barrier,
       // to see each other's maps, and nothing waits for the record of this tile to be published.
       if (tq == 3) {
-        if (tt > 0 && __all_sync(0xffffffffu, (pre >> 32) == 1ull)) {
-          hin_pref = __uint_as_float((uint32_t)pre);
-          have_hin = true;
+        if (tt > 0) {
+          bool all = __all_sync(0xffffffffu, (pre >> 32) == 1ull);
+          if (!all) {
+            // the predecessor's CTA runs a little behind: ask once more before taking the long way
+            pre = ld_relaxed_u64(incl + (rec - (int64_t)per_tt * 4) * kSub + lane);
+            all = __all_sync(0xffffffffu, (pre >> 32) == 1ull);
+          }
+          if (all) {
+            hin_pref = __uint_as_float((uint32_t)pre);
+            have_hin = true;
+          }
         }
         if (have_hin) s_hin[lane] = hin_pref;
         if (lane == 0) *s_known = have_hin ? 1 : 0;
