@@ -382,8 +382,9 @@ def run_gpu(args, cfg):
     k["gbs"] = k["bytes"] / (k["ms"] * 1e-3) / 1e9
     k["tflops"] = k["flops"] / (k["ms"] * 1e-3) / 1e12
   # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of each kernel at this
-  # workload, from the ncu capture summarised in profiles/ncu_full_cfg1_path_kernels.md.
-  ncu_traffic = {"conv1d_prefill": 288.3e6, "rglru_fused": 596.5e6}
+  # workload, from the ncu captures summarised in profiles/ncu_full_cfg1_path_kernels.md and
+  # profiles/ncu_full_cfg1_rglru_chan_kernel.md.
+  ncu_traffic = {"conv1d_prefill": 288.3e6, "rglru_fused": 490.1e6}
   dom_name = max(kernels, key=lambda k: kernels[k]["ms"])
   dom = kernels[dom_name]
   path_bytes = 3 * b * t * e * 2 + 2 * p["rg_lru.input_gate.w"].numel() * 2
@@ -398,7 +399,7 @@ def run_gpu(args, cfg):
       "kernels": {k: {"ms": round(v["ms"], 4), "GB/s": round(v["gbs"], 1),
                       "TFLOP/s": round(v["tflops"], 2)} for k, v in kernels.items()},
       "two_kernel_route": {k: round(v, 4) for k, v in two_kernel.items()},
-      "note": ("rglru_fused is bounded by the SFU and issue pipes (5 SFU operations and ~70 "
+      "note": ("rglru_fused is bounded by the SFU and issue pipes (7 SFU operations and ~63 "
                "instructions per element with the reference's bfloat16 roundings), not by HBM; "
                "frac is its algorithmic bytes over its time against the measured copy bandwidth"),
   }
