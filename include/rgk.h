@@ -57,7 +57,7 @@ enum {
   RGK_GATES_TCGEN05 = 2, /* tensor-core gate kernel, then the scan kernel (bfloat16, head width
                             256); RGK_ESHAPE if the shape is not covered */
   RGK_GATES_FUSED = 3    /* gates, gate arithmetic and scan in one tensor-core kernel (bfloat16,
-                            head width 256, T a multiple of 128); RGK_ESHAPE otherwise */
+                            head width 256, any T); RGK_ESHAPE otherwise */
 };
 
 RGK_API int rgk_abi_version(void);

@@ -128,9 +128,8 @@ int run_rglru(const void* c, const void* pos, int pos64, const rgk_params* p, co
   const int bw = (int)(E / H);
   const bool fused_ok = rgk::rglru_chan_supported(dtype, bw, B, T);
   if (gates_impl == RGK_GATES_FUSED && !fused_ok)
-    return fail(RGK_ESHAPE, "the fused RG-LRU kernel covers bfloat16, head width 256 and sequence "
-                            "lengths that are multiples of 128 (dtype %d, head width %d, T %lld)",
-                dtype, bw, (long long)T);
+    return fail(RGK_ESHAPE, "the fused RG-LRU kernel covers bfloat16 and head width 256 "
+                            "(dtype %d, head width %d, T %lld)", dtype, bw, (long long)T);
   if (fused_ok && (gates_impl == RGK_GATES_AUTO || gates_impl == RGK_GATES_FUSED)) {
     const void* packed = p->gates_packed;
     if (packed == nullptr) {

@@ -4,8 +4,9 @@
 // run of 32 tokens: gate arithmetic, the linear recurrence and the join with the other branch all
 // happen in its registers, in time order, with no transposition (recurrentgemma torch/layers.py:
 // 127-137, 313-365, 140-191; join of torch/modules.py:627-628, 646).  The recurrence coefficients a
-// and the normalised input never reach HBM.  bfloat16, heads of width 256, sequence length a
-// multiple of 128.
+// and the normalised input never reach HBM.  bfloat16, heads of width 256, any sequence length
+// (the last time tile of a sequence may be partial: the copy engine fills rows past the end with
+// zeros and drops them from the stores, and those tokens act as the identity map).
 //
 // Units of work: 128 consecutive tokens of one sequence x one half of a head (128 channels).  Units
 // are numbered time-major and dealt out round-robin to persistent CTAs, one per SM, so the unit that
@@ -85,11 +86,12 @@ struct QuarterRecord {
 
 // 16 tokens of one channel: gates from the accumulators, (a, x) packed per token pair, and the
 // running map (P, H) of the thread's tokens.  `ct` points at the thread's column of the warp's conv
-// tile (row stride 32 elements); `rs` holds the reset bits of the 16 tokens.
+// tile (row stride 32 elements); `rs` holds the reset bits of the 16 tokens, `inv` the bits of tokens
+// past the end of the sequence (the kResets variant handles both).
 template <bool kResets>
 __device__ __forceinline__ void gates_16(const uint32_t (&zx)[16], const uint32_t (&za)[16],
                                          const uint16_t* ct, uint32_t bx2, uint32_t ba2,
-                                         uint32_t m8sp2, uint32_t rs, uint32_t* a_out,
+                                         uint32_t m8sp2, uint32_t rs, uint32_t inv, uint32_t* a_out,
                                          uint32_t* x_out, float& P, float& H) {
 #pragma unroll
   for (int jp = 0; jp < 8; ++jp) {
@@ -104,6 +106,12 @@ __device__ __forceinline__ void gates_16(const uint32_t (&zx)[16], const uint32_
                             (((rs >> (2 * jp + 1)) & 1u) ? 0u : 0xffff0000u);
       a2 &= keep;
       mult2 = (mult2 & keep) | (0x3f803f80u & ~keep);
+      // a token past the end of the sequence: the identity map (a = 1, x = 0)
+      const uint32_t live = (((inv >> (2 * jp)) & 1u) ? 0u : 0x0000ffffu) |
+                            (((inv >> (2 * jp + 1)) & 1u) ? 0u : 0xffff0000u);
+      a2 = (a2 & live) | (0x3f803f80u & ~live);
+      mult2 = (mult2 & live) | (0x3f803f80u & ~live);
+      gx2 &= live;
     }
     const uint32_t x2 = bmul2(bmul2(c2, gx2), mult2);
     a_out[jp] = a2;
@@ -141,7 +149,7 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
   volatile int* s_abort = reinterpret_cast<volatile int*>(smem + kOffAbort);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tiles_t = T_ / kUT;
+  const int tiles_t = (T_ + kUT - 1) / kUT;
   const int per_tt = B * groups;                         // units per time tile
   const int n_my = (n_units - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
 
@@ -171,13 +179,12 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
         const int u = blockIdx.x + t * gridDim.x;
         const int tt = u / per_tt, rem = u - tt * per_tt;
         const int b = rem / groups, grp = rem - b * groups;
-        const int row0 = b * T_ + tt * kUT;
         for (int kb = 0; kb < kKBlocks; ++kb, ++it) {
           const int s = it % kRing;
           ok = mbar_wait_relaxed(bar_empty(s), ((it / kRing) & 1) ^ 1, s_abort);
           if (!ok) break;
           mbar_expect_tx(bar_full(s), kStage);
-          tma_load_2d(s_base + kOffRing + s * kStage, &map_c, (grp >> 1) * kHW + kb * kKB, row0,
+          tma_load_3d(s_base + kOffRing + s * kStage, &map_c, (grp >> 1) * kHW + kb * kKB, tt * kUT, b,
                       bar_full(s));
           tma_load_2d(s_base + kOffRing + s * kStage + kCBytes, &map_w, kb * kKB, grp * 2 * kUC,
                       bar_full(s));
@@ -225,27 +232,31 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
     const uint32_t tile_c_s = smem_u32(tile_c), tile_y_s = smem_u32(tile_y);
     bool ok = true;
 
-    auto unit_xy = [&](int t, int& x, int& y) {
+    auto unit_xy = [&](int t, int& x, int& y, int& z) {     // channel, token in sequence, sequence
       const int u = blockIdx.x + t * gridDim.x;
       const int tt = u / per_tt, rem = u - tt * per_tt;
       const int b = rem / groups, grp = rem - b * groups;
       x = (grp >> 1) * kHW + (grp & 1) * kUC + chq * kSub;
-      y = b * T_ + tt * kUT + tq * kSub;
+      y = tt * kUT + tq * kSub;
+      z = b;
+    };
+    // whether this lane's token of unit t starts a document (tokens past the end do not)
+    auto lane_reset = [&](int t) {
+      int x, y, z;
+      unit_xy(t, x, y, z);
+      const int tok = y + lane;
+      return tok < T_ && pos_is_zero(pos, pos64, (int64_t)z * T_ + tok);
     };
     if (lane == 0 && n_my > 0) {
-      int x, y;
-      unit_xy(0, x, y);
+      int x, y, z;
+      unit_xy(0, x, y, z);
       mbar_expect_tx(bar_ct(warp), kSubBytes);
-      tma_load_2d(tile_c_s, &map_ct, x, y, bar_ct(warp));
+      tma_load_3d(tile_c_s, &map_ct, x, y, z, bar_ct(warp));
     }
 
     // whether this lane's token of the next unit starts a document: asked for a unit ahead
     bool reset_next = false;
-    if (n_my > 0) {
-      int x, y;
-      unit_xy(0, x, y);
-      reset_next = pos_is_zero(pos, pos64, (int64_t)y + lane);
-    }
+    if (n_my > 0) reset_next = lane_reset(0);
 
     for (int t = 0; t < n_my; ++t) {
       const int as = t & 1, par = t & 1;
@@ -253,13 +264,16 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
       const int tt = u / per_tt, rem = u - tt * per_tt;
       const int b = rem / groups, grp = rem - b * groups;
       const int e0 = (grp >> 1) * kHW + (grp & 1) * kUC + chq * kSub;     // first channel of the warp
-      const int row0 = b * T_ + tt * kUT + tq * kSub;                     // first token of the warp
+      const int tok0 = tt * kUT + tq * kSub;                              // first token of the warp
       const int64_t rec = (int64_t)u * 4 + chq;
       float2* s_qmap = reinterpret_cast<float2*>(smem + kOffQmap) + ((par * 4 + chq) * 4) * 32;
       float* s_hin = reinterpret_cast<float*>(smem + kOffHin) + (par * 4 + chq) * 32;
       volatile int* s_known = reinterpret_cast<volatile int*>(smem + kOffKnown) + (par * 4 + chq);
 
       const uint32_t resets = __ballot_sync(0xffffffffu, reset_next);
+      // tokens of this warp past the end of the sequence (only in a sequence's last time tile)
+      const int n_live = T_ - tok0;
+      const uint32_t invalid = n_live >= 32 ? 0u : (n_live <= 0 ? 0xffffffffu : (0xffffffffu << n_live));
       const uint32_t bxv = __ldg(reinterpret_cast<const uint16_t*>(bias_x) + e0 + lane);
       const uint32_t bav = __ldg(reinterpret_cast<const uint16_t*>(bias_a) + e0 + lane);
       const uint32_t spv = __ldg(reinterpret_cast<const uint16_t*>(m8sp) + e0 + lane);
@@ -300,11 +314,12 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
           if (lane == 0 && ok) mbar_arrive(bar_acc_empty(as));
         }
         const uint32_t rs = (resets >> (half * 16)) & 0xffffu;
-        if (rs == 0u)
-          gates_16<false>(zx, za, ct + half * 16 * kSub, bx2, ba2, m8sp2, rs, a_pk + half * 8,
+        const uint32_t inv = (invalid >> (half * 16)) & 0xffffu;
+        if ((rs | inv) == 0u)
+          gates_16<false>(zx, za, ct + half * 16 * kSub, bx2, ba2, m8sp2, rs, inv, a_pk + half * 8,
                           x_pk + half * 8, P, H);
         else
-          gates_16<true>(zx, za, ct + half * 16 * kSub, bx2, ba2, m8sp2, rs, a_pk + half * 8,
+          gates_16<true>(zx, za, ct + half * 16 * kSub, bx2, ba2, m8sp2, rs, inv, a_pk + half * 8,
                          x_pk + half * 8, P, H);
         if (half == 0) {
           // the previous unit's output tile must have been read by its store before the buffer is
@@ -313,23 +328,19 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
             bulk_wait_read();
             if constexpr (kJoin != 0) {
               mbar_expect_tx(bar_yt(warp), kSubBytes);
-              tma_load_2d(tile_y_s, &map_yt, e0, row0, bar_yt(warp));
+              tma_load_3d(tile_y_s, &map_yt, e0, tok0, b, bar_yt(warp));
             }
           }
         }
       }
       __threadfence_block();                 // the tile's loads are complete before it is refilled
       __syncwarp();
-      if (t + 1 < n_my) {
-        int x, y;
-        unit_xy(t + 1, x, y);
-        reset_next = pos_is_zero(pos, pos64, (int64_t)y + lane);
-      }
+      if (t + 1 < n_my) reset_next = lane_reset(t + 1);
       if (lane == 0 && t + 1 < n_my) {       // the conv tile is free: fetch the next unit's
-        int x, y;
-        unit_xy(t + 1, x, y);
+        int x, y, z;
+        unit_xy(t + 1, x, y, z);
         mbar_expect_tx(bar_ct(warp), kSubBytes);
-        tma_load_2d(tile_c_s, &map_ct, x, y, bar_ct(warp));
+        tma_load_3d(tile_c_s, &map_ct, x, y, z, bar_ct(warp));
       }
 
       // The incoming state is normally known before the tile's own map is (the predecessor's
@@ -475,7 +486,7 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) {
-        tma_store_2d(&map_ot, e0, row0, tile_y_s);
+        tma_store_3d(&map_ot, e0, tok0, b, tile_y_s);
         bulk_commit();
       }
     }
@@ -518,6 +529,23 @@ bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, 
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Tensor map of bfloat16 activations [B, T, E] with boxes of box_rows tokens x box_cols channels of
+// one sequence: rows past the end of a sequence read as zero and are dropped from stores.
+bool make_map_bte(CUtensorMap* map, const void* base, uint64_t B, uint64_t T, uint64_t E,
+                  uint32_t box_rows, uint32_t box_cols, bool swizzle128) {
+  EncodeTiledFn fn = tensor_map_encoder();
+  if (fn == nullptr) return false;
+  const cuuint64_t dims[3] = {E, T, B};
+  const cuuint64_t strides[2] = {E * 2, T * E * 2};
+  const cuuint32_t box[3] = {box_cols, box_rows, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box,
+            estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+            swizzle128 ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 struct ChanLayout {
   int64_t n_units, n_rec;
   size_t flags_off, m8sp_off, agg_off, incl_off, total;
@@ -526,7 +554,7 @@ struct ChanLayout {
 ChanLayout chan_layout(int64_t B, int64_t T, int64_t E) {
   ChanLayout L;
   const int64_t groups = E / kUC;
-  L.n_units = (T / kUT) * B * groups;
+  L.n_units = ((T + kUT - 1) / kUT) * B * groups;
   L.n_rec = L.n_units * 4;
   auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
   L.flags_off = sizeof(WsHeader);
@@ -540,12 +568,11 @@ ChanLayout chan_layout(int64_t B, int64_t T, int64_t E) {
 }  // namespace
 
 bool rglru_chan_supported(int dtype, int bw, int64_t B, int64_t T) {
-  return dtype == 1 && bw == kHW && B >= 1 && T >= kUT && T % kUT == 0 &&
-         B * T < ((int64_t)1 << 31);
+  return dtype == 1 && bw == kHW && B >= 1 && T >= 1 && B * T < ((int64_t)1 << 31);
 }
 
 size_t rglru_chan_workspace_bytes(int64_t B, int64_t T, int64_t E) {
-  if (T < kUT || T % kUT != 0) return 0;
+  if (T < 1) return 0;
   return chan_layout(B, T, E).total;
 }
 
@@ -565,12 +592,12 @@ cudaError_t launch_rglru_chan(const void* c, const void* pos, int pos64, const v
   if ((err = cudaGetLastError()) != cudaSuccess) return err;
 
   CUtensorMap map_c, map_w, map_ct, map_yt, map_ot;
-  const uint64_t rows = (uint64_t)(B * T);
-  if (!make_map(&map_c, c, rows, (uint64_t)E, kUT, kKB, true) ||
+  const uint64_t Bu = (uint64_t)B, Tu = (uint64_t)T, Eu = (uint64_t)E;
+  if (!make_map_bte(&map_c, c, Bu, Tu, Eu, kUT, kKB, true) ||
       !make_map(&map_w, packed_w, (uint64_t)H * 4 * kUC, kHW, 2 * kUC, kKB, true) ||
-      !make_map(&map_ct, c, rows, (uint64_t)E, kSub, kSub, false) ||
-      !make_map(&map_ot, out, rows, (uint64_t)E, kSub, kSub, false) ||
-      !make_map(&map_yt, yb != nullptr ? yb : out, rows, (uint64_t)E, kSub, kSub, false))
+      !make_map_bte(&map_ct, c, Bu, Tu, Eu, kSub, kSub, false) ||
+      !make_map_bte(&map_ot, out, Bu, Tu, Eu, kSub, kSub, false) ||
+      !make_map_bte(&map_yt, yb != nullptr ? yb : out, Bu, Tu, Eu, kSub, kSub, false))
     return cudaErrorInvalidValue;
   static int num_sms = 0;
   if (num_sms == 0) {

@@ -328,6 +328,7 @@ def test_block_fused_matches_composed(rg):
 
 
 @pytest.mark.parametrize("shape", [(1, 128, 256, 1), (2, 384, 512, 2), (1, 8192, 256, 1),
+                                   (3, 77, 256, 1), (2, 200, 512, 2), (1, 1001, 256, 1),
                                    (3, 1024, 2560, 10), (37, 384, 512, 2), (40, 256, 512, 2),
                                    (8, 4096, 2560, 10)],
                          ids=lambda s: "x".join(map(str, s)))
@@ -335,9 +336,9 @@ def test_fused_rglru_kernel(rg, oracle, shape):
   """Gates + gate arithmetic + scan (+ join) in one tensor-core kernel against the two-kernel
   tensor-core route (same roundings; only the association of the carries differs) and, on the
   smaller shapes, against the oracle.  Covers one unit per sequence, carries inside one round of
-  CTAs (B = 1, long T), carries across rounds, and the one-pass kernel that takes over when there are
-  at least as many (sequence, half head) pairs as SMs (B = 37 and 40 with two heads: the state
-  comes from the same CTA's previous round, or from another CTA's)."""
+  CTAs (B = 1, long T), sequence lengths that end inside a time tile, carries across rounds, and
+  workloads with as many (sequence, half head) pairs as SMs or a few more (B = 37 and 40 with two
+  heads: the incoming state comes from the same CTA's previous round, or from another CTA's)."""
   from recurrentgemma_b200 import _lib
   b, t, e, h = shape
   case = C.Case(f"fused_{b}_{t}_{e}", "rglru", "bfloat16", b, t, e, h, pos="multi")
@@ -372,9 +373,10 @@ def test_fused_rglru_kernel(rg, oracle, shape):
                             p["rg_lru.a_gate.w"], p["rg_lru.a_gate.b"], h0.cpu())
     assert_close(y_f, y_r, tol, "fused vs oracle y")
     assert_close(h_f, h_r, tol, "fused vs oracle h")
-  with pytest.raises(_lib.RgkError):      # T not a multiple of 128
-    m.gates_impl = _lib.GATES_FUSED
-    m(x[:, :100].contiguous(), pos[:, :100].contiguous())
+  with pytest.raises(_lib.RgkError):      # head width other than 256
+    m2 = rg.RGLRU(256, 2, device=DEV, dtype=dt)
+    m2.gates_impl = _lib.GATES_FUSED
+    m2(torch.zeros(1, 128, 256, device=DEV, dtype=dt), torch.arange(128, device=DEV)[None])
 
 
 def test_host_pipeline_matches_device_call(rg):
