@@ -101,10 +101,26 @@ conv1d_prefill_kernel(const T* __restrict__ x, const void* __restrict__ pos, int
   for (int k = 0; k < 4; ++k) wv[k] = *reinterpret_cast<const uint4*>(w + (int64_t)k * E + e0);
   const uint4 bv = *reinterpret_cast<const uint4*>(bias + e0);
 
+  // The common case - no document starts in the window, no sequence edge - is straight-line code:
+  // four products and four sums per pack, nothing to decide per row.
+  const bool plain = nz == ((1u << (kConvRows + 3)) - 1u) && t_begin >= 3 && t_begin + kConvRows <= T_;
+  if (plain) {
+#pragma unroll
+    for (int r = 0; r < kConvRows; ++r) {
+      const int i = r + 3;
+      uint4 acc = Ops::mul(xr[i], wv[3]);
+      acc = Ops::add(acc, Ops::mul(xr[i - 1], wv[2]));
+      acc = Ops::add(acc, Ops::mul(xr[i - 2], wv[1]));
+      acc = Ops::add(acc, Ops::mul(xr[i - 3], wv[0]));
+      acc = Ops::add(acc, bv);
+      st_stream(out + (row0 + t_begin + r) * E + e0, acc);
+    }
+    if (cache_out == nullptr || t_begin + kConvRows < T_) return;
+  }
 #pragma unroll
   for (int r = 0; r < kConvRows; ++r) {
     const int t = t_begin + r;
-    if (t < T_) {
+    if (!plain && t < T_) {
       const int i = r + 3;                       // index of row t inside xr
       // Tap s reaches row t-s and survives while rows t-s+1 .. t start no document.  A masked or
       // left-padded tap contributes round(acc + 0) = acc, so it is skipped
