@@ -348,7 +348,7 @@ def run_gpu(args, cfg):
                   "scan_join_GB/s": 4 * n_el * es / t_scan / 1e6}
     del a_t, c, y2
 
-    # The whole RecurrentBlock (config 1 as BASELINE.json words it): the three projections on the
+    # The whole RecurrentBlock at the same shapes: the three projections on the
     # tcgen05 GEMM around the sub-path, one library call.
     import math
     gb = torch.Generator(device="cpu").manual_seed(77)

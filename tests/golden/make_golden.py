@@ -94,7 +94,8 @@ def run_case(case: C.Case, layers, modules) -> dict:
 
 def main():
   ap = argparse.ArgumentParser()
-  ap.add_argument("--reference", default="/root/reference")
+  ap.add_argument("--reference", default=os.environ.get("RECURRENTGEMMA_REFERENCE", "reference"),
+                  help="path of a recurrentgemma checkout")
   args = ap.parse_args()
   _, layers, modules = import_reference(args.reference)
   total = 0
