@@ -3,11 +3,12 @@
 // (rnn_scan with one token) and the join of torch/modules.py:627-628, 646.
 //
 // The "tokens" of the contraction are the batch rows.  A CTA serves 128 rows x one quarter of a
-// head (64 channels): its 256 threads first build the A operand in shared memory - the conv output
-// of those rows for all 256 channels of the head, computed from the new token and the three cached
-// rows with the reference's bfloat16 roundings and written in the 128-byte-swizzled K-major layout
-// tcgen05 reads - while TMA brings the 64 x-gate and 64 a-gate weight rows (64 KiB, pre-packed
-// K-major).  Sixteen tcgen05.mma (M 128, N 128, K 16) leave both gates of every channel in TMEM;
+// head (64 channels); the four CTAs of a head form a cluster.  The A operand - the conv output of
+// the 128 rows for all 256 channels of the head, computed from the new token and the three cached
+// rows with the reference's bfloat16 roundings, in the 128-byte-swizzled K-major layout tcgen05
+// reads - is built once per cluster: each CTA computes the slice of its own 64 channels and stores it
+// into the shared memory of all four (distributed shared memory), while TMA brings the CTA's 64
+// x-gate and 64 a-gate weight rows (64 KiB, pre-packed K-major).  Sixteen tcgen05.mma (M 128, N 128, K 16) leave both gates of every channel in TMEM;
 // the epilogue does the gate arithmetic, the state update h = a h + x in float32 (stored
 // unrounded), the join with gelu(y branch), and writes out / state / shifted conv cache.
 //
@@ -35,7 +36,8 @@ constexpr int kOffBar = kOffConst + 3 * (kChanCta / 2) * 4;    // two mbarriers
 constexpr int kOffTmem = kOffBar + 16;
 constexpr int kOffAbort = kOffTmem + 4;
 constexpr int kSmem = kOffAbort + 4 + 1024;
-constexpr int kThreadsDec = 256;
+constexpr int kThreadsDec = 512;
+constexpr int kEpiCols = kChanCta / (kThreadsDec / 128);   // channels per epilogue thread: 16
 constexpr uint32_t kIdescDec = tc_idesc_bf16(kRowsM, kN);
 
 __device__ __forceinline__ uint4 mul4(const uint4& a, const uint4& b) {
@@ -113,64 +115,77 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __nv_bfloat16*
   }
 
   // ---- A operand: conv output of 128 rows x the head's 256 channels ------------------------------
+  // The four CTAs of a head (a cluster) need the same A tile.  Each computes the K slice of its own
+  // 64 channels and stores it into the shared memory of all four: a quarter of the loads and of the
+  // arithmetic per CTA.
   {
-    const int pk = tid & 31;                      // 16-byte pack of the head's channels
-    const int e = head * kHeadW + pk * 8;
+    const int pk = tid & 7;                       // 16-byte pack inside this CTA's slice of channels
+    const int e = chan0 + pk * 8;
     uint4 wv[4];
 #pragma unroll
     for (int k = 0; k < 4; ++k) wv[k] = *reinterpret_cast<const uint4*>(conv_w + (int64_t)k * E + e);
     const uint4 bv = *reinterpret_cast<const uint4*>(conv_b + e);
-    const bool own = (pk >> 3) == quarter;        // this CTA also shifts the cache of its channels
-    uint8_t* a_slice = smem + kOffA + (pk >> 3) * kASlice;
+    uint32_t a_remote[4];                         // this slice inside each CTA of the cluster
+#pragma unroll
+    for (int d = 0; d < 4; ++d)
+      asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
+                   : "=r"(a_remote[d]) : "r"(s_base + kOffA + quarter * kASlice), "r"(d));
     // Everything above (barriers, TMEM, the per-channel constants) is independent of the kernel
     // before this one on the stream, which in a decode loop is the previous layer: with
     // programmatic dependent launch it overlaps that kernel's tail.  The activations below are its
     // output, so wait for it here, then let the next layer's prologue start in turn.
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    // 16 rows per thread, in two batches of 8 whose 32 loads are all issued before the first use:
-    // the step is latency bound, so bytes in flight are what counts.
-    constexpr int kBatch = 8;
-#pragma unroll 1
-    for (int r0 = warp; r0 < kRowsM; r0 += kBatch * (kThreadsDec / 32)) {
-      uint4 xv[kBatch][4];
+    // two rows per thread, their 8 loads all issued before the first use
+    constexpr int kPer = kRowsM * 8 / kThreadsDec;     // rows per thread: 2
+    constexpr int kRowStep = kThreadsDec / 8;
+    uint4 xv[kPer][4];
 #pragma unroll
-      for (int i = 0; i < kBatch; ++i) {
-        const int r = r0 + i * (kThreadsDec / 32);
-        const int64_t m = min((int64_t)tile * kRowsM + r, (int64_t)M - 1);   // clamped: never out of range
-        const __nv_bfloat16* cr = cache_in + m * 3 * E + e;
-        xv[i][0] = *reinterpret_cast<const uint4*>(cr);
-        xv[i][1] = *reinterpret_cast<const uint4*>(cr + E);
-        xv[i][2] = *reinterpret_cast<const uint4*>(cr + 2 * (int64_t)E);
-        xv[i][3] = *reinterpret_cast<const uint4*>(xb + m * E + e);
-      }
+    for (int i = 0; i < kPer; ++i) {
+      const int r = (tid >> 3) + kRowStep * i;
+      const int64_t m = min((int64_t)tile * kRowsM + r, (int64_t)M - 1);   // clamped: never out of range
+      const __nv_bfloat16* cr = cache_in + m * 3 * E + e;
+      xv[i][0] = *reinterpret_cast<const uint4*>(cr);
+      xv[i][1] = *reinterpret_cast<const uint4*>(cr + E);
+      xv[i][2] = *reinterpret_cast<const uint4*>(cr + 2 * (int64_t)E);
+      xv[i][3] = *reinterpret_cast<const uint4*>(xb + m * E + e);
+    }
+    // every CTA of the cluster is running before its shared memory is written from outside
+    asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
 #pragma unroll
-      for (int i = 0; i < kBatch; ++i) {
-        const int r = r0 + i * (kThreadsDec / 32);
-        const int64_t m = (int64_t)tile * kRowsM + r;
-        // newest tap first (torch/layers.py:491-517 with prompt_len = 3), then the bias
-        uint4 acc = mul4(xv[i][3], wv[3]);
-        acc = add4(acc, mul4(xv[i][2], wv[2]));
-        acc = add4(acc, mul4(xv[i][1], wv[1]));
-        acc = add4(acc, mul4(xv[i][0], wv[0]));
-        acc = add4(acc, bv);
-        if (m < M) {
-          if (own && cache_out != nullptr) {
-            __nv_bfloat16* co = cache_out + m * 3 * E + e;
-            *reinterpret_cast<uint4*>(co) = xv[i][1];
-            *reinterpret_cast<uint4*>(co + E) = xv[i][2];
-            *reinterpret_cast<uint4*>(co + 2 * (int64_t)E) = xv[i][3];
-          }
-        } else {
-          acc = make_uint4(0u, 0u, 0u, 0u);
+    for (int i = 0; i < kPer; ++i) {
+      const int r = (tid >> 3) + kRowStep * i;
+      const int64_t m = (int64_t)tile * kRowsM + r;
+      // newest tap first (torch/layers.py:491-517 with prompt_len = 3), then the bias
+      uint4 acc = mul4(xv[i][3], wv[3]);
+      acc = add4(acc, mul4(xv[i][2], wv[2]));
+      acc = add4(acc, mul4(xv[i][1], wv[1]));
+      acc = add4(acc, mul4(xv[i][0], wv[0]));
+      acc = add4(acc, bv);
+      if (m < M) {
+        if (cache_out != nullptr) {               // these are this CTA's own channels: shift the cache
+          __nv_bfloat16* co = cache_out + m * 3 * E + e;
+          *reinterpret_cast<uint4*>(co) = xv[i][1];
+          *reinterpret_cast<uint4*>(co + E) = xv[i][2];
+          *reinterpret_cast<uint4*>(co + 2 * (int64_t)E) = xv[i][3];
         }
-        *reinterpret_cast<uint4*>(a_slice + r * 128 + (((pk & 7) ^ (r & 7)) << 4)) = acc;
+      } else {
+        acc = make_uint4(0u, 0u, 0u, 0u);
       }
+      const uint32_t off = r * 128 + ((pk ^ (r & 7)) << 4);
+#pragma unroll
+      for (int d = 0; d < 4; ++d)
+        asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};"
+                     :: "r"(a_remote[d] + off), "r"(acc.x), "r"(acc.y), "r"(acc.z), "r"(acc.w) : "memory");
     }
   }
-  // make the generic-proxy writes of the A tile visible to the tensor core (async proxy)
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-  __syncthreads();
+  // The tile is complete when all four CTAs have stored their slices: the generic-proxy writes are
+  // fenced towards the tensor core's (async) proxy, then released and acquired across the cluster.
+  asm volatile("fence.proxy.async;" ::: "memory");
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+  asm volatile("fence.proxy.async;" ::: "memory");
 
   // ---- MMA ------------------------------------------------------------------------------------------
   if (tid == 0) {
@@ -189,39 +204,41 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __nv_bfloat16*
     }
   }
 
-  // ---- epilogue: 8 warps = 4 TMEM lane quarters x 2 halves of the 64 channels ---------------------
+  // ---- epilogue: 16 warps = 4 TMEM lane quarters x 4 groups of 16 channels ------------------------
   {
-    const int lane_base = (warp & 3) * 32, col_half = warp >> 2;
+    const int lane_base = (warp & 3) * 32, col_grp = warp >> 2;
     const int r = lane_base + lane;
     const int64_t m = (int64_t)tile * kRowsM + r;
     const bool row_ok = m < M;
     const int64_t m_ld = row_ok ? m : 0;
     const bool is_reset = row_ok && pos_is_zero(pos, pos64, m);
-    const int e = chan0 + col_half * 32;
+    const int e = chan0 + col_grp * kEpiCols;
     // inputs of the state update and of the join, in flight while the MMA runs
-    float4 hv[8];
-    uint4 yv[4];
+    float4 hv[kEpiCols / 4];
+    uint4 yv[kEpiCols / 8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) hv[j] = *reinterpret_cast<const float4*>(h_in + m_ld * E + e + 4 * j);
+    for (int j = 0; j < kEpiCols / 4; ++j)
+      hv[j] = *reinterpret_cast<const float4*>(h_in + m_ld * E + e + 4 * j);
     if constexpr (kMul) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) yv[j] = *reinterpret_cast<const uint4*>(yb + m_ld * E + e + 8 * j);
+      for (int j = 0; j < kEpiCols / 8; ++j)
+        yv[j] = *reinterpret_cast<const uint4*>(yb + m_ld * E + e + 8 * j);
     }
     if (mbar_wait(bar_mma, 0, s_abort)) {
       tc_fence_after();
-      uint32_t zx[32], za[32];
-      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lane_base) << 16) + col_half * 32;
-      tc_ld_32x32(t_row, zx);
-      tc_ld_32x32(t_row + kChanCta, za);
-      // conv outputs of these 32 channels: slice `quarter` of the A tile, units col_half*4 .. +3
-      uint4 cv[4];
+      uint32_t zx[kEpiCols], za[kEpiCols];
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lane_base) << 16) + col_grp * kEpiCols;
+      tc_ld_32x16(t_row, zx);
+      tc_ld_32x16(t_row + kChanCta, za);
+      // conv outputs of these 16 channels: slice `quarter` of the A tile, units col_grp*2, +1
+      uint4 cv[kEpiCols / 8];
       const uint8_t* a_row = smem + kOffA + quarter * kASlice + r * 128;
 #pragma unroll
-      for (int j = 0; j < 4; ++j)
-        cv[j] = *reinterpret_cast<const uint4*>(a_row + (((col_half * 4 + j) ^ (r & 7)) << 4));
+      for (int j = 0; j < kEpiCols / 8; ++j)
+        cv[j] = *reinterpret_cast<const uint4*>(a_row + (((col_grp * (kEpiCols / 8) + j) ^ (r & 7)) << 4));
       tc_wait_ld();
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
+      for (int j = 0; j < kEpiCols / 8; ++j) {
         const uint32_t cp[4] = {cv[j].x, cv[j].y, cv[j].z, cv[j].w};
         const uint32_t yp[4] = {yv[j].x, yv[j].y, yv[j].z, yv[j].w};
         float hn[8];
@@ -229,7 +246,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __nv_bfloat16*
 #pragma unroll
         for (int p = 0; p < 4; ++p) {
           const int n = j * 8 + p * 2;
-          const int pair = (col_half * 32 + n) >> 1;
+          const int pair = (col_grp * kEpiCols + n) >> 1;
           uint32_t a2, xn2;
           gate_pair(__uint_as_float(zx[n]), __uint_as_float(zx[n + 1]), __uint_as_float(za[n]),
                     __uint_as_float(za[n + 1]), s_const[pair], s_const[kChanCta / 2 + pair],
@@ -307,11 +324,15 @@ cudaError_t launch_path_decode_tc(const void* xb, const void* yb, const void* po
   cfg.blockDim = dim3(kThreadsDec);
   cfg.dynamicSmemBytes = kSmem;
   cfg.stream = s;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
+  attr[1].id = cudaLaunchAttributeClusterDimension;      // the four channel quarters of a head
+  attr[1].val.clusterDim.x = 4;
+  attr[1].val.clusterDim.y = 1;
+  attr[1].val.clusterDim.z = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = 2;
 #define RGK_DEC(MUL)                                                                               \
   cudaLaunchKernelEx(&cfg, decode_tc_kernel<MUL>, map_w, (const T_*)xb, (const T_*)yb, pos, pos64, \
                      (const T_*)conv_w, (const T_*)conv_b, (const T_*)a_param, (const T_*)bx,      \
