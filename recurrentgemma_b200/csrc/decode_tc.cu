@@ -185,7 +185,6 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __nv_bfloat16*
   asm volatile("fence.proxy.async;" ::: "memory");
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-  asm volatile("fence.proxy.async;" ::: "memory");
 
   // ---- MMA ------------------------------------------------------------------------------------------
   if (tid == 0) {
