@@ -368,7 +368,20 @@ def run_gpu(args, cfg):
     block_info = {"ms": t_blk, "tokens_per_s": b * t / (t_blk * 1e-3),
                   "linear_ms": t_lin, "linear_TFLOP/s": 2 * b * t * e * e / (t_lin * 1e-3) / 1e12,
                   "what": "RecurrentBlock.forward prefill, same shapes, projections on the tcgen05 GEMM"}
-    del blk, x_in
+    # One step further out: recurrent_block(temporal_pre_norm(x)) + x, the temporal half of the
+    # reference's ResidualBlock, as one library call (RMSNorm kernel; residual in linear_out's
+    # epilogue), and the RMSNorm kernel alone against its HBM roofline (read x, write x).
+    norm = rg.RMSNorm(e, device=dev, dtype=dt)
+    norm.load_state_dict({"scale": (torch.randn(e, generator=gb) * 0.3).to(dt).to(dev)})
+    for _ in range(2):
+      rg.recurrent_residual(x_in, pos, norm, blk)
+    torch.cuda.synchronize()
+    t_res = _time_loop(lambda: rg.recurrent_residual(x_in, pos, norm, blk), ksteps, stream)
+    t_norm = _time_loop(lambda: norm(x_in), ksteps, stream)
+    block_info["residual_ms"] = t_res
+    block_info["rmsnorm_ms"] = t_norm
+    block_info["rmsnorm_GB/s"] = 2 * b * t * e * 2 / (t_norm * 1e-3) / 1e9
+    del blk, x_in, norm
   if rank != 0:
     if world > 1:
       dist.destroy_process_group()

@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define RGK_ABI_VERSION 2
+#define RGK_ABI_VERSION 3
 
 #if defined(__GNUC__)
 #define RGK_API __attribute__((visibility("default")))
@@ -236,6 +236,30 @@ RGK_API int rgk_recurrent_block_prefill(const void* x, const void* segment_pos, 
                                         int64_t E, int H, int W, int dtype, void* out,
                                         float* h_last, void* conv_cache_out, void* workspace,
                                         size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * RMSNorm.forward (recurrentgemma/torch/layers.py:65-73) over the last dimension of x [M, D]:
+ *   out = x * rsqrt(mean(x^2) + eps) * (scale + 1)
+ * with one rounding per tensor operation of the reference in bfloat16.  D a multiple of the
+ * 16-byte pack (8 bfloat16 / 4 float32) and at most 1024 packs; RGK_ESHAPE otherwise.
+ * ---------------------------------------------------------------------------------------------- */
+RGK_API int rgk_rmsnorm(const void* x, const void* scale, int64_t M, int64_t D, float eps, int dtype,
+                        void* out, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * The temporal half of ResidualBlock.forward for a recurrent block
+ * (recurrentgemma/torch/modules.py:897-902), prefill form:
+ *   out = RecurrentBlock(RMSNorm(x; norm_scale)) + x
+ * RMSNorm runs as its own kernel, the residual is added in the epilogue of linear_out's GEMM.
+ * Same coverage and outputs as rgk_recurrent_block_prefill.
+ * workspace: rgk_residual_workspace_bytes(B, T, D, E, dtype) bytes, 256-byte aligned.
+ * ---------------------------------------------------------------------------------------------- */
+RGK_API size_t rgk_residual_workspace_bytes(int64_t B, int64_t T, int64_t D, int64_t E, int dtype);
+RGK_API int rgk_residual_block_prefill(const void* x, const void* segment_pos, int pos_dtype,
+                                       const rgk_block_params* p, const void* norm_scale, float eps,
+                                       int64_t B, int64_t T, int64_t D, int64_t E, int H, int W,
+                                       int dtype, void* out, float* h_last, void* conv_cache_out,
+                                       void* workspace, size_t workspace_bytes, void* stream);
 
 /* Scratch needed by the calls above for a problem of this size (an upper bound over the entry
  * points, so one buffer serves all of them).  Returns 0 on invalid arguments. */

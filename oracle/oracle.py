@@ -45,6 +45,7 @@ def lib() -> ctypes.CDLL:
     _lib.rgo_rglru.restype = ctypes.c_int
     _lib.rgo_recurrent_path.restype = ctypes.c_int
     _lib.rgo_recurrent_block.restype = ctypes.c_int
+    _lib.rgo_residual_temporal.restype = ctypes.c_int
   return _lib
 
 
@@ -221,6 +222,44 @@ def recurrent_block(
       _p(_f(h0)), _p(cache_in), bsz, t, d, e, heads, wd, dt, _p(out), _p(h), _p(cc))
   if rc:
     raise RuntimeError(f"oracle recurrent_block failed ({rc})")
+  cdt = x.dtype if conv_cache is None else conv_cache.dtype
+  return _t(out, x.dtype), _t(h, torch.float32), _t(cc, cdt)
+
+
+def rmsnorm(x: torch.Tensor, scale: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+  """RMSNorm.forward over the last dimension."""
+  d = x.shape[-1]
+  m = x.numel() // d
+  out = _out(tuple(x.shape))
+  lib().rgo_rmsnorm(_p(_f(x)), _p(_f(scale)), ctypes.c_int64(m), d, ctypes.c_float(eps), _mode(x),
+                    _p(out))
+  return _t(out, x.dtype)
+
+
+def residual_temporal(
+    x: torch.Tensor, segment_pos: torch.Tensor, norm_scale: torch.Tensor, p: dict,
+    h0: Optional[torch.Tensor] = None, conv_cache: Optional[torch.Tensor] = None,
+    eps: float = 1e-6,
+):
+  """recurrent_block(rmsnorm(x)) + x.  Returns (out, rg_lru_state float32, conv1d_state)."""
+  dt = _mode(x)
+  bsz, t, d = x.shape
+  e = p["linear_x_w"].shape[0]
+  heads = p["gate_x_w"].shape[0]
+  wd = p["conv_w"].shape[0]
+  out = _out((bsz, t, d))
+  h = _out((bsz, e))
+  cc = _out((bsz, wd - 1, e))
+  cache_in = None if conv_cache is None else _f(conv_cache.to(x.dtype))
+  rc = lib().rgo_residual_temporal(
+      _p(_f(x)), _p(_i64(segment_pos)), _p(_f(norm_scale)), ctypes.c_float(eps),
+      _p(_f(p["linear_y_w"])), _p(_f(p["linear_y_b"])),
+      _p(_f(p["linear_x_w"])), _p(_f(p["linear_x_b"])), _p(_f(p["linear_out_w"])),
+      _p(_f(p["linear_out_b"])), _p(_f(p["conv_w"])), _p(_f(p["conv_b"])), _p(_f(p["a_param"])),
+      _p(_f(p["gate_x_w"])), _p(_f(p["gate_x_b"])), _p(_f(p["gate_a_w"])), _p(_f(p["gate_a_b"])),
+      _p(_f(h0)), _p(cache_in), bsz, t, d, e, heads, wd, dt, _p(out), _p(h), _p(cc))
+  if rc:
+    raise RuntimeError(f"oracle residual_temporal failed ({rc})")
   cdt = x.dtype if conv_cache is None else conv_cache.dtype
   return _t(out, x.dtype), _t(h, torch.float32), _t(cc, cdt)
 

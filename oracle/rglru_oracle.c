@@ -64,7 +64,7 @@ static inline float gelu_tanhf_(float z) {
   return 0.5f * z * (1.0f + tanhf(inner));
 }
 
-RGO_API int rgo_version(void) { return 1; }
+RGO_API int rgo_version(void) { return 2; }
 
 /* ---------------------------------------------------------------------------------------------
  * BlockDiagonalLinear.forward, layers.py:127-137.
@@ -385,6 +385,53 @@ RGO_API int rgo_recurrent_block(const float* x, const int64_t* segment_pos, cons
                               h0, conv_cache_in, B, T, E, H, W, dt, z, h_last, conv_cache_out);
   if (rc == 0) rgo_linear(z, wout, bout, M, E, D, dt, out);
   free(xb); free(yb); free(z);
+  return rc;
+}
+
+/* ---------------------------------------------------------------------------------------------
+ * RMSNorm.forward, layers.py:65-73:
+ *   var = mean(square(x), -1);  normed = x * rsqrt(var + eps);  out = normed * (scale + 1)
+ * x [M, D], scale [D].  Each tensor operation rounds in bfloat16 mode: the squares, the mean (one
+ * rounding of the float32 sum divided by D), var + eps, the reciprocal square root, the product
+ * with it, scale + 1 and the final product.
+ * ------------------------------------------------------------------------------------------- */
+RGO_API void rgo_rmsnorm(const float* x, const float* scale, int64_t M, int D, float eps, int dt,
+                         float* out) {
+#pragma omp parallel for schedule(static)
+  for (int64_t m = 0; m < M; ++m) {
+    const float* xr = x + m * D;
+    float sum = 0.0f;
+    for (int k = 0; k < D; ++k) sum += rnd(xr[k] * xr[k], dt);
+    const float var = rnd(sum / (float)D, dt);
+    const float r = rnd(1.0f / sqrtf(rnd(var + eps, dt)), dt);
+    for (int k = 0; k < D; ++k)
+      out[m * D + k] = rnd(rnd(xr[k] * r, dt) * rnd(scale[k] + 1.0f, dt), dt);
+  }
+}
+
+/* ---------------------------------------------------------------------------------------------
+ * The temporal half of ResidualBlock.forward for a recurrent block, modules.py:897-902:
+ *   residual = recurrent_block(temporal_pre_norm(x)) + x
+ * ------------------------------------------------------------------------------------------- */
+RGO_API int rgo_residual_temporal(const float* x, const int64_t* segment_pos,
+                                  const float* norm_scale, float eps, const float* wy,
+                                  const float* by, const float* wxl, const float* bxl,
+                                  const float* wout, const float* bout, const float* conv_w,
+                                  const float* conv_b, const float* a_param, const float* gwx,
+                                  const float* gbx, const float* gwa, const float* gba,
+                                  const float* h0, const float* conv_cache_in, int B, int T, int D,
+                                  int E, int H, int W, int dt, float* out, float* h_last,
+                                  float* conv_cache_out) {
+  const int64_t M = (int64_t)B * T;
+  float* xn = (float*)malloc(sizeof(float) * (size_t)(M * D));
+  if (!xn) return -1;
+  rgo_rmsnorm(x, norm_scale, M, D, eps, dt, xn);
+  int rc = rgo_recurrent_block(xn, segment_pos, wy, by, wxl, bxl, wout, bout, conv_w, conv_b,
+                               a_param, gwx, gbx, gwa, gba, h0, conv_cache_in, B, T, D, E, H, W,
+                               dt, out, h_last, conv_cache_out);
+  if (rc == 0)
+    for (int64_t i = 0; i < M * D; ++i) out[i] = rnd(out[i] + x[i], dt);
+  free(xn);
   return rc;
 }
 

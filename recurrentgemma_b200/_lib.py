@@ -62,6 +62,11 @@ SIGNATURES = {
     "rgk_recurrent_block_prefill": (_int, [_vp, _vp, _int, ctypes.POINTER(RgkBlockParams), _i64,
                                            _i64, _i64, _i64, _int, _int, _int, _vp, _vp, _vp, _vp,
                                            _sz, _vp]),
+    "rgk_rmsnorm": (_int, [_vp, _vp, _i64, _i64, ctypes.c_float, _int, _vp, _vp]),
+    "rgk_residual_workspace_bytes": (_sz, [_i64, _i64, _i64, _i64, _int]),
+    "rgk_residual_block_prefill": (_int, [_vp, _vp, _int, ctypes.POINTER(RgkBlockParams), _vp,
+                                          ctypes.c_float, _i64, _i64, _i64, _i64, _int, _int, _int,
+                                          _vp, _vp, _vp, _vp, _sz, _vp]),
     "rgk_workspace_bytes": (_sz, [_i64, _i64, _i64, _int]),
     "rgk_workspace_status": (_int, [_vp, _vp]),
 }
@@ -93,7 +98,7 @@ def load() -> ctypes.CDLL:
       fn = getattr(lib, name)
       fn.restype = res
       fn.argtypes = args
-    if lib.rgk_abi_version() != 2:
+    if lib.rgk_abi_version() != 3:
       raise RuntimeError("librgk.so has a different ABI version; rebuild it")
     _lib = lib
     return lib

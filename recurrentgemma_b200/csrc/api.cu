@@ -408,7 +408,7 @@ int rgk_dense_linear(const void* x, const void* weight, const void* bias, int64_
               "(dtype %d, K=%lld, N=%lld)", dtype, (long long)K, (long long)N);
   if (M == 0) return RGK_OK;
   RGK_CHECK_DEVICE();
-  RGK_CUDA(rgk::launch_dense_tc(x, weight, bias, M, (int)K, (int)N, act == RGK_ACT_GELU_TANH, out,
+  RGK_CUDA(rgk::launch_dense_tc(x, weight, bias, nullptr, M, (int)K, (int)N, act == RGK_ACT_GELU_TANH, out,
                                 status, static_cast<cudaStream_t>(stream)),
            "dense linear launch");
   return RGK_OK;
@@ -421,11 +421,44 @@ size_t rgk_block_workspace_bytes(int64_t B, int64_t T, int64_t D, int64_t E, int
   return carve(nullptr, B, T, E, dtype).total + 2 * act;
 }
 
-int rgk_recurrent_block_prefill(const void* x, const void* segment_pos, int pos_dtype,
-                                const rgk_block_params* p, int64_t B, int64_t T, int64_t D,
-                                int64_t E, int H, int W, int dtype, void* out, float* h_last,
-                                void* conv_cache_out, void* workspace, size_t workspace_bytes,
-                                void* stream) {
+// Validation and launches shared by the block entry points.  x_in is what linear_x / linear_y read
+// (the block input, or its RMSNorm), residual (may be NULL) is added to linear_out's result, `ws` is
+// a block workspace.
+static int block_prefill_impl(const void* x_in, const void* residual, const void* segment_pos,
+                              int pos_dtype, const rgk_block_params* p, int64_t B, int64_t T,
+                              int64_t D, int64_t E, int H, int dtype, void* out, float* h_last,
+                              void* conv_cache_out, void* workspace, cudaStream_t s) {
+  const PathWs w = carve(workspace, B, T, E, dtype);
+  const size_t act = up256(static_cast<size_t>(B) * T * E * elem_size(dtype));
+  char* xb = static_cast<char*>(workspace) + w.total;   // later reused for the joined output
+  char* yb = xb + act;
+  int* status = static_cast<int*>(workspace);
+  const int64_t M = B * T;
+  int rc;
+  // y branch with its gelu in the GEMM epilogue, x branch plain
+  RGK_CUDA(rgk::launch_dense_tc(x_in, p->linear_y_w, p->linear_y_b, nullptr, M, (int)D, (int)E, 1, yb,
+                                status, s),
+           "linear_y launch");
+  RGK_CUDA(rgk::launch_dense_tc(x_in, p->linear_x_w, p->linear_x_b, nullptr, M, (int)D, (int)E, 0, xb,
+                                status, s),
+           "linear_x launch");
+  RGK_CUDA(rgk::launch_conv1d_prefill(xb, segment_pos, pos_dtype, p->path.conv_w, p->path.conv_b, B,
+                                      T, E, dtype, w.c, conv_cache_out, s),
+           "conv1d_prefill launch");
+  // the conv has consumed xb: its buffer now receives y * gelu(yb)
+  if ((rc = run_rglru(w.c, segment_pos, pos_dtype, &p->path, nullptr, yb, 1, B, T, E, H, dtype,
+                      RGK_GATES_AUTO, w.wpack, w.a, w.xn, w.scan, xb, h_last, s)))
+    return rc;
+  RGK_CUDA(rgk::launch_dense_tc(xb, p->linear_out_w, p->linear_out_b, residual, M, (int)E, (int)D, 0,
+                                out, status, s),
+           "linear_out launch");
+  return RGK_OK;
+}
+
+static int check_block_args(const void* x, const void* segment_pos, int pos_dtype,
+                            const rgk_block_params* p, int64_t B, int64_t T, int64_t D, int64_t E,
+                            int H, int W, int dtype, const void* out, const float* h_last,
+                            const void* conv_cache_out) {
   int rc = check_common(B, T, E, dtype);
   if (rc) return rc;
   if ((rc = check_heads(E, H))) return rc;
@@ -447,6 +480,17 @@ int rgk_recurrent_block_prefill(const void* x, const void* segment_pos, int pos_
   RGK_REQUIRE(rgk::gates_tc_supported(dtype, bw, B * T > 0 ? B * T : 1), RGK_ESHAPE,
               "the fused block covers bfloat16 with head width 256 only (dtype %d, head width %d)",
               dtype, bw);
+  return RGK_OK;
+}
+
+int rgk_recurrent_block_prefill(const void* x, const void* segment_pos, int pos_dtype,
+                                const rgk_block_params* p, int64_t B, int64_t T, int64_t D,
+                                int64_t E, int H, int W, int dtype, void* out, float* h_last,
+                                void* conv_cache_out, void* workspace, size_t workspace_bytes,
+                                void* stream) {
+  int rc = check_block_args(x, segment_pos, pos_dtype, p, B, T, D, E, H, W, dtype, out, h_last,
+                            conv_cache_out);
+  if (rc) return rc;
   if (B * T * E == 0) return RGK_OK;
   const size_t need = rgk_block_workspace_bytes(B, T, D, E, dtype);
   RGK_REQUIRE(workspace != nullptr && workspace_bytes >= need, RGK_EWORKSPACE,
@@ -455,29 +499,61 @@ int rgk_recurrent_block_prefill(const void* x, const void* segment_pos, int pos_
               "workspace must be 256-byte aligned");
   RGK_CHECK_DEVICE();
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const PathWs w = carve(workspace, B, T, E, dtype);
-  const size_t act = up256(static_cast<size_t>(B) * T * E * elem_size(dtype));
-  char* xb = static_cast<char*>(workspace) + w.total;   // later reused for the joined output
-  char* yb = xb + act;
-  int* status = static_cast<int*>(workspace);
-  const int64_t M = B * T;
   RGK_CUDA(cudaMemsetAsync(workspace, 0, sizeof(int), s), "cudaMemsetAsync");
-  // y branch with its gelu in the GEMM epilogue, x branch plain
-  RGK_CUDA(rgk::launch_dense_tc(x, p->linear_y_w, p->linear_y_b, M, (int)D, (int)E, 1, yb, status, s),
-           "linear_y launch");
-  RGK_CUDA(rgk::launch_dense_tc(x, p->linear_x_w, p->linear_x_b, M, (int)D, (int)E, 0, xb, status, s),
-           "linear_x launch");
-  RGK_CUDA(rgk::launch_conv1d_prefill(xb, segment_pos, pos_dtype, p->path.conv_w, p->path.conv_b, B,
-                                      T, E, dtype, w.c, conv_cache_out, s),
-           "conv1d_prefill launch");
-  // the conv has consumed xb: its buffer now receives y * gelu(yb)
-  if ((rc = run_rglru(w.c, segment_pos, pos_dtype, &p->path, nullptr, yb, 1, B, T, E, H, dtype,
-                      RGK_GATES_AUTO, w.wpack, w.a, w.xn, w.scan, xb, h_last, s)))
-    return rc;
-  RGK_CUDA(rgk::launch_dense_tc(xb, p->linear_out_w, p->linear_out_b, M, (int)E, (int)D, 0, out,
-                                status, s),
-           "linear_out launch");
+  return block_prefill_impl(x, nullptr, segment_pos, pos_dtype, p, B, T, D, E, H, dtype, out, h_last,
+                            conv_cache_out, workspace, s);
+}
+
+int rgk_rmsnorm(const void* x, const void* scale, int64_t M, int64_t D, float eps, int dtype,
+                void* out, void* stream) {
+  RGK_REQUIRE(dtype == RGK_F32 || dtype == RGK_BF16, RGK_EINVAL, "unknown dtype %d", dtype);
+  RGK_REQUIRE(M >= 0 && D >= 1, RGK_EINVAL, "bad size (M=%lld D=%lld)", (long long)M, (long long)D);
+  RGK_REQUIRE(x && scale && out, RGK_EINVAL, "NULL pointer argument");
+  RGK_REQUIRE(aligned16(x) && aligned16(scale) && aligned16(out), RGK_EALIGN,
+              "pointers must be 16-byte aligned");
+  RGK_REQUIRE(rgk::rmsnorm_supported(dtype, D), RGK_ESHAPE,
+              "RMSNorm covers widths that are multiples of a 16-byte pack, up to 1024 packs "
+              "(dtype %d, D=%lld)", dtype, (long long)D);
+  if (M == 0) return RGK_OK;
+  RGK_CHECK_DEVICE();
+  RGK_CUDA(rgk::launch_rmsnorm(x, scale, M, D, eps, dtype, out, static_cast<cudaStream_t>(stream)),
+           "rmsnorm launch");
   return RGK_OK;
+}
+
+size_t rgk_residual_workspace_bytes(int64_t B, int64_t T, int64_t D, int64_t E, int dtype) {
+  const size_t block = rgk_block_workspace_bytes(B, T, D, E, dtype);
+  if (block == 0) return 0;
+  if (T < 1) T = 1;
+  return block + up256(static_cast<size_t>(B) * T * D * elem_size(dtype));
+}
+
+int rgk_residual_block_prefill(const void* x, const void* segment_pos, int pos_dtype,
+                               const rgk_block_params* p, const void* norm_scale, float eps,
+                               int64_t B, int64_t T, int64_t D, int64_t E, int H, int W, int dtype,
+                               void* out, float* h_last, void* conv_cache_out, void* workspace,
+                               size_t workspace_bytes, void* stream) {
+  int rc = check_block_args(x, segment_pos, pos_dtype, p, B, T, D, E, H, W, dtype, out, h_last,
+                            conv_cache_out);
+  if (rc) return rc;
+  RGK_REQUIRE(norm_scale != nullptr, RGK_EINVAL, "norm_scale is NULL");
+  RGK_REQUIRE(aligned16(norm_scale), RGK_EALIGN, "norm_scale must be 16-byte aligned");
+  RGK_REQUIRE(rgk::rmsnorm_supported(dtype, D), RGK_ESHAPE, "block width %lld is not covered by the "
+              "RMSNorm kernel", (long long)D);
+  if (B * T * E == 0) return RGK_OK;
+  const size_t block = rgk_block_workspace_bytes(B, T, D, E, dtype);
+  const size_t need = rgk_residual_workspace_bytes(B, T, D, E, dtype);
+  RGK_REQUIRE(workspace != nullptr && workspace_bytes >= need, RGK_EWORKSPACE,
+              "workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+  RGK_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255u) == 0, RGK_EALIGN,
+              "workspace must be 256-byte aligned");
+  RGK_CHECK_DEVICE();
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  RGK_CUDA(cudaMemsetAsync(workspace, 0, sizeof(int), s), "cudaMemsetAsync");
+  void* xn = static_cast<char*>(workspace) + block;      // temporal_pre_norm(x)
+  RGK_CUDA(rgk::launch_rmsnorm(x, norm_scale, B * T, D, eps, dtype, xn, s), "rmsnorm launch");
+  return block_prefill_impl(xn, x, segment_pos, pos_dtype, p, B, T, D, E, H, dtype, out, h_last,
+                            conv_cache_out, workspace, s);
 }
 
 int rgk_recurrent_path_decode(const void* xb, const void* yb, const void* segment_pos,

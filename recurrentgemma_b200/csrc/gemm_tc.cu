@@ -35,10 +35,11 @@ constexpr int kSmemG = kOffAbortG + 4 + 1024;
 static_assert(kSmemG <= 232448, "exceeds the 227 KiB of shared memory a CTA may use");
 constexpr uint32_t kIdescG = tc_idesc_bf16(BM, BN);
 
-template <bool kGelu>
+template <int kMode>   // 0: bias only, 1: gelu_tanh of the rounded result, 2: + residual (rounded again)
 __global__ void __launch_bounds__(kThreadsG, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-               const __nv_bfloat16* __restrict__ bias, int64_t M, int N, int K, int m_tiles,
+               const __nv_bfloat16* __restrict__ bias, const __nv_bfloat16* __restrict__ residual,
+               int64_t M, int N, int K, int m_tiles,
                int n_tiles, __nv_bfloat16* __restrict__ out, int* status) {
   extern __shared__ uint8_t smem_raw[];
   // aligned by an offset into the shared array, so that the address space stays known to the
@@ -138,6 +139,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         uint32_t acc[32];
         tc_ld_32x32(t_row + cc * 32, acc);
         const int nc = n0 + cc * 32;         // first output column of this chunk
+        // the residual pieces this thread will add after the transposition: in flight during the
+        // epilogue arithmetic
+        uint4 rv[4];
+        if constexpr (kMode == 2) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int64_t grow = m0 + lane_base + (lane >> 2) + 8 * k;
+            const int gcol = nc + (lane & 3) * 8;
+            rv[k] = (grow < M && gcol < N) ? ld_stream(residual + grow * N + gcol)
+                                           : make_uint4(0u, 0u, 0u, 0u);
+          }
+        }
         float bv[32];
 #pragma unroll
         for (int j = 0; j < 32; j += 2) {
@@ -155,7 +168,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             const int n = j * 8 + p * 2;
             float v0 = __uint_as_float(acc[n]) + bv[n], v1 = __uint_as_float(acc[n + 1]) + bv[n + 1];
             uint32_t pk = pack_bf16x2(v0, v1);
-            if constexpr (kGelu) pk = pack_bf16x2(gelu_tanh_<true>(bf16_lo(pk)), gelu_tanh_<true>(bf16_hi(pk)));
+            if constexpr (kMode == 1) pk = pack_bf16x2(gelu_tanh_<true>(bf16_lo(pk)), gelu_tanh_<true>(bf16_hi(pk)));
             o[p] = pk;
           }
           ov[j] = make_uint4(o[0], o[1], o[2], o[3]);
@@ -169,10 +182,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
           const int r = (lane >> 2) + 8 * k, piece = lane & 3;
-          const uint4 v = *reinterpret_cast<const uint4*>(stage + r * 64 + ((piece ^ ((r >> 1) & 3)) << 4));
+          uint4 v = *reinterpret_cast<const uint4*>(stage + r * 64 + ((piece ^ ((r >> 1) & 3)) << 4));
           const int64_t grow = m0 + lane_base + r;
           const int gcol = nc + piece * 8;
-          if (grow < M && gcol < N) *reinterpret_cast<uint4*>(out + grow * N + gcol) = v;
+          if (grow < M && gcol < N) {
+            if constexpr (kMode == 2) {
+              // the residual stream joins here: round(round(acc + bias) + residual), the two tensor
+              // operations of the reference (torch/modules.py:899-902)
+              v = make_uint4(badd2(v.x, rv[k].x), badd2(v.y, rv[k].y), badd2(v.z, rv[k].z),
+                             badd2(v.w, rv[k].w));
+            }
+            *reinterpret_cast<uint4*>(out + grow * N + gcol) = v;
+          }
         }
         __syncwarp();
       }
@@ -212,8 +233,9 @@ bool dense_tc_supported(int dtype, int64_t M, int64_t K, int64_t N) {
          N % 8 == 0 && K < (1 << 24) && N < (1 << 24);
 }
 
-cudaError_t launch_dense_tc(const void* x, const void* w, const void* bias, int64_t M, int K, int N,
-                            int gelu, void* out, int* status, cudaStream_t s) {
+cudaError_t launch_dense_tc(const void* x, const void* w, const void* bias, const void* residual,
+                            int64_t M, int K, int N, int gelu, void* out, int* status,
+                            cudaStream_t s) {
   if (M == 0) return cudaSuccess;
   CUtensorMap map_x, map_w;
   if (!make_kmajor_map(&map_x, x, (uint64_t)M, (uint64_t)K, BM) ||
@@ -224,19 +246,21 @@ cudaError_t launch_dense_tc(const void* x, const void* w, const void* bias, int6
     int dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
-    cudaFuncSetAttribute(gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemG);
-    cudaFuncSetAttribute(gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemG);
+    cudaFuncSetAttribute(gemm_tc_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemG);
+    cudaFuncSetAttribute(gemm_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemG);
+    cudaFuncSetAttribute(gemm_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemG);
   }
   const int m_tiles = (int)((M + BM - 1) / BM), n_tiles = (N + BN - 1) / BN;
   const int total = m_tiles * n_tiles;
   const int grid = total < num_sms ? total : num_sms;
   using T_ = __nv_bfloat16;
-  if (gelu)
-    gemm_tc_kernel<true><<<grid, kThreadsG, kSmemG, s>>>(map_x, map_w, (const T_*)bias, M, N, K,
-                                                        m_tiles, n_tiles, (T_*)out, status);
-  else
-    gemm_tc_kernel<false><<<grid, kThreadsG, kSmemG, s>>>(map_x, map_w, (const T_*)bias, M, N, K,
-                                                         m_tiles, n_tiles, (T_*)out, status);
+  if (gelu && residual) return cudaErrorInvalidValue;
+#define RGK_GEMM(MODE)                                                                          \
+  gemm_tc_kernel<MODE><<<grid, kThreadsG, kSmemG, s>>>(map_x, map_w, (const T_*)bias,           \
+                                                       (const T_*)residual, M, N, K, m_tiles,   \
+                                                       n_tiles, (T_*)out, status)
+  if (gelu) RGK_GEMM(1); else if (residual) RGK_GEMM(2); else RGK_GEMM(0);
+#undef RGK_GEMM
   return cudaGetLastError();
 }
 

@@ -61,11 +61,19 @@ cudaError_t launch_rglru_chan(const void* c, const void* pos, int pos64, const v
                               void* out, float* h_last, void* ws, cudaStream_t s);
 
 // gemm_tc.cu: out [M,N] = x [M,K] W[N,K]^T + bias (bfloat16, float32 accumulation) on tcgen05;
-// gelu != 0 applies gelu_tanh to the rounded result.  status: optional device int raised on a
-// bounded-wait timeout.
+// gelu != 0 applies gelu_tanh to the rounded result; residual != null adds a [M,N] tensor to the
+// rounded result and rounds again (not together with gelu).  status: optional device int raised on
+// a bounded-wait timeout.
 bool dense_tc_supported(int dtype, int64_t M, int64_t K, int64_t N);
-cudaError_t launch_dense_tc(const void* x, const void* w, const void* bias, int64_t M, int K, int N,
-                            int gelu, void* out, int* status, cudaStream_t s);
+cudaError_t launch_dense_tc(const void* x, const void* w, const void* bias, const void* residual,
+                            int64_t M, int K, int N, int gelu, void* out, int* status,
+                            cudaStream_t s);
+
+// rmsnorm.cu: out [M,D] = x * rsqrt(mean(x^2) + eps) * (scale + 1) with the reference's roundings
+// (torch/layers.py:65-73); one warp per row held in registers.
+bool rmsnorm_supported(int dtype, int64_t D);
+cudaError_t launch_rmsnorm(const void* x, const void* scale, int64_t M, int64_t D, float eps,
+                           int dtype, void* out, cudaStream_t s);
 
 // scan.cu
 size_t scan_workspace_bytes(int64_t B, int64_t T, int64_t E, int dtype);

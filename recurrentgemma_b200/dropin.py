@@ -8,10 +8,15 @@ Two ways, both leaving state_dict keys unchanged (recurrentgemma/torch/modules.p
     every recurrent block constructed afterwards is ours.
   * ``convert(model)`` after building (or loading) it: replaces each
     `model.blocks[i].recurrent_block` by a `RecurrentBlock` that shares the same parameters.
+  * ``fuse_temporal_residual(model)`` after ``convert``: each residual block with a recurrent block
+    computes `recurrent_block(temporal_pre_norm(x)) + x` (recurrentgemma/torch/modules.py:897-902)
+    through `modules.recurrent_residual`; its channel norm and MLP stay the reference's.
 
 The reference package is not a dependency of this library; it is imported only here, on request.
 """
 from __future__ import annotations
+
+import types
 
 import torch
 from torch import nn
@@ -48,4 +53,28 @@ def convert(model: nn.Module) -> nn.Module:
   for block in model.blocks:
     if hasattr(block, "recurrent_block"):
       block.recurrent_block = from_reference(block.recurrent_block)
+  return model
+
+
+def _residual_forward(self, x, segment_pos, cache=None, return_cache=True):
+  """ResidualBlock.forward (recurrentgemma/torch/modules.py:897-911) with the temporal half as one
+  library call."""
+  residual, cache = b200_modules.recurrent_residual(
+      x, segment_pos, self.temporal_pre_norm, self.recurrent_block, cache, return_cache)
+  x = self.channel_pre_norm(residual)
+  x = self.mlp_block(x)
+  return x + residual, cache
+
+
+def fuse_temporal_residual(model: nn.Module) -> nn.Module:
+  """For every converted recurrent residual block: `temporal_pre_norm` becomes a B200 `RMSNorm`
+  sharing the same parameter, and `forward` routes the temporal half through
+  `modules.recurrent_residual`.  state_dict keys are unchanged.  Returns the model."""
+  for block in model.blocks:
+    if isinstance(getattr(block, "recurrent_block", None), b200_modules.RecurrentBlock):
+      old = block.temporal_pre_norm
+      norm = b200_layers.RMSNorm(old.width, old.eps, device="meta", dtype=old.scale.dtype)
+      norm.load_state_dict(old.state_dict(), assign=True)
+      block.temporal_pre_norm = norm
+      block.forward = types.MethodType(_residual_forward, block)
   return model

@@ -53,6 +53,35 @@ def rnn_param_init(
   return tensor
 
 
+class RMSNorm(nn.Module):
+  """RMS norm over the last dimension (recurrentgemma/torch/layers.py:27-73): same constructor,
+  parameter name (`scale`, zero-initialised) and forward."""
+
+  def __init__(self, width: int, eps: float = 1e-6, device=None, dtype=None):
+    super().__init__()
+    self.width = width
+    self.eps = eps
+    self.scale = nn.Parameter(torch.empty([self.width], device=device, dtype=dtype))
+    self.reset_parameters()
+
+  def reset_parameters(self) -> None:
+    torch.nn.init.zeros_(self.scale)
+
+  @torch.no_grad()
+  def forward(self, x: torch.Tensor) -> torch.Tensor:
+    dev = _lib.require_cuda(x, self.scale)
+    _same_dtype(x, self.scale)
+    assert x.shape[-1] == self.width
+    xc = x.contiguous()
+    out = torch.empty_like(xc)
+    m = xc.numel() // self.width
+    with torch.cuda.device(dev):
+      _lib.check(_lib.load().rgk_rmsnorm(
+          xc.data_ptr(), self.scale.data_ptr(), m, self.width, float(self.eps),
+          _lib.dtype_code(x.dtype), out.data_ptr(), _lib.stream_ptr(dev)))
+    return out
+
+
 class BlockDiagonalLinear(nn.Module):
   """Block-diagonal linear layer: y[..., h, :] = x[..., h, :] @ w[h] + b[h]."""
 

@@ -144,9 +144,7 @@ class RecurrentBlock(nn.Module):
   ) -> Tuple[torch.Tensor, Optional[RecurrentBlockCache]]:
     """Returns (block output [B,T,width], updated cache or None)."""
     dev = _lib.require_cuda(x, segment_pos, self.linear_x.weight)
-    if (cache is None and x.dtype == torch.bfloat16 and self.lru_width // self.num_heads == 256
-        and self.conv1d_temporal_width == 4 and self.width % 8 == 0
-        and self.rg_lru.gates_impl != _lib.GATES_SIMT):
+    if self._fusable(x, cache):
       return self._forward_fused(x, segment_pos, return_cache, dev)
     yb = self.linear_y(x)
     xb = self.linear_x(x)
@@ -154,15 +152,19 @@ class RecurrentBlock(nn.Module):
                                   return_cache)
     return self.linear_out(z), new_cache
 
-  def _forward_fused(self, x, segment_pos, return_cache, dev):
+  def _forward_fused(self, x, segment_pos, return_cache, dev, norm=None):
     """Prefill of the whole block in one library call: the three projections on the tcgen05 GEMM
-    (gelu of the y branch in its epilogue), the RG-LRU + Conv1D sub-path in between."""
+    (gelu of the y branch in its epilogue), the RG-LRU + Conv1D sub-path in between.  With `norm`
+    (an RMSNorm) the call computes block(norm(x)) + x: the norm as its own kernel, the residual in
+    the epilogue of linear_out."""
     bs, l, d = x.shape
     e = self.lru_width
     params = [self.linear_y.weight, self.linear_y.bias, self.linear_x.weight, self.linear_x.bias,
               self.linear_out.weight, self.linear_out.bias, self.conv_1d.w, self.conv_1d.b,
               self.rg_lru.a_param, self.rg_lru.input_gate.w, self.rg_lru.input_gate.b,
               self.rg_lru.a_gate.w, self.rg_lru.a_gate.b]
+    if norm is not None:
+      params.append(norm.scale)
     layers._same_dtype(x, *params)
     pos = layers._pos(segment_pos, bs, l)
     xc = x.contiguous()
@@ -178,14 +180,27 @@ class RecurrentBlock(nn.Module):
         linear_out_b=self.linear_out.bias.data_ptr())
     with torch.cuda.device(dev):
       dt = _lib.dtype_code(x.dtype)
-      ws = _lib.workspace(dev, int(lib.rgk_block_workspace_bytes(bs, l, d, e, dt)))
-      _lib.check(lib.rgk_recurrent_block_prefill(
-          xc.data_ptr(), pos.data_ptr(), _lib.pos_code(pos), ctypes.byref(p), bs, l, d, e,
-          self.num_heads, 4, dt, out.data_ptr(), _lib.ptr(h_last), _lib.ptr(conv_state),
-          ws.data_ptr(), ws.numel(), _lib.stream_ptr(dev)))
+      if norm is None:
+        ws = _lib.workspace(dev, int(lib.rgk_block_workspace_bytes(bs, l, d, e, dt)))
+        _lib.check(lib.rgk_recurrent_block_prefill(
+            xc.data_ptr(), pos.data_ptr(), _lib.pos_code(pos), ctypes.byref(p), bs, l, d, e,
+            self.num_heads, 4, dt, out.data_ptr(), _lib.ptr(h_last), _lib.ptr(conv_state),
+            ws.data_ptr(), ws.numel(), _lib.stream_ptr(dev)))
+      else:
+        ws = _lib.workspace(dev, int(lib.rgk_residual_workspace_bytes(bs, l, d, e, dt)))
+        _lib.check(lib.rgk_residual_block_prefill(
+            xc.data_ptr(), pos.data_ptr(), _lib.pos_code(pos), ctypes.byref(p),
+            norm.scale.data_ptr(), float(norm.eps), bs, l, d, e, self.num_heads, 4, dt,
+            out.data_ptr(), _lib.ptr(h_last), _lib.ptr(conv_state), ws.data_ptr(), ws.numel(),
+            _lib.stream_ptr(dev)))
     if not return_cache:
       return out, None
     return out, RecurrentBlockCache(rg_lru_state=h_last, conv1d_state=conv_state)
+
+  def _fusable(self, x: torch.Tensor, cache) -> bool:
+    return (cache is None and x.dtype == torch.bfloat16
+            and self.lru_width // self.num_heads == 256 and self.conv1d_temporal_width == 4
+            and self.width % 8 == 0 and self.rg_lru.gates_impl != _lib.GATES_SIMT)
 
   @classmethod
   def init_cache(cls, batch_size: int, lru_width: int, dtype: torch.dtype,
@@ -198,3 +213,21 @@ class RecurrentBlock(nn.Module):
                                               conv1d_temporal_width=conv1d_temporal_width,
                                               device=device),
     )
+
+
+@torch.no_grad()
+def recurrent_residual(
+    x: torch.Tensor, segment_pos: torch.Tensor, temporal_pre_norm: layers.RMSNorm,
+    recurrent_block: RecurrentBlock, cache: Optional[RecurrentBlockCache] = None,
+    return_cache: bool = True,
+) -> Tuple[torch.Tensor, Optional[RecurrentBlockCache]]:
+  """The temporal half of ResidualBlock.forward for a recurrent block
+  (recurrentgemma/torch/modules.py:897-902): recurrent_block(temporal_pre_norm(x)) + x, with the
+  updated cache.  bfloat16 prefill with head width 256 runs as one library call (RMSNorm kernel,
+  the block's kernels, residual add in the epilogue of linear_out); other cases compose the
+  modules."""
+  dev = _lib.require_cuda(x, segment_pos, recurrent_block.linear_x.weight)
+  if recurrent_block._fusable(x, cache) and temporal_pre_norm.width == recurrent_block.width:
+    return recurrent_block._forward_fused(x, segment_pos, return_cache, dev, norm=temporal_pre_norm)
+  y, new_cache = recurrent_block(temporal_pre_norm(x), segment_pos, cache, return_cache)
+  return y + x, new_cache

@@ -19,7 +19,7 @@ import torch
 @dataclasses.dataclass(frozen=True)
 class Case:
   name: str
-  kind: str            # "blockdiag" | "conv1d" | "rglru" | "rnn_scan" | "block"
+  kind: str            # "blockdiag" | "conv1d" | "rglru" | "rnn_scan" | "block" | "rmsnorm" | "residual"
   dtype: str           # "float32" | "bfloat16"
   batch: int
   seq: int
@@ -131,7 +131,11 @@ def make_params(case: Case) -> Dict[str, torch.Tensor]:
       "conv_1d.w": normal(n, "conv_w", (w, e), math.sqrt(1.0 / w), dt),
       "conv_1d.b": normal(n, "conv_b", (e,), 0.2, dt),
   }
-  if case.kind == "block":
+  if case.kind == "rmsnorm":
+    return {"scale": normal(n, "norm_scale", (e,), 0.3, dt)}
+  if case.kind == "residual":
+    p["temporal_pre_norm.scale"] = normal(n, "norm_scale", (d,), 0.3, dt)
+  if case.kind in ("block", "residual"):
     p.update({
         "linear_y.weight": normal(n, "linear_y_w", (e, d), math.sqrt(1.0 / d), dt),
         "linear_y.bias": normal(n, "linear_y_b", (e,), 0.1, dt),
@@ -147,7 +151,7 @@ def make_inputs(case: Case) -> Dict[str, Optional[torch.Tensor]]:
   """Activations, positions, optional initial state and the decode-step tokens of a case."""
   dt = case.torch_dtype
   n = case.name
-  in_width = case.model_width if case.kind == "block" else case.lru_width
+  in_width = case.model_width if case.kind in ("block", "residual") else case.lru_width
   out: Dict[str, Optional[torch.Tensor]] = {
       "x": normal(n, "x", (case.batch, case.seq, in_width), 1.0, dt),
       "segment_pos": make_segment_pos(case.pos, case.batch, case.seq, n),
@@ -215,6 +219,15 @@ def golden_cases():
         _c(f"block_{s}_128_h1_l256_multi", "block", dt, 2, 67, 256, 1, width=128, pos="multi"),
         _c(f"block_{s}_256_h8_l256", "block", dt, 2, 64, 256, 8, width=256),
         _c(f"block_{s}_128_h2_l512_pad", "block", dt, 3, 21, 512, 2, width=128, pos="padded"),
+        # Row counts are multiples of 64 in the prefill form: ATen's CPU kernels round the
+        # bfloat16 rsqrt of RMSNorm once in their vectorised body (as CUDA does and as the oracle
+        # does) but twice (sqrt, then reciprocal) in the scalar loop that handles the last
+        # n mod 64 elements, so only full vector blocks pin the rounding model exactly.
+        _c(f"rmsnorm_{s}_128", "rmsnorm", dt, 2, 32, 128, decode_steps=0),
+        _c(f"rmsnorm_{s}_2560", "rmsnorm", dt, 4, 16, 2560, decode_steps=0),
+        _c(f"residual_{s}_128_h1_l256_multi", "residual", dt, 2, 64, 256, 1, width=128,
+           pos="multi"),
+        _c(f"residual_{s}_256_h2_l512", "residual", dt, 4, 48, 512, 2, width=256),
     ]
   return cases
 

@@ -87,6 +87,28 @@ def run_case(case: C.Case, layers, modules) -> dict:
         out[f"out_step{i}"] = _np(y)
         out[f"h_step{i}"] = _np(cache.rg_lru_state)
         out[f"cache_step{i}"] = _np(cache.conv1d_state)
+    elif case.kind == "rmsnorm":
+      m = layers.RMSNorm(case.lru_width, dtype=dt)
+      m.load_state_dict(p)
+      out["out"] = _np(m(inp["x"]))
+
+    elif case.kind == "residual":
+      # the temporal half of ResidualBlock.forward (modules.py:897-902) from its own parts:
+      # residual = recurrent_block(temporal_pre_norm(x)) + x
+      norm = layers.RMSNorm(case.model_width, dtype=dt)
+      norm.load_state_dict({"scale": p["temporal_pre_norm.scale"]})
+      m = modules.RecurrentBlock(case.model_width, case.heads, case.lru_width,
+                                 case.temporal_width, dtype=dt)
+      m.load_state_dict({k: v for k, v in p.items() if not k.startswith("temporal_pre_norm.")})
+      y, cache = m(norm(inp["x"]), pos)
+      out["out"] = _np(y + inp["x"])
+      out["h"], out["cache"] = _np(cache.rg_lru_state), _np(cache.conv1d_state)
+      for i in range(case.decode_steps):
+        xs = inp[f"x_step{i}"]
+        y, cache = m(norm(xs), C.decode_positions(case, pos, i), cache)
+        out[f"out_step{i}"] = _np(y + xs)
+        out[f"h_step{i}"] = _np(cache.rg_lru_state)
+        out[f"cache_step{i}"] = _np(cache.conv1d_state)
     else:
       raise ValueError(case.kind)
   return out
@@ -96,12 +118,16 @@ def main():
   ap = argparse.ArgumentParser()
   ap.add_argument("--reference", default=os.environ.get("RECURRENTGEMMA_REFERENCE", "reference"),
                   help="path of a recurrentgemma checkout")
+  ap.add_argument("--only-missing", action="store_true",
+                  help="leave fixtures that already exist untouched")
   args = ap.parse_args()
   _, layers, modules = import_reference(args.reference)
   total = 0
   for case in C.golden_cases():
-    res = run_case(case, layers, modules)
     path = os.path.join(HERE, case.name + ".npz")
+    if args.only_missing and os.path.exists(path):
+      continue
+    res = run_case(case, layers, modules)
     np.savez_compressed(path, **res)
     total += os.path.getsize(path)
     print(f"{case.name:44s} {os.path.getsize(path)/1024:8.1f} KiB")

@@ -56,6 +56,17 @@ def test_convert_keeps_state_dict_and_cache_layout(rg):
     assert a.shape == b.shape and a.dtype == b.dtype
   with pytest.raises(RuntimeError, match="no CPU path"):
     model(torch.zeros(1, 4, dtype=torch.long), torch.arange(4)[None])
+  # the temporal half of the residual blocks as one call: same keys, same parameter storage
+  from recurrentgemma_b200 import layers
+  model = dropin.fuse_temporal_residual(model)
+  after = model.state_dict()
+  assert sorted(after) == sorted(before)
+  for k in before:
+    assert torch.equal(before[k], after[k]), k
+  assert isinstance(model.blocks[0].temporal_pre_norm, layers.RMSNorm)
+  assert not isinstance(model.blocks[2].temporal_pre_norm, layers.RMSNorm)
+  with pytest.raises(RuntimeError, match="no CPU path"):
+    model(torch.zeros(1, 4, dtype=torch.long), torch.arange(4)[None])
 
 
 def test_install_rebinds_reference_names(rg):
@@ -79,6 +90,7 @@ def test_signatures_match_reference(rg):
   from recurrentgemma.torch import layers as ref_layers, modules as ref_modules
   from recurrentgemma_b200 import layers, modules
   pairs = [(ref_layers.RGLRU, layers.RGLRU), (ref_layers.Conv1D, layers.Conv1D),
+           (ref_layers.RMSNorm, layers.RMSNorm),
            (ref_layers.BlockDiagonalLinear, layers.BlockDiagonalLinear),
            (ref_modules.RecurrentBlock, modules.RecurrentBlock)]
   for ref_cls, our_cls in pairs:

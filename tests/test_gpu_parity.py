@@ -98,6 +98,24 @@ def test_golden(case, rg, oracle):
     assert none is None
     assert_close(y3, g["out"], tol, "return_cache=False")
 
+  elif case.kind == "rmsnorm":
+    m = rg.RMSNorm(case.lru_width, device=DEV, dtype=case.torch_dtype)
+    m.load_state_dict(p)
+    chk(m(ic["x"]), "out")
+
+  elif case.kind == "residual":
+    norm = rg.RMSNorm(case.model_width, device=DEV, dtype=case.torch_dtype)
+    norm.load_state_dict({"scale": p["temporal_pre_norm.scale"]})
+    m = _block(rg, case, {k: v for k, v in p.items() if not k.startswith("temporal_pre_norm.")})
+    y, cache = rg.recurrent_residual(ic["x"], pos, norm, m)
+    chk(y, "out"); chk(cache.rg_lru_state, "h"); chk(cache.conv1d_state, "cache")
+    for i in range(case.decode_steps):
+      y, cache = rg.recurrent_residual(ic[f"x_step{i}"],
+                                       C.decode_positions(case, inp["segment_pos"], i).to(DEV),
+                                       norm, m, cache)
+      chk(y, f"out_step{i}"); chk(cache.rg_lru_state, f"h_step{i}")
+      chk(cache.conv1d_state, f"cache_step{i}")
+
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
 @pytest.mark.parametrize("shape", [(2, 1031, 320), (1, 9000, 64), (3, 257, 72), (1, 5, 8),
@@ -425,3 +443,45 @@ def test_gate_kernel_repeatable_at_full_size(rg):
       ys.append(y.clone())
     for y in ys[1:]:
       assert_close(y, ys[0], 2e-3, f"run-to-run, gates_impl {impl}")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("shape", [(1, 8), (5, 136), (33, 2560), (7, 4096), (3, 8192)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_rmsnorm_vs_oracle(rg, oracle, dtype, shape):
+  """RMSNorm rows of every register-tile size of the kernel, against the oracle."""
+  m_rows, d = shape
+  if dtype == torch.float32 and d > 4096:
+    pytest.skip("float32 rows hold at most 1024 packs of 4")
+  name = f"rmsnorm_{m_rows}_{d}_{dtype}"
+  x = (C.normal(name, "x", (m_rows, d), 1.0) * C.uniform(name, "row", (m_rows, 1), 0.01, 30.0)).to(dtype)
+  sc = C.normal(name, "scale", (d,), 0.3, dtype)
+  norm = rg.RMSNorm(d, device=DEV, dtype=dtype)
+  norm.load_state_dict({"scale": sc})
+  assert_close(norm(x.to(DEV)), oracle.rmsnorm(x, sc), TOL[dtype], "rmsnorm")
+  with pytest.raises(Exception):
+    rg.RMSNorm(10, device=DEV, dtype=dtype)(torch.zeros(2, 10, device=DEV, dtype=dtype))
+
+
+def test_residual_fused_vs_composed_and_oracle(rg, oracle):
+  """recurrent_block(rmsnorm(x)) + x in one library call (RMSNorm kernel, residual in the epilogue
+  of linear_out) against the composition of the modules and against the oracle."""
+  case = C.Case("residual_fused", "residual", "bfloat16", 2, 300, 512, 2, width=384, pos="multi")
+  p = C.make_params(case)
+  inp = C.make_inputs(case)
+  dt = torch.bfloat16
+  norm = rg.RMSNorm(384, device=DEV, dtype=dt)
+  norm.load_state_dict({"scale": p["temporal_pre_norm.scale"]})
+  bp = {k: v for k, v in p.items() if not k.startswith("temporal_pre_norm.")}
+  m = _block(rg, case, bp)
+  x, pos = inp["x"].to(DEV), inp["segment_pos"].to(DEV)
+  y_f, c_f = rg.recurrent_residual(x, pos, norm, m)
+  y_b, c_b = m(norm(x), pos)
+  y_c = y_b + x
+  assert_close(y_f, y_c, 1e-6, "fused vs composed")
+  assert torch.equal(c_f.conv1d_state, c_b.conv1d_state)
+  y_r, h_r, c_r = oracle.residual_temporal(inp["x"], inp["segment_pos"],
+                                           p["temporal_pre_norm.scale"], oracle.params_of(bp))
+  assert_close(y_f, y_r, TOL[dt], "fused vs oracle")
+  assert_close(c_f.rg_lru_state, h_r, TOL[dt], "state")
+  assert_close(c_f.conv1d_state, c_r, TOL[dt], "conv state")

@@ -31,9 +31,13 @@ def test_oracle_matches_reference(case, oracle):
   pos = inp["segment_pos"]
   mism = []
 
-  def chk(out, key):
-    assert_close(out, g[key], tol, f"{case.name}:{key}")
-    mism.append(_frac_mismatch(out, g[key]))
+  def chk(out, key, loose=False):
+    # loose: decode steps of the residual cases, where the reference's CPU kernel rounds the
+    # bfloat16 rsqrt of RMSNorm twice (see tests/cases.py); the tolerance is the path's own.
+    assert_close(out, g[key], 2e-2 if loose and case.dtype == "bfloat16" else tol,
+                 f"{case.name}:{key}")
+    if not loose:
+      mism.append(_frac_mismatch(out, g[key]))
 
   if case.kind == "blockdiag":
     chk(oracle.blockdiag_linear(inp["x"], p["rg_lru.input_gate.w"], p["rg_lru.input_gate.b"]),
@@ -64,6 +68,17 @@ def test_oracle_matches_reference(case, oracle):
       y, h, cache = oracle.recurrent_block(inp[f"x_step{i}"], C.decode_positions(case, pos, i), op,
                                            h, cache)
       chk(y, f"out_step{i}"); chk(h, f"h_step{i}"); chk(cache, f"cache_step{i}")
+  elif case.kind == "rmsnorm":
+    chk(oracle.rmsnorm(inp["x"], p["scale"]), "out")
+  elif case.kind == "residual":
+    op = oracle.params_of(p)
+    ns = p["temporal_pre_norm.scale"]
+    y, h, cache = oracle.residual_temporal(inp["x"], pos, ns, op)
+    chk(y, "out"); chk(h, "h"); chk(cache, "cache")
+    for i in range(case.decode_steps):
+      y, h, cache = oracle.residual_temporal(inp[f"x_step{i}"], C.decode_positions(case, pos, i),
+                                             ns, op, h, cache)
+      chk(y, f"out_step{i}", True); chk(h, f"h_step{i}", True); chk(cache, f"cache_step{i}", True)
   # bfloat16: the rounding model must hold almost everywhere, not merely within tolerance.
   if case.dtype == "bfloat16":
     assert max(mism) < 0.03, f"{case.name}: {max(mism):.3%} of elements differ from the reference"
