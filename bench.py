@@ -381,7 +381,25 @@ def run_gpu(args, cfg):
     block_info["residual_ms"] = t_res
     block_info["rmsnorm_ms"] = t_norm
     block_info["rmsnorm_GB/s"] = 2 * b * t * e * 2 / (t_norm * 1e-3) / 1e9
-    del blk, x_in, norm
+    # ... and the channel half: mlp_block(channel_pre_norm(r)) + r with the 2B model's expanded
+    # width, i.e. the whole residual block of the recurrent kind.
+    xw = 3 * e
+    mlp = rg.MLPBlock(e, xw, device=dev, dtype=dt)
+    mlp.load_state_dict({
+        "ffw_up.w": (torch.randn((2, e, xw), generator=gb) * math.sqrt(1.0 / e)).to(dt).to(dev),
+        "ffw_up.b": torch.zeros((2, 1, 1, xw), dtype=dt, device=dev),
+        "ffw_down.weight": (torch.randn((e, xw), generator=gb) * math.sqrt(1.0 / xw)).to(dt).to(dev),
+        "ffw_down.bias": torch.zeros(e, dtype=dt, device=dev)})
+    for _ in range(2):
+      rg.residual_block(x_in, pos, norm, blk, norm, mlp)
+    torch.cuda.synchronize()
+    t_mlp = _time_loop(lambda: mlp(x_in, pre_norm=norm), ksteps, stream)
+    t_full = _time_loop(lambda: rg.residual_block(x_in, pos, norm, blk, norm, mlp), ksteps, stream)
+    block_info["mlp_channel_ms"] = t_mlp
+    block_info["mlp_TFLOP/s"] = 6 * b * t * e * xw / (t_mlp * 1e-3) / 1e12
+    block_info["residual_block_ms"] = t_full
+    block_info["residual_block_tokens_per_s"] = b * t / (t_full * 1e-3)
+    del blk, x_in, norm, mlp
   if rank != 0:
     if world > 1:
       dist.destroy_process_group()

@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define RGK_ABI_VERSION 3
+#define RGK_ABI_VERSION 4
 
 #if defined(__GNUC__)
 #define RGK_API __attribute__((visibility("default")))
@@ -260,6 +260,32 @@ RGK_API int rgk_residual_block_prefill(const void* x, const void* segment_pos, i
                                        int64_t B, int64_t T, int64_t D, int64_t E, int H, int W,
                                        int dtype, void* out, float* h_last, void* conv_cache_out,
                                        void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * MLPBlock.forward (recurrentgemma/torch/modules.py:740-752) and the channel half of
+ * ResidualBlock.forward (torch/modules.py:904-908), bfloat16:
+ *   mlp(x)   = ffw_down( gelu_tanh(x w_up[0] + b_up[0]) * (x w_up[1] + b_up[1]) )
+ *   channel  = mlp(RMSNorm(r; norm_scale)) + r
+ * ffw_up runs as ONE tcgen05 GEMM over weights packed gate/value-interleaved and K-major
+ * (rgk_pack_mlp_up: w_up [2, D, X] (in, out), b_up [2, X] -> rgk_mlp_pack_bytes(D, X) bytes, once
+ * per set of weights) whose epilogue forms gelu(gate) * value, so the [M, 2X] pre-activations never
+ * reach HBM; ffw_down is the dense GEMM with the optional residual [M, D] added in its epilogue.
+ * D a multiple of 8, X a multiple of 64; RGK_ESHAPE otherwise and for float32.
+ * workspace: rgk_mlp_workspace_bytes(M, D, X, dtype) bytes, 256-byte aligned (its first word is the
+ * status word of rgk_workspace_status).
+ * ---------------------------------------------------------------------------------------------- */
+RGK_API size_t rgk_mlp_pack_bytes(int64_t D, int64_t X);
+RGK_API int rgk_pack_mlp_up(const void* w_up, const void* b_up, int64_t D, int64_t X, int dtype,
+                            void* packed_out, void* stream);
+RGK_API size_t rgk_mlp_workspace_bytes(int64_t M, int64_t D, int64_t X, int dtype);
+RGK_API int rgk_mlp_block(const void* x, const void* packed_up, const void* down_w,
+                          const void* down_b, const void* residual, int64_t M, int64_t D, int64_t X,
+                          int dtype, void* out, void* workspace, size_t workspace_bytes,
+                          void* stream);
+RGK_API int rgk_residual_channel(const void* residual_in, const void* norm_scale, float eps,
+                                 const void* packed_up, const void* down_w, const void* down_b,
+                                 int64_t M, int64_t D, int64_t X, int dtype, void* out,
+                                 void* workspace, size_t workspace_bytes, void* stream);
 
 /* Scratch needed by the calls above for a problem of this size (an upper bound over the entry
  * points, so one buffer serves all of them).  Returns 0 on invalid arguments. */

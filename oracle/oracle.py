@@ -46,6 +46,8 @@ def lib() -> ctypes.CDLL:
     _lib.rgo_recurrent_path.restype = ctypes.c_int
     _lib.rgo_recurrent_block.restype = ctypes.c_int
     _lib.rgo_residual_temporal.restype = ctypes.c_int
+    _lib.rgo_mlp.restype = ctypes.c_int
+    _lib.rgo_residual_channel.restype = ctypes.c_int
   return _lib
 
 
@@ -262,6 +264,37 @@ def residual_temporal(
     raise RuntimeError(f"oracle residual_temporal failed ({rc})")
   cdt = x.dtype if conv_cache is None else conv_cache.dtype
   return _t(out, x.dtype), _t(h, torch.float32), _t(cc, cdt)
+
+
+def mlp(x: torch.Tensor, w_up: torch.Tensor, b_up: torch.Tensor, w_down: torch.Tensor,
+        b_down: torch.Tensor) -> torch.Tensor:
+  """MLPBlock.forward: w_up [2, D, X], b_up [2, 1, 1, X] (or [2, X]), w_down [D, X], b_down [D]."""
+  d = x.shape[-1]
+  m = x.numel() // d
+  xw = w_up.shape[-1]
+  out = _out(tuple(x.shape))
+  rc = lib().rgo_mlp(_p(_f(x)), _p(_f(w_up)), _p(_f(b_up.reshape(2, xw))), _p(_f(w_down)),
+                     _p(_f(b_down)), ctypes.c_int64(m), d, xw, _mode(x), _p(out))
+  if rc:
+    raise RuntimeError(f"oracle mlp failed ({rc})")
+  return _t(out, x.dtype)
+
+
+def residual_channel(residual: torch.Tensor, norm_scale: torch.Tensor, w_up: torch.Tensor,
+                     b_up: torch.Tensor, w_down: torch.Tensor, b_down: torch.Tensor,
+                     eps: float = 1e-6) -> torch.Tensor:
+  """mlp_block(channel_pre_norm(residual)) + residual."""
+  d = residual.shape[-1]
+  m = residual.numel() // d
+  xw = w_up.shape[-1]
+  out = _out(tuple(residual.shape))
+  rc = lib().rgo_residual_channel(
+      _p(_f(residual)), _p(_f(norm_scale)), ctypes.c_float(eps), _p(_f(w_up)),
+      _p(_f(b_up.reshape(2, xw))), _p(_f(w_down)), _p(_f(b_down)), ctypes.c_int64(m), d, xw,
+      _mode(residual), _p(out))
+  if rc:
+    raise RuntimeError(f"oracle residual_channel failed ({rc})")
+  return _t(out, residual.dtype)
 
 
 def params_of(state_dict: dict, prefix: str = "") -> dict:

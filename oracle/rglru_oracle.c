@@ -64,7 +64,7 @@ static inline float gelu_tanhf_(float z) {
   return 0.5f * z * (1.0f + tanhf(inner));
 }
 
-RGO_API int rgo_version(void) { return 2; }
+RGO_API int rgo_version(void) { return 3; }
 
 /* ---------------------------------------------------------------------------------------------
  * BlockDiagonalLinear.forward, layers.py:127-137.
@@ -431,6 +431,59 @@ RGO_API int rgo_residual_temporal(const float* x, const int64_t* segment_pos,
                                dt, out, h_last, conv_cache_out);
   if (rc == 0)
     for (int64_t i = 0; i < M * D; ++i) out[i] = rnd(out[i] + x[i], dt);
+  free(xn);
+  return rc;
+}
+
+/* ---------------------------------------------------------------------------------------------
+ * MLPBlock.forward, modules.py:740-752 with Einsum.forward, layers.py:700-703:
+ *   out_c = einsum("...td,cdD->c...tD", x, w)[c] + b[c]   (c = 0, 1; two tensor operations, so the
+ *           contraction is rounded before the bias is added and the sum is rounded again)
+ *   act   = gelu_tanh(out_0) * out_1
+ *   y     = ffw_down(act)  (nn.Linear: one rounding of accumulator + bias)
+ * x [M, D], w_up [2, D, X] (in, out), b_up [2, X], w_down [D, X] (nn.Linear layout), b_down [D].
+ * ------------------------------------------------------------------------------------------- */
+RGO_API int rgo_mlp(const float* x, const float* w_up, const float* b_up, const float* w_down,
+                    const float* b_down, int64_t M, int D, int X, int dt, float* out) {
+  float* act = (float*)malloc(sizeof(float) * (size_t)(M * X));
+  if (!act) return -1;
+#pragma omp parallel for schedule(static)
+  for (int64_t m = 0; m < M; ++m) {
+    float* acc = (float*)malloc(sizeof(float) * (size_t)(2 * X));
+    for (int j = 0; j < 2 * X; ++j) acc[j] = 0.0f;
+    const float* xr = x + m * D;
+    for (int k = 0; k < D; ++k) {
+      const float xv = xr[k];
+      const float* w0 = w_up + (int64_t)k * X;
+      const float* w1 = w_up + ((int64_t)D + k) * X;
+      for (int j = 0; j < X; ++j) { acc[j] += xv * w0[j]; acc[X + j] += xv * w1[j]; }
+    }
+    for (int j = 0; j < X; ++j) {
+      const float o0 = rnd(rnd(acc[j], dt) + b_up[j], dt);
+      const float o1 = rnd(rnd(acc[X + j], dt) + b_up[X + j], dt);
+      act[m * X + j] = rnd(rnd(gelu_tanhf_(o0), dt) * o1, dt);
+    }
+    free(acc);
+  }
+  rgo_linear(act, w_down, b_down, M, X, D, dt, out);
+  free(act);
+  return 0;
+}
+
+/* ---------------------------------------------------------------------------------------------
+ * The channel half of ResidualBlock.forward, modules.py:904-908:
+ *   out = mlp_block(channel_pre_norm(residual)) + residual
+ * ------------------------------------------------------------------------------------------- */
+RGO_API int rgo_residual_channel(const float* residual, const float* norm_scale, float eps,
+                                 const float* w_up, const float* b_up, const float* w_down,
+                                 const float* b_down, int64_t M, int D, int X, int dt,
+                                 float* out) {
+  float* xn = (float*)malloc(sizeof(float) * (size_t)(M * D));
+  if (!xn) return -1;
+  rgo_rmsnorm(residual, norm_scale, M, D, eps, dt, xn);
+  int rc = rgo_mlp(xn, w_up, b_up, w_down, b_down, M, D, X, dt, out);
+  if (rc == 0)
+    for (int64_t i = 0; i < M * D; ++i) out[i] = rnd(out[i] + residual[i], dt);
   free(xn);
   return rc;
 }

@@ -4,11 +4,14 @@ The public names mirror `recurrentgemma.torch` for the modules on that path; `dr
 into a reference `Griffin`.  Importing the package does not load the CUDA library; the first
 forward does, and raises if it has not been built.
 """
-from recurrentgemma_b200.layers import BlockDiagonalLinear, Conv1D, RGLRU, RMSNorm, rnn_scan
-from recurrentgemma_b200.modules import (RecurrentBlock, RecurrentBlockCache, dense_linear,
-                                         recurrent_path, recurrent_residual)
+from recurrentgemma_b200.layers import (BlockDiagonalLinear, Conv1D, Einsum, RGLRU, RMSNorm,
+                                        rnn_scan)
+from recurrentgemma_b200.modules import (MLPBlock, RecurrentBlock, RecurrentBlockCache,
+                                         dense_linear, recurrent_path, recurrent_residual,
+                                         residual_block)
 
 __all__ = [
-    "BlockDiagonalLinear", "Conv1D", "RGLRU", "RMSNorm", "rnn_scan", "RecurrentBlock",
-    "RecurrentBlockCache", "recurrent_path", "recurrent_residual", "dense_linear",
+    "BlockDiagonalLinear", "Conv1D", "Einsum", "RGLRU", "RMSNorm", "rnn_scan", "RecurrentBlock",
+    "RecurrentBlockCache", "MLPBlock", "recurrent_path", "recurrent_residual", "residual_block",
+    "dense_linear",
 ]

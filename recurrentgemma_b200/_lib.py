@@ -67,6 +67,12 @@ SIGNATURES = {
     "rgk_residual_block_prefill": (_int, [_vp, _vp, _int, ctypes.POINTER(RgkBlockParams), _vp,
                                           ctypes.c_float, _i64, _i64, _i64, _i64, _int, _int, _int,
                                           _vp, _vp, _vp, _vp, _sz, _vp]),
+    "rgk_mlp_pack_bytes": (_sz, [_i64, _i64]),
+    "rgk_pack_mlp_up": (_int, [_vp, _vp, _i64, _i64, _int, _vp, _vp]),
+    "rgk_mlp_workspace_bytes": (_sz, [_i64, _i64, _i64, _int]),
+    "rgk_mlp_block": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _vp, _sz, _vp]),
+    "rgk_residual_channel": (_int, [_vp, _vp, ctypes.c_float, _vp, _vp, _vp, _i64, _i64, _i64, _int,
+                                    _vp, _vp, _sz, _vp]),
     "rgk_workspace_bytes": (_sz, [_i64, _i64, _i64, _int]),
     "rgk_workspace_status": (_int, [_vp, _vp]),
 }
@@ -98,7 +104,7 @@ def load() -> ctypes.CDLL:
       fn = getattr(lib, name)
       fn.restype = res
       fn.argtypes = args
-    if lib.rgk_abi_version() != 3:
+    if lib.rgk_abi_version() != 4:
       raise RuntimeError("librgk.so has a different ABI version; rebuild it")
     _lib = lib
     return lib

@@ -556,6 +556,109 @@ int rgk_residual_block_prefill(const void* x, const void* segment_pos, int pos_d
                             conv_cache_out, workspace, s);
 }
 
+// ---- MLP block and the channel half of the residual block --------------------------------------
+
+static size_t mlp_pack_w_bytes(int64_t D, int64_t X) { return up256(static_cast<size_t>(2 * X) * D * 2); }
+
+size_t rgk_mlp_pack_bytes(int64_t D, int64_t X) {
+  if (D < 8 || X < 64 || D % 8 != 0 || X % 64 != 0) return 0;
+  return mlp_pack_w_bytes(D, X) + up256(static_cast<size_t>(2 * X) * 2);
+}
+
+int rgk_pack_mlp_up(const void* w, const void* b, int64_t D, int64_t X, int dtype, void* packed_out,
+                    void* stream) {
+  RGK_REQUIRE(dtype == RGK_BF16, RGK_ESHAPE, "the packed MLP weights are bfloat16 only (dtype %d)",
+              dtype);
+  RGK_REQUIRE(w && b && packed_out, RGK_EINVAL, "NULL pointer argument");
+  RGK_REQUIRE(D >= 8 && D % 8 == 0 && X >= 64 && X % 64 == 0 && D < (1 << 24) && X < (1 << 23),
+              RGK_ESHAPE, "the MLP kernels cover widths that are multiples of 8 and expanded widths "
+              "that are multiples of 64 (D=%lld, X=%lld)", (long long)D, (long long)X);
+  RGK_REQUIRE(aligned16(w) && aligned16(b) && aligned16(packed_out), RGK_EALIGN,
+              "pointers must be 16-byte aligned");
+  RGK_CHECK_DEVICE();
+  char* out = static_cast<char*>(packed_out);
+  RGK_CUDA(rgk::launch_pack_mlp_up(w, b, (int)D, (int)X, out, out + mlp_pack_w_bytes(D, X),
+                                   static_cast<cudaStream_t>(stream)),
+           "pack_mlp_up launch");
+  return RGK_OK;
+}
+
+size_t rgk_mlp_workspace_bytes(int64_t M, int64_t D, int64_t X, int dtype) {
+  if (M < 0 || D < 1 || X < 1 || dtype != RGK_BF16) return 0;
+  if (M < 1) M = 1;
+  return 256 + up256(static_cast<size_t>(M) * X * 2) + up256(static_cast<size_t>(M) * D * 2);
+}
+
+// out = ffw_down(gelu(up_0) * up_1) [+ residual]; x_in is the MLP's input.
+static int mlp_impl(const void* x_in, const void* packed_up, const void* down_w, const void* down_b,
+                    const void* residual, int64_t M, int64_t D, int64_t X, void* out,
+                    void* workspace, cudaStream_t s) {
+  int* status = static_cast<int*>(workspace);
+  char* act = static_cast<char*>(workspace) + 256;
+  const char* pw = static_cast<const char*>(packed_up);
+  RGK_CUDA(rgk::launch_dense_tc(x_in, pw, pw + mlp_pack_w_bytes(D, X), nullptr, M, (int)D,
+                                (int)(2 * X), 2, act, status, s),
+           "ffw_up launch");
+  RGK_CUDA(rgk::launch_dense_tc(act, down_w, down_b, residual, M, (int)X, (int)D, 0, out, status, s),
+           "ffw_down launch");
+  return RGK_OK;
+}
+
+static int check_mlp_args(const void* x, const void* packed_up, const void* down_w,
+                          const void* down_b, int64_t M, int64_t D, int64_t X, int dtype,
+                          const void* out, const void* workspace, size_t workspace_bytes) {
+  RGK_REQUIRE(dtype == RGK_BF16, RGK_ESHAPE, "the MLP kernels are bfloat16 only (dtype %d)", dtype);
+  RGK_REQUIRE(M >= 0 && M < ((int64_t)1 << 31), RGK_EINVAL, "bad row count %lld", (long long)M);
+  RGK_REQUIRE(D >= 8 && D % 8 == 0 && X >= 64 && X % 64 == 0 && D < (1 << 24) && X < (1 << 23),
+              RGK_ESHAPE, "the MLP kernels cover widths that are multiples of 8 and expanded widths "
+              "that are multiples of 64 (D=%lld, X=%lld)", (long long)D, (long long)X);
+  RGK_REQUIRE(x && packed_up && down_w && out, RGK_EINVAL, "NULL pointer argument");
+  RGK_REQUIRE(aligned16(x) && aligned16(packed_up) && aligned16(down_w) && aligned16(down_b) &&
+                  aligned16(out),
+              RGK_EALIGN, "pointers must be 16-byte aligned");
+  if (M == 0) return RGK_OK;
+  const size_t need = rgk_mlp_workspace_bytes(M, D, X, dtype);
+  RGK_REQUIRE(workspace != nullptr && workspace_bytes >= need, RGK_EWORKSPACE,
+              "workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+  RGK_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255u) == 0, RGK_EALIGN,
+              "workspace must be 256-byte aligned");
+  return RGK_OK;
+}
+
+int rgk_mlp_block(const void* x, const void* packed_up, const void* down_w, const void* down_b,
+                  const void* residual, int64_t M, int64_t D, int64_t X, int dtype, void* out,
+                  void* workspace, size_t workspace_bytes, void* stream) {
+  int rc = check_mlp_args(x, packed_up, down_w, down_b, M, D, X, dtype, out, workspace,
+                          workspace_bytes);
+  if (rc) return rc;
+  RGK_REQUIRE(aligned16(residual), RGK_EALIGN, "pointers must be 16-byte aligned");
+  if (M == 0) return RGK_OK;
+  RGK_CHECK_DEVICE();
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  RGK_CUDA(cudaMemsetAsync(workspace, 0, sizeof(int), s), "cudaMemsetAsync");
+  return mlp_impl(x, packed_up, down_w, down_b, residual, M, D, X, out, workspace, s);
+}
+
+int rgk_residual_channel(const void* residual_in, const void* norm_scale, float eps,
+                         const void* packed_up, const void* down_w, const void* down_b, int64_t M,
+                         int64_t D, int64_t X, int dtype, void* out, void* workspace,
+                         size_t workspace_bytes, void* stream) {
+  int rc = check_mlp_args(residual_in, packed_up, down_w, down_b, M, D, X, dtype, out, workspace,
+                          workspace_bytes);
+  if (rc) return rc;
+  RGK_REQUIRE(norm_scale != nullptr, RGK_EINVAL, "norm_scale is NULL");
+  RGK_REQUIRE(aligned16(norm_scale), RGK_EALIGN, "norm_scale must be 16-byte aligned");
+  RGK_REQUIRE(rgk::rmsnorm_supported(dtype, D), RGK_ESHAPE, "block width %lld is not covered by the "
+              "RMSNorm kernel", (long long)D);
+  if (M == 0) return RGK_OK;
+  RGK_CHECK_DEVICE();
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  RGK_CUDA(cudaMemsetAsync(workspace, 0, sizeof(int), s), "cudaMemsetAsync");
+  void* xn = static_cast<char*>(workspace) + 256 + up256(static_cast<size_t>(M) * X * 2);
+  RGK_CUDA(rgk::launch_rmsnorm(residual_in, norm_scale, M, D, eps, dtype, xn, s), "rmsnorm launch");
+  return mlp_impl(xn, packed_up, down_w, down_b, residual_in, M, D, X, out, workspace, s);
+}
+
 int rgk_recurrent_path_decode(const void* xb, const void* yb, const void* segment_pos,
                               int pos_dtype, const rgk_params* p, const float* h_in,
                               const void* conv_cache_in, int64_t B, int64_t E, int H, int W,

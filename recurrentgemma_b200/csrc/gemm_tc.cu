@@ -35,7 +35,12 @@ constexpr int kSmemG = kOffAbortG + 4 + 1024;
 static_assert(kSmemG <= 232448, "exceeds the 227 KiB of shared memory a CTA may use");
 constexpr uint32_t kIdescG = tc_idesc_bf16(BM, BN);
 
-template <int kMode>   // 0: bias only, 1: gelu_tanh of the rounded result, 2: + residual (rounded again)
+// kMode 0: bias only; 1: gelu_tanh of the rounded result; 2: + residual (rounded again);
+// 3: GeGLU - W holds, per group of 128 rows, 64 gate rows then the 64 value rows of the same
+//    features (see pack_mlp_up_kernel); out [M, N/2] = gelu_tanh(gate) * value, where gate and
+//    value are round(round(acc) + bias): the contraction and the bias add are two tensor operations
+//    in the reference (torch/layers.py:700-703, torch/modules.py:749-751).
+template <int kMode>
 __global__ void __launch_bounds__(kThreadsG, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                const __nv_bfloat16* __restrict__ bias, const __nv_bfloat16* __restrict__ residual,
@@ -134,6 +139,57 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       tc_fence_after();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lane_base) << 16) + as * BN +
                              col_half * 128;
+      if constexpr (kMode == 3) {
+        // this warp's 128 accumulator columns are one group: gate columns 0-63, value columns 64-127
+        const int n_out = N / 2;
+        const int oc0 = n0 / 2;                // first output feature of the group
+#pragma unroll 1
+        for (int cc = 0; cc < 2; ++cc) {       // 32 features at a time
+          uint4 ov[4];
+#pragma unroll
+          for (int hf = 0; hf < 2; ++hf) {     // 16 features: bounded register use
+            uint32_t ag[16], av[16];
+            tc_ld_32x16(t_row + cc * 32 + hf * 16, ag);
+            tc_ld_32x16(t_row + 64 + cc * 32 + hf * 16, av);
+            const int nb = n0 + cc * 32 + hf * 16;
+            uint4 bg[2], bvv[2];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              bg[j] = *reinterpret_cast<const uint4*>(bias + nb + 8 * j);
+              bvv[j] = *reinterpret_cast<const uint4*>(bias + nb + 64 + 8 * j);
+            }
+            tc_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              const uint32_t bgp[4] = {bg[j].x, bg[j].y, bg[j].z, bg[j].w};
+              const uint32_t bvp[4] = {bvv[j].x, bvv[j].y, bvv[j].z, bvv[j].w};
+              uint32_t o[4];
+#pragma unroll
+              for (int p = 0; p < 4; ++p) {
+                const int n = j * 8 + p * 2;
+                const uint32_t g2 = badd2(pack_bf16x2(__uint_as_float(ag[n]), __uint_as_float(ag[n + 1])), bgp[p]);
+                const uint32_t v2 = badd2(pack_bf16x2(__uint_as_float(av[n]), __uint_as_float(av[n + 1])), bvp[p]);
+                const uint32_t a2 = pack_bf16x2(gelu_tanh_<true>(bf16_lo(g2)), gelu_tanh_<true>(bf16_hi(g2)));
+                o[p] = bmul2(a2, v2);
+              }
+              ov[hf * 2 + j] = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            *reinterpret_cast<uint4*>(stage + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) = ov[j];
+          __syncwarp();
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int r = (lane >> 2) + 8 * k, piece = lane & 3;
+            const uint4 v = *reinterpret_cast<const uint4*>(stage + r * 64 + ((piece ^ ((r >> 1) & 3)) << 4));
+            const int64_t grow = m0 + lane_base + r;
+            const int gcol = oc0 + cc * 32 + piece * 8;
+            if (grow < M && gcol < n_out) *reinterpret_cast<uint4*>(out + grow * n_out + gcol) = v;
+          }
+          __syncwarp();
+        }
+      } else {
 #pragma unroll 1
       for (int cc = 0; cc < 4; ++cc) {
         uint32_t acc[32];
@@ -197,6 +253,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         }
         __syncwarp();
       }
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_acc_empty(as));
@@ -210,6 +267,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"(512)
                  : "memory");
+  }
+}
+
+// ffw_up of the MLP block: w [2, D, X] (in, out) and b [2, X] into the K-major, gate/value
+// interleaved layout of mode 3: packed row g*128 + c*64 + i = column (feature) g*64 + i of w[c].
+__global__ void pack_mlp_up_kernel(const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ b,
+                                   int D, int X, __nv_bfloat16* __restrict__ packed_w,
+                                   __nv_bfloat16* __restrict__ packed_b) {
+  __shared__ __nv_bfloat16 tile[32][33];
+  // grid: (D / 32 rounded up, X / 32, 2); block 32 x 8
+  const int c = blockIdx.z, k0 = blockIdx.x * 32, f0 = blockIdx.y * 32;
+  const __nv_bfloat16* src = w + (int64_t)c * D * X;
+  for (int r = threadIdx.y; r < 32; r += 8) {                      // r walks k, x walks features
+    const int k = k0 + r, f = f0 + threadIdx.x;
+    tile[r][threadIdx.x] = (k < D && f < X) ? src[(int64_t)k * X + f] : __float2bfloat16(0.0f);
+  }
+  __syncthreads();
+  for (int r = threadIdx.y; r < 32; r += 8) {                      // r walks features, x walks k
+    const int f = f0 + r, k = k0 + threadIdx.x;
+    if (f < X && k < D) {
+      const int64_t row = (int64_t)(f / 64) * 128 + c * 64 + (f % 64);
+      packed_w[row * D + k] = tile[threadIdx.x][r];
+      if (k == 0) packed_b[row] = b[(int64_t)c * X + f];
+    }
   }
 }
 
@@ -249,18 +330,28 @@ cudaError_t launch_dense_tc(const void* x, const void* w, const void* bias, cons
     cudaFuncSetAttribute(gemm_tc_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemG);
     cudaFuncSetAttribute(gemm_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemG);
     cudaFuncSetAttribute(gemm_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemG);
+    cudaFuncSetAttribute(gemm_tc_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemG);
   }
   const int m_tiles = (int)((M + BM - 1) / BM), n_tiles = (N + BN - 1) / BN;
   const int total = m_tiles * n_tiles;
   const int grid = total < num_sms ? total : num_sms;
   using T_ = __nv_bfloat16;
-  if (gelu && residual) return cudaErrorInvalidValue;
+  if ((gelu != 0) + (residual != nullptr) > 1) return cudaErrorInvalidValue;
 #define RGK_GEMM(MODE)                                                                          \
   gemm_tc_kernel<MODE><<<grid, kThreadsG, kSmemG, s>>>(map_x, map_w, (const T_*)bias,           \
                                                        (const T_*)residual, M, N, K, m_tiles,   \
                                                        n_tiles, (T_*)out, status)
-  if (gelu) RGK_GEMM(1); else if (residual) RGK_GEMM(2); else RGK_GEMM(0);
+  if (gelu == 2) RGK_GEMM(3); else if (gelu) RGK_GEMM(1); else if (residual) RGK_GEMM(2); else RGK_GEMM(0);
 #undef RGK_GEMM
+  return cudaGetLastError();
+}
+
+cudaError_t launch_pack_mlp_up(const void* w, const void* b, int D, int X, void* packed_w,
+                               void* packed_b, cudaStream_t s) {
+  using T_ = __nv_bfloat16;
+  const dim3 grid((unsigned)((D + 31) / 32), (unsigned)((X + 31) / 32), 2), block(32, 8);
+  pack_mlp_up_kernel<<<grid, block, 0, s>>>((const T_*)w, (const T_*)b, D, X, (T_*)packed_w,
+                                           (T_*)packed_b);
   return cudaGetLastError();
 }
 

@@ -61,13 +61,18 @@ cudaError_t launch_rglru_chan(const void* c, const void* pos, int pos64, const v
                               void* out, float* h_last, void* ws, cudaStream_t s);
 
 // gemm_tc.cu: out [M,N] = x [M,K] W[N,K]^T + bias (bfloat16, float32 accumulation) on tcgen05;
-// gelu != 0 applies gelu_tanh to the rounded result; residual != null adds a [M,N] tensor to the
-// rounded result and rounds again (not together with gelu).  status: optional device int raised on
+// gelu == 1 applies gelu_tanh to the rounded result; gelu == 2 is the GeGLU epilogue of the MLP
+// block (W and bias packed by launch_pack_mlp_up, N = 2 X, out [M, X]); residual != null adds a
+// [M,N] tensor to the rounded result and rounds again (not together with gelu).  status: optional device int raised on
 // a bounded-wait timeout.
 bool dense_tc_supported(int dtype, int64_t M, int64_t K, int64_t N);
 cudaError_t launch_dense_tc(const void* x, const void* w, const void* bias, const void* residual,
                             int64_t M, int K, int N, int gelu, void* out, int* status,
                             cudaStream_t s);
+
+// ffw_up.w [2, D, X], ffw_up.b [2, X] -> packed_w [2X, D], packed_b [2X] (gemm_tc.cu, mode 3).
+cudaError_t launch_pack_mlp_up(const void* w, const void* b, int D, int X, void* packed_w,
+                               void* packed_b, cudaStream_t s);
 
 // rmsnorm.cu: out [M,D] = x * rsqrt(mean(x^2) + eps) * (scale + 1) with the reference's roundings
 // (torch/layers.py:65-73); one warp per row held in registers.

@@ -11,6 +11,9 @@ Two ways, both leaving state_dict keys unchanged (recurrentgemma/torch/modules.p
   * ``fuse_temporal_residual(model)`` after ``convert``: each residual block with a recurrent block
     computes `recurrent_block(temporal_pre_norm(x)) + x` (recurrentgemma/torch/modules.py:897-902)
     through `modules.recurrent_residual`; its channel norm and MLP stay the reference's.
+  * ``fuse_residual_block(model)`` after ``convert``: the whole forward of those residual blocks
+    (recurrentgemma/torch/modules.py:897-911) runs on this library: both norms, the recurrent
+    block, the MLP and both residual adds.
 
 The reference package is not a dependency of this library; it is imported only here, on request.
 """
@@ -77,4 +80,33 @@ def fuse_temporal_residual(model: nn.Module) -> nn.Module:
       norm.load_state_dict(old.state_dict(), assign=True)
       block.temporal_pre_norm = norm
       block.forward = types.MethodType(_residual_forward, block)
+  return model
+
+
+def _share(new: nn.Module, old: nn.Module) -> nn.Module:
+  new.load_state_dict(old.state_dict(), assign=True)
+  return new
+
+
+def _full_residual_forward(self, x, segment_pos, cache=None, return_cache=True):
+  """ResidualBlock.forward (recurrentgemma/torch/modules.py:897-911), every step on this library."""
+  return b200_modules.residual_block(x, segment_pos, self.temporal_pre_norm, self.recurrent_block,
+                                     self.channel_pre_norm, self.mlp_block, cache, return_cache)
+
+
+def fuse_residual_block(model: nn.Module) -> nn.Module:
+  """For every converted recurrent residual block: both norms become B200 `RMSNorm`s and the MLP a
+  B200 `MLPBlock`, all sharing the existing parameters, and `forward` becomes
+  `modules.residual_block`.  state_dict keys are unchanged.  Returns the model."""
+  for block in model.blocks:
+    if isinstance(getattr(block, "recurrent_block", None), b200_modules.RecurrentBlock):
+      for name in ("temporal_pre_norm", "channel_pre_norm"):
+        old = getattr(block, name)
+        setattr(block, name, _share(
+            b200_layers.RMSNorm(old.width, old.eps, device="meta", dtype=old.scale.dtype), old))
+      old = block.mlp_block
+      block.mlp_block = _share(b200_modules.MLPBlock(
+          old.width, old.expanded_width, old.final_w_init_variance_scale, device="meta",
+          dtype=old.ffw_down.weight.dtype), old)
+      block.forward = types.MethodType(_full_residual_forward, block)
   return model

@@ -82,6 +82,36 @@ class RMSNorm(nn.Module):
     return out
 
 
+class Einsum(nn.Module):
+  """Einsum with a bias (recurrentgemma/torch/layers.py:653-703): same constructor and parameter
+  names (`w`, `b`).  Called on its own it is a library contraction; inside `modules.MLPBlock` its
+  parameters feed the packed tensor-core GEMM."""
+
+  def __init__(self, w_shape, b_shape, eqn: str, w_init_variance_scale: float = 1.0, device=None,
+               dtype=None):
+    super().__init__()
+    self.w_shape = tuple(w_shape)
+    self.b_shape = tuple(b_shape)
+    self.eqn = eqn
+    self.w_init_variance_scale = w_init_variance_scale
+    self.w = nn.Parameter(torch.empty(self.w_shape, device=device, dtype=dtype))
+    self.b = nn.Parameter(torch.empty(self.b_shape, device=device, dtype=dtype))
+    self.reset_parameters()
+
+  def reset_parameters(self) -> None:
+    self.w_init_(self.w)
+    torch.nn.init.zeros_(self.b)
+
+  def w_init_(self, w: torch.Tensor) -> None:
+    torch.nn.init.normal_(w, mean=0.0, std=math.sqrt(self.w_init_variance_scale / self.w_shape[1]))
+
+  @torch.no_grad()
+  def forward(self, x: torch.Tensor) -> torch.Tensor:
+    _lib.require_cuda(x, self.w)
+    _same_dtype(x, self.w, self.b)
+    return torch.einsum(self.eqn, x, self.w) + self.b
+
+
 class BlockDiagonalLinear(nn.Module):
   """Block-diagonal linear layer: y[..., h, :] = x[..., h, :] @ w[h] + b[h]."""
 

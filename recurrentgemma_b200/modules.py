@@ -231,3 +231,101 @@ def recurrent_residual(
     return recurrent_block._forward_fused(x, segment_pos, return_cache, dev, norm=temporal_pre_norm)
   y, new_cache = recurrent_block(temporal_pre_norm(x), segment_pos, cache, return_cache)
   return y + x, new_cache
+
+class MLPBlock(nn.Module):
+  """The gated MLP of a residual block (recurrentgemma/torch/modules.py:683-752): same constructor,
+  parameter names (`ffw_up.w [2, width, expanded]`, `ffw_up.b [2, 1, 1, expanded]`,
+  `ffw_down.weight/.bias`) and forward."""
+
+  def __init__(self, width: int, expanded_width: int, final_w_init_variance_scale: float = 1.0,
+               device=None, dtype=None):
+    super().__init__()
+    self.width = width
+    self.expanded_width = expanded_width
+    self.final_w_init_variance_scale = final_w_init_variance_scale
+    self.ffw_up = layers.Einsum(w_shape=(2, self.width, self.expanded_width),
+                                b_shape=(2, 1, 1, self.expanded_width), eqn="...td,cdD->c...tD",
+                                device=device, dtype=dtype)
+    self.ffw_down = nn.Linear(self.expanded_width, self.width, device=device, dtype=dtype)
+    self.reset_parameters()
+
+  def reset_parameters(self) -> None:
+    self.ffw_up.reset_parameters()
+    self.out_w_init_(self.ffw_down.weight)
+    torch.nn.init.zeros_(self.ffw_down.bias)
+
+  def out_w_init_(self, w: torch.Tensor) -> None:
+    torch.nn.init.normal_(w, mean=0.0,
+                          std=math.sqrt(self.final_w_init_variance_scale / self.expanded_width))
+
+  def _fusable(self, x: torch.Tensor) -> bool:
+    return (x.dtype == torch.bfloat16 and self.width % 8 == 0 and self.expanded_width % 64 == 0)
+
+  def _packed_up(self) -> int:
+    """Device pointer of the K-major, gate/value-interleaved copy of ffw_up the GeGLU GEMM reads,
+    rebuilt when either parameter is replaced or modified in place (derived, never in the
+    state_dict)."""
+    w, b = self.ffw_up.w, self.ffw_up.b
+    key = (w.data_ptr(), w._version, b.data_ptr(), b._version)
+    if getattr(self, "_pack_key", None) != key:
+      lib = _lib.load()
+      buf = torch.empty(int(lib.rgk_mlp_pack_bytes(self.width, self.expanded_width)),
+                        dtype=torch.uint8, device=w.device)
+      with torch.cuda.device(w.device):
+        _lib.check(lib.rgk_pack_mlp_up(w.data_ptr(), b.data_ptr(), self.width, self.expanded_width,
+                                       _lib.RGK_BF16, buf.data_ptr(), _lib.stream_ptr(w.device)))
+      self._pack_buf, self._pack_key = buf, key
+    return self._pack_buf.data_ptr()
+
+  @torch.no_grad()
+  def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None,
+              pre_norm: Optional[layers.RMSNorm] = None) -> torch.Tensor:
+    """ffw_down(gelu(up_0) * up_1).  The two optional arguments (not in the reference) select the
+    channel half of a residual block as one call: with `pre_norm` the MLP reads pre_norm(x) and
+    x is added to the result; with `residual` alone that tensor is added."""
+    dev = _lib.require_cuda(x, self.ffw_up.w)
+    params = [self.ffw_up.w, self.ffw_up.b, self.ffw_down.weight, self.ffw_down.bias]
+    if pre_norm is not None:
+      params.append(pre_norm.scale)
+    layers._same_dtype(x, *params)
+    assert x.shape[-1] == self.width
+    if not self._fusable(x):
+      xin = x if pre_norm is None else pre_norm(x)
+      out = self.ffw_up(xin)
+      y = self.ffw_down(torch.nn.functional.gelu(out[0], approximate="tanh") * out[1])
+      if pre_norm is not None:
+        return y + x
+      return y if residual is None else y + residual
+    xc = x.contiguous()
+    m = xc.numel() // self.width
+    out = torch.empty_like(xc)
+    lib = _lib.load()
+    dt = _lib.dtype_code(x.dtype)
+    with torch.cuda.device(dev):
+      ws = _lib.workspace(dev, int(lib.rgk_mlp_workspace_bytes(m, self.width, self.expanded_width, dt)))
+      if pre_norm is not None:
+        _lib.check(lib.rgk_residual_channel(
+            xc.data_ptr(), pre_norm.scale.data_ptr(), float(pre_norm.eps), self._packed_up(),
+            self.ffw_down.weight.data_ptr(), self.ffw_down.bias.data_ptr(), m, self.width,
+            self.expanded_width, dt, out.data_ptr(), ws.data_ptr(), ws.numel(),
+            _lib.stream_ptr(dev)))
+      else:
+        rc = None if residual is None else residual.contiguous()
+        _lib.check(lib.rgk_mlp_block(
+            xc.data_ptr(), self._packed_up(), self.ffw_down.weight.data_ptr(),
+            self.ffw_down.bias.data_ptr(), _lib.ptr(rc), m, self.width, self.expanded_width, dt,
+            out.data_ptr(), ws.data_ptr(), ws.numel(), _lib.stream_ptr(dev)))
+    return out
+
+
+@torch.no_grad()
+def residual_block(
+    x: torch.Tensor, segment_pos: torch.Tensor, temporal_pre_norm: layers.RMSNorm,
+    recurrent_block: RecurrentBlock, channel_pre_norm: layers.RMSNorm, mlp_block: MLPBlock,
+    cache: Optional[RecurrentBlockCache] = None, return_cache: bool = True,
+) -> Tuple[torch.Tensor, Optional[RecurrentBlockCache]]:
+  """ResidualBlock.forward for a recurrent block (recurrentgemma/torch/modules.py:897-911):
+  r = recurrent_block(temporal_pre_norm(x)) + x;  out = mlp_block(channel_pre_norm(r)) + r."""
+  r, new_cache = recurrent_residual(x, segment_pos, temporal_pre_norm, recurrent_block, cache,
+                                    return_cache)
+  return mlp_block(r, pre_norm=channel_pre_norm), new_cache

@@ -19,7 +19,7 @@ import torch
 @dataclasses.dataclass(frozen=True)
 class Case:
   name: str
-  kind: str            # "blockdiag" | "conv1d" | "rglru" | "rnn_scan" | "block" | "rmsnorm" | "residual"
+  kind: str            # "blockdiag" | "conv1d" | "rglru" | "rnn_scan" | "block" | "rmsnorm" | "residual" | "mlp" | "resblock"
   dtype: str           # "float32" | "bfloat16"
   batch: int
   seq: int
@@ -30,6 +30,7 @@ class Case:
   pos: str = "half"    # segment_pos pattern, see make_segment_pos
   with_h0: bool = False
   decode_steps: int = 2
+  expanded: int = 0    # mlp expanded width (kinds "mlp" and "resblock")
 
   @property
   def torch_dtype(self) -> torch.dtype:
@@ -133,16 +134,33 @@ def make_params(case: Case) -> Dict[str, torch.Tensor]:
   }
   if case.kind == "rmsnorm":
     return {"scale": normal(n, "norm_scale", (e,), 0.3, dt)}
-  if case.kind == "residual":
+  mlp = {}
+  if case.kind in ("mlp", "resblock"):
+    xw = case.expanded
+    mlp = {
+        "mlp_block.ffw_up.w": normal(n, "ffw_up_w", (2, d, xw), math.sqrt(1.0 / d), dt),
+        "mlp_block.ffw_up.b": normal(n, "ffw_up_b", (2, 1, 1, xw), 0.2, dt),
+        "mlp_block.ffw_down.weight": normal(n, "ffw_down_w", (d, xw), math.sqrt(1.0 / xw), dt),
+        "mlp_block.ffw_down.bias": normal(n, "ffw_down_b", (d,), 0.1, dt),
+    }
+  if case.kind == "mlp":
+    return mlp
+  if case.kind in ("residual", "resblock"):
     p["temporal_pre_norm.scale"] = normal(n, "norm_scale", (d,), 0.3, dt)
-  if case.kind in ("block", "residual"):
+  if case.kind == "resblock":
+    p["channel_pre_norm.scale"] = normal(n, "channel_norm_scale", (d,), 0.3, dt)
+    p.update(mlp)
+    p = {("recurrent_block." + k if k.split(".")[0] in ("rg_lru", "conv_1d") else k): v
+         for k, v in p.items()}
+  if case.kind in ("block", "residual", "resblock"):
+    pre = "recurrent_block." if case.kind == "resblock" else ""
     p.update({
-        "linear_y.weight": normal(n, "linear_y_w", (e, d), math.sqrt(1.0 / d), dt),
-        "linear_y.bias": normal(n, "linear_y_b", (e,), 0.1, dt),
-        "linear_x.weight": normal(n, "linear_x_w", (e, d), math.sqrt(1.0 / d), dt),
-        "linear_x.bias": normal(n, "linear_x_b", (e,), 0.1, dt),
-        "linear_out.weight": normal(n, "linear_out_w", (d, e), math.sqrt(1.0 / e), dt),
-        "linear_out.bias": normal(n, "linear_out_b", (d,), 0.1, dt),
+        pre + "linear_y.weight": normal(n, "linear_y_w", (e, d), math.sqrt(1.0 / d), dt),
+        pre + "linear_y.bias": normal(n, "linear_y_b", (e,), 0.1, dt),
+        pre + "linear_x.weight": normal(n, "linear_x_w", (e, d), math.sqrt(1.0 / d), dt),
+        pre + "linear_x.bias": normal(n, "linear_x_b", (e,), 0.1, dt),
+        pre + "linear_out.weight": normal(n, "linear_out_w", (d, e), math.sqrt(1.0 / e), dt),
+        pre + "linear_out.bias": normal(n, "linear_out_b", (d,), 0.1, dt),
     })
   return p
 
@@ -151,7 +169,8 @@ def make_inputs(case: Case) -> Dict[str, Optional[torch.Tensor]]:
   """Activations, positions, optional initial state and the decode-step tokens of a case."""
   dt = case.torch_dtype
   n = case.name
-  in_width = case.model_width if case.kind in ("block", "residual") else case.lru_width
+  in_width = (case.model_width if case.kind in ("block", "residual", "mlp", "resblock")
+              else case.lru_width)
   out: Dict[str, Optional[torch.Tensor]] = {
       "x": normal(n, "x", (case.batch, case.seq, in_width), 1.0, dt),
       "segment_pos": make_segment_pos(case.pos, case.batch, case.seq, n),
@@ -228,6 +247,11 @@ def golden_cases():
         _c(f"residual_{s}_128_h1_l256_multi", "residual", dt, 2, 64, 256, 1, width=128,
            pos="multi"),
         _c(f"residual_{s}_256_h2_l512", "residual", dt, 4, 48, 512, 2, width=256),
+        _c(f"mlp_{s}_128_x384", "mlp", dt, 2, 32, 128, width=128, expanded=384, decode_steps=0),
+        _c(f"mlp_{s}_256_x768", "mlp", dt, 2, 33, 256, width=256, expanded=768, decode_steps=0),
+        # a whole residual block of the recurrent kind (modules.py:897-911)
+        _c(f"resblock_{s}_128_h1_l256_x384", "resblock", dt, 2, 64, 256, 1, width=128,
+           expanded=384, pos="multi"),
     ]
   return cases
 

@@ -109,6 +109,26 @@ def run_case(case: C.Case, layers, modules) -> dict:
         out[f"out_step{i}"] = _np(y + xs)
         out[f"h_step{i}"] = _np(cache.rg_lru_state)
         out[f"cache_step{i}"] = _np(cache.conv1d_state)
+    elif case.kind == "mlp":
+      m = modules.MLPBlock(case.model_width, case.expanded, dtype=dt)
+      m.load_state_dict({k[len("mlp_block."):]: v for k, v in p.items()})
+      out["out"] = _np(m(inp["x"]))
+
+    elif case.kind == "resblock":
+      from recurrentgemma import common  # pylint: disable=import-outside-toplevel
+      m = modules.ResidualBlock(
+          width=case.model_width, mlp_expanded_width=case.expanded, num_heads=case.heads,
+          attention_window_size=16, temporal_block_type=common.TemporalBlockType.RECURRENT,
+          lru_width=case.lru_width, conv1d_temporal_width=case.temporal_width, dtype=dt)
+      m.load_state_dict(p)
+      y, cache = m(inp["x"], pos)
+      out["out"] = _np(y)
+      out["h"], out["cache"] = _np(cache.rg_lru_state), _np(cache.conv1d_state)
+      for i in range(case.decode_steps):
+        y, cache = m(inp[f"x_step{i}"], C.decode_positions(case, pos, i), cache)
+        out[f"out_step{i}"] = _np(y)
+        out[f"h_step{i}"] = _np(cache.rg_lru_state)
+        out[f"cache_step{i}"] = _np(cache.conv1d_state)
     else:
       raise ValueError(case.kind)
   return out

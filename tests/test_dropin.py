@@ -67,6 +67,17 @@ def test_convert_keeps_state_dict_and_cache_layout(rg):
   assert not isinstance(model.blocks[2].temporal_pre_norm, layers.RMSNorm)
   with pytest.raises(RuntimeError, match="no CPU path"):
     model(torch.zeros(1, 4, dtype=torch.long), torch.arange(4)[None])
+  # ... and the whole residual block
+  model = dropin.fuse_residual_block(model)
+  after = model.state_dict()
+  assert sorted(after) == sorted(before)
+  for k in before:
+    assert torch.equal(before[k], after[k]), k
+  assert isinstance(model.blocks[1].mlp_block, modules.MLPBlock)
+  assert isinstance(model.blocks[1].channel_pre_norm, layers.RMSNorm)
+  assert not isinstance(model.blocks[2].mlp_block, modules.MLPBlock)
+  with pytest.raises(RuntimeError, match="no CPU path"):
+    model(torch.zeros(1, 4, dtype=torch.long), torch.arange(4)[None])
 
 
 def test_install_rebinds_reference_names(rg):
@@ -90,7 +101,7 @@ def test_signatures_match_reference(rg):
   from recurrentgemma.torch import layers as ref_layers, modules as ref_modules
   from recurrentgemma_b200 import layers, modules
   pairs = [(ref_layers.RGLRU, layers.RGLRU), (ref_layers.Conv1D, layers.Conv1D),
-           (ref_layers.RMSNorm, layers.RMSNorm),
+           (ref_layers.RMSNorm, layers.RMSNorm), (ref_layers.Einsum, layers.Einsum),
            (ref_layers.BlockDiagonalLinear, layers.BlockDiagonalLinear),
            (ref_modules.RecurrentBlock, modules.RecurrentBlock)]
   for ref_cls, our_cls in pairs:
@@ -101,6 +112,11 @@ def test_signatures_match_reference(rg):
     if hasattr(ref_cls, "init_cache"):
       assert (list(inspect.signature(ref_cls.init_cache).parameters) ==
               list(inspect.signature(our_cls.init_cache).parameters)), ref_cls.__name__
+  # MLPBlock: same constructor; forward takes the reference's argument first (two optional
+  # extensions follow)
+  assert (list(inspect.signature(ref_modules.MLPBlock.__init__).parameters) ==
+          list(inspect.signature(modules.MLPBlock.__init__).parameters))
+  assert list(inspect.signature(modules.MLPBlock.forward).parameters)[:2] == ["self", "x"]
   ref_scan = list(inspect.signature(ref_layers.rnn_scan).parameters)
   our_scan = list(inspect.signature(layers.rnn_scan).parameters)
   assert our_scan[:len(ref_scan)] == ref_scan

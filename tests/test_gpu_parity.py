@@ -116,6 +116,31 @@ def test_golden(case, rg, oracle):
       chk(y, f"out_step{i}"); chk(cache.rg_lru_state, f"h_step{i}")
       chk(cache.conv1d_state, f"cache_step{i}")
 
+  elif case.kind == "mlp":
+    m = rg.MLPBlock(case.model_width, case.expanded, device=DEV, dtype=case.torch_dtype)
+    m.load_state_dict({k[len("mlp_block."):]: v for k, v in p.items()})
+    chk(m(ic["x"]), "out")
+
+  elif case.kind == "resblock":
+    dt = case.torch_dtype
+    tn = rg.RMSNorm(case.model_width, device=DEV, dtype=dt)
+    tn.load_state_dict({"scale": p["temporal_pre_norm.scale"]})
+    cn = rg.RMSNorm(case.model_width, device=DEV, dtype=dt)
+    cn.load_state_dict({"scale": p["channel_pre_norm.scale"]})
+    blk = _block(rg, case, {k[len("recurrent_block."):]: v for k, v in p.items()
+                            if k.startswith("recurrent_block.")})
+    mlp = rg.MLPBlock(case.model_width, case.expanded, device=DEV, dtype=dt)
+    mlp.load_state_dict({k[len("mlp_block."):]: v for k, v in p.items()
+                         if k.startswith("mlp_block.")})
+    y, cache = rg.residual_block(ic["x"], pos, tn, blk, cn, mlp)
+    chk(y, "out"); chk(cache.rg_lru_state, "h"); chk(cache.conv1d_state, "cache")
+    for i in range(case.decode_steps):
+      y, cache = rg.residual_block(ic[f"x_step{i}"],
+                                   C.decode_positions(case, inp["segment_pos"], i).to(DEV),
+                                   tn, blk, cn, mlp, cache)
+      chk(y, f"out_step{i}"); chk(cache.rg_lru_state, f"h_step{i}")
+      chk(cache.conv1d_state, f"cache_step{i}")
+
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
 @pytest.mark.parametrize("shape", [(2, 1031, 320), (1, 9000, 64), (3, 257, 72), (1, 5, 8),
@@ -485,3 +510,32 @@ def test_residual_fused_vs_composed_and_oracle(rg, oracle):
   assert_close(y_f, y_r, TOL[dt], "fused vs oracle")
   assert_close(c_f.rg_lru_state, h_r, TOL[dt], "state")
   assert_close(c_f.conv1d_state, c_r, TOL[dt], "conv state")
+
+
+@pytest.mark.parametrize("shape", [(1, 64, 64), (200, 256, 768), (300, 384, 7680), (129, 2560, 320)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_mlp_vs_oracle(rg, oracle, shape):
+  """The GeGLU GEMM (gate/value-interleaved packed weights, gelu(gate) * value in the epilogue) and
+  the down projection with the residual in its epilogue, against the oracle: partial row tiles,
+  expanded widths that end inside a 256-column tile, and many tiles."""
+  m_rows, d, xw = shape
+  dt = torch.bfloat16
+  case = C.Case(f"mlp_{m_rows}_{d}_{xw}", "mlp", "bfloat16", 1, m_rows, d, width=d, expanded=xw,
+                decode_steps=0)
+  p = C.make_params(case)
+  x = C.make_inputs(case)["x"][0]
+  mlp = rg.MLPBlock(d, xw, device=DEV, dtype=dt)
+  mlp.load_state_dict({k[len("mlp_block."):]: v for k, v in p.items()})
+  args = (p["mlp_block.ffw_up.w"], p["mlp_block.ffw_up.b"], p["mlp_block.ffw_down.weight"],
+          p["mlp_block.ffw_down.bias"])
+  assert_close(mlp(x.to(DEV)), oracle.mlp(x, *args), TOL[dt], "mlp")
+  sc = C.normal(case.name, "scale", (d,), 0.3, dt)
+  norm = rg.RMSNorm(d, device=DEV, dtype=dt)
+  norm.load_state_dict({"scale": sc})
+  assert_close(mlp(x.to(DEV), pre_norm=norm), oracle.residual_channel(x, sc, *args), TOL[dt],
+               "channel half")
+  # in-place modification of a parameter invalidates the packed copy
+  with torch.no_grad():
+    mlp.ffw_up.b.add_(1.0)
+  assert_close(mlp(x.to(DEV)), oracle.mlp(x, args[0], (args[1].float() + 1.0).to(dt), *args[2:]),
+               TOL[dt], "after bias update")

@@ -79,6 +79,20 @@ def test_oracle_matches_reference(case, oracle):
       y, h, cache = oracle.residual_temporal(inp[f"x_step{i}"], C.decode_positions(case, pos, i),
                                              ns, op, h, cache)
       chk(y, f"out_step{i}", True); chk(h, f"h_step{i}", True); chk(cache, f"cache_step{i}", True)
+  elif case.kind == "mlp":
+    chk(oracle.mlp(inp["x"], p["mlp_block.ffw_up.w"], p["mlp_block.ffw_up.b"],
+                   p["mlp_block.ffw_down.weight"], p["mlp_block.ffw_down.bias"]), "out")
+  elif case.kind == "resblock":
+    op = oracle.params_of(p, "recurrent_block.")
+    mlp = (p["channel_pre_norm.scale"], p["mlp_block.ffw_up.w"], p["mlp_block.ffw_up.b"],
+           p["mlp_block.ffw_down.weight"], p["mlp_block.ffw_down.bias"])
+    r, h, cache = oracle.residual_temporal(inp["x"], pos, p["temporal_pre_norm.scale"], op)
+    chk(oracle.residual_channel(r, *mlp), "out"); chk(h, "h"); chk(cache, "cache")
+    for i in range(case.decode_steps):
+      r, h, cache = oracle.residual_temporal(inp[f"x_step{i}"], C.decode_positions(case, pos, i),
+                                             p["temporal_pre_norm.scale"], op, h, cache)
+      chk(oracle.residual_channel(r, *mlp), f"out_step{i}", True)
+      chk(h, f"h_step{i}", True); chk(cache, f"cache_step{i}", True)
   # bfloat16: the rounding model must hold almost everywhere, not merely within tolerance.
   if case.dtype == "bfloat16":
     assert max(mism) < 0.03, f"{case.name}: {max(mism):.3%} of elements differ from the reference"
