@@ -430,6 +430,13 @@ def run_gpu(args, cfg):
       "kernels": {k: {"ms": round(v["ms"], 4), "GB/s": round(v["gbs"], 1),
                       "TFLOP/s": round(v["tflops"], 2)} for k, v in kernels.items()},
       "two_kernel_route": {k: round(v, 4) for k, v in two_kernel.items()},
+      # what actually bounds the fused kernel: special-function operations (4 ex2, 2 rcp, 1 sqrt per
+      # element; 16 per SM and clock) and instruction issue, see profiles/
+      "sfu": {"ops_per_element": 7, "achieved_Gops": 7 * b * t * e / (kernels["rglru_fused"]["ms"] * 1e-3) / 1e9
+              if "rglru_fused" in kernels else None,
+              "peak_Gops": 148 * 16 * 1.965, "unit": "G special-function ops/s",
+              "frac": (7 * b * t * e / (kernels["rglru_fused"]["ms"] * 1e-3) / 1e9) / (148 * 16 * 1.965)
+              if "rglru_fused" in kernels else None},
       "note": ("rglru_fused is bounded by the SFU and issue pipes (7 SFU operations and ~63 "
                "instructions per element with the reference's bfloat16 roundings), not by HBM; "
                "frac is its algorithmic bytes over its time against the measured copy bandwidth"),
@@ -656,7 +663,7 @@ def main():
   ap.add_argument("--seq", type=int, default=None, help="cfg3: sequence length (default 65536)")
   ap.add_argument("--gather", action="store_true", help="cfg3: all_gather the output every step")
   ap.add_argument("--gpus", type=int, default=1)
-  ap.add_argument("--steps", type=int, default=200)
+  ap.add_argument("--steps", type=int, default=600)
   ap.add_argument("--warmup", type=int, default=3)
   ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
   ap.add_argument("--batch", type=int, default=None, help="override the per-GPU batch (profiling)")
