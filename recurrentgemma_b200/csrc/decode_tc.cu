@@ -280,17 +280,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __nv_bfloat16*
   }
 }
 
-bool make_w_map(CUtensorMap* map, const void* packed, int H) {
-  EncodeTiledFn fn = tensor_map_encoder();
-  if (fn == nullptr) return false;
-  const cuuint64_t dims[2] = {256, (cuuint64_t)H * 2 * 256};
-  const cuuint64_t strides[1] = {512};
-  const cuuint32_t box[2] = {64, kChanCta};
-  const cuuint32_t estr[2] = {1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(packed), dims, strides, box,
-            estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
+
 
 }  // namespace
 
@@ -303,7 +293,8 @@ cudaError_t launch_path_decode_tc(const void* xb, const void* yb, const void* po
   if (B == 0) return cudaSuccess;
   using T_ = __nv_bfloat16;
   CUtensorMap map_w;
-  if (!make_w_map(&map_w, packed_w, H)) return cudaErrorInvalidValue;
+  if (!tensor_map_2d(&map_w, packed_w, (uint64_t)H * 2 * 256, 256, kChanCta, 64, true))
+    return cudaErrorInvalidValue;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(decode_tc_kernel<true>,

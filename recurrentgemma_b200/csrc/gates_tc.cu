@@ -295,18 +295,7 @@ __global__ void pack_gate_weights_kernel(const __nv_bfloat16* __restrict__ wx,
     dst[(int64_t)(n0 + r) * kHeadWidth + k0 + threadIdx.x] = tile[threadIdx.x][r];
 }
 
-// 2-D bfloat16 row-major tensor [rows, cols]; box = box_rows x 64 columns, 128-byte swizzle.
-bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
-  EncodeTiledFn fn = tensor_map_encoder();
-  if (fn == nullptr) return false;
-  const cuuint64_t dims[2] = {cols, rows};
-  const cuuint64_t strides[1] = {cols * 2};
-  const cuuint32_t box[2] = {kKSlice, box_rows};
-  const cuuint32_t estr[2] = {1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
-            estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
+
 
 }  // namespace
 
@@ -337,8 +326,8 @@ cudaError_t launch_gates_tc(const void* c, const void* pos, int pos64, const voi
   }
 
   CUtensorMap map_c, map_w;
-  if (!make_map(&map_c, c, (uint64_t)M, (uint64_t)E, kTileM) ||
-      !make_map(&map_w, packed_w, (uint64_t)H * 2 * kTileN, kHeadWidth, kTileN))
+  if (!tensor_map_2d(&map_c, c, (uint64_t)M, (uint64_t)E, kTileM, kKSlice, true) ||
+      !tensor_map_2d(&map_w, packed_w, (uint64_t)H * 2 * kTileN, kHeadWidth, kTileN, kKSlice, true))
     return cudaErrorInvalidValue;
 
   static int num_sms = 0;

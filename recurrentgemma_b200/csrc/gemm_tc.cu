@@ -294,18 +294,7 @@ __global__ void pack_mlp_up_kernel(const __nv_bfloat16* __restrict__ w, const __
   }
 }
 
-bool make_kmajor_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
-                     uint32_t box_rows) {
-  EncodeTiledFn fn = tensor_map_encoder();
-  if (fn == nullptr) return false;
-  const cuuint64_t dims[2] = {cols, rows};
-  const cuuint64_t strides[1] = {cols * 2};
-  const cuuint32_t box[2] = {BK, box_rows};
-  const cuuint32_t estr[2] = {1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
-            estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
+
 
 }  // namespace
 
@@ -319,8 +308,8 @@ cudaError_t launch_dense_tc(const void* x, const void* w, const void* bias, cons
                             cudaStream_t s) {
   if (M == 0) return cudaSuccess;
   CUtensorMap map_x, map_w;
-  if (!make_kmajor_map(&map_x, x, (uint64_t)M, (uint64_t)K, BM) ||
-      !make_kmajor_map(&map_w, w, (uint64_t)N, (uint64_t)K, BN))
+  if (!tensor_map_2d(&map_x, x, (uint64_t)M, (uint64_t)K, BM, BK, true) ||
+      !tensor_map_2d(&map_w, w, (uint64_t)N, (uint64_t)K, BN, BK, true))
     return cudaErrorInvalidValue;
   static int num_sms = 0;
   if (num_sms == 0) {

@@ -181,7 +181,7 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
         const int b = rem / groups, grp = rem - b * groups;
         for (int kb = 0; kb < kKBlocks; ++kb, ++it) {
           const int s = it % kRing;
-          ok = mbar_wait_relaxed(bar_empty(s), ((it / kRing) & 1) ^ 1, s_abort);
+          ok = mbar_wait(bar_empty(s), ((it / kRing) & 1) ^ 1, s_abort);
           if (!ok) break;
           mbar_expect_tx(bar_full(s), kStage);
           tma_load_3d(s_base + kOffRing + s * kStage, &map_c, (grp >> 1) * kHW + kb * kKB, tt * kUT, b,
@@ -198,12 +198,12 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
       bool ok = true;
       for (int t = 0; t < n_my && ok; ++t) {
         const int as = t & 1;
-        ok = mbar_wait_relaxed(bar_acc_empty(as), ((t >> 1) & 1) ^ 1, s_abort);
+        ok = mbar_wait(bar_acc_empty(as), ((t >> 1) & 1) ^ 1, s_abort);
         if (!ok) break;
         tc_fence_after();
         for (int kb = 0; kb < kKBlocks; ++kb, ++it) {
           const int s = it % kRing;
-          ok = mbar_wait_relaxed(bar_full(s), (it / kRing) & 1, s_abort);
+          ok = mbar_wait(bar_full(s), (it / kRing) & 1, s_abort);
           if (!ok) break;
           tc_fence_after();
           const uint32_t c0 = s_base + kOffRing + s * kStage, w0 = c0 + kCBytes;
@@ -514,37 +514,11 @@ __global__ void m8sp_chan_kernel(const __nv_bfloat16* __restrict__ a_param, int 
 }
 
 // Tensor map of a row-major bfloat16 matrix [rows, cols] with boxes of box_rows x box_cols.
-bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
-              uint32_t box_cols, bool swizzle128) {
-  EncodeTiledFn fn = tensor_map_encoder();
-  if (fn == nullptr) return false;
-  const cuuint64_t dims[2] = {cols, rows};
-  const cuuint64_t strides[1] = {cols * 2};
-  const cuuint32_t box[2] = {box_cols, box_rows};
-  const cuuint32_t estr[2] = {1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
-            estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
-            swizzle128 ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
+
 
 // Tensor map of bfloat16 activations [B, T, E] with boxes of box_rows tokens x box_cols channels of
 // one sequence: rows past the end of a sequence read as zero and are dropped from stores.
-bool make_map_bte(CUtensorMap* map, const void* base, uint64_t B, uint64_t T, uint64_t E,
-                  uint32_t box_rows, uint32_t box_cols, bool swizzle128) {
-  EncodeTiledFn fn = tensor_map_encoder();
-  if (fn == nullptr) return false;
-  const cuuint64_t dims[3] = {E, T, B};
-  const cuuint64_t strides[2] = {E * 2, T * E * 2};
-  const cuuint32_t box[3] = {box_cols, box_rows, 1};
-  const cuuint32_t estr[3] = {1, 1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box,
-            estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
-            swizzle128 ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
+
 
 struct ChanLayout {
   int64_t n_units, n_rec;
@@ -593,11 +567,11 @@ cudaError_t launch_rglru_chan(const void* c, const void* pos, int pos64, const v
 
   CUtensorMap map_c, map_w, map_ct, map_yt, map_ot;
   const uint64_t Bu = (uint64_t)B, Tu = (uint64_t)T, Eu = (uint64_t)E;
-  if (!make_map_bte(&map_c, c, Bu, Tu, Eu, kUT, kKB, true) ||
-      !make_map(&map_w, packed_w, (uint64_t)H * 4 * kUC, kHW, 2 * kUC, kKB, true) ||
-      !make_map_bte(&map_ct, c, Bu, Tu, Eu, kSub, kSub, false) ||
-      !make_map_bte(&map_ot, out, Bu, Tu, Eu, kSub, kSub, false) ||
-      !make_map_bte(&map_yt, yb != nullptr ? yb : out, Bu, Tu, Eu, kSub, kSub, false))
+  if (!tensor_map_bte(&map_c, c, Bu, Tu, Eu, kUT, kKB, true) ||
+      !tensor_map_2d(&map_w, packed_w, (uint64_t)H * 4 * kUC, kHW, 2 * kUC, kKB, true) ||
+      !tensor_map_bte(&map_ct, c, Bu, Tu, Eu, kSub, kSub, false) ||
+      !tensor_map_bte(&map_ot, out, Bu, Tu, Eu, kSub, kSub, false) ||
+      !tensor_map_bte(&map_yt, yb != nullptr ? yb : out, Bu, Tu, Eu, kSub, kSub, false))
     return cudaErrorInvalidValue;
   static int num_sms = 0;
   if (num_sms == 0) {

@@ -379,22 +379,6 @@ scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
   }
 }
 
-// 3-D tensor map over [B, T, E] with a box of kRows x 64 channels of one batch row.
-template <typename T>
-bool make_scan_map(CUtensorMap* map, const void* base, int64_t B, int64_t T_, int64_t E) {
-  EncodeTiledFn fn = tensor_map_encoder();
-  if (fn == nullptr) return false;
-  const cuuint64_t dims[3] = {(cuuint64_t)E, (cuuint64_t)T_, (cuuint64_t)B};
-  const cuuint64_t strides[2] = {(cuuint64_t)E * sizeof(T), (cuuint64_t)T_ * E * sizeof(T)};
-  const cuuint32_t box[3] = {kChan, (cuuint32_t)ScanCfg<T>::kRows, 1};
-  const cuuint32_t estr[3] = {1, 1, 1};
-  const CUtensorMapDataType dt = sizeof(T) == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
-                                                : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
-  return fn(map, dt, 3, const_cast<void*>(base), dims, strides, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
-            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 template <typename T, int kJoin>
 cudaError_t launch_scan_typed(const void* x, const void* a, const uint8_t* reset, const void* pos,
                               int pos64, const float* h0, const void* y_mul, int64_t B, int64_t T_,
@@ -402,7 +386,10 @@ cudaError_t launch_scan_typed(const void* x, const void* a, const uint8_t* reset
                               float* h_last, WsHeader* hdr, unsigned* flags, float2* agg, float* incl,
                               cudaStream_t s) {
   CUtensorMap map_x, map_a;
-  if (!make_scan_map<T>(&map_x, x, B, T_, E) || !make_scan_map<T>(&map_a, a, B, T_, E))
+  if (!tensor_map_bte(&map_x, x, (uint64_t)B, (uint64_t)T_, (uint64_t)E, ScanCfg<T>::kRows, kChan, false,
+                      (int)sizeof(T)) ||
+      !tensor_map_bte(&map_a, a, (uint64_t)B, (uint64_t)T_, (uint64_t)E, ScanCfg<T>::kRows, kChan, false,
+                      (int)sizeof(T)))
     return cudaErrorInvalidValue;
   static bool attr_set = false;
   if (!attr_set) {

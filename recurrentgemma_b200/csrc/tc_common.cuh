@@ -24,13 +24,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   return false;
 }
 
-// The same for a single-thread role whose waits are long (a producer waiting for a free stage, an
-// MMA issuer waiting for operands).
-__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity,
-                                                  volatile int* abort_flag) {
-  return mbar_wait(bar, parity, abort_flag);
-}
-
 __device__ __forceinline__ void tc_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 }
@@ -176,10 +169,6 @@ __device__ __forceinline__ float ld_cg_f32(const float* p) {
 __device__ __forceinline__ void named_bar_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" :: "r"(id), "r"(threads) : "memory");
 }
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y, uint32_t src) {
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
-               :: "l"(map), "r"(x), "r"(y), "r"(src) : "memory");
-}
 __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, int x, int y, int z, uint32_t src) {
   asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];"
                :: "l"(map), "r"(x), "r"(y), "r"(z), "r"(src) : "memory");
@@ -187,10 +176,6 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, int x, int 
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_read() {
   asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-}
-// waits until all but the most recent bulk group of this thread have read their source
-__device__ __forceinline__ void bulk_wait_read_1() {
-  asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
 }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async() {
@@ -234,94 +219,5 @@ __device__ __forceinline__ void gate_tokens(float zx0, float zx1, float za0, flo
   mult2 = pack_bf16x2(sqrtf_approx(bf16_lo(om2)), sqrtf_approx(bf16_hi(om2)));
 }
 
-// gelu_tanh of 16 values in place, stage by stage (see gelu_fast_f).
-__device__ __forceinline__ void gelu_fast_x16(float (&z)[16]) {
-  constexpr float k0 = -1.5957691216057308f * 1.4426950408889634f;
-  constexpr float k1 = k0 * 0.044715f;
-  float w[16];
-#pragma unroll
-  for (int i = 0; i < 16; ++i) w[i] = z[i] * z[i];
-#pragma unroll
-  for (int i = 0; i < 16; ++i) w[i] = fmaf(w[i], k1, k0);
-#pragma unroll
-  for (int i = 0; i < 16; ++i) w[i] *= z[i];
-#pragma unroll
-  for (int i = 0; i < 16; ++i) w[i] = ex2f(w[i]);
-#pragma unroll
-  for (int i = 0; i < 16; ++i) w[i] += 1.0f;
-#pragma unroll
-  for (int i = 0; i < 16; ++i) w[i] = rcpf(w[i]);
-#pragma unroll
-  for (int i = 0; i < 16; ++i) z[i] *= w[i];
-}
-
-// The same arithmetic for 16 consecutive tokens of one channel (8 token pairs), written stage by
-// stage over all pairs: every instruction is followed by seven independent ones, so a warp that
-// runs alone on its scheduler still fills the pipelines.
-__device__ __forceinline__ void gate_tokens_x8(const uint32_t (&zx)[16], const uint32_t (&za)[16],
-                                               uint32_t bx2, uint32_t ba2, uint32_t m8sp2,
-                                               uint32_t (&a2)[8], uint32_t (&gx2)[8],
-                                               uint32_t (&mult2)[8]) {
-  constexpr float kNegLog2e = -1.4426950408889634f;
-  constexpr float kLog2e = 1.4426950408889634f;
-  constexpr uint32_t kFloor = 0xc226c226u;     // -41.5: keeps the product of two denominators finite
-  uint32_t zx2[8], za2[8];
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    zx2[j] = pack_bf16x2(__uint_as_float(zx[2 * j]), __uint_as_float(zx[2 * j + 1]));
-    za2[j] = pack_bf16x2(__uint_as_float(za[2 * j]), __uint_as_float(za[2 * j + 1]));
-  }
-#pragma unroll
-  for (int j = 0; j < 8; ++j) { zx2[j] = badd2(zx2[j], bx2); za2[j] = badd2(za2[j], ba2); }
-#pragma unroll
-  for (int j = 0; j < 8; ++j) { zx2[j] = bmax2(zx2[j], kFloor); za2[j] = bmax2(za2[j], kFloor); }
-  float dx[16], da[16];
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    dx[2 * j] = bf16_lo(zx2[j]) * kNegLog2e;
-    dx[2 * j + 1] = bf16_hi(zx2[j]) * kNegLog2e;
-    da[2 * j] = bf16_lo(za2[j]) * kNegLog2e;
-    da[2 * j + 1] = bf16_hi(za2[j]) * kNegLog2e;
-  }
-#pragma unroll
-  for (int i = 0; i < 16; ++i) { dx[i] = ex2f(dx[i]); da[i] = ex2f(da[i]); }
-#pragma unroll
-  for (int i = 0; i < 16; ++i) { dx[i] += 1.0f; da[i] += 1.0f; }
-  float r[16];
-#pragma unroll
-  for (int i = 0; i < 16; ++i) r[i] = dx[i] * da[i];
-#pragma unroll
-  for (int i = 0; i < 16; ++i) r[i] = rcpf(r[i]);
-#pragma unroll
-  for (int i = 0; i < 16; ++i) { da[i] *= r[i]; dx[i] *= r[i]; }   // da: x-gate, dx: a-gate
-  uint32_t la2[8];
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    gx2[j] = pack_bf16x2(da[2 * j], da[2 * j + 1]);
-    la2[j] = pack_bf16x2(dx[2 * j], dx[2 * j + 1]);
-  }
-  // log_a = (-8 gate_a) softplus(a_param): -8 is exact in bfloat16 and folded into the constant
-#pragma unroll
-  for (int j = 0; j < 8; ++j) la2[j] = bmul2(la2[j], m8sp2);
-  float e[16];
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    e[2 * j] = bf16_lo(la2[j]) * kLog2e;
-    e[2 * j + 1] = bf16_hi(la2[j]) * kLog2e;
-  }
-#pragma unroll
-  for (int i = 0; i < 16; ++i) e[i] = ex2f(e[i]);
-  uint32_t om2[8];
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    a2[j] = pack_bf16x2(e[2 * j], e[2 * j + 1]);
-    om2[j] = pack_bf16x2(e[2 * j] * e[2 * j], e[2 * j + 1] * e[2 * j + 1]);   // exp(2 log_a)
-  }
-#pragma unroll
-  for (int j = 0; j < 8; ++j) om2[j] = bsub2(0x3f803f80u, om2[j]);             // 1 - a^2
-#pragma unroll
-  for (int j = 0; j < 8; ++j)
-    mult2[j] = pack_bf16x2(sqrtf_approx(bf16_lo(om2[j])), sqrtf_approx(bf16_hi(om2[j])));
-}
 
 }  // namespace rgk
