@@ -47,6 +47,7 @@ def lib() -> ctypes.CDLL:
     _lib.rgo_recurrent_block.restype = ctypes.c_int
     _lib.rgo_residual_temporal.restype = ctypes.c_int
     _lib.rgo_mlp.restype = ctypes.c_int
+    _lib.rgo_attention_block.restype = ctypes.c_int
     _lib.rgo_residual_channel.restype = ctypes.c_int
   return _lib
 
@@ -295,6 +296,33 @@ def residual_channel(residual: torch.Tensor, norm_scale: torch.Tensor, w_up: tor
   if rc:
     raise RuntimeError(f"oracle residual_channel failed ({rc})")
   return _t(out, residual.dtype)
+
+
+def attention_block(x: torch.Tensor, segment_pos: torch.Tensor, wq: torch.Tensor, wk: torch.Tensor,
+                    wv: torch.Tensor, wf: torch.Tensor, bf: torch.Tensor, num_heads: int,
+                    window: int, cache=None):
+  """LocalAttentionBlock.forward.  cache: None (prefill) or (keys [B,W,1,Hd], values, num_tokens [B]).
+  Returns (out, (keys, values, num_tokens int32))."""
+  bsz, t, d = x.shape
+  hd = d // num_heads
+  out = _out((bsz, t, d))
+  nk, nv = _out((bsz, window, hd)), _out((bsz, window, hd))
+  nn_ = np.zeros((bsz,), dtype=np.int64)
+  if cache is None:
+    ck = cv = cn = None
+  else:
+    ck = _f(cache[0].reshape(bsz, window, hd))
+    cv = _f(cache[1].reshape(bsz, window, hd))
+    cn = _i64(cache[2])
+  rc = lib().rgo_attention_block(
+      _p(_f(x)), _p(_i64(segment_pos)), _p(_f(wq)), _p(_f(wk)), _p(_f(wv)), _p(_f(wf)), _p(_f(bf)),
+      _p(ck), _p(cv), _p(cn), bsz, t, d, num_heads, window, _mode(x), _p(out), _p(nk), _p(nv),
+      _p(nn_))
+  if rc:
+    raise RuntimeError(f"oracle attention_block failed ({rc})")
+  return _t(out, x.dtype), (_t(nk, x.dtype).reshape(bsz, window, 1, hd),
+                            _t(nv, x.dtype).reshape(bsz, window, 1, hd),
+                            torch.from_numpy(nn_).to(torch.int32))
 
 
 def params_of(state_dict: dict, prefix: str = "") -> dict:

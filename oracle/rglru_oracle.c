@@ -64,7 +64,7 @@ static inline float gelu_tanhf_(float z) {
   return 0.5f * z * (1.0f + tanhf(inner));
 }
 
-RGO_API int rgo_version(void) { return 3; }
+RGO_API int rgo_version(void) { return 4; }
 
 /* ---------------------------------------------------------------------------------------------
  * BlockDiagonalLinear.forward, layers.py:127-137.
@@ -486,6 +486,190 @@ RGO_API int rgo_residual_channel(const float* residual, const float* norm_scale,
     for (int64_t i = 0; i < M * D; ++i) out[i] = rnd(out[i] + residual[i], dt);
   free(xn);
   return rc;
+}
+
+/* ---------------------------------------------------------------------------------------------
+ * LocalAttentionBlock.forward, modules.py:399-493, with its helpers: _apply_rope (modules.py:58-86),
+ * _compute_forward_pass_mask / _compute_causal_mask (89-140), _compute_cache_mask (143-163),
+ * _attention_cache_from_prompt (238-258), _update_attention_cache (166-196).
+ *
+ * Multi-query attention: N query heads of dimension Hd = D / N, ONE key/value head.  Rotary
+ * embedding on the first half of every head (pairs (i, i + Hd/4) of that half, wavelength 10000),
+ * positions = segment_pos.  Prefill (no cache): key s is visible to query t iff s <= t,
+ * t <= s + W and both belong to the same document (documents start where segment_pos == 0), t and s
+ * being indices in the sequence.  Decode (cache of W slots, T == 1): the cache slot j holds the
+ * token of absolute position j + k W (if that is < num_tokens) or j + (k - 1) W, k = num_tokens / W;
+ * a slot is visible iff its position is >= 0 and >= num_tokens - W; the new token always is.
+ * Roundings in bfloat16 mode: projections (one rounding each), sin / cos cast to bfloat16, every
+ * product and sum of the rotation, logits (rounded contraction, then the exact scaling by
+ * Hd^-1/2 when that is a power of two, rounded otherwise), softmax in float32 over the masked
+ * logits (masked = -2.3819763e38), probabilities cast to bfloat16, the second contraction rounded,
+ * proj_final one rounding.
+ * ------------------------------------------------------------------------------------------- */
+static void rope_inplace(float* x, const int64_t* pos, int64_t rows, int heads, int hd, int dt) {
+  /* x [rows, heads, hd]; pos [rows] */
+  const int half = hd / 2, quarter = hd / 4;
+#pragma omp parallel for schedule(static)
+  for (int64_t r = 0; r < rows; ++r) {
+    for (int i = 0; i < quarter; ++i) {
+      const float exponent = 2.0f * (float)i / (float)half;
+      const float timescale = powf(10000.0f, exponent);
+      const float inv = 1.0f / timescale;
+      const float ang = (float)pos[r] * inv;
+      const float sn = rnd(sinf(ang), dt), cs = rnd(cosf(ang), dt);
+      for (int n = 0; n < heads; ++n) {
+        float* h = x + (r * heads + n) * hd;
+        const float a = h[i], b = h[i + quarter];
+        h[i] = rnd(rnd(a * cs, dt) - rnd(b * sn, dt), dt);
+        h[i + quarter] = rnd(rnd(b * cs, dt) + rnd(a * sn, dt), dt);
+      }
+    }
+  }
+}
+
+RGO_API void rgo_rope(float* x, const int64_t* pos, int64_t rows, int heads, int hd, int dt) {
+  rope_inplace(x, pos, rows, heads, hd, dt);
+}
+
+/* q [B,T,N,Hd] (rotated), k / v [B,S,Hd], visible(b,t,s) given as a byte mask [B,T,S]:
+ * encoded [B,T,N*Hd] */
+static void attention_core(const float* q, const float* k, const float* v, const unsigned char* vis,
+                           int B, int T, int S, int N, int Hd, int dt, float* enc) {
+  const float scale = 1.0f / sqrtf((float)Hd);
+#pragma omp parallel for collapse(2) schedule(static)
+  for (int b = 0; b < B; ++b) {
+    for (int t = 0; t < T; ++t) {
+      float* lg = (float*)malloc(sizeof(float) * (size_t)S);
+      for (int n = 0; n < N; ++n) {
+        const float* qr = q + (((int64_t)b * T + t) * N + n) * Hd;
+        float mx = -3.0e38f;
+        for (int s = 0; s < S; ++s) {
+          const float* kr = k + ((int64_t)b * S + s) * Hd;
+          float acc = 0.0f;
+          for (int d = 0; d < Hd; ++d) acc += qr[d] * kr[d];
+          float l = rnd(rnd(acc, dt) * scale, dt);
+          if (!vis[((int64_t)b * T + t) * S + s]) l = -2.3819763e38f;
+          lg[s] = l;
+          if (l > mx) mx = l;
+        }
+        float sum = 0.0f;
+        for (int s = 0; s < S; ++s) { lg[s] = expf(lg[s] - mx); sum += lg[s]; }
+        float* o = enc + ((int64_t)b * T + t) * N * Hd + (int64_t)n * Hd;
+        for (int d = 0; d < Hd; ++d) o[d] = 0.0f;
+        for (int s = 0; s < S; ++s) {
+          const float p = rnd(lg[s] / sum, dt);
+          if (p == 0.0f) continue;
+          const float* vr = v + ((int64_t)b * S + s) * Hd;
+          for (int d = 0; d < Hd; ++d) o[d] += p * vr[d];
+        }
+        for (int d = 0; d < Hd; ++d) o[d] = rnd(o[d], dt);
+      }
+      free(lg);
+    }
+  }
+}
+
+/* Prefill (cache_k == NULL) or one decode step (cache given, T == 1).
+ * x [B,T,D]; wq [D,D], wk / wv [Hd,D], wf [D,D], bf [D] (nn.Linear layouts);
+ * cache_k / cache_v [B,W,Hd], cache_n [B] (int64);  out [B,T,D];
+ * new_k / new_v [B,W,Hd], new_n [B] (may be NULL: return_cache = False). */
+RGO_API int rgo_attention_block(const float* x, const int64_t* segment_pos, const float* wq,
+                                const float* wk, const float* wv, const float* wf, const float* bf,
+                                const float* cache_k, const float* cache_v, const int64_t* cache_n,
+                                int B, int T, int D, int N, int W, int dt, float* out, float* new_k,
+                                float* new_v, int64_t* new_n) {
+  const int Hd = D / N;
+  const int64_t M = (int64_t)B * T;
+  if (cache_k != NULL && T != 1) return -2;
+  float* q = (float*)malloc(sizeof(float) * (size_t)(M * D));
+  float* k = (float*)malloc(sizeof(float) * (size_t)(M * Hd));
+  float* v = (float*)malloc(sizeof(float) * (size_t)(M * Hd));
+  float* enc = (float*)malloc(sizeof(float) * (size_t)(M * D));
+  if (!q || !k || !v || !enc) { free(q); free(k); free(v); free(enc); return -1; }
+  rgo_linear(x, wq, NULL, M, D, D, dt, q);
+  rgo_linear(x, wk, NULL, M, D, Hd, dt, k);
+  rgo_linear(x, wv, NULL, M, D, Hd, dt, v);
+  rope_inplace(q, segment_pos, M, N, Hd, dt);
+  rope_inplace(k, segment_pos, M, 1, Hd, dt);
+  if (cache_k == NULL) {
+    unsigned char* vis = (unsigned char*)malloc((size_t)B * T * T);
+    for (int b = 0; b < B; ++b) {
+      int* seg = (int*)malloc(sizeof(int) * (size_t)T);
+      int c = 0;
+      for (int t = 0; t < T; ++t) { if (segment_pos[(int64_t)b * T + t] == 0) ++c; seg[t] = c; }
+      for (int t = 0; t < T; ++t)
+        for (int s = 0; s < T; ++s)
+          vis[((int64_t)b * T + t) * T + s] = (unsigned char)(s <= t && t <= s + W && seg[s] == seg[t]);
+      free(seg);
+    }
+    attention_core(q, k, v, vis, B, T, T, N, Hd, dt, enc);
+    free(vis);
+    if (new_k != NULL) {
+      /* the last w = min(W, T) keys / values, rolled by num_tokens mod W, right padded with zeros */
+      const int w = W < T ? W : T;
+      for (int b = 0; b < B; ++b) {
+        const int64_t nt = segment_pos[(int64_t)b * T + T - 1] + 1;
+        new_n[b] = nt;
+        for (int64_t i = 0; i < (int64_t)W * Hd; ++i) {
+          new_k[(int64_t)b * W * Hd + i] = 0.0f;
+          new_v[(int64_t)b * W * Hd + i] = 0.0f;
+        }
+        const int64_t shift = ((nt % W) + W) % W;
+        for (int j = 0; j < w; ++j) {
+          /* rolled[j] = tail[(j - shift) mod w] */
+          const int64_t src = (((int64_t)j - shift) % w + w) % w;
+          const int64_t row = (int64_t)b * T + (T - w) + src;
+          for (int d = 0; d < Hd; ++d) {
+            new_k[((int64_t)b * W + j) * Hd + d] = k[row * Hd + d];
+            new_v[((int64_t)b * W + j) * Hd + d] = v[row * Hd + d];
+          }
+        }
+      }
+    }
+  } else {
+    const int S = W + 1;
+    float* kk = (float*)malloc(sizeof(float) * (size_t)B * S * Hd);
+    float* vv = (float*)malloc(sizeof(float) * (size_t)B * S * Hd);
+    unsigned char* vis = (unsigned char*)malloc((size_t)B * S);
+    for (int b = 0; b < B; ++b) {
+      const int64_t nt = cache_n[b];
+      const int64_t kq = nt / W;
+      for (int j = 0; j < W; ++j) {
+        const int64_t now = j + kq * W, prev = j + (kq - 1) * W;
+        const int64_t kp = now < nt ? now : prev;
+        vis[(int64_t)b * S + j] = (unsigned char)(kp >= 0 && nt >= kp && nt <= kp + W);
+        for (int d = 0; d < Hd; ++d) {
+          kk[((int64_t)b * S + j) * Hd + d] = cache_k[((int64_t)b * W + j) * Hd + d];
+          vv[((int64_t)b * S + j) * Hd + d] = cache_v[((int64_t)b * W + j) * Hd + d];
+        }
+      }
+      vis[(int64_t)b * S + W] = 1;
+      for (int d = 0; d < Hd; ++d) {
+        kk[((int64_t)b * S + W) * Hd + d] = k[(int64_t)b * Hd + d];
+        vv[((int64_t)b * S + W) * Hd + d] = v[(int64_t)b * Hd + d];
+      }
+    }
+    attention_core(q, kk, vv, vis, B, 1, S, N, Hd, dt, enc);
+    if (new_k != NULL) {
+      for (int b = 0; b < B; ++b) {
+        const int64_t nt = cache_n[b];
+        for (int64_t i = 0; i < (int64_t)W * Hd; ++i) {
+          new_k[(int64_t)b * W * Hd + i] = cache_k[(int64_t)b * W * Hd + i];
+          new_v[(int64_t)b * W * Hd + i] = cache_v[(int64_t)b * W * Hd + i];
+        }
+        const int64_t slot = nt % W;
+        for (int d = 0; d < Hd; ++d) {
+          new_k[((int64_t)b * W + slot) * Hd + d] = k[(int64_t)b * Hd + d];
+          new_v[((int64_t)b * W + slot) * Hd + d] = v[(int64_t)b * Hd + d];
+        }
+        new_n[b] = nt + 1;
+      }
+    }
+    free(kk); free(vv); free(vis);
+  }
+  rgo_linear(enc, wf, bf, M, D, D, dt, out);
+  free(q); free(k); free(v); free(enc);
+  return 0;
 }
 
 /* ---------------------------------------------------------------------------------------------

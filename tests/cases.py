@@ -20,6 +20,7 @@ import torch
 class Case:
   name: str
   kind: str            # "blockdiag" | "conv1d" | "rglru" | "rnn_scan" | "block" | "rmsnorm" | "residual" | "mlp" | "resblock"
+                       # | "attention"
   dtype: str           # "float32" | "bfloat16"
   batch: int
   seq: int
@@ -31,6 +32,7 @@ class Case:
   with_h0: bool = False
   decode_steps: int = 2
   expanded: int = 0    # mlp expanded width (kinds "mlp" and "resblock")
+  window: int = 0      # attention window size (kind "attention")
 
   @property
   def torch_dtype(self) -> torch.dtype:
@@ -134,6 +136,15 @@ def make_params(case: Case) -> Dict[str, torch.Tensor]:
   }
   if case.kind == "rmsnorm":
     return {"scale": normal(n, "norm_scale", (e,), 0.3, dt)}
+  if case.kind == "attention":
+    hd = d // h
+    return {
+        "proj_q.weight": normal(n, "proj_q_w", (d, d), math.sqrt(1.0 / d), dt),
+        "proj_k.weight": normal(n, "proj_k_w", (hd, d), math.sqrt(1.0 / d), dt),
+        "proj_v.weight": normal(n, "proj_v_w", (hd, d), math.sqrt(1.0 / d), dt),
+        "proj_final.weight": normal(n, "proj_final_w", (d, d), math.sqrt(1.0 / d), dt),
+        "proj_final.bias": normal(n, "proj_final_b", (d,), 0.1, dt),
+    }
   mlp = {}
   if case.kind in ("mlp", "resblock"):
     xw = case.expanded
@@ -169,7 +180,7 @@ def make_inputs(case: Case) -> Dict[str, Optional[torch.Tensor]]:
   """Activations, positions, optional initial state and the decode-step tokens of a case."""
   dt = case.torch_dtype
   n = case.name
-  in_width = (case.model_width if case.kind in ("block", "residual", "mlp", "resblock")
+  in_width = (case.model_width if case.kind in ("block", "residual", "mlp", "resblock", "attention")
               else case.lru_width)
   out: Dict[str, Optional[torch.Tensor]] = {
       "x": normal(n, "x", (case.batch, case.seq, in_width), 1.0, dt),
@@ -249,6 +260,11 @@ def golden_cases():
         _c(f"residual_{s}_256_h2_l512", "residual", dt, 4, 48, 512, 2, width=256),
         _c(f"mlp_{s}_128_x384", "mlp", dt, 2, 32, 128, width=128, expanded=384, decode_steps=0),
         _c(f"mlp_{s}_256_x768", "mlp", dt, 2, 33, 256, width=256, expanded=768, decode_steps=0),
+        # local attention (modules.py:399-493): window shorter and longer than the sequence,
+        # documents inside the window, the model's head dimension of 256
+        _c(f"attn_{s}_128_h2_w16", "attention", dt, 2, 40, 128, 2, width=128, window=16, pos="multi"),
+        _c(f"attn_{s}_128_h2_w64", "attention", dt, 2, 24, 128, 2, width=128, window=64),
+        _c(f"attn_{s}_512_h2_w64", "attention", dt, 2, 80, 512, 2, width=512, window=64),
         # a whole residual block of the recurrent kind (modules.py:897-911)
         _c(f"resblock_{s}_128_h1_l256_x384", "resblock", dt, 2, 64, 256, 1, width=128,
            expanded=384, pos="multi"),

@@ -37,7 +37,8 @@ def import_reference(path: str):
 
 
 def _np(t):
-  return t.detach().to(torch.float32).numpy()
+  # a copy: the reference updates its attention cache in place during later decode steps
+  return t.detach().to(torch.float32).numpy().copy()
 
 
 def run_case(case: C.Case, layers, modules) -> dict:
@@ -109,6 +110,19 @@ def run_case(case: C.Case, layers, modules) -> dict:
         out[f"out_step{i}"] = _np(y + xs)
         out[f"h_step{i}"] = _np(cache.rg_lru_state)
         out[f"cache_step{i}"] = _np(cache.conv1d_state)
+    elif case.kind == "attention":
+      m = modules.LocalAttentionBlock(case.model_width, case.heads, case.window, dtype=dt)
+      m.load_state_dict(p)
+      y, cache = m(inp["x"], pos)
+      out["out"] = _np(y)
+      out["keys"], out["values"] = _np(cache.keys), _np(cache.values)
+      out["num_tokens"] = cache.num_tokens.numpy().astype(np.int64)
+      for i in range(case.decode_steps):
+        y, cache = m(inp[f"x_step{i}"], C.decode_positions(case, pos, i), cache)
+        out[f"out_step{i}"] = _np(y)
+        out[f"keys_step{i}"], out[f"values_step{i}"] = _np(cache.keys), _np(cache.values)
+        out[f"num_tokens_step{i}"] = cache.num_tokens.numpy().astype(np.int64)
+
     elif case.kind == "mlp":
       m = modules.MLPBlock(case.model_width, case.expanded, dtype=dt)
       m.load_state_dict({k[len("mlp_block."):]: v for k, v in p.items()})

@@ -79,6 +79,17 @@ def test_oracle_matches_reference(case, oracle):
       y, h, cache = oracle.residual_temporal(inp[f"x_step{i}"], C.decode_positions(case, pos, i),
                                              ns, op, h, cache)
       chk(y, f"out_step{i}", True); chk(h, f"h_step{i}", True); chk(cache, f"cache_step{i}", True)
+  elif case.kind == "attention":
+    w = (p["proj_q.weight"], p["proj_k.weight"], p["proj_v.weight"], p["proj_final.weight"],
+         p["proj_final.bias"])
+    y, cache = oracle.attention_block(inp["x"], pos, *w, case.heads, case.window)
+    chk(y, "out"); chk(cache[0], "keys"); chk(cache[1], "values")
+    assert torch.equal(cache[2].long(), torch.from_numpy(g["num_tokens"]))
+    for i in range(case.decode_steps):
+      y, cache = oracle.attention_block(inp[f"x_step{i}"], C.decode_positions(case, pos, i), *w,
+                                        case.heads, case.window, cache)
+      chk(y, f"out_step{i}"); chk(cache[0], f"keys_step{i}"); chk(cache[1], f"values_step{i}")
+      assert torch.equal(cache[2].long(), torch.from_numpy(g[f"num_tokens_step{i}"]))
   elif case.kind == "mlp":
     chk(oracle.mlp(inp["x"], p["mlp_block.ffw_up.w"], p["mlp_block.ffw_up.b"],
                    p["mlp_block.ffw_down.weight"], p["mlp_block.ffw_down.bias"]), "out")
