@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define RGK_ABI_VERSION 4
+#define RGK_ABI_VERSION 5
 
 #if defined(__GNUC__)
 #define RGK_API __attribute__((visibility("default")))
@@ -286,6 +286,25 @@ RGK_API int rgk_residual_channel(const void* residual_in, const void* norm_scale
                                  const void* packed_up, const void* down_w, const void* down_b,
                                  int64_t M, int64_t D, int64_t X, int dtype, void* out,
                                  void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Pieces of LocalAttentionBlock.forward (recurrentgemma/torch/modules.py:399-493).
+ * rgk_rope: _apply_rope (torch/modules.py:58-86) in place on x [rows, heads, head_dim], positions
+ *   [rows]: the first half of every head is rotated, float32 or bfloat16.
+ * rgk_local_attention_prefill: the attention proper without a cache - logits of rotated queries
+ *   q [B,T,N,head_dim] and keys k [B,T,head_dim] (one key/value head), the causal / window / same
+ *   document mask of torch/modules.py:89-140, float32 softmax of the bfloat16-rounded logits,
+ *   probabilities rounded to bfloat16, product with v [B,T,head_dim] -> out [B,T,N*head_dim].
+ *   bfloat16 with head_dim 256; RGK_ESHAPE otherwise.
+ * workspace: rgk_attention_workspace_bytes(B, T) bytes, 256-byte aligned (first word: status).
+ * ---------------------------------------------------------------------------------------------- */
+RGK_API int rgk_rope(void* x, const void* segment_pos, int pos_dtype, int64_t rows, int heads,
+                     int head_dim, int dtype, void* stream);
+RGK_API size_t rgk_attention_workspace_bytes(int64_t B, int64_t T);
+RGK_API int rgk_local_attention_prefill(const void* q, const void* k, const void* v,
+                                        const void* segment_pos, int pos_dtype, int64_t B, int64_t T,
+                                        int N, int head_dim, int window, int dtype, void* out,
+                                        void* workspace, size_t workspace_bytes, void* stream);
 
 /* Scratch needed by the calls above for a problem of this size (an upper bound over the entry
  * points, so one buffer serves all of them).  Returns 0 on invalid arguments. */

@@ -6,12 +6,13 @@ forward does, and raises if it has not been built.
 """
 from recurrentgemma_b200.layers import (BlockDiagonalLinear, Conv1D, Einsum, RGLRU, RMSNorm,
                                         rnn_scan)
-from recurrentgemma_b200.modules import (MLPBlock, RecurrentBlock, RecurrentBlockCache,
+from recurrentgemma_b200.modules import (AttentionBlockCache, LocalAttentionBlock, MLPBlock,
+                                         RecurrentBlock, RecurrentBlockCache,
                                          dense_linear, recurrent_path, recurrent_residual,
                                          residual_block)
 
 __all__ = [
     "BlockDiagonalLinear", "Conv1D", "Einsum", "RGLRU", "RMSNorm", "rnn_scan", "RecurrentBlock",
-    "RecurrentBlockCache", "MLPBlock", "recurrent_path", "recurrent_residual", "residual_block",
+    "RecurrentBlockCache", "MLPBlock", "LocalAttentionBlock", "AttentionBlockCache", "recurrent_path", "recurrent_residual", "residual_block",
     "dense_linear",
 ]

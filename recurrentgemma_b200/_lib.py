@@ -73,6 +73,10 @@ SIGNATURES = {
     "rgk_mlp_block": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _vp, _sz, _vp]),
     "rgk_residual_channel": (_int, [_vp, _vp, ctypes.c_float, _vp, _vp, _vp, _i64, _i64, _i64, _int,
                                     _vp, _vp, _sz, _vp]),
+    "rgk_rope": (_int, [_vp, _vp, _int, _i64, _int, _int, _int, _vp]),
+    "rgk_attention_workspace_bytes": (_sz, [_i64, _i64]),
+    "rgk_local_attention_prefill": (_int, [_vp, _vp, _vp, _vp, _int, _i64, _i64, _int, _int, _int,
+                                           _int, _vp, _vp, _sz, _vp]),
     "rgk_workspace_bytes": (_sz, [_i64, _i64, _i64, _int]),
     "rgk_workspace_status": (_int, [_vp, _vp]),
 }
@@ -104,7 +108,7 @@ def load() -> ctypes.CDLL:
       fn = getattr(lib, name)
       fn.restype = res
       fn.argtypes = args
-    if lib.rgk_abi_version() != 4:
+    if lib.rgk_abi_version() != 5:
       raise RuntimeError("librgk.so has a different ABI version; rebuild it")
     _lib = lib
     return lib

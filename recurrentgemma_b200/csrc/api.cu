@@ -659,6 +659,55 @@ int rgk_residual_channel(const void* residual_in, const void* norm_scale, float 
   return mlp_impl(xn, packed_up, down_w, down_b, residual_in, M, D, X, out, workspace, s);
 }
 
+// ---- local attention ----------------------------------------------------------------------------
+
+int rgk_rope(void* x, const void* segment_pos, int pos_dtype, int64_t rows, int heads, int head_dim,
+             int dtype, void* stream) {
+  RGK_REQUIRE(dtype == RGK_F32 || dtype == RGK_BF16, RGK_EINVAL, "unknown dtype %d", dtype);
+  RGK_REQUIRE(pos_dtype == RGK_I32 || pos_dtype == RGK_I64, RGK_EINVAL, "unknown index dtype");
+  RGK_REQUIRE(rows >= 0 && heads >= 1 && head_dim >= 4 && head_dim % 4 == 0, RGK_EINVAL,
+              "bad size (rows=%lld heads=%d head_dim=%d)", (long long)rows, heads, head_dim);
+  RGK_REQUIRE(x && segment_pos, RGK_EINVAL, "NULL pointer argument");
+  if (rows == 0) return RGK_OK;
+  RGK_CHECK_DEVICE();
+  RGK_CUDA(rgk::launch_rope(x, segment_pos, pos_dtype == RGK_I64, rows, heads, head_dim, dtype,
+                            static_cast<cudaStream_t>(stream)),
+           "rope launch");
+  return RGK_OK;
+}
+
+size_t rgk_attention_workspace_bytes(int64_t B, int64_t T) {
+  if (B < 0 || T < 0) return 0;
+  return rgk::attention_workspace_bytes(B < 1 ? 1 : B, T < 1 ? 1 : T);
+}
+
+int rgk_local_attention_prefill(const void* q, const void* k, const void* v, const void* segment_pos,
+                                int pos_dtype, int64_t B, int64_t T, int N, int head_dim, int window,
+                                int dtype, void* out, void* workspace, size_t workspace_bytes,
+                                void* stream) {
+  RGK_REQUIRE(pos_dtype == RGK_I32 || pos_dtype == RGK_I64, RGK_EINVAL, "unknown index dtype");
+  RGK_REQUIRE(B >= 0 && T >= 0 && N >= 1 && window >= 1, RGK_EINVAL, "bad size");
+  RGK_REQUIRE(q && k && v && segment_pos && out, RGK_EINVAL, "NULL pointer argument");
+  RGK_REQUIRE(aligned16(q) && aligned16(k) && aligned16(v) && aligned16(out), RGK_EALIGN,
+              "pointers must be 16-byte aligned");
+  RGK_REQUIRE(rgk::attention_supported(dtype, head_dim, B > 0 ? B : 1, T > 0 ? T : 1, N), RGK_ESHAPE,
+              "the attention kernel covers bfloat16 with head dimension 256 (dtype %d, head_dim %d)",
+              dtype, head_dim);
+  if (B * T == 0) return RGK_OK;
+  const size_t need = rgk_attention_workspace_bytes(B, T);
+  RGK_REQUIRE(workspace != nullptr && workspace_bytes >= need, RGK_EWORKSPACE,
+              "workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+  RGK_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255u) == 0, RGK_EALIGN,
+              "workspace must be 256-byte aligned");
+  RGK_CHECK_DEVICE();
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  RGK_CUDA(cudaMemsetAsync(workspace, 0, sizeof(int), s), "cudaMemsetAsync");
+  RGK_CUDA(rgk::launch_attention_prefill(q, k, v, segment_pos, pos_dtype == RGK_I64, B, T, N, window,
+                                         out, workspace, s),
+           "attention launch");
+  return RGK_OK;
+}
+
 int rgk_recurrent_path_decode(const void* xb, const void* yb, const void* segment_pos,
                               int pos_dtype, const rgk_params* p, const float* h_in,
                               const void* conv_cache_in, int64_t B, int64_t E, int H, int W,

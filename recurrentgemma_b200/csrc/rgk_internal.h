@@ -74,6 +74,17 @@ cudaError_t launch_dense_tc(const void* x, const void* w, const void* bias, cons
 cudaError_t launch_pack_mlp_up(const void* w, const void* b, int D, int X, void* packed_w,
                                void* packed_b, cudaStream_t s);
 
+// attention.cu: rotary embedding in place (x [rows, heads, hd], the first half of each head), and
+// the local multi-query attention of the attention blocks in prefill form: q [B,T,N,256] and
+// k [B,T,256] rotated, v [B,T,256], bfloat16 -> out [B,T,N*256].  ws: attention_workspace_bytes.
+cudaError_t launch_rope(void* x, const void* pos, int pos64, int64_t rows, int heads, int hd,
+                        int dtype, cudaStream_t s);
+bool attention_supported(int dtype, int hd, int64_t B, int64_t T, int N);
+size_t attention_workspace_bytes(int64_t B, int64_t T);
+cudaError_t launch_attention_prefill(const void* q, const void* k, const void* v, const void* pos,
+                                     int pos64, int64_t B, int64_t T, int N, int window, void* out,
+                                     void* ws, cudaStream_t s);
+
 // rmsnorm.cu: out [M,D] = x * rsqrt(mean(x^2) + eps) * (scale + 1) with the reference's roundings
 // (torch/layers.py:65-73); one warp per row held in registers.
 bool rmsnorm_supported(int dtype, int64_t D);

@@ -329,3 +329,157 @@ def residual_block(
   r, new_cache = recurrent_residual(x, segment_pos, temporal_pre_norm, recurrent_block, cache,
                                     return_cache)
   return mlp_block(r, pre_norm=channel_pre_norm), new_cache
+
+class AttentionBlockCache(NamedTuple):
+  """Field order and dtypes of recurrentgemma/torch/modules.py:40-46: a ring buffer of the last
+  `window` keys and values and the number of tokens seen."""
+  keys: torch.Tensor        # [B, window, 1, head_dim]
+  values: torch.Tensor      # [B, window, 1, head_dim]
+  num_tokens: torch.Tensor  # [B] int32
+
+
+def _rope(x: torch.Tensor, segment_pos: torch.Tensor) -> torch.Tensor:
+  """Rotary embedding of x [B, T, heads, head_dim] in place (torch/modules.py:58-86)."""
+  b, t, heads, hd = x.shape
+  pos = segment_pos.contiguous()
+  dev = x.device
+  with torch.cuda.device(dev):
+    _lib.check(_lib.load().rgk_rope(x.data_ptr(), pos.data_ptr(), _lib.pos_code(pos), b * t, heads,
+                                    hd, _lib.dtype_code(x.dtype), _lib.stream_ptr(dev)))
+  return x
+
+
+def _cache_from_prompt(keys: torch.Tensor, values: torch.Tensor, segment_pos: torch.Tensor,
+                       window: int) -> AttentionBlockCache:
+  """The last min(window, T) keys / values, rolled by num_tokens mod window so that slot j holds
+  the token whose position is j modulo the window, right padded with zeros
+  (torch/modules.py:238-258)."""
+  b, t = keys.shape[:2]
+  w = min(window, t)
+  num_tokens = segment_pos[:, -1] + 1
+  shift = (num_tokens % window).long()
+  src = (torch.arange(w, device=keys.device)[None, :] - shift[:, None]) % w       # [B, w]
+  idx = (t - w + src)[:, :, None, None].expand(b, w, 1, keys.shape[-1])
+  k = torch.gather(keys, 1, idx)
+  v = torch.gather(values, 1, idx)
+  if w < window:
+    pad = torch.zeros((b, window - w, 1, keys.shape[-1]), dtype=keys.dtype, device=keys.device)
+    k, v = torch.cat([k, pad], dim=1), torch.cat([v, pad], dim=1)
+  return AttentionBlockCache(keys=k.contiguous(), values=v.contiguous(),
+                             num_tokens=num_tokens.to(torch.int32))
+
+
+class LocalAttentionBlock(nn.Module):
+  """Local multi-query attention (recurrentgemma/torch/modules.py:293-493): same constructor,
+  parameter names (`proj_q/k/v.weight`, `proj_final.weight/.bias`), forward and cache.  bfloat16
+  prefill with head dimension 256 runs on the library (projections on the tcgen05 GEMM, rotary
+  kernel, the two-pass tcgen05 attention kernel); the decode step and other shapes compose the
+  rotary kernel with library contractions."""
+
+  def __init__(self, width: int, num_heads: int, window_size: int,
+               final_w_init_variance_scale: float = 1.0, device=None, dtype=None):
+    super().__init__()
+    self.width = width
+    self.num_heads = num_heads
+    self.window_size = window_size
+    self.final_w_init_variance_scale = final_w_init_variance_scale
+    self.proj_q = nn.Linear(self.width, self.width, bias=False, device=device, dtype=dtype)
+    self.proj_k = nn.Linear(self.width, self.head_dim, bias=False, device=device, dtype=dtype)
+    self.proj_v = nn.Linear(self.width, self.head_dim, bias=False, device=device, dtype=dtype)
+    self.proj_final = nn.Linear(self.width, self.width, bias=True, device=device, dtype=dtype)
+    self.reset_parameters()
+
+  def reset_parameters(self) -> None:
+    self.w_init_(self.proj_q.weight)
+    self.w_init_(self.proj_k.weight)
+    self.w_init_(self.proj_v.weight)
+    self.out_w_init_(self.proj_final.weight)
+    torch.nn.init.zeros_(self.proj_final.bias)
+
+  @property
+  def head_dim(self) -> int:
+    return self.width // self.num_heads
+
+  def w_init_(self, w: torch.Tensor) -> None:
+    torch.nn.init.normal_(w, mean=0.0, std=math.sqrt(1.0 / self.width))
+
+  def out_w_init_(self, w: torch.Tensor) -> None:
+    torch.nn.init.normal_(w, mean=0.0, std=math.sqrt(self.final_w_init_variance_scale / self.width))
+
+  def _linear(self, x: torch.Tensor, lin: nn.Linear) -> torch.Tensor:
+    if x.dtype == torch.bfloat16 and x.numel() // x.shape[-1] >= 64:
+      return dense_linear(x, lin.weight, lin.bias)
+    return lin(x)
+
+  @torch.no_grad()
+  def forward(
+      self, x: torch.Tensor, segment_pos: torch.Tensor,
+      cache: Optional[AttentionBlockCache] = None, return_cache: bool = True,
+  ) -> Tuple[torch.Tensor, Optional[AttentionBlockCache]]:
+    """Returns (block output [B,T,width], updated cache or None)."""
+    dev = _lib.require_cuda(x, segment_pos, self.proj_q.weight)
+    layers._same_dtype(x, self.proj_q.weight, self.proj_k.weight, self.proj_v.weight,
+                       self.proj_final.weight, self.proj_final.bias)
+    b, t, _ = x.shape
+    assert segment_pos.shape == (b, t), segment_pos.shape
+    n, hd, w = self.num_heads, self.head_dim, self.window_size
+    q = self._linear(x, self.proj_q).view(b, t, n, hd)
+    k = self._linear(x, self.proj_k).view(b, t, 1, hd)
+    v = self._linear(x, self.proj_v).view(b, t, 1, hd)
+    q, k = _rope(q.contiguous(), segment_pos), _rope(k.contiguous(), segment_pos)
+    new_cache = None
+    if cache is None:
+      if return_cache:
+        new_cache = _cache_from_prompt(k, v, segment_pos, w)
+      if x.dtype == torch.bfloat16 and hd == 256:
+        enc = torch.empty((b, t, n * hd), dtype=x.dtype, device=dev)
+        pos = segment_pos.contiguous()
+        lib = _lib.load()
+        with torch.cuda.device(dev):
+          ws = _lib.workspace(dev, int(lib.rgk_attention_workspace_bytes(b, t)))
+          _lib.check(lib.rgk_local_attention_prefill(
+              q.data_ptr(), k.data_ptr(), v.contiguous().data_ptr(), pos.data_ptr(),
+              _lib.pos_code(pos), b, t, n, hd, w, _lib.dtype_code(x.dtype), enc.data_ptr(),
+              ws.data_ptr(), ws.numel(), _lib.stream_ptr(dev)))
+        return self._linear(enc, self.proj_final), new_cache
+      idx = torch.arange(t, device=dev)
+      start = torch.where(segment_pos == 0, idx[None, :], torch.zeros_like(segment_pos))
+      start = torch.cummax(start, dim=1).values                      # start of each token's document
+      lo = torch.maximum(start, idx[None, :] - w)
+      visible = (idx[None, None, :] >= lo[:, :, None]) & (idx[None, None, :] <= idx[None, :, None])
+      keys, values = k, v
+    else:
+      assert t == 1, "with a cache the block takes one token at a time"
+      nt = cache.num_tokens.long()
+      kq = nt // w
+      j = torch.arange(w, device=dev)[None, :]
+      now, prev = j + kq[:, None] * w, j + (kq[:, None] - 1) * w
+      kpos = torch.where(now < nt[:, None], now, prev)
+      vis = (kpos >= 0) & (kpos <= nt[:, None]) & (nt[:, None] <= kpos + w)
+      visible = torch.cat([vis, torch.ones((b, 1), dtype=torch.bool, device=dev)], dim=1)[:, None, :]
+      keys = torch.cat([cache.keys, k], dim=1)
+      values = torch.cat([cache.values, v], dim=1)
+      if return_cache:
+        slot = (nt % w)
+        rows = torch.arange(b, device=dev)
+        nk, nv = cache.keys.clone(), cache.values.clone()
+        nk[rows, slot] = k[:, 0]
+        nv[rows, slot] = v[:, 0]
+        new_cache = AttentionBlockCache(keys=nk, values=nv, num_tokens=cache.num_tokens + 1)
+    # library contractions with the reference's roundings: logits rounded, scaled, masked, float32
+    # softmax, probabilities cast back, second contraction
+    logits = torch.einsum("btnh,bsh->bnts", q, keys[:, :, 0]) * (hd ** -0.5)
+    masked = torch.where(visible[:, None], logits, torch.full_like(logits, -2.3819763e38))
+    probs = torch.softmax(masked.float(), dim=-1).to(x.dtype)
+    enc = torch.einsum("bnts,bsh->btnh", probs, values[:, :, 0]).reshape(b, t, n * hd)
+    return self._linear(enc, self.proj_final), new_cache
+
+  @classmethod
+  def init_cache(cls, batch_size: int, window_size: int, heads_dim: int, dtype: torch.dtype,
+                 device=None) -> AttentionBlockCache:
+    """Empty cache (recurrentgemma/torch/modules.py:478-493)."""
+    shape = (batch_size, window_size, 1, heads_dim)
+    return AttentionBlockCache(
+        keys=torch.zeros(shape, device=device, dtype=dtype),
+        values=torch.zeros(shape, device=device, dtype=dtype),
+        num_tokens=torch.zeros([batch_size], dtype=torch.int32, device=device))

@@ -116,6 +116,20 @@ def test_golden(case, rg, oracle):
       chk(y, f"out_step{i}"); chk(cache.rg_lru_state, f"h_step{i}")
       chk(cache.conv1d_state, f"cache_step{i}")
 
+  elif case.kind == "attention":
+    m = rg.LocalAttentionBlock(case.model_width, case.heads, case.window, device=DEV,
+                               dtype=case.torch_dtype)
+    m.load_state_dict(p)
+    y, cache = m(ic["x"], pos)
+    assert cache._fields == ("keys", "values", "num_tokens")
+    chk(y, "out"); chk(cache.keys, "keys"); chk(cache.values, "values")
+    assert torch.equal(cache.num_tokens.cpu().long(), torch.from_numpy(g["num_tokens"]))
+    assert cache.num_tokens.dtype == torch.int32
+    for i in range(case.decode_steps):
+      y, cache = m(ic[f"x_step{i}"], C.decode_positions(case, inp["segment_pos"], i).to(DEV), cache)
+      chk(y, f"out_step{i}"); chk(cache.keys, f"keys_step{i}"); chk(cache.values, f"values_step{i}")
+      assert torch.equal(cache.num_tokens.cpu().long(), torch.from_numpy(g[f"num_tokens_step{i}"]))
+
   elif case.kind == "mlp":
     m = rg.MLPBlock(case.model_width, case.expanded, device=DEV, dtype=case.torch_dtype)
     m.load_state_dict({k[len("mlp_block."):]: v for k, v in p.items()})
@@ -539,3 +553,37 @@ def test_mlp_vs_oracle(rg, oracle, shape):
     mlp.ffw_up.b.add_(1.0)
   assert_close(mlp(x.to(DEV)), oracle.mlp(x, args[0], (args[1].float() + 1.0).to(dt), *args[2:]),
                TOL[dt], "after bias update")
+
+
+@pytest.mark.parametrize("shape", [(2, 300, 2, 100, "multi"), (1, 129, 3, 512, "half"),
+                                   (3, 77, 1, 16, "padded"), (2, 1000, 2, 257, "multi"),
+                                   (1, 2500, 2, 2048, "arange")],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_attention_kernel_vs_oracle(rg, oracle, shape):
+  """The two-pass tcgen05 attention kernel (head dimension 256) against the oracle: windows shorter
+  and longer than the sequence, documents inside the window, left padding, sequence lengths that end
+  inside a tile, query tiles whose window spans many key tiles."""
+  b, t, heads, window, pattern = shape
+  d = heads * 256
+  dt = torch.bfloat16
+  case = C.Case(f"attn_{b}_{t}_{heads}_{window}", "attention", "bfloat16", b, t, d, heads, width=d,
+                window=window, pos=pattern, decode_steps=1)
+  p = C.make_params(case)
+  inp = C.make_inputs(case)
+  m = rg.LocalAttentionBlock(d, heads, window, device=DEV, dtype=dt)
+  m.load_state_dict(p)
+  x, pos = inp["x"], inp["segment_pos"]
+  y, cache = m(x.to(DEV), pos.to(DEV))
+  w = (p["proj_q.weight"], p["proj_k.weight"], p["proj_v.weight"], p["proj_final.weight"],
+       p["proj_final.bias"])
+  y_r, c_r = oracle.attention_block(x, pos, *w, heads, window)
+  assert_close(y, y_r, TOL[dt], "prefill output")
+  assert_close(cache.keys, c_r[0], TOL[dt], "cached keys")
+  assert_close(cache.values, c_r[1], TOL[dt], "cached values")
+  assert torch.equal(cache.num_tokens.cpu(), c_r[2])
+  xs, ps = inp["x_step0"], C.decode_positions(case, pos, 0)
+  y1, cache1 = m(xs.to(DEV), ps.to(DEV), cache)
+  y1_r, c1_r = oracle.attention_block(xs, ps, *w, heads, window, c_r)
+  assert_close(y1, y1_r, TOL[dt], "decode output")
+  assert_close(cache1.keys, c1_r[0], TOL[dt], "decode keys")
+  assert torch.equal(cache1.num_tokens.cpu(), c1_r[2])
