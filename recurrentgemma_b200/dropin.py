@@ -11,9 +11,9 @@ Two ways, both leaving state_dict keys unchanged (recurrentgemma/torch/modules.p
   * ``fuse_temporal_residual(model)`` after ``convert``: each residual block with a recurrent block
     computes `recurrent_block(temporal_pre_norm(x)) + x` (recurrentgemma/torch/modules.py:897-902)
     through `modules.recurrent_residual`; its channel norm and MLP stay the reference's.
-  * ``fuse_residual_block(model)`` after ``convert``: the whole forward of those residual blocks
-    (recurrentgemma/torch/modules.py:897-911) runs on this library: both norms, the recurrent
-    block, the MLP and both residual adds.
+  * ``fuse_residual_block(model)`` after ``convert``: the whole forward of every residual block
+    (recurrentgemma/torch/modules.py:897-911) runs on this library: both norms, the temporal block
+    (recurrent, or local attention), the MLP and both residual adds.
 
 The reference package is not a dependency of this library; it is imported only here, on request.
 """
@@ -90,23 +90,33 @@ def _share(new: nn.Module, old: nn.Module) -> nn.Module:
 
 def _full_residual_forward(self, x, segment_pos, cache=None, return_cache=True):
   """ResidualBlock.forward (recurrentgemma/torch/modules.py:897-911), every step on this library."""
-  return b200_modules.residual_block(x, segment_pos, self.temporal_pre_norm, self.recurrent_block,
+  return b200_modules.residual_block(x, segment_pos, self.temporal_pre_norm, self.temporal_block,
                                      self.channel_pre_norm, self.mlp_block, cache, return_cache)
 
 
 def fuse_residual_block(model: nn.Module) -> nn.Module:
-  """For every converted recurrent residual block: both norms become B200 `RMSNorm`s and the MLP a
-  B200 `MLPBlock`, all sharing the existing parameters, and `forward` becomes
+  """For every residual block: both norms become B200 `RMSNorm`s, the MLP a B200 `MLPBlock` and a
+  local attention block a B200 `LocalAttentionBlock` (recurrent blocks were replaced by
+  ``convert``), all sharing the existing parameters, and `forward` becomes
   `modules.residual_block`.  state_dict keys are unchanged.  Returns the model."""
   for block in model.blocks:
-    if isinstance(getattr(block, "recurrent_block", None), b200_modules.RecurrentBlock):
-      for name in ("temporal_pre_norm", "channel_pre_norm"):
-        old = getattr(block, name)
+    if hasattr(block, "attention_block"):
+      old = block.attention_block
+      if not isinstance(old, b200_modules.LocalAttentionBlock):
+        block.attention_block = _share(b200_modules.LocalAttentionBlock(
+            old.width, old.num_heads, old.window_size, old.final_w_init_variance_scale,
+            device="meta", dtype=old.proj_q.weight.dtype), old)
+    elif not isinstance(getattr(block, "recurrent_block", None), b200_modules.RecurrentBlock):
+      continue
+    for name in ("temporal_pre_norm", "channel_pre_norm"):
+      old = getattr(block, name)
+      if not isinstance(old, b200_layers.RMSNorm):
         setattr(block, name, _share(
             b200_layers.RMSNorm(old.width, old.eps, device="meta", dtype=old.scale.dtype), old))
-      old = block.mlp_block
+    old = block.mlp_block
+    if not isinstance(old, b200_modules.MLPBlock):
       block.mlp_block = _share(b200_modules.MLPBlock(
           old.width, old.expanded_width, old.final_w_init_variance_scale, device="meta",
           dtype=old.ffw_down.weight.dtype), old)
-      block.forward = types.MethodType(_full_residual_forward, block)
+    block.forward = types.MethodType(_full_residual_forward, block)
   return model

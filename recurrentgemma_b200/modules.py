@@ -321,14 +321,21 @@ class MLPBlock(nn.Module):
 @torch.no_grad()
 def residual_block(
     x: torch.Tensor, segment_pos: torch.Tensor, temporal_pre_norm: layers.RMSNorm,
-    recurrent_block: RecurrentBlock, channel_pre_norm: layers.RMSNorm, mlp_block: MLPBlock,
-    cache: Optional[RecurrentBlockCache] = None, return_cache: bool = True,
-) -> Tuple[torch.Tensor, Optional[RecurrentBlockCache]]:
-  """ResidualBlock.forward for a recurrent block (recurrentgemma/torch/modules.py:897-911):
-  r = recurrent_block(temporal_pre_norm(x)) + x;  out = mlp_block(channel_pre_norm(r)) + r."""
-  r, new_cache = recurrent_residual(x, segment_pos, temporal_pre_norm, recurrent_block, cache,
-                                    return_cache)
+    temporal_block: nn.Module, channel_pre_norm: layers.RMSNorm, mlp_block: MLPBlock,
+    cache=None, return_cache: bool = True,
+):
+  """ResidualBlock.forward (recurrentgemma/torch/modules.py:897-911) for either kind of temporal
+  block (a `RecurrentBlock` or a `LocalAttentionBlock`):
+  r = temporal_block(temporal_pre_norm(x)) + x;  out = mlp_block(channel_pre_norm(r)) + r.
+  Returns (out, updated cache of the temporal block or None)."""
+  if isinstance(temporal_block, RecurrentBlock):
+    r, new_cache = recurrent_residual(x, segment_pos, temporal_pre_norm, temporal_block, cache,
+                                      return_cache)
+  else:
+    y, new_cache = temporal_block(temporal_pre_norm(x), segment_pos, cache, return_cache)
+    r = y + x
   return mlp_block(r, pre_norm=channel_pre_norm), new_cache
+
 
 class AttentionBlockCache(NamedTuple):
   """Field order and dtypes of recurrentgemma/torch/modules.py:40-46: a ring buffer of the last

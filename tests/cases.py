@@ -20,7 +20,7 @@ import torch
 class Case:
   name: str
   kind: str            # "blockdiag" | "conv1d" | "rglru" | "rnn_scan" | "block" | "rmsnorm" | "residual" | "mlp" | "resblock"
-                       # | "attention"
+                       # | "attention" | "resblock_attn"
   dtype: str           # "float32" | "bfloat16"
   batch: int
   seq: int
@@ -136,15 +136,27 @@ def make_params(case: Case) -> Dict[str, torch.Tensor]:
   }
   if case.kind == "rmsnorm":
     return {"scale": normal(n, "norm_scale", (e,), 0.3, dt)}
-  if case.kind == "attention":
+  if case.kind in ("attention", "resblock_attn"):
     hd = d // h
-    return {
-        "proj_q.weight": normal(n, "proj_q_w", (d, d), math.sqrt(1.0 / d), dt),
-        "proj_k.weight": normal(n, "proj_k_w", (hd, d), math.sqrt(1.0 / d), dt),
-        "proj_v.weight": normal(n, "proj_v_w", (hd, d), math.sqrt(1.0 / d), dt),
-        "proj_final.weight": normal(n, "proj_final_w", (d, d), math.sqrt(1.0 / d), dt),
-        "proj_final.bias": normal(n, "proj_final_b", (d,), 0.1, dt),
+    pre = "attention_block." if case.kind == "resblock_attn" else ""
+    att = {
+        pre + "proj_q.weight": normal(n, "proj_q_w", (d, d), math.sqrt(1.0 / d), dt),
+        pre + "proj_k.weight": normal(n, "proj_k_w", (hd, d), math.sqrt(1.0 / d), dt),
+        pre + "proj_v.weight": normal(n, "proj_v_w", (hd, d), math.sqrt(1.0 / d), dt),
+        pre + "proj_final.weight": normal(n, "proj_final_w", (d, d), math.sqrt(1.0 / d), dt),
+        pre + "proj_final.bias": normal(n, "proj_final_b", (d,), 0.1, dt),
     }
+    if case.kind == "resblock_attn":
+      xw = case.expanded
+      att.update({
+          "temporal_pre_norm.scale": normal(n, "norm_scale", (d,), 0.3, dt),
+          "channel_pre_norm.scale": normal(n, "channel_norm_scale", (d,), 0.3, dt),
+          "mlp_block.ffw_up.w": normal(n, "ffw_up_w", (2, d, xw), math.sqrt(1.0 / d), dt),
+          "mlp_block.ffw_up.b": normal(n, "ffw_up_b", (2, 1, 1, xw), 0.2, dt),
+          "mlp_block.ffw_down.weight": normal(n, "ffw_down_w", (d, xw), math.sqrt(1.0 / xw), dt),
+          "mlp_block.ffw_down.bias": normal(n, "ffw_down_b", (d,), 0.1, dt),
+      })
+    return att
   mlp = {}
   if case.kind in ("mlp", "resblock"):
     xw = case.expanded
@@ -180,7 +192,8 @@ def make_inputs(case: Case) -> Dict[str, Optional[torch.Tensor]]:
   """Activations, positions, optional initial state and the decode-step tokens of a case."""
   dt = case.torch_dtype
   n = case.name
-  in_width = (case.model_width if case.kind in ("block", "residual", "mlp", "resblock", "attention")
+  in_width = (case.model_width
+              if case.kind in ("block", "residual", "mlp", "resblock", "attention", "resblock_attn")
               else case.lru_width)
   out: Dict[str, Optional[torch.Tensor]] = {
       "x": normal(n, "x", (case.batch, case.seq, in_width), 1.0, dt),
@@ -265,6 +278,9 @@ def golden_cases():
         _c(f"attn_{s}_128_h2_w16", "attention", dt, 2, 40, 128, 2, width=128, window=16, pos="multi"),
         _c(f"attn_{s}_128_h2_w64", "attention", dt, 2, 24, 128, 2, width=128, window=64),
         _c(f"attn_{s}_512_h2_w64", "attention", dt, 2, 80, 512, 2, width=512, window=64),
+        # a whole residual block of the attention kind, head dimension 256
+        _c(f"resblock_attn_{s}_512_h2_w48", "resblock_attn", dt, 2, 64, 512, 2, width=512,
+           window=48, expanded=384, pos="multi"),
         # a whole residual block of the recurrent kind (modules.py:897-911)
         _c(f"resblock_{s}_128_h1_l256_x384", "resblock", dt, 2, 64, 256, 1, width=128,
            expanded=384, pos="multi"),

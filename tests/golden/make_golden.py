@@ -123,6 +123,20 @@ def run_case(case: C.Case, layers, modules) -> dict:
         out[f"keys_step{i}"], out[f"values_step{i}"] = _np(cache.keys), _np(cache.values)
         out[f"num_tokens_step{i}"] = cache.num_tokens.numpy().astype(np.int64)
 
+    elif case.kind == "resblock_attn":
+      from recurrentgemma import common  # pylint: disable=import-outside-toplevel
+      m = modules.ResidualBlock(
+          width=case.model_width, mlp_expanded_width=case.expanded, num_heads=case.heads,
+          attention_window_size=case.window, temporal_block_type=common.TemporalBlockType.ATTENTION,
+          dtype=dt)
+      m.load_state_dict(p)
+      y, cache = m(inp["x"], pos)
+      out["out"] = _np(y)
+      out["keys"], out["values"] = _np(cache.keys), _np(cache.values)
+      for i in range(case.decode_steps):
+        y, cache = m(inp[f"x_step{i}"], C.decode_positions(case, pos, i), cache)
+        out[f"out_step{i}"] = _np(y)
+
     elif case.kind == "mlp":
       m = modules.MLPBlock(case.model_width, case.expanded, dtype=dt)
       m.load_state_dict({k[len("mlp_block."):]: v for k, v in p.items()})

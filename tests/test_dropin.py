@@ -75,7 +75,15 @@ def test_convert_keeps_state_dict_and_cache_layout(rg):
     assert torch.equal(before[k], after[k]), k
   assert isinstance(model.blocks[1].mlp_block, modules.MLPBlock)
   assert isinstance(model.blocks[1].channel_pre_norm, layers.RMSNorm)
-  assert not isinstance(model.blocks[2].mlp_block, modules.MLPBlock)
+  assert isinstance(model.blocks[2].mlp_block, modules.MLPBlock)
+  assert isinstance(model.blocks[2].attention_block, modules.LocalAttentionBlock)
+  ref_ac = rg.LocalAttentionBlock.init_cache(batch_size=3, window_size=16, heads_dim=64,
+                                             dtype=torch.bfloat16)
+  our_ac = modules.LocalAttentionBlock.init_cache(batch_size=3, window_size=16, heads_dim=64,
+                                                  dtype=torch.bfloat16)
+  assert ref_ac._fields == our_ac._fields
+  for a, b in zip(ref_ac, our_ac):
+    assert a.shape == b.shape and a.dtype == b.dtype
   with pytest.raises(RuntimeError, match="no CPU path"):
     model(torch.zeros(1, 4, dtype=torch.long), torch.arange(4)[None])
 
@@ -102,6 +110,7 @@ def test_signatures_match_reference(rg):
   from recurrentgemma_b200 import layers, modules
   pairs = [(ref_layers.RGLRU, layers.RGLRU), (ref_layers.Conv1D, layers.Conv1D),
            (ref_layers.RMSNorm, layers.RMSNorm), (ref_layers.Einsum, layers.Einsum),
+           (ref_modules.LocalAttentionBlock, modules.LocalAttentionBlock),
            (ref_layers.BlockDiagonalLinear, layers.BlockDiagonalLinear),
            (ref_modules.RecurrentBlock, modules.RecurrentBlock)]
   for ref_cls, our_cls in pairs:

@@ -130,6 +130,26 @@ def test_golden(case, rg, oracle):
       chk(y, f"out_step{i}"); chk(cache.keys, f"keys_step{i}"); chk(cache.values, f"values_step{i}")
       assert torch.equal(cache.num_tokens.cpu().long(), torch.from_numpy(g[f"num_tokens_step{i}"]))
 
+  elif case.kind == "resblock_attn":
+    dt = case.torch_dtype
+    tn = rg.RMSNorm(case.model_width, device=DEV, dtype=dt)
+    tn.load_state_dict({"scale": p["temporal_pre_norm.scale"]})
+    cn = rg.RMSNorm(case.model_width, device=DEV, dtype=dt)
+    cn.load_state_dict({"scale": p["channel_pre_norm.scale"]})
+    att = rg.LocalAttentionBlock(case.model_width, case.heads, case.window, device=DEV, dtype=dt)
+    att.load_state_dict({k[len("attention_block."):]: v for k, v in p.items()
+                         if k.startswith("attention_block.")})
+    mlp = rg.MLPBlock(case.model_width, case.expanded, device=DEV, dtype=dt)
+    mlp.load_state_dict({k[len("mlp_block."):]: v for k, v in p.items()
+                         if k.startswith("mlp_block.")})
+    y, cache = rg.residual_block(ic["x"], pos, tn, att, cn, mlp)
+    chk(y, "out"); chk(cache.keys, "keys"); chk(cache.values, "values")
+    for i in range(case.decode_steps):
+      y, cache = rg.residual_block(ic[f"x_step{i}"],
+                                   C.decode_positions(case, inp["segment_pos"], i).to(DEV),
+                                   tn, att, cn, mlp, cache)
+      chk(y, f"out_step{i}")
+
   elif case.kind == "mlp":
     m = rg.MLPBlock(case.model_width, case.expanded, device=DEV, dtype=case.torch_dtype)
     m.load_state_dict({k[len("mlp_block."):]: v for k, v in p.items()})

@@ -90,6 +90,22 @@ def test_oracle_matches_reference(case, oracle):
                                         case.heads, case.window, cache)
       chk(y, f"out_step{i}"); chk(cache[0], f"keys_step{i}"); chk(cache[1], f"values_step{i}")
       assert torch.equal(cache[2].long(), torch.from_numpy(g[f"num_tokens_step{i}"]))
+  elif case.kind == "resblock_attn":
+    w = tuple(p["attention_block." + k] for k in ("proj_q.weight", "proj_k.weight", "proj_v.weight",
+                                                  "proj_final.weight", "proj_final.bias"))
+    mlp = (p["channel_pre_norm.scale"], p["mlp_block.ffw_up.w"], p["mlp_block.ffw_up.b"],
+           p["mlp_block.ffw_down.weight"], p["mlp_block.ffw_down.bias"])
+    ns = p["temporal_pre_norm.scale"]
+    x = inp["x"]
+    y, cache = oracle.attention_block(oracle.rmsnorm(x, ns), pos, *w, case.heads, case.window)
+    r = (y.float() + x.float()).to(x.dtype)
+    chk(oracle.residual_channel(r, *mlp), "out"); chk(cache[0], "keys"); chk(cache[1], "values")
+    for i in range(case.decode_steps):
+      xs = inp[f"x_step{i}"]
+      y, cache = oracle.attention_block(oracle.rmsnorm(xs, ns), C.decode_positions(case, pos, i), *w,
+                                        case.heads, case.window, cache)
+      r = (y.float() + xs.float()).to(xs.dtype)
+      chk(oracle.residual_channel(r, *mlp), f"out_step{i}", True)
   elif case.kind == "mlp":
     chk(oracle.mlp(inp["x"], p["mlp_block.ffw_up.w"], p["mlp_block.ffw_up.b"],
                    p["mlp_block.ffw_down.weight"], p["mlp_block.ffw_down.bias"]), "out")
