@@ -399,7 +399,47 @@ def run_gpu(args, cfg):
     block_info["mlp_TFLOP/s"] = 6 * b * t * e * xw / (t_mlp * 1e-3) / 1e12
     block_info["residual_block_ms"] = t_full
     block_info["residual_block_tokens_per_s"] = b * t / (t_full * 1e-3)
-    del blk, x_in, norm, mlp
+    # The other temporal block of the model: local (sliding-window, multi-query) attention with the
+    # 2B model's geometry (10 heads of 256, window 2048): the block, its attention kernel alone
+    # (rotary embedding done), and the residual block of the attention kind.
+    heads, hd, window = 10, 256, 2048
+    att = rg.LocalAttentionBlock(e, heads, window, device=dev, dtype=dt)
+    att.load_state_dict({
+        "proj_q.weight": (torch.randn((e, e), generator=gb) * math.sqrt(1.0 / e)).to(dt).to(dev),
+        "proj_k.weight": (torch.randn((hd, e), generator=gb) * math.sqrt(1.0 / e)).to(dt).to(dev),
+        "proj_v.weight": (torch.randn((hd, e), generator=gb) * math.sqrt(1.0 / e)).to(dt).to(dev),
+        "proj_final.weight": (torch.randn((e, e), generator=gb) * math.sqrt(1.0 / e)).to(dt).to(dev),
+        "proj_final.bias": torch.zeros(e, dtype=dt, device=dev)})
+    q = torch.randn((b, t, heads, hd), generator=gb).to(dt).to(dev)
+    k = torch.randn((b, t, hd), generator=gb).to(dt).to(dev)
+    v = torch.randn((b, t, hd), generator=gb).to(dt).to(dev)
+    enc = torch.empty((b, t, heads * hd), dtype=dt, device=dev)
+    aws = _lib.workspace(dev, int(lib.rgk_attention_workspace_bytes(b, t)))
+    pos_i32 = 1 if pos.dtype == torch.int64 else 0
+
+    def k_attn():
+      _lib.check(lib.rgk_local_attention_prefill(
+          q.data_ptr(), k.data_ptr(), v.data_ptr(), pos.data_ptr(), pos_i32, b, t, heads, hd,
+          window, 1, enc.data_ptr(), aws.data_ptr(), aws.numel(), sp))
+
+    for _ in range(2):
+      rg.residual_block(x_in, pos, norm, att, norm, mlp)
+      k_attn()
+    torch.cuda.synchronize()
+    t_att = _time_loop(lambda: att(x_in, pos), ksteps, stream)
+    t_core = _time_loop(k_attn, ksteps, stream)
+    t_full_att = _time_loop(lambda: rg.residual_block(x_in, pos, norm, att, norm, mlp), ksteps,
+                            stream)
+    # 4 * head_dim flops per visible (query, key) pair; the kernel computes the logits twice
+    # (two-pass softmax), so its tensor work is 6 * head_dim per pair of every touched tile
+    pairs = b * heads * sum(min(i, window) + 1 for i in range(t))
+    block_info["attention"] = {
+        "what": "LocalAttentionBlock.forward prefill, 10 heads x 256, window 2048, same B and T",
+        "block_ms": t_att, "kernel_ms": t_core,
+        "kernel_useful_TFLOP/s": pairs * 4 * hd / (t_core * 1e-3) / 1e12,
+        "residual_block_ms": t_full_att,
+        "residual_block_tokens_per_s": b * t / (t_full_att * 1e-3)}
+    del blk, x_in, norm, mlp, att, q, k, v, enc
   if rank != 0:
     if world > 1:
       dist.destroy_process_group()

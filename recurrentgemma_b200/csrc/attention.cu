@@ -16,13 +16,19 @@
 // logits, forms the normalised probabilities, rounds them, and accumulates P V on the tensor cores.
 //
 // A unit of work is (sequence, query head, 128 queries); units are dealt out round-robin to
-// persistent CTAs.  Roles in a CTA (10 warps):
-//   warps 0-7  softmax: group g = warp / 4 takes the key tiles of parity g (its own S accumulator
-//              and P buffer), thread = query row (TMEM lane quarter warp % 4);
-//   warp 8     TMA producer: per key tile four K-slices of 64 of the query tile and of the key tile
-//              into a 3-stage ring, in pass 2 also the two 64-key slices of the transposed values;
-//   warp 9     TMEM allocation and MMA issue: S = Q K^T (M 128, N 128, 16 K-steps) into S[parity],
-//              O += P V (M 128, N 256, 8 K-steps) once the group has written P[parity].
+// persistent CTAs.  Roles in a CTA (18 warps):
+//   warps 0-15 softmax: group g = (warp / 4) % 2 takes the key tiles of parity g (its own S
+//              accumulator); a thread owns a query row (TMEM lane quarter warp % 4) and the 64 keys
+//              of column half warp / 8 of every tile of its group.  In pass 2 it writes the rounded
+//              probabilities back into tensor memory over the logits it has just read (two
+//              bfloat16 per 32-bit column, the layout of an operand A held in tensor memory);
+//   warp 16    TMA producer: the query tile once per unit (four slices of 64 of the head dimension,
+//              resident for both passes), the key tiles as slices of 64 into a 5-slot ring, in
+//              pass 2 also the two 64-key slices of the transposed values;
+//   warp 17    TMEM allocation and MMA issue: S = Q K^T (M 128, N 128, 16 K-steps) into S[parity],
+//              O += P V (M 128, N 256, 8 K-steps, A = P from tensor memory) once the group has
+//              written P.  The tensor pipe runs in issue order, so the next Q K^T into S[parity]
+//              cannot overtake the P V that reads P there.
 // TMEM: S[0], S[1] (128 columns each), O (256 columns).  All waits are bounded; on expiry the
 // status word is raised and the CTA runs to its end.
 #include <cuda.h>
@@ -104,28 +110,34 @@ __global__ void transpose_v_kernel(const __nv_bfloat16* __restrict__ v, int T_, 
 constexpr int kHd = 256;                  // head dimension = K of Q K^T, N of P V
 constexpr int kTq = 128, kTk = 128;       // queries / keys per tile
 constexpr int kSl = 64;                   // slice width (one 128-byte swizzle row of bfloat16)
-constexpr int kQkStage = 2 * kTq * kSl * 2;          // Q slice + K slice: 32 KiB
-constexpr int kRingA = 3;
+constexpr int kSlice = kTq * kSl * 2;                // a [128 x 64] bfloat16 slice: 16 KiB
+constexpr int kRingK = 5;                            // key slices in flight
 constexpr int kVStage = kHd * kSl * 2;               // a 64-key slice of V^T: 32 KiB
-constexpr int kPBytes = kTq * kTk * 2;               // 32 KiB per group
-constexpr int kOffQk = 0;
-constexpr int kOffV = kRingA * kQkStage;             //  98304
-constexpr int kOffP = kOffV + 2 * kVStage;           // 163840
-// The groups' partial (max, sum) of a row, float2 [2 groups][128 rows], are exchanged between the
-// passes through the first bytes of the P buffers: no MMA reads P then (the logits of this unit's
-// pass 1 were produced after the last P V of the previous unit, and tcgen05 runs in issue order).
-constexpr int kOffMl = kOffP;
-constexpr int kOffBarA = kOffP + 2 * kPBytes;        // 229376
-constexpr int kNumBarA = 2 * kRingA + 4 + 8 + 2;     // ring, v, s_full/s_empty/p_full/p_empty [2], o
+constexpr int kOffQ = 0;                             // the query tile, four slices
+constexpr int kOffK = (kHd / kSl) * kSlice;          //  65536
+constexpr int kOffV = kOffK + kRingK * kSlice;       // 147456
+// The partial (max, sum) of a row, float2 [2 groups x 2 column halves][128 rows], exchanged between
+// the passes.
+constexpr int kOffMl = kOffV + 2 * kVStage;          // 212992
+constexpr int kOffBarA = kOffMl + 4 * kTq * 8;       // 217088
+constexpr int kNumBarA = 2 + 2 * kRingK + 4 + 6 + 2; // q, key ring, v, s_full/s_empty/p_full [2], o
 constexpr int kOffTmemA = kOffBarA + kNumBarA * 8;
 constexpr int kOffAbortA = kOffTmemA + 4;
 constexpr int kSmemA = kOffAbortA + 4 + 1024;
 static_assert(kSmemA <= 232448, "exceeds the 227 KiB of shared memory a CTA may use");
-constexpr int kSoftWarps = 8;
+constexpr int kSoftWarps = 16;
 constexpr int kThreadsA = (kSoftWarps + 2) * 32;
 constexpr uint32_t kIdescS = tc_idesc_bf16(kTq, kTk);
 constexpr uint32_t kIdescO = tc_idesc_bf16(kTq, kHd);
 constexpr float kNegBig = -3.0e38f;
+
+// Two floats rounded to bfloat16 and widened again, through the packed conversion (the scalar one
+// occupies the special-function pipe that the exponentials need).
+__device__ __forceinline__ void round2_bf16(float a, float b, float& ra, float& rb) {
+  const uint32_t pk = pack_bf16x2(a, b);
+  ra = __uint_as_float(pk << 16);
+  rb = __uint_as_float(pk & 0xffff0000u);
+}
 
 __global__ void __launch_bounds__(kThreadsA, 1)
 attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -136,16 +148,16 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   const uint32_t s_base = smem_u32(smem);
   const uint32_t bar0 = s_base + kOffBarA;
-  auto bar_full = [&](int s) { return bar0 + 8u * s; };
-  auto bar_empty = [&](int s) { return bar0 + 8u * (kRingA + s); };
-  auto bar_v_full = [&](int s) { return bar0 + 8u * (2 * kRingA + s); };
-  auto bar_v_empty = [&](int s) { return bar0 + 8u * (2 * kRingA + 2 + s); };
-  auto bar_s_full = [&](int g) { return bar0 + 8u * (2 * kRingA + 4 + g); };
-  auto bar_s_empty = [&](int g) { return bar0 + 8u * (2 * kRingA + 6 + g); };
-  auto bar_p_full = [&](int g) { return bar0 + 8u * (2 * kRingA + 8 + g); };
-  auto bar_p_empty = [&](int g) { return bar0 + 8u * (2 * kRingA + 10 + g); };
-  const uint32_t bar_o_full = bar0 + 8u * (2 * kRingA + 12);
-  const uint32_t bar_o_empty = bar0 + 8u * (2 * kRingA + 13);
+  const uint32_t bar_q_full = bar0, bar_q_empty = bar0 + 8u;
+  auto bar_full = [&](int s) { return bar0 + 8u * (2 + s); };
+  auto bar_empty = [&](int s) { return bar0 + 8u * (2 + kRingK + s); };
+  auto bar_v_full = [&](int s) { return bar0 + 8u * (2 + 2 * kRingK + s); };
+  auto bar_v_empty = [&](int s) { return bar0 + 8u * (2 + 2 * kRingK + 2 + s); };
+  auto bar_s_full = [&](int g) { return bar0 + 8u * (2 + 2 * kRingK + 4 + g); };
+  auto bar_s_empty = [&](int g) { return bar0 + 8u * (2 + 2 * kRingK + 6 + g); };
+  auto bar_p_full = [&](int g) { return bar0 + 8u * (2 + 2 * kRingK + 8 + g); };
+  const uint32_t bar_o_full = bar0 + 8u * (2 + 2 * kRingK + 10);
+  const uint32_t bar_o_empty = bar0 + 8u * (2 + 2 * kRingK + 11);
   volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(smem + kOffTmemA);
   volatile int* s_abort = reinterpret_cast<volatile int*>(smem + kOffAbortA);
   float2* s_ml = reinterpret_cast<float2*>(smem + kOffMl);
@@ -156,14 +168,16 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
   if (threadIdx.x == 0) {
     *s_abort = 0;
-    for (int s = 0; s < kRingA; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
+    mbar_init(bar_q_full, 1);
+    mbar_init(bar_q_empty, 1);
+    for (int s = 0; s < kRingK; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar_v_full(s), 1); mbar_init(bar_v_empty(s), 1);
-      mbar_init(bar_s_full(s), 1); mbar_init(bar_s_empty(s), 4);
-      mbar_init(bar_p_full(s), 4); mbar_init(bar_p_empty(s), 1);
+      mbar_init(bar_s_full(s), 1); mbar_init(bar_s_empty(s), 8);
+      mbar_init(bar_p_full(s), 8);
     }
     mbar_init(bar_o_full, 1);
-    mbar_init(bar_o_empty, 4);
+    mbar_init(bar_o_empty, 8);
     mbar_fence_init();
   }
   if (warp == kSoftWarps + 1) {
@@ -189,31 +203,49 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
   if (warp == kSoftWarps) {
     // ------------------------------ TMA producer --------------------------------------------------
-    if (lane == 0) {
-      unsigned it = 0, iv = 0;
+    // The whole warp runs the loop and waits; one elected lane issues.
+    {
+      int slot = 0;
+      unsigned slot_phase = 1, iv = 0;
       bool ok = true;
       for (int i = 0; i < n_my && ok; ++i) {
         int b, n, t0, j_lo, j_hi;
         unit_of(i, b, n, t0, j_lo, j_hi);
+        // the query tile, once the previous unit's last Q K^T has read the old one
+        ok = mbar_wait(bar_q_empty, (i & 1) ^ 1, s_abort);
+        if (!ok) break;
+        if (elect_one()) {
+          mbar_expect_tx(bar_q_full, (kHd / kSl) * kSlice);
+#pragma unroll
+          for (int ks = 0; ks < kHd / kSl; ++ks)
+            tma_load_3d(s_base + kOffQ + ks * kSlice, &map_q, n * kHd + ks * kSl, t0, b, bar_q_full);
+        }
+        __syncwarp();
         for (int pass = 0; pass < 2 && ok; ++pass) {
           for (int j = j_lo; j <= j_hi && ok; ++j) {
-            for (int ks = 0; ks < kHd / kSl; ++ks, ++it) {
-              const int s = it % kRingA;
-              ok = mbar_wait(bar_empty(s), ((it / kRingA) & 1) ^ 1, s_abort);
+#pragma unroll
+            for (int ks = 0; ks < kHd / kSl; ++ks) {
+              if (ok) ok = mbar_wait(bar_empty(slot), slot_phase, s_abort);
               if (!ok) break;
-              mbar_expect_tx(bar_full(s), kQkStage);
-              const uint32_t dst = s_base + kOffQk + s * kQkStage;
-              tma_load_3d(dst, &map_q, n * kHd + ks * kSl, t0, b, bar_full(s));
-              tma_load_3d(dst + kTq * kSl * 2, &map_k, ks * kSl, j * kTk, b, bar_full(s));
+              if (elect_one()) {
+                mbar_expect_tx(bar_full(slot), kSlice);
+                tma_load_3d(s_base + kOffK + slot * kSlice, &map_k, ks * kSl, j * kTk, b,
+                            bar_full(slot));
+              }
+              __syncwarp();
+              if (++slot == kRingK) { slot = 0; slot_phase ^= 1; }
             }
             if (pass == 1 && ok) {
               for (int c = 0; c < kTk / kSl; ++c, ++iv) {
                 const int s = iv & 1;
                 ok = mbar_wait(bar_v_empty(s), ((iv >> 1) & 1) ^ 1, s_abort);
                 if (!ok) break;
-                mbar_expect_tx(bar_v_full(s), kVStage);
-                tma_load_3d(s_base + kOffV + s * kVStage, &map_vt, j * kTk + c * kSl, 0, b,
-                            bar_v_full(s));
+                if (elect_one()) {
+                  mbar_expect_tx(bar_v_full(s), kVStage);
+                  tma_load_3d(s_base + kOffV + s * kVStage, &map_vt, j * kTk + c * kSl, 0, b,
+                              bar_v_full(s));
+                }
+                __syncwarp();
               }
             }
           }
@@ -222,75 +254,95 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     }
   } else if (warp == kSoftWarps + 1) {
     // ------------------------------ MMA issue -----------------------------------------------------
-    if (lane == 0) {
-      unsigned it = 0, iv = 0;
+    // The whole warp runs the loop and waits; one elected lane issues.
+    {
+      int slot = 0;
+      unsigned slot_phase = 0, iv = 0;
       unsigned s_use[2] = {0, 0}, p_use[2] = {0, 0};
       bool ok = true;
       auto issue_qk = [&](int g) {
         // S[g] = Q K^T for the next key tile in the ring
         if (ok) ok = mbar_wait(bar_s_empty(g), (s_use[g] & 1) ^ 1, s_abort);
         ++s_use[g];
-        if (ok) tc_fence_after();
-        for (int ks = 0; ks < kHd / kSl && ok; ++ks, ++it) {
-          const int s = it % kRingA;
-          ok = mbar_wait(bar_full(s), (it / kRingA) & 1, s_abort);
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < kHd / kSl; ++ks) {
+          // (every lane sees the same barrier state and abort flag, so `ok` stays warp-uniform)
+          if (ok) ok = mbar_wait(bar_full(slot), slot_phase, s_abort);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t q0 = s_base + kOffQk + s * kQkStage, k0 = q0 + kTq * kSl * 2;
+          // a K step of 16 bfloat16 is 32 bytes = 2 units of the descriptor's start address
+          const uint64_t dq = smem_desc_sw128(s_base + kOffQ + ks * kSlice);
+          const uint64_t dk = smem_desc_sw128(s_base + kOffK + slot * kSlice);
+          if (elect_one()) {
 #pragma unroll
-          for (int kk = 0; kk < kSl / 16; ++kk)
-            tc_mma_bf16(tmem_base + g * kTk, smem_desc_sw128(q0 + kk * 32), smem_desc_sw128(k0 + kk * 32),
-                        kIdescS, (ks | kk) != 0 ? 1u : 0u);
-          tc_commit(bar_empty(s));
+            for (int kk = 0; kk < kSl / 16; ++kk)
+              tc_mma_bf16(tmem_base + g * kTk, dq + 2 * kk, dk + 2 * kk, kIdescS,
+                          (ks | kk) != 0 ? 1u : 0u);
+            tc_commit(bar_empty(slot));
+          }
+          __syncwarp();
+          if (++slot == kRingK) { slot = 0; slot_phase ^= 1; }
         }
-        if (ok) tc_commit(bar_s_full(g));
+        if (ok && elect_one()) tc_commit(bar_s_full(g));
+        __syncwarp();
       };
       auto issue_pv = [&](int g, bool first) {
-        // O += P[g] V for the key tile whose probabilities group g has just written
+        // O += P V for the key tile whose probabilities group g has just written over S[g]: the
+        // keys of half c are the 32 columns from S[g] + 64 c, 8 columns per K step of 16
         if (ok) ok = mbar_wait(bar_p_full(g), p_use[g] & 1, s_abort);
         ++p_use[g];
-        if (ok) tc_fence_after();
-        for (int c = 0; c < kTk / kSl && ok; ++c, ++iv) {
+        tc_fence_after();
+        for (int c = 0; c < kTk / kSl; ++c, ++iv) {
           const int s = iv & 1;
-          ok = mbar_wait(bar_v_full(s), (iv >> 1) & 1, s_abort);
+          if (ok) ok = mbar_wait(bar_v_full(s), (iv >> 1) & 1, s_abort);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t p0 = s_base + kOffP + g * kPBytes + c * (kTq * kSl * 2);
-          const uint32_t v0 = s_base + kOffV + s * kVStage;
+          const uint32_t p0 = tmem_base + g * kTk + c * 64;
+          const uint64_t dv = smem_desc_sw128(s_base + kOffV + s * kVStage);
+          if (elect_one()) {
 #pragma unroll
-          for (int kk = 0; kk < kSl / 16; ++kk)
-            tc_mma_bf16(tmem_base + 2 * kTk, smem_desc_sw128(p0 + kk * 32), smem_desc_sw128(v0 + kk * 32),
-                        kIdescO, (first && c == 0 && kk == 0) ? 0u : 1u);
-          tc_commit(bar_v_empty(s));
+            for (int kk = 0; kk < kSl / 16; ++kk)
+              tc_mma_bf16_ts(tmem_base + 2 * kTk, p0 + kk * 8, dv + 2 * kk, kIdescO,
+                             (first && c == 0 && kk == 0) ? 0u : 1u);
+            tc_commit(bar_v_empty(s));
+          }
+          __syncwarp();
         }
-        if (ok) tc_commit(bar_p_empty(g));
       };
-      for (int i = 0; i < n_my && ok; ++i) {
+      for (int i = 0; i < n_my; ++i) {
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
         int b, n, t0, j_lo, j_hi;
         unit_of(i, b, n, t0, j_lo, j_hi);
         const int nt = j_hi - j_lo + 1;
+        ok = mbar_wait(bar_q_full, i & 1, s_abort);
         // pass 1: logits only
         for (int j = 0; j < nt && ok; ++j) issue_qk(j & 1);
         // pass 2: logits one tile ahead of the probabilities
         if (ok) ok = mbar_wait(bar_o_empty, (i & 1) ^ 1, s_abort);
-        if (ok) tc_fence_after();
-        if (nt > 0) issue_qk(0);
+        tc_fence_after();
+        if (nt > 0 && ok) issue_qk(0);
         for (int j = 0; j < nt && ok; ++j) {
           if (j + 1 < nt) issue_qk((j + 1) & 1);
-          issue_pv(j & 1, j == 0);
+          if (j + 1 == nt && ok) {                 // the unit's last Q K^T is in the pipe
+            if (elect_one()) tc_commit(bar_q_empty);
+            __syncwarp();
+          }
+          if (ok) issue_pv(j & 1, j == 0);
         }
-        if (ok) tc_commit(bar_o_full);
+        if (ok && elect_one()) tc_commit(bar_o_full);
+        __syncwarp();
       }
     }
   } else {
     // ------------------------------ softmax and epilogue ------------------------------------------
-    const int g = warp >> 2, quarter = warp & 3;
+    const int g = (warp >> 2) & 1, quarter = warp & 3, chalf = warp >> 3;
     const int row = quarter * 32 + lane;                     // query row inside the tile = TMEM lane
-    const uint32_t t_s = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + g * kTk;
-    const uint32_t t_o = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + 2 * kTk;
-    uint8_t* p_buf = smem + kOffP + g * kPBytes;
+    const uint32_t t_s = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + g * kTk + chalf * 64;
+    const uint32_t t_o = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + 2 * kTk + chalf * 128;
     constexpr float kScale = 0.0625f * 1.4426950408889634f;  // hd^-1/2 log2(e): exponent per logit unit
-    unsigned cs = 0, cp = 0;
+    unsigned cs = 0;
     bool ok = true;
     for (int i = 0; i < n_my; ++i) {
       int b, n, t0, j_lo, j_hi;
@@ -302,15 +354,15 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       const int lo = row_ok ? lo_all[(int64_t)b * T_ + t] : 0;
       const int hi = row_ok ? t : 0;
 
-      // ---- pass 1: row maximum and sum over this group's key tiles --------------------------------
+      // ---- pass 1: row maximum and sum over this thread's keys ------------------------------------
       float m = kNegBig, l = 0.0f;
       for (int j = g; j < nt; j += 2) {
         if (ok) ok = mbar_wait(bar_s_full(g), cs & 1, s_abort);
         ++cs;
         tc_fence_after();
-        const int s0 = (j_lo + j) * kTk;
+        const int s0 = (j_lo + j) * kTk + chalf * 64;
 #pragma unroll 1
-        for (int cc = 0; cc < 4; ++cc) {
+        for (int cc = 0; cc < 2; ++cc) {
           uint32_t acc[32];
           if (ok) {
             tc_ld_32x32(t_s + cc * 32, acc);
@@ -322,50 +374,68 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           const int sc = s0 + cc * 32;
           float v[32];
           float cm = kNegBig;
+          if (sc > hi || sc + 31 < lo) {                    // nothing visible in these 32 keys
 #pragma unroll
-          for (int c = 0; c < 32; ++c) {
-            const float sv = round_bf16(__uint_as_float(acc[c]));
-            v[c] = (sc + c >= lo && sc + c <= hi) ? sv : kNegBig;
-            cm = fmaxf(cm, v[c]);
+            for (int c = 0; c < 32; ++c) v[c] = kNegBig;
+          } else if (sc >= lo && sc + 31 <= hi) {           // all visible: the common case
+#pragma unroll
+            for (int c = 0; c < 32; c += 2) {
+              round2_bf16(__uint_as_float(acc[c]), __uint_as_float(acc[c + 1]), v[c], v[c + 1]);
+              cm = fmaxf(cm, fmaxf(v[c], v[c + 1]));
+            }
+          } else {
+#pragma unroll
+            for (int c = 0; c < 32; c += 2) {
+              round2_bf16(__uint_as_float(acc[c]), __uint_as_float(acc[c + 1]), v[c], v[c + 1]);
+              if (!(sc + c >= lo && sc + c <= hi)) v[c] = kNegBig;
+              if (!(sc + c + 1 >= lo && sc + c + 1 <= hi)) v[c + 1] = kNegBig;
+              cm = fmaxf(cm, fmaxf(v[c], v[c + 1]));
+            }
           }
           if (cm > kNegBig) {
             const float m_new = fmaxf(m, cm);
+            const float off = -m_new * kScale;
             float add = 0.0f;
+            // a masked key contributes 2^(-huge) = 0
 #pragma unroll
-            for (int c = 0; c < 32; ++c) add += v[c] > kNegBig ? ex2f((v[c] - m_new) * kScale) : 0.0f;
-            l = l * ex2f((m - m_new) * kScale) + add;
+            for (int c = 0; c < 32; ++c) add += ex2f(fmaf(v[c], kScale, off));
+            l = l * ex2f(fmaxf((m - m_new) * kScale, -200.0f)) + add;
             m = m_new;
           }
+          __syncwarp();
         }
         tc_fence_before();
         __syncwarp();
         if (lane == 0 && ok) mbar_arrive(bar_s_empty(g));
       }
-      // both groups' partial (m, l) -> the row's final ones
-      s_ml[g * kTq + row] = make_float2(m, l);
+      // the four partial (m, l) of a row -> its final ones
+      s_ml[(g * 2 + chalf) * kTq + row] = make_float2(m, l);
       named_bar_sync(1, kSoftWarps * 32);
       {
-        const float2 o = s_ml[(g ^ 1) * kTq + row];
-        const float m_all = fmaxf(m, o.x);
+        float m_all = kNegBig;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) m_all = fmaxf(m_all, s_ml[k * kTq + row].x);
         float l_all = 0.0f;
-        if (m > kNegBig) l_all += l * ex2f((m - m_all) * kScale);
-        if (o.x > kNegBig) l_all += o.y * ex2f((o.x - m_all) * kScale);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 o = s_ml[k * kTq + row];
+          if (o.x > kNegBig) l_all += o.y * ex2f((o.x - m_all) * kScale);
+        }
         m = m_all;
         l = l_all;
       }
-      named_bar_sync(1, kSoftWarps * 32);      // s_ml may be rewritten by the next unit
-      const float inv_l = l > 0.0f ? 1.0f / l : 0.0f;
+      named_bar_sync(1, kSoftWarps * 32);      // the exchange area may be rewritten from here on
+      // p = 2^(s k - (m k + log2 l)): the normalisation rides in the exponent
+      const float off2 = -(m * kScale + log2f(fmaxf(l, 1e-30f)));
 
       // ---- pass 2: normalised probabilities, rounded, into P[g] -----------------------------------
       for (int j = g; j < nt; j += 2) {
         if (ok) ok = mbar_wait(bar_s_full(g), cs & 1, s_abort);
         ++cs;
-        if (ok) ok = mbar_wait(bar_p_empty(g), (cp & 1) ^ 1, s_abort);
-        ++cp;
         tc_fence_after();
-        const int s0 = (j_lo + j) * kTk;
+        const int s0 = (j_lo + j) * kTk + chalf * 64;
 #pragma unroll 1
-        for (int cc = 0; cc < 4; ++cc) {
+        for (int cc = 0; cc < 2; ++cc) {
           uint32_t acc[32];
           if (ok) {
             tc_ld_32x32(t_s + cc * 32, acc);
@@ -376,26 +446,33 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           }
           const int sc = s0 + cc * 32;
           uint32_t pk[16];
+          if (sc >= lo && sc + 31 <= hi) {                  // all visible
 #pragma unroll
-          for (int c = 0; c < 32; c += 2) {
-            float p0 = 0.0f, p1 = 0.0f;
-            if (sc + c >= lo && sc + c <= hi)
-              p0 = ex2f((round_bf16(__uint_as_float(acc[c])) - m) * kScale) * inv_l;
-            if (sc + c + 1 >= lo && sc + c + 1 <= hi)
-              p1 = ex2f((round_bf16(__uint_as_float(acc[c + 1])) - m) * kScale) * inv_l;
-            pk[c >> 1] = pack_bf16x2(p0, p1);
-          }
-          // 32 keys = 64 bytes = four 16-byte units of this row in slice cc / 2
-          uint8_t* prow = p_buf + (cc >> 1) * (kTq * kSl * 2) + row * 128;
+            for (int c = 0; c < 32; c += 2) {
+              float s0v, s1v;
+              round2_bf16(__uint_as_float(acc[c]), __uint_as_float(acc[c + 1]), s0v, s1v);
+              pk[c >> 1] = pack_bf16x2(ex2f(fmaf(s0v, kScale, off2)), ex2f(fmaf(s1v, kScale, off2)));
+            }
+          } else if (sc > hi || sc + 31 < lo) {             // none visible
 #pragma unroll
-          for (int u4 = 0; u4 < 4; ++u4) {
-            const int unit = (cc & 1) * 4 + u4;
-            *reinterpret_cast<uint4*>(prow + ((unit ^ (row & 7)) << 4)) =
-                make_uint4(pk[4 * u4], pk[4 * u4 + 1], pk[4 * u4 + 2], pk[4 * u4 + 3]);
+            for (int c = 0; c < 16; ++c) pk[c] = 0u;
+          } else {
+#pragma unroll
+            for (int c = 0; c < 32; c += 2) {
+              float s0v, s1v;
+              round2_bf16(__uint_as_float(acc[c]), __uint_as_float(acc[c + 1]), s0v, s1v);
+              const float p0 = (sc + c >= lo && sc + c <= hi) ? ex2f(fmaf(s0v, kScale, off2)) : 0.0f;
+              const float p1 =
+                  (sc + c + 1 >= lo && sc + c + 1 <= hi) ? ex2f(fmaf(s1v, kScale, off2)) : 0.0f;
+              pk[c >> 1] = pack_bf16x2(p0, p1);
+            }
           }
+          // 32 keys = 16 columns, over logits this thread has already read
+          __syncwarp();
+          if (ok) tc_st_32x16(t_s + cc * 16, pk);
         }
+        tc_wait_st();
         tc_fence_before();
-        fence_proxy_async();
         __syncwarp();
         if (lane == 0 && ok) {
           mbar_arrive(bar_s_empty(g));
@@ -407,9 +484,10 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       if (g == 0) {
         if (ok) ok = mbar_wait(bar_o_full, i & 1, s_abort);
         tc_fence_after();
-        __nv_bfloat16* orow = out + ((int64_t)b * T_ + t) * ((int64_t)N * kHd) + (int64_t)n * kHd;
+        __nv_bfloat16* orow = out + ((int64_t)b * T_ + t) * ((int64_t)N * kHd) + (int64_t)n * kHd +
+                              chalf * 128;
 #pragma unroll 1
-        for (int cc = 0; cc < kHd / 32; ++cc) {
+        for (int cc = 0; cc < 4; ++cc) {
           uint32_t acc[32];
           if (ok) {
             tc_ld_32x32(t_o + cc * 32, acc);
