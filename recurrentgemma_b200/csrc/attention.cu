@@ -23,12 +23,13 @@
 //              probabilities back into tensor memory over the logits it has just read (two
 //              bfloat16 per 32-bit column, the layout of an operand A held in tensor memory);
 //   warp 16    TMA producer: the query tile once per unit (four slices of 64 of the head dimension,
-//              resident for both passes), the key tiles as slices of 64 into a 5-slot ring, in
-//              pass 2 also the two 64-key slices of the transposed values;
-//   warp 17    TMEM allocation and MMA issue: S = Q K^T (M 128, N 128, 16 K-steps) into S[parity],
-//              O += P V (M 128, N 256, 8 K-steps, A = P from tensor memory) once the group has
-//              written P.  The tensor pipe runs in issue order, so the next Q K^T into S[parity]
-//              cannot overtake the P V that reads P there.
+//              resident for both passes) and the key tiles as slices of 64 into a 5-slot ring;
+//   warp 19    TMA producer of the transposed values (two 64-key slices per key tile of pass 2);
+//   warp 17    TMEM allocation and issue of S = Q K^T (M 128, N 128, 16 K-steps) into S[parity];
+//   warp 18    issue of O += P V (M 128, N 256, 8 K-steps, A = P from tensor memory) once the
+//              group has written P.  Two issuing warps, so that a P V never queues behind the
+//              sixteen instructions of the next Q K^T; the Q K^T warp waits for the P V that read
+//              P from S[parity] before it overwrites S[parity].
 // TMEM: S[0], S[1] (128 columns each), O (256 columns).  All waits are bounded; on expiry the
 // status word is raised and the CTA runs to its end.
 #include <cuda.h>
@@ -120,13 +121,13 @@ constexpr int kOffV = kOffK + kRingK * kSlice;       // 147456
 // the passes.
 constexpr int kOffMl = kOffV + 2 * kVStage;          // 212992
 constexpr int kOffBarA = kOffMl + 4 * kTq * 8;       // 217088
-constexpr int kNumBarA = 2 + 2 * kRingK + 4 + 6 + 2; // q, key ring, v, s_full/s_empty/p_full [2], o
+constexpr int kNumBarA = 2 + 2 * kRingK + 4 + 8 + 2; // q, key ring, v, s_full/s_empty/p_full/pv_done [2], o
 constexpr int kOffTmemA = kOffBarA + kNumBarA * 8;
 constexpr int kOffAbortA = kOffTmemA + 4;
 constexpr int kSmemA = kOffAbortA + 4 + 1024;
 static_assert(kSmemA <= 232448, "exceeds the 227 KiB of shared memory a CTA may use");
 constexpr int kSoftWarps = 16;
-constexpr int kThreadsA = (kSoftWarps + 2) * 32;
+constexpr int kThreadsA = (kSoftWarps + 4) * 32;
 constexpr uint32_t kIdescS = tc_idesc_bf16(kTq, kTk);
 constexpr uint32_t kIdescO = tc_idesc_bf16(kTq, kHd);
 constexpr float kNegBig = -3.0e38f;
@@ -156,8 +157,9 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   auto bar_s_full = [&](int g) { return bar0 + 8u * (2 + 2 * kRingK + 4 + g); };
   auto bar_s_empty = [&](int g) { return bar0 + 8u * (2 + 2 * kRingK + 6 + g); };
   auto bar_p_full = [&](int g) { return bar0 + 8u * (2 + 2 * kRingK + 8 + g); };
-  const uint32_t bar_o_full = bar0 + 8u * (2 + 2 * kRingK + 10);
-  const uint32_t bar_o_empty = bar0 + 8u * (2 + 2 * kRingK + 11);
+  auto bar_pv_done = [&](int g) { return bar0 + 8u * (2 + 2 * kRingK + 10 + g); };
+  const uint32_t bar_o_full = bar0 + 8u * (2 + 2 * kRingK + 12);
+  const uint32_t bar_o_empty = bar0 + 8u * (2 + 2 * kRingK + 13);
   volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(smem + kOffTmemA);
   volatile int* s_abort = reinterpret_cast<volatile int*>(smem + kOffAbortA);
   float2* s_ml = reinterpret_cast<float2*>(smem + kOffMl);
@@ -175,6 +177,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       mbar_init(bar_v_full(s), 1); mbar_init(bar_v_empty(s), 1);
       mbar_init(bar_s_full(s), 1); mbar_init(bar_s_empty(s), 8);
       mbar_init(bar_p_full(s), 8);
+      mbar_init(bar_pv_done(s), 1);
     }
     mbar_init(bar_o_full, 1);
     mbar_init(bar_o_empty, 8);
@@ -206,7 +209,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     // The whole warp runs the loop and waits; one elected lane issues.
     {
       int slot = 0;
-      unsigned slot_phase = 1, iv = 0;
+      unsigned slot_phase = 1;
       bool ok = true;
       for (int i = 0; i < n_my && ok; ++i) {
         int b, n, t0, j_lo, j_hi;
@@ -235,45 +238,66 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
               __syncwarp();
               if (++slot == kRingK) { slot = 0; slot_phase ^= 1; }
             }
-            if (pass == 1 && ok) {
-              for (int c = 0; c < kTk / kSl; ++c, ++iv) {
-                const int s = iv & 1;
-                ok = mbar_wait(bar_v_empty(s), ((iv >> 1) & 1) ^ 1, s_abort);
-                if (!ok) break;
-                if (elect_one()) {
-                  mbar_expect_tx(bar_v_full(s), kVStage);
-                  tma_load_3d(s_base + kOffV + s * kVStage, &map_vt, j * kTk + c * kSl, 0, b,
-                              bar_v_full(s));
-                }
-                __syncwarp();
-              }
+          }
+        }
+      }
+    }
+  } else if (warp == kSoftWarps + 3) {
+    // ------------------------------ TMA producer of V^T -------------------------------------------
+    {
+      unsigned iv = 0;
+      bool ok = true;
+      for (int i = 0; i < n_my && ok; ++i) {
+        int b, n, t0, j_lo, j_hi;
+        unit_of(i, b, n, t0, j_lo, j_hi);
+        for (int j = j_lo; j <= j_hi && ok; ++j) {
+#pragma unroll
+          for (int c = 0; c < kTk / kSl; ++c, ++iv) {
+            const int s = iv & 1;
+            if (ok) ok = mbar_wait(bar_v_empty(s), ((iv >> 1) & 1) ^ 1, s_abort);
+            if (!ok) break;
+            if (elect_one()) {
+              mbar_expect_tx(bar_v_full(s), kVStage);
+              tma_load_3d(s_base + kOffV + s * kVStage, &map_vt, j * kTk + c * kSl, 0, b,
+                          bar_v_full(s));
             }
+            __syncwarp();
           }
         }
       }
     }
   } else if (warp == kSoftWarps + 1) {
-    // ------------------------------ MMA issue -----------------------------------------------------
+    // ------------------------------ Q K^T issue ---------------------------------------------------
     // The whole warp runs the loop and waits; one elected lane issues.
     {
       int slot = 0;
-      unsigned slot_phase = 0, iv = 0;
-      unsigned s_use[2] = {0, 0}, p_use[2] = {0, 0};
+      unsigned slot_phase = 0;
+      unsigned s_use[2] = {0, 0};
+      unsigned pv_issued[2] = {0, 0}, pv_seen[2] = {0, 0};   // P V on S[g]: scheduled / waited for
       bool ok = true;
+      bool k_ready = false;      // the next key slice was already there when last asked
       auto issue_qk = [&](int g) {
-        // S[g] = Q K^T for the next key tile in the ring
+        // S[g] = Q K^T for the next key tile in the ring, once the softmax warps have read the old
+        // logits and every P V that takes its probabilities from S[g] has completed
         if (ok) ok = mbar_wait(bar_s_empty(g), (s_use[g] & 1) ^ 1, s_abort);
         ++s_use[g];
+        while (ok && pv_seen[g] != pv_issued[g]) {
+          ok = mbar_wait(bar_pv_done(g), pv_seen[g] & 1, s_abort);
+          ++pv_seen[g];
+        }
         tc_fence_after();
 #pragma unroll
         for (int ks = 0; ks < kHd / kSl; ++ks) {
           // (every lane sees the same barrier state and abort flag, so `ok` stays warp-uniform)
-          if (ok) ok = mbar_wait(bar_full(slot), slot_phase, s_abort);
+          if (ok && !k_ready) ok = mbar_wait(bar_full(slot), slot_phase, s_abort);
           if (!ok) break;
           tc_fence_after();
           // a K step of 16 bfloat16 is 32 bytes = 2 units of the descriptor's start address
           const uint64_t dq = smem_desc_sw128(s_base + kOffQ + ks * kSlice);
           const uint64_t dk = smem_desc_sw128(s_base + kOffK + slot * kSlice);
+          // ask about the slice after this one now; the answer is looked at after the issue
+          const int slot_n = slot + 1 == kRingK ? 0 : slot + 1;
+          k_ready = mbar_test(bar_full(slot_n), slot_n == 0 ? slot_phase ^ 1 : slot_phase);
           if (elect_one()) {
 #pragma unroll
             for (int kk = 0; kk < kSl / 16; ++kk)
@@ -287,29 +311,6 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         if (ok && elect_one()) tc_commit(bar_s_full(g));
         __syncwarp();
       };
-      auto issue_pv = [&](int g, bool first) {
-        // O += P V for the key tile whose probabilities group g has just written over S[g]: the
-        // keys of half c are the 32 columns from S[g] + 64 c, 8 columns per K step of 16
-        if (ok) ok = mbar_wait(bar_p_full(g), p_use[g] & 1, s_abort);
-        ++p_use[g];
-        tc_fence_after();
-        for (int c = 0; c < kTk / kSl; ++c, ++iv) {
-          const int s = iv & 1;
-          if (ok) ok = mbar_wait(bar_v_full(s), (iv >> 1) & 1, s_abort);
-          if (!ok) break;
-          tc_fence_after();
-          const uint32_t p0 = tmem_base + g * kTk + c * 64;
-          const uint64_t dv = smem_desc_sw128(s_base + kOffV + s * kVStage);
-          if (elect_one()) {
-#pragma unroll
-            for (int kk = 0; kk < kSl / 16; ++kk)
-              tc_mma_bf16_ts(tmem_base + 2 * kTk, p0 + kk * 8, dv + 2 * kk, kIdescO,
-                             (first && c == 0 && kk == 0) ? 0u : 1u);
-            tc_commit(bar_v_empty(s));
-          }
-          __syncwarp();
-        }
-      };
       for (int i = 0; i < n_my; ++i) {
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
@@ -319,17 +320,56 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         ok = mbar_wait(bar_q_full, i & 1, s_abort);
         // pass 1: logits only
         for (int j = 0; j < nt && ok; ++j) issue_qk(j & 1);
-        // pass 2: logits one tile ahead of the probabilities
-        if (ok) ok = mbar_wait(bar_o_empty, (i & 1) ^ 1, s_abort);
-        tc_fence_after();
-        if (nt > 0 && ok) issue_qk(0);
+        // pass 2: the logits again; the other warp issues P V for tile j once its P is written
         for (int j = 0; j < nt && ok; ++j) {
-          if (j + 1 < nt) issue_qk((j + 1) & 1);
-          if (j + 1 == nt && ok) {                 // the unit's last Q K^T is in the pipe
-            if (elect_one()) tc_commit(bar_q_empty);
+          issue_qk(j & 1);
+          ++pv_issued[j & 1];
+        }
+        if (ok && elect_one()) tc_commit(bar_q_empty);       // the unit's last Q K^T is in the pipe
+        __syncwarp();
+      }
+    }
+  } else if (warp == kSoftWarps + 2) {
+    // ------------------------------ P V issue -----------------------------------------------------
+    {
+      unsigned iv = 0;
+      unsigned p_use[2] = {0, 0};
+      bool ok = true;
+      for (int i = 0; i < n_my; ++i) {
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        int b, n, t0, j_lo, j_hi;
+        unit_of(i, b, n, t0, j_lo, j_hi);
+        const int nt = j_hi - j_lo + 1;
+        // the epilogue has read the previous unit's accumulator
+        ok = mbar_wait(bar_o_empty, (i & 1) ^ 1, s_abort);
+        tc_fence_after();
+        for (int j = 0; j < nt && ok; ++j) {
+          // O += P V for the key tile whose probabilities group g has just written over S[g]: the
+          // keys of half c are the 32 columns from S[g] + 64 c, 8 columns per K step of 16
+          const int g = j & 1;
+          ok = mbar_wait(bar_p_full(g), p_use[g] & 1, s_abort);
+          ++p_use[g];
+          tc_fence_after();
+#pragma unroll
+          for (int c = 0; c < kTk / kSl; ++c, ++iv) {
+            const int s = iv & 1;
+            if (ok) ok = mbar_wait(bar_v_full(s), (iv >> 1) & 1, s_abort);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t p0 = tmem_base + g * kTk + c * 64;
+            const uint64_t dv = smem_desc_sw128(s_base + kOffV + s * kVStage);
+            if (elect_one()) {
+#pragma unroll
+              for (int kk = 0; kk < kSl / 16; ++kk)
+                tc_mma_bf16_ts(tmem_base + 2 * kTk, p0 + kk * 8, dv + 2 * kk, kIdescO,
+                               (j == 0 && c == 0 && kk == 0) ? 0u : 1u);
+              tc_commit(bar_v_empty(s));
+            }
             __syncwarp();
           }
-          if (ok) issue_pv(j & 1, j == 0);
+          if (ok && elect_one()) tc_commit(bar_pv_done(g));
+          __syncwarp();
         }
         if (ok && elect_one()) tc_commit(bar_o_full);
         __syncwarp();

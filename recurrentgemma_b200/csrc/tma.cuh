@@ -37,6 +37,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity,
       : "=r"(ok) : "r"(bar), "r"(parity), "r"(hint_ns) : "memory");
   return ok != 0;
 }
+// Non-blocking test of a phase; lets a caller ask early and look at the answer later.
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,
                                             uint32_t bar) {
   asm volatile(
