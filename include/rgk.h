@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define RGK_ABI_VERSION 5
+#define RGK_ABI_VERSION 6
 
 #if defined(__GNUC__)
 #define RGK_API __attribute__((visibility("default")))
@@ -305,6 +305,25 @@ RGK_API int rgk_local_attention_prefill(const void* q, const void* k, const void
                                         const void* segment_pos, int pos_dtype, int64_t B, int64_t T,
                                         int N, int head_dim, int window, int dtype, void* out,
                                         void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * The two ends of Griffin.forward around the residual blocks, and greedy sampling.
+ * rgk_embed: Embedder.encode (recurrentgemma/torch/modules.py:991-998): out [M,D] =
+ *   table[tokens[m], :] * scale (scale = sqrt(D) rounded to bfloat16, or 1), tokens RGK_I32 or
+ *   RGK_I64, float32 or bfloat16, D a multiple of a 16-byte pack.  A token outside
+ *   [0, V) reads the nearest row (the reference raises).
+ * rgk_logits: Embedder.decode followed by the soft cap (torch/modules.py:1001-1003,
+ *   torch/griffin.py:180-185): out [M,V] = x [M,D] table[V,D]^T, then tanh(. / cap) * cap when
+ *   cap != 0, with the bfloat16 rounding of each of the reference's tensor operations.  tcgen05
+ *   GEMM, bfloat16 only, D and V multiples of 8.  status: as for rgk_dense_linear.
+ * rgk_argmax: torch.argmax(logits, dim=-1) (torch/sampler.py:131-132): out [M] int32 = index of
+ *   the first maximum of every row of x [M,V], float32 or bfloat16.
+ * ---------------------------------------------------------------------------------------------- */
+RGK_API int rgk_embed(const void* tokens, int token_dtype, const void* table, int64_t M, int64_t V,
+                      int64_t D, float scale, int dtype, void* out, void* stream);
+RGK_API int rgk_logits(const void* x, const void* table, int64_t M, int64_t D, int64_t V, float cap,
+                       int dtype, void* out, int* status, void* stream);
+RGK_API int rgk_argmax(const void* x, int64_t M, int64_t V, int dtype, int* out, void* stream);
 
 /* Scratch needed by the calls above for a problem of this size (an upper bound over the entry
  * points, so one buffer serves all of them).  Returns 0 on invalid arguments. */

@@ -337,3 +337,53 @@ def params_of(state_dict: dict, prefix: str = "") -> dict:
       "gate_a_w": "rg_lru.a_gate.w", "gate_a_b": "rg_lru.a_gate.b",
   }
   return {k: state_dict[prefix + v] for k, v in names.items() if prefix + v in state_dict}
+
+
+def embed(tokens: torch.Tensor, table: torch.Tensor, scale_by_sqrt_dim: bool) -> torch.Tensor:
+  """Embedder.encode (modules.py:991-998): rows of the table, times sqrt(width) rounded to bfloat16."""
+  x = _f(table)[tokens.numpy().astype(np.int64)]
+  if scale_by_sqrt_dim:
+    scale = float(torch.tensor(float(np.sqrt(table.shape[1]))).to(torch.bfloat16))
+    x = x * np.float32(scale)
+  return _t(x, table.dtype)
+
+
+def logits(x: torch.Tensor, table: torch.Tensor, soft_cap: float) -> torch.Tensor:
+  """Embedder.decode and the soft cap (modules.py:1001-1003, griffin.py:180-185): each of the
+  contraction, the division, the tanh and the product is one tensor operation of the reference,
+  rounded to the activation dtype."""
+  out = linear(x, table, None)
+  if soft_cap:
+    r = lambda a: _f(_t(a, x.dtype))            # round to the activation dtype, back to float32
+    q = r(_f(out) / np.float32(soft_cap))
+    out = _t(r(np.tanh(q.astype(np.float64)).astype(np.float32)) * np.float32(soft_cap), x.dtype)
+  return out
+
+
+def griffin(sd: dict, block_kinds, num_heads: int, window: int, soft_cap: float,
+            tokens: torch.Tensor, segment_pos: torch.Tensor, cache=None):
+  """Griffin.forward (griffin.py:136-194) from the pieces above.  sd: the model's state_dict;
+  cache: None or {"blocks.i": (h, conv) | (keys, values, num_tokens)}.  Returns (logits, cache)."""
+  x = embed(tokens, sd["embedder.input_embedding"], True)
+  new_cache = {}
+  for i, kind in enumerate(block_kinds):
+    pre = f"blocks.{i}."
+    p = {k[len(pre):]: v for k, v in sd.items() if k.startswith(pre)}
+    mlp_p = (p["channel_pre_norm.scale"], p["mlp_block.ffw_up.w"], p["mlp_block.ffw_up.b"],
+             p["mlp_block.ffw_down.weight"], p["mlp_block.ffw_down.bias"])
+    c = None if cache is None else cache[pre[:-1]]
+    if kind == "recurrent":
+      op = params_of(p, "recurrent_block.")
+      h0, conv = (None, None) if c is None else c
+      r, h, conv = residual_temporal(x, segment_pos, p["temporal_pre_norm.scale"], op, h0, conv)
+      new_cache[pre[:-1]] = (h, conv)
+    else:
+      w = tuple(p["attention_block." + k] for k in ("proj_q.weight", "proj_k.weight",
+                                                    "proj_v.weight", "proj_final.weight",
+                                                    "proj_final.bias"))
+      y, ac = attention_block(rmsnorm(x, p["temporal_pre_norm.scale"]), segment_pos, *w, num_heads,
+                              window, c)
+      r = (y.float() + x.float()).to(x.dtype)
+      new_cache[pre[:-1]] = ac
+    x = residual_channel(r, *mlp_p)
+  return logits(rmsnorm(x, sd["final_norm.scale"]), sd["embedder.input_embedding"], soft_cap), new_cache

@@ -6,13 +6,16 @@ forward does, and raises if it has not been built.
 """
 from recurrentgemma_b200.layers import (BlockDiagonalLinear, Conv1D, Einsum, RGLRU, RMSNorm,
                                         rnn_scan)
-from recurrentgemma_b200.modules import (AttentionBlockCache, LocalAttentionBlock, MLPBlock,
-                                         RecurrentBlock, RecurrentBlockCache,
-                                         dense_linear, recurrent_path, recurrent_residual,
-                                         residual_block)
+from recurrentgemma_b200.modules import (AttentionBlockCache, Embedder, LocalAttentionBlock,
+                                         MLPBlock, RecurrentBlock, RecurrentBlockCache,
+                                         ResidualBlock, argmax, dense_linear, recurrent_path,
+                                         recurrent_residual, residual_block)
+from recurrentgemma_b200.griffin import Griffin, GriffinConfig, TemporalBlockType
+from recurrentgemma_b200.sampler import GreedySampler
 
 __all__ = [
     "BlockDiagonalLinear", "Conv1D", "Einsum", "RGLRU", "RMSNorm", "rnn_scan", "RecurrentBlock",
-    "RecurrentBlockCache", "MLPBlock", "LocalAttentionBlock", "AttentionBlockCache", "recurrent_path", "recurrent_residual", "residual_block",
-    "dense_linear",
+    "RecurrentBlockCache", "MLPBlock", "LocalAttentionBlock", "AttentionBlockCache", "ResidualBlock",
+    "Embedder", "Griffin", "GriffinConfig", "TemporalBlockType", "GreedySampler", "argmax",
+    "recurrent_path", "recurrent_residual", "residual_block", "dense_linear",
 ]

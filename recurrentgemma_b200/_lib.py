@@ -77,6 +77,9 @@ SIGNATURES = {
     "rgk_attention_workspace_bytes": (_sz, [_i64, _i64]),
     "rgk_local_attention_prefill": (_int, [_vp, _vp, _vp, _vp, _int, _i64, _i64, _int, _int, _int,
                                            _int, _vp, _vp, _sz, _vp]),
+    "rgk_embed": (_int, [_vp, _int, _vp, _i64, _i64, _i64, ctypes.c_float, _int, _vp, _vp]),
+    "rgk_logits": (_int, [_vp, _vp, _i64, _i64, _i64, ctypes.c_float, _int, _vp, _vp, _vp]),
+    "rgk_argmax": (_int, [_vp, _i64, _i64, _int, _vp, _vp]),
     "rgk_workspace_bytes": (_sz, [_i64, _i64, _i64, _int]),
     "rgk_workspace_status": (_int, [_vp, _vp]),
 }
@@ -108,7 +111,7 @@ def load() -> ctypes.CDLL:
       fn = getattr(lib, name)
       fn.restype = res
       fn.argtypes = args
-    if lib.rgk_abi_version() != 5:
+    if lib.rgk_abi_version() != 6:
       raise RuntimeError("librgk.so has a different ABI version; rebuild it")
     _lib = lib
     return lib

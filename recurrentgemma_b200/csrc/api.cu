@@ -414,6 +414,58 @@ int rgk_dense_linear(const void* x, const void* weight, const void* bias, int64_
   return RGK_OK;
 }
 
+int rgk_embed(const void* tokens, int token_dtype, const void* table, int64_t M, int64_t V,
+              int64_t D, float scale, int dtype, void* out, void* stream) {
+  RGK_REQUIRE(dtype == RGK_F32 || dtype == RGK_BF16, RGK_EINVAL, "unknown dtype %d", dtype);
+  RGK_REQUIRE(token_dtype == RGK_I32 || token_dtype == RGK_I64, RGK_EINVAL,
+              "unknown token dtype %d", token_dtype);
+  RGK_REQUIRE(M >= 0 && V >= 1 && D >= 1, RGK_EINVAL, "bad size (M=%lld V=%lld D=%lld)",
+              (long long)M, (long long)V, (long long)D);
+  RGK_REQUIRE(tokens && table && out, RGK_EINVAL, "NULL pointer argument");
+  RGK_REQUIRE(aligned16(table) && aligned16(out), RGK_EALIGN, "pointers must be 16-byte aligned");
+  RGK_REQUIRE((D * (int64_t)elem_size(dtype)) % 16 == 0, RGK_ESHAPE,
+              "the embedding width must be a multiple of a 16-byte pack (D=%lld)", (long long)D);
+  if (M == 0) return RGK_OK;
+  RGK_CHECK_DEVICE();
+  RGK_CUDA(rgk::launch_embed(tokens, token_dtype == RGK_I64, table, M, V, D, scale, dtype, out,
+                             static_cast<cudaStream_t>(stream)),
+           "embed launch");
+  return RGK_OK;
+}
+
+int rgk_logits(const void* x, const void* table, int64_t M, int64_t D, int64_t V, float cap,
+               int dtype, void* out, int* status, void* stream) {
+  RGK_REQUIRE(dtype == RGK_F32 || dtype == RGK_BF16, RGK_EINVAL, "unknown dtype %d", dtype);
+  RGK_REQUIRE(M >= 0 && D >= 1 && V >= 1, RGK_EINVAL, "bad size (M=%lld D=%lld V=%lld)",
+              (long long)M, (long long)D, (long long)V);
+  RGK_REQUIRE(cap >= 0.0f, RGK_EINVAL, "the soft cap must not be negative");
+  RGK_REQUIRE(x && table && out, RGK_EINVAL, "NULL pointer argument");
+  RGK_REQUIRE(aligned16(x) && aligned16(table) && aligned16(out), RGK_EALIGN,
+              "pointers must be 16-byte aligned");
+  RGK_REQUIRE(rgk::dense_tc_supported(dtype, M > 0 ? M : 1, D, V), RGK_ESHAPE,
+              "the tensor-core logits cover bfloat16 with D and V multiples of 8 "
+              "(dtype %d, D=%lld, V=%lld)", dtype, (long long)D, (long long)V);
+  if (M == 0) return RGK_OK;
+  RGK_CHECK_DEVICE();
+  RGK_CUDA(rgk::launch_dense_tc(x, table, nullptr, nullptr, M, (int)D, (int)V, 0, out, status,
+                                static_cast<cudaStream_t>(stream), cap),
+           "logits launch");
+  return RGK_OK;
+}
+
+int rgk_argmax(const void* x, int64_t M, int64_t V, int dtype, int* out, void* stream) {
+  RGK_REQUIRE(dtype == RGK_F32 || dtype == RGK_BF16, RGK_EINVAL, "unknown dtype %d", dtype);
+  RGK_REQUIRE(M >= 0 && V >= 1 && V < ((int64_t)1 << 31), RGK_EINVAL, "bad size (M=%lld V=%lld)",
+              (long long)M, (long long)V);
+  RGK_REQUIRE(x && out, RGK_EINVAL, "NULL pointer argument");
+  RGK_REQUIRE(aligned16(x), RGK_EALIGN, "pointers must be 16-byte aligned");
+  if (M == 0) return RGK_OK;
+  RGK_CHECK_DEVICE();
+  RGK_CUDA(rgk::launch_argmax(x, M, V, dtype, out, static_cast<cudaStream_t>(stream)),
+           "argmax launch");
+  return RGK_OK;
+}
+
 size_t rgk_block_workspace_bytes(int64_t B, int64_t T, int64_t D, int64_t E, int dtype) {
   if (B < 0 || T < 0 || D < 0 || E < 0 || (dtype != RGK_F32 && dtype != RGK_BF16)) return 0;
   if (T < 1) T = 1;

@@ -39,13 +39,15 @@ constexpr uint32_t kIdescG = tc_idesc_bf16(BM, BN);
 // 3: GeGLU - W holds, per group of 128 rows, 64 gate rows then the 64 value rows of the same
 //    features (see pack_mlp_up_kernel); out [M, N/2] = gelu_tanh(gate) * value, where gate and
 //    value are round(round(acc) + bias): the contraction and the bias add are two tensor operations
-//    in the reference (torch/layers.py:700-703, torch/modules.py:749-751).
+//    in the reference (torch/layers.py:700-703, torch/modules.py:749-751);
+// 4: logits soft cap - round(tanh(round(round(acc) / cap)) * cap), the three tensor operations of
+//    torch/griffin.py:183-185 after the contraction of torch/modules.py:1003.
 template <int kMode>
 __global__ void __launch_bounds__(kThreadsG, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                const __nv_bfloat16* __restrict__ bias, const __nv_bfloat16* __restrict__ residual,
                int64_t M, int N, int K, int m_tiles,
-               int n_tiles, __nv_bfloat16* __restrict__ out, int* status) {
+               int n_tiles, __nv_bfloat16* __restrict__ out, int* status, float cap) {
   extern __shared__ uint8_t smem_raw[];
   // aligned by an offset into the shared array, so that the address space stays known to the
   // compiler (shared-memory load/store instructions instead of generic ones)
@@ -225,6 +227,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             float v0 = __uint_as_float(acc[n]) + bv[n], v1 = __uint_as_float(acc[n + 1]) + bv[n + 1];
             uint32_t pk = pack_bf16x2(v0, v1);
             if constexpr (kMode == 1) pk = pack_bf16x2(gelu_tanh_<true>(bf16_lo(pk)), gelu_tanh_<true>(bf16_hi(pk)));
+            if constexpr (kMode == 4) {
+              uint32_t t = pack_bf16x2(__fdiv_rn(bf16_lo(pk), cap), __fdiv_rn(bf16_hi(pk), cap));
+              t = pack_bf16x2(tanhf(bf16_lo(t)), tanhf(bf16_hi(t)));
+              pk = pack_bf16x2(bf16_lo(t) * cap, bf16_hi(t) * cap);
+            }
             o[p] = pk;
           }
           ov[j] = make_uint4(o[0], o[1], o[2], o[3]);
@@ -305,7 +312,7 @@ bool dense_tc_supported(int dtype, int64_t M, int64_t K, int64_t N) {
 
 cudaError_t launch_dense_tc(const void* x, const void* w, const void* bias, const void* residual,
                             int64_t M, int K, int N, int gelu, void* out, int* status,
-                            cudaStream_t s) {
+                            cudaStream_t s, float cap) {
   if (M == 0) return cudaSuccess;
   CUtensorMap map_x, map_w;
   if (!tensor_map_2d(&map_x, x, (uint64_t)M, (uint64_t)K, BM, BK, true) ||
@@ -320,6 +327,7 @@ cudaError_t launch_dense_tc(const void* x, const void* w, const void* bias, cons
     cudaFuncSetAttribute(gemm_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemG);
     cudaFuncSetAttribute(gemm_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemG);
     cudaFuncSetAttribute(gemm_tc_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemG);
+    cudaFuncSetAttribute(gemm_tc_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemG);
   }
   const int m_tiles = (int)((M + BM - 1) / BM), n_tiles = (N + BN - 1) / BN;
   const int total = m_tiles * n_tiles;
@@ -329,8 +337,10 @@ cudaError_t launch_dense_tc(const void* x, const void* w, const void* bias, cons
 #define RGK_GEMM(MODE)                                                                          \
   gemm_tc_kernel<MODE><<<grid, kThreadsG, kSmemG, s>>>(map_x, map_w, (const T_*)bias,           \
                                                        (const T_*)residual, M, N, K, m_tiles,   \
-                                                       n_tiles, (T_*)out, status)
-  if (gelu == 2) RGK_GEMM(3); else if (gelu) RGK_GEMM(1); else if (residual) RGK_GEMM(2); else RGK_GEMM(0);
+                                                       n_tiles, (T_*)out, status, cap)
+  if (cap != 0.0f && (gelu != 0 || residual != nullptr || bias != nullptr)) return cudaErrorInvalidValue;
+  if (cap != 0.0f) RGK_GEMM(4);
+  else if (gelu == 2) RGK_GEMM(3); else if (gelu) RGK_GEMM(1); else if (residual) RGK_GEMM(2); else RGK_GEMM(0);
 #undef RGK_GEMM
   return cudaGetLastError();
 }

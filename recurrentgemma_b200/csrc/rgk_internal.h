@@ -63,12 +63,19 @@ cudaError_t launch_rglru_chan(const void* c, const void* pos, int pos64, const v
 // gemm_tc.cu: out [M,N] = x [M,K] W[N,K]^T + bias (bfloat16, float32 accumulation) on tcgen05;
 // gelu == 1 applies gelu_tanh to the rounded result; gelu == 2 is the GeGLU epilogue of the MLP
 // block (W and bias packed by launch_pack_mlp_up, N = 2 X, out [M, X]); residual != null adds a
-// [M,N] tensor to the rounded result and rounds again (not together with gelu).  status: optional device int raised on
-// a bounded-wait timeout.
+// [M,N] tensor to the rounded result and rounds again (not together with gelu).  cap != 0 (no bias,
+// gelu or residual) is the logits soft cap: tanh(acc / cap) * cap with every rounding of the
+// reference.  status: optional device int raised on a bounded-wait timeout.
 bool dense_tc_supported(int dtype, int64_t M, int64_t K, int64_t N);
 cudaError_t launch_dense_tc(const void* x, const void* w, const void* bias, const void* residual,
                             int64_t M, int K, int N, int gelu, void* out, int* status,
-                            cudaStream_t s);
+                            cudaStream_t s, float cap = 0.0f);
+
+// embed.cu: rows of the embedding table scaled by a constant (Embedder.encode), and the index of
+// the first maximum of every row of a [M, V] matrix (greedy sampling).
+cudaError_t launch_embed(const void* tokens, int tokens64, const void* table, int64_t M, int64_t V,
+                         int64_t D, float scale, int dtype, void* out, cudaStream_t s);
+cudaError_t launch_argmax(const void* x, int64_t M, int64_t V, int dtype, int* out, cudaStream_t s);
 
 // ffw_up.w [2, D, X], ffw_up.b [2, X] -> packed_w [2X, D], packed_b [2X] (gemm_tc.cu, mode 3).
 cudaError_t launch_pack_mlp_up(const void* w, const void* b, int D, int X, void* packed_w,

@@ -28,10 +28,12 @@ def recurrent_path(
     xb: torch.Tensor, yb: Optional[torch.Tensor], segment_pos: torch.Tensor,
     conv_1d: layers.Conv1D, rg_lru: layers.RGLRU,
     cache: Optional[RecurrentBlockCache] = None, return_cache: bool = True,
-    out: Optional[torch.Tensor] = None,
+    out: Optional[torch.Tensor] = None, inplace: bool = False,
 ) -> Tuple[torch.Tensor, Optional[RecurrentBlockCache]]:
   """RGLRU(Conv1D(xb)) * gelu_tanh(yb): the sub-path of RecurrentBlock.forward between the
-  input projections and `linear_out` (recurrentgemma/torch/modules.py:631-646)."""
+  input projections and `linear_out` (recurrentgemma/torch/modules.py:631-646).  With `inplace`
+  a decode step overwrites the tensors of `cache` and returns that cache (an extension for
+  decode loops that run as a CUDA graph; the reference always returns new tensors)."""
   bs, l, e = xb.shape
   dev = _lib.require_cuda(xb, yb, segment_pos, conv_1d.w, rg_lru.a_param)
   layers._same_dtype(xb, conv_1d.w, conv_1d.b, rg_lru.a_param, rg_lru.input_gate.w,
@@ -64,8 +66,13 @@ def recurrent_path(
       assert cache.rg_lru_state.shape == (bs, e) and cache.conv1d_state.shape == (bs, 3, e)
       h_in = cache.rg_lru_state.contiguous()
       conv_in = cache.conv1d_state.to(xb.dtype).contiguous()
-      h_last = torch.empty_like(h_in)
-      conv_state = torch.empty_like(conv_in)
+      if inplace:
+        assert h_in is cache.rg_lru_state and conv_in is cache.conv1d_state, (
+            "an in-place step needs a contiguous cache in the activation dtype")
+        h_last, conv_state = h_in, conv_in
+      else:
+        h_last = torch.empty_like(h_in)
+        conv_state = torch.empty_like(conv_in)
       _lib.check(lib.rgk_recurrent_path_decode(
           xc.data_ptr(), _lib.ptr(yc), pos.data_ptr(), _lib.pos_code(pos), ctypes.byref(p),
           h_in.data_ptr(), conv_in.data_ptr(), bs, e, rg_lru.num_heads, 4, dt, rg_lru.gates_impl,
@@ -141,15 +148,17 @@ class RecurrentBlock(nn.Module):
   def forward(
       self, x: torch.Tensor, segment_pos: torch.Tensor,
       cache: Optional[RecurrentBlockCache] = None, return_cache: bool = True,
+      inplace: bool = False,
   ) -> Tuple[torch.Tensor, Optional[RecurrentBlockCache]]:
-    """Returns (block output [B,T,width], updated cache or None)."""
+    """Returns (block output [B,T,width], updated cache or None).  `inplace`: see
+    `recurrent_path`."""
     dev = _lib.require_cuda(x, segment_pos, self.linear_x.weight)
     if self._fusable(x, cache):
       return self._forward_fused(x, segment_pos, return_cache, dev)
     yb = self.linear_y(x)
     xb = self.linear_x(x)
     z, new_cache = recurrent_path(xb, yb, segment_pos, self.conv_1d, self.rg_lru, cache,
-                                  return_cache)
+                                  return_cache, inplace=inplace)
     return self.linear_out(z), new_cache
 
   def _forward_fused(self, x, segment_pos, return_cache, dev, norm=None):
@@ -219,7 +228,7 @@ class RecurrentBlock(nn.Module):
 def recurrent_residual(
     x: torch.Tensor, segment_pos: torch.Tensor, temporal_pre_norm: layers.RMSNorm,
     recurrent_block: RecurrentBlock, cache: Optional[RecurrentBlockCache] = None,
-    return_cache: bool = True,
+    return_cache: bool = True, inplace: bool = False,
 ) -> Tuple[torch.Tensor, Optional[RecurrentBlockCache]]:
   """The temporal half of ResidualBlock.forward for a recurrent block
   (recurrentgemma/torch/modules.py:897-902): recurrent_block(temporal_pre_norm(x)) + x, with the
@@ -229,7 +238,8 @@ def recurrent_residual(
   dev = _lib.require_cuda(x, segment_pos, recurrent_block.linear_x.weight)
   if recurrent_block._fusable(x, cache) and temporal_pre_norm.width == recurrent_block.width:
     return recurrent_block._forward_fused(x, segment_pos, return_cache, dev, norm=temporal_pre_norm)
-  y, new_cache = recurrent_block(temporal_pre_norm(x), segment_pos, cache, return_cache)
+  y, new_cache = recurrent_block(temporal_pre_norm(x), segment_pos, cache, return_cache,
+                                 inplace=inplace)
   return y + x, new_cache
 
 class MLPBlock(nn.Module):
@@ -322,17 +332,19 @@ class MLPBlock(nn.Module):
 def residual_block(
     x: torch.Tensor, segment_pos: torch.Tensor, temporal_pre_norm: layers.RMSNorm,
     temporal_block: nn.Module, channel_pre_norm: layers.RMSNorm, mlp_block: MLPBlock,
-    cache=None, return_cache: bool = True,
+    cache=None, return_cache: bool = True, inplace: bool = False,
 ):
   """ResidualBlock.forward (recurrentgemma/torch/modules.py:897-911) for either kind of temporal
   block (a `RecurrentBlock` or a `LocalAttentionBlock`):
   r = temporal_block(temporal_pre_norm(x)) + x;  out = mlp_block(channel_pre_norm(r)) + r.
-  Returns (out, updated cache of the temporal block or None)."""
+  Returns (out, updated cache of the temporal block or None).  `inplace`: a decode step overwrites
+  the tensors of `cache` instead of returning new ones."""
   if isinstance(temporal_block, RecurrentBlock):
     r, new_cache = recurrent_residual(x, segment_pos, temporal_pre_norm, temporal_block, cache,
-                                      return_cache)
+                                      return_cache, inplace)
   else:
-    y, new_cache = temporal_block(temporal_pre_norm(x), segment_pos, cache, return_cache)
+    y, new_cache = temporal_block(temporal_pre_norm(x), segment_pos, cache, return_cache,
+                                  inplace=inplace)
     r = y + x
   return mlp_block(r, pre_norm=channel_pre_norm), new_cache
 
@@ -422,8 +434,11 @@ class LocalAttentionBlock(nn.Module):
   def forward(
       self, x: torch.Tensor, segment_pos: torch.Tensor,
       cache: Optional[AttentionBlockCache] = None, return_cache: bool = True,
+      inplace: bool = False,
   ) -> Tuple[torch.Tensor, Optional[AttentionBlockCache]]:
-    """Returns (block output [B,T,width], updated cache or None)."""
+    """Returns (block output [B,T,width], updated cache or None).  With `inplace` a decode step
+    writes the new key and value into their ring slot of `cache` and bumps its `num_tokens`
+    (an extension for decode loops that run as a CUDA graph) instead of cloning the ring."""
     dev = _lib.require_cuda(x, segment_pos, self.proj_q.weight)
     layers._same_dtype(x, self.proj_q.weight, self.proj_k.weight, self.proj_v.weight,
                        self.proj_final.weight, self.proj_final.bias)
@@ -463,12 +478,28 @@ class LocalAttentionBlock(nn.Module):
       now, prev = j + kq[:, None] * w, j + (kq[:, None] - 1) * w
       kpos = torch.where(now < nt[:, None], now, prev)
       vis = (kpos >= 0) & (kpos <= nt[:, None]) & (nt[:, None] <= kpos + w)
+      slot = (nt % w)
+      rows = torch.arange(b, device=dev)
+      if inplace:
+        # the ring is read where it lies (the new token's own logit and value are added beside
+        # it), then the slot is overwritten: no copy of the ring
+        scale = hd ** -0.5
+        lg = torch.einsum("bnh,bsh->bns", q[:, 0], cache.keys[:, :, 0]) * scale
+        lg_self = (q[:, 0] * k[:, 0]).sum(-1, dtype=torch.float32).to(x.dtype) * scale
+        lg = torch.where(vis[:, None, :], lg, torch.full_like(lg, -2.3819763e38))
+        probs = torch.softmax(torch.cat([lg, lg_self[:, :, None]], dim=-1).float(), dim=-1).to(x.dtype)
+        enc = (torch.einsum("bns,bsh->bnh", probs[:, :, :w], cache.values[:, :, 0]).float()
+               + probs[:, :, w:].float() * v[:, 0].float()).to(x.dtype).reshape(b, 1, n * hd)
+        if return_cache:
+          cache.keys[rows, slot] = k[:, 0]
+          cache.values[rows, slot] = v[:, 0]
+          cache.num_tokens.add_(1)
+          new_cache = cache
+        return self._linear(enc, self.proj_final), new_cache
       visible = torch.cat([vis, torch.ones((b, 1), dtype=torch.bool, device=dev)], dim=1)[:, None, :]
       keys = torch.cat([cache.keys, k], dim=1)
       values = torch.cat([cache.values, v], dim=1)
       if return_cache:
-        slot = (nt % w)
-        rows = torch.arange(b, device=dev)
         nk, nv = cache.keys.clone(), cache.values.clone()
         nk[rows, slot] = k[:, 0]
         nv[rows, slot] = v[:, 0]
@@ -490,3 +521,153 @@ class LocalAttentionBlock(nn.Module):
         keys=torch.zeros(shape, device=device, dtype=dtype),
         values=torch.zeros(shape, device=device, dtype=dtype),
         num_tokens=torch.zeros([batch_size], dtype=torch.int32, device=device))
+
+
+class ResidualBlock(nn.Module):
+  """Griffin's residual block (recurrentgemma/torch/modules.py:755-945): same constructor
+  arguments, attribute and parameter names (`temporal_pre_norm`, `recurrent_block` or
+  `attention_block`, `channel_pre_norm`, `mlp_block`), forward and cache.  `temporal_block_type`
+  is "recurrent" / "attention" or a member of an enumeration with those names (the reference's
+  `common.TemporalBlockType`)."""
+
+  def __init__(self, width: int, mlp_expanded_width: int, num_heads: int,
+               attention_window_size: int, temporal_block_type, lru_width: Optional[int] = None,
+               conv1d_temporal_width: int = 4, final_w_init_variance_scale: float = 1.0,
+               device=None, dtype=None):
+    super().__init__()
+    self.width = width
+    self.mlp_expanded_width = mlp_expanded_width
+    self.num_heads = num_heads
+    self.attention_window_size = attention_window_size
+    self.temporal_block_type = temporal_block_type
+    self.lru_width = lru_width
+    self.conv1d_temporal_width = conv1d_temporal_width
+    self.final_w_init_variance_scale = final_w_init_variance_scale
+    self.temporal_pre_norm = layers.RMSNorm(width, device=device, dtype=dtype)
+    if block_kind(temporal_block_type) == "recurrent":
+      self.recurrent_block = RecurrentBlock(
+          width=width, num_heads=num_heads, lru_width=lru_width,
+          conv1d_temporal_width=conv1d_temporal_width,
+          final_w_init_variance_scale=final_w_init_variance_scale, device=device, dtype=dtype)
+    else:
+      self.attention_block = LocalAttentionBlock(
+          width=width, num_heads=num_heads, window_size=attention_window_size,
+          final_w_init_variance_scale=final_w_init_variance_scale, device=device, dtype=dtype)
+    self.channel_pre_norm = layers.RMSNorm(width, device=device, dtype=dtype)
+    self.mlp_block = MLPBlock(width, mlp_expanded_width, final_w_init_variance_scale,
+                              device=device, dtype=dtype)
+
+  def reset_parameters(self) -> None:
+    self.temporal_pre_norm.reset_parameters()
+    self.temporal_block.reset_parameters()
+    self.channel_pre_norm.reset_parameters()
+    self.mlp_block.reset_parameters()
+
+  @property
+  def temporal_block(self) -> nn.Module:
+    if block_kind(self.temporal_block_type) == "recurrent":
+      return self.recurrent_block
+    return self.attention_block
+
+  def forward(self, x: torch.Tensor, segment_pos: torch.Tensor, cache=None,
+              return_cache: bool = True, inplace: bool = False):
+    """Returns (block output [B,T,width], updated cache of the temporal block or None)."""
+    return residual_block(x, segment_pos, self.temporal_pre_norm, self.temporal_block,
+                          self.channel_pre_norm, self.mlp_block, cache, return_cache, inplace)
+
+  @classmethod
+  def init_cache(cls, batch_size: int, width: int, num_heads: int, attention_window_size: int,
+                 temporal_block_type, dtype: torch.dtype, lru_width: Optional[int] = None,
+                 conv1d_temporal_width: int = 4, device=None):
+    """Empty cache of the block's kind (recurrentgemma/torch/modules.py:913-945)."""
+    if block_kind(temporal_block_type) == "recurrent":
+      return RecurrentBlock.init_cache(batch_size=batch_size, lru_width=lru_width or width,
+                                       dtype=dtype, conv1d_temporal_width=conv1d_temporal_width,
+                                       device=device)
+    return LocalAttentionBlock.init_cache(batch_size=batch_size, window_size=attention_window_size,
+                                          heads_dim=width // num_heads, dtype=dtype, device=device)
+
+
+def block_kind(temporal_block_type) -> str:
+  """"recurrent" or "attention" from a string or an enumeration member of that name."""
+  name = getattr(temporal_block_type, "name", temporal_block_type)
+  kind = str(name).lower()
+  if kind not in ("recurrent", "attention"):
+    raise ValueError(f"unknown temporal block type {temporal_block_type!r}")
+  return kind
+
+
+class Embedder(nn.Module):
+  """Token embeddings tied to the output projection (recurrentgemma/torch/modules.py:945-1003):
+  `input_embedding` [vocab_size, embed_dim]; `encode` gathers rows (scaled by sqrt(embed_dim)
+  rounded to bfloat16 when `scale_by_sqrt_dim`), `decode` multiplies by the transposed table.
+  `decode(x, soft_cap)` also applies Griffin's logits soft cap in the same kernel
+  (recurrentgemma/torch/griffin.py:183-185)."""
+
+  def __init__(self, vocab_size: int, embed_dim: int, scale_by_sqrt_dim: bool, device=None,
+               dtype=None):
+    super().__init__()
+    self.vocab_size = vocab_size
+    self.embed_dim = embed_dim
+    self.scale_by_sqrt_dim = scale_by_sqrt_dim
+    self.input_embedding = nn.Parameter(
+        torch.empty([vocab_size, embed_dim], device=device, dtype=dtype))
+    self.reset_parameters()
+
+  def reset_parameters(self) -> None:
+    torch.nn.init.normal_(self.input_embedding, mean=0.0, std=math.sqrt(1.0 / self.embed_dim))
+
+  @torch.no_grad()
+  def encode(self, x: torch.Tensor) -> torch.Tensor:
+    """tokens [...] (int32 / int64) -> activations [..., embed_dim]."""
+    table = self.input_embedding
+    dev = _lib.require_cuda(x, table)
+    if x.dtype not in (torch.int32, torch.int64):
+      raise TypeError(f"tokens must be int32 or int64, got {x.dtype}")
+    scale = 1.0
+    if self.scale_by_sqrt_dim:
+      scale = float(torch.tensor(math.sqrt(self.embed_dim)).type(torch.bfloat16))
+    tok = x.contiguous()
+    out = torch.empty((*x.shape, self.embed_dim), dtype=table.dtype, device=dev)
+    with torch.cuda.device(dev):
+      _lib.check(_lib.load().rgk_embed(
+          tok.data_ptr(), 1 if tok.dtype == torch.int64 else 0, table.data_ptr(), tok.numel(),
+          self.vocab_size, self.embed_dim, scale, _lib.dtype_code(table.dtype), out.data_ptr(),
+          _lib.stream_ptr(dev)))
+    return out
+
+  @torch.no_grad()
+  def decode(self, x: torch.Tensor, soft_cap: float = 0.0) -> torch.Tensor:
+    """activations [..., embed_dim] -> logits [..., vocab_size] (capped when soft_cap != 0)."""
+    table = self.input_embedding
+    dev = _lib.require_cuda(x, table)
+    layers._same_dtype(x, table)
+    assert x.shape[-1] == self.embed_dim
+    if x.dtype == torch.bfloat16 and self.embed_dim % 8 == 0 and self.vocab_size % 8 == 0:
+      xc = x.contiguous()
+      out = torch.empty((*x.shape[:-1], self.vocab_size), dtype=x.dtype, device=dev)
+      with torch.cuda.device(dev):
+        _lib.check(_lib.load().rgk_logits(
+            xc.data_ptr(), table.data_ptr(), xc.numel() // self.embed_dim, self.embed_dim,
+            self.vocab_size, float(soft_cap), _lib.dtype_code(x.dtype), out.data_ptr(), None,
+            _lib.stream_ptr(dev)))
+      return out
+    logits = x @ table.T                     # float32 and odd shapes: a library contraction
+    if soft_cap:
+      logits = torch.tanh(logits / soft_cap) * soft_cap
+    return logits
+
+
+@torch.no_grad()
+def argmax(logits: torch.Tensor) -> torch.Tensor:
+  """torch.argmax(logits, dim=-1) as int32 (greedy sampling,
+  recurrentgemma/torch/sampler.py:131-132): the first maximum of every row."""
+  dev = _lib.require_cuda(logits)
+  v = logits.shape[-1]
+  xc = logits.contiguous()
+  out = torch.empty(logits.shape[:-1], dtype=torch.int32, device=dev)
+  with torch.cuda.device(dev):
+    _lib.check(_lib.load().rgk_argmax(xc.data_ptr(), xc.numel() // v, v,
+                                      _lib.dtype_code(logits.dtype), out.data_ptr(),
+                                      _lib.stream_ptr(dev)))
+  return out

@@ -20,7 +20,7 @@ import torch
 class Case:
   name: str
   kind: str            # "blockdiag" | "conv1d" | "rglru" | "rnn_scan" | "block" | "rmsnorm" | "residual" | "mlp" | "resblock"
-                       # | "attention" | "resblock_attn"
+                       # | "attention" | "resblock_attn" | "griffin"
   dtype: str           # "float32" | "bfloat16"
   batch: int
   seq: int
@@ -33,6 +33,7 @@ class Case:
   decode_steps: int = 2
   expanded: int = 0    # mlp expanded width (kinds "mlp" and "resblock")
   window: int = 0      # attention window size (kind "attention")
+  vocab: int = 0       # vocabulary size (kind "griffin")
 
   @property
   def torch_dtype(self) -> torch.dtype:
@@ -119,8 +120,28 @@ def geometric_segment_pos(batch: int, seq: int, mean_len: float, seed: int) -> t
   return (idx - last_start).contiguous()
 
 
+GRIFFIN_BLOCKS = ("recurrent", "recurrent", "attention")   # the model's repeating pattern
+GRIFFIN_SOFT_CAP = 30.0
+
+
+def make_griffin_params(case: Case) -> Dict[str, torch.Tensor]:
+  """The state_dict of a three-block Griffin (griffin.py:52-80): embedder, blocks.{i}, final_norm."""
+  dt = case.torch_dtype
+  d, xw = case.model_width, case.expanded
+  p = {"embedder.input_embedding": normal(case.name, "embedding", (case.vocab, d),
+                                          math.sqrt(1.0 / d), dt),
+       "final_norm.scale": normal(case.name, "final_norm_scale", (d,), 0.3, dt)}
+  for i, kind in enumerate(GRIFFIN_BLOCKS):
+    sub = dataclasses.replace(case, name=f"{case.name}/blocks.{i}",
+                              kind="resblock" if kind == "recurrent" else "resblock_attn")
+    p.update({f"blocks.{i}.{k}": v for k, v in make_params(sub).items()})
+  return p
+
+
 def make_params(case: Case) -> Dict[str, torch.Tensor]:
   """Parameters named as in the reference state_dict of RecurrentBlock (modules.py:531-560)."""
+  if case.kind == "griffin":
+    return make_griffin_params(case)
   dt = case.torch_dtype
   e, h, d, w = case.lru_width, case.heads, case.model_width, case.temporal_width
   bw = e // h
@@ -192,6 +213,10 @@ def make_inputs(case: Case) -> Dict[str, Optional[torch.Tensor]]:
   """Activations, positions, optional initial state and the decode-step tokens of a case."""
   dt = case.torch_dtype
   n = case.name
+  if case.kind == "griffin":
+    g = torch.Generator(device="cpu").manual_seed(_seed(n, "tokens"))
+    return {"tokens": torch.randint(0, case.vocab, (case.batch, case.seq), generator=g),
+            "segment_pos": make_segment_pos(case.pos, case.batch, case.seq, n), "h0": None}
   in_width = (case.model_width
               if case.kind in ("block", "residual", "mlp", "resblock", "attention", "resblock_attn")
               else case.lru_width)
@@ -281,6 +306,10 @@ def golden_cases():
         # a whole residual block of the attention kind, head dimension 256
         _c(f"resblock_attn_{s}_512_h2_w48", "resblock_attn", dt, 2, 64, 512, 2, width=512,
            window=48, expanded=384, pos="multi"),
+        # a three-block Griffin (recurrent, recurrent, attention) from token ids to capped logits,
+        # two documents per row, then greedy decode steps that wrap the attention window
+        _c(f"griffin_{s}_512_h2_v1024", "griffin", dt, 2, 64, 512, 2, width=512, window=48,
+           expanded=768, vocab=1024, decode_steps=3),
         # a whole residual block of the recurrent kind (modules.py:897-911)
         _c(f"resblock_{s}_128_h1_l256_x384", "resblock", dt, 2, 64, 256, 1, width=128,
            expanded=384, pos="multi"),

@@ -137,6 +137,33 @@ def run_case(case: C.Case, layers, modules) -> dict:
         y, cache = m(inp[f"x_step{i}"], C.decode_positions(case, pos, i), cache)
         out[f"out_step{i}"] = _np(y)
 
+    elif case.kind == "griffin":
+      from recurrentgemma import common  # pylint: disable=import-outside-toplevel
+      from recurrentgemma.torch import griffin  # pylint: disable=import-outside-toplevel
+      kinds = {"recurrent": common.TemporalBlockType.RECURRENT,
+               "attention": common.TemporalBlockType.ATTENTION}
+      cfg = common.GriffinConfig(
+          vocab_size=case.vocab, width=case.model_width, mlp_expanded_width=case.expanded,
+          num_heads=case.heads, block_types=tuple(kinds[k] for k in C.GRIFFIN_BLOCKS),
+          embeddings_scale_by_sqrt_dim=True, attention_window_size=case.window,
+          logits_soft_cap=C.GRIFFIN_SOFT_CAP, lru_width=case.lru_width)
+      m = griffin.Griffin(cfg, gradient_checkpointing=False, dtype=dt)
+      m.load_state_dict(p)
+      logits, cache = m(inp["tokens"], pos)
+      out["logits"] = _np(logits)
+      out["h_0"] = _np(cache["blocks.0"].rg_lru_state)
+      out["conv_1"] = _np(cache["blocks.1"].conv1d_state)
+      out["keys_2"] = _np(cache["blocks.2"].keys)
+      tok = torch.argmax(logits[:, -1], dim=-1)
+      for i in range(case.decode_steps):
+        out[f"tokens_step{i}"] = tok.numpy().astype(np.int64)
+        logits, cache = m(tok[:, None], C.decode_positions(case, pos, i), cache)
+        out[f"logits_step{i}"] = _np(logits)
+        tok = torch.argmax(logits[:, 0], dim=-1)
+      out["tokens_final"] = tok.numpy().astype(np.int64)
+      out["h_0_final"] = _np(cache["blocks.0"].rg_lru_state)
+      out["keys_2_final"] = _np(cache["blocks.2"].keys)
+
     elif case.kind == "mlp":
       m = modules.MLPBlock(case.model_width, case.expanded, dtype=dt)
       m.load_state_dict({k[len("mlp_block."):]: v for k, v in p.items()})

@@ -104,23 +104,47 @@ def test_install_rebinds_reference_names(rg):
 
 
 def test_signatures_match_reference(rg):
-  """Constructor and forward parameter names of the mirrored classes equal the reference's."""
+  """Constructor and forward parameter names of the mirrored classes equal the reference's; what
+  a mirror adds comes after them and has a default (`inplace`, `device`, a fused soft cap)."""
   import inspect
+  from recurrentgemma.torch import griffin as ref_griffin
   from recurrentgemma.torch import layers as ref_layers, modules as ref_modules
-  from recurrentgemma_b200 import layers, modules
+  from recurrentgemma_b200 import griffin, layers, modules
+
+  def same(ref_fn, our_fn, what):
+    ref_p = list(inspect.signature(ref_fn).parameters)
+    ours = inspect.signature(our_fn).parameters
+    our_p = list(ours)
+    assert our_p[:len(ref_p)] == ref_p, (what, ref_p, our_p)
+    for extra in our_p[len(ref_p):]:
+      assert ours[extra].default is not inspect.Parameter.empty, (what, extra)
+
   pairs = [(ref_layers.RGLRU, layers.RGLRU), (ref_layers.Conv1D, layers.Conv1D),
            (ref_layers.RMSNorm, layers.RMSNorm), (ref_layers.Einsum, layers.Einsum),
            (ref_modules.LocalAttentionBlock, modules.LocalAttentionBlock),
            (ref_layers.BlockDiagonalLinear, layers.BlockDiagonalLinear),
-           (ref_modules.RecurrentBlock, modules.RecurrentBlock)]
+           (ref_modules.RecurrentBlock, modules.RecurrentBlock),
+           (ref_modules.ResidualBlock, modules.ResidualBlock),
+           (ref_griffin.Griffin, griffin.Griffin)]
   for ref_cls, our_cls in pairs:
     for fn in ("__init__", "forward", "reset_parameters"):
-      ref_p = list(inspect.signature(getattr(ref_cls, fn)).parameters)
-      our_p = list(inspect.signature(getattr(our_cls, fn)).parameters)
-      assert ref_p == our_p, (ref_cls.__name__, fn, ref_p, our_p)
+      same(getattr(ref_cls, fn), getattr(our_cls, fn), (ref_cls.__name__, fn))
     if hasattr(ref_cls, "init_cache"):
-      assert (list(inspect.signature(ref_cls.init_cache).parameters) ==
-              list(inspect.signature(our_cls.init_cache).parameters)), ref_cls.__name__
+      same(ref_cls.init_cache, our_cls.init_cache, (ref_cls.__name__, "init_cache"))
+  for fn in ("__init__", "encode", "decode", "reset_parameters"):
+    same(getattr(ref_modules.Embedder, fn), getattr(modules.Embedder, fn), ("Embedder", fn))
+  # the whole model: the same state_dict keys and shapes, the same cache structure
+  ref_model = ref_griffin.Griffin(_config(), device="meta", dtype=torch.float32)
+  our_model = griffin.Griffin(_config(), device="meta", dtype=torch.float32)
+  ref_sd, our_sd = ref_model.state_dict(), our_model.state_dict()
+  assert list(ref_sd) == list(our_sd)
+  assert all(ref_sd[k].shape == our_sd[k].shape for k in ref_sd)
+  ref_cache = ref_model.init_cache(2, torch.float32)
+  our_cache = our_model.init_cache(2, torch.float32)
+  assert list(ref_cache) == list(our_cache)
+  for k in ref_cache:
+    assert type(ref_cache[k])._fields == type(our_cache[k])._fields
+    assert all(a.shape == b.shape and a.dtype == b.dtype for a, b in zip(ref_cache[k], our_cache[k]))
   # MLPBlock: same constructor; forward takes the reference's argument first (two optional
   # extensions follow)
   assert (list(inspect.signature(ref_modules.MLPBlock.__init__).parameters) ==
@@ -129,3 +153,32 @@ def test_signatures_match_reference(rg):
   ref_scan = list(inspect.signature(ref_layers.rnn_scan).parameters)
   our_scan = list(inspect.signature(layers.rnn_scan).parameters)
   assert our_scan[:len(ref_scan)] == ref_scan
+
+
+def test_config_preset_and_sampler_positions(rg):
+  """The 2B preset equals the reference's, and prompt positions follow the reference sampler's
+  formula for left-padded prompts (torch/sampler.py:253-256)."""
+  from recurrentgemma import common
+  from recurrentgemma_b200 import griffin, sampler
+  ref = common.GriffinConfig.from_preset(common.Preset.RECURRENT_GEMMA_2B_V1)
+  ours = griffin.GriffinConfig.recurrent_gemma_2b()
+  for f in ours._fields:
+    a, b = getattr(ref, f), getattr(ours, f)
+    if f == "block_types":
+      assert [t.name for t in a] == [t.name for t in b]
+    else:
+      assert a == b, f
+  assert ours.num_layers == ref.num_layers == 26
+  assert griffin.GriffinConfig.recurrent_gemma_2b(max_sequence_length=512).attention_window_size == 512
+  model = griffin.Griffin(_config(), device="cpu", dtype=torch.float32)
+  s = sampler.GreedySampler(model)
+  lengths = torch.tensor([7, 3, 1])
+  pos = s.positions(7, lengths)
+  expect = torch.clip(torch.arange(7)[None] - 7 + lengths[:, None], min=-1).to(torch.int32)
+  assert torch.equal(pos, expect)
+  assert pos[1].tolist() == [-1, -1, -1, -1, 0, 1, 2]
+  # a private copy of a cache shares no storage with the original
+  cache = model.init_cache(2, torch.float32)
+  own = sampler._own(cache)
+  assert list(own) == list(cache)
+  assert all(a.data_ptr() != b.data_ptr() for k in cache for a, b in zip(cache[k], own[k]))

@@ -31,6 +31,18 @@ def _block(rg, case, p):
   return m
 
 
+def _griffin(rg, case, p):
+  kinds = {"recurrent": rg.TemporalBlockType.RECURRENT, "attention": rg.TemporalBlockType.ATTENTION}
+  cfg = rg.GriffinConfig(
+      vocab_size=case.vocab, width=case.model_width, mlp_expanded_width=case.expanded,
+      num_heads=case.heads, block_types=tuple(kinds[k] for k in C.GRIFFIN_BLOCKS),
+      embeddings_scale_by_sqrt_dim=True, attention_window_size=case.window,
+      logits_soft_cap=C.GRIFFIN_SOFT_CAP, lru_width=case.lru_width)
+  m = rg.Griffin(cfg, device=DEV, dtype=case.torch_dtype)
+  m.load_state_dict(p)
+  return m
+
+
 @pytest.mark.parametrize("case", CASES, ids=[c.name for c in CASES])
 def test_golden(case, rg, oracle):
   g = load_golden(case.name)
@@ -149,6 +161,30 @@ def test_golden(case, rg, oracle):
                                    C.decode_positions(case, inp["segment_pos"], i).to(DEV),
                                    tn, att, cn, mlp, cache)
       chk(y, f"out_step{i}")
+
+  elif case.kind == "griffin":
+    m = _griffin(rg, case, p)
+    logits, cache = m(ic["tokens"], pos)
+    chk(logits, "logits"); chk(cache["blocks.0"].rg_lru_state, "h_0")
+    chk(cache["blocks.1"].conv1d_state, "conv_1"); chk(cache["blocks.2"].keys, "keys_2")
+    only_logits, none = m(ic["tokens"], pos, return_cache=False)
+    assert none is None and torch.equal(only_logits, logits)
+    assert m(ic["tokens"], pos, return_logits=False, return_cache=False) == (None, None)
+    # decode steps on the reference's greedy tokens: new tensors per step (the reference's
+    # contract), and the in-place form on a private copy of the cache
+    from recurrentgemma_b200 import sampler as sampler_lib
+    own = sampler_lib._own(cache)
+    for i in range(case.decode_steps):
+      tok = torch.from_numpy(g[f"tokens_step{i}"])[:, None].to(DEV)
+      ps = C.decode_positions(case, inp["segment_pos"], i).to(DEV)
+      logits, cache = m(tok, ps, cache)
+      chk(logits, f"logits_step{i}")
+      logits2, own2 = m(tok, ps, own, inplace_cache=True)
+      assert own2["blocks.2"].keys is own["blocks.2"].keys
+      assert_close(logits2, g[f"logits_step{i}"], tol, f"in-place logits_step{i}")
+    chk(cache["blocks.0"].rg_lru_state, "h_0_final"); chk(cache["blocks.2"].keys, "keys_2_final")
+    chk(own["blocks.0"].rg_lru_state, "h_0_final"); chk(own["blocks.2"].keys, "keys_2_final")
+    assert torch.equal(own["blocks.2"].num_tokens, cache["blocks.2"].num_tokens)
 
   elif case.kind == "mlp":
     m = rg.MLPBlock(case.model_width, case.expanded, device=DEV, dtype=case.torch_dtype)
@@ -607,3 +643,72 @@ def test_attention_kernel_vs_oracle(rg, oracle, shape):
   assert_close(y1, y1_r, TOL[dt], "decode output")
   assert_close(cache1.keys, c1_r[0], TOL[dt], "decode keys")
   assert torch.equal(cache1.num_tokens.cpu(), c1_r[2])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_embed_logits_argmax_vs_oracle(rg, oracle, dtype):
+  """Embedder.encode / decode + soft cap / argmax through the C ABI against the oracle."""
+  dt = {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype]
+  v, d, m = 1000 if dtype == "float32" else 1024, 256, 70
+  g = torch.Generator(device="cpu").manual_seed(5)
+  emb = rg.Embedder(v, d, scale_by_sqrt_dim=True, device=DEV, dtype=dt)
+  table = (torch.randn((v, d), generator=g) * d ** -0.5).to(dt)
+  emb.load_state_dict({"input_embedding": table})
+  tok = torch.randint(0, v, (2, 35), generator=g)
+  for t in (tok, tok.to(torch.int32)):
+    assert_close(emb.encode(t.to(DEV)), oracle.embed(tok, table, True), 0.0, "encode")
+  x = (torch.randn((m, d), generator=g) * 6.0).to(dt)
+  for cap in (0.0, 30.0):
+    assert_close(emb.decode(x.to(DEV), cap), oracle.logits(x, table, cap), TOL[dt], f"decode cap {cap}")
+  # argmax: the first maximum, also where a row holds the same value many times
+  lg = oracle.logits(x, table, 30.0)
+  lg[3, 17] = lg[3, 900] = lg[3].max() + 1
+  lg[5] = 0.25
+  assert torch.equal(rg.argmax(lg.to(DEV)).cpu().long(), torch.argmax(lg.float(), dim=-1))
+  with pytest.raises(TypeError):
+    emb.encode(tok.to(DEV).float())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_sampler(rg, dtype):
+  """The captured decode loop reproduces step-by-step decoding, the reference's greedy tokens in
+  float32, and prefill(T) followed by decoding == prefill(T-1) + the last token as a step."""
+  s = "f32" if dtype == "float32" else "bf16"
+  case = C.case_by_name(f"griffin_{s}_512_h2_v1024")
+  g = load_golden(case.name)
+  m = _griffin(rg, case, C.make_params(case))
+  tokens = C.make_inputs(case)["tokens"].to(DEV)
+  steps = 9
+  eager = rg.GreedySampler(m, use_cuda_graph=False)(tokens, steps, return_logits=True)
+  graph = rg.GreedySampler(m, use_cuda_graph=True)(tokens, steps, return_logits=True)
+  assert eager.tokens.shape == (case.batch, steps) and eager.tokens.dtype == torch.int32
+  assert torch.equal(eager.tokens, graph.tokens)
+  assert torch.equal(eager.logits, graph.logits)
+  # the prompt's positions here are 0..T-1 (one document), not the fixture's two documents, so
+  # compare with a plain forward of the same positions
+  pos = torch.arange(case.seq, device=DEV, dtype=torch.int32).repeat(case.batch, 1)
+  logits, cache = m(tokens, pos)
+  assert_close(eager.logits[:, 0], logits[:, -1], TOL[case.torch_dtype], "first logits")
+  tok = rg.argmax(logits[:, -1])
+  if dtype == "float32":
+    assert torch.equal(tok, eager.tokens[:, 0])
+  ref = [tok]
+  for i in range(steps - 1):
+    lg, cache = m(ref[-1][:, None], pos[:, -1:] + 1 + i, cache)
+    ref.append(rg.argmax(lg[:, 0]))
+    assert_close(eager.logits[:, i + 1], lg[:, 0], TOL[case.torch_dtype], f"logits {i + 1}")
+  if dtype == "float32":
+    assert torch.equal(torch.stack(ref, dim=1), eager.tokens)
+  # left padding: lengths differ, positions of the padding are -1
+  lengths = torch.tensor([case.seq, case.seq - 5])
+  padded = rg.GreedySampler(m)(tokens, 4, input_lengths=lengths)
+  assert padded.tokens.shape == (case.batch, 4)
+  assert torch.equal(padded.tokens[0], eager.tokens[0, :4]) or dtype == "bfloat16"
+  # EOS: everything after a sequence's first EOS is padding
+  eos = int(eager.tokens[0, 2])
+  out = rg.GreedySampler(m, eos_id=eos, pad_id=-7)(tokens, steps)
+  first = int((eager.tokens[0] == eos).nonzero()[0])
+  assert torch.equal(out.tokens[0, :first + 1], eager.tokens[0, :first + 1])
+  assert bool((out.tokens[0, first + 1:] == -7).all())

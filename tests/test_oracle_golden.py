@@ -106,6 +106,20 @@ def test_oracle_matches_reference(case, oracle):
                                         case.heads, case.window, cache)
       r = (y.float() + xs.float()).to(xs.dtype)
       chk(oracle.residual_channel(r, *mlp), f"out_step{i}", True)
+  elif case.kind == "griffin":
+    run = lambda tok, ps, cache: oracle.griffin(p, C.GRIFFIN_BLOCKS, case.heads, case.window,
+                                                C.GRIFFIN_SOFT_CAP, tok, ps, cache)
+    lg, cache = run(inp["tokens"], pos, None)
+    # the first block's state pins the rounding model bit for bit; three blocks deep, one-ulp
+    # differences of a few elements have passed through dense contractions, so the later tensors
+    # are held to the path's tolerance only
+    chk(cache["blocks.0"][0], "h_0"); chk(cache["blocks.1"][1], "conv_1")
+    chk(lg, "logits", True); chk(cache["blocks.2"][0], "keys_2", True)
+    for i in range(case.decode_steps):
+      tok = torch.from_numpy(g[f"tokens_step{i}"])[:, None]
+      lg, cache = run(tok, C.decode_positions(case, pos, i), cache)
+      chk(lg, f"logits_step{i}", True)
+    chk(cache["blocks.0"][0], "h_0_final", True); chk(cache["blocks.2"][0], "keys_2_final", True)
   elif case.kind == "mlp":
     chk(oracle.mlp(inp["x"], p["mlp_block.ffw_up.w"], p["mlp_block.ffw_up.b"],
                    p["mlp_block.ffw_down.weight"], p["mlp_block.ffw_down.bias"]), "out")
