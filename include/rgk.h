@@ -307,6 +307,26 @@ RGK_API int rgk_local_attention_prefill(const void* q, const void* k, const void
                                         void* workspace, size_t workspace_bytes, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * LocalAttentionBlock.forward with a cache: one new token per sequence against the ring buffer
+ * (recurrentgemma/torch/modules.py:437-476, mask of torch/modules.py:155-184, ring update of
+ * torch/modules.py:187-286).
+ *   q [B,N,head_dim] and k_new [B,head_dim] rotated (rgk_rope), v_new [B,head_dim];
+ *   keys, values [B,W,head_dim] (the cache's [B,W,1,head_dim]), num_tokens [B] int32
+ *   ->  out [B,N*head_dim]: bfloat16-rounded scaled logits over the W ring entries the query sees
+ *   (positions num_tokens - W .. num_tokens - 1) and the new key, float32 softmax, probabilities
+ *   rounded, product with the values.  update != 0: afterwards k_new / v_new are stored in ring slot
+ *   num_tokens % W and num_tokens grows by one, all in place (clone the cache first for the
+ *   reference's functional form).  float32 or bfloat16, head_dim 256, N in {1,2,4,8,10,16},
+ *   N (W + 1) floats within 200 KiB; RGK_ESHAPE otherwise.
+ * workspace: rgk_attention_decode_workspace_bytes(B, N, W) bytes, 256-byte aligned.
+ * ---------------------------------------------------------------------------------------------- */
+RGK_API size_t rgk_attention_decode_workspace_bytes(int64_t B, int N, int window);
+RGK_API int rgk_local_attention_decode(const void* q, const void* k_new, const void* v_new,
+                                       void* keys, void* values, int* num_tokens, int64_t B, int N,
+                                       int head_dim, int window, int dtype, int update, void* out,
+                                       void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
  * The two ends of Griffin.forward around the residual blocks, and greedy sampling.
  * rgk_embed: Embedder.encode (recurrentgemma/torch/modules.py:991-998): out [M,D] =
  *   table[tokens[m], :] * scale (scale = sqrt(D) rounded to bfloat16, or 1), tokens RGK_I32 or

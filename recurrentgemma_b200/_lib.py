@@ -77,6 +77,9 @@ SIGNATURES = {
     "rgk_attention_workspace_bytes": (_sz, [_i64, _i64]),
     "rgk_local_attention_prefill": (_int, [_vp, _vp, _vp, _vp, _int, _i64, _i64, _int, _int, _int,
                                            _int, _vp, _vp, _sz, _vp]),
+    "rgk_attention_decode_workspace_bytes": (_sz, [_i64, _int, _int]),
+    "rgk_local_attention_decode": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _int, _int, _int, _int,
+                                          _int, _vp, _vp, _sz, _vp]),
     "rgk_embed": (_int, [_vp, _int, _vp, _i64, _i64, _i64, ctypes.c_float, _int, _vp, _vp]),
     "rgk_logits": (_int, [_vp, _vp, _i64, _i64, _i64, ctypes.c_float, _int, _vp, _vp, _vp]),
     "rgk_argmax": (_int, [_vp, _i64, _i64, _int, _vp, _vp]),

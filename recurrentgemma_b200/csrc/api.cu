@@ -760,6 +760,40 @@ int rgk_local_attention_prefill(const void* q, const void* k, const void* v, con
   return RGK_OK;
 }
 
+size_t rgk_attention_decode_workspace_bytes(int64_t B, int N, int window) {
+  if (B < 0 || N < 1 || window < 1) return 0;
+  return rgk::attention_decode_workspace_bytes(B < 1 ? 1 : B, N, window);
+}
+
+int rgk_local_attention_decode(const void* q, const void* k_new, const void* v_new, void* keys,
+                               void* values, int* num_tokens, int64_t B, int N, int head_dim,
+                               int window, int dtype, int update, void* out, void* workspace,
+                               size_t workspace_bytes, void* stream) {
+  RGK_REQUIRE(dtype == RGK_F32 || dtype == RGK_BF16, RGK_EINVAL, "unknown dtype %d", dtype);
+  RGK_REQUIRE(B >= 0 && N >= 1 && window >= 1, RGK_EINVAL, "bad size");
+  RGK_REQUIRE(q && k_new && v_new && keys && values && num_tokens && out, RGK_EINVAL,
+              "NULL pointer argument");
+  RGK_REQUIRE(aligned16(q) && aligned16(k_new) && aligned16(v_new) && aligned16(keys) &&
+                  aligned16(values) && aligned16(out), RGK_EALIGN,
+              "pointers must be 16-byte aligned");
+  RGK_REQUIRE(rgk::attention_decode_supported(head_dim, N, window), RGK_ESHAPE,
+              "the decode attention kernel covers head dimension 256, 1/2/4/8/10/16 query heads and "
+              "heads x (window + 1) floats within 200 KiB (head_dim %d, heads %d, window %d)",
+              head_dim, N, window);
+  if (B == 0) return RGK_OK;
+  const size_t need = rgk_attention_decode_workspace_bytes(B, N, window);
+  RGK_REQUIRE(workspace != nullptr && workspace_bytes >= need, RGK_EWORKSPACE,
+              "workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+  RGK_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255u) == 0, RGK_EALIGN,
+              "workspace must be 256-byte aligned");
+  RGK_CHECK_DEVICE();
+  RGK_CUDA(rgk::launch_attention_decode(q, k_new, v_new, keys, values, num_tokens, B, N, window,
+                                        dtype, update, out, workspace,
+                                        static_cast<cudaStream_t>(stream)),
+           "decode attention launch");
+  return RGK_OK;
+}
+
 int rgk_recurrent_path_decode(const void* xb, const void* yb, const void* segment_pos,
                               int pos_dtype, const rgk_params* p, const float* h_in,
                               const void* conv_cache_in, int64_t B, int64_t E, int H, int W,

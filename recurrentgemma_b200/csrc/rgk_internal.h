@@ -71,6 +71,16 @@ cudaError_t launch_dense_tc(const void* x, const void* w, const void* bias, cons
                             int64_t M, int K, int N, int gelu, void* out, int* status,
                             cudaStream_t s, float cap = 0.0f);
 
+// attention_decode.cu: one new token per sequence against the ring cache keys / values [B,W,256]
+// (num_tokens [B] int32 tokens seen so far): q [B,N,256] and k_new [B,256] rotated, v_new [B,256]
+// -> out [B,N*256]; update != 0 then stores k_new / v_new in ring slot num_tokens % W and adds one
+// to num_tokens.  ws: attention_decode_workspace_bytes.
+bool attention_decode_supported(int hd, int N, int W);
+size_t attention_decode_workspace_bytes(int64_t B, int N, int W);
+cudaError_t launch_attention_decode(const void* q, const void* k_new, const void* v_new, void* keys,
+                                    void* values, int* num_tokens, int64_t B, int N, int W,
+                                    int dtype, int update, void* out, void* ws, cudaStream_t s);
+
 // embed.cu: rows of the embedding table scaled by a constant (Embedder.encode), and the index of
 // the first maximum of every row of a [M, V] matrix (greedy sampling).
 cudaError_t launch_embed(const void* tokens, int tokens64, const void* table, int64_t M, int64_t V,

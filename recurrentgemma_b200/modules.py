@@ -18,6 +18,10 @@ from recurrentgemma_b200 import _lib
 from recurrentgemma_b200 import layers
 
 
+# Fewest rows for which the tensor-core GEMM of the library is used (see MLPBlock._fusable).
+SMALL_M = 1024
+
+
 class RecurrentBlockCache(NamedTuple):
   """Field order and dtypes of recurrentgemma/torch/modules.py:32-37."""
   rg_lru_state: torch.Tensor   # [B, lru_width] float32
@@ -269,7 +273,10 @@ class MLPBlock(nn.Module):
                           std=math.sqrt(self.final_w_init_variance_scale / self.expanded_width))
 
   def _fusable(self, x: torch.Tensor) -> bool:
-    return (x.dtype == torch.bfloat16 and self.width % 8 == 0 and self.expanded_width % 64 == 0)
+    # below SMALL_M rows the 128 x 256 tiles of the GEMM leave most SMs without a tile (a decode
+    # step has M = batch): library contractions, which split K, are used there
+    return (x.dtype == torch.bfloat16 and self.width % 8 == 0 and self.expanded_width % 64 == 0
+            and x.numel() // x.shape[-1] >= SMALL_M)
 
   def _packed_up(self) -> int:
     """Device pointer of the K-major, gate/value-interleaved copy of ffw_up the GeGLU GEMM reads,
@@ -301,8 +308,12 @@ class MLPBlock(nn.Module):
     assert x.shape[-1] == self.width
     if not self._fusable(x):
       xin = x if pre_norm is None else pre_norm(x)
-      out = self.ffw_up(xin)
-      y = self.ffw_down(torch.nn.functional.gelu(out[0], approximate="tanh") * out[1])
+      # ffw_up as two plain contractions (the einsum of layers.Einsum would first make a permuted
+      # copy of the weights): the contraction and the bias add are two tensor operations
+      w, bias = self.ffw_up.w, self.ffw_up.b.reshape(2, -1)
+      gate = torch.matmul(xin, w[0]) + bias[0]
+      value = torch.matmul(xin, w[1]) + bias[1]
+      y = self.ffw_down(torch.nn.functional.gelu(gate, approximate="tanh") * value)
       if pre_norm is not None:
         return y + x
       return y if residual is None else y + residual
@@ -392,8 +403,9 @@ class LocalAttentionBlock(nn.Module):
   """Local multi-query attention (recurrentgemma/torch/modules.py:293-493): same constructor,
   parameter names (`proj_q/k/v.weight`, `proj_final.weight/.bias`), forward and cache.  bfloat16
   prefill with head dimension 256 runs on the library (projections on the tcgen05 GEMM, rotary
-  kernel, the two-pass tcgen05 attention kernel); the decode step and other shapes compose the
-  rotary kernel with library contractions."""
+  kernel, the two-pass tcgen05 attention kernel), and so does the decode step with head dimension
+  256 (rotary kernel, the two ring kernels; projections of a handful of rows are library GEMMs);
+  other shapes compose the rotary kernel with library contractions."""
 
   def __init__(self, width: int, num_heads: int, window_size: int,
                final_w_init_variance_scale: float = 1.0, device=None, dtype=None):
@@ -426,7 +438,7 @@ class LocalAttentionBlock(nn.Module):
     torch.nn.init.normal_(w, mean=0.0, std=math.sqrt(self.final_w_init_variance_scale / self.width))
 
   def _linear(self, x: torch.Tensor, lin: nn.Linear) -> torch.Tensor:
-    if x.dtype == torch.bfloat16 and x.numel() // x.shape[-1] >= 64:
+    if x.dtype == torch.bfloat16 and x.numel() // x.shape[-1] >= SMALL_M:
       return dense_linear(x, lin.weight, lin.bias)
     return lin(x)
 
@@ -472,6 +484,26 @@ class LocalAttentionBlock(nn.Module):
       keys, values = k, v
     else:
       assert t == 1, "with a cache the block takes one token at a time"
+      lib = _lib.load()
+      if (hd == 256 and n in (1, 2, 4, 8, 10, 16) and n * (w + 1) * 4 <= 200 * 1024
+          and cache.keys.dtype == x.dtype and cache.num_tokens.dtype == torch.int32):
+        # the library's decode kernels work on the ring in place; the reference's functional form
+        # is the same step on a copy of the cache
+        if inplace or not return_cache:
+          ring = cache
+          assert ring.keys.is_contiguous() and ring.values.is_contiguous()
+        else:
+          ring = AttentionBlockCache(keys=cache.keys.clone(), values=cache.values.clone(),
+                                     num_tokens=cache.num_tokens.clone())
+        enc = torch.empty((b, 1, n * hd), dtype=x.dtype, device=dev)
+        with torch.cuda.device(dev):
+          ws = _lib.workspace(dev, int(lib.rgk_attention_decode_workspace_bytes(b, n, w)))
+          _lib.check(lib.rgk_local_attention_decode(
+              q.data_ptr(), k.data_ptr(), v.contiguous().data_ptr(), ring.keys.data_ptr(),
+              ring.values.data_ptr(), ring.num_tokens.data_ptr(), b, n, hd, w,
+              _lib.dtype_code(x.dtype), 1 if return_cache else 0, enc.data_ptr(), ws.data_ptr(),
+              ws.numel(), _lib.stream_ptr(dev)))
+        return self._linear(enc, self.proj_final), (ring if return_cache else None)
       nt = cache.num_tokens.long()
       kq = nt // w
       j = torch.arange(w, device=dev)[None, :]

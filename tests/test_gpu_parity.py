@@ -24,6 +24,16 @@ def rg():
   return m
 
 
+@pytest.fixture(autouse=True)
+def _library_gemm_at_every_size(request, monkeypatch):
+  """The modules hand contractions of fewer than `modules.SMALL_M` rows to library GEMMs (decode
+  steps); the fixtures are small, so the tests lower that bound to reach this library's GEMM
+  kernels - except the sampler test, which keeps the default and so covers the other route."""
+  if not request.node.name.startswith("test_greedy_sampler"):
+    from recurrentgemma_b200 import modules
+    monkeypatch.setattr(modules, "SMALL_M", 1)
+
+
 def _block(rg, case, p):
   m = rg.RecurrentBlock(case.model_width, case.heads, case.lru_width, case.temporal_width,
                         device=DEV, dtype=case.torch_dtype)
