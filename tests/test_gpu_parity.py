@@ -722,3 +722,42 @@ def test_greedy_sampler(rg, dtype):
   first = int((eager.tokens[0] == eos).nonzero()[0])
   assert torch.equal(out.tokens[0, :first + 1], eager.tokens[0, :first + 1])
   assert bool((out.tokens[0, first + 1:] == -7).all())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("heads,window,prompt", [(10, 40, 7), (10, 40, 40), (4, 24, 61), (1, 8, 1)])
+def test_attention_decode_kernels_vs_oracle(rg, oracle, dtype, heads, window, prompt):
+  """The decode-step kernels on the ring cache (head dimension 256) against the oracle: a ring that
+  is not yet full, one that is exactly full, one that has wrapped; six steps each, in the
+  reference's functional form and in place."""
+  d = heads * 256
+  dt = {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype]
+  case = C.Case(f"attn_dec_{heads}_{window}_{prompt}", "attention", dtype, 3, prompt, d, heads,
+                width=d, window=window, pos="arange", decode_steps=6)
+  p = C.make_params(case)
+  inp = C.make_inputs(case)
+  m = rg.LocalAttentionBlock(d, heads, window, device=DEV, dtype=dt)
+  m.load_state_dict(p)
+  w = (p["proj_q.weight"], p["proj_k.weight"], p["proj_v.weight"], p["proj_final.weight"],
+       p["proj_final.bias"])
+  pos = inp["segment_pos"]
+  _, cache = m(inp["x"].to(DEV), pos.to(DEV))
+  _, c_r = oracle.attention_block(inp["x"], pos, *w, heads, window)
+  own = rg.AttentionBlockCache(*[t.clone() for t in cache])
+  for i in range(case.decode_steps):
+    xs, ps = inp[f"x_step{i}"], C.decode_positions(case, pos, i)
+    before = [t.clone() for t in cache]
+    y, cache_new = m(xs.to(DEV), ps.to(DEV), cache)
+    assert all(torch.equal(a, b) for a, b in zip(before, cache)), "the functional form must not write"
+    y2, own2 = m(xs.to(DEV), ps.to(DEV), own, inplace=True)
+    assert own2 is own
+    y_r, c_r = oracle.attention_block(xs, ps, *w, heads, window, c_r)
+    for out, ring, what in ((y, cache_new, "functional"), (y2, own, "in place")):
+      assert_close(out, y_r, TOL[dt], f"step {i} output ({what})")
+      assert_close(ring.keys, c_r[0], TOL[dt], f"step {i} keys ({what})")
+      assert_close(ring.values, c_r[1], TOL[dt], f"step {i} values ({what})")
+      assert torch.equal(ring.num_tokens.cpu(), c_r[2])
+    y3, none = m(xs.to(DEV), ps.to(DEV), cache, return_cache=False)
+    assert none is None and torch.equal(y3, y)
+    cache = cache_new
