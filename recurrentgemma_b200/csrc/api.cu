@@ -820,10 +820,11 @@ int rgk_recurrent_path_decode(const void* xb, const void* yb, const void* segmen
   RGK_CHECK_DEVICE();
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int bw = (int)(E / H);
-  if (gates_impl != RGK_GATES_SIMT && rgk::gates_tc_supported(dtype, bw, B) &&
-      conv_cache_out != conv_cache_in) {
+  if (gates_impl != RGK_GATES_SIMT && rgk::gates_tc_supported(dtype, bw, B)) {
     // The whole step in one kernel, and nothing else on the stream: the status word is not
     // cleared here (the kernel only ever raises it), so a decode loop is one launch per layer.
+    // The states may be updated in place: every element of h and of the conv cache is read and
+    // then written by one and the same thread.
     const void* packed = p->gates_packed;
     if (packed == nullptr) {
       RGK_CUDA(rgk::launch_pack_gate_weights(p->gate_x_w, p->gate_a_w, H, w.wpack, s),
@@ -837,7 +838,6 @@ int rgk_recurrent_path_decode(const void* xb, const void* yb, const void* segmen
              "fused decode launch");
     return RGK_OK;
   }
-  RGK_CUDA(cudaMemsetAsync(workspace, 0, sizeof(int), s), "cudaMemsetAsync");
   RGK_CUDA(cudaMemsetAsync(workspace, 0, sizeof(int), s), "cudaMemsetAsync");
   RGK_CUDA(rgk::launch_conv1d_decode(xb, conv_cache_in, p->conv_w, p->conv_b, B, E, dtype, w.c,
                                      conv_cache_out, s),

@@ -53,10 +53,10 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __nv_bfloat16*
                  const __nv_bfloat16* __restrict__ yb, const void* __restrict__ pos, int pos64,
                  const __nv_bfloat16* __restrict__ conv_w, const __nv_bfloat16* __restrict__ conv_b,
                  const __nv_bfloat16* __restrict__ a_param, const __nv_bfloat16* __restrict__ bias_x,
-                 const __nv_bfloat16* __restrict__ bias_a, const float* __restrict__ h_in,
-                 const __nv_bfloat16* __restrict__ cache_in, int M, int E,
-                 __nv_bfloat16* __restrict__ out, float* __restrict__ h_out,
-                 __nv_bfloat16* __restrict__ cache_out, WsHeader* hdr) {
+                 const __nv_bfloat16* __restrict__ bias_a, const float* h_in,
+                 const __nv_bfloat16* cache_in, int M, int E,
+                 __nv_bfloat16* __restrict__ out, float* h_out,
+                 __nv_bfloat16* cache_out, WsHeader* hdr) {
   extern __shared__ uint8_t smem_raw[];
   // aligned by an offset into the shared array, so that the address space stays known to the
   // compiler (shared-memory load/store instructions instead of generic ones)

@@ -33,6 +33,7 @@ class GreedySampler:
     self.eos_id = eos_id
     self.pad_id = pad_id
     self.use_cuda_graph = use_cuda_graph
+    self._state = None
     self._graph = None
     self._graph_key = None
 
@@ -50,6 +51,28 @@ class GreedySampler:
     pos = torch.arange(prompt_length, device=self.device, dtype=torch.int32)[None]
     pos = pos - prompt_length + input_lengths.to(self.device, torch.int32)[:, None]
     return torch.clip(pos, min=-1)
+
+  def _captured_step(self, b: int, cache):
+    """Static buffers for a batch of b sequences and the CUDA graph of one step on them, made on
+    first use and kept; `cache` (a model cache holding the prompt) is copied into the buffers."""
+    dev = self.device
+    if self._graph_key != (b, dev):
+      state = {"last_token": torch.zeros((b, 1), dtype=torch.int32, device=dev),
+               "next_token": torch.zeros((b, 1), dtype=torch.int32, device=dev),
+               "positions": torch.zeros((b, 1), dtype=torch.int32, device=dev),
+               "cache": _own(cache), "logits": None}
+      # one eager step creates every lazily made buffer of a decode step; capturing then records
+      # the launches without running them
+      self._step(state)
+      graph = torch.cuda.CUDAGraph()
+      torch.cuda.synchronize(dev)
+      with torch.cuda.graph(graph):
+        self._step(state)
+      self._state, self._graph, self._graph_key = state, graph, (b, dev)
+    for name, c in cache.items():
+      for dst, src in zip(self._state["cache"][name], c):
+        dst.copy_(src)
+    return self._state, self._graph
 
   def _step(self, state) -> None:
     """One sampling step (recurrentgemma/torch/sampler.py:137-187) on static buffers: reads
@@ -94,28 +117,16 @@ class GreedySampler:
       out_logits[:, 0] = logits[:, 0]
     first = modules.argmax(logits[:, 0])
     out_tokens[:, 0] = first
-    state = {
-        "last_token": first[:, None].clone(),
-        "next_token": torch.empty((b, 1), dtype=torch.int32, device=dev),
-        "positions": (pos[:, -1:] + 1).contiguous(),
-        "cache": _own(cache),
-        "logits": None,
-    }
     graph = None
-    if self.use_cuda_graph and total_generation_steps > 2:
-      # one eager step warms every lazily created buffer up, then the step is captured
-      self._step(state)
-      out_tokens[:, 1] = state["next_token"][:, 0]
-      if return_logits:
-        out_logits[:, 1] = state["logits"][:, 0]
-      start = 2
-      graph = torch.cuda.CUDAGraph()
-      torch.cuda.synchronize(dev)
-      with torch.cuda.graph(graph):
-        self._step(state)
+    if self.use_cuda_graph and total_generation_steps > 1:
+      state, graph = self._captured_step(b, cache)
+      state["last_token"].copy_(first[:, None])
+      state["positions"].copy_(pos[:, -1:] + 1)
     else:
-      start = 1
-    for step in range(start, total_generation_steps):
+      state = {"last_token": first[:, None].clone(),
+               "next_token": torch.empty((b, 1), dtype=torch.int32, device=dev),
+               "positions": (pos[:, -1:] + 1).contiguous(), "cache": _own(cache), "logits": None}
+    for step in range(1, total_generation_steps):
       if graph is None:
         self._step(state)
       else:
