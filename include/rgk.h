@@ -345,6 +345,14 @@ RGK_API int rgk_logits(const void* x, const void* table, int64_t M, int64_t D, i
                        int dtype, void* out, int* status, void* stream);
 RGK_API int rgk_argmax(const void* x, int64_t M, int64_t V, int dtype, int* out, void* stream);
 
+/* The element-wise part of MLPBlock.forward (recurrentgemma/torch/layers.py:700-703,
+ * torch/modules.py:749-751) for callers that contract ffw_up elsewhere (a decode step of a few
+ * rows): up [2,M,X] (the two contractions, rounded), bias [2,X]  ->  out [M,X] =
+ * gelu_tanh(up[0] + bias[0]) * (up[1] + bias[1]), each of the four tensor operations rounded.
+ * float32 or bfloat16; X a multiple of a 16-byte pack. */
+RGK_API int rgk_geglu_bias(const void* up, const void* bias, int64_t M, int64_t X, int dtype,
+                           void* out, void* stream);
+
 /* Scratch needed by the calls above for a problem of this size (an upper bound over the entry
  * points, so one buffer serves all of them).  Returns 0 on invalid arguments. */
 RGK_API size_t rgk_workspace_bytes(int64_t B, int64_t T, int64_t E, int dtype);

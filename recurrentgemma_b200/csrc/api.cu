@@ -466,6 +466,22 @@ int rgk_argmax(const void* x, int64_t M, int64_t V, int dtype, int* out, void* s
   return RGK_OK;
 }
 
+int rgk_geglu_bias(const void* up, const void* bias, int64_t M, int64_t X, int dtype, void* out,
+                   void* stream) {
+  RGK_REQUIRE(dtype == RGK_F32 || dtype == RGK_BF16, RGK_EINVAL, "unknown dtype %d", dtype);
+  RGK_REQUIRE(M >= 0 && X >= 1, RGK_EINVAL, "bad size (M=%lld X=%lld)", (long long)M, (long long)X);
+  RGK_REQUIRE(up && bias && out, RGK_EINVAL, "NULL pointer argument");
+  RGK_REQUIRE(aligned16(up) && aligned16(bias) && aligned16(out), RGK_EALIGN,
+              "pointers must be 16-byte aligned");
+  RGK_REQUIRE((X * (int64_t)elem_size(dtype)) % 16 == 0, RGK_ESHAPE,
+              "the expanded width must be a multiple of a 16-byte pack (X=%lld)", (long long)X);
+  if (M == 0) return RGK_OK;
+  RGK_CHECK_DEVICE();
+  RGK_CUDA(rgk::launch_geglu_bias(up, bias, M, X, dtype, out, static_cast<cudaStream_t>(stream)),
+           "geglu launch");
+  return RGK_OK;
+}
+
 size_t rgk_block_workspace_bytes(int64_t B, int64_t T, int64_t D, int64_t E, int dtype) {
   if (B < 0 || T < 0 || D < 0 || E < 0 || (dtype != RGK_F32 && dtype != RGK_BF16)) return 0;
   if (T < 1) T = 1;

@@ -3,7 +3,11 @@
 //   embed_kernel   Embedder.encode: out[m, :] = table[tokens[m], :] * scale, one rounding in
 //                  bfloat16 (the reference multiplies by sqrt(width) cast to bfloat16; the caller
 //                  passes that constant, or 1);
-//   argmax_kernel  greedy sampling: the index of the first maximum of each row of the logits.
+//   argmax_kernel  greedy sampling: the index of the first maximum of each row of the logits;
+//   geglu_bias_kernel  the element-wise part of MLPBlock.forward for a decode step, where the two
+//                  halves of ffw_up come from a library contraction (torch/layers.py:700-703,
+//                  torch/modules.py:749-751): gelu(up[0] + b[0]) * (up[1] + b[1]), each of the four
+//                  tensor operations rounded.
 #include "rgk_common.cuh"
 #include "rgk_internal.h"
 
@@ -85,7 +89,46 @@ __global__ void argmax_kernel(const T* __restrict__ x, int64_t M, int64_t V, int
   }
 }
 
+// up [2, M, X], bias [2, X] -> out [M, X]; one 16-byte pack per thread.
+template <typename T>
+__global__ void geglu_bias_kernel(const T* __restrict__ up, const T* __restrict__ bias, int64_t M,
+                                  int64_t X, T* __restrict__ out) {
+  constexpr int kPer = 16 / (int)sizeof(T);
+  constexpr bool kBf16 = Traits<T>::kBf16;
+  const int64_t packs_row = X / kPer;
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= M * packs_row) return;
+  const int64_t col = (idx % packs_row) * kPer, off = (idx / packs_row) * X + col;
+  float g[kPer], v[kPer], bg[kPer], bv[kPer], o[kPer];
+  unpack<T>(ld_stream(up + off), g);
+  unpack<T>(ld_stream(up + M * X + off), v);
+  unpack<T>(*reinterpret_cast<const uint4*>(bias + col), bg);
+  unpack<T>(*reinterpret_cast<const uint4*>(bias + X + col), bv);
+#pragma unroll
+  for (int i = 0; i < kPer; ++i) {
+    const float gate = rnd<kBf16>(g[i] + bg[i]), value = rnd<kBf16>(v[i] + bv[i]);
+    o[i] = rnd<kBf16>(gelu_tanh_<kBf16>(gate)) * value;
+  }
+  *reinterpret_cast<uint4*>(out + off) = pack<T>(o);
+}
+
 }  // namespace
+
+cudaError_t launch_geglu_bias(const void* up, const void* bias, int64_t M, int64_t X, int dtype,
+                              void* out, cudaStream_t s) {
+  if (M == 0) return cudaSuccess;
+  const int per = dtype == 1 ? 8 : 4;
+  const int64_t n = M * (X / per);
+  const unsigned grid = (unsigned)((n + 255) / 256);
+  if (dtype == 1)
+    geglu_bias_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)up,
+                                                         (const __nv_bfloat16*)bias, M, X,
+                                                         (__nv_bfloat16*)out);
+  else
+    geglu_bias_kernel<float><<<grid, 256, 0, s>>>((const float*)up, (const float*)bias, M, X,
+                                                  (float*)out);
+  return cudaGetLastError();
+}
 
 cudaError_t launch_embed(const void* tokens, int tokens64, const void* table, int64_t M, int64_t V,
                          int64_t D, float scale, int dtype, void* out, cudaStream_t s) {

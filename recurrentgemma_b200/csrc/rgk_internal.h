@@ -86,6 +86,9 @@ cudaError_t launch_attention_decode(const void* q, const void* k_new, const void
 cudaError_t launch_embed(const void* tokens, int tokens64, const void* table, int64_t M, int64_t V,
                          int64_t D, float scale, int dtype, void* out, cudaStream_t s);
 cudaError_t launch_argmax(const void* x, int64_t M, int64_t V, int dtype, int* out, cudaStream_t s);
+// up [2,M,X], bias [2,X] -> out [M,X] = gelu_tanh(up[0] + bias[0]) * (up[1] + bias[1]), four roundings.
+cudaError_t launch_geglu_bias(const void* up, const void* bias, int64_t M, int64_t X, int dtype,
+                              void* out, cudaStream_t s);
 
 // ffw_up.w [2, D, X], ffw_up.b [2, X] -> packed_w [2X, D], packed_b [2X] (gemm_tc.cu, mode 3).
 cudaError_t launch_pack_mlp_up(const void* w, const void* b, int D, int X, void* packed_w,

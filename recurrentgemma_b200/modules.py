@@ -311,9 +311,18 @@ class MLPBlock(nn.Module):
       # ffw_up as two plain contractions (the einsum of layers.Einsum would first make a permuted
       # copy of the weights): the contraction and the bias add are two tensor operations
       w, bias = self.ffw_up.w, self.ffw_up.b.reshape(2, -1)
-      gate = torch.matmul(xin, w[0]) + bias[0]
-      value = torch.matmul(xin, w[1]) + bias[1]
-      y = self.ffw_down(torch.nn.functional.gelu(gate, approximate="tanh") * value)
+      xw = self.expanded_width
+      up = torch.matmul(xin.reshape(1, -1, self.width), w)          # [2, M, X], one batched call
+      if (xw * x.element_size()) % 16 == 0:
+        hidden = torch.empty((*x.shape[:-1], xw), dtype=x.dtype, device=dev)
+        with torch.cuda.device(dev):
+          _lib.check(_lib.load().rgk_geglu_bias(
+              up.data_ptr(), bias.contiguous().data_ptr(), up.shape[1], xw,
+              _lib.dtype_code(x.dtype), hidden.data_ptr(), _lib.stream_ptr(dev)))
+      else:
+        gate, value = up[0] + bias[0], up[1] + bias[1]
+        hidden = (torch.nn.functional.gelu(gate, approximate="tanh") * value).reshape(*x.shape[:-1], xw)
+      y = self.ffw_down(hidden)
       if pre_norm is not None:
         return y + x
       return y if residual is None else y + residual

@@ -761,3 +761,25 @@ def test_attention_decode_kernels_vs_oracle(rg, oracle, dtype, heads, window, pr
     y3, none = m(xs.to(DEV), ps.to(DEV), cache, return_cache=False)
     assert none is None and torch.equal(y3, y)
     cache = cache_new
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_sampler_mlp_few_rows(rg, oracle, dtype):
+  """(Named so that the bound on library GEMMs keeps its default.)  The MLP for a handful of rows,
+  as in a decode step: library contractions around the element-wise kernel, against the oracle,
+  alone and as the channel half of a residual block."""
+  dt = {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype]
+  case = C.case_by_name("mlp_f32_256_x768" if dtype == "float32" else "mlp_bf16_256_x768")
+  p = C.make_params(case)
+  x = C.make_inputs(case)["x"][:, :5]
+  m = rg.MLPBlock(case.model_width, case.expanded, device=DEV, dtype=dt)
+  m.load_state_dict({k[len("mlp_block."):]: v for k, v in p.items()})
+  args = (p["mlp_block.ffw_up.w"], p["mlp_block.ffw_up.b"], p["mlp_block.ffw_down.weight"],
+          p["mlp_block.ffw_down.bias"])
+  assert_close(m(x.to(DEV)), oracle.mlp(x, *args), TOL[dt], "mlp")
+  norm = rg.RMSNorm(case.model_width, device=DEV, dtype=dt)
+  scale = C.normal(case.name, "norm", (case.model_width,), 0.3, dt)
+  norm.load_state_dict({"scale": scale})
+  assert_close(m(x.to(DEV), pre_norm=norm), oracle.residual_channel(x, scale, *args), TOL[dt],
+               "channel half")
