@@ -714,7 +714,7 @@ def run_griffin(args):
   dev = torch.device("cuda", local)
   if world > 1:
     dist.init_process_group("nccl", device_id=dev)
-  total_b, prompt, gen_steps = args.batch or 64, args.seq or 2048, 512
+  total_b, prompt, gen_steps = args.batch or 64, args.seq or 2048, args.gen_steps
   b = max(1, total_b // world)
   cfg = rg.GriffinConfig.recurrent_gemma_2b()
   torch.manual_seed(17)                        # the same weights on every rank
@@ -789,6 +789,7 @@ def main():
   ap.add_argument("--seq", type=int, default=None,
                   help="cfg3: sequence length (default 65536); cfg4: prompt length (default 2048)")
   ap.add_argument("--gather", action="store_true", help="cfg3: all_gather the output every step")
+  ap.add_argument("--gen-steps", type=int, default=512, help="cfg4: greedy decode steps (default 512)")
   ap.add_argument("--gpus", type=int, default=1)
   ap.add_argument("--steps", type=int, default=600)
   ap.add_argument("--warmup", type=int, default=3)
