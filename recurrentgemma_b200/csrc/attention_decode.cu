@@ -41,14 +41,18 @@ __device__ __forceinline__ void load_row(const T* row, int lane, float (&f)[kPer
 // filled.  So the visible slots are exactly j < nt.
 __device__ __forceinline__ int visible_slots(int nt, int W) { return nt < W ? nt : W; }
 
-// grid (B, splits): the warps of CTA (b, c) take entries 8 c + warp, + 8 splits, ... of the W ring
-// rows followed by the new key (entry W).  logits: float [B, kN, W + 1].
+constexpr int kSplits = 8;                 // CTAs per sequence in the logits kernel
+
+// grid (B, kSplits): the warps of CTA (b, c) take entries 8 c + warp, + 8 kSplits, ... of the W ring
+// rows followed by the new key (entry W).  logits: float [B, kN, W + 1]; stats: float2 [B, kSplits, kN] = the maximum of the CTA's
+// visible logits of a head and the sum of exp(logit - maximum) over them.
 template <typename T, int kN>
 __global__ void __launch_bounds__(256)
 attn_decode_logits_kernel(const T* __restrict__ q, const T* __restrict__ k_new,
                           const T* __restrict__ keys, const int* __restrict__ num_tokens, int W,
-                          float* __restrict__ logits) {
+                          float* __restrict__ logits, float2* __restrict__ stats) {
   constexpr bool kBf16 = Traits<T>::kBf16;
+  __shared__ float2 s_part[8][kN];
   const int b = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nt = num_tokens[b];
   const float scale = 0.0625f;                     // 256^-1/2
@@ -58,6 +62,7 @@ attn_decode_logits_kernel(const T* __restrict__ q, const T* __restrict__ k_new,
   float* lg = logits + (int64_t)b * kN * (W + 1);
   const int stride = gridDim.y * 8;
   const int n_vis = visible_slots(nt, W);
+  float m_run = kMasked, l_run = 0.0f;             // lanes < kN: this warp's statistics of head `lane`
   for (int s = blockIdx.y * 8 + warp; s <= W; s += stride) {
     const bool self = s == W;
     if (!self && s >= n_vis) {
@@ -84,87 +89,67 @@ attn_decode_logits_kernel(const T* __restrict__ q, const T* __restrict__ k_new,
 #pragma unroll
     for (int n = 0; n < kN; ++n)
       if (lane == n) mine = rnd<kBf16>(rnd<kBf16>(part[n]) * scale);
-    if (lane < kN) lg[(int64_t)lane * (W + 1) + s] = mine;
+    if (lane < kN) {
+      lg[(int64_t)lane * (W + 1) + s] = mine;
+      const float m_new = fmaxf(m_run, mine);
+      l_run = l_run * __expf(m_run - m_new) + __expf(mine - m_new);
+      m_run = m_new;
+    }
+  }
+  if (lane < kN) s_part[warp][lane] = make_float2(m_run, l_run);
+  __syncthreads();
+  if (threadIdx.x < kN) {
+    float m = kMasked, l = 0.0f;
+    for (int w = 0; w < 8; ++w) m = fmaxf(m, s_part[w][threadIdx.x].x);
+    for (int w = 0; w < 8; ++w) {
+      const float2 p = s_part[w][threadIdx.x];
+      if (p.x > kMasked) l += p.y * __expf(p.x - m);
+    }
+    stats[((int64_t)b * kSplits + blockIdx.y) * kN + threadIdx.x] = make_float2(m, l);
   }
 }
 
-// grid (B, 4): CTA (b, dq) owns 64 of the 256 value columns.  Threads: warp w takes ring rows
-// w, w + 8, ...; a lane holds two adjacent columns.  The probabilities of all kN heads of this
-// sequence are first formed in shared memory (each CTA of a sequence repeats that small step).
+// grid (B, 4): CTA (b, dq) owns 64 of the 256 value columns.  A warp reads four ring rows per
+// instruction: lane = (row of the four, 8 adjacent columns).  The 8 lanes of a row form that row's
+// probabilities (head j and j + 8 in lane j) from the logits and the sequence's statistics, and
+// pass them round by shuffles.
 template <typename T, int kN>
 __global__ void __launch_bounds__(256)
-attn_decode_values_kernel(const float* __restrict__ logits, const T* __restrict__ k_new,
-                          const T* __restrict__ v_new, T* __restrict__ keys, T* __restrict__ values,
+attn_decode_values_kernel(const float* __restrict__ logits, const float2* __restrict__ stats,
+                          const T* __restrict__ k_new, const T* __restrict__ v_new,
+                          T* __restrict__ keys, T* __restrict__ values,
                           int* __restrict__ num_tokens, int W, int update, T* __restrict__ out) {
   constexpr bool kBf16 = Traits<T>::kBf16;
-  extern __shared__ float s_p[];                   // [kN][W + 1] probabilities, then the partial sums
-  __shared__ float s_red[8][kN];
-  __shared__ float s_stat[2][kN];
+  static_assert(kN <= 16, "two heads per lane of a row's eight");
+  __shared__ float s_acc[8][kN][64];
+  __shared__ float s_stat[2][16];                  // maximum and 1 / sum of every head
   const int b = blockIdx.x, dq = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nt = num_tokens[b];
   const int L = W + 1;
   const float* lg = logits + (int64_t)b * kN * L;
-  // ---- softmax statistics of every head: maximum, then the sum of exponentials -----------------
-  float mx[kN], sm[kN];
-#pragma unroll
-  for (int n = 0; n < kN; ++n) {
-    float m = kMasked;
-    for (int s = threadIdx.x; s < L; s += 256) m = fmaxf(m, lg[(int64_t)n * L + s]);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-    if (lane == 0) s_red[warp][n] = m;
-  }
-  __syncthreads();
-  if (threadIdx.x < kN) {
-    float m = kMasked;
-    for (int w = 0; w < 8; ++w) m = fmaxf(m, s_red[w][threadIdx.x]);
-    s_stat[0][threadIdx.x] = m;
-  }
-  __syncthreads();
-#pragma unroll
-  for (int n = 0; n < kN; ++n) {
-    mx[n] = s_stat[0][n];
-    float a = 0.0f;
-    for (int s = threadIdx.x; s < L; s += 256) {
-      const float v = lg[(int64_t)n * L + s];
-      const float e = v > kMasked ? __expf(v - mx[n]) : 0.0f;
-      s_p[n * L + s] = e;
-      a += e;
+  if (threadIdx.x < 16) {
+    float m = kMasked, l = 0.0f;
+    if (threadIdx.x < kN) {
+      const float2* st = stats + (int64_t)b * kSplits * kN + threadIdx.x;
+      for (int c = 0; c < kSplits; ++c) m = fmaxf(m, st[c * kN].x);
+      for (int c = 0; c < kSplits; ++c) {
+        const float2 p = st[c * kN];
+        if (p.x > kMasked) l += p.y * __expf(p.x - m);
+      }
     }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
-    sm[n] = a;
-  }
-  __syncthreads();                                 // s_red is rewritten
-#pragma unroll
-  for (int n = 0; n < kN; ++n)
-    if (lane == 0) s_red[warp][n] = sm[n];
-  __syncthreads();
-  if (threadIdx.x < kN) {
-    float a = 0.0f;
-    for (int w = 0; w < 8; ++w) a += s_red[w][threadIdx.x];
-    s_stat[1][threadIdx.x] = a;
+    s_stat[0][threadIdx.x] = m;
+    s_stat[1][threadIdx.x] = l > 0.0f ? 1.0f / l : 0.0f;
   }
   __syncthreads();
-  // normalised probabilities, rounded to the activation dtype as the reference casts them
-#pragma unroll
-  for (int n = 0; n < kN; ++n) {
-    const float inv = 1.0f / s_stat[1][n];
-    for (int s = threadIdx.x; s < L; s += 256) s_p[n * L + s] = rnd<kBf16>(s_p[n * L + s] * inv);
-  }
-  __syncthreads();
-  // ---- probabilities x values over this CTA's 64 columns ----------------------------------------
-  // a lane holds 8 adjacent columns of one of the 4 rows its warp reads per instruction
-  const int r4 = lane >> 3, c8 = (lane & 7) * 8;
+  const int r4 = lane >> 3, j = lane & 7, c8 = j * 8;
+  const float m_lo = s_stat[0][j], inv_lo = s_stat[1][j];
+  const float m_hi = s_stat[0][j + 8], inv_hi = s_stat[1][j + 8];
   const int n_vis = visible_slots(nt, W);
   float acc[kN][8];
 #pragma unroll
   for (int n = 0; n < kN; ++n)
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[n][i] = 0.0f;
-  auto row_of = [&](int s) {
-    return s == W ? v_new + (int64_t)b * kHdD : values + ((int64_t)b * W + s) * kHdD;
-  };
   auto load8 = [&](const T* p, float (&f)[8]) {
     if constexpr (kBf16) {
       unpack<T>(ld_stream(p), f);
@@ -175,22 +160,34 @@ attn_decode_values_kernel(const float* __restrict__ logits, const T* __restrict_
   };
   // entries n_vis .. W - 1 are empty; entry W (the new value) is taken as if it were entry n_vis
   const int total = n_vis + 1;
+  // (the trip count is the same for every lane of a warp: the shuffles below need all of them)
 #pragma unroll 1
-  for (int e0 = warp * 4 + r4; e0 < total; e0 += 4 * 32) {
-    float vf[4][8];
+  for (int base = warp * 4; base < total; base += 4 * 32) {
+    float vf[4][8], p_lo[4], p_hi[4];
     int ss[4];
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
-      const int e = e0 + 32 * u;
+      const int e = base + r4 + 32 * u;
       ss[u] = e < total ? (e == n_vis ? W : e) : -1;
-      if (ss[u] >= 0) load8(row_of(ss[u]) + dq * 64 + c8, vf[u]);
+      if (ss[u] >= 0) {
+        const T* row = ss[u] == W ? v_new + (int64_t)b * kHdD : values + ((int64_t)b * W + ss[u]) * kHdD;
+        load8(row + dq * 64 + c8, vf[u]);
+        p_lo[u] = j < kN ? lg[(int64_t)j * L + ss[u]] : kMasked;
+        p_hi[u] = j + 8 < kN ? lg[(int64_t)(j + 8) * L + ss[u]] : kMasked;
+      } else {
+        p_lo[u] = p_hi[u] = kMasked;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) vf[u][i] = 0.0f;
+      }
     }
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
-      if (ss[u] < 0) continue;
+      // normalised probabilities, rounded to the activation dtype as the reference casts them
+      const float pl = p_lo[u] > kMasked ? rnd<kBf16>(__expf(p_lo[u] - m_lo) * inv_lo) : 0.0f;
+      const float ph = p_hi[u] > kMasked ? rnd<kBf16>(__expf(p_hi[u] - m_hi) * inv_hi) : 0.0f;
 #pragma unroll
       for (int n = 0; n < kN; ++n) {
-        const float p = s_p[n * L + ss[u]];
+        const float p = __shfl_sync(0xffffffffu, n < 8 ? pl : ph, (lane & 24) | (n & 7));
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[n][i] = fmaf(p, vf[u][i], acc[n][i]);
       }
@@ -204,20 +201,18 @@ attn_decode_values_kernel(const float* __restrict__ logits, const T* __restrict_
       acc[n][i] += __shfl_xor_sync(0xffffffffu, acc[n][i], 8);
       acc[n][i] += __shfl_xor_sync(0xffffffffu, acc[n][i], 16);
     }
-  __syncthreads();                                 // the probabilities are no longer needed
-  float* s_acc = s_p;                              // [8 warps][kN][64]
   if (r4 == 0) {
 #pragma unroll
     for (int n = 0; n < kN; ++n)
 #pragma unroll
-      for (int i = 0; i < 8; ++i) s_acc[(warp * kN + n) * 64 + c8 + i] = acc[n][i];
+      for (int i = 0; i < 8; ++i) s_acc[warp][n][c8 + i] = acc[n][i];
   }
   __syncthreads();
   for (int i = threadIdx.x; i < kN * 64; i += 256) {
     const int n = i / 64, c = i % 64;
     float a = 0.0f;
 #pragma unroll
-    for (int w = 0; w < 8; ++w) a += s_acc[(w * kN + n) * 64 + c];
+    for (int w = 0; w < 8; ++w) a += s_acc[w][n][c];
     out[((int64_t)b * kN + n) * kHdD + dq * 64 + c] = Traits<T>::kBf16 ? (T)__float2bfloat16(a) : (T)a;
   }
   // ---- the new token takes its ring slot (its 64 columns of both rows) --------------------------
@@ -240,20 +235,12 @@ __global__ void bump_tokens_kernel(int* num_tokens, int B) {
 template <typename T, int kN>
 cudaError_t launch_decode_t(const void* q, const void* k_new, const void* v_new, void* keys,
                             void* values, int* num_tokens, int64_t B, int W, int update, void* out,
-                            float* logits, cudaStream_t s) {
-  const int splits = 8;
-  attn_decode_logits_kernel<T, kN><<<dim3((unsigned)B, splits), 256, 0, s>>>(
-      (const T*)q, (const T*)k_new, (const T*)keys, num_tokens, W, logits);
-  const size_t a = (size_t)kN * (W + 1), r = (size_t)8 * kN * 64;
-  const size_t smem = (a > r ? a : r) * sizeof(float);
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaFuncSetAttribute(attn_decode_values_kernel<T, kN>,
-                         cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    attr_set = true;
-  }
-  attn_decode_values_kernel<T, kN><<<dim3((unsigned)B, 4), 256, smem, s>>>(
-      logits, (const T*)k_new, (const T*)v_new, (T*)keys, (T*)values, num_tokens, W, update, (T*)out);
+                            float* logits, float2* stats, cudaStream_t s) {
+  attn_decode_logits_kernel<T, kN><<<dim3((unsigned)B, kSplits), 256, 0, s>>>(
+      (const T*)q, (const T*)k_new, (const T*)keys, num_tokens, W, logits, stats);
+  attn_decode_values_kernel<T, kN><<<dim3((unsigned)B, 4), 256, 0, s>>>(
+      logits, stats, (const T*)k_new, (const T*)v_new, (T*)keys, (T*)values, num_tokens, W, update,
+      (T*)out);
   if (update) bump_tokens_kernel<<<(unsigned)((B + 255) / 256), 256, 0, s>>>(num_tokens, (int)B);
   return cudaGetLastError();
 }
@@ -262,12 +249,15 @@ cudaError_t launch_decode_t(const void* q, const void* k_new, const void* v_new,
 
 bool attention_decode_supported(int hd, int N, int W) {
   const bool heads = N == 1 || N == 2 || N == 4 || N == 8 || N == 10 || N == 16;
-  // the probabilities of one sequence live in shared memory
-  return hd == kHdD && heads && W >= 1 && (size_t)N * (W + 1) * sizeof(float) <= 200 * 1024;
+  return hd == kHdD && heads && W >= 1;
 }
 
-size_t attention_decode_workspace_bytes(int64_t B, int N, int W) {
+// the logits [B, N, W + 1], then the per-CTA softmax statistics [B, kSplits, N]
+static size_t decode_logits_bytes(int64_t B, int N, int W) {
   return (((size_t)B * N * (W + 1) * sizeof(float)) + 255) & ~(size_t)255;
+}
+size_t attention_decode_workspace_bytes(int64_t B, int N, int W) {
+  return decode_logits_bytes(B, N, W) + ((((size_t)B * kSplits * N * sizeof(float2)) + 255) & ~(size_t)255);
 }
 
 cudaError_t launch_attention_decode(const void* q, const void* k_new, const void* v_new, void* keys,
@@ -275,12 +265,13 @@ cudaError_t launch_attention_decode(const void* q, const void* k_new, const void
                                     int dtype, int update, void* out, void* ws, cudaStream_t s) {
   if (B == 0) return cudaSuccess;
   float* lg = reinterpret_cast<float*>(ws);
+  float2* st = reinterpret_cast<float2*>(reinterpret_cast<uint8_t*>(ws) + decode_logits_bytes(B, N, W));
 #define RGK_DEC(NN)                                                                              \
   case NN:                                                                                       \
     return dtype == 1 ? launch_decode_t<__nv_bfloat16, NN>(q, k_new, v_new, keys, values,        \
-                                                           num_tokens, B, W, update, out, lg, s) \
+                                                           num_tokens, B, W, update, out, lg, st, s) \
                       : launch_decode_t<float, NN>(q, k_new, v_new, keys, values, num_tokens, B, \
-                                                   W, update, out, lg, s)
+                                                   W, update, out, lg, st, s)
   switch (N) {
     RGK_DEC(1); RGK_DEC(2); RGK_DEC(4); RGK_DEC(8); RGK_DEC(10); RGK_DEC(16);
     default: return cudaErrorInvalidValue;
