@@ -316,7 +316,7 @@ RGK_API int rgk_local_attention_prefill(const void* q, const void* k, const void
  *   (positions num_tokens - W .. num_tokens - 1) and the new key, float32 softmax, probabilities
  *   rounded, product with the values.  update != 0: afterwards k_new / v_new are stored in ring slot
  *   num_tokens % W and num_tokens grows by one, all in place (clone the cache first for the
- *   reference's functional form).  float32 or bfloat16, head_dim 256, N in {1,2,4,8,10,16};
+ *   reference's functional form).  float32 or bfloat16, head_dim 256, N in {1,2,4,8,10};
  *   RGK_ESHAPE otherwise.
  * workspace: rgk_attention_decode_workspace_bytes(B, N, W) bytes, 256-byte aligned.
  * ---------------------------------------------------------------------------------------------- */

@@ -793,7 +793,7 @@ int rgk_local_attention_decode(const void* q, const void* k_new, const void* v_n
                   aligned16(values) && aligned16(out), RGK_EALIGN,
               "pointers must be 16-byte aligned");
   RGK_REQUIRE(rgk::attention_decode_supported(head_dim, N, window), RGK_ESHAPE,
-              "the decode attention kernel covers head dimension 256 and 1/2/4/8/10/16 query heads "
+              "the decode attention kernel covers head dimension 256 and 1/2/4/8/10 query heads "
               "(head_dim %d, heads %d, window %d)",
               head_dim, N, window);
   if (B == 0) return RGK_OK;

@@ -494,7 +494,7 @@ class LocalAttentionBlock(nn.Module):
     else:
       assert t == 1, "with a cache the block takes one token at a time"
       lib = _lib.load()
-      if (hd == 256 and n in (1, 2, 4, 8, 10, 16)
+      if (hd == 256 and n in (1, 2, 4, 8, 10)
           and cache.keys.dtype == x.dtype and cache.num_tokens.dtype == torch.int32):
         # the library's decode kernels work on the ring in place; the reference's functional form
         # is the same step on a copy of the cache
