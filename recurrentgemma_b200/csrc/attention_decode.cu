@@ -10,10 +10,12 @@
 //                                per CTA;
 //   attn_decode_finish_kernel    sum of the partials, rounded; then the new key and value take
 //                                their ring slot and num_tokens grows.
-// All three are bandwidth work on the ring (2 W 256 elements per sequence) and run on the CUDA
-// cores.  A warp reads a 256-element row as one 16-byte pack per lane and has the loads of a whole
-// batch of rows in flight before it uses the first: with 16 CTAs per sequence that is several MB
-// in flight, which a ring walked row by row does not reach.
+// All three are bandwidth work on the ring (2 W 256 elements per sequence): 16 CTAs per sequence,
+// every warp with the loads of a whole batch of rows in flight before it uses the first.  The
+// float32 kernels do their arithmetic on the CUDA cores (a warp reads a 256-element row as one pack
+// per lane; ~200 instructions per row, which is what bounds them); the bfloat16 kernels use the
+// warp-level tensor-core instruction (m16n8k16), ~6 instructions per row - a tile is 16 ring rows
+// by 16 padded heads, far below the 128-row tiles of tcgen05.
 #include <math.h>
 
 #include "rgk_common.cuh"
@@ -234,23 +236,269 @@ attn_decode_values_kernel(const float* __restrict__ logits, const float2* __rest
   }
 }
 
-// grid (B), 256 threads = the 256 columns: out [B, kN, 256] = the rounded sum of the partials; then
-// (update != 0) the new key and value take ring slot num_tokens % W and num_tokens grows by one.
+// ------------------------------------------------------------------------------------------------
+// bfloat16: the same two kernels on the warp-level tensor-core instruction (m16n8k16), which cuts
+// the instruction count per ring row from ~200 to ~6 and leaves the kernels to the memory system.
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                          uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
+      "{%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Two running (maximum, sum of exponentials) pairs into one.
+__device__ __forceinline__ void merge_stats(float& m, float& l, float mo, float lo) {
+  const float m_new = fmaxf(m, mo);
+  l = l * __expf(m - m_new) + lo * __expf(mo - m_new);
+  m = m_new;
+}
+
+// Logits of a tile of 16 entries x 16 (padded) heads per warp.  In the fragments of the
+// instruction, lane (g = lane / 4, t = lane % 4) holds rows g and g + 8 of A and column g of B at
+// the contraction indices 2t, 2t+1, 2t+8, 2t+9.  The contraction runs over the 256 elements of a
+// row in any order, as long as A and B agree on it: a lane therefore takes the 8 consecutive
+// elements 32 i + 8 t .. + 7 of its rows with one 16-byte load and feeds them to two instructions
+// (elements 0-3, then 4-7), and does the same with its head's row of q.
+template <int kN>
+__global__ void __launch_bounds__(kWarps * 32)
+attn_decode_logits_mma_kernel(const __nv_bfloat16* __restrict__ q,
+                              const __nv_bfloat16* __restrict__ k_new,
+                              const __nv_bfloat16* __restrict__ keys,
+                              const int* __restrict__ num_tokens, int W,
+                              float* __restrict__ logits, float2* __restrict__ stats) {
+  constexpr int kTiles = kN > 8 ? 2 : 1;           // groups of 8 heads
+  __shared__ float2 s_part[kWarps][kHeadPad];
+  const int b = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int nt = num_tokens[b];
+  const int n_vis = visible_slots(nt, W);
+  const int total = n_vis + 1;
+  const int chunk = chunk_of(total);
+  const int e_begin = blockIdx.y * chunk, e_end = min(e_begin + chunk, total);
+  uint4 qb[kTiles][8];
+#pragma unroll
+  for (int h = 0; h < kTiles; ++h) {
+    const int head = h * 8 + g;
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      qb[h][i] = head < kN ? *reinterpret_cast<const uint4*>(q + ((int64_t)b * kN + head) * kHdD + i * 32 + t * 8)
+                           : make_uint4(0u, 0u, 0u, 0u);
+  }
+  float* lg = logits + (int64_t)b * (W + 1) * kHeadPad;
+  float m_run[kTiles][2], l_run[kTiles][2];        // heads 8 h + 2 t and + 1, over this lane's rows
+#pragma unroll
+  for (int h = 0; h < kTiles; ++h) {
+    m_run[h][0] = m_run[h][1] = kMasked;
+    l_run[h][0] = l_run[h][1] = 0.0f;
+  }
+  for (int e0 = e_begin + 16 * warp; e0 < e_end; e0 += 16 * kWarps) {
+    const int r0 = e0 + g, r1 = e0 + g + 8;
+    // rows past the end of the CTA's range are loaded as its last row and ignored
+    const int c0 = min(r0, e_end - 1), c1 = min(r1, e_end - 1);
+    const __nv_bfloat16* p0 = (c0 == n_vis ? k_new + (int64_t)b * kHdD : keys + ((int64_t)b * W + c0) * kHdD) + t * 8;
+    const __nv_bfloat16* p1 = (c1 == n_vis ? k_new + (int64_t)b * kHdD : keys + ((int64_t)b * W + c1) * kHdD) + t * 8;
+    uint4 ra[8], rb[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      ra[i] = ld_stream(p0 + i * 32);
+      rb[i] = ld_stream(p1 + i * 32);
+    }
+    float acc[kTiles][4];
+#pragma unroll
+    for (int h = 0; h < kTiles; ++h) acc[h][0] = acc[h][1] = acc[h][2] = acc[h][3] = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+#pragma unroll
+      for (int h = 0; h < kTiles; ++h) {
+        mma_16816(acc[h], ra[i].x, rb[i].x, ra[i].y, rb[i].y, qb[h][i].x, qb[h][i].y);
+        mma_16816(acc[h], ra[i].z, rb[i].z, ra[i].w, rb[i].w, qb[h][i].z, qb[h][i].w);
+      }
+    }
+    // two tensor operations in the reference: the contraction, then the scaling by 256^-1/2
+#pragma unroll
+    for (int h = 0; h < kTiles; ++h) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[h][j] = round_bf16(round_bf16(acc[h][j]) * 0.0625f);
+      if (r0 < e_end) {
+        *reinterpret_cast<float2*>(lg + (int64_t)r0 * kHeadPad + h * 8 + t * 2) = make_float2(acc[h][0], acc[h][1]);
+        merge_stats(m_run[h][0], l_run[h][0], acc[h][0], 1.0f);
+        merge_stats(m_run[h][1], l_run[h][1], acc[h][1], 1.0f);
+      }
+      if (r1 < e_end) {
+        *reinterpret_cast<float2*>(lg + (int64_t)r1 * kHeadPad + h * 8 + t * 2) = make_float2(acc[h][2], acc[h][3]);
+        merge_stats(m_run[h][0], l_run[h][0], acc[h][2], 1.0f);
+        merge_stats(m_run[h][1], l_run[h][1], acc[h][3], 1.0f);
+      }
+    }
+  }
+  // the 8 lanes that share t, then the warps
+#pragma unroll
+  for (int h = 0; h < kTiles; ++h)
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+#pragma unroll
+      for (int o = 4; o < 32; o <<= 1) {
+        const float mo = __shfl_xor_sync(0xffffffffu, m_run[h][j], o);
+        const float lo = __shfl_xor_sync(0xffffffffu, l_run[h][j], o);
+        merge_stats(m_run[h][j], l_run[h][j], mo, lo);
+      }
+      if (g == 0) s_part[warp][h * 8 + t * 2 + j] = make_float2(m_run[h][j], l_run[h][j]);
+    }
+  __syncthreads();
+  if (threadIdx.x < kN) {
+    float m = kMasked, l = 0.0f;
+    for (int w = 0; w < kWarps; ++w) {
+      const float2 p = s_part[w][threadIdx.x];
+      merge_stats(m, l, p.x, p.y);
+    }
+    stats[((int64_t)b * kSplits + blockIdx.y) * kN + threadIdx.x] = make_float2(m, l);
+  }
+}
+
+// Probabilities x values on the same instruction.  All warps of a CTA walk the CTA's entries, 16
+// at a time, each for its own 32 of the 256 columns, so no sums cross warps: A = the rounded
+// probabilities [16 padded heads x 16 entries], formed in registers from the logits (every warp
+// repeats that small step), B = 16 entries x 32 columns of the values, which have to be read
+// across rows (two entries of one column per register): the warp copies the piece into shared
+// memory with 16-byte loads and takes the fragments back with ldmatrix.trans.  Rows of the piece
+// are padded to 80 bytes so that the 8 row addresses of a matrix fall into different banks.
+constexpr int kPieceRow = 64 + 16;
+constexpr int kPiece = 16 * kPieceRow;                           // 1280 bytes per warp
+constexpr int kAhead = 5;                                        // tiles whose loads are in flight
+
+template <int kN>
+__global__ void __launch_bounds__(kWarps * 32)
+attn_decode_values_mma_kernel(const float* __restrict__ logits, const float2* __restrict__ stats,
+                              const __nv_bfloat16* __restrict__ v_new,
+                              const __nv_bfloat16* __restrict__ values,
+                              const int* __restrict__ num_tokens, int W,
+                              float* __restrict__ partial) {
+  constexpr int kTiles = kN > 8 ? 2 : 1;           // groups of 8 heads (rows g and g + 8 of A)
+  __shared__ __align__(16) uint8_t s_piece[kWarps][kPiece];
+  __shared__ float s_stat[2][kHeadPad];
+  const int b = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int nt = num_tokens[b];
+  const int n_vis = visible_slots(nt, W);
+  const int total = n_vis + 1;
+  const int chunk = chunk_of(total);
+  const int e_begin = blockIdx.y * chunk, e_end = min(e_begin + chunk, total);
+  const float* lg = logits + (int64_t)b * (W + 1) * kHeadPad;
+  {
+    // thread (head, CTA of the logits kernel) takes one pair of statistics; the 16 lanes of a head
+    // merge theirs in four steps
+    static_assert(kSplits == 16 && kWarps * 32 == kHeadPad * kSplits, "one thread per pair");
+    const int head = threadIdx.x >> 4, c = threadIdx.x & 15;
+    float m = kMasked, l = 0.0f;
+    if (head < kN) {
+      const float2 p = stats[((int64_t)b * kSplits + c) * kN + head];
+      m = p.x;
+      l = p.y;
+    }
+#pragma unroll
+    for (int o = 1; o < 16; o <<= 1) {
+      const float mo = __shfl_xor_sync(0xffffffffu, m, o), lo = __shfl_xor_sync(0xffffffffu, l, o);
+      merge_stats(m, l, mo, lo);
+    }
+    if (c == 0) {
+      s_stat[0][head] = m;
+      s_stat[1][head] = l > 0.0f ? 1.0f / l : 0.0f;
+    }
+  }
+  __syncthreads();
+  // this lane's two heads (rows g and g + 8 of A)
+  const float m0 = s_stat[0][g], i0 = s_stat[1][g], m1 = s_stat[0][g + 8], i1 = s_stat[1][g + 8];
+  uint8_t* piece = s_piece[warp];
+  const uint32_t piece_u32 = static_cast<uint32_t>(__cvta_generic_to_shared(piece));
+  // ldmatrix.x4.trans: lane L gives the address of row L % 8 of matrix L / 8; matrices 0 and 1 are
+  // entries 0-7 and 8-15 of one group of 8 columns, matrices 2 and 3 the same of the next group
+  const uint32_t ld_base = piece_u32 + (((lane >> 3) & 1) * 8 + (lane & 7)) * kPieceRow + (lane >> 4) * 16;
+  // a lane copies 16 bytes of rows lane / 4 and lane / 4 + 8 of a tile: columns 32 warp + 8 t .. + 7
+  const int col = warp * 32 + t * 8;
+  auto row_ptr = [&](int e) {
+    return (e == n_vis ? v_new + (int64_t)b * kHdD : values + ((int64_t)b * W + e) * kHdD) + col;
+  };
+  // the logit of entry e and head `head`, or "none"
+  auto logit = [&](int e, int head) {
+    return (e < e_end && head < kN) ? lg[(int64_t)e * kHeadPad + head] : kMasked;
+  };
+  auto prob = [&](float v, float m, float inv) {
+    return v > kMasked ? round_bf16(__expf(v - m) * inv) : 0.0f;
+  };
+  float acc[4][4];                                 // four groups of 8 columns
+#pragma unroll
+  for (int n = 0; n < 4; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.0f;
+  for (int e0 = e_begin; e0 < e_end; e0 += 16 * kAhead) {
+    uint4 lo[kAhead], hi[kAhead];                  // rows past the end as zeros
+    float lv[kAhead][kTiles][4];                   // this lane's logits: entries 2t, 2t+1, 2t+8, 2t+9
+#pragma unroll
+    for (int u = 0; u < kAhead; ++u) {
+      const int ea = e0 + 16 * u + g, eb = ea + 8;
+      lo[u] = ea < e_end ? ld_stream(row_ptr(ea)) : make_uint4(0u, 0u, 0u, 0u);
+      hi[u] = eb < e_end ? ld_stream(row_ptr(eb)) : make_uint4(0u, 0u, 0u, 0u);
+      const int pa = e0 + 16 * u + 2 * t;
+#pragma unroll
+      for (int h = 0; h < kTiles; ++h) {
+        lv[u][h][0] = logit(pa, g + 8 * h);
+        lv[u][h][1] = logit(pa + 1, g + 8 * h);
+        lv[u][h][2] = logit(pa + 8, g + 8 * h);
+        lv[u][h][3] = logit(pa + 9, g + 8 * h);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kAhead; ++u) {
+      const int et = e0 + 16 * u;
+      if (et < e_end) {                            // (the same for every lane of the warp)
+        // the probabilities of this lane's heads at its four pairs of entries
+        const uint32_t a0 = pack_bf16x2(prob(lv[u][0][0], m0, i0), prob(lv[u][0][1], m0, i0));
+        const uint32_t a2 = pack_bf16x2(prob(lv[u][0][2], m0, i0), prob(lv[u][0][3], m0, i0));
+        uint32_t a1 = 0u, a3 = 0u;
+        if (kTiles == 2) {
+          a1 = pack_bf16x2(prob(lv[u][kTiles - 1][0], m1, i1), prob(lv[u][kTiles - 1][1], m1, i1));
+          a3 = pack_bf16x2(prob(lv[u][kTiles - 1][2], m1, i1), prob(lv[u][kTiles - 1][3], m1, i1));
+        }
+        __syncwarp();                              // the previous tile's fragments have been read
+        *reinterpret_cast<uint4*>(piece + g * kPieceRow + t * 16) = lo[u];
+        *reinterpret_cast<uint4*>(piece + (g + 8) * kPieceRow + t * 16) = hi[u];
+        __syncwarp();
+#pragma unroll
+        for (int n2 = 0; n2 < 2; ++n2) {           // two groups of 8 columns per ldmatrix
+          uint32_t b0, b1, b2, b3;
+          asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(ld_base + n2 * 32));
+          mma_16816(acc[2 * n2], a0, a1, a2, a3, b0, b1);
+          mma_16816(acc[2 * n2 + 1], a0, a1, a2, a3, b2, b3);
+        }
+      }
+    }
+  }
+  // C fragment: (head g, columns 8 n + 2 t, + 1) and (head g + 8, the same columns)
+  float* dst = partial + (((int64_t)b * kSplits + blockIdx.y) * kN) * kHdD + warp * 32 + t * 2;
+#pragma unroll
+  for (int n = 0; n < 4; ++n) {
+    if (g < kN) *reinterpret_cast<float2*>(dst + g * kHdD + n * 8) = make_float2(acc[n][0], acc[n][1]);
+    if (g + 8 < kN) *reinterpret_cast<float2*>(dst + (g + 8) * kHdD + n * 8) = make_float2(acc[n][2], acc[n][3]);
+  }
+}
+
+// grid (B, kN), 256 threads = the 256 columns: out [B, kN, 256] = the rounded sum of the partials;
+// then (update != 0; the CTAs of head 0) the new key and value take ring slot num_tokens % W and
+// num_tokens grows by one.
 template <typename T, int kN>
 __global__ void __launch_bounds__(kHdD)
 attn_decode_finish_kernel(const float* __restrict__ partial, const T* __restrict__ k_new,
                           const T* __restrict__ v_new, T* __restrict__ keys, T* __restrict__ values,
                           int* __restrict__ num_tokens, int W, int update, T* __restrict__ out) {
-  const int b = blockIdx.x, c = threadIdx.x;
-  const int nt = num_tokens[b];
+  const int b = blockIdx.x, n = blockIdx.y, c = threadIdx.x;
+  float a = 0.0f;
 #pragma unroll
-  for (int n = 0; n < kN; ++n) {
-    float a = 0.0f;
-#pragma unroll
-    for (int s = 0; s < kSplits; ++s) a += partial[(((int64_t)b * kSplits + s) * kN + n) * kHdD + c];
-    out[((int64_t)b * kN + n) * kHdD + c] = static_cast<T>(a);
-  }
-  if (update) {
+  for (int s = 0; s < kSplits; ++s) a += partial[(((int64_t)b * kSplits + s) * kN + n) * kHdD + c];
+  out[((int64_t)b * kN + n) * kHdD + c] = static_cast<T>(a);
+  if (update && n == 0) {
+    const int nt = num_tokens[b];
     const int slot = nt % W;
     keys[((int64_t)b * W + slot) * kHdD + c] = k_new[(int64_t)b * kHdD + c];
     values[((int64_t)b * W + slot) * kHdD + c] = v_new[(int64_t)b * kHdD + c];
@@ -279,11 +527,19 @@ cudaError_t launch_decode_t(const void* q, const void* k_new, const void* v_new,
   float* lg = reinterpret_cast<float*>(base);
   float2* st = reinterpret_cast<float2*>(base + logits_bytes(B, W));
   float* part = reinterpret_cast<float*>(base + logits_bytes(B, W) + stats_bytes(B, kN));
-  attn_decode_logits_kernel<T, kN><<<dim3((unsigned)B, kSplits), kWarps * 32, 0, s>>>(
-      (const T*)q, (const T*)k_new, (const T*)keys, num_tokens, W, lg, st);
-  attn_decode_values_kernel<T, kN><<<dim3((unsigned)B, kSplits), kWarps * 32, 0, s>>>(
-      lg, st, (const T*)v_new, (const T*)values, num_tokens, W, part);
-  attn_decode_finish_kernel<T, kN><<<(unsigned)B, kHdD, 0, s>>>(
+  const dim3 grid((unsigned)B, kSplits);
+  if constexpr (Traits<T>::kBf16) {
+    attn_decode_logits_mma_kernel<kN><<<grid, kWarps * 32, 0, s>>>(
+        (const T*)q, (const T*)k_new, (const T*)keys, num_tokens, W, lg, st);
+    attn_decode_values_mma_kernel<kN><<<grid, kWarps * 32, 0, s>>>(
+        lg, st, (const T*)v_new, (const T*)values, num_tokens, W, part);
+  } else {
+    attn_decode_logits_kernel<T, kN><<<grid, kWarps * 32, 0, s>>>(
+        (const T*)q, (const T*)k_new, (const T*)keys, num_tokens, W, lg, st);
+    attn_decode_values_kernel<T, kN><<<grid, kWarps * 32, 0, s>>>(
+        lg, st, (const T*)v_new, (const T*)values, num_tokens, W, part);
+  }
+  attn_decode_finish_kernel<T, kN><<<dim3((unsigned)B, kN), kHdD, 0, s>>>(
       part, (const T*)k_new, (const T*)v_new, (T*)keys, (T*)values, num_tokens, W, update, (T*)out);
   return cudaGetLastError();
 }
