@@ -726,7 +726,8 @@ def test_greedy_sampler(rg, dtype):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("heads,window,prompt", [(10, 40, 7), (10, 40, 40), (4, 24, 61), (1, 8, 1)])
+@pytest.mark.parametrize("heads,window,prompt", [(10, 40, 7), (10, 40, 40), (4, 24, 61), (1, 8, 1),
+                                                 (8, 300, 310), (10, 2048, 150)])
 def test_attention_decode_kernels_vs_oracle(rg, oracle, dtype, heads, window, prompt):
   """The decode-step kernels on the ring cache (head dimension 256) against the oracle: a ring that
   is not yet full, one that is exactly full, one that has wrapped; six steps each, in the
