@@ -245,6 +245,10 @@ RGK_API int rgk_recurrent_block_prefill(const void* x, const void* segment_pos, 
  * ---------------------------------------------------------------------------------------------- */
 RGK_API int rgk_rmsnorm(const void* x, const void* scale, int64_t M, int64_t D, float eps, int dtype,
                         void* out, void* stream);
+/* The same with the residual add in front (recurrentgemma/torch/modules.py:902-904):
+ * sum_out [M,D] = a + b (one rounding), out [M,D] = RMSNorm(sum_out). */
+RGK_API int rgk_add_rmsnorm(const void* a, const void* b, const void* scale, int64_t M, int64_t D,
+                            float eps, int dtype, void* sum_out, void* out, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
  * The temporal half of ResidualBlock.forward for a recurrent block

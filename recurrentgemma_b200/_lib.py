@@ -83,6 +83,7 @@ SIGNATURES = {
     "rgk_embed": (_int, [_vp, _int, _vp, _i64, _i64, _i64, ctypes.c_float, _int, _vp, _vp]),
     "rgk_logits": (_int, [_vp, _vp, _i64, _i64, _i64, ctypes.c_float, _int, _vp, _vp, _vp]),
     "rgk_argmax": (_int, [_vp, _i64, _i64, _int, _vp, _vp]),
+    "rgk_add_rmsnorm": (_int, [_vp, _vp, _vp, _i64, _i64, ctypes.c_float, _int, _vp, _vp, _vp]),
     "rgk_geglu_bias": (_int, [_vp, _vp, _i64, _i64, _int, _vp, _vp]),
     "rgk_workspace_bytes": (_sz, [_i64, _i64, _i64, _int]),
     "rgk_workspace_status": (_int, [_vp, _vp]),

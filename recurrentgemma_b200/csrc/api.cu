@@ -589,6 +589,24 @@ int rgk_rmsnorm(const void* x, const void* scale, int64_t M, int64_t D, float ep
   return RGK_OK;
 }
 
+int rgk_add_rmsnorm(const void* a, const void* b, const void* scale, int64_t M, int64_t D, float eps,
+                    int dtype, void* sum_out, void* out, void* stream) {
+  RGK_REQUIRE(dtype == RGK_F32 || dtype == RGK_BF16, RGK_EINVAL, "unknown dtype %d", dtype);
+  RGK_REQUIRE(M >= 0 && D >= 1, RGK_EINVAL, "bad size (M=%lld D=%lld)", (long long)M, (long long)D);
+  RGK_REQUIRE(a && b && scale && sum_out && out, RGK_EINVAL, "NULL pointer argument");
+  RGK_REQUIRE(aligned16(a) && aligned16(b) && aligned16(scale) && aligned16(sum_out) && aligned16(out),
+              RGK_EALIGN, "pointers must be 16-byte aligned");
+  RGK_REQUIRE(rgk::rmsnorm_supported(dtype, D), RGK_ESHAPE,
+              "RMSNorm covers widths that are multiples of a 16-byte pack, up to 1024 packs "
+              "(dtype %d, D=%lld)", dtype, (long long)D);
+  if (M == 0) return RGK_OK;
+  RGK_CHECK_DEVICE();
+  RGK_CUDA(rgk::launch_rmsnorm(a, scale, M, D, eps, dtype, out, static_cast<cudaStream_t>(stream), b,
+                               sum_out),
+           "add + rmsnorm launch");
+  return RGK_OK;
+}
+
 size_t rgk_residual_workspace_bytes(int64_t B, int64_t T, int64_t D, int64_t E, int dtype) {
   const size_t block = rgk_block_workspace_bytes(B, T, D, E, dtype);
   if (block == 0) return 0;

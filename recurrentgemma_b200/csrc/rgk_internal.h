@@ -109,7 +109,8 @@ cudaError_t launch_attention_prefill(const void* q, const void* k, const void* v
 // (torch/layers.py:65-73); one warp per row held in registers.
 bool rmsnorm_supported(int dtype, int64_t D);
 cudaError_t launch_rmsnorm(const void* x, const void* scale, int64_t M, int64_t D, float eps,
-                           int dtype, void* out, cudaStream_t s);
+                           int dtype, void* out, cudaStream_t s, const void* addend = nullptr,
+                           void* sum_out = nullptr);
 
 // scan.cu
 size_t scan_workspace_bytes(int64_t B, int64_t T, int64_t E, int dtype);

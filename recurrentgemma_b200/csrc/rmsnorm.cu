@@ -4,7 +4,9 @@
 // HBM-bound: one warp owns a row, reads it once into registers (16-byte packs, lane-strided),
 // reduces the sum of squares with shuffles and writes the row once.  In bfloat16 every tensor
 // operation of the reference rounds: the squares, the mean, var + eps, the reciprocal square root,
-// both products and scale + 1.
+// both products and scale + 1.  With an addend the kernel first forms x + addend (one rounding),
+// writes that sum as well and normalises it: the residual add in front of a block's second norm
+// (torch/modules.py:902-904) without a pass of its own.
 #include "rgk_common.cuh"
 #include "rgk_internal.h"
 
@@ -27,8 +29,8 @@ __device__ __forceinline__ uint32_t bf2add(uint32_t a, uint32_t b) {
 
 template <typename T, int kPacks>   // kPacks: packs per lane this instantiation can hold
 __global__ void __launch_bounds__(kNormWarps * 32)
-rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ scale, int64_t M, int D, float eps,
-               T* __restrict__ out) {
+rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ addend, const T* __restrict__ scale,
+               int64_t M, int D, float eps, T* __restrict__ sum_out, T* __restrict__ out) {
   constexpr int kPack = Traits<T>::kPack;
   constexpr bool kBf16 = Traits<T>::kBf16;
   const int lane = threadIdx.x & 31;
@@ -41,6 +43,18 @@ rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ scale, int64_t M, 
   for (int i = 0; i < kPacks; ++i) {
     const int pk = lane + 32 * i;
     v[i] = pk < packs ? ld_stream(xr + (int64_t)pk * kPack) : make_uint4(0u, 0u, 0u, 0u);
+    if (addend != nullptr && pk < packs) {
+      const uint4 w = ld_stream(addend + row * D + (int64_t)pk * kPack);
+      if constexpr (kBf16) {
+        v[i] = make_uint4(bf2add(v[i].x, w.x), bf2add(v[i].y, w.y), bf2add(v[i].z, w.z), bf2add(v[i].w, w.w));
+      } else {
+        v[i].x = __float_as_uint(__fadd_rn(__uint_as_float(v[i].x), __uint_as_float(w.x)));
+        v[i].y = __float_as_uint(__fadd_rn(__uint_as_float(v[i].y), __uint_as_float(w.y)));
+        v[i].z = __float_as_uint(__fadd_rn(__uint_as_float(v[i].z), __uint_as_float(w.z)));
+        v[i].w = __float_as_uint(__fadd_rn(__uint_as_float(v[i].w), __uint_as_float(w.w)));
+      }
+      st_stream(sum_out + row * D + (int64_t)pk * kPack, v[i]);
+    }
   }
   float sum = 0.0f;
 #pragma unroll
@@ -96,13 +110,14 @@ rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ scale, int64_t M, 
 }
 
 template <typename T>
-cudaError_t launch_typed(const void* x, const void* scale, int64_t M, int64_t D, float eps,
-                         void* out, cudaStream_t s) {
+cudaError_t launch_typed(const void* x, const void* addend, const void* scale, int64_t M, int64_t D,
+                         float eps, void* sum_out, void* out, cudaStream_t s) {
   const int packs_per_lane = (int)((D / Traits<T>::kPack + 31) / 32);
   const unsigned grid = (unsigned)((M + kNormWarps - 1) / kNormWarps);
   const dim3 block(kNormWarps * 32);
 #define RGK_NORM(P)                                                                           \
-  rmsnorm_kernel<T, P><<<grid, block, 0, s>>>((const T*)x, (const T*)scale, M, (int)D, eps, (T*)out)
+  rmsnorm_kernel<T, P><<<grid, block, 0, s>>>((const T*)x, (const T*)addend, (const T*)scale, M, (int)D, \
+                                              eps, (T*)sum_out, (T*)out)
   if (packs_per_lane <= 4) RGK_NORM(4);
   else if (packs_per_lane <= 10) RGK_NORM(10);
   else if (packs_per_lane <= 16) RGK_NORM(16);
@@ -119,10 +134,10 @@ bool rmsnorm_supported(int dtype, int64_t D) {
 }
 
 cudaError_t launch_rmsnorm(const void* x, const void* scale, int64_t M, int64_t D, float eps,
-                           int dtype, void* out, cudaStream_t s) {
+                           int dtype, void* out, cudaStream_t s, const void* addend, void* sum_out) {
   if (M == 0) return cudaSuccess;
-  return dtype ? launch_typed<__nv_bfloat16>(x, scale, M, D, eps, out, s)
-               : launch_typed<float>(x, scale, M, D, eps, out, s);
+  return dtype ? launch_typed<__nv_bfloat16>(x, addend, scale, M, D, eps, sum_out, out, s)
+               : launch_typed<float>(x, addend, scale, M, D, eps, sum_out, out, s);
 }
 
 }  // namespace rgk

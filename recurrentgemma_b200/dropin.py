@@ -21,7 +21,6 @@ from __future__ import annotations
 
 import types
 
-import torch
 from torch import nn
 
 from recurrentgemma_b200 import layers as b200_layers

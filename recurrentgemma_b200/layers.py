@@ -81,6 +81,22 @@ class RMSNorm(nn.Module):
           _lib.dtype_code(x.dtype), out.data_ptr(), _lib.stream_ptr(dev)))
     return out
 
+  @torch.no_grad()
+  def add_norm(self, a: torch.Tensor, b: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(a + b, forward(a + b)) in one kernel: the residual add in front of a block's second norm
+    (recurrentgemma/torch/modules.py:902-904)."""
+    dev = _lib.require_cuda(a, b, self.scale)
+    _same_dtype(a, b, self.scale)
+    assert a.shape == b.shape and a.shape[-1] == self.width
+    ac, bc = a.contiguous(), b.contiguous()
+    total, out = torch.empty_like(ac), torch.empty_like(ac)
+    with torch.cuda.device(dev):
+      _lib.check(_lib.load().rgk_add_rmsnorm(
+          ac.data_ptr(), bc.data_ptr(), self.scale.data_ptr(), ac.numel() // self.width, self.width,
+          float(self.eps), _lib.dtype_code(a.dtype), total.data_ptr(), out.data_ptr(),
+          _lib.stream_ptr(dev)))
+    return total, out
+
 
 class Einsum(nn.Module):
   """Einsum with a bias (recurrentgemma/torch/layers.py:653-703): same constructor and parameter

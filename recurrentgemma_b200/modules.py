@@ -359,14 +359,16 @@ def residual_block(
   r = temporal_block(temporal_pre_norm(x)) + x;  out = mlp_block(channel_pre_norm(r)) + r.
   Returns (out, updated cache of the temporal block or None).  `inplace`: a decode step overwrites
   the tensors of `cache` instead of returning new ones."""
-  if isinstance(temporal_block, RecurrentBlock):
+  if (isinstance(temporal_block, RecurrentBlock) and temporal_block._fusable(x, cache)
+      and temporal_pre_norm.width == temporal_block.width):
+    # bfloat16 prefill of the recurrent kind: each half is one library call
     r, new_cache = recurrent_residual(x, segment_pos, temporal_pre_norm, temporal_block, cache,
                                       return_cache, inplace)
-  else:
-    y, new_cache = temporal_block(temporal_pre_norm(x), segment_pos, cache, return_cache,
-                                  inplace=inplace)
-    r = y + x
-  return mlp_block(r, pre_norm=channel_pre_norm), new_cache
+    return mlp_block(r, pre_norm=channel_pre_norm), new_cache
+  y, new_cache = temporal_block(temporal_pre_norm(x), segment_pos, cache, return_cache,
+                                inplace=inplace)
+  r, normed = channel_pre_norm.add_norm(y, x)        # the residual add rides in the norm kernel
+  return mlp_block(normed, residual=r), new_cache
 
 
 class AttentionBlockCache(NamedTuple):

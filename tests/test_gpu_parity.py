@@ -784,3 +784,22 @@ def test_greedy_sampler_mlp_few_rows(rg, oracle, dtype):
   norm.load_state_dict({"scale": scale})
   assert_close(m(x.to(DEV), pre_norm=norm), oracle.residual_channel(x, scale, *args), TOL[dt],
                "channel half")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("rows,width", [(64, 2560), (5, 128), (130, 512)])
+def test_add_rmsnorm_vs_oracle(rg, oracle, dtype, rows, width):
+  """The residual add fused into the norm kernel: the sum is the rounded a + b, the normalised
+  output equals the norm kernel (and the oracle) on that sum."""
+  dt = {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype]
+  a = C.normal(f"addnorm_{rows}_{width}", "a", (rows, width), 1.0, dt)
+  b = C.normal(f"addnorm_{rows}_{width}", "b", (rows, width), 2.0, dt)
+  scale = C.normal(f"addnorm_{rows}_{width}", "scale", (width,), 0.3, dt)
+  norm = rg.RMSNorm(width, device=DEV, dtype=dt)
+  norm.load_state_dict({"scale": scale})
+  total, normed = norm.add_norm(a.to(DEV), b.to(DEV))
+  ref_total = (a.float() + b.float()).to(dt)
+  assert torch.equal(total.cpu(), ref_total)
+  assert torch.equal(normed, norm(total))
+  assert_close(normed, oracle.rmsnorm(ref_total, scale), TOL[dt], "normalised sum")
