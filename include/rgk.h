@@ -56,8 +56,15 @@ enum {
                             multiple of 16; float32 or bfloat16) */
   RGK_GATES_TCGEN05 = 2, /* tensor-core gate kernel, then the scan kernel (bfloat16, head width
                             256); RGK_ESHAPE if the shape is not covered */
-  RGK_GATES_FUSED = 3    /* gates, gate arithmetic and scan in one tensor-core kernel (bfloat16,
-                            head width 256, any T); RGK_ESHAPE otherwise */
+  RGK_GATES_FUSED = 3,   /* gates, gate arithmetic and scan in one tensor-core kernel (bfloat16,
+                            head width 256, any T); RGK_ESHAPE otherwise.  The input gate and the
+                            gelu of the join are evaluated with packed bfloat16 tanh approximations:
+                            within the path's tolerance of the reference (2e-2 of the largest
+                            output), a third to a half of the outputs differ by one bfloat16 step */
+  RGK_GATES_FUSED_EXACT = 4 /* the same kernel with every rounding of the reference (sigmoids and
+                            gelu in float32 before their rounding): outputs agree with the
+                            reference's bfloat16 arithmetic on all but a fraction of a percent of
+                            the elements; about 10 % slower */
 };
 
 RGK_API int rgk_abi_version(void);

@@ -17,7 +17,7 @@ LIB_PATH = os.path.join(_HERE, "librgk.so")
 
 RGK_F32, RGK_BF16 = 0, 1
 RGK_I32, RGK_I64 = 0, 1
-GATES_AUTO, GATES_SIMT, GATES_TCGEN05, GATES_FUSED = 0, 1, 2, 3
+GATES_AUTO, GATES_SIMT, GATES_TCGEN05, GATES_FUSED, GATES_FUSED_EXACT = 0, 1, 2, 3, 4
 
 _vp, _i64, _int, _sz = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_size_t
 

@@ -127,10 +127,12 @@ int run_rglru(const void* c, const void* pos, int pos64, const rgk_params* p, co
               float* h_last, cudaStream_t s) {
   const int bw = (int)(E / H);
   const bool fused_ok = rgk::rglru_chan_supported(dtype, bw, B, T);
-  if (gates_impl == RGK_GATES_FUSED && !fused_ok)
+  const bool want_fused = gates_impl >= RGK_GATES_FUSED;
+  if (want_fused && !fused_ok)
     return fail(RGK_ESHAPE, "the fused RG-LRU kernel covers bfloat16 and head width 256 "
                             "(dtype %d, head width %d, T %lld)", dtype, bw, (long long)T);
-  if (fused_ok && (gates_impl == RGK_GATES_AUTO || gates_impl == RGK_GATES_FUSED)) {
+  if (fused_ok && (gates_impl == RGK_GATES_AUTO || want_fused)) {
+    const int math = gates_impl == RGK_GATES_FUSED_EXACT ? rgk::kMathExact : rgk::kMathFast;
     const void* packed = p->gates_packed;
     if (packed == nullptr) {
       cudaError_t e = rgk::launch_pack_gate_weights(p->gate_x_w, p->gate_a_w, H, wpack, s);
@@ -139,12 +141,12 @@ int run_rglru(const void* c, const void* pos, int pos64, const rgk_params* p, co
     }
     cudaError_t e = rgk::launch_rglru_chan(c, pos, pos64, p->a_param, p->gate_x_b, p->gate_a_b,
                                            packed, h0, yb, y_activated, B, T, H, out, h_last,
-                                           scan_ws, s);
+                                           scan_ws, math, s);
     if (e != cudaSuccess) return cuda_fail(e, "fused RG-LRU launch");
     return RGK_OK;
   }
   int rc = run_gates(c, pos, pos64, p, B * T, H, bw, dtype,
-                     gates_impl == RGK_GATES_FUSED ? RGK_GATES_AUTO : gates_impl, wpack, a_buf,
+                     want_fused ? RGK_GATES_AUTO : gates_impl, wpack, a_buf,
                      xn_buf, scan_ws, s);
   if (rc) return rc;
   cudaError_t e = rgk::launch_scan(xn_buf, a_buf, nullptr, nullptr, 0, h0, yb, y_activated, B, T, E,
@@ -338,7 +340,7 @@ int rgk_rglru_forward(const void* x, const void* segment_pos, int pos_dtype, con
   if ((rc = check_heads(E, H))) return rc;
   if ((rc = check_params(p, false))) return rc;
   RGK_REQUIRE(pos_dtype == RGK_I32 || pos_dtype == RGK_I64, RGK_EINVAL, "unknown index dtype");
-  RGK_REQUIRE(gates_impl >= RGK_GATES_AUTO && gates_impl <= RGK_GATES_FUSED, RGK_EINVAL,
+  RGK_REQUIRE(gates_impl >= RGK_GATES_AUTO && gates_impl <= RGK_GATES_FUSED_EXACT, RGK_EINVAL,
               "unknown gates_impl %d", gates_impl);
   RGK_REQUIRE(x && segment_pos && y, RGK_EINVAL, "NULL pointer argument");
   RGK_REQUIRE(aligned16(x) && aligned16(y) && aligned16(h0) && aligned16(h_last), RGK_EALIGN,
@@ -369,7 +371,7 @@ int rgk_recurrent_path_prefill(const void* xb, const void* yb, const void* segme
   if ((rc = check_params(p, true))) return rc;
   RGK_REQUIRE(W == 4, RGK_ESHAPE, "temporal width %d is not supported (only 4)", W);
   RGK_REQUIRE(pos_dtype == RGK_I32 || pos_dtype == RGK_I64, RGK_EINVAL, "unknown index dtype");
-  RGK_REQUIRE(gates_impl >= RGK_GATES_AUTO && gates_impl <= RGK_GATES_FUSED, RGK_EINVAL,
+  RGK_REQUIRE(gates_impl >= RGK_GATES_AUTO && gates_impl <= RGK_GATES_FUSED_EXACT, RGK_EINVAL,
               "unknown gates_impl %d", gates_impl);
   RGK_REQUIRE(xb && segment_pos && out, RGK_EINVAL, "NULL pointer argument");
   RGK_REQUIRE(aligned16(xb) && aligned16(yb) && aligned16(out) && aligned16(h0) &&
@@ -840,7 +842,7 @@ int rgk_recurrent_path_decode(const void* xb, const void* yb, const void* segmen
   if ((rc = check_params(p, true))) return rc;
   RGK_REQUIRE(W == 4, RGK_ESHAPE, "temporal width %d is not supported (only 4)", W);
   RGK_REQUIRE(pos_dtype == RGK_I32 || pos_dtype == RGK_I64, RGK_EINVAL, "unknown index dtype");
-  RGK_REQUIRE(gates_impl >= RGK_GATES_AUTO && gates_impl <= RGK_GATES_FUSED, RGK_EINVAL,
+  RGK_REQUIRE(gates_impl >= RGK_GATES_AUTO && gates_impl <= RGK_GATES_FUSED_EXACT, RGK_EINVAL,
               "unknown gates_impl %d", gates_impl);
   RGK_REQUIRE(xb && segment_pos && h_in && conv_cache_in && out && h_out, RGK_EINVAL,
               "NULL pointer argument");

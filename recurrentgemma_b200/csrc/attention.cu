@@ -612,13 +612,12 @@ cudaError_t launch_attention_prefill(const void* q, const void* k, const void* v
       !tensor_map_bte(&map_k, k, (uint64_t)B, (uint64_t)T, kHd, kTk, kSl, true) ||
       !tensor_map_bte(&map_vt, vt, (uint64_t)B, kHd, (uint64_t)Tp, kHd, kSl, true))
     return cudaErrorInvalidValue;
-  static int num_sms = 0;
-  if (num_sms == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
-    cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemA);
-  }
+  static PerDeviceOnce once;
+  int num_sms = 0;
+  cudaError_t e0 = once.run([] {
+    return cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemA);
+  }, &num_sms);
+  if (e0 != cudaSuccess) return e0;
   const int q_tiles = (int)((T + kTq - 1) / kTq);
   const int n_units = (int)(B * N * q_tiles);
   const int grid = n_units < num_sms ? n_units : num_sms;

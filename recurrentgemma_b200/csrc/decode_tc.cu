@@ -295,16 +295,15 @@ cudaError_t launch_path_decode_tc(const void* xb, const void* yb, const void* po
   CUtensorMap map_w;
   if (!tensor_map_2d(&map_w, packed_w, (uint64_t)H * 2 * 256, 256, kChanCta, 64, true))
     return cudaErrorInvalidValue;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static PerDeviceOnce once;
+  cudaError_t e0 = once.run([] {
     cudaError_t e = cudaFuncSetAttribute(decode_tc_kernel<true>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(decode_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               kSmem);
     if (e != cudaSuccess) return e;
-    attr_set = true;
-  }
+    return cudaFuncSetAttribute(decode_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                kSmem);
+  });
+  if (e0 != cudaSuccess) return e0;
   const dim3 grid((unsigned)(H * 4), (unsigned)((B + kRowsM - 1) / kRowsM));
   const int E = H * kHeadW;
   // Launched with programmatic stream serialization: the kernel may start while its predecessor

@@ -330,13 +330,12 @@ cudaError_t launch_gates_tc(const void* c, const void* pos, int pos64, const voi
       !tensor_map_2d(&map_w, packed_w, (uint64_t)H * 2 * kTileN, kHeadWidth, kTileN, kKSlice, true))
     return cudaErrorInvalidValue;
 
-  static int num_sms = 0;
-  if (num_sms == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
-    cudaFuncSetAttribute(gates_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-  }
+  static PerDeviceOnce once;
+  int num_sms = 0;
+  cudaError_t e0 = once.run([] {
+    return cudaFuncSetAttribute(gates_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+  }, &num_sms);
+  if (e0 != cudaSuccess) return e0;
   const int groups = 2 * H;
   const int tiles = (int)((M + kTileM - 1) / kTileM);
   int cpg = num_sms / groups;

@@ -318,17 +318,17 @@ cudaError_t launch_dense_tc(const void* x, const void* w, const void* bias, cons
   if (!tensor_map_2d(&map_x, x, (uint64_t)M, (uint64_t)K, BM, BK, true) ||
       !tensor_map_2d(&map_w, w, (uint64_t)N, (uint64_t)K, BN, BK, true))
     return cudaErrorInvalidValue;
-  static int num_sms = 0;
-  if (num_sms == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
-    cudaFuncSetAttribute(gemm_tc_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemG);
-    cudaFuncSetAttribute(gemm_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemG);
-    cudaFuncSetAttribute(gemm_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemG);
-    cudaFuncSetAttribute(gemm_tc_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemG);
-    cudaFuncSetAttribute(gemm_tc_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemG);
-  }
+  static PerDeviceOnce once;
+  int num_sms = 0;
+  cudaError_t e0 = once.run([] {
+    cudaError_t e;
+    if ((e = cudaFuncSetAttribute(gemm_tc_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemG)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(gemm_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemG)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(gemm_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemG)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(gemm_tc_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemG)) != cudaSuccess) return e;
+    return cudaFuncSetAttribute(gemm_tc_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemG);
+  }, &num_sms);
+  if (e0 != cudaSuccess) return e0;
   const int m_tiles = (int)((M + BM - 1) / BM), n_tiles = (N + BN - 1) / BN;
   const int total = m_tiles * n_tiles;
   const int grid = total < num_sms ? total : num_sms;

@@ -6,7 +6,51 @@
 #include <stddef.h>
 #include <stdint.h>
 
+#include <mutex>
+
 namespace rgk {
+
+// One-time set-up per device.  cudaFuncSetAttribute applies to the function on the CURRENT device
+// only, so a launcher that needs more than the default dynamic shared memory runs its set-up the
+// first time it sees each device (a process may drive several), under a lock, and caches that
+// device's SM count.  A failed set-up is retried by the next call.
+class PerDeviceOnce {
+ public:
+  template <typename F>
+  cudaError_t run(F&& setup, int* num_sms = nullptr) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lock(mu_);
+    if (sms_[dev] == 0) {
+      int n = 0;
+      if ((e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
+      if ((e = setup()) != cudaSuccess) return e;
+      sms_[dev] = n;
+    }
+    if (num_sms != nullptr) *num_sms = sms_[dev];
+    return cudaSuccess;
+  }
+
+ private:
+  static constexpr int kMaxDevices = 64;
+  std::mutex mu_;
+  int sms_[kMaxDevices] = {};
+};
+
+// How the fused RG-LRU kernel evaluates the two sigmoids of the gates and the gelu of the join.
+//   kMathExact  sigmoids as 1 / (1 + 2^(-z log2 e)) in float32 with one reciprocal for the four
+//               denominators of a token pair (both gates), gelu as z / (1 + 2^w) with one reciprocal
+//               per token pair; every rounding of the reference, so that the outputs agree with
+//               the reference's bfloat16 arithmetic on all but a fraction of a percent of the elements.
+//   kMathFast   the input gate as 0.5 + 0.5 tanh(z / 2) and the gelu as 0.5 z (1 + tanh u) in
+//               packed bfloat16 (tanh.approx.bf16x2): 5.5 instead of 6 special-function operations
+//               and about 15 fewer instructions per element; a third to a half of the outputs then
+//               differ from the reference's by one bfloat16 step.  The recurrence gate keeps the
+//               exact form: where a = exp(log_a) sits near 1 a one-step change of that gate flips
+//               the rounding of a, and the state of such a slow channel drifts from the reference's.
+enum { kMathExact = 0, kMathFast = 1 };
 
 // conv1d.cu
 cudaError_t launch_conv1d_prefill(const void* x, const void* pos, int pos64, const void* w,
@@ -51,14 +95,15 @@ cudaError_t launch_path_decode_tc(const void* xb, const void* yb, const void* po
 
 // rglru_chan_tc.cu: gate projections + gate arithmetic + scan (+ join) in one kernel with
 // channel-major accumulators (TMEM lane = channel), so that gate arithmetic, recurrence and join
-// run in registers in time order; bfloat16, head width 256, T a multiple of 128.
+// run in registers in time order; bfloat16, head width 256, any T.  math: one of the kMath*
+// variants of tc_common.cuh (how the sigmoids and the gelu are evaluated).
 // ws: rglru_chan_workspace_bytes(B, T, E) bytes whose first word is the caller's status word.
 bool rglru_chan_supported(int dtype, int bw, int64_t B, int64_t T);
 size_t rglru_chan_workspace_bytes(int64_t B, int64_t T, int64_t E);
 cudaError_t launch_rglru_chan(const void* c, const void* pos, int pos64, const void* a_param,
                               const void* bx, const void* ba, const void* packed_w, const float* h0,
                               const void* yb, int y_activated, int64_t B, int64_t T, int H,
-                              void* out, float* h_last, void* ws, cudaStream_t s);
+                              void* out, float* h_last, void* ws, int math, cudaStream_t s);
 
 // gemm_tc.cu: out [M,N] = x [M,K] W[N,K]^T + bias (bfloat16, float32 accumulation) on tcgen05;
 // gelu == 1 applies gelu_tanh to the rounded result; gelu == 2 is the GeGLU epilogue of the MLP

@@ -19,15 +19,18 @@
 //             of two TMEM accumulator sets (2 x 128 columns each);
 //   epilogue  16 warps = 4 channel quarters (the warp's TMEM lane quarter) x 4 token quarters.
 //             A warp fetches its own 32 x 32 tiles of the conv output and of the other branch by
-//             TMA into 2 KiB buffers, and writes its outputs into the second buffer, which a TMA
-//             store sends to HBM: every global access of the kernel is a bulk tensor copy.
+//             TMA (64-byte swizzle) into 2 KiB buffers, transposes each in place (ldmatrix.trans +
+//             stmatrix) so that a thread finds the 32 tokens of its channel as four 16-byte pieces,
+//             writes its outputs the same way, transposes back and hands the tile to a TMA store:
+//             every global access of the kernel is a bulk tensor copy, every shared-memory access
+//             of the tiles a 16-byte one.
 // Per unit an epilogue thread: tcgen05.ld of 2 x 16 columns -> gate arithmetic on token pairs in
 // packed bfloat16 with the reference's roundings -> (a, x) kept packed in 32 registers while the
 // 32-token map (P, H): h -> P h + H is accumulated -> the four token quarters of a channel quarter
 // meet at a 128-thread named barrier; the last one publishes the tile's map, resolves the incoming
 // state (decoupled look-back over earlier time tiles, normally one already inclusive record) and
 // publishes the inclusive state -> second named barrier -> replay from registers with the true
-// incoming state, join, 2-byte stores into the output tile.
+// incoming state, join, 16-byte stores into the output tile.
 // All waits (mbarriers, look-back flags) are bounded; on expiry WsHeader::status is raised, the
 // affected values are taken as zero and the kernel runs to completion.
 #include <cuda.h>
@@ -84,22 +87,57 @@ struct QuarterRecord {
   float H[kSub];
 };
 
+// In-place transposition of a warp's 32 x 32 bfloat16 tile (rows of 64 bytes, 64-byte swizzle:
+// 16-byte piece j of row r at position j ^ ((r >> 1) & 3)).  ldmatrix.trans hands thread T of the
+// warp, for each 8 x 8 block, the elements (rows 2 (T % 4) and 2 (T % 4) + 1, column T / 4) packed
+// into one register - the fragment (row T / 4, columns 2 (T % 4), + 1) of the transposed block,
+// which stmatrix stores.  The whole tile sits in registers between the two, so it is written back
+// over itself, rows and columns exchanged, in the same swizzled layout.  Every access is
+// conflict-free.  ld_base = tile + lane * 64 + (((lane >> 1) & 3) << 4): the address of the lane's
+// own row at piece 0; st_base = tile + (lane & 7) * 64 + (((lane >> 3) ^ ((lane >> 1) & 3)) << 4).
+__device__ __forceinline__ void transpose_tile(uint32_t ld_base, uint32_t st_base) {
+  uint32_t r[4][4];
+#pragma unroll
+  for (int q = 0; q < 4; ++q)
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[q][0]), "=r"(r[q][1]), "=r"(r[q][2]), "=r"(r[q][3])
+                 : "r"(ld_base ^ (uint32_t)(q << 4)) : "memory");
+  __syncwarp();
+#pragma unroll
+  for (int q = 0; q < 4; ++q)
+    asm volatile("stmatrix.sync.aligned.m8n8.x4.shared.b16 [%0], {%1, %2, %3, %4};"
+                 :: "r"(st_base + (uint32_t)(q * 512)), "r"(r[q][0]), "r"(r[q][1]), "r"(r[q][2]),
+                    "r"(r[q][3]) : "memory");
+  __syncwarp();
+}
+// Piece k (tokens 8 k .. 8 k + 7 as four token pairs) of the lane's own row of a transposed tile.
+__device__ __forceinline__ uint4 lds_piece(uint32_t ld_base, int k) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(ld_base ^ (uint32_t)(k << 4)) : "memory");
+  return v;
+}
+__device__ __forceinline__ void sts_piece(uint32_t ld_base, int k, const uint4& v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"
+               :: "r"(ld_base ^ (uint32_t)(k << 4)), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
 // 16 tokens of one channel: gates from the accumulators, (a, x) packed per token pair, and the
-// running map (P, H) of the thread's tokens.  `ct` points at the thread's column of the warp's conv
-// tile (row stride 32 elements); `rs` holds the reset bits of the 16 tokens, `inv` the bits of tokens
-// past the end of the sequence (the kResets variant handles both).
-template <bool kResets>
+// running map (P, H) of the thread's tokens.  c holds the conv outputs of the 16 tokens as 8 token
+// pairs; `rs` holds the reset bits of the 16 tokens, `inv` the bits of tokens past the end of the
+// sequence (the kResets variant handles both; the other one has no branch inside the unrolled loop,
+// so that the compiler interleaves the eight independent pairs).
+template <bool kResets, int kMath>
 __device__ __forceinline__ void gates_16(const uint32_t (&zx)[16], const uint32_t (&za)[16],
-                                         const uint16_t* ct, uint32_t bx2, uint32_t ba2,
+                                         const uint32_t (&c)[8], uint32_t bx2, uint32_t ba2, uint32_t hbx2,
                                          uint32_t m8sp2, uint32_t rs, uint32_t inv, uint32_t* a_out,
                                          uint32_t* x_out, float& P, float& H) {
 #pragma unroll
   for (int jp = 0; jp < 8; ++jp) {
-    const uint32_t c2 = (uint32_t)ct[(2 * jp) * kSub] | ((uint32_t)ct[(2 * jp + 1) * kSub] << 16);
     uint32_t a2, gx2, mult2;
-    gate_tokens(__uint_as_float(zx[2 * jp]), __uint_as_float(zx[2 * jp + 1]),
-                __uint_as_float(za[2 * jp]), __uint_as_float(za[2 * jp + 1]), bx2, ba2, m8sp2, a2, gx2,
-                mult2);
+    gate_tokens<kMath>(__uint_as_float(zx[2 * jp]), __uint_as_float(zx[2 * jp + 1]),
+                       __uint_as_float(za[2 * jp]), __uint_as_float(za[2 * jp + 1]), bx2, ba2, hbx2,
+                       m8sp2, a2, gx2, mult2);
     if constexpr (kResets) {
       // a token that starts a document: a = 0, multiplier = 1 (torch/layers.py:343-350, 166)
       const uint32_t keep = (((rs >> (2 * jp)) & 1u) ? 0u : 0x0000ffffu) |
@@ -113,7 +151,7 @@ __device__ __forceinline__ void gates_16(const uint32_t (&zx)[16], const uint32_
       mult2 = (mult2 & live) | (0x3f803f80u & ~live);
       gx2 &= live;
     }
-    const uint32_t x2 = bmul2(bmul2(c2, gx2), mult2);
+    const uint32_t x2 = bmul2(bmul2(c[jp], gx2), mult2);
     a_out[jp] = a2;
     x_out[jp] = x2;
     const float a0 = bf16_lo(a2), a1 = bf16_hi(a2);
@@ -124,7 +162,23 @@ __device__ __forceinline__ void gates_16(const uint32_t (&zx)[16], const uint32_
   }
 }
 
-template <int kJoin>   // 0: out = y, 1: out = y * gelu_tanh(yb), 2: out = y * yb
+// Position of a unit (time tile, sequence, half head), advanced by the grid size without divisions.
+struct UnitPos {
+  int tt, b, grp;
+};
+struct UnitStep {
+  int d_tt, d_b, d_g, B, groups;
+  __device__ __forceinline__ void advance(UnitPos& u) const {
+    u.grp += d_g;
+    if (u.grp >= groups) { u.grp -= groups; u.b += 1; }
+    u.b += d_b;
+    if (u.b >= B) { u.b -= B; u.tt += 1; }
+    u.tt += d_tt;
+  }
+};
+
+// kJoin 0: out = y, 1: out = y * gelu_tanh(yb), 2: out = y * yb;  kMath: see tc_common.cuh
+template <int kJoin, int kMath>
 __global__ void __launch_bounds__(kThreads, 1)
 rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_w,
                   const __grid_constant__ CUtensorMap map_ct, const __grid_constant__ CUtensorMap map_yt,
@@ -225,47 +279,59 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
     const int chq = warp & 3;                // channel quarter = TMEM lane quarter of this warp
     const int tq = warp >> 2;                // token quarter: tokens 32 tq .. 32 tq + 31 of the unit
     const int set_id = 1 + chq;              // named barrier of the four token quarters
-    uint8_t* tile_c = smem + kOffTiles + warp * 2 * kSubBytes;
-    uint8_t* tile_y = tile_c + kSubBytes;
-    const uint16_t* ct = reinterpret_cast<const uint16_t*>(tile_c) + lane;
-    uint16_t* yt = reinterpret_cast<uint16_t*>(tile_y) + lane;
-    const uint32_t tile_c_s = smem_u32(tile_c), tile_y_s = smem_u32(tile_y);
-    bool ok = true;
+    const uint32_t tile_c_s = s_base + kOffTiles + warp * 2 * kSubBytes, tile_y_s = tile_c_s + kSubBytes;
+    // addresses of the in-place transposition and of the lane's own row (see transpose_tile)
+    const uint32_t row_off = lane * 64 + (((lane >> 1) & 3) << 4);
+    const uint32_t st_off = (lane & 7) * 64 + (((lane >> 3) ^ ((lane >> 1) & 3)) << 4);
+    bool ok = true;                          // false once a bounded wait expired: later waits are skipped
 
-    auto unit_xy = [&](int t, int& x, int& y, int& z) {     // channel, token in sequence, sequence
-      const int u = blockIdx.x + t * gridDim.x;
-      const int tt = u / per_tt, rem = u - tt * per_tt;
-      const int b = rem / groups, grp = rem - b * groups;
-      x = (grp >> 1) * kHW + (grp & 1) * kUC + chq * kSub;
-      y = tt * kUT + tq * kSub;
-      z = b;
-    };
-    // whether this lane's token of unit t starts a document (tokens past the end do not)
-    auto lane_reset = [&](int t) {
-      int x, y, z;
-      unit_xy(t, x, y, z);
-      const int tok = y + lane;
-      return tok < T_ && pos_is_zero(pos, pos64, (int64_t)z * T_ + tok);
+    // unit positions without divisions in the loop
+    UnitStep step;
+    step.B = B; step.groups = groups;
+    step.d_tt = (int)gridDim.x / per_tt;
+    {
+      const int d_rem = (int)gridDim.x - step.d_tt * per_tt;
+      step.d_b = d_rem / groups;
+      step.d_g = d_rem - step.d_b * groups;
+    }
+    UnitPos cur, nxt;
+    {
+      const int u = blockIdx.x;
+      cur.tt = u / per_tt;
+      const int rem = u - cur.tt * per_tt;
+      cur.b = rem / groups;
+      cur.grp = rem - cur.b * groups;
+    }
+    auto chan0 = [&](const UnitPos& u) { return (u.grp >> 1) * kHW + (u.grp & 1) * kUC + chq * kSub; };
+    // whether this lane's token of a unit starts a document (tokens past the end do not)
+    auto lane_reset = [&](const UnitPos& u) {
+      const int tok = u.tt * kUT + tq * kSub + lane;
+      return tok < T_ && pos_is_zero(pos, pos64, (int64_t)u.b * T_ + tok);
     };
     if (lane == 0 && n_my > 0) {
-      int x, y, z;
-      unit_xy(0, x, y, z);
       mbar_expect_tx(bar_ct(warp), kSubBytes);
-      tma_load_3d(tile_c_s, &map_ct, x, y, z, bar_ct(warp));
+      tma_load_3d(tile_c_s, &map_ct, chan0(cur), cur.tt * kUT + tq * kSub, cur.b, bar_ct(warp));
     }
-
-    // whether this lane's token of the next unit starts a document: asked for a unit ahead
-    bool reset_next = false;
-    if (n_my > 0) reset_next = lane_reset(0);
+    // whether this lane's token of the next unit starts a document, and the constants of this
+    // lane's channel in the next unit (gate biases, -8 softplus(a_param)): asked for a unit ahead
+    bool reset_next = n_my > 0 ? lane_reset(cur) : false;
+    uint32_t bxv = 0u, bav = 0u, spv = 0u;
+    auto load_consts = [&](const UnitPos& u) {
+      const int e = chan0(u) + lane;
+      bxv = __ldg(reinterpret_cast<const uint16_t*>(bias_x) + e);
+      bav = __ldg(reinterpret_cast<const uint16_t*>(bias_a) + e);
+      spv = __ldg(reinterpret_cast<const uint16_t*>(m8sp) + e);
+    };
+    if (n_my > 0) load_consts(cur);
 
     for (int t = 0; t < n_my; ++t) {
       const int as = t & 1, par = t & 1;
-      const int u = blockIdx.x + t * gridDim.x;
-      const int tt = u / per_tt, rem = u - tt * per_tt;
-      const int b = rem / groups, grp = rem - b * groups;
-      const int e0 = (grp >> 1) * kHW + (grp & 1) * kUC + chq * kSub;     // first channel of the warp
+      const int tt = cur.tt, b = cur.b;
+      const int e0 = chan0(cur);                                          // first channel of the warp
       const int tok0 = tt * kUT + tq * kSub;                              // first token of the warp
-      const int64_t rec = (int64_t)u * 4 + chq;
+      const int64_t rec = ((int64_t)(tt * per_tt + b * groups + cur.grp)) * 4 + chq;
+      nxt = cur;
+      step.advance(nxt);
       float2* s_qmap = reinterpret_cast<float2*>(smem + kOffQmap) + ((par * 4 + chq) * 4) * 32;
       float* s_hin = reinterpret_cast<float*>(smem + kOffHin) + (par * 4 + chq) * 32;
       volatile int* s_known = reinterpret_cast<volatile int*>(smem + kOffKnown) + (par * 4 + chq);
@@ -274,10 +340,8 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
       // tokens of this warp past the end of the sequence (only in a sequence's last time tile)
       const int n_live = T_ - tok0;
       const uint32_t invalid = n_live >= 32 ? 0u : (n_live <= 0 ? 0xffffffffu : (0xffffffffu << n_live));
-      const uint32_t bxv = __ldg(reinterpret_cast<const uint16_t*>(bias_x) + e0 + lane);
-      const uint32_t bav = __ldg(reinterpret_cast<const uint16_t*>(bias_a) + e0 + lane);
-      const uint32_t spv = __ldg(reinterpret_cast<const uint16_t*>(m8sp) + e0 + lane);
       const uint32_t bx2 = bxv | (bxv << 16), ba2 = bav | (bav << 16), m8sp2 = spv | (spv << 16);
+      const uint32_t hbx2 = bmul2(bx2, 0x3f003f00u);
 
       // the last token quarter asks for its predecessor's inclusive state now (normally published
       // most of a round ago) and looks at the answer after the gate arithmetic
@@ -289,8 +353,11 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
         else pre = ld_relaxed_u64(incl + (rec - (int64_t)per_tt * 4) * kSub + lane);
       }
 
-      // ---- gates of the thread's 32 tokens, 16 at a time ------------------------------------------
+      // ---- the conv tile: transposed in place, a thread then finds its channel's 32 tokens ----------
       if (ok) ok = mbar_wait(bar_ct(warp), t & 1, s_abort);
+      transpose_tile(tile_c_s + row_off, tile_c_s + st_off);
+
+      // ---- gates of the thread's 32 tokens, 16 at a time ------------------------------------------
       if (ok) ok = mbar_wait(bar_acc_full(as), (t >> 1) & 1, s_abort);
       tc_fence_after();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(chq * 32) << 16) + as * 2 * kUT + tq * kSub;
@@ -298,29 +365,37 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
       float P = 1.0f, H = 0.0f;
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
-        uint32_t zx[16], za[16];
-        if (ok) {
-          tc_ld_32x16(t_row + half * 16, zx);
-          tc_ld_32x16(t_row + kUT + half * 16, za);
-          tc_wait_ld();
-        } else {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) { zx[i] = 0u; za[i] = 0u; }
+        uint32_t zx[16], za[16], c[8];
+        tc_ld_32x16(t_row + half * 16, zx);
+        tc_ld_32x16(t_row + kUT + half * 16, za);
+        {
+          const uint4 c0 = lds_piece(tile_c_s + row_off, 2 * half), c1 = lds_piece(tile_c_s + row_off, 2 * half + 1);
+          c[0] = c0.x; c[1] = c0.y; c[2] = c0.z; c[3] = c0.w;
+          c[4] = c1.x; c[5] = c1.y; c[6] = c1.z; c[7] = c1.w;
         }
+        tc_wait_ld();
         if (half == 1) {
           // the accumulator set has been read: it may be overwritten
           tc_fence_before();
           __syncwarp();
           if (lane == 0 && ok) mbar_arrive(bar_acc_empty(as));
+          // ... and so has the conv tile: the next unit's is fetched into it (the generic-proxy
+          // accesses of every lane are ordered before the copy engine's write)
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0 && t + 1 < n_my) {
+            mbar_expect_tx(bar_ct(warp), kSubBytes);
+            tma_load_3d(tile_c_s, &map_ct, chan0(nxt), nxt.tt * kUT + tq * kSub, nxt.b, bar_ct(warp));
+          }
         }
         const uint32_t rs = (resets >> (half * 16)) & 0xffffu;
         const uint32_t inv = (invalid >> (half * 16)) & 0xffffu;
         if ((rs | inv) == 0u)
-          gates_16<false>(zx, za, ct + half * 16 * kSub, bx2, ba2, m8sp2, rs, inv, a_pk + half * 8,
-                          x_pk + half * 8, P, H);
+          gates_16<false, kMath>(zx, za, c, bx2, ba2, hbx2, m8sp2, rs, inv, a_pk + half * 8,
+                                 x_pk + half * 8, P, H);
         else
-          gates_16<true>(zx, za, ct + half * 16 * kSub, bx2, ba2, m8sp2, rs, inv, a_pk + half * 8,
-                         x_pk + half * 8, P, H);
+          gates_16<true, kMath>(zx, za, c, bx2, ba2, hbx2, m8sp2, rs, inv, a_pk + half * 8,
+                                x_pk + half * 8, P, H);
         if (half == 0) {
           // the previous unit's output tile must have been read by its store before the buffer is
           // written again; then the other branch's tile of this unit is fetched into it
@@ -333,15 +408,8 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
           }
         }
       }
-      __threadfence_block();                 // the tile's loads are complete before it is refilled
-      __syncwarp();
-      if (t + 1 < n_my) reset_next = lane_reset(t + 1);
-      if (lane == 0 && t + 1 < n_my) {       // the conv tile is free: fetch the next unit's
-        int x, y, z;
-        unit_xy(t + 1, x, y, z);
-        mbar_expect_tx(bar_ct(warp), kSubBytes);
-        tma_load_3d(tile_c_s, &map_ct, x, y, z, bar_ct(warp));
-      }
+      if (t + 1 < n_my) load_consts(nxt);
+      if (t + 1 < n_my) reset_next = lane_reset(nxt);
 
       // The incoming state is normally known before the tile's own map is (the predecessor's
       // inclusive record was there at the start of the unit): then the quarters need one barrier,
@@ -465,30 +533,37 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
       }
       if constexpr (kJoin != 0) {
         if (ok) ok = mbar_wait(bar_yt(warp), t & 1, s_abort);
+        transpose_tile(tile_y_s + row_off, tile_y_s + st_off);
       }
 #pragma unroll
-      for (int jp = 0; jp < 16; ++jp) {
-        const uint32_t a2 = a_pk[jp], x2 = x_pk[jp];
-        h = fmaf(bf16_lo(a2), h, bf16_lo(x2));
-        const float y0 = h;
-        h = fmaf(bf16_hi(a2), h, bf16_hi(x2));
-        uint32_t y2 = pack_bf16x2(y0, h);
-        if constexpr (kJoin == 1) {
-          const float z0 = __uint_as_float((uint32_t)yt[(2 * jp) * kSub] << 16);
-          const float z1 = __uint_as_float((uint32_t)yt[(2 * jp + 1) * kSub] << 16);
-          y2 = bmul2(y2, pack_bf16x2(gelu_fast_f(z0), gelu_fast_f(z1)));
-        } else if constexpr (kJoin == 2) {
-          y2 = bmul2(y2, (uint32_t)yt[(2 * jp) * kSub] | ((uint32_t)yt[(2 * jp + 1) * kSub] << 16));
+      for (int k = 0; k < 4; ++k) {
+        uint32_t z[4] = {0u, 0u, 0u, 0u}, o[4];
+        if constexpr (kJoin != 0) {
+          const uint4 zv = lds_piece(tile_y_s + row_off, k);
+          z[0] = zv.x; z[1] = zv.y; z[2] = zv.z; z[3] = zv.w;
         }
-        yt[(2 * jp) * kSub] = (uint16_t)(y2 & 0xffffu);
-        yt[(2 * jp + 1) * kSub] = (uint16_t)(y2 >> 16);
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          const uint32_t a2 = a_pk[4 * k + w], x2 = x_pk[4 * k + w];
+          h = fmaf(bf16_lo(a2), h, bf16_lo(x2));
+          const float y0 = h;
+          h = fmaf(bf16_hi(a2), h, bf16_hi(x2));
+          uint32_t y2 = pack_bf16x2(y0, h);
+          if constexpr (kJoin == 1) y2 = join_gelu2<kMath>(y2, z[w]);
+          else if constexpr (kJoin == 2) y2 = bmul2(y2, z[w]);
+          o[w] = y2;
+        }
+        sts_piece(tile_y_s + row_off, k, make_uint4(o[0], o[1], o[2], o[3]));
       }
+      __syncwarp();
+      transpose_tile(tile_y_s + row_off, tile_y_s + st_off);
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) {
         tma_store_3d(&map_ot, e0, tok0, b, tile_y_s);
         bulk_commit();
       }
+      cur = nxt;
     }
     if (lane == 0) bulk_wait_all();
   }
@@ -539,6 +614,25 @@ ChanLayout chan_layout(int64_t B, int64_t T, int64_t E) {
   return L;
 }
 
+// The kernel needs more dynamic shared memory than the default limit: the attribute is a property
+// of the function on ONE device, so it is set (and the SM count read) once per device.
+template <int kMath>
+cudaError_t chan_set_smem() {
+  cudaError_t e;
+  if ((e = cudaFuncSetAttribute(rglru_chan_kernel<0, kMath>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem)) != cudaSuccess) return e;
+  if ((e = cudaFuncSetAttribute(rglru_chan_kernel<1, kMath>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem)) != cudaSuccess) return e;
+  return cudaFuncSetAttribute(rglru_chan_kernel<2, kMath>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+}
+
+cudaError_t chan_device_setup(int* num_sms) {
+  static PerDeviceOnce once;
+  return once.run([] {
+    cudaError_t e = chan_set_smem<kMathExact>();
+    if (e != cudaSuccess) return e;
+    return chan_set_smem<kMathFast>();
+  }, num_sms);
+}
+
 }  // namespace
 
 bool rglru_chan_supported(int dtype, int bw, int64_t B, int64_t T) {
@@ -553,7 +647,7 @@ size_t rglru_chan_workspace_bytes(int64_t B, int64_t T, int64_t E) {
 cudaError_t launch_rglru_chan(const void* c, const void* pos, int pos64, const void* a_param,
                               const void* bx, const void* ba, const void* packed_w, const float* h0,
                               const void* yb, int y_activated, int64_t B, int64_t T, int H,
-                              void* out, float* h_last, void* ws, cudaStream_t s) {
+                              void* out, float* h_last, void* ws, int math, cudaStream_t s) {
   using T_ = __nv_bfloat16;
   const int E = H * kHW;
   const ChanLayout L = chan_layout(B, T, E);
@@ -569,31 +663,31 @@ cudaError_t launch_rglru_chan(const void* c, const void* pos, int pos64, const v
   const uint64_t Bu = (uint64_t)B, Tu = (uint64_t)T, Eu = (uint64_t)E;
   if (!tensor_map_bte(&map_c, c, Bu, Tu, Eu, kUT, kKB, true) ||
       !tensor_map_2d(&map_w, packed_w, (uint64_t)H * 4 * kUC, kHW, 2 * kUC, kKB, true) ||
-      !tensor_map_bte(&map_ct, c, Bu, Tu, Eu, kSub, kSub, false) ||
-      !tensor_map_bte(&map_ot, out, Bu, Tu, Eu, kSub, kSub, false) ||
-      !tensor_map_bte(&map_yt, yb != nullptr ? yb : out, Bu, Tu, Eu, kSub, kSub, false))
+      !tensor_map_bte_sw64(&map_ct, c, Bu, Tu, Eu, kSub, kSub) ||
+      !tensor_map_bte_sw64(&map_ot, out, Bu, Tu, Eu, kSub, kSub) ||
+      !tensor_map_bte_sw64(&map_yt, yb != nullptr ? yb : out, Bu, Tu, Eu, kSub, kSub))
     return cudaErrorInvalidValue;
-  static int num_sms = 0;
-  if (num_sms == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
-    cudaFuncSetAttribute(rglru_chan_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
-    cudaFuncSetAttribute(rglru_chan_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
-    cudaFuncSetAttribute(rglru_chan_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
-  }
+  int num_sms = 0;
+  if ((err = chan_device_setup(&num_sms)) != cudaSuccess) return err;
   const int groups = 2 * H;
   const int n_units = (int)L.n_units;
   const int grid = n_units < num_sms ? n_units : num_sms;   // all CTAs resident: look-back may spin
-#define RGK_CHAN(J)                                                                              \
-  rglru_chan_kernel<J><<<grid, kThreads, kSmem, s>>>(                                            \
+#define RGK_CHAN(J, M)                                                                           \
+  rglru_chan_kernel<J, M><<<grid, kThreads, kSmem, s>>>(                                         \
       map_c, map_w, map_ct, map_yt, map_ot, pos, pos64, (const T_*)bx, (const T_*)ba, m8sp, h0,  \
       (int)B, (int)T, E, groups, n_units, h_last, reinterpret_cast<WsHeader*>(base),             \
       reinterpret_cast<unsigned*>(base + L.flags_off),                                           \
       reinterpret_cast<QuarterRecord*>(base + L.agg_off),                                        \
       reinterpret_cast<unsigned long long*>(base + L.incl_off))
+#define RGK_CHAN_J(M)                                                                            \
+  if (join == 0) RGK_CHAN(0, M); else if (join == 1) RGK_CHAN(1, M); else RGK_CHAN(2, M)
   const int join = yb == nullptr ? 0 : (y_activated ? 2 : 1);
-  if (join == 0) RGK_CHAN(0); else if (join == 1) RGK_CHAN(1); else RGK_CHAN(2);
+  switch (math) {
+    case kMathExact: RGK_CHAN_J(kMathExact); break;
+    case kMathFast: RGK_CHAN_J(kMathFast); break;
+    default: return cudaErrorInvalidValue;
+  }
+#undef RGK_CHAN_J
 #undef RGK_CHAN
   return cudaGetLastError();
 }

@@ -391,14 +391,12 @@ cudaError_t launch_scan_typed(const void* x, const void* a, const uint8_t* reset
       !tensor_map_bte(&map_a, a, (uint64_t)B, (uint64_t)T_, (uint64_t)E, ScanCfg<T>::kRows, kChan, false,
                       (int)sizeof(T)))
     return cudaErrorInvalidValue;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(scan_kernel<T, kJoin>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         ScanSmem<T>::kBytes);
-    if (e != cudaSuccess) return e;
-    attr_set = true;
-  }
+  static PerDeviceOnce once;
+  cudaError_t e = once.run([] {
+    return cudaFuncSetAttribute(scan_kernel<T, kJoin>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                ScanSmem<T>::kBytes);
+  });
+  if (e != cudaSuccess) return e;
   scan_kernel<T, kJoin><<<grid, kThreads, ScanSmem<T>::kBytes, s>>>(
       map_x, map_a, reset, pos, pos64, h0, (const T*)y_mul, (int)B, (int)T_, (int)E, tiles_t, groups,
       (T*)y, h_last, hdr, flags, agg, incl);

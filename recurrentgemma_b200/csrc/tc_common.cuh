@@ -3,6 +3,7 @@
 #pragma once
 
 #include "rgk_common.cuh"
+#include "rgk_internal.h"
 #include "tma.cuh"
 
 namespace rgk {
@@ -221,31 +222,50 @@ __device__ __forceinline__ uint32_t bmax2(uint32_t a, uint32_t b) {
   asm("max.NaN.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
   return r;
 }
-__device__ __forceinline__ float gelu_fast_f(float z) {
-  constexpr float k0 = -1.5957691216057308f * 1.4426950408889634f;
-  constexpr float k1 = k0 * 0.044715f;
-  const float w = z * fmaf(z * z, k1, k0);
-  return z * rcpf(ex2f(w) + 1.0f);
+__device__ __forceinline__ uint32_t bfma2(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t r;
+  asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+  return r;
+}
+// tanh of both halves on the special-function unit; the result carries bfloat16 precision
+__device__ __forceinline__ uint32_t btanh2(uint32_t a) {
+  uint32_t r;
+  asm("tanh.approx.bf16x2 %0, %1;" : "=r"(r) : "r"(a));
+  return r;
 }
 
 // Gate arithmetic of ONE channel for two consecutive tokens (torch/layers.py:338-353), every
 // tensor-level result rounded to bfloat16 where torch rounds it.
 //   zx, za   float32 accumulators of the two tokens;  bx2, ba2, m8sp2: the channel's biases and
-//   -8 softplus(a_param), each duplicated into both halves.
+//   -8 softplus(a_param), each duplicated into both halves;  hbx2: half the input-gate bias.
 // Returns packed a, x-gate and input multiplier, resets not yet applied.
+template <int kMath>
 __device__ __forceinline__ void gate_tokens(float zx0, float zx1, float za0, float za1, uint32_t bx2,
-                                            uint32_t ba2, uint32_t m8sp2, uint32_t& a2,
+                                            uint32_t ba2, uint32_t hbx2, uint32_t m8sp2, uint32_t& a2,
                                             uint32_t& gx2, uint32_t& mult2) {
   constexpr float kNegLog2e = -1.4426950408889634f;
-  constexpr uint32_t kFloor = 0xc226c226u;     // -41.5: keeps the product of two denominators finite
-  const uint32_t zx2 = bmax2(badd2(pack_bf16x2(zx0, zx1), bx2), kFloor);
-  const uint32_t za2 = bmax2(badd2(pack_bf16x2(za0, za1), ba2), kFloor);
-  // sigmoid(z) = 1 / (1 + 2^(-z log2 e)); the two gates of a token share one reciprocal
-  const float dx0 = 1.0f + ex2f(bf16_lo(zx2) * kNegLog2e), dx1 = 1.0f + ex2f(bf16_hi(zx2) * kNegLog2e);
-  const float da0 = 1.0f + ex2f(bf16_lo(za2) * kNegLog2e), da1 = 1.0f + ex2f(bf16_hi(za2) * kNegLog2e);
-  const float r0 = rcpf(dx0 * da0), r1 = rcpf(dx1 * da1);
-  gx2 = pack_bf16x2(r0 * da0, r1 * da1);
-  const uint32_t ga2 = pack_bf16x2(r0 * dx0, r1 * dx1);
+  uint32_t ga2;
+  if constexpr (kMath == kMathExact) {
+    constexpr uint32_t kFloor = 0xc1acc1acu;   // -21.5: the product of four denominators stays finite
+    const uint32_t zx2 = bmax2(badd2(pack_bf16x2(zx0, zx1), bx2), kFloor);
+    const uint32_t za2 = bmax2(badd2(pack_bf16x2(za0, za1), ba2), kFloor);
+    const float dx0 = 1.0f + ex2f(bf16_lo(zx2) * kNegLog2e), dx1 = 1.0f + ex2f(bf16_hi(zx2) * kNegLog2e);
+    const float da0 = 1.0f + ex2f(bf16_lo(za2) * kNegLog2e), da1 = 1.0f + ex2f(bf16_hi(za2) * kNegLog2e);
+    const float p0 = dx0 * da0, p1 = dx1 * da1;
+    const float r = rcpf(p0 * p1);
+    const float r0 = r * p1, r1 = r * p0;      // 1 / p0, 1 / p1
+    gx2 = pack_bf16x2(r0 * da0, r1 * da1);
+    ga2 = pack_bf16x2(r0 * dx0, r1 * dx1);
+  } else {
+    constexpr uint32_t kFloor = 0xc226c226u;   // -41.5: the product of two denominators stays finite
+    constexpr uint32_t kHalf2 = 0x3f003f00u;
+    // round(0.5 zx + 0.5 bx) = 0.5 round(zx + bx): the reference's rounding of the biased value
+    gx2 = bfma2(btanh2(bfma2(pack_bf16x2(zx0, zx1), kHalf2, hbx2)), kHalf2, kHalf2);
+    const uint32_t za2 = bmax2(badd2(pack_bf16x2(za0, za1), ba2), kFloor);
+    const float da0 = 1.0f + ex2f(bf16_lo(za2) * kNegLog2e), da1 = 1.0f + ex2f(bf16_hi(za2) * kNegLog2e);
+    const float r = rcpf(da0 * da1);
+    ga2 = pack_bf16x2(r * da1, r * da0);
+  }
   // log_a = (-8 gate_a) softplus(a_param): -8 is exact in bfloat16 and folded into the constant
   const uint32_t la2 = bmul2(ga2, m8sp2);
   const float e0 = ex2f(bf16_lo(la2) * -kNegLog2e), e1 = ex2f(bf16_hi(la2) * -kNegLog2e);
@@ -254,5 +274,28 @@ __device__ __forceinline__ void gate_tokens(float zx0, float zx1, float za0, flo
   mult2 = pack_bf16x2(sqrtf_approx(bf16_lo(om2)), sqrtf_approx(bf16_hi(om2)));
 }
 
+// y2 * gelu_tanh(z2) for a token pair of one channel (torch/modules.py:289-291, 646): the gelu
+// rounded to bfloat16, then the product rounded.
+template <int kMath>
+__device__ __forceinline__ uint32_t join_gelu2(uint32_t y2, uint32_t z2) {
+  if constexpr (kMath == kMathExact) {
+    constexpr float k0 = -1.5957691216057308f * 1.4426950408889634f;
+    constexpr float k1 = k0 * 0.044715f;
+    const float z0 = bf16_lo(z2), z1 = bf16_hi(z2);
+    // gelu_tanh(z) = z sigmoid(2u) = z / (1 + 2^w); the exponent is capped so that the product of
+    // the two denominators stays finite (the quotient is below 1e-18 |z| there either way)
+    const float d0 = 1.0f + ex2f(fminf(z0 * fmaf(z0 * z0, k1, k0), 60.0f));
+    const float d1 = 1.0f + ex2f(fminf(z1 * fmaf(z1 * z1, k1, k0), 60.0f));
+    const float r = rcpf(d0 * d1);
+    return bmul2(y2, pack_bf16x2(z0 * (r * d1), z1 * (r * d0)));
+  } else {
+    constexpr uint32_t kK0 = 0x3f4c3f4cu;      // sqrt(2/pi) = 0.7979 -> 0.796875
+    constexpr uint32_t kK1 = 0x3d123d12u;      // 0.044715 sqrt(2/pi) = 0.035677 -> 0.035645
+    constexpr uint32_t kHalf2 = 0x3f003f00u;
+    const uint32_t u2 = bmul2(z2, bfma2(bmul2(z2, z2), kK1, kK0));
+    const uint32_t hz2 = bmul2(z2, kHalf2);
+    return bmul2(y2, bfma2(btanh2(u2), hz2, hz2));
+  }
+}
 
 }  // namespace rgk

@@ -113,4 +113,20 @@ inline bool tensor_map_bte(CUtensorMap* map, const void* base, uint64_t B, uint6
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// The same with the 64-byte swizzle (box_cols * elem_bytes must be 64): within each 64-byte row of
+// the shared-memory box, 16-byte piece j of row r sits at position j ^ ((r >> 1) & 3), so that
+// eight consecutive rows of one piece, and the four pieces of one row, fall into distinct banks.
+inline bool tensor_map_bte_sw64(CUtensorMap* map, const void* base, uint64_t B, uint64_t T,
+                                uint64_t E, uint32_t box_rows, uint32_t box_cols) {
+  EncodeTiledFn fn = tensor_map_encoder();
+  if (fn == nullptr) return false;
+  const cuuint64_t dims[3] = {E, T, B};
+  const cuuint64_t strides[2] = {E * (cuuint64_t)2, T * E * (cuuint64_t)2};
+  const cuuint32_t box[3] = {box_cols, box_rows, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box,
+            estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 }  // namespace rgk

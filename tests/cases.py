@@ -110,14 +110,7 @@ def make_segment_pos(pattern: str, batch: int, seq: int, case: str = "") -> torc
   return pos.contiguous()
 
 
-def geometric_segment_pos(batch: int, seq: int, mean_len: float, seed: int) -> torch.Tensor:
-  """Documents with Geometric(1/mean_len) lengths (support >= 1); t = 0 starts a document."""
-  g = torch.Generator(device="cpu").manual_seed(seed)
-  starts = torch.rand((batch, seq), generator=g) < (1.0 / mean_len)
-  starts[:, 0] = True
-  idx = torch.arange(seq, dtype=torch.int64).repeat(batch, 1)
-  last_start = torch.where(starts, idx, torch.zeros_like(idx)).cummax(dim=1).values
-  return (idx - last_start).contiguous()
+from recurrentgemma_b200.synthetic import geometric_segment_pos  # noqa: E402,F401  (re-exported)
 
 
 GRIFFIN_BLOCKS = ("recurrent", "recurrent", "attention")   # the model's repeating pattern

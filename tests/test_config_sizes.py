@@ -1,0 +1,107 @@
+"""Parity at the sizes of the benchmark configurations (not only at fixture sizes): the float32
+RG-LRU layer, one GPU's shard of the long head-sharded scan, and the full-size prefill workload.
+Channels of different heads and different batch rows never mix, so where the oracle would take
+minutes the full-size CUDA result is checked on (row, head) slices, which are exact sub-problems."""
+import pytest
+import torch
+
+from recurrentgemma_b200 import synthetic
+from tests.util import TOL, assert_close, norm_err
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def rg():
+  import recurrentgemma_b200 as m
+  from recurrentgemma_b200 import _lib
+  _lib.load()
+  return m
+
+
+def _lru(rg, p, e, h, dt):
+  m = rg.RGLRU(e, h, device=DEV, dtype=dt)
+  m.load_state_dict(p)
+  return m
+
+
+def _head_params(p, head):
+  return (p["a_param"][head * 256:(head + 1) * 256], p["input_gate.w"][head:head + 1],
+          p["input_gate.b"][head:head + 1], p["a_gate.w"][head:head + 1], p["a_gate.b"][head:head + 1])
+
+
+def test_rglru_layer_float32_at_config_size(rg, oracle):
+  """Single RG-LRU layer forward in float32: batch 2, 1024 tokens, lru_width 2560, 10 heads, document
+  starts at t = 0 and t = 512, no initial state; y and the final state against the oracle at 1e-5
+  (recurrentgemma torch/layers.py:313-365, 140-191)."""
+  from recurrentgemma_b200 import _lib
+  b, t, e, h = 2, 1024, 2560, 10
+  g = torch.Generator(device="cpu").manual_seed(0)
+  p = synthetic.rglru_params(e, h, g, torch.float32)
+  x = torch.randn((b, t, e), generator=g)
+  pos = torch.arange(t, dtype=torch.int64)
+  pos[512:] -= 512
+  pos = pos.repeat(b, 1)
+  m = _lru(rg, p, e, h, torch.float32)
+  y, h_last = m(x.to(DEV), pos.to(DEV))
+  _lib.workspace_status(_lib.workspace(torch.device(DEV), 1))
+  y_r, h_r = oracle.rglru(x, pos, p["a_param"], p["input_gate.w"], p["input_gate.b"], p["a_gate.w"],
+                          p["a_gate.b"], None)
+  assert_close(y, y_r, TOL[torch.float32], "y")
+  assert_close(h_last, h_r, TOL[torch.float32], "final state")
+  # the token after a document start sees nothing of the previous document
+  assert float(y[:, 512].abs().max()) <= float(y_r[:, 512].abs().max()) * (1 + 1e-5) + 1e-6
+
+
+@pytest.mark.parametrize("impl_name", ["GATES_FUSED", "GATES_FUSED_EXACT"])
+def test_long_scan_shard_vs_oracle(rg, oracle, impl_name):
+  """What one of eight GPUs runs in the long head-sharded scan: bfloat16 RG-LRU, batch 4, 65536
+  tokens, 2 heads of 256 channels, documents of geometric length (mean 2048).  512 time tiles per
+  sequence, carries resolved many tiles deep.  One (row, head) slice against the oracle; the
+  workspace status must stay clean (no bounded wait expired)."""
+  from recurrentgemma_b200 import _lib
+  b, t, e, h = 4, 65536, 512, 2
+  dt = torch.bfloat16
+  g = torch.Generator(device="cpu").manual_seed(3)
+  p = synthetic.rglru_params(e, h, g, dt)
+  x = torch.randn((b, t, e), generator=g).to(dt)
+  pos = synthetic.geometric_segment_pos(b, t, 2048.0, 5)
+  m = _lru(rg, p, e, h, dt)
+  m.gates_impl = getattr(_lib, impl_name)
+  y, h_last = m(x.to(DEV), pos.to(DEV))
+  _lib.workspace_status(_lib.workspace(torch.device(DEV), 1))
+  row, head = 2, 1
+  sl = slice(head * 256, (head + 1) * 256)
+  y_r, h_r = oracle.rglru(x[row:row + 1, :, sl].contiguous(), pos[row:row + 1], *_head_params(p, head),
+                          None)
+  assert_close(y[row:row + 1, :, sl], y_r, TOL[dt], "y slice")
+  assert_close(h_last[row:row + 1, sl], h_r, TOL[dt], "final state slice")
+
+
+def test_prefill_workload_slices_vs_oracle(rg, oracle):
+  """The prefill workload at full size (batch 8, 4096 tokens, 2560 channels, 10 heads, bfloat16, with
+  an initial state) through the fused kernel, against the oracle on two (row, head) slices, and the
+  share of output elements that differ from the oracle's bits."""
+  from recurrentgemma_b200 import _lib
+  b, t, e, h = 8, 4096, 2560, 10
+  dt = torch.bfloat16
+  g = torch.Generator(device="cpu").manual_seed(8)
+  p = synthetic.rglru_params(e, h, g, dt)
+  x = torch.randn((b, t, e), generator=g).to(dt)
+  h0 = torch.randn((b, e), generator=g) * 0.5
+  pos = synthetic.geometric_segment_pos(b, t, 1024.0, 9)
+  pos[:, 0] = 1                    # the first token continues a document: the initial state counts
+  m = _lru(rg, p, e, h, dt)
+  for impl, max_mismatch in ((_lib.GATES_FUSED, 0.6), (_lib.GATES_FUSED_EXACT, 0.01)):
+    m.gates_impl = impl
+    y, h_last = m(x.to(DEV), pos.to(DEV), h0.to(DEV))
+    _lib.workspace_status(_lib.workspace(torch.device(DEV), 1))
+    for row, head in ((0, 0), (7, 9)):
+      sl = slice(head * 256, (head + 1) * 256)
+      y_r, h_r = oracle.rglru(x[row:row + 1, :, sl].contiguous(), pos[row:row + 1],
+                              *_head_params(p, head), h0[row:row + 1, sl].contiguous())
+      assert_close(y[row:row + 1, :, sl], y_r, TOL[dt], f"y slice ({row}, {head})")
+      assert_close(h_last[row:row + 1, sl], h_r, TOL[dt], f"final state slice ({row}, {head})")
+      mismatch = float((y[row:row + 1, :, sl].cpu() != y_r).float().mean())
+      assert mismatch <= max_mismatch, (impl, mismatch)

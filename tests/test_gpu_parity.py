@@ -476,26 +476,32 @@ def test_fused_rglru_kernel(rg, oracle, shape):
   h0 = C.normal(case.name, "h0", (b, e), 0.5).to(DEV)
   yb = C.normal(case.name, "yb", (b, t, e), 1.0, dt).to(DEV)
   ws = _lib.workspace(torch.device(DEV), 1)
-  m.gates_impl = _lib.GATES_FUSED
-  y_f, h_f = m(x, pos, h0)
-  _lib.workspace_status(ws)
-  o_f, c_f = rg.recurrent_path(x, yb, pos, conv, m)
-  _lib.workspace_status(ws)
   m.gates_impl = _lib.GATES_TCGEN05
   y_u, h_u = m(x, pos, h0)
   o_u, c_u = rg.recurrent_path(x, yb, pos, conv, m)
   tol = TOL[dt]
-  assert_close(y_f, y_u, 5e-3, "fused vs two-kernel y")
-  assert_close(h_f, h_u, 5e-3, "fused vs two-kernel h")
-  assert_close(o_f, o_u, 5e-3, "fused vs two-kernel path out")
-  assert_close(c_f.rg_lru_state, c_u.rg_lru_state, 5e-3, "fused vs two-kernel path state")
-  assert float((y_f != y_u).float().mean()) < 0.02
+  y_r = None
   if b * t * e <= 8 << 20:
     y_r, h_r = oracle.rglru(inp["x"], inp["segment_pos"], p["rg_lru.a_param"],
                             p["rg_lru.input_gate.w"], p["rg_lru.input_gate.b"],
                             p["rg_lru.a_gate.w"], p["rg_lru.a_gate.b"], h0.cpu())
-    assert_close(y_f, y_r, tol, "fused vs oracle y")
-    assert_close(h_f, h_r, tol, "fused vs oracle h")
+  # GATES_FUSED_EXACT keeps every rounding of the reference: it must agree with the two-kernel route
+  # almost bit for bit.  GATES_FUSED evaluates the input gate and the gelu with packed tanh
+  # approximations: it is held to the path's tolerance (against the oracle where that is affordable).
+  for impl, cmp_tol, max_mismatch in ((_lib.GATES_FUSED_EXACT, 1e-2, 0.02), (_lib.GATES_FUSED, tol, 0.7)):
+    m.gates_impl = impl
+    y_f, h_f = m(x, pos, h0)
+    _lib.workspace_status(ws)
+    o_f, c_f = rg.recurrent_path(x, yb, pos, conv, m)
+    _lib.workspace_status(ws)
+    assert_close(y_f, y_u, cmp_tol, f"fused ({impl}) vs two-kernel y")
+    assert_close(h_f, h_u, cmp_tol, f"fused ({impl}) vs two-kernel h")
+    assert_close(o_f, o_u, cmp_tol, f"fused ({impl}) vs two-kernel path out")
+    assert_close(c_f.rg_lru_state, c_u.rg_lru_state, cmp_tol, f"fused ({impl}) vs two-kernel path state")
+    assert float((y_f != y_u).float().mean()) < max_mismatch
+    if y_r is not None:
+      assert_close(y_f, y_r, tol, f"fused ({impl}) vs oracle y")
+      assert_close(h_f, h_r, tol, f"fused ({impl}) vs oracle h")
   with pytest.raises(_lib.RgkError):      # head width other than 256
     m2 = rg.RGLRU(256, 2, device=DEV, dtype=dt)
     m2.gates_impl = _lib.GATES_FUSED
