@@ -12,12 +12,19 @@ region).  With N > 1 (torchrun, one process per GPU) every rank runs the whole w
 GPU - the path shards by batch without any collective - and `value` is the sum (weak scaling).
 
 `--impl reference` times the CPU restatement of the reference's own implementation of the same
-sub-path (oracle/, OpenMP over the host cores) on a bounded sample of the workload.
+sub-path (oracle/, OpenMP over all host cores) on the same workload, K steps after W warm-ups.
+
+The default line also carries the other workloads as extra keys, each a few hundred milliseconds:
+`long_scan` (RG-LRU at 9B dims, batch 4 x 65536 tokens, heads sharded over the N ranks, with and
+without the all_gather that reassembles the output), `decode_step` (26 decode layers, batch 256)
+and `rglru_fp32` (the float32 RG-LRU layer); `--headline-only` skips them.
 """
 from __future__ import annotations
 
 import argparse
+import hashlib
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -53,7 +60,6 @@ def _workload_name(cfg):
 # synthetic inputs (seeded; shapes and distributions of the workload)
 # ------------------------------------------------------------------------------------------------
 def make_params(cfg, device, seed):
-  import math
   g = torch.Generator(device="cpu").manual_seed(seed)
   e, h, w = cfg["lru_width"], cfg["heads"], cfg["conv_width"]
   bw = e // h
@@ -146,37 +152,69 @@ class ClockSampler:
 # ------------------------------------------------------------------------------------------------
 # CPU legs (the oracle: the reference's algorithm restated in C, OpenMP over the host cores)
 # ------------------------------------------------------------------------------------------------
-def cpu_leg(cfg, steps, warmup, sample_batch=1):
+def cpu_leg(cfg, steps, warmup, seed=1, gpu_out=None):
+  """Times oracle.recurrent_path on the WHOLE workload (all batch rows) with every host core, and
+  the linear scan alone in both reference forms (torch rnn_scan, JAX lru_linear_scan restated).
+  gpu_out: the CUDA path's output on the same inputs (CPU tensor) - the oracle then also serves as
+  the checker, and the leg reports the error and the share of elements whose bits differ."""
   from oracle import oracle
   oracle.lib()
-  p = make_params(cfg, "cpu", 1)
+  threads = oracle.set_threads(os.cpu_count() or 1)     # a launcher may have exported OMP_NUM_THREADS=1
+  torch.set_num_threads(max(1, os.cpu_count() or 1))
+  p = make_params(cfg, "cpu", seed)
   op = oracle.params_of(p)
-  xb, yb, pos = make_activations(cfg, "cpu", 1, batch=sample_batch)
+  xb, yb, pos = make_activations(cfg, "cpu", seed)
   times = []
+  out = None
   for i in range(warmup + steps):
     t0 = time.perf_counter()
-    oracle.recurrent_path(xb, yb, pos, op)
+    out, _, _ = oracle.recurrent_path(xb, yb, pos, op)
     if i >= warmup:
       times.append(time.perf_counter() - t0)
-  tokens = sample_batch * cfg["seq"]
-  best = min(times)
+  tokens = cfg["batch"] * cfg["seq"]
   mean = sum(times) / len(times)
-  return {
-      "value": tokens / mean, "best": tokens / best, "unit": UNIT, "cores": os.cpu_count(),
+  leg = {
+      "value": tokens / mean, "best": tokens / min(times), "unit": UNIT, "cores": threads,
       "kind": "port",
-      "sample": (f"oracle/rglru_oracle.c recurrent_path (OpenMP, {os.cpu_count()} threads) on "
-                 f"{sample_batch} of {cfg['batch']} batch rows x {cfg['seq']} tokens x "
-                 f"{cfg['lru_width']} channels, mean of {steps} after {warmup} warm-up"),
+      "sample": (f"oracle/rglru_oracle.c recurrent_path (OpenMP, {threads} threads of "
+                 f"{os.cpu_count()} host cores) on the whole workload: {cfg['batch']} batch rows x "
+                 f"{cfg['seq']} tokens x {cfg['lru_width']} channels, mean of {steps} after {warmup} "
+                 f"warm-up"),
       "seconds_per_sample": mean,
   }
+  # The recurrence alone, h_t = a_t h_{t-1} + x_t over the same [B, T, E] shape, in the torch
+  # reference's form (rnn_scan, torch/layers.py:140-191) and in the JAX reference's
+  # (lru_linear_scan, jax/scan.py:74-120), both restated in C: jax itself is not installed.
+  g = torch.Generator(device="cpu").manual_seed(seed + 7)
+  a = (torch.rand(xb.shape, generator=g) * 0.4 + 0.6).to(xb.dtype)
+  no_reset = torch.zeros(xb.shape[:2], dtype=torch.bool)
+  scan = {}
+  for name, fn in (("torch_rnn_scan_restatement", lambda: oracle.rnn_scan(xb, a, no_reset, None)),
+                   ("jax_linear_scan_restatement", lambda: oracle.jax_linear_scan(xb, a, None))):
+    fn()
+    t0 = time.perf_counter()
+    fn()
+    scan[name] = tokens / (time.perf_counter() - t0)
+  scan["unit"] = UNIT
+  scan["note"] = ("the recurrence alone on [B, T, E] bfloat16 inputs; the JAX figure is a C restatement of "
+                  "lru_linear_scan, the genuine JAX scan is unavailable on this box (jax is not installed)")
+  leg["linear_scan_only"] = scan
+  if gpu_out is not None:
+    o, r = gpu_out.float(), out.float()
+    leg["parity"] = {
+        "what": "CUDA path output against the oracle on the whole workload",
+        "normalised_max_error": float((o - r).abs().max() / r.abs().max().clamp_min(1e-30)),
+        "tolerance": 2e-2,
+        "fraction_of_elements_differing": float((gpu_out != out).float().mean()),
+    }
+  return leg
 
 
 def run_reference(args, cfg):
   rank = int(os.environ.get("RANK", "0"))
   if rank != 0:
     return
-  steps = max(1, min(args.steps, 5))
-  warmup = max(1, min(args.warmup, 1))
+  steps, warmup = max(1, args.steps), max(0, args.warmup)
   leg = cpu_leg(cfg, steps, warmup)
   line = {
       "impl": "reference", "metric": METRIC, "value": leg["value"], "unit": UNIT,
@@ -184,7 +222,8 @@ def run_reference(args, cfg):
       "ms_per_step": leg["seconds_per_sample"] * 1e3, "higher_is_better": True, "scaling": "weak",
       "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
       "config": {"workload": _workload_name(cfg), "step": leg["sample"]},
-      "cpu_baseline": {k: leg[k] for k in ("value", "unit", "cores", "kind", "sample")},
+      "cpu_baseline": {k: leg[k] for k in ("value", "unit", "cores", "kind", "sample",
+                                            "linear_scan_only")},
       "e2e": {"value": leg["value"], "unit": UNIT, "h2d_bytes_per_step": 0,
               "d2h_bytes_per_step": 0},
   }
@@ -251,6 +290,18 @@ def run_gpu(args, cfg):
     step()
   torch.cuda.synchronize()
   _lib.workspace_status(_lib.workspace(dev, 1))
+  # A step is `passes` back-to-back passes of the path over the batch, so that the timed region of
+  # K steps lasts at least a quarter of a second whatever K is.
+  est_ms = _time_loop(step, 5, stream)
+  passes = max(1, int(math.ceil(250.0 / (max(args.steps, 1) * est_ms))))
+  if world > 1:
+    pt = torch.tensor([passes], device=dev)
+    dist.all_reduce(pt, op=dist.ReduceOp.MAX)
+    passes = int(pt.item())
+
+  def timed_step():
+    for _ in range(passes):
+      step()
 
   clocks = ClockSampler(local)
   if rank == 0:
@@ -258,19 +309,21 @@ def run_gpu(args, cfg):
   if world > 1:
     dist.barrier()
   torch.cuda.synchronize()
-  ms = _time_loop(step, args.steps, stream)
+  ms = _time_loop(timed_step, args.steps, stream)
   torch.cuda.synchronize()
+  _lib.workspace_status(_lib.workspace(dev, 1))
   if world > 1:
     tmax = torch.tensor([ms], device=dev)
     dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
     dist.barrier()
     ms = float(tmax.item())
   clk = clocks.stop() if rank == 0 else None
+  ms_pass = ms / passes
 
   # end to end through the public API, host buffers
   e2e_ms = None
   if not args.no_e2e:
-    e2e_steps = max(2, min(args.steps, 10))
+    e2e_steps = max(2, min(max(args.steps, 30), 60))
     for _ in range(2):
       step_e2e()
     torch.cuda.synchronize()
@@ -285,6 +338,16 @@ def run_gpu(args, cfg):
       tmax = torch.tensor([e2e_ms], device=dev)
       dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
       e2e_ms = float(tmax.item())
+
+  # The long head-sharded scan: every rank takes part (heads split over the ranks).
+  long_scan = None
+  if not args.headline_only:
+    del xb, yb, out
+    torch.cuda.empty_cache()
+    long_scan = long_scan_leg(dev, rank, world, steps=10, warmup=3)
+    xb, yb = xb_h.to(dev), yb_h.to(dev)
+    out = torch.empty_like(xb)
+    step()
 
   # Per-kernel device times: each stage through its own C-ABI entry point on preallocated buffers,
   # CUDA events on the launch stream (torch's current stream is the stream the library is given).
@@ -350,7 +413,6 @@ def run_gpu(args, cfg):
 
     # The whole RecurrentBlock at the same shapes: the three projections on the
     # tcgen05 GEMM around the sub-path, one library call.
-    import math
     gb = torch.Generator(device="cpu").manual_seed(77)
     blk = rg.RecurrentBlock(e, h, e, device=dev, dtype=dt)
     sd = dict(p)
@@ -448,74 +510,222 @@ def run_gpu(args, cfg):
   hbm_gbs, bf16_tf, which = _peaks()
   block_info["linear_frac_of_bf16_peak"] = block_info["linear_TFLOP/s"] / bf16_tf
   tokens = b * t
-  value = world * tokens / (ms * 1e-3)
+  value = world * tokens * passes / (ms * 1e-3)
   for k in kernels.values():
     k["gbs"] = k["bytes"] / (k["ms"] * 1e-3) / 1e9
     k["tflops"] = k["flops"] / (k["ms"] * 1e-3) / 1e12
-  # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of each kernel at this
-  # workload, from the ncu captures summarised in profiles/ncu_full_cfg1_path_kernels.md and
-  # profiles/ncu_full_cfg1_rglru_chan_kernel.md.
-  ncu_traffic = {"conv1d_prefill": 288.3e6, "rglru_fused": 490.1e6}
   dom_name = max(kernels, key=lambda k: kernels[k]["ms"])
   dom = kernels[dom_name]
   path_bytes = 3 * b * t * e * 2 + 2 * p["rg_lru.input_gate.w"].numel() * 2
+  sfu_ops = 5.5     # per element: tanh (input gate), ex2 + half a rcp (recurrence gate), ex2, sqrt, tanh (gelu)
   roofline = {
       "bound": "hbm", "kernel": dom_name, "achieved": dom["gbs"], "peak": hbm_gbs, "unit": "GB/s",
       "frac": dom["gbs"] / hbm_gbs, "peak_source": which,
-      "traffic": ncu_traffic.get(dom_name) if cfg["batch"] == CFG1["batch"] else None,
+      "traffic": _recorded_traffic(dom_name) if cfg["batch"] == CFG1["batch"] else None,
       "algorithmic_bytes": dom["bytes"],
-      "path": {"algorithmic_bytes": path_bytes, "achieved": path_bytes / (ms * 1e-3) / 1e9,
-               "frac": path_bytes / (ms * 1e-3) / 1e9 / hbm_gbs,
-               "frac_of_nominal_8TBs": path_bytes / (ms * 1e-3) / 1e9 / 8000.0},
+      "path": {"algorithmic_bytes": path_bytes, "achieved": path_bytes / (ms_pass * 1e-3) / 1e9,
+               "frac": path_bytes / (ms_pass * 1e-3) / 1e9 / hbm_gbs,
+               "frac_of_nominal_8TBs": path_bytes / (ms_pass * 1e-3) / 1e9 / 8000.0},
       "kernels": {k: {"ms": round(v["ms"], 4), "GB/s": round(v["gbs"], 1),
                       "TFLOP/s": round(v["tflops"], 2)} for k, v in kernels.items()},
       "two_kernel_route": {k: round(v, 4) for k, v in two_kernel.items()},
-      # what actually bounds the fused kernel: special-function operations (4 ex2, 2 rcp, 1 sqrt per
-      # element; 16 per SM and clock) and instruction issue, see profiles/
-      "sfu": {"ops_per_element": 7, "achieved_Gops": 7 * b * t * e / (kernels["rglru_fused"]["ms"] * 1e-3) / 1e9
-              if "rglru_fused" in kernels else None,
+      "sfu": {"ops_per_element": sfu_ops,
+              "achieved_Gops": sfu_ops * b * t * e / (kernels["rglru_fused"]["ms"] * 1e-3) / 1e9,
               "peak_Gops": 148 * 16 * 1.965, "unit": "G special-function ops/s",
-              "frac": (7 * b * t * e / (kernels["rglru_fused"]["ms"] * 1e-3) / 1e9) / (148 * 16 * 1.965)
-              if "rglru_fused" in kernels else None},
-      "note": ("rglru_fused is bounded by the SFU and issue pipes (7 SFU operations and ~63 "
-               "instructions per element with the reference's bfloat16 roundings), not by HBM; "
-               "frac is its algorithmic bytes over its time against the measured copy bandwidth"),
+              "frac": (sfu_ops * b * t * e / (kernels["rglru_fused"]["ms"] * 1e-3) / 1e9) / (148 * 16 * 1.965)},
+      "note": ("rglru_fused is bounded by instruction issue and the special-function pipe (about 55 "
+               "instructions and 5.5 special-function operations per element), not by HBM; frac is "
+               "its algorithmic bytes over its time against the measured copy bandwidth"),
   }
-  cpu = None if args.no_cpu else cpu_leg(cfg, 2, 1)
+  cpu = None
+  if not args.no_cpu:
+    step()
+    torch.cuda.synchronize()
+    cpu = cpu_leg(cfg, 2, 1, seed=1 + rank, gpu_out=out.cpu())
   line = {
       "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
       "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
       "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
       "config": {"workload": _workload_name(cfg), "per_gpu_batch": b, "seq_len": t,
+                 "passes_per_step": passes, "ms_per_pass": ms_pass,
+                 "step": f"{passes} passes of the path over the batch (timed region {ms * args.steps / 1e3:.2f} s)",
                  "parallelism": f"batch-sharded x{world}, no collective",
                  "cache": "inputs (336 MB) larger than L2 (126 MB); no flush"},
       "roofline": roofline,
       "cpu_baseline": None if cpu is None else {k: cpu[k] for k in
-                                                ("value", "unit", "cores", "kind", "sample")},
+                                                ("value", "unit", "cores", "kind", "sample",
+                                                 "linear_scan_only", "parity")},
       "block_prefill": block_info,
       "clocks": clk,
-      "gpu_launches": 3 * args.steps,
+      # per pass: the conv kernel, the per-channel constant kernel and the fused RG-LRU kernel
+      "gpu_launches": 3 * passes * args.steps,
   }
+  if long_scan is not None:
+    line["long_scan"] = long_scan
+  if not args.headline_only:
+    line["decode_step"] = decode_leg(dev, steps=50)
+    line["rglru_fp32"] = rglru_fp32_leg(dev, steps=50)
   if e2e_ms is not None:
+    h2d = 2 * b * t * e * 2
     line["e2e"] = {"value": world * tokens / (e2e_ms * 1e-3), "unit": UNIT,
-                   "h2d_bytes_per_step": 2 * b * t * e * 2, "d2h_bytes_per_step": b * t * e * 2 + b * e * 4,
-                   "ms_per_step": e2e_ms}
+                   "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": b * t * e * 2 + b * e * 4,
+                   "ms_per_step": e2e_ms, "steps": e2e_steps,
+                   # both copy directions overlap; the larger one, host to device, sets the time
+                   "bound": "pcie_h2d", "h2d_GB/s_per_gpu": h2d / (e2e_ms * 1e-3) / 1e9}
   print(json.dumps(line), flush=True)
   if world > 1:
     dist.destroy_process_group()
 
 
+def _recorded_traffic(kernel: str):
+  """DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of a kernel at the
+  headline workload, from the record of ncu captures kept beside the summaries - but only if the
+  kernel's source file still has the checksum it had when the capture was made; else None."""
+  path = os.path.join(ROOT, "profiles", "dram_traffic.json")
+  try:
+    with open(path) as f:
+      rec = json.load(f).get(kernel)
+    if rec is None:
+      return None
+    with open(os.path.join(ROOT, rec["source"]), "rb") as f:
+      sha = hashlib.sha256(f.read()).hexdigest()
+    return float(rec["dram_bytes_per_launch"]) if sha == rec["source_sha256"] else None
+  except (OSError, KeyError, ValueError):
+    return None
+
+
+# ------------------------------------------------------------------------------------------------
+# secondary workloads carried as extra keys of the default line
+# ------------------------------------------------------------------------------------------------
+def long_scan_leg(dev, rank, world, steps, warmup, seq=65536, gather=True):
+  """RG-LRU forward (gate projections + gate arithmetic + scan) at 9B dims: lru_width 4096, 16
+  heads, batch 4, `seq` tokens, bfloat16, documents of geometric length (mean 2048).  Rank r owns
+  heads [16 r / N, 16 (r+1) / N): strong scaling with no collective inside the path.  Timed twice:
+  the path alone, and with the all_gather that reassembles the [B, T, E] output on every rank inside
+  the timed region.  Returns the dictionary on rank 0, None elsewhere."""
+  import ctypes
+  import torch.distributed as dist
+  import recurrentgemma_b200 as rg
+  from recurrentgemma_b200 import _lib, sharding, synthetic
+  b, t, e, h = 4, seq, 4096, 16
+  dt = torch.bfloat16
+  if h % world != 0:
+    return {"unavailable": f"16 heads do not split over {world} ranks"} if rank == 0 else None
+  cfg = dict(batch=b, seq=t, lru_width=e, heads=h, conv_width=4)
+  p = make_params(cfg, "cpu", 3)
+  h0, h1 = sharding.head_range(h, world, rank)
+  e_loc = (h1 - h0) * (e // h)
+  pl = {k: v.to(dev) for k, v in sharding.shard_state_dict(p, e, h, world, rank).items()}
+  lru = rg.RGLRU(e_loc, h1 - h0, device=dev, dtype=dt)
+  lru.load_state_dict({k[len("rg_lru."):]: v for k, v in pl.items() if k.startswith("rg_lru.")})
+  gen = torch.Generator(device=dev).manual_seed(11 + rank)
+  x = torch.randn((b, t, e_loc), generator=gen, device=dev, dtype=torch.float32).to(dt)
+  pos = synthetic.geometric_segment_pos(b, t, 2048.0, 5).to(dev)
+  y = torch.empty_like(x)
+  full = torch.empty((world, b, t, e_loc), dtype=dt, device=dev) if world > 1 else None
+  h_last = torch.empty((b, e_loc), dtype=torch.float32, device=dev)
+  lib = _lib.load()
+  ws = _lib.workspace(dev, _lib.workspace_bytes(b, t, e_loc, dt))
+  prm = lru._params()
+  stream = torch.cuda.current_stream(dev)
+
+  def path():
+    _lib.check(lib.rgk_rglru_forward(x.data_ptr(), pos.data_ptr(), _lib.RGK_I64, ctypes.byref(prm),
+                                     None, b, t, e_loc, h1 - h0, _lib.RGK_BF16, lru.gates_impl,
+                                     y.data_ptr(), h_last.data_ptr(), ws.data_ptr(), ws.numel(),
+                                     stream.cuda_stream))
+
+  def path_and_gather():
+    path()
+    if world > 1:
+      dist.all_gather_into_tensor(full, y)     # [N, B, T, E/N]: slice r holds rank r's channels
+
+  def timed(fn):
+    for _ in range(warmup):
+      fn()
+    torch.cuda.synchronize()
+    _lib.workspace_status(ws)
+    if world > 1:
+      dist.barrier()
+    torch.cuda.synchronize()
+    ms = _time_loop(fn, steps, stream)
+    torch.cuda.synchronize()
+    if world > 1:
+      tmax = torch.tensor([ms], device=dev)
+      dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+      ms = float(tmax.item())
+    return ms
+
+  ms_path = timed(path)
+  ms_gather = timed(path_and_gather) if (gather and world > 1) else ms_path
+  del x, y, full
+  torch.cuda.empty_cache()
+  if rank != 0:
+    return None
+  hbm, _, which = _peaks()
+  alg = (2 * b * t * e * 2 + 2 * h * 256 * 256 * 2 + b * t * 8) / world   # per GPU
+  recv = (world - 1) * b * t * e_loc * 2                                   # bytes a rank receives
+  return {
+      "workload": f"cfg3: RG-LRU forward B{b} T{t} E{e} H{h} bf16, geometric documents (mean 2048), "
+                  f"heads sharded x{world}",
+      "scaling": "strong", "n_gpus": world, "steps": steps,
+      "ms_per_step": ms_path, "tokens_per_s": b * t / (ms_path * 1e-3),
+      "roofline": {"bound": "hbm", "algorithmic_bytes_per_gpu": alg,
+                   "achieved": alg / (ms_path * 1e-3) / 1e9, "peak": hbm, "unit": "GB/s",
+                   "frac": alg / (ms_path * 1e-3) / 1e9 / hbm, "peak_source": which},
+      "with_gather": {
+          "ms_per_step": ms_gather, "tokens_per_s": b * t / (ms_gather * 1e-3),
+          "collective": "all_gather_into_tensor of the [B, T, E/N] outputs (NCCL), inside the timed region",
+          "bytes_received_per_gpu": recv,
+          # what the reassembly alone costs at the measured peer bandwidth of this pool (770 GB/s
+          # per direction per GPU): the floor of this leg whatever the scan does
+          "nvlink_floor_ms": recv / 770e9 * 1e3,
+      },
+  }
+
+
+def rglru_fp32_leg(dev, steps):
+  """The float32 RG-LRU layer (batch 2, 1024 tokens, lru_width 2560, 10 heads, document starts at 0
+  and 512): microseconds per forward, against its HBM bound (x in, y out, gate weights) and against
+  the float32-accurate gate contraction it is actually bound by."""
+  import recurrentgemma_b200 as rg
+  from recurrentgemma_b200 import synthetic
+  b, t, e, h = 2, 1024, 2560, 10
+  g = torch.Generator(device="cpu").manual_seed(0)
+  p = synthetic.rglru_params(e, h, g, torch.float32)
+  m = rg.RGLRU(e, h, device=dev, dtype=torch.float32)
+  m.load_state_dict(p)
+  x = torch.randn((b, t, e), generator=g).to(dev)
+  pos = torch.arange(t, dtype=torch.int64)
+  pos[512:] -= 512
+  pos = pos.repeat(b, 1).to(dev)
+  for _ in range(3):
+    m(x, pos)
+  torch.cuda.synchronize()
+  ms = _time_loop(lambda: m(x, pos), steps, torch.cuda.current_stream(dev))
+  hbm, _, which = _peaks()
+  alg = 2 * b * t * e * 4 + 2 * h * 256 * 256 * 4
+  flops = 2 * 2 * b * t * e * 256
+  return {"workload": "cfg0: RGLRU.forward float32 B2 T1024 E2560 H10, resets at 0 and 512",
+          "us_per_forward": ms * 1e3, "tokens_per_s": b * t / (ms * 1e-3),
+          "roofline": {"bound": "hbm", "algorithmic_bytes": alg, "achieved": alg / (ms * 1e-3) / 1e9,
+                       "peak": hbm, "unit": "GB/s", "frac": alg / (ms * 1e-3) / 1e9 / hbm,
+                       "peak_source": which},
+          "gate_contraction": {"flops": flops, "achieved_TFLOP/s": flops / (ms * 1e-3) / 1e12,
+                               "note": "float32-accurate FMA on the CUDA cores (no float32 tensor-core "
+                                       "mode meets the 1e-5 bar in one pass)"}}
+
+
 # ------------------------------------------------------------------------------------------------
 # cfg2: single-token decode step of the recurrent path through 26 layers (secondary workload)
 # ------------------------------------------------------------------------------------------------
-def run_decode(args):
+def decode_leg(dev, steps):
   """Per-step latency of 26 back-to-back RG-LRU + Conv1D decode steps at 2B dims (batch 256,
   lru_width 2560, 10 heads, bf16, cached conv window and fp32 state), layer i feeding layer i+1,
-  replayed from a CUDA graph (one kernel per layer).  Prints one JSON line."""
+  replayed from a CUDA graph (one kernel per layer), and the same with the block's three dense
+  projections around every step.  Returns the dictionary of results."""
   import recurrentgemma_b200 as rg
   from recurrentgemma_b200 import _lib, modules
-  dev = torch.device("cuda", 0)
-  torch.cuda.set_device(dev)
   dt = torch.bfloat16
   b, e, h, n_layers = 256, CFG1["lru_width"], CFG1["heads"], 26
   layers = []
@@ -545,10 +755,10 @@ def run_decode(args):
     step()
   torch.cuda.synchronize()
   t0 = time.perf_counter()
-  for _ in range(args.steps):
+  for _ in range(steps):
     step()
   torch.cuda.synchronize()
-  eager_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+  eager_ms = (time.perf_counter() - t0) * 1e3 / steps
   graph = torch.cuda.CUDAGraph()
   side = torch.cuda.Stream()
   with torch.cuda.stream(side):
@@ -560,12 +770,11 @@ def run_decode(args):
   for _ in range(3):
     graph.replay()
   torch.cuda.synchronize()
-  graph_ms = _time_loop(graph.replay, args.steps, torch.cuda.current_stream())
+  graph_ms = _time_loop(graph.replay, steps, torch.cuda.current_stream())
 
   # The full-RecurrentBlock variant of the same step: linear_x / linear_y / linear_out as library
   # GEMMs (M = batch is too small for the 128 x 256 tensor-core tiles) around the fused kernel,
   # 26 blocks captured in one CUDA graph.
-  import math
   blocks = []
   for i, (conv, lru, cache, _) in enumerate(layers):
     blk = rg.RecurrentBlock(e, h, e, device=dev, dtype=dt)
@@ -594,42 +803,41 @@ def run_decode(args):
   for _ in range(3):
     graph_b.replay()
   torch.cuda.synchronize()
-  block_ms = _time_loop(graph_b.replay, args.steps, torch.cuda.current_stream())
+  block_ms = _time_loop(graph_b.replay, steps, torch.cuda.current_stream())
   block_bytes = n_layers * 3 * e * e * 2
   path_bytes = n_layers * (2 * b * e * 2 + b * e * 2 + 2 * b * 3 * e * 2 + 2 * b * e * 4 +
                            2 * 256 * e * 2)
   hbm, _, which = _peaks()
-  print(json.dumps({
+  return {
       "metric": "recurrent_path_decode_step_latency", "value": graph_ms, "unit": "ms",
-      "higher_is_better": False, "n_gpus": 1, "steps": args.steps, "dtype": "bf16",
+      "higher_is_better": False, "n_gpus": 1, "steps": steps, "dtype": "bf16",
       "data": "synthetic",
       "config": {"workload": "cfg2: RG-LRU+Conv1D decode step x26 layers, B256 E2560 H10 bf16, "
                              "CUDA-graph replay, one fused kernel per layer"},
       "eager_python_ms": eager_ms, "tokens_per_s": b / (graph_ms * 1e-3),
-      "full_block": {"ms": block_ms, "what": "RecurrentBlock.forward decode x26 (library GEMMs for "
-                     "the three projections around the fused kernel), CUDA-graph replay",
+      "full_block": {"ms": block_ms, "what": "RecurrentBlock.forward decode x26 (the three "
+                     "projections around the fused kernel), CUDA-graph replay",
                      "algorithmic_bytes": path_bytes + block_bytes,
-                     "GB/s": (path_bytes + block_bytes) / (block_ms * 1e-3) / 1e9},
+                     "GB/s": (path_bytes + block_bytes) / (block_ms * 1e-3) / 1e9,
+                     "frac": (path_bytes + block_bytes) / (block_ms * 1e-3) / 1e9 / hbm},
       "roofline": {"bound": "hbm", "algorithmic_bytes": path_bytes,
                    "achieved": path_bytes / (graph_ms * 1e-3) / 1e9, "peak": hbm, "unit": "GB/s",
                    "frac": path_bytes / (graph_ms * 1e-3) / 1e9 / hbm, "peak_source": which},
-      "gpu_launches": n_layers * args.steps}), flush=True)
+      "gpu_launches": n_layers * steps}
+
+
+def run_decode(args):
+  dev = torch.device("cuda", 0)
+  torch.cuda.set_device(dev)
+  print(json.dumps(decode_leg(dev, args.steps)), flush=True)
 
 
 # ------------------------------------------------------------------------------------------------
 # cfg3: long-sequence RG-LRU at 9B dims, channels sharded by whole heads (secondary workload)
 # ------------------------------------------------------------------------------------------------
 def run_long_scan(args):
-  """RG-LRU forward (gate projections + gate arithmetic + scan) at 9B dims: lru_width 4096, 16
-  heads, batch 4, 65536 tokens, bf16, documents of geometric length (mean 2048).  With N ranks
-  (torchrun) rank r owns heads [16 r / N, 16 (r+1) / N): strong scaling, no collective inside the
-  path; the timed region ends with the all_gather that reassembles the output when --gather is
-  given.  Prints one JSON line on rank 0."""
+  """The long head-sharded scan alone (see long_scan_leg); one JSON line on rank 0."""
   import torch.distributed as dist
-  import ctypes
-  import recurrentgemma_b200 as rg
-  from recurrentgemma_b200 import _lib, sharding
-  from tests import cases as C
   rank = int(os.environ.get("RANK", "0"))
   world = int(os.environ.get("WORLD_SIZE", "1"))
   local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -637,60 +845,13 @@ def run_long_scan(args):
   dev = torch.device("cuda", local)
   if world > 1:
     dist.init_process_group("nccl", device_id=dev)
-  b, t, e, h = 4, args.seq or 65536, 4096, 16
-  dt = torch.bfloat16
-  cfg = dict(batch=b, seq=t, lru_width=e, heads=h, conv_width=4)
-  p = make_params(cfg, "cpu", 3)
-  h0, h1 = sharding.head_range(h, world, rank)
-  e_loc = (h1 - h0) * (e // h)
-  pl = {k: v.to(dev) for k, v in sharding.shard_state_dict(p, e, h, world, rank).items()}
-  lru = rg.RGLRU(e_loc, h1 - h0, device=dev, dtype=dt)
-  lru.load_state_dict({k[len("rg_lru."):]: v for k, v in pl.items() if k.startswith("rg_lru.")})
-  gen = torch.Generator(device=dev).manual_seed(11 + rank)
-  x = torch.randn((b, t, e_loc), generator=gen, device=dev, dtype=torch.float32).to(dt)
-  pos = C.geometric_segment_pos(b, t, 2048.0, 5).to(dev)
-  y = torch.empty_like(x)
-  h_last = torch.empty((b, e_loc), dtype=torch.float32, device=dev)
-  lib = _lib.load()
-  ws = _lib.workspace(dev, _lib.workspace_bytes(b, t, e_loc, dt))
-  prm = lru._params()
-  stream = torch.cuda.current_stream(dev)
-
-  def step():
-    _lib.check(lib.rgk_rglru_forward(x.data_ptr(), pos.data_ptr(), _lib.RGK_I64, ctypes.byref(prm),
-                                     None, b, t, e_loc, h1 - h0, _lib.RGK_BF16, lru.gates_impl,
-                                     y.data_ptr(), h_last.data_ptr(), ws.data_ptr(), ws.numel(),
-                                     stream.cuda_stream))
-    if args.gather and world > 1:
-      sharding.gather_channels(y)
-
-  for _ in range(max(args.warmup, 3)):
-    step()
-  torch.cuda.synchronize()
-  _lib.workspace_status(ws)
-  if world > 1:
-    dist.barrier()
-  torch.cuda.synchronize()
-  ms = _time_loop(step, args.steps, stream)
-  torch.cuda.synchronize()
-  if world > 1:
-    tmax = torch.tensor([ms], device=dev)
-    dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
-    ms = float(tmax.item())
+  leg = long_scan_leg(dev, rank, world, steps=args.steps, warmup=max(args.warmup, 3),
+                      seq=args.seq or 65536, gather=True)
   if rank == 0:
-    hbm, _, which = _peaks()
-    alg = (2 * b * t * e * 2 + 2 * h * 256 * 256 * 2 + b * t * 8) / world   # per GPU
-    print(json.dumps({
-        "metric": "rglru_long_scan_tokens_per_s", "value": b * t / (ms * 1e-3), "unit": "tokens/s",
-        "n_gpus": world, "steps": args.steps, "ms_per_step": ms, "higher_is_better": True,
-        "scaling": "strong", "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"cfg3: RG-LRU forward B{b} T{t} E{e} H{h} bf16, geometric documents "
-                               f"(mean 2048), heads sharded x{world}",
-                   "gather_output": bool(args.gather)},
-        "roofline": {"bound": "hbm", "algorithmic_bytes_per_gpu": alg,
-                     "achieved": alg / (ms * 1e-3) / 1e9, "peak": hbm, "unit": "GB/s",
-                     "frac": alg / (ms * 1e-3) / 1e9 / hbm, "peak_source": which},
-        "gpu_launches": 3 * args.steps}), flush=True)
+    leg.update({"metric": "rglru_long_scan_tokens_per_s", "value": leg["tokens_per_s"],
+                "unit": "tokens/s", "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+                "gpu_launches": 3 * args.steps})
+    print(json.dumps(leg), flush=True)
   if world > 1:
     dist.destroy_process_group()
 
@@ -800,15 +961,16 @@ def main():
                        "(long head-sharded scan) or cfg4 (the whole 2B model: prompt + greedy decode)")
   ap.add_argument("--seq", type=int, default=None,
                   help="cfg3: sequence length (default 65536); cfg4: prompt length (default 2048)")
-  ap.add_argument("--gather", action="store_true", help="cfg3: all_gather the output every step")
   ap.add_argument("--gen-steps", type=int, default=512, help="cfg4: greedy decode steps (default 512)")
   ap.add_argument("--gpus", type=int, default=1)
-  ap.add_argument("--steps", type=int, default=600)
+  ap.add_argument("--steps", type=int, default=20)
   ap.add_argument("--warmup", type=int, default=3)
   ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
   ap.add_argument("--batch", type=int, default=None, help="override the per-GPU batch (profiling)")
   ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
   ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg")
+  ap.add_argument("--headline-only", action="store_true",
+                  help="cfg1: skip the long_scan / decode_step / rglru_fp32 legs")
   args = ap.parse_args()
   cfg = dict(CFG1)
   if args.batch:

@@ -42,6 +42,8 @@ def lib() -> ctypes.CDLL:
     build()
     _lib = ctypes.CDLL(_LIB_PATH)
     _lib.rgo_version.restype = ctypes.c_int
+    _lib.rgo_set_threads.restype = ctypes.c_int
+    _lib.rgo_max_threads.restype = ctypes.c_int
     _lib.rgo_rglru.restype = ctypes.c_int
     _lib.rgo_recurrent_path.restype = ctypes.c_int
     _lib.rgo_recurrent_block.restype = ctypes.c_int
@@ -50,6 +52,12 @@ def lib() -> ctypes.CDLL:
     _lib.rgo_attention_block.restype = ctypes.c_int
     _lib.rgo_residual_channel.restype = ctypes.c_int
   return _lib
+
+
+def set_threads(n: int) -> int:
+  """Sets the OpenMP thread count of the oracle's loops (n <= 0: leave it) and returns the count in
+  force.  Timed baselines call this: a launcher may have exported OMP_NUM_THREADS=1."""
+  return int(lib().rgo_set_threads(int(n)))
 
 
 def _mode(t: torch.Tensor) -> int:

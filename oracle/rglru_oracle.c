@@ -64,7 +64,22 @@ static inline float gelu_tanhf_(float z) {
   return 0.5f * z * (1.0f + tanhf(inner));
 }
 
-RGO_API int rgo_version(void) { return 4; }
+RGO_API int rgo_version(void) { return 5; }
+
+/* OpenMP thread count of the parallel loops below.  A launcher may have exported OMP_NUM_THREADS=1
+ * to every process it starts (torch.distributed.run does), so a timed baseline sets the count
+ * itself and reports what the runtime then gives.  Without OpenMP both return 1. */
+#ifdef _OPENMP
+#include <omp.h>
+RGO_API int rgo_set_threads(int n) {
+  if (n > 0) omp_set_num_threads(n);
+  return omp_get_max_threads();
+}
+RGO_API int rgo_max_threads(void) { return omp_get_max_threads(); }
+#else
+RGO_API int rgo_set_threads(int n) { (void)n; return 1; }
+RGO_API int rgo_max_threads(void) { return 1; }
+#endif
 
 /* ---------------------------------------------------------------------------------------------
  * BlockDiagonalLinear.forward, layers.py:127-137.

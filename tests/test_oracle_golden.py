@@ -155,3 +155,31 @@ def test_prefill_state_equals_decode_state(oracle):
   assert keep.any()
   assert_close(h_b[keep], h_full[keep], 1e-6, "state")
   assert_close(y_b[keep], y_full[keep][:, -1:], 1e-6, "last output")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+def test_jax_linear_scan_restatement_equals_rnn_scan(oracle, dtype):
+  """The restatement of the JAX reference's lru_linear_scan (jax/scan.py:74-120: a vmapped lax.scan
+  of h = a h + x in the accumulation dtype, outputs cast to the input dtype) computes what the torch
+  reference's rnn_scan computes once the reset mask is folded into a (torch/layers.py:166-168)."""
+  b, t, e = 3, 97, 130
+  x = C.normal("jaxscan", "x", (b, t, e), 1.0, dtype)
+  a = C.uniform("jaxscan", "a", (b, t, e), 0.3, 0.999).to(dtype)
+  h0 = C.normal("jaxscan", "h0", (b, e), 0.5)
+  reset = C.make_segment_pos("multi", b, t, "jaxscan") == 0
+  y_t, h_t = oracle.rnn_scan(x, a, reset, h0)
+  a_masked = (a.float() * (~reset)[..., None].float()).to(dtype)
+  y_j, h_j = oracle.jax_linear_scan(x, a_masked, h0)
+  assert torch.equal(y_t, y_j)
+  assert torch.equal(h_t, h_j)
+
+
+def test_thread_count_is_settable(oracle):
+  """Timed baselines set the OpenMP thread count themselves (a launcher may export
+  OMP_NUM_THREADS=1): the oracle reports the count in force."""
+  import os
+  before = oracle.set_threads(0)
+  assert before >= 1
+  want = min(2, os.cpu_count() or 1)
+  assert oracle.set_threads(want) in (want, 1)      # 1: built without OpenMP
+  oracle.set_threads(before)
