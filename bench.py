@@ -597,12 +597,13 @@ def _recorded_traffic(kernel: str):
 # ------------------------------------------------------------------------------------------------
 # secondary workloads carried as extra keys of the default line
 # ------------------------------------------------------------------------------------------------
-def long_scan_leg(dev, rank, world, steps, warmup, seq=65536, gather=True):
+def long_scan_leg(dev, rank, world, steps, warmup, seq=65536, gather=True, shard_of=0):
   """RG-LRU forward (gate projections + gate arithmetic + scan) at 9B dims: lru_width 4096, 16
   heads, batch 4, `seq` tokens, bfloat16, documents of geometric length (mean 2048).  Rank r owns
   heads [16 r / N, 16 (r+1) / N): strong scaling with no collective inside the path.  Timed twice:
   the path alone, and with the all_gather that reassembles the [B, T, E] output on every rank inside
-  the timed region.  Returns the dictionary on rank 0, None elsewhere."""
+  the timed region.  shard_of = N > 0 (single process): time what ONE of N GPUs would run, with no
+  collective - for development on one GPU.  Returns the dictionary on rank 0, None elsewhere."""
   import ctypes
   import torch.distributed as dist
   import recurrentgemma_b200 as rg
@@ -613,9 +614,10 @@ def long_scan_leg(dev, rank, world, steps, warmup, seq=65536, gather=True):
     return {"unavailable": f"16 heads do not split over {world} ranks"} if rank == 0 else None
   cfg = dict(batch=b, seq=t, lru_width=e, heads=h, conv_width=4)
   p = make_params(cfg, "cpu", 3)
-  h0, h1 = sharding.head_range(h, world, rank)
+  parts = shard_of if (shard_of and world == 1) else world
+  h0, h1 = sharding.head_range(h, parts, rank)
   e_loc = (h1 - h0) * (e // h)
-  pl = {k: v.to(dev) for k, v in sharding.shard_state_dict(p, e, h, world, rank).items()}
+  pl = {k: v.to(dev) for k, v in sharding.shard_state_dict(p, e, h, parts, rank).items()}
   lru = rg.RGLRU(e_loc, h1 - h0, device=dev, dtype=dt)
   lru.load_state_dict({k[len("rg_lru."):]: v for k, v in pl.items() if k.startswith("rg_lru.")})
   gen = torch.Generator(device=dev).manual_seed(11 + rank)
@@ -663,11 +665,11 @@ def long_scan_leg(dev, rank, world, steps, warmup, seq=65536, gather=True):
   if rank != 0:
     return None
   hbm, _, which = _peaks()
-  alg = (2 * b * t * e * 2 + 2 * h * 256 * 256 * 2 + b * t * 8) / world   # per GPU
+  alg = (2 * b * t * e * 2 + 2 * h * 256 * 256 * 2 + b * t * 8) / parts   # per GPU
   recv = (world - 1) * b * t * e_loc * 2                                   # bytes a rank receives
   return {
       "workload": f"cfg3: RG-LRU forward B{b} T{t} E{e} H{h} bf16, geometric documents (mean 2048), "
-                  f"heads sharded x{world}",
+                  f"heads sharded x{parts}" + (" (one shard timed on one GPU)" if parts != world else ""),
       "scaling": "strong", "n_gpus": world, "steps": steps,
       "ms_per_step": ms_path, "tokens_per_s": b * t / (ms_path * 1e-3),
       "roofline": {"bound": "hbm", "algorithmic_bytes_per_gpu": alg,
@@ -846,7 +848,7 @@ def run_long_scan(args):
   if world > 1:
     dist.init_process_group("nccl", device_id=dev)
   leg = long_scan_leg(dev, rank, world, steps=args.steps, warmup=max(args.warmup, 3),
-                      seq=args.seq or 65536, gather=True)
+                      seq=args.seq or 65536, gather=True, shard_of=args.shard_of)
   if rank == 0:
     leg.update({"metric": "rglru_long_scan_tokens_per_s", "value": leg["tokens_per_s"],
                 "unit": "tokens/s", "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
@@ -961,6 +963,8 @@ def main():
                        "(long head-sharded scan) or cfg4 (the whole 2B model: prompt + greedy decode)")
   ap.add_argument("--seq", type=int, default=None,
                   help="cfg3: sequence length (default 65536); cfg4: prompt length (default 2048)")
+  ap.add_argument("--shard-of", type=int, default=0,
+                  help="cfg3 on one GPU: time the shard one of this many GPUs would run (development)")
   ap.add_argument("--gen-steps", type=int, default=512, help="cfg4: greedy decode steps (default 512)")
   ap.add_argument("--gpus", type=int, default=1)
   ap.add_argument("--steps", type=int, default=20)

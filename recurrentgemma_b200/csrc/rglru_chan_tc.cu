@@ -81,11 +81,10 @@ __device__ __forceinline__ void st_relaxed_u64(unsigned long long* p, unsigned l
   asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" :: "l"(p), "l"(v) : "memory");
 }
 
-// Look-back record of one (unit, channel quarter): 32 channels.
-struct QuarterRecord {
-  float P[kSub];
-  float H[kSub];
-};
+// The map of one (unit, channel quarter) travels the same way: two words per channel, {P, token}
+// and {H, token}.  A reader that looks back over several earlier tiles asks for the state words and
+// the map words of all of them at once and uses whatever has arrived: one round trip to memory.
+constexpr int kLookback = 2;             // earlier tiles asked for per round trip (more cost registers)
 
 // In-place transposition of a warp's 32 x 32 bfloat16 tile (rows of 64 bytes, 64-byte swizzle:
 // 16-byte piece j of row r at position j ^ ((r >> 1) & 3)).  ldmatrix.trans hands thread T of the
@@ -162,6 +161,71 @@ __device__ __forceinline__ void gates_16(const uint32_t (&zx)[16], const uint32_
   }
 }
 
+// Decoupled look-back of one channel (lane): composes the published maps of earlier tiles of the
+// chain, nearest first, until a tile with a known state (or the start of the sequence) is met, and
+// returns the state entering tile tt.
+__device__ __forceinline__ float look_back(const unsigned long long* agg, const unsigned long long* incl,
+                                        const float* h0, int64_t rec, int tt, int per_tt, int b, int E,
+                                        int chan, int lane, int use_agg, bool* timed_out_p) {
+  float hin = 0.0f;
+  bool timed_out = false;
+  {
+    float Pc = 1.0f, Hc = 0.0f;
+    int pred = tt - 1;                 // the nearest tile not yet absorbed
+    bool done = false;
+    unsigned spins = 0;
+    const int depth = use_agg ? kLookback : 1;
+    while (!done) {
+      unsigned long long wi[kLookback], wp[kLookback], wh[kLookback];
+#pragma unroll
+      for (int i = 0; i < kLookback; ++i) {
+        const int pt = pred - i;
+        wi[i] = 0ull; wp[i] = 0ull; wh[i] = 0ull;
+        if (i < depth && pt >= 0) {
+          const int64_t rp = (rec - (int64_t)(tt - pt) * per_tt * 4) * kSub + lane;
+          wi[i] = ld_relaxed_u64(incl + rp);
+          if (use_agg) {
+            wp[i] = ld_relaxed_u64(agg + rp * 2);
+            wh[i] = ld_relaxed_u64(agg + rp * 2 + 1);
+          }
+        }
+      }
+      bool progress = false;
+#pragma unroll
+      for (int i = 0; i < kLookback; ++i) {
+        if (!done && pred >= 0 && i < depth) {
+          // entries of this batch are consumed strictly in order: entry i belongs to `pred` only
+          // while every earlier entry was absorbed
+          if ((wi[i] >> 32) == 1ull) {
+            hin = fmaf(Pc, __uint_as_float((uint32_t)wi[i]), Hc);
+            done = true;
+            progress = true;
+          } else if ((wp[i] >> 32) == 1ull && (wh[i] >> 32) == 1ull) {
+            Hc = fmaf(Pc, __uint_as_float((uint32_t)wh[i]), Hc);
+            Pc *= __uint_as_float((uint32_t)wp[i]);
+            --pred;
+            progress = true;
+          } else {
+            break;
+          }
+        }
+      }
+      if (!done && pred < 0) {
+        // every tile back to the start of the sequence was absorbed as a map
+        const float hs = h0 != nullptr ? h0[(int64_t)b * E + chan] : 0.0f;
+        hin = fmaf(Pc, hs, Hc);
+        done = true;
+      }
+      if (!done && !progress) {
+        if (++spins > kLookbackSpins) { timed_out = true; break; }
+        __nanosleep(32);
+      }
+    }
+  }
+  *timed_out_p = timed_out;
+  return hin;
+}
+
 // Position of a unit (time tile, sequence, half head), advanced by the grid size without divisions.
 struct UnitPos {
   int tt, b, grp;
@@ -186,7 +250,7 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
                   const __nv_bfloat16* __restrict__ bias_x, const __nv_bfloat16* __restrict__ bias_a,
                   const __nv_bfloat16* __restrict__ m8sp, const float* __restrict__ h0, int B, int T_,
                   int E, int groups, int n_units, float* __restrict__ h_last, WsHeader* hdr,
-                  unsigned* flags, QuarterRecord* agg, unsigned long long* incl) {
+                  unsigned long long* agg, unsigned long long* incl, int use_agg) {
   extern __shared__ uint8_t smem_raw[];
   // aligned by an offset into the shared array, so that the address space stays known to the
   // compiler (shared-memory load/store instructions instead of generic ones)
@@ -445,78 +509,22 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
         }
         float hin = hin_pref;
         if (!known) {
-          agg[rec].P[lane] = Pt;
-          agg[rec].H[lane] = Ht;
+          // Decoupled look-back, one channel per lane.  With use_agg (fewer chains than CTAs: the
+          // earlier tiles of this chain are in flight on other SMs) the tile's own map is published
+          // first, and maps of earlier tiles are composed until a tile with a known state is met;
+          // otherwise only the predecessor's state is waited for (it was dealt out a round earlier).
+          if (use_agg) {
+            st_relaxed_u64(agg + (rec * kSub + lane) * 2, kToken | (unsigned long long)__float_as_uint(Pt));
+            st_relaxed_u64(agg + (rec * kSub + lane) * 2 + 1, kToken | (unsigned long long)__float_as_uint(Ht));
+          }
+          bool timed_out = false;
+          if (ok) hin = look_back(agg, incl, h0, rec, tt, per_tt, b, E, e0 + lane, lane, use_agg, &timed_out);
           __syncwarp();
-          if (lane == 0) st_release_u32(&flags[rec], 1u);
-          if (ok) {
-            // decoupled look-back: lane l polls the flag of the l-th earlier time tile
-            float Pc = 1.0f, Hc = 0.0f;
-            int base = tt - 1;
-            bool done = false, timed_out = false;
-            while (!done) {
-              const int pred = base - lane;
-              const int64_t rp = rec - (int64_t)(tt - pred) * per_tt * 4;
-              unsigned f = 2u;
-              int L = 32;
-              unsigned spins = 0;
-              while (true) {
-                if (pred >= 0) {
-                  // inclusive if the predecessor's first state word carries the token, else
-                  // whatever its flag says (1: its map is published)
-                  f = (ld_relaxed_u64(incl + rp * kSub) >> 32) == 1ull ? 2u : ld_acquire_u32(&flags[rp]);
-                }
-                const unsigned im = __ballot_sync(0xffffffffu, f == 2u);
-                L = im ? (__ffs(im) - 1) : 32;
-                const unsigned need = (L >= 31) ? 0xffffffffu : ((2u << L) - 1u);
-                if ((__ballot_sync(0xffffffffu, f == 0u) & need) == 0u) break;
-                if (++spins > kLookbackSpins) { timed_out = true; break; }
-                __nanosleep(32);
-              }
-              if (timed_out) break;
-              __syncwarp();
-              const int n_agg = L < 32 ? L : 32;
-              // records are fetched eight at a time, all loads before the first use
-              for (int j0 = 0; j0 < n_agg; j0 += 8) {
-                float pj[8], hj[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                  const int j = min(j0 + i, n_agg - 1);
-                  const int64_t r2 = rec - (int64_t)(tt - (base - j)) * per_tt * 4;
-                  pj[i] = ld_cg_f32(agg[r2].P + lane);
-                  hj[i] = ld_cg_f32(agg[r2].H + lane);
-                }
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                  if (j0 + i < n_agg) {
-                    Hc = fmaf(Pc, hj[i], Hc);
-                    Pc *= pj[i];
-                  }
-                }
-              }
-              if (L < 32) {
-                const int64_t r2 = rec - (int64_t)(tt - (base - L)) * per_tt * 4;
-                // the 32 state words were stored by one instruction but are 32 separate words: each
-                // lane waits for the token of its own
-                unsigned long long v = ld_relaxed_u64(incl + r2 * kSub + lane);
-                for (unsigned k = 0; (v >> 32) != 1ull && k < kLookbackSpins; ++k) {
-                  __nanosleep(32);
-                  v = ld_relaxed_u64(incl + r2 * kSub + lane);
-                }
-                if (!__all_sync(0xffffffffu, (v >> 32) == 1ull)) timed_out = true;
-                hin = fmaf(Pc, __uint_as_float((uint32_t)v), Hc);
-                done = true;
-              } else {
-                base -= 32;
-              }
-            }
-            if (timed_out) {
-              if (lane == 0) atomicExch(&hdr->status, kStatusTimeout);
-              hin = 0.0f;
-            }
-          } else {
+          if (__any_sync(0xffffffffu, timed_out)) {
+            if (lane == 0) atomicExch(&hdr->status, kStatusTimeout);
             hin = 0.0f;
           }
+          if (!ok) hin = 0.0f;
           s_hin[lane] = hin;
         }
         const float h_end = fmaf(Pt, hin, Ht);
@@ -597,7 +605,7 @@ __global__ void m8sp_chan_kernel(const __nv_bfloat16* __restrict__ a_param, int 
 
 struct ChanLayout {
   int64_t n_units, n_rec;
-  size_t flags_off, m8sp_off, agg_off, incl_off, total;
+  size_t m8sp_off, agg_off, incl_off, total;
 };
 
 ChanLayout chan_layout(int64_t B, int64_t T, int64_t E) {
@@ -606,11 +614,10 @@ ChanLayout chan_layout(int64_t B, int64_t T, int64_t E) {
   L.n_units = ((T + kUT - 1) / kUT) * B * groups;
   L.n_rec = L.n_units * 4;
   auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
-  L.flags_off = sizeof(WsHeader);
-  L.incl_off = up(L.flags_off + (size_t)L.n_rec * sizeof(unsigned));
-  L.m8sp_off = up(L.incl_off + (size_t)L.n_rec * kSub * sizeof(unsigned long long));
-  L.agg_off = up(L.m8sp_off + (size_t)E * 2);
-  L.total = up(L.agg_off + (size_t)L.n_rec * sizeof(QuarterRecord));
+  L.incl_off = sizeof(WsHeader);
+  L.agg_off = up(L.incl_off + (size_t)L.n_rec * kSub * sizeof(unsigned long long));
+  L.m8sp_off = up(L.agg_off + (size_t)L.n_rec * kSub * 2 * sizeof(unsigned long long));
+  L.total = up(L.m8sp_off + (size_t)E * 2);
   return L;
 }
 
@@ -652,8 +659,19 @@ cudaError_t launch_rglru_chan(const void* c, const void* pos, int pos64, const v
   const int E = H * kHW;
   const ChanLayout L = chan_layout(B, T, E);
   char* base = static_cast<char*>(ws);
-  // flags and state words start at zero (the status word before them belongs to the caller)
-  cudaError_t err = cudaMemsetAsync(base + sizeof(int), 0, L.m8sp_off - sizeof(int), s);
+  int num_sms = 0;
+  cudaError_t err = chan_device_setup(&num_sms);
+  if (err != cudaSuccess) return err;
+  const int groups = 2 * H;
+  const int n_units = (int)L.n_units;
+  const int grid = n_units < num_sms ? n_units : num_sms;   // all CTAs resident: look-back may spin
+  // With fewer units per time tile than CTAs, consecutive tiles of a chain are in flight at once
+  // and carries are resolved from published maps; otherwise a tile's predecessor was dealt out a
+  // round earlier and only its state is ever waited for.
+  const int use_agg = (int64_t)B * groups < grid ? 1 : 0;
+  // state words (and map words, where used) start without their token; the status word before
+  // them belongs to the caller
+  err = cudaMemsetAsync(base + sizeof(int), 0, (use_agg ? L.m8sp_off : L.agg_off) - sizeof(int), s);
   if (err != cudaSuccess) return err;
   T_* m8sp = reinterpret_cast<T_*>(base + L.m8sp_off);
   m8sp_chan_kernel<<<(E + 255) / 256, 256, 0, s>>>((const T_*)a_param, E, m8sp);
@@ -667,18 +685,12 @@ cudaError_t launch_rglru_chan(const void* c, const void* pos, int pos64, const v
       !tensor_map_bte_sw64(&map_ot, out, Bu, Tu, Eu, kSub, kSub) ||
       !tensor_map_bte_sw64(&map_yt, yb != nullptr ? yb : out, Bu, Tu, Eu, kSub, kSub))
     return cudaErrorInvalidValue;
-  int num_sms = 0;
-  if ((err = chan_device_setup(&num_sms)) != cudaSuccess) return err;
-  const int groups = 2 * H;
-  const int n_units = (int)L.n_units;
-  const int grid = n_units < num_sms ? n_units : num_sms;   // all CTAs resident: look-back may spin
 #define RGK_CHAN(J, M)                                                                           \
   rglru_chan_kernel<J, M><<<grid, kThreads, kSmem, s>>>(                                         \
       map_c, map_w, map_ct, map_yt, map_ot, pos, pos64, (const T_*)bx, (const T_*)ba, m8sp, h0,  \
       (int)B, (int)T, E, groups, n_units, h_last, reinterpret_cast<WsHeader*>(base),             \
-      reinterpret_cast<unsigned*>(base + L.flags_off),                                           \
-      reinterpret_cast<QuarterRecord*>(base + L.agg_off),                                        \
-      reinterpret_cast<unsigned long long*>(base + L.incl_off))
+      reinterpret_cast<unsigned long long*>(base + L.agg_off),                                   \
+      reinterpret_cast<unsigned long long*>(base + L.incl_off), use_agg)
 #define RGK_CHAN_J(M)                                                                            \
   if (join == 0) RGK_CHAN(0, M); else if (join == 1) RGK_CHAN(1, M); else RGK_CHAN(2, M)
   const int join = yb == nullptr ? 0 : (y_activated ? 2 : 1);
