@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define RGK_ABI_VERSION 6
+#define RGK_ABI_VERSION 7
 
 #if defined(__GNUC__)
 #define RGK_API __attribute__((visibility("default")))
@@ -368,12 +368,21 @@ RGK_API int rgk_geglu_bias(const void* up, const void* bias, int64_t M, int64_t 
  * points, so one buffer serves all of them).  Returns 0 on invalid arguments. */
 RGK_API size_t rgk_workspace_bytes(int64_t B, int64_t T, int64_t E, int dtype);
 
-/* Copies the status word the kernels of the last call on `workspace` left behind to the host
- * (synchronises `stream`).  RGK_OK, or RGK_ETIMEOUT if a bounded device-side wait gave up.
- * Every call clears the word before its kernels run, except the single-kernel decode step, which
- * only ever raises it: after a decode loop the word tells whether any step since the last
- * clearing call timed out. */
-RGK_API int rgk_workspace_status(const void* workspace, void* stream);
+/* The first int of a workspace is its status word.  Kernels only ever RAISE it (to RGK_ETIMEOUT,
+ * when a bounded device-side wait gave up); no call of this library clears it, so the word tells
+ * whether anything went wrong on this workspace since the caller last cleared it.  A new workspace
+ * must start with the word at 0 (cudaMemset the first 4 bytes once).
+ * rgk_workspace_status synchronises `stream`, copies the word to the host and returns RGK_OK or
+ * RGK_ETIMEOUT; a raised word is cleared as it is reported. */
+RGK_API int rgk_workspace_status(void* workspace, void* stream);
+
+/* Self-test of the failure path (no counterpart in the reference): runs a small scan in which the
+ * records of the first time tile are never published, with the poll limit of the look-back lowered
+ * to 200, so that the bounded waits of the next tile run out within microseconds.  The kernel must
+ * finish by itself and leave RGK_ETIMEOUT in the status word (rgk_workspace_status then returns
+ * it).  Nothing faults, traps or waits without a limit.  workspace: at least 1 MiB, 256-byte
+ * aligned; its contents are overwritten. */
+RGK_API int rgk_selftest_wait_expiry(void* workspace, size_t workspace_bytes, void* stream);
 
 #ifdef __cplusplus
 }

@@ -12,10 +12,12 @@ from recurrentgemma_b200.modules import (AttentionBlockCache, Embedder, LocalAtt
                                          recurrent_residual, residual_block)
 from recurrentgemma_b200.griffin import Griffin, GriffinConfig, TemporalBlockType
 from recurrentgemma_b200.sampler import GreedySampler
+from recurrentgemma_b200._lib import RgkError, check_status
 
 __all__ = [
     "BlockDiagonalLinear", "Conv1D", "Einsum", "RGLRU", "RMSNorm", "rnn_scan", "RecurrentBlock",
     "RecurrentBlockCache", "MLPBlock", "LocalAttentionBlock", "AttentionBlockCache", "ResidualBlock",
     "Embedder", "Griffin", "GriffinConfig", "TemporalBlockType", "GreedySampler", "argmax",
-    "recurrent_path", "recurrent_residual", "residual_block", "dense_linear",
+    "recurrent_path", "recurrent_residual", "residual_block", "dense_linear", "check_status",
+    "RgkError",
 ]

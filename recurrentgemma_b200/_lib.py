@@ -16,6 +16,9 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "librgk.so")
 
 RGK_F32, RGK_BF16 = 0, 1
+# rgk_status codes of include/rgk.h
+(RGK_OK, RGK_EINVAL, RGK_ESHAPE, RGK_EALIGN, RGK_EARCH, RGK_ECUDA, RGK_EWORKSPACE,
+ RGK_ETIMEOUT) = 0, -1, -2, -3, -4, -5, -6, -7
 RGK_I32, RGK_I64 = 0, 1
 GATES_AUTO, GATES_SIMT, GATES_TCGEN05, GATES_FUSED, GATES_FUSED_EXACT = 0, 1, 2, 3, 4
 
@@ -87,6 +90,7 @@ SIGNATURES = {
     "rgk_geglu_bias": (_int, [_vp, _vp, _i64, _i64, _int, _vp, _vp]),
     "rgk_workspace_bytes": (_sz, [_i64, _i64, _i64, _int]),
     "rgk_workspace_status": (_int, [_vp, _vp]),
+    "rgk_selftest_wait_expiry": (_int, [_vp, _sz, _vp]),
 }
 
 _lib = None
@@ -116,7 +120,7 @@ def load() -> ctypes.CDLL:
       fn = getattr(lib, name)
       fn.restype = res
       fn.argtypes = args
-    if lib.rgk_abi_version() != 6:
+    if lib.rgk_abi_version() != 7:
       raise RuntimeError("librgk.so has a different ABI version; rebuild it")
     _lib = lib
     return lib
@@ -179,8 +183,13 @@ def workspace(dev: torch.device, nbytes: int) -> torch.Tensor:
   buf = _workspaces.get(key)
   if buf is None or buf.numel() < nbytes:
     with torch.cuda.device(dev):
-      buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=dev)
-    _workspaces[key] = buf
+      new = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=dev)
+      # the status word (first int): kernels only ever raise it, nobody but its reader clears it
+      if buf is None:
+        new[:4].zero_()
+      else:
+        new[:4].copy_(buf[:4])
+    _workspaces[key] = buf = new
   return buf
 
 
@@ -188,6 +197,29 @@ def workspace_bytes(b: int, t: int, e: int, dt: torch.dtype) -> int:
   return int(load().rgk_workspace_bytes(b, t, e, dtype_code(dt)))
 
 
-def workspace_status(ws: torch.Tensor) -> None:
-  """Raises RgkError(RGK_ETIMEOUT) if a bounded device wait expired in the last call on `ws`."""
-  check(load().rgk_workspace_status(ws.data_ptr(), stream_ptr(ws.device)))
+def workspace_status(ws: torch.Tensor, stream: Optional[int] = None) -> None:
+  """Raises RgkError(RGK_ETIMEOUT) if a bounded device wait expired in any call on `ws` since the
+  word was last read as raised (synchronises the stream; a raised word is cleared as it is reported)."""
+  check(load().rgk_workspace_status(ws.data_ptr(),
+                                    stream_ptr(ws.device) if stream is None else stream))
+
+
+def status_ptr(dev: torch.device) -> int:
+  """Device address of the status word of the current stream's workspace: what entry points with an
+  `int* status` argument are given, so that their timeouts show up in `check_status` too."""
+  return workspace(dev, 4).data_ptr()
+
+
+def check_status(device: Optional[torch.device] = None) -> None:
+  """Raises RgkError(RGK_ETIMEOUT) if any kernel launched through this package on `device` (every
+  stream that has a workspace) gave up on a bounded wait since the last check.  The kernels finish
+  on their own after such an expiry, but what they computed is invalid, and nothing else reports
+  it: call this wherever the host synchronises anyway (it synchronises those streams)."""
+  index = None
+  if device is not None:
+    device = torch.device(device)
+    index = device.index if device.index is not None else torch.cuda.current_device()
+  for (dev_index, stream), buf in list(_workspaces.items()):
+    if index is None or dev_index == index:
+      with torch.cuda.device(dev_index):
+        workspace_status(buf, stream)

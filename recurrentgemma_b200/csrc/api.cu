@@ -198,13 +198,17 @@ size_t rgk_workspace_bytes(int64_t B, int64_t T, int64_t E, int dtype) {
   return carve(nullptr, B, T, E, dtype).total;
 }
 
-int rgk_workspace_status(const void* workspace, void* stream) {
+int rgk_workspace_status(void* workspace, void* stream) {
   RGK_REQUIRE(workspace != nullptr, RGK_EINVAL, "workspace is NULL");
   int status = 0;
   RGK_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)), "cudaStreamSynchronize");
   RGK_CUDA(cudaMemcpy(&status, workspace, sizeof(int), cudaMemcpyDeviceToHost), "cudaMemcpy");
-  if (status == rgk::kStatusTimeout)
-    return fail(RGK_ETIMEOUT, "a bounded device-side wait expired; results of that call are invalid");
+  if (status == rgk::kStatusTimeout) {
+    // reported once: the word is cleared so that later calls are judged on their own
+    RGK_CUDA(cudaMemset(workspace, 0, sizeof(int)), "cudaMemset");
+    return fail(RGK_ETIMEOUT, "a bounded device-side wait expired since the status word was last "
+                              "cleared; results of the calls on this workspace since then are invalid");
+  }
   return RGK_OK;
 }
 
@@ -275,8 +279,6 @@ int rgk_linear_scan(const void* x, const void* a, const uint8_t* reset, const fl
   RGK_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255u) == 0, RGK_EALIGN,
               "workspace must be 256-byte aligned");
   RGK_CHECK_DEVICE();
-  RGK_CUDA(cudaMemsetAsync(workspace, 0, sizeof(int), static_cast<cudaStream_t>(stream)),
-           "cudaMemsetAsync");
   RGK_CUDA(rgk::launch_scan(x, a, reset, nullptr, 0, h0, y_mul, 0, B, T, E, dtype, y, h_last,
                             workspace, static_cast<cudaStream_t>(stream)),
            "scan launch");
@@ -331,6 +333,30 @@ int rgk_linear_scan_static(const void* x, const void* a, const uint8_t* reset, c
   return RGK_OK;
 }
 
+int rgk_selftest_wait_expiry(void* workspace, size_t workspace_bytes, void* stream) {
+  // A scan over 2 sequences x 3 time tiles x 64 channels whose first time tile is never launched:
+  // the tiles of the second time tile look back for records nobody publishes, give up after 200
+  // polls (tens of microseconds), raise the status word, take a zero carry and finish.
+  const int64_t B = 2, T = 3 * 128, E = 64;
+  const size_t act = static_cast<size_t>(B * T * E) * 2;
+  const size_t need = up256(rgk::scan_workspace_bytes(B, T, E, RGK_BF16)) + 3 * up256(act);
+  RGK_REQUIRE(workspace != nullptr && workspace_bytes >= need, RGK_EWORKSPACE,
+              "workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+  RGK_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255u) == 0, RGK_EALIGN,
+              "workspace must be 256-byte aligned");
+  RGK_CHECK_DEVICE();
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  char* base = static_cast<char*>(workspace);
+  char* x = base + up256(rgk::scan_workspace_bytes(B, T, E, RGK_BF16));
+  char* a = x + up256(act);
+  char* y = a + up256(act);
+  RGK_CUDA(cudaMemsetAsync(x, 0, 3 * up256(act), s), "cudaMemsetAsync");
+  RGK_CUDA(rgk::launch_scan(x, a, nullptr, nullptr, 0, nullptr, nullptr, 0, B, T, E, RGK_BF16, y,
+                            nullptr, workspace, s, /*skip_time_tiles=*/1, /*spin_limit=*/200),
+           "scan launch");
+  return RGK_OK;
+}
+
 int rgk_rglru_forward(const void* x, const void* segment_pos, int pos_dtype, const rgk_params* p,
                       const float* h0, int64_t B, int64_t T, int64_t E, int H, int dtype,
                       int gates_impl, void* y, float* h_last, void* workspace,
@@ -354,7 +380,6 @@ int rgk_rglru_forward(const void* x, const void* segment_pos, int pos_dtype, con
   RGK_CHECK_DEVICE();
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int bw = (int)(E / H);
-  RGK_CUDA(cudaMemsetAsync(workspace, 0, sizeof(int), s), "cudaMemsetAsync");
   (void)bw;
   return run_rglru(x, segment_pos, pos_dtype, p, h0, nullptr, 0, B, T, E, H, dtype, gates_impl,
                    w.wpack, w.a, w.xn, w.scan, y, h_last, s);
@@ -387,7 +412,6 @@ int rgk_recurrent_path_prefill(const void* xb, const void* yb, const void* segme
   RGK_CHECK_DEVICE();
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int bw = (int)(E / H);
-  RGK_CUDA(cudaMemsetAsync(workspace, 0, sizeof(int), s), "cudaMemsetAsync");
   RGK_CUDA(rgk::launch_conv1d_prefill(xb, segment_pos, pos_dtype, p->conv_w, p->conv_b, B, T, E,
                                       dtype, w.c, conv_cache_out, s),
            "conv1d_prefill launch");
@@ -569,7 +593,6 @@ int rgk_recurrent_block_prefill(const void* x, const void* segment_pos, int pos_
               "workspace must be 256-byte aligned");
   RGK_CHECK_DEVICE();
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  RGK_CUDA(cudaMemsetAsync(workspace, 0, sizeof(int), s), "cudaMemsetAsync");
   return block_prefill_impl(x, nullptr, segment_pos, pos_dtype, p, B, T, D, E, H, dtype, out, h_last,
                             conv_cache_out, workspace, s);
 }
@@ -637,7 +660,6 @@ int rgk_residual_block_prefill(const void* x, const void* segment_pos, int pos_d
               "workspace must be 256-byte aligned");
   RGK_CHECK_DEVICE();
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  RGK_CUDA(cudaMemsetAsync(workspace, 0, sizeof(int), s), "cudaMemsetAsync");
   void* xn = static_cast<char*>(workspace) + block;      // temporal_pre_norm(x)
   RGK_CUDA(rgk::launch_rmsnorm(x, norm_scale, B * T, D, eps, dtype, xn, s), "rmsnorm launch");
   return block_prefill_impl(xn, x, segment_pos, pos_dtype, p, B, T, D, E, H, dtype, out, h_last,
@@ -723,7 +745,6 @@ int rgk_mlp_block(const void* x, const void* packed_up, const void* down_w, cons
   if (M == 0) return RGK_OK;
   RGK_CHECK_DEVICE();
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  RGK_CUDA(cudaMemsetAsync(workspace, 0, sizeof(int), s), "cudaMemsetAsync");
   return mlp_impl(x, packed_up, down_w, down_b, residual, M, D, X, out, workspace, s);
 }
 
@@ -741,7 +762,6 @@ int rgk_residual_channel(const void* residual_in, const void* norm_scale, float 
   if (M == 0) return RGK_OK;
   RGK_CHECK_DEVICE();
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  RGK_CUDA(cudaMemsetAsync(workspace, 0, sizeof(int), s), "cudaMemsetAsync");
   void* xn = static_cast<char*>(workspace) + 256 + up256(static_cast<size_t>(M) * X * 2);
   RGK_CUDA(rgk::launch_rmsnorm(residual_in, norm_scale, M, D, eps, dtype, xn, s), "rmsnorm launch");
   return mlp_impl(xn, packed_up, down_w, down_b, residual_in, M, D, X, out, workspace, s);
@@ -789,7 +809,6 @@ int rgk_local_attention_prefill(const void* q, const void* k, const void* v, con
               "workspace must be 256-byte aligned");
   RGK_CHECK_DEVICE();
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  RGK_CUDA(cudaMemsetAsync(workspace, 0, sizeof(int), s), "cudaMemsetAsync");
   RGK_CUDA(rgk::launch_attention_prefill(q, k, v, segment_pos, pos_dtype == RGK_I64, B, T, N, window,
                                          out, workspace, s),
            "attention launch");
@@ -857,9 +876,8 @@ int rgk_recurrent_path_decode(const void* xb, const void* yb, const void* segmen
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int bw = (int)(E / H);
   if (gates_impl != RGK_GATES_SIMT && rgk::gates_tc_supported(dtype, bw, B)) {
-    // The whole step in one kernel, and nothing else on the stream: the status word is not
-    // cleared here (the kernel only ever raises it), so a decode loop is one launch per layer.
-    // The states may be updated in place: every element of h and of the conv cache is read and
+    // The whole step in one kernel, and nothing else on the stream: a decode loop is one launch
+    // per layer.  The states may be updated in place: every element of h and of the conv cache is read and
     // then written by one and the same thread.
     const void* packed = p->gates_packed;
     if (packed == nullptr) {
@@ -874,7 +892,6 @@ int rgk_recurrent_path_decode(const void* xb, const void* yb, const void* segmen
              "fused decode launch");
     return RGK_OK;
   }
-  RGK_CUDA(cudaMemsetAsync(workspace, 0, sizeof(int), s), "cudaMemsetAsync");
   RGK_CUDA(rgk::launch_conv1d_decode(xb, conv_cache_in, p->conv_w, p->conv_b, B, E, dtype, w.c,
                                      conv_cache_out, s),
            "conv1d_decode launch");

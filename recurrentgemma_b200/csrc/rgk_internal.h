@@ -160,11 +160,12 @@ cudaError_t launch_rmsnorm(const void* x, const void* scale, int64_t M, int64_t 
 // scan.cu
 size_t scan_workspace_bytes(int64_t B, int64_t T, int64_t E, int dtype);
 // y_mul (optional): the join y * gelu_tanh(y_mul), or y * y_mul when y_activated != 0 (the factor
-// was already passed through gelu by whoever produced it).
+// was already passed through gelu by whoever produced it).  skip_time_tiles / spin_limit: only for
+// the wait-expiry self-test (rgk_selftest_wait_expiry); 0 = the whole problem, the default limit.
 cudaError_t launch_scan(const void* x, const void* a, const uint8_t* reset, const void* pos,
                         int pos64, const float* h0, const void* y_mul, int y_activated, int64_t B,
                         int64_t T, int64_t E, int dtype, void* y, float* h_last, void* ws,
-                        cudaStream_t s);
+                        cudaStream_t s, int skip_time_tiles = 0, unsigned spin_limit = 0);
 
 // The scan's built-in scratch (a __device__ array inside scan.cu): its size, and its address on the
 // current device (looked up with cudaGetSymbolAddress on first use per device).

@@ -101,7 +101,7 @@ scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
             const uint8_t* __restrict__ reset, const void* __restrict__ pos, int pos64,
             const float* __restrict__ h0, const T* __restrict__ y_mul, int B, int T_, int E,
             int tiles_t, int groups, T* __restrict__ y, float* __restrict__ h_last, WsHeader* hdr,
-            unsigned* flags, float2* agg, float* incl) {
+            unsigned* flags, float2* agg, float* incl, unsigned ticket_base, unsigned spin_limit) {
   using Cfg = ScanCfg<T>;
   using Sm = ScanSmem<T>;
   constexpr bool kMul = kJoin != 0;
@@ -122,7 +122,7 @@ scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
 
   const int tid = threadIdx.x;
   if (tid == 0) {
-    s_misc[0] = atomicAdd(&hdr->ticket, 1u);
+    s_misc[0] = atomicAdd(&hdr->ticket, 1u) + ticket_base;
     mbar_init(bar, 1);
     mbar_fence_init();
   }
@@ -261,7 +261,7 @@ scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
         const unsigned need = (L >= 31) ? 0xffffffffu : ((2u << L) - 1u);
         const unsigned zero = __ballot_sync(0xffffffffu, f == 0u) & need;
         if (zero == 0u) break;
-        if (++spins > kSpinLimit) { timed_out = true; break; }
+        if (++spins > spin_limit) { timed_out = true; break; }
         __nanosleep(32);
       }
       if (timed_out) break;
@@ -384,7 +384,7 @@ cudaError_t launch_scan_typed(const void* x, const void* a, const uint8_t* reset
                               int pos64, const float* h0, const void* y_mul, int64_t B, int64_t T_,
                               int64_t E, int tiles_t, int groups, unsigned grid, void* y,
                               float* h_last, WsHeader* hdr, unsigned* flags, float2* agg, float* incl,
-                              cudaStream_t s) {
+                              unsigned ticket_base, unsigned spin_limit, cudaStream_t s) {
   CUtensorMap map_x, map_a;
   if (!tensor_map_bte(&map_x, x, (uint64_t)B, (uint64_t)T_, (uint64_t)E, ScanCfg<T>::kRows, kChan, false,
                       (int)sizeof(T)) ||
@@ -399,7 +399,7 @@ cudaError_t launch_scan_typed(const void* x, const void* a, const uint8_t* reset
   if (e != cudaSuccess) return e;
   scan_kernel<T, kJoin><<<grid, kThreads, ScanSmem<T>::kBytes, s>>>(
       map_x, map_a, reset, pos, pos64, h0, (const T*)y_mul, (int)B, (int)T_, (int)E, tiles_t, groups,
-      (T*)y, h_last, hdr, flags, agg, incl);
+      (T*)y, h_last, hdr, flags, agg, incl, ticket_base, spin_limit);
   return cudaGetLastError();
 }
 
@@ -432,22 +432,27 @@ size_t scan_workspace_bytes(int64_t B, int64_t T, int64_t E, int dtype) {
 cudaError_t launch_scan(const void* x, const void* a, const uint8_t* reset, const void* pos,
                         int pos64, const float* h0, const void* y_mul, int y_activated, int64_t B,
                         int64_t T, int64_t E, int dtype, void* y, float* h_last, void* ws,
-                        cudaStream_t s) {
+                        cudaStream_t s, int skip_time_tiles, unsigned spin_limit) {
   if (B == 0 || T == 0 || E == 0) return cudaSuccess;
   const ScanLayout L = scan_layout(B, T, E, dtype);
   char* base = static_cast<char*>(ws);
   // Ticket and flags start every launch at zero (the status word before them belongs to the
-  // caller, which clears it once per API call).
+  // caller).
   cudaError_t err = cudaMemsetAsync(base + sizeof(int), 0, L.agg_off - sizeof(int), s);
   if (err != cudaSuccess) return err;
   WsHeader* hdr = reinterpret_cast<WsHeader*>(base);
   unsigned* flags = reinterpret_cast<unsigned*>(base + L.flags_off);
   float2* agg = reinterpret_cast<float2*>(base + L.agg_off);
   float* incl = reinterpret_cast<float*>(base + L.incl_off);
-  const unsigned grid = (unsigned)L.ntiles;
+  // skip_time_tiles > 0 (the wait-expiry self-test only): the first time tiles of every sequence are
+  // never launched, so their successors find no published record and their bounded waits run out.
+  const int64_t skipped = (int64_t)skip_time_tiles * B * L.groups;
+  if (skipped < 0 || skipped >= L.ntiles) return cudaErrorInvalidValue;
+  const unsigned grid = (unsigned)(L.ntiles - skipped);
+  const unsigned limit = spin_limit != 0 ? spin_limit : kSpinLimit;
 #define RGK_SCAN_LAUNCH(TYPE, JOIN)                                                               \
   launch_scan_typed<TYPE, JOIN>(x, a, reset, pos, pos64, h0, y_mul, B, T, E, L.tiles_t, L.groups, \
-                                grid, y, h_last, hdr, flags, agg, incl, s)
+                                grid, y, h_last, hdr, flags, agg, incl, (unsigned)skipped, limit, s)
   const int join = y_mul == nullptr ? 0 : (y_activated ? 2 : 1);
   if (dtype) {
     if (join == 0) return RGK_SCAN_LAUNCH(__nv_bfloat16, 0);

@@ -11,6 +11,7 @@ from typing import Optional, Tuple
 
 import torch
 
+from recurrentgemma_b200 import _lib
 from recurrentgemma_b200 import layers
 from recurrentgemma_b200 import modules
 
@@ -80,4 +81,6 @@ class HostPipeline:
       cur.wait_stream(self.s_cmp)
       cur.wait_stream(self.s_out)
       self.s_out.synchronize()
+    # the host is synchronised here anyway: a bounded device wait that gave up must not go unseen
+    _lib.check_status(self.device)
     return h_all, c_all

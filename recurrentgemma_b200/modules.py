@@ -105,7 +105,7 @@ def dense_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Ten
   with torch.cuda.device(dev):
     _lib.check(_lib.load().rgk_dense_linear(
         xc.data_ptr(), wc.data_ptr(), _lib.ptr(bc), xc.numel() // k, k, n, _lib.dtype_code(x.dtype),
-        1 if gelu else 0, out.data_ptr(), None, _lib.stream_ptr(dev)))
+        1 if gelu else 0, out.data_ptr(), _lib.status_ptr(dev), _lib.stream_ptr(dev)))
   return out
 
 
@@ -692,8 +692,8 @@ class Embedder(nn.Module):
       with torch.cuda.device(dev):
         _lib.check(_lib.load().rgk_logits(
             xc.data_ptr(), table.data_ptr(), xc.numel() // self.embed_dim, self.embed_dim,
-            self.vocab_size, float(soft_cap), _lib.dtype_code(x.dtype), out.data_ptr(), None,
-            _lib.stream_ptr(dev)))
+            self.vocab_size, float(soft_cap), _lib.dtype_code(x.dtype), out.data_ptr(),
+            _lib.status_ptr(dev), _lib.stream_ptr(dev)))
       return out
     logits = x @ table.T                     # float32 and odd shapes: a library contraction
     if soft_cap:

@@ -15,6 +15,7 @@ from typing import NamedTuple, Optional
 
 import torch
 
+from recurrentgemma_b200 import _lib
 from recurrentgemma_b200 import modules
 
 
@@ -87,11 +88,15 @@ class GreedySampler:
   @torch.no_grad()
   def __call__(self, tokens: torch.Tensor, total_generation_steps: int,
                input_lengths: Optional[torch.Tensor] = None,
-               return_logits: bool = False) -> SamplerOutput:
+               return_logits: bool = False, check_status: bool = False) -> SamplerOutput:
     """tokens [B, prompt_length] (left padded; `input_lengths` [B] gives the true lengths,
     default: no padding).  Generates `total_generation_steps` tokens per sequence greedily.
     Sequences that produce `eos_id` keep running (the reference stops the whole batch only when
-    every sequence is done); positions after the first EOS are overwritten with `pad_id`."""
+    every sequence is done); positions after the first EOS are overwritten with `pad_id`.
+    The call enqueues the whole generation and returns without synchronising; with
+    `check_status` it waits for the device at the end and raises if a kernel gave up on a bounded
+    wait (the tokens are then invalid) - otherwise call `recurrentgemma_b200.check_status()` where
+    the host synchronises next."""
     dev = self.device
     tokens = tokens.to(dev)
     b, prompt_length = tokens.shape
@@ -138,6 +143,8 @@ class GreedySampler:
       done = torch.cumsum((out_tokens == self.eos_id).int(), dim=1)
       after = (done - (out_tokens == self.eos_id).int()) > 0
       out_tokens = torch.where(after, torch.full_like(out_tokens, self.pad_id), out_tokens)
+    if check_status:
+      _lib.check_status(dev)
     return SamplerOutput(out_tokens, out_logits)
 
 

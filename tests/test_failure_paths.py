@@ -1,0 +1,96 @@
+"""The failure path of the bounded device-side waits, and one process driving two GPUs.
+
+No test here faults, traps or hangs a GPU: the expiry is produced by a wait that is given nothing to
+wait for (records that are never published) with its poll limit lowered, after which the kernel
+finishes on its own and leaves an error status for the host to read."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def lib():
+  from recurrentgemma_b200 import _lib
+  return _lib.load()
+
+
+def test_bounded_wait_expires_and_is_reported(lib):
+  """rgk_selftest_wait_expiry launches a scan whose first time tile is never run: the look-back of
+  the next tile gives up after 200 polls, the kernel returns, and the status word holds
+  RGK_ETIMEOUT.  Reading the word reports it once and clears it; the next (healthy) call on the
+  same workspace leaves it clean."""
+  from recurrentgemma_b200 import _lib
+  import recurrentgemma_b200 as rg
+  dev = torch.device(DEV)
+  ws = _lib.workspace(dev, 1 << 20)
+  _lib.workspace_status(ws)                       # clean before
+  with torch.cuda.device(dev):
+    _lib.check(lib.rgk_selftest_wait_expiry(ws.data_ptr(), ws.numel(), _lib.stream_ptr(dev)))
+  torch.cuda.synchronize()                        # the kernel has returned by itself
+  with pytest.raises(_lib.RgkError) as err:
+    rg.check_status(dev)
+  assert err.value.code == _lib.RGK_ETIMEOUT
+  rg.check_status(dev)                            # reported once, then cleared
+  # a healthy scan on the same workspace afterwards
+  x = torch.randn(2, 300, 128, device=dev)
+  a = torch.rand(2, 300, 128, device=dev)
+  reset = torch.zeros(2, 300, dtype=torch.bool, device=dev)
+  y, h = rg.rnn_scan(x, a, reset, None)
+  ref = torch.zeros(2, 128, device=dev)
+  for t in range(300):
+    ref = a[:, t] * ref + x[:, t]
+  torch.testing.assert_close(h, ref, rtol=1e-5, atol=1e-5)
+  rg.check_status(dev)
+
+
+def test_status_word_survives_workspace_growth(lib):
+  """The package's per-stream workspace grows on demand; a raised status word moves with it."""
+  from recurrentgemma_b200 import _lib
+  import recurrentgemma_b200 as rg
+  dev = torch.device(DEV)
+  ws = _lib.workspace(dev, 1 << 20)
+  with torch.cuda.device(dev):
+    _lib.check(lib.rgk_selftest_wait_expiry(ws.data_ptr(), ws.numel(), _lib.stream_ptr(dev)))
+  bigger = _lib.workspace(dev, ws.numel() * 2)
+  assert bigger.numel() >= ws.numel() * 2
+  with pytest.raises(_lib.RgkError):
+    rg.check_status(dev)
+  rg.check_status(dev)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs in one process")
+def test_second_device_in_one_process():
+  """Function attributes (dynamic shared memory above the default limit) are per device: after
+  cuda:0 has run the kernels, the same process runs them on cuda:1 - the built-in-scratch scan and
+  a tensor-core entry point (plain kernels on each device's own memory, no peer access)."""
+  import ctypes
+  import recurrentgemma_b200 as rg
+  from recurrentgemma_b200 import _lib, synthetic
+  lib = _lib.load()
+  outs = []
+  for index in (0, 1):
+    dev = torch.device("cuda", index)
+    with torch.cuda.device(dev):
+      g = torch.Generator().manual_seed(5)
+      p = synthetic.rglru_params(512, 2, g, torch.bfloat16)
+      x = torch.randn((2, 384, 512), generator=g).to(torch.bfloat16).to(dev)
+      pos = torch.arange(384).repeat(2, 1).to(dev)
+      m = rg.RGLRU(512, 2, device=dev, dtype=torch.bfloat16)
+      m.load_state_dict(p)
+      y, h = m(x, pos)                                        # fused tcgen05 kernel
+      w = torch.randn((512, 512), generator=g).to(torch.bfloat16).to(dev)
+      z = rg.dense_linear(x, w, None)                         # tcgen05 GEMM
+      xs = torch.randn((2, 300, 128), generator=g).to(dev)
+      a = torch.rand((2, 300, 128), generator=g).to(dev)
+      ys = torch.empty_like(xs)
+      hs = torch.empty((2, 128), device=dev)
+      _lib.check(lib.rgk_linear_scan_static(xs.data_ptr(), a.data_ptr(), None, None, None, 2, 300,
+                                            128, _lib.RGK_F32, ys.data_ptr(), hs.data_ptr(), None,
+                                            _lib.stream_ptr(dev)))
+      torch.cuda.synchronize(dev)
+      rg.check_status(dev)
+      outs.append((y.float().cpu(), z.float().cpu(), ys.cpu()))
+  for a0, a1 in zip(outs[0], outs[1]):
+    torch.testing.assert_close(a0, a1, rtol=2e-2, atol=2e-2)
