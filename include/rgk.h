@@ -6,7 +6,8 @@
  * Python method cited beside it (paths inside the recurrentgemma checkout).  All pointers are
  * DEVICE pointers unless stated otherwise; tensors are dense, row-major and contiguous; nothing is
  * allocated, freed or retained by the library (scratch comes from the caller, see
- * rgk_workspace_bytes).  Every call only enqueues work on `stream` (a cudaStream_t) and returns
+ * rgk_workspace_bytes; the one exception is rgk_linear_scan_static, which runs on an array built
+ * into the library's device image).  Every call only enqueues work on `stream` (a cudaStream_t) and returns
  * 0 or a negative rgk_status; it never synchronises, throws or exits.  There is no CPU path: on a
  * device that is not compute capability 10.x every call returns RGK_EARCH.
  *
@@ -197,8 +198,9 @@ RGK_API int rgk_recurrent_path_prefill(const void* xb, const void* yb, const voi
  * The same sub-path for one decode step (T == 1 with caches)       torch/modules.py:631-646,
  *   xb, yb [B,E]; conv_cache_in [B,W-1,E]; h_in [B,E] float32     torch/layers.py:170-177, 469-474
  *   ->  out [B,E], h_out [B,E] float32, conv_cache_out [B,W-1,E]
- * h_out may alias h_in and conv_cache_out may alias conv_cache_in (in-place state update; aliasing
- * the conv cache selects a three-kernel path instead of the fused single-kernel step).
+ * h_out may alias h_in and conv_cache_out may alias conv_cache_in (in-place state update: the
+ * fused single-kernel step reads and then writes every state element from one and the same
+ * thread, so it runs in place as well).
  * segment_pos [B] still selects the reset behaviour of the RG-LRU (a position of 0 drops h_in).
  * ---------------------------------------------------------------------------------------------- */
 RGK_API int rgk_recurrent_path_decode(const void* xb, const void* yb, const void* segment_pos,

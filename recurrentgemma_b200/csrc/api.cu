@@ -872,6 +872,8 @@ int rgk_recurrent_path_decode(const void* xb, const void* yb, const void* segmen
   const PathWs w = carve(workspace, B, 1, E, dtype);
   RGK_REQUIRE(workspace != nullptr && workspace_bytes >= w.total, RGK_EWORKSPACE,
               "workspace of %zu bytes needed, %zu given", w.total, workspace_bytes);
+  RGK_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255u) == 0, RGK_EALIGN,
+              "workspace must be 256-byte aligned");
   RGK_CHECK_DEVICE();
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int bw = (int)(E / H);

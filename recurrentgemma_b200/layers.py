@@ -42,14 +42,16 @@ def rnn_param_init(
     tensor: torch.Tensor, min_rad: float, max_rad: float, transform: str = "softplus",
     eps: float = 1e-8,
 ) -> torch.Tensor:
-  """Ring-uniform init of the RG-LRU's `a_param` (recurrentgemma/torch/layers.py:194-213)."""
+  """Ring-uniform init of the RG-LRU's `a_param` (recurrentgemma/torch/layers.py:194-213):
+  softplus^-1(-0.5 ln u) with u uniform over [min_rad^2, max_rad^2) + eps.  The draw and every step
+  after it happen in place in the tensor's own dtype, as in the reference, so that one seed gives
+  the reference's values bit for bit (also in bfloat16, where each step rounds)."""
   if transform != "softplus":
     raise NotImplementedError(transform)
   with torch.no_grad():
-    u = torch.empty_like(tensor, dtype=torch.float32).uniform_(min_rad ** 2 + eps,
-                                                               max_rad ** 2 + eps)
-    a_real = -0.5 * torch.log(u)
-    tensor.copy_(torch.log(torch.expm1(a_real)))
+    tensor.uniform_(min_rad ** 2 + eps, max_rad ** 2 + eps)      # u
+    tensor.log_().mul_(-0.5)                                      # a_real = -0.5 ln u
+    tensor.exp_().sub_(1.0).log_()                                # ln(e^a_real - 1)
   return tensor
 
 
@@ -228,10 +230,26 @@ class RGLRU(nn.Module):
   def a_param_init(self, w: torch.Tensor) -> torch.Tensor:
     return rnn_param_init(w, min_rad=0.9, max_rad=0.999)
 
+  def invalidate_packed(self) -> None:
+    """Drops the packed copy of the gate weights; the next forward rebuilds it.  Needed after a
+    write that torch does not count (`param.data.copy_(...)`, a raw pointer write): the copy is
+    otherwise refreshed when a weight tensor is replaced, modified in place through autograd-visible
+    operations, loaded from a state_dict or moved / cast with `.to()` / `.cuda()`."""
+    self._pack_key = None
+
+  def _load_from_state_dict(self, *args, **kwargs):
+    self.invalidate_packed()
+    return super()._load_from_state_dict(*args, **kwargs)
+
+  def _apply(self, fn, *args, **kwargs):
+    self.invalidate_packed()
+    return super()._apply(fn, *args, **kwargs)
+
   def _packed_gates(self) -> Optional[int]:
     """Device pointer of the K-major copy of the gate weights the tcgen05 kernels read, rebuilt
     whenever either weight tensor is replaced or modified in place (a derived, non-persistent
-    buffer: it never enters the state_dict)."""
+    buffer: it never enters the state_dict).  Writes through `.data` bypass the version counter:
+    call `invalidate_packed()` after them."""
     wx, wa = self.input_gate.w, self.a_gate.w
     if (not wx.is_cuda or wx.dtype != torch.bfloat16 or self.width // self.num_heads != 256 or
         self.gates_impl == _lib.GATES_SIMT):

@@ -278,10 +278,24 @@ class MLPBlock(nn.Module):
     return (x.dtype == torch.bfloat16 and self.width % 8 == 0 and self.expanded_width % 64 == 0
             and x.numel() // x.shape[-1] >= SMALL_M)
 
+  def invalidate_packed(self) -> None:
+    """Drops the packed copy of ffw_up; the next forward rebuilds it.  Needed after a write that
+    torch does not count (`param.data.copy_(...)`); state_dict loads, `.to()` and counted in-place
+    writes refresh it by themselves."""
+    self._pack_key = None
+
+  def _load_from_state_dict(self, *args, **kwargs):
+    self.invalidate_packed()
+    return super()._load_from_state_dict(*args, **kwargs)
+
+  def _apply(self, fn, *args, **kwargs):
+    self.invalidate_packed()
+    return super()._apply(fn, *args, **kwargs)
+
   def _packed_up(self) -> int:
     """Device pointer of the K-major, gate/value-interleaved copy of ffw_up the GeGLU GEMM reads,
     rebuilt when either parameter is replaced or modified in place (derived, never in the
-    state_dict)."""
+    state_dict).  Writes through `.data` bypass the version counter: call `invalidate_packed()`."""
     w, b = self.ffw_up.w, self.ffw_up.b
     key = (w.data_ptr(), w._version, b.data_ptr(), b._version)
     if getattr(self, "_pack_key", None) != key:

@@ -51,20 +51,37 @@ def batch_range(batch: int, world: int, rank: int) -> Tuple[int, int]:
 
 def shard_state_dict(sd: Dict[str, torch.Tensor], width: int, num_heads: int, world: int,
                      rank: int) -> Dict[str, torch.Tensor]:
-  """Slices the RG-LRU / Conv1D entries of a state_dict (of an RGLRU, a Conv1D or a whole
-  RecurrentBlock) to this rank's heads.  Entries that are not on the path are returned whole."""
+  """Slices the RG-LRU / Conv1D entries of a state_dict to this rank's heads: the state_dict of an
+  RGLRU, of a Conv1D (bare keys `w` [W, width] and `b` [width]) or of a RecurrentBlock.  Entries
+  that are not on the path are returned whole - in particular the block's dense projections
+  (`linear_x`, `linear_y`: a head-sharded block needs their output rows sliced, `linear_out` its
+  input columns, with a reduction after it), which this function does not attempt.  Raises if
+  nothing in the dictionary was recognised, rather than returning it unsliced."""
   h0, h1 = head_range(num_heads, world, rank)
   e0, e1 = channel_range(width, num_heads, world, rank)
   out = {}
+  hits = 0
   for name, t in sd.items():
     sliced = t
     for suffix, axis in _HEAD_AXIS.items():
       if name.endswith(suffix):
         sliced = t.narrow(axis, h0, h1 - h0)
+        hits += 1
     for suffix, axis in _CHANNEL_AXIS.items():
       if name.endswith(suffix):
         sliced = t.narrow(axis, e0, e1 - e0)
+        hits += 1
+    # a Conv1D's own state_dict: w [W, width], b [width]
+    if name == "w" and t.ndim == 2 and t.shape[1] == width:
+      sliced = t.narrow(1, e0, e1 - e0)
+      hits += 1
+    if name == "b" and t.ndim == 1 and t.shape[0] == width:
+      sliced = t.narrow(0, e0, e1 - e0)
+      hits += 1
     out[name] = sliced.contiguous()
+  if sd and hits == 0:
+    raise ValueError("no RG-LRU / Conv1D parameter found in the state_dict: nothing was sliced "
+                     f"(keys: {sorted(sd)[:6]} ...)")
   return out
 
 

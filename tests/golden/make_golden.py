@@ -36,6 +36,9 @@ def import_reference(path: str):
   return rg, layers, modules
 
 
+PARAM_INIT_SEED, PARAM_INIT_WIDTH = 7, 2560
+
+
 def _np(t):
   # a copy: the reference updates its attention cache in place during later decode steps
   return t.detach().to(torch.float32).numpy().copy()
@@ -206,6 +209,17 @@ def main():
     np.savez_compressed(path, **res)
     total += os.path.getsize(path)
     print(f"{case.name:44s} {os.path.getsize(path)/1024:8.1f} KiB")
+  # rnn_param_init (torch/layers.py:194-213) draws from torch's global generator: the fixture pins
+  # what a given seed produces, in both dtypes the path runs in.
+  path = os.path.join(HERE, "rnn_param_init.npz")
+  if not (args.only_missing and os.path.exists(path)):
+    res = {}
+    for name, dt in (("float32", torch.float32), ("bfloat16", torch.bfloat16)):
+      torch.manual_seed(PARAM_INIT_SEED)
+      res[name] = _np(layers.rnn_param_init(torch.empty(PARAM_INIT_WIDTH, dtype=dt), min_rad=0.9,
+                                            max_rad=0.999))
+    np.savez_compressed(path, **res)
+    total += os.path.getsize(path)
   print(f"total {total/1024:.1f} KiB")
 
 

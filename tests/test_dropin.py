@@ -1,8 +1,11 @@
-"""Structural drop-in check against the reference checkout, when one is available.
+"""Drop-in checks against the reference checkout, when one is available.
 
-Runs on CPU: the reference `Griffin` is built, its recurrent blocks are swapped for ours, and the
-state_dict keys, cache types and the "no CPU path" behaviour are checked.  Skipped where the
-checkout is absent (e.g. on a GPU box)."""
+On CPU: the reference `Griffin` is built, its recurrent blocks are swapped for ours, and the
+state_dict keys, cache types and the "no CPU path" behaviour are checked.  Where a checkout AND a
+GPU are present, the converted model also runs on the GPU against the untouched model on the CPU.
+The checkout is found through RECURRENTGEMMA_REFERENCE, else as a directory `reference` beside
+this repository; without one every test here is skipped (the reference sources are never copied
+into this repository, so a machine that only receives the repository has none)."""
 import os
 import sys
 import types
@@ -10,7 +13,8 @@ import types
 import pytest
 import torch
 
-REF = os.environ.get("RECURRENTGEMMA_REFERENCE", "/root/reference")
+_REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REF = os.environ.get("RECURRENTGEMMA_REFERENCE") or os.path.join(os.path.dirname(_REPO), "reference")
 
 pytestmark = pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "recurrentgemma", "torch")),
                                 reason="reference checkout not available")
@@ -182,3 +186,41 @@ def test_config_preset_and_sampler_positions(rg):
   own = sampler._own(cache)
   assert list(own) == list(cache)
   assert all(a.data_ptr() != b.data_ptr() for k in cache for a, b in zip(cache[k], own[k]))
+
+
+@pytest.mark.gpu
+def test_converted_reference_model_on_gpu_matches_reference_on_cpu(rg):
+  """The reference `Griffin` (recurrentgemma/torch/griffin.py:131-190) with `dropin.convert` and
+  `dropin.fuse_residual_block` applied, on the GPU in bfloat16, against the untouched reference model
+  on the CPU: logits and caches of a prefill and of two decode steps fed with the returned caches -
+  the equivalence the reference checks for itself in torch/sampler_test.py:150-230."""
+  import copy
+  from recurrentgemma_b200 import dropin
+  from tests.util import TOL, assert_close
+  if not torch.cuda.is_available():
+    pytest.skip("needs a GPU")
+  torch.manual_seed(3)
+  dt = torch.bfloat16
+  ref = rg.Griffin(_config(), dtype=dt)
+  with torch.no_grad():
+    for prm in ref.parameters():          # norm scales and biases start at zero: make them count
+      if prm.abs().sum() == 0:
+        prm.normal_(0.0, 0.1)
+  ours = dropin.fuse_residual_block(dropin.convert(copy.deepcopy(ref))).to("cuda")
+  b, t = 2, 24
+  tokens = torch.randint(0, 64, (b, t + 2))
+  pos = torch.arange(t + 2)[None].repeat(b, 1)
+  with torch.no_grad():
+    lr, cr = ref(tokens[:, :t], pos[:, :t], None, return_logits=True, return_cache=True)
+    lo, co = ours(tokens[:, :t].cuda(), pos[:, :t].cuda(), None, return_logits=True, return_cache=True)
+    assert_close(lo, lr, TOL[dt], "prefill logits")
+    for i in range(2):
+      lr, cr = ref(tokens[:, t + i:t + i + 1], pos[:, t + i:t + i + 1], cr, return_logits=True,
+                   return_cache=True)
+      lo, co = ours(tokens[:, t + i:t + i + 1].cuda(), pos[:, t + i:t + i + 1].cuda(), co,
+                    return_logits=True, return_cache=True)
+      assert_close(lo, lr, TOL[dt], f"decode step {i} logits")
+    for name in cr:
+      for a, r in zip(co[name], cr[name]):
+        if r.dtype.is_floating_point:
+          assert_close(a, r, TOL[dt], f"cache {name}")

@@ -94,3 +94,33 @@ def test_second_device_in_one_process():
       outs.append((y.float().cpu(), z.float().cpu(), ys.cpu()))
   for a0, a1 in zip(outs[0], outs[1]):
     torch.testing.assert_close(a0, a1, rtol=2e-2, atol=2e-2)
+
+
+def test_packed_gate_weights_follow_uncounted_writes():
+  """`param.data.copy_()` (the usual checkpoint-loader idiom) neither moves the tensor nor bumps its
+  version counter, so the K-major copy of the gate weights cannot notice it: load_state_dict and
+  `.to()` refresh the copy by themselves, a `.data` write needs `invalidate_packed()`."""
+  import recurrentgemma_b200 as rg
+  from recurrentgemma_b200 import synthetic
+  dev = torch.device(DEV)
+  g = torch.Generator().manual_seed(11)
+  p1 = synthetic.rglru_params(256, 1, g, torch.bfloat16)
+  p2 = synthetic.rglru_params(256, 1, g, torch.bfloat16)
+  x = torch.randn((1, 256, 256), generator=g).to(torch.bfloat16).to(dev)
+  pos = torch.arange(256).repeat(1, 1).to(dev)
+  ref = rg.RGLRU(256, 1, device=dev, dtype=torch.bfloat16)
+  ref.load_state_dict(p2)
+  y2, _ = ref(x, pos)
+  m = rg.RGLRU(256, 1, device=dev, dtype=torch.bfloat16)
+  m.load_state_dict(p1)
+  y1, _ = m(x, pos)
+  assert not torch.equal(y1, y2)
+  m.load_state_dict(p2)                       # refreshed by the load hook
+  assert torch.equal(m(x, pos)[0], y2)
+  m.load_state_dict(p1)
+  m(x, pos)
+  for name, t in p2.items():                  # an uncounted write ...
+    mod, attr = name.rsplit(".", 1) if "." in name else ("", name)
+    getattr(m.get_submodule(mod) if mod else m, attr).data.copy_(t.to(dev))
+  m.invalidate_packed()                       # ... needs the explicit call
+  assert torch.equal(m(x, pos)[0], y2)

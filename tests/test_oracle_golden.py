@@ -183,3 +183,16 @@ def test_thread_count_is_settable(oracle):
   want = min(2, os.cpu_count() or 1)
   assert oracle.set_threads(want) in (want, 1)      # 1: built without OpenMP
   oracle.set_threads(before)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+def test_rnn_param_init_matches_reference_on_a_seed(dtype):
+  """rnn_param_init (torch/layers.py:194-213) draws from torch's global generator; the same seed
+  must give the reference's a_param exactly (fixture generated by the reference)."""
+  from recurrentgemma_b200 import layers
+  from tests.golden import make_golden as G
+  g = load_golden("rnn_param_init")
+  torch.manual_seed(G.PARAM_INIT_SEED)
+  t = layers.rnn_param_init(torch.empty(G.PARAM_INIT_WIDTH, dtype=dtype), min_rad=0.9, max_rad=0.999)
+  name = "float32" if dtype == torch.float32 else "bfloat16"
+  assert torch.equal(t.float(), torch.from_numpy(g[name]))

@@ -37,6 +37,12 @@ def test_shard_state_dict_shapes():
   assert s1["linear_x.weight"].shape == sd["linear_x.weight"].shape   # not on the sharded path
   assert torch.equal(s1["rg_lru.a_param"], sd["rg_lru.a_param"][256:])
   assert torch.equal(s1["conv_1d.w"], sd["conv_1d.w"][:, 256:])
+  # a Conv1D's own state_dict has bare keys
+  bare = sharding.shard_state_dict({"w": sd["conv_1d.w"], "b": sd["conv_1d.b"]}, 512, 4, 2, 0)
+  assert torch.equal(bare["w"], sd["conv_1d.w"][:, :256]) and bare["b"].shape == (256,)
+  # a dictionary with nothing of the path in it is refused rather than passed through
+  with pytest.raises(ValueError):
+    sharding.shard_state_dict({"linear_x.weight": sd["linear_x.weight"]}, 512, 4, 2, 0)
 
 
 def _worker(rank: int, world: int, port: int, out_dir: str):
