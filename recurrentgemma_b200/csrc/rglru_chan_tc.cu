@@ -57,14 +57,15 @@ constexpr int kSub = 32;                 // a warp's tile: 32 tokens x 32 channe
 constexpr int kSubBytes = kSub * kSub * 2;
 constexpr int kOffRing = 0;
 constexpr int kOffTiles = kRing * kStage;                      // per warp: conv tile, then y/out tile
-constexpr int kOffQmap = kOffTiles + kEpi * 2 * kSubBytes;     // float2 [2 parity][4 chq][4 tq][32]
-constexpr int kOffHin = kOffQmap + 2 * 4 * 4 * 32 * 8;         // float  [2 parity][4 chq][32]
+constexpr int kOffQmap = kOffTiles + kEpi * 2 * kSubBytes;     // float2 [2 parity][4 chq][3 tq][32]
+constexpr int kOffHin = kOffQmap + 2 * 4 * 3 * 32 * 8;         // float  [2 parity][4 chq][32]
 constexpr int kOffKnown = kOffHin + 2 * 4 * 32 * 4;              // int    [2 parity][4 chq]
 constexpr int kOffBar = kOffKnown + 2 * 4 * 4;
 constexpr int kNumBar = 2 * kRing + 4 + 2 * kEpi;
 constexpr int kOffTmem = kOffBar + kNumBar * 8;
 constexpr int kOffAbort = kOffTmem + 4;
-constexpr int kSmem = kOffAbort + 4 + 1024;
+constexpr int kOffLut = (kOffAbort + 4 + 15) & ~15;            // {a, multiplier} by log_a, see tc_common.cuh
+constexpr int kSmem = kOffLut + kLutEntries * 4 + 1024;
 static_assert(kSmem <= 232448, "exceeds the 227 KiB of shared memory a CTA may use");
 constexpr uint32_t kIdesc = tc_idesc_bf16(kUC, kUT);
 constexpr unsigned kLookbackSpins = 1u << 20;
@@ -130,13 +131,13 @@ template <bool kResets, int kMath>
 __device__ __forceinline__ void gates_16(const uint32_t (&zx)[16], const uint32_t (&za)[16],
                                          const uint32_t (&c)[8], uint32_t bx2, uint32_t ba2, uint32_t hbx2,
                                          uint32_t m8sp2, uint32_t rs, uint32_t inv, uint32_t* a_out,
-                                         uint32_t* x_out, float& P, float& H) {
+                                         uint32_t* x_out, float& P, float& H, const uint32_t* lut) {
 #pragma unroll
   for (int jp = 0; jp < 8; ++jp) {
     uint32_t a2, gx2, mult2;
-    gate_tokens<kMath>(__uint_as_float(zx[2 * jp]), __uint_as_float(zx[2 * jp + 1]),
-                       __uint_as_float(za[2 * jp]), __uint_as_float(za[2 * jp + 1]), bx2, ba2, hbx2,
-                       m8sp2, a2, gx2, mult2);
+    gate_tokens<kMath, true>(__uint_as_float(zx[2 * jp]), __uint_as_float(zx[2 * jp + 1]),
+                             __uint_as_float(za[2 * jp]), __uint_as_float(za[2 * jp + 1]), bx2, ba2,
+                             hbx2, m8sp2, a2, gx2, mult2, lut);
     if constexpr (kResets) {
       // a token that starts a document: a = 0, multiplier = 1 (torch/layers.py:343-350, 166)
       const uint32_t keep = (((rs >> (2 * jp)) & 1u) ? 0u : 0x0000ffffu) |
@@ -271,6 +272,10 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
   const int per_tt = B * groups;                         // units per time tile
   const int n_my = (n_units - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
 
+  // a = exp(log_a) and the input multiplier by log_a: computed once per CTA with the very
+  // operations the gate arithmetic would use, so that looking them up changes no bit
+  uint32_t* s_lut = reinterpret_cast<uint32_t*>(smem + kOffLut);
+  for (int i = threadIdx.x; i < kLutEntries; i += kThreads) s_lut[i] = a_mult_entry(i);
   if (threadIdx.x == 0) {
     *s_abort = 0;
     for (int s = 0; s < kRing; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
@@ -396,7 +401,7 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
       const int64_t rec = ((int64_t)(tt * per_tt + b * groups + cur.grp)) * 4 + chq;
       nxt = cur;
       step.advance(nxt);
-      float2* s_qmap = reinterpret_cast<float2*>(smem + kOffQmap) + ((par * 4 + chq) * 4) * 32;
+      float2* s_qmap = reinterpret_cast<float2*>(smem + kOffQmap) + ((par * 4 + chq) * 3) * 32;
       float* s_hin = reinterpret_cast<float*>(smem + kOffHin) + (par * 4 + chq) * 32;
       volatile int* s_known = reinterpret_cast<volatile int*>(smem + kOffKnown) + (par * 4 + chq);
 
@@ -456,10 +461,10 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
         const uint32_t inv = (invalid >> (half * 16)) & 0xffffu;
         if ((rs | inv) == 0u)
           gates_16<false, kMath>(zx, za, c, bx2, ba2, hbx2, m8sp2, rs, inv, a_pk + half * 8,
-                                 x_pk + half * 8, P, H);
+                                 x_pk + half * 8, P, H, s_lut);
         else
           gates_16<true, kMath>(zx, za, c, bx2, ba2, hbx2, m8sp2, rs, inv, a_pk + half * 8,
-                                x_pk + half * 8, P, H);
+                                x_pk + half * 8, P, H, s_lut);
         if (half == 0) {
           // the previous unit's output tile must have been read by its store before the buffer is
           // written again; then the other branch's tile of this unit is fetched into it
@@ -494,7 +499,7 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
         if (have_hin) s_hin[lane] = hin_pref;
         if (lane == 0) *s_known = have_hin ? 1 : 0;
       }
-      s_qmap[tq * 32 + lane] = make_float2(P, H);
+      if (tq < 3) s_qmap[tq * 32 + lane] = make_float2(P, H);   // the last quarter keeps its own
       named_bar_sync(set_id, 128);
       const bool known = *s_known != 0;
 
@@ -502,11 +507,13 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
       if (tq == 3) {
         float Pt = 1.0f, Ht = 0.0f;
 #pragma unroll
-        for (int qq = 0; qq < 4; ++qq) {
+        for (int qq = 0; qq < 3; ++qq) {
           const float2 m = s_qmap[qq * 32 + lane];
           Ht = fmaf(m.x, Ht, m.y);
           Pt *= m.x;
         }
+        Ht = fmaf(P, Ht, H);
+        Pt *= P;
         float hin = hin_pref;
         if (!known) {
           // Decoupled look-back, one channel per lane.  With use_agg (fewer chains than CTAs: the

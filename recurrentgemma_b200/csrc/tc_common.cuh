@@ -239,10 +239,45 @@ __device__ __forceinline__ uint32_t btanh2(uint32_t a) {
 //   zx, za   float32 accumulators of the two tokens;  bx2, ba2, m8sp2: the channel's biases and
 //   -8 softplus(a_param), each duplicated into both halves;  hbx2: half the input-gate bias.
 // Returns packed a, x-gate and input multiplier, resets not yet applied.
-template <int kMath>
+// a = exp(log_a) and the input multiplier sqrt(1 - exp(2 log_a)) of a token pair, every rounding
+// of the reference (torch/layers.py:343-350): both are functions of the bfloat16 value log_a alone.
+__device__ __forceinline__ void a_mult_of_log_a(uint32_t la2, uint32_t& a2, uint32_t& mult2) {
+  constexpr float kLog2e = 1.4426950408889634f;
+  const float e0 = ex2f(bf16_lo(la2) * kLog2e), e1 = ex2f(bf16_hi(la2) * kLog2e);
+  a2 = pack_bf16x2(e0, e1);
+  const uint32_t om2 = bsub2(0x3f803f80u, pack_bf16x2(e0 * e0, e1 * e1));   // 1 - exp(2 log_a)
+  mult2 = pack_bf16x2(sqrtf_approx(bf16_lo(om2)), sqrtf_approx(bf16_hi(om2)));
+}
+
+// The same from a table in shared memory, indexed by the magnitude bits of log_a (log_a <= 0).
+// Up to 2^-11 both roundings give a = 1, multiplier 0 (the first entry); from 128 on a = 0,
+// multiplier 1 (the last entry): 18 binades x 128 values, one 32-bit entry {a, multiplier} each.
+constexpr uint32_t kLutBase = 0x3a00u;                 // bits of 2^-11
+constexpr int kLutEntries = 0x4300 - 0x3a00;           // up to 128.0 (exclusive)
+__device__ __forceinline__ uint32_t a_mult_entry(uint32_t index) {
+  const uint32_t la = 0x8000u | (kLutBase + index);
+  uint32_t a2, mult2;
+  a_mult_of_log_a(la | (la << 16), a2, mult2);
+  return (a2 & 0xffffu) | (mult2 << 16);
+}
+__device__ __forceinline__ void a_mult_lookup(uint32_t la2, const uint32_t* lut, uint32_t& a2,
+                                              uint32_t& mult2) {
+  constexpr uint32_t kBase2 = kLutBase | (kLutBase << 16);
+  constexpr uint32_t kTop2 = (kLutBase + kLutEntries - 1) | ((kLutBase + kLutEntries - 1) << 16);
+  uint32_t m = la2 & 0x7fff7fffu, t;
+  asm("max.u16x2 %0, %1, %2;" : "=r"(t) : "r"(m), "r"(kBase2));
+  asm("min.u16x2 %0, %1, %2;" : "=r"(m) : "r"(t), "r"(kTop2));
+  m -= kBase2;                                          // no borrow: each half is at least the base
+  const uint32_t e0 = lut[m & 0xffffu], e1 = lut[m >> 16];
+  asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(a2) : "r"(e0), "r"(e1));
+  asm("prmt.b32 %0, %1, %2, 0x7632;" : "=r"(mult2) : "r"(e0), "r"(e1));
+}
+
+template <int kMath, bool kLut = false>
 __device__ __forceinline__ void gate_tokens(float zx0, float zx1, float za0, float za1, uint32_t bx2,
                                             uint32_t ba2, uint32_t hbx2, uint32_t m8sp2, uint32_t& a2,
-                                            uint32_t& gx2, uint32_t& mult2) {
+                                            uint32_t& gx2, uint32_t& mult2,
+                                            const uint32_t* lut = nullptr) {
   constexpr float kNegLog2e = -1.4426950408889634f;
   uint32_t ga2;
   if constexpr (kMath == kMathExact) {
@@ -268,10 +303,11 @@ __device__ __forceinline__ void gate_tokens(float zx0, float zx1, float za0, flo
   }
   // log_a = (-8 gate_a) softplus(a_param): -8 is exact in bfloat16 and folded into the constant
   const uint32_t la2 = bmul2(ga2, m8sp2);
-  const float e0 = ex2f(bf16_lo(la2) * -kNegLog2e), e1 = ex2f(bf16_hi(la2) * -kNegLog2e);
-  a2 = pack_bf16x2(e0, e1);
-  const uint32_t om2 = bsub2(0x3f803f80u, pack_bf16x2(e0 * e0, e1 * e1));   // 1 - exp(2 log_a)
-  mult2 = pack_bf16x2(sqrtf_approx(bf16_lo(om2)), sqrtf_approx(bf16_hi(om2)));
+  if constexpr (kLut) {
+    a_mult_lookup(la2, lut, a2, mult2);
+  } else {
+    a_mult_of_log_a(la2, a2, mult2);
+  }
 }
 
 // y2 * gelu_tanh(z2) for a token pair of one channel (torch/modules.py:289-291, 646): the gelu
