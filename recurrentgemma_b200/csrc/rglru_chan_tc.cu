@@ -422,21 +422,26 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
         else pre = ld_relaxed_u64(incl + (rec - (int64_t)per_tt * 4) * kSub + lane);
       }
 
-      // ---- the conv tile: transposed in place, a thread then finds its channel's 32 tokens ----------
-      if (ok) ok = mbar_wait(bar_ct(warp), t & 1, s_abort);
-      transpose_tile(tile_c_s + row_off, tile_c_s + st_off);
-
       // ---- gates of the thread's 32 tokens, 16 at a time ------------------------------------------
       if (ok) ok = mbar_wait(bar_acc_full(as), (t >> 1) & 1, s_abort);
       tc_fence_after();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(chq * 32) << 16) + as * 2 * kUT + tq * kSub;
+      uint32_t zx[16], za[16];
+      tc_ld_32x16(t_row, zx);
+      tc_ld_32x16(t_row + kUT, za);
+      // while the accumulator columns are on their way from tensor memory: the conv tile is
+      // transposed in place, a thread then finds its channel's 32 tokens in its own row
+      if (ok) ok = mbar_wait(bar_ct(warp), t & 1, s_abort);
+      transpose_tile(tile_c_s + row_off, tile_c_s + st_off);
       uint32_t a_pk[16], x_pk[16];
       float P = 1.0f, H = 0.0f;
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
-        uint32_t zx[16], za[16], c[8];
-        tc_ld_32x16(t_row + half * 16, zx);
-        tc_ld_32x16(t_row + kUT + half * 16, za);
+        uint32_t c[8];
+        if (half == 1) {
+          tc_ld_32x16(t_row + 16, zx);
+          tc_ld_32x16(t_row + kUT + 16, za);
+        }
         {
           const uint4 c0 = lds_piece(tile_c_s + row_off, 2 * half), c1 = lds_piece(tile_c_s + row_off, 2 * half + 1);
           c[0] = c0.x; c[1] = c0.y; c[2] = c0.z; c[3] = c0.w;
