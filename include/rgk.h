@@ -44,7 +44,9 @@ typedef enum rgk_status {
   RGK_EARCH = -4,      /* current device is not sm_100 */
   RGK_ECUDA = -5,      /* a CUDA runtime call failed (message holds cudaGetErrorString) */
   RGK_EWORKSPACE = -6, /* workspace missing or too small */
-  RGK_ETIMEOUT = -7    /* a bounded device-side wait expired (reported by rgk_workspace_status) */
+  RGK_ETIMEOUT = -7,   /* a bounded device-side wait expired (reported by rgk_workspace_status) */
+  RGK_EBOUNDS = -8     /* only from a library built with -DRGK_CHECKS: a computed index fell outside
+                          its array; the access was skipped (reported by rgk_workspace_status) */
 } rgk_status;
 
 enum { RGK_F32 = 0, RGK_BF16 = 1 };

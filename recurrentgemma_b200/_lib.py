@@ -13,12 +13,13 @@ from typing import Optional
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "librgk.so")
+# RGK_LIBRARY selects another build of the library, e.g. librgk_checks.so (range-checked indices)
+LIB_PATH = os.environ.get("RGK_LIBRARY") or os.path.join(_HERE, "librgk.so")
 
 RGK_F32, RGK_BF16 = 0, 1
 # rgk_status codes of include/rgk.h
 (RGK_OK, RGK_EINVAL, RGK_ESHAPE, RGK_EALIGN, RGK_EARCH, RGK_ECUDA, RGK_EWORKSPACE,
- RGK_ETIMEOUT) = 0, -1, -2, -3, -4, -5, -6, -7
+ RGK_ETIMEOUT, RGK_EBOUNDS) = 0, -1, -2, -3, -4, -5, -6, -7, -8
 RGK_I32, RGK_I64 = 0, 1
 GATES_AUTO, GATES_SIMT, GATES_TCGEN05, GATES_FUSED, GATES_FUSED_EXACT = 0, 1, 2, 3, 4
 

@@ -203,6 +203,11 @@ int rgk_workspace_status(void* workspace, void* stream) {
   int status = 0;
   RGK_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)), "cudaStreamSynchronize");
   RGK_CUDA(cudaMemcpy(&status, workspace, sizeof(int), cudaMemcpyDeviceToHost), "cudaMemcpy");
+  if (status == rgk::kStatusBounds) {
+    RGK_CUDA(cudaMemset(workspace, 0, sizeof(int)), "cudaMemset");
+    return fail(RGK_EBOUNDS, "a range-checked index fell outside its array (checks build); the "
+                             "access was skipped and the results are invalid");
+  }
   if (status == rgk::kStatusTimeout) {
     // reported once: the word is cleared so that later calls are judged on their own
     RGK_CUDA(cudaMemset(workspace, 0, sizeof(int)), "cudaMemset");

@@ -17,6 +17,23 @@ struct WsHeader {
 static_assert(sizeof(WsHeader) == 256, "header is 256 bytes");
 
 constexpr int kStatusTimeout = -7;
+constexpr int kStatusBounds = -8;
+
+// Range checks of computed indices for the -DRGK_CHECKS build (python -m recurrentgemma_b200.build
+// --checks): an index outside its array raises WsHeader::status to kStatusBounds and the access is
+// skipped - nothing traps, the kernel runs on.  In the normal build the macro is the bare condition
+// `true`, so that `if (RGK_IN_RANGE(...)) access;` costs nothing.
+#ifdef RGK_CHECKS
+#define RGK_IN_RANGE(index, count, status_ptr) \
+  rgk::index_in_range((long long)(index), (long long)(count), (status_ptr))
+#else
+#define RGK_IN_RANGE(index, count, status_ptr) true
+#endif
+__device__ __forceinline__ bool index_in_range(long long index, long long count, int* status) {
+  if (index >= 0 && index < count) return true;
+  if (status != nullptr) atomicExch(status, kStatusBounds);
+  return false;
+}
 
 // ------------------------------------------------------------------------------------------------
 // dtype traits.  A "pack" is 16 bytes: 4 float32 or 8 bfloat16 channels.

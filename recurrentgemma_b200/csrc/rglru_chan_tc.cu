@@ -167,7 +167,8 @@ __device__ __forceinline__ void gates_16(const uint32_t (&zx)[16], const uint32_
 // returns the state entering tile tt.
 __device__ __forceinline__ float look_back(const unsigned long long* agg, const unsigned long long* incl,
                                         const float* h0, int64_t rec, int tt, int per_tt, int b, int E,
-                                        int chan, int lane, int use_agg, bool* timed_out_p) {
+                                        int chan, int lane, int use_agg, bool* timed_out_p,
+                                        int64_t n_words, int64_t n_state, int* status) {
   float hin = 0.0f;
   bool timed_out = false;
   {
@@ -184,10 +185,12 @@ __device__ __forceinline__ float look_back(const unsigned long long* agg, const 
         wi[i] = 0ull; wp[i] = 0ull; wh[i] = 0ull;
         if (i < depth && pt >= 0) {
           const int64_t rp = (rec - (int64_t)(tt - pt) * per_tt * 4) * kSub + lane;
-          wi[i] = ld_relaxed_u64(incl + rp);
-          if (use_agg) {
-            wp[i] = ld_relaxed_u64(agg + rp * 2);
-            wh[i] = ld_relaxed_u64(agg + rp * 2 + 1);
+          if (RGK_IN_RANGE(rp, n_words, status)) {
+            wi[i] = ld_relaxed_u64(incl + rp);
+            if (use_agg) {
+              wp[i] = ld_relaxed_u64(agg + rp * 2);
+              wh[i] = ld_relaxed_u64(agg + rp * 2 + 1);
+            }
           }
         }
       }
@@ -213,7 +216,8 @@ __device__ __forceinline__ float look_back(const unsigned long long* agg, const 
       }
       if (!done && pred < 0) {
         // every tile back to the start of the sequence was absorbed as a map
-        const float hs = h0 != nullptr ? h0[(int64_t)b * E + chan] : 0.0f;
+        const float hs = (h0 != nullptr && RGK_IN_RANGE((int64_t)b * E + chan, n_state, status))
+                             ? h0[(int64_t)b * E + chan] : 0.0f;
         hin = fmaf(Pc, hs, Hc);
         done = true;
       }
@@ -353,6 +357,9 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
     const uint32_t row_off = lane * 64 + (((lane >> 1) & 3) << 4);
     const uint32_t st_off = (lane & 7) * 64 + (((lane >> 3) ^ ((lane >> 1) & 3)) << 4);
     bool ok = true;                          // false once a bounded wait expired: later waits are skipped
+    // extents of the record arrays and of the state tensors, for the range checks of the checks build
+    const int64_t n_words = (int64_t)n_units * 4 * kSub, n_state = (int64_t)B * E;
+    (void)n_words; (void)n_state;
 
     // unit positions without divisions in the loop
     UnitStep step;
@@ -418,8 +425,12 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
       bool have_hin = tt == 0;
       unsigned long long pre = 0ull;
       if (tq == 3) {
-        if (tt == 0) hin_pref = h0 != nullptr ? h0[(int64_t)b * E + e0 + lane] : 0.0f;
-        else pre = ld_relaxed_u64(incl + (rec - (int64_t)per_tt * 4) * kSub + lane);
+        if (tt == 0) {
+          if (h0 != nullptr && RGK_IN_RANGE((int64_t)b * E + e0 + lane, n_state, &hdr->status))
+            hin_pref = h0[(int64_t)b * E + e0 + lane];
+        } else if (RGK_IN_RANGE((rec - (int64_t)per_tt * 4) * kSub + lane, n_words, &hdr->status)) {
+          pre = ld_relaxed_u64(incl + (rec - (int64_t)per_tt * 4) * kSub + lane);
+        }
       }
 
       // ---- gates of the thread's 32 tokens, 16 at a time ------------------------------------------
@@ -525,12 +536,13 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
           // earlier tiles of this chain are in flight on other SMs) the tile's own map is published
           // first, and maps of earlier tiles are composed until a tile with a known state is met;
           // otherwise only the predecessor's state is waited for (it was dealt out a round earlier).
-          if (use_agg) {
+          if (use_agg && RGK_IN_RANGE(rec * kSub + lane, n_words, &hdr->status)) {
             st_relaxed_u64(agg + (rec * kSub + lane) * 2, kToken | (unsigned long long)__float_as_uint(Pt));
             st_relaxed_u64(agg + (rec * kSub + lane) * 2 + 1, kToken | (unsigned long long)__float_as_uint(Ht));
           }
           bool timed_out = false;
-          if (ok) hin = look_back(agg, incl, h0, rec, tt, per_tt, b, E, e0 + lane, lane, use_agg, &timed_out);
+          if (ok) hin = look_back(agg, incl, h0, rec, tt, per_tt, b, E, e0 + lane, lane, use_agg, &timed_out,
+                                 n_words, n_state, &hdr->status);
           __syncwarp();
           if (__any_sync(0xffffffffu, timed_out)) {
             if (lane == 0) atomicExch(&hdr->status, kStatusTimeout);
@@ -540,8 +552,11 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
           s_hin[lane] = hin;
         }
         const float h_end = fmaf(Pt, hin, Ht);
-        st_relaxed_u64(incl + rec * kSub + lane, kToken | (unsigned long long)__float_as_uint(h_end));
-        if (h_last != nullptr && tt == tiles_t - 1) h_last[(int64_t)b * E + e0 + lane] = h_end;
+        if (RGK_IN_RANGE(rec * kSub + lane, n_words, &hdr->status))
+          st_relaxed_u64(incl + rec * kSub + lane, kToken | (unsigned long long)__float_as_uint(h_end));
+        if (h_last != nullptr && tt == tiles_t - 1 &&
+            RGK_IN_RANGE((int64_t)b * E + e0 + lane, n_state, &hdr->status))
+          h_last[(int64_t)b * E + e0 + lane] = h_end;
       }
       if (!known) named_bar_sync(set_id, 128);
 

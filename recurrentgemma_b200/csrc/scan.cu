@@ -129,6 +129,9 @@ scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
   __syncthreads();
   const unsigned tile = s_misc[0];
   const int nseq = B * groups;
+  // extents for the range checks of the checks build
+  const int64_t n_tiles_all = (int64_t)tiles_t * nseq, n_act = (int64_t)B * T_ * E;
+  (void)n_tiles_all; (void)n_act;
   const int tt = tile / nseq;
   const int seq = tile - tt * nseq;
   const int b = seq / groups;
@@ -232,9 +235,9 @@ scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
       const int e = g * kChan + tid;
       const float hin = (h0 != nullptr && e < E) ? h0[(int64_t)b * E + e] : 0.0f;
       s_hin[tid] = hin;
-      incl[rec * kChan + tid] = fmaf(P, hin, Hh);
+      if (RGK_IN_RANGE(rec, n_tiles_all, &hdr->status)) incl[rec * kChan + tid] = fmaf(P, hin, Hh);
     } else {
-      agg[rec * kChan + tid] = make_float2(P, Hh);
+      if (RGK_IN_RANGE(rec, n_tiles_all, &hdr->status)) agg[rec * kChan + tid] = make_float2(P, Hh);
     }
   }
   // The barrier orders the 64 record stores before thread 0's release store, and a release is
@@ -255,7 +258,8 @@ scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
       int L = 32;
       unsigned spins = 0;
       while (true) {
-        if (pred >= 0) f = ld_acquire(&flags[(int64_t)pred * nseq + seq]);
+        if (pred >= 0 && RGK_IN_RANGE((int64_t)pred * nseq + seq, n_tiles_all, &hdr->status))
+          f = ld_acquire(&flags[(int64_t)pred * nseq + seq]);
         const unsigned incl_mask = __ballot_sync(0xffffffffu, f == 2u);
         L = incl_mask ? (__ffs(incl_mask) - 1) : 32;
         const unsigned need = (L >= 31) ? 0xffffffffu : ((2u << L) - 1u);
@@ -374,7 +378,8 @@ scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
         }
         o = pack<T>(out);
       }
-      st_stream(y + (row0 + t0 + r) * E + e0, o);
+      if (RGK_IN_RANGE((row0 + t0 + r) * E + e0, n_act, &hdr->status))
+        st_stream(y + (row0 + t0 + r) * E + e0, o);
     }
   }
 }

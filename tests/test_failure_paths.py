@@ -124,3 +124,26 @@ def test_packed_gate_weights_follow_uncounted_writes():
     getattr(m.get_submodule(mod) if mod else m, attr).data.copy_(t.to(dev))
   m.invalidate_packed()                       # ... needs the explicit call
   assert torch.equal(m(x, pos)[0], y2)
+
+
+def test_range_checked_build_runs_the_path_tests_clean():
+  """librgk_checks.so (-DRGK_CHECKS) range-checks the computed indices of the look-back records, the
+  states and the outputs of the scan and of the fused RG-LRU kernel: an index outside its array would
+  raise the status word to RGK_EBOUNDS and skip the access.  The scan and fused-kernel parity tests
+  (ragged lengths, many time tiles, carries across rounds, the long shard) run on that build in a
+  child process; they check the status word after every call, so a bad index fails them."""
+  import os
+  import subprocess
+  import sys
+  from recurrentgemma_b200 import _lib
+  root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+  lib_path = os.path.join(root, "recurrentgemma_b200", "librgk_checks.so")
+  if not os.path.exists(lib_path):
+    pytest.skip("librgk_checks.so not built (python -m recurrentgemma_b200.build --checks)")
+  env = dict(os.environ, RGK_LIBRARY=lib_path)
+  cmd = [sys.executable, "-m", "pytest", "-x", "-q", "-m", "gpu",
+         os.path.join(root, "tests", "test_gpu_parity.py"), os.path.join(root, "tests", "test_config_sizes.py"),
+         "-k", "fused_rglru_kernel or scan_vs_oracle or long_scan_shard or static", "-p", "no:cacheprovider"]
+  r = subprocess.run(cmd, env=env, cwd=root, capture_output=True, text=True, timeout=900)
+  assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
+  assert " passed" in r.stdout
