@@ -619,7 +619,9 @@ __global__ void m8sp_chan_kernel(const __nv_bfloat16* __restrict__ a_param, int 
   const int e = blockIdx.x * blockDim.x + threadIdx.x;
   if (e < E) {
     const float s = round_bf16(softplus_(__bfloat162float(a_param[e])));
-    m8sp[e] = __float2bfloat16_rn(-8.0f * s);
+    // clamped to the range of the kernel's table of exp(log_a): beyond it a = exp(log_a) is 0 in
+    // float32 either way (the gate would have to be below 0.7 at softplus(a_param) above 16)
+    m8sp[e] = __float2bfloat16_rn(fmaxf(-8.0f * s, kLogAFloor));
   }
 }
 

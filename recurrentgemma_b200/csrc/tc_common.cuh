@@ -250,10 +250,12 @@ __device__ __forceinline__ void a_mult_of_log_a(uint32_t la2, uint32_t& a2, uint
 }
 
 // The same from a table in shared memory, indexed by the magnitude bits of log_a (log_a <= 0).
-// Up to 2^-11 both roundings give a = 1, multiplier 0 (the first entry); from 128 on a = 0,
-// multiplier 1 (the last entry): 18 binades x 128 values, one 32-bit entry {a, multiplier} each.
+// Up to 2^-11 both roundings give a = 1, multiplier 0 (the first entry); the table ends below 128,
+// where a has long underflowed to 0 and the multiplier is 1: 18 binades x 128 values, one 32-bit
+// entry {a, multiplier} each.  kLogAFloor: the most negative log_a the table covers.
 constexpr uint32_t kLutBase = 0x3a00u;                 // bits of 2^-11
 constexpr int kLutEntries = 0x4300 - 0x3a00;           // up to 128.0 (exclusive)
+constexpr float kLogAFloor = -127.5f;
 __device__ __forceinline__ uint32_t a_mult_entry(uint32_t index) {
   const uint32_t la = 0x8000u | (kLutBase + index);
   uint32_t a2, mult2;
@@ -262,13 +264,14 @@ __device__ __forceinline__ uint32_t a_mult_entry(uint32_t index) {
 }
 __device__ __forceinline__ void a_mult_lookup(uint32_t la2, const uint32_t* lut, uint32_t& a2,
                                               uint32_t& mult2) {
-  constexpr uint32_t kBase2 = kLutBase | (kLutBase << 16);
-  constexpr uint32_t kTop2 = (kLutBase + kLutEntries - 1) | ((kLutBase + kLutEntries - 1) << 16);
-  uint32_t m = la2 & 0x7fff7fffu, t;
-  asm("max.u16x2 %0, %1, %2;" : "=r"(t) : "r"(m), "r"(kBase2));
-  asm("min.u16x2 %0, %1, %2;" : "=r"(m) : "r"(t), "r"(kTop2));
-  m -= kBase2;                                          // no borrow: each half is at least the base
-  const uint32_t e0 = lut[m & 0xffffu], e1 = lut[m >> 16];
+  // log_a is at most -2^-11 after the packed minimum (smaller magnitudes share the first entry),
+  // and at least -127.5 because the per-channel factor -8 softplus(a_param) is clamped there when
+  // it is computed (the gate is at most 1): the bits of each half, sign included, index the table
+  // directly, relative to the bits of -2^-11.
+  uint32_t m;
+  asm("min.bf16x2 %0, %1, %2;" : "=r"(m) : "r"(la2), "r"(0x80008000u | kLutBase | (kLutBase << 16)));
+  const uint32_t* base = lut - (0x8000u | kLutBase);
+  const uint32_t e0 = base[m & 0xffffu], e1 = base[m >> 16];
   asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(a2) : "r"(e0), "r"(e1));
   asm("prmt.b32 %0, %1, %2, 0x7632;" : "=r"(mult2) : "r"(e0), "r"(e1));
 }
