@@ -689,7 +689,7 @@ def long_scan_leg(dev, rank, world, steps, warmup, seq=65536, gather=True, shard
 def rglru_fp32_leg(dev, steps):
   """The float32 RG-LRU layer (batch 2, 1024 tokens, lru_width 2560, 10 heads, document starts at 0
   and 512): microseconds per forward, against its HBM bound (x in, y out, gate weights) and against
-  the float32-accurate gate contraction it is actually bound by."""
+  the gate contraction (three TF32 tensor-core products per float32 product) it is bound by."""
   import recurrentgemma_b200 as rg
   from recurrentgemma_b200 import synthetic
   b, t, e, h = 2, 1024, 2560, 10
@@ -714,8 +714,9 @@ def rglru_fp32_leg(dev, steps):
                        "peak": hbm, "unit": "GB/s", "frac": alg / (ms * 1e-3) / 1e9 / hbm,
                        "peak_source": which},
           "gate_contraction": {"flops": flops, "achieved_TFLOP/s": flops / (ms * 1e-3) / 1e12,
-                               "note": "float32-accurate FMA on the CUDA cores (no float32 tensor-core "
-                                       "mode meets the 1e-5 bar in one pass)"}}
+                               "note": "float32 products as three TF32 products on the tensor cores "
+                                       "(hi/lo split of both operands, float32 accumulation); the "
+                                       "figure counts each float32 multiply-add once"}}
 
 
 # ------------------------------------------------------------------------------------------------

@@ -57,8 +57,9 @@ enum {
   RGK_GATES_AUTO = 0,    /* the fastest kernel that covers the shape (see below) */
   RGK_GATES_SIMT = 1,    /* CUDA-core gate kernel, then the scan kernel (any head width that is a
                             multiple of 16; float32 or bfloat16) */
-  RGK_GATES_TCGEN05 = 2, /* tensor-core gate kernel, then the scan kernel (bfloat16, head width
-                            256); RGK_ESHAPE if the shape is not covered */
+  RGK_GATES_TCGEN05 = 2, /* tensor-core gate kernel, then the scan kernel (head width 256: bfloat16,
+                            or float32 as three TF32 products per float32 product); RGK_ESHAPE if
+                            the shape is not covered */
   RGK_GATES_FUSED = 3,   /* gates, gate arithmetic and scan in one tensor-core kernel (bfloat16,
                             head width 256, any T); RGK_ESHAPE otherwise.  The input gate and the
                             gelu of the join are evaluated with packed bfloat16 tanh approximations:

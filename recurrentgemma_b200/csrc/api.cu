@@ -103,9 +103,16 @@ int run_gates(const void* c, const void* pos, int pos64, const rgk_params* p, in
               int bw, int dtype, int gates_impl, void* wpack, void* a, void* xn, void* ws_header,
               cudaStream_t s) {
   const bool tc_ok = rgk::gates_tc_supported(dtype, bw, M);
-  if (gates_impl == RGK_GATES_TCGEN05 && !tc_ok)
-    return fail(RGK_ESHAPE, "the tcgen05 gate kernel covers bfloat16 with head width 256 only "
+  const bool tf32_ok = rgk::gates_tf32_supported(dtype, bw, M);
+  if (gates_impl == RGK_GATES_TCGEN05 && !tc_ok && !tf32_ok)
+    return fail(RGK_ESHAPE, "the tcgen05 gate kernels cover head width 256 only "
                             "(dtype %d, head width %d)", dtype, bw);
+  if (tf32_ok && gates_impl != RGK_GATES_SIMT) {
+    cudaError_t e = rgk::launch_gates_tf32(c, pos, pos64, p->a_param, p->gate_x_w, p->gate_x_b,
+                                           p->gate_a_w, p->gate_a_b, M, H, wpack, a, xn, ws_header, s);
+    if (e != cudaSuccess) return cuda_fail(e, "tcgen05 TF32 gates launch");
+    return RGK_OK;
+  }
   if (tc_ok && gates_impl != RGK_GATES_SIMT) {
     cudaError_t e = rgk::launch_gates_tc(
         c, pos, pos64, p->a_param, p->gate_x_w, p->gate_x_b, p->gate_a_w, p->gate_a_b, M, H,
@@ -177,8 +184,9 @@ PathWs carve(void* ws, int64_t B, int64_t T, int64_t E, int dtype) {
   w.a = base ? base + scan_bytes + act : nullptr;
   w.xn = base ? base + scan_bytes + 2 * act : nullptr;
   w.wpack = base ? base + scan_bytes + 3 * act : nullptr;
-  // K-major copy of both gate weights for the tensor-core kernel: 2 * E * 256 bfloat16.
-  w.total = scan_bytes + 3 * act + up256(static_cast<size_t>(E) * 1024);
+  // K-major copy of both gate weights for the tensor-core kernels: 2 * E * 256 bfloat16, or for
+  // float32 the same split into a high and a low part (2 * 2 * E * 256 float32).
+  w.total = scan_bytes + 3 * act + up256(static_cast<size_t>(E) * (dtype == RGK_BF16 ? 1024 : 4096));
   return w;
 }
 

@@ -78,6 +78,16 @@ cudaError_t launch_gates_tc(const void* c, const void* pos, int pos64, const voi
                             int64_t M, int H, void* packed_w, int packed_ready, void* a_out,
                             void* xn_out, void* ws_header, cudaStream_t s);
 
+// gates_tf32.cu: the same for float32 and head width 256, as three TF32 products per float32
+// product (hi/lo split of both operands, float32 accumulation in tensor memory).  packed_w:
+// gates_tf32_packed_bytes(H) bytes of scratch for the split K-major copies of the weights.
+bool gates_tf32_supported(int dtype, int bw, int64_t M);
+size_t gates_tf32_packed_bytes(int H);
+cudaError_t launch_gates_tf32(const void* c, const void* pos, int pos64, const void* a_param,
+                              const void* wx, const void* bx, const void* wa, const void* ba,
+                              int64_t M, int H, void* packed_w, void* a_out, void* xn_out,
+                              void* ws_header, cudaStream_t s);
+
 // Packs the gate weights only (the first step of launch_gates_tc), for callers that keep the
 // packed copy across calls; launch_gates_tc with packed_ready != 0 then skips its own packing.
 cudaError_t launch_pack_gate_weights(const void* wx, const void* wa, int H, void* packed_w,
