@@ -13,9 +13,10 @@
 //
 // One CTA per (128-token tile, head, channel half): N = 256 accumulator columns = the 128 x-gate and
 // the 128 a-gate outputs of the half's channels, so that an epilogue thread finds both gates of a
-// channel in its own TMEM lane.  K = 256 arrives in eight slices of 32 (128-byte rows, 128-byte
-// swizzle) through a two-stage ring: activations 16 KiB, their low part 16 KiB (written by the
-// helper warps), weights hi and lo 32 KiB each.  A single thread issues three
+// channel in its own TMEM lane.  K = 256 arrives in sixteen slices of 16 (64-byte rows, 64-byte
+// swizzle) through a four-stage ring: activations 8 KiB, their low part 8 KiB (written by the
+// helper warps), weights hi and lo 16 KiB each - the per-slice hand-offs (copy engine -> split ->
+// tensor core -> release) of a CTA are serial, so more and smaller stages in flight hide them.  A single thread issues three
 // tcgen05.mma.cta_group::1.kind::tf32 (M 128, N 256, K 8) per K step.  The epilogue (16 warps: TMEM
 // lane quarter x 32-channel chunk) reads the accumulators, applies the float32-accurate gate
 // arithmetic and writes a and the normalised input for the scan kernel.
@@ -34,12 +35,16 @@ constexpr int kHW = 256;                 // head width = K
 constexpr int kTM = 128;                 // tokens per tile (MMA M)
 constexpr int kTN = 256;                 // accumulator columns: 128 x-gate + 128 a-gate
 constexpr int kHalf = 128;               // channels per CTA
-constexpr int kKS = 32;                  // K per slice: 32 float32 = 128 bytes
-constexpr int kSlices = kHW / kKS;       // 8
-constexpr int kStages = 2;
-constexpr int kABytes = kTM * kKS * 4;   // 16 KiB
-constexpr int kBBytes = kTN * kKS * 4;   // 32 KiB
-constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes;     // A, A_lo, B_hi, B_lo = 96 KiB
+constexpr int kKS = 16;                  // K per slice: 16 float32 = 64 bytes (64-byte swizzle); 32 also works
+constexpr int kSlices = kHW / kKS;
+constexpr int kStages = 64 / kKS;        // 4 stages of 48 KiB, or 2 of 96 KiB
+constexpr int kABytes = kTM * kKS * 4;
+constexpr int kBBytes = kTN * kKS * 4;
+constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes;     // A, A_lo, B_hi, B_lo
+constexpr bool kSw128 = kKS == 32;
+__device__ __forceinline__ uint64_t tf32_desc(uint32_t addr) {
+  return kSw128 ? smem_desc_sw128(addr) : smem_desc_sw64(addr);
+}
 constexpr int kEpi = 16;
 constexpr int kThreadsF = (kEpi + 2) * 32;
 constexpr int kOffSp = kStages * kStageBytes;               // float [128]: softplus(a_param)
@@ -144,8 +149,8 @@ gates_tf32_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         const uint32_t b_hi = a_hi + 2 * kABytes, b_lo = b_hi + kBBytes;
 #pragma unroll
         for (int ks = 0; ks < kKS / 8; ++ks) {
-          const uint64_t dah = smem_desc_sw128(a_hi + ks * 32), dal = smem_desc_sw128(a_lo + ks * 32);
-          const uint64_t dbh = smem_desc_sw128(b_hi + ks * 32), dbl = smem_desc_sw128(b_lo + ks * 32);
+          const uint64_t dah = tf32_desc(a_hi + ks * 32), dal = tf32_desc(a_lo + ks * 32);
+          const uint64_t dbh = tf32_desc(b_hi + ks * 32), dbl = tf32_desc(b_lo + ks * 32);
           tc_mma_tf32(tmem_base, dah, dbh, kIdescF, (kb | ks) != 0 ? 1u : 0u);
           tc_mma_tf32(tmem_base, dal, dbh, kIdescF, 1u);
           tc_mma_tf32(tmem_base, dah, dbl, kIdescF, 1u);
@@ -157,16 +162,17 @@ gates_tf32_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
   } else {
     // ------------------------------ helper, then epilogue ------------------------------------------
     // During the main loop: the low parts of the activation slice (element-wise, so the swizzled
-    // layout carries over address for address).  512 threads x 8 elements = one 128 x 32 slice.
+    // layout carries over address for address).  512 threads cover one 128-token slice.
     bool ok = true;
     for (int kb = 0; kb < kSlices && ok; ++kb) {
       const int s = kb % kStages;
       ok = mbar_wait(bar_full(s), (kb / kStages) & 1, s_abort);
       if (!ok) break;
-      float4* src = reinterpret_cast<float4*>(smem + s * kStageBytes) + threadIdx.x * 2;
-      float4* dst = reinterpret_cast<float4*>(smem + s * kStageBytes + kABytes) + threadIdx.x * 2;
+      constexpr int kPer = kABytes / 16 / (kEpi * 32);          // 16-byte pieces per thread
+      float4* src = reinterpret_cast<float4*>(smem + s * kStageBytes) + threadIdx.x * kPer;
+      float4* dst = reinterpret_cast<float4*>(smem + s * kStageBytes + kABytes) + threadIdx.x * kPer;
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
+      for (int i = 0; i < kPer; ++i) {
         const float4 v = src[i];
         dst[i] = make_float4(tf32_low_part(v.x), tf32_low_part(v.y), tf32_low_part(v.z),
                              tf32_low_part(v.w));
@@ -298,9 +304,9 @@ cudaError_t launch_gates_tf32(const void* c, const void* pos, int pos64, const v
   if (err != cudaSuccess) return err;
 
   CUtensorMap map_x, map_wh, map_wl;
-  if (!tensor_map_2d(&map_x, c, (uint64_t)M, (uint64_t)E, kTM, kKS, true, 4) ||
-      !tensor_map_2d(&map_wh, hi, (uint64_t)H * 2 * kTN, kHW, kTN, kKS, true, 4) ||
-      !tensor_map_2d(&map_wl, lo, (uint64_t)H * 2 * kTN, kHW, kTN, kKS, true, 4))
+  if (!tensor_map_2d(&map_x, c, (uint64_t)M, (uint64_t)E, kTM, kKS, kSw128, 4, !kSw128) ||
+      !tensor_map_2d(&map_wh, hi, (uint64_t)H * 2 * kTN, kHW, kTN, kKS, kSw128, 4, !kSw128) ||
+      !tensor_map_2d(&map_wl, lo, (uint64_t)H * 2 * kTN, kHW, kTN, kKS, kSw128, 4, !kSw128))
     return cudaErrorInvalidValue;
   static PerDeviceOnce once;
   cudaError_t e0 = once.run([] {

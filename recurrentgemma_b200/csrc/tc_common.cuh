@@ -115,6 +115,17 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
   return d;
 }
 
+// The same for rows of 64 bytes stored with the 64-byte swizzle: groups of 8 rows 512 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_sw64(uint32_t addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((addr & 0x3ffffu) >> 4);
+  d |= static_cast<uint64_t>(1) << 16;
+  d |= static_cast<uint64_t>(512 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(4) << 61;                       // SWIZZLE_64B
+  return d;
+}
+
 // Instruction descriptor of tcgen05.mma kind::f16: D float32, A and B bfloat16, both K-major.
 constexpr uint32_t tc_idesc_bf16(int m, int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);

@@ -79,9 +79,11 @@ inline EncodeTiledFn tensor_map_encoder() {
 
 // Tensor map of a dense row-major matrix [rows, cols] of 2- or 4-byte elements, copied in boxes of
 // box_rows x box_cols.  swizzle128: the 128-byte swizzle tcgen05 operands use (box_cols * elem_bytes
-// must then be 128), with 256-byte L2 promotion; otherwise no swizzle and 128-byte promotion.
+// must then be 128), with 256-byte L2 promotion; swizzle64: the 64-byte swizzle (rows of 64 bytes);
+// otherwise no swizzle and 128-byte promotion.
 inline bool tensor_map_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
-                          uint32_t box_rows, uint32_t box_cols, bool swizzle128, int elem_bytes = 2) {
+                          uint32_t box_rows, uint32_t box_cols, bool swizzle128, int elem_bytes = 2,
+                          bool swizzle64 = false) {
   EncodeTiledFn fn = tensor_map_encoder();
   if (fn == nullptr) return false;
   const cuuint64_t dims[2] = {cols, rows};
@@ -90,7 +92,8 @@ inline bool tensor_map_2d(CUtensorMap* map, const void* base, uint64_t rows, uin
   const cuuint32_t estr[2] = {1, 1};
   return fn(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
             2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+            swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                       : (swizzle64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE),
             swizzle128 ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
