@@ -807,6 +807,43 @@ def decode_leg(dev, steps):
     graph_b.replay()
   torch.cuda.synchronize()
   block_ms = _time_loop(graph_b.replay, steps, torch.cuda.current_stream())
+
+  # The same 26 blocks at a serving-sized batch (16 rows), where the projections are bound by
+  # streaming their weights: on library GEMMs (SMALL_ROWS = 0) and on this library's few-row
+  # tensor-core kernel (linear_y and linear_x in one launch), each as a CUDA graph.
+  b_small = 16
+  x_small, pos_small = x0[:b_small].contiguous(), pos[:b_small].contiguous()
+  caches_small = [modules.RecurrentBlockCache(c.rg_lru_state[:b_small].clone(),
+                                              c.conv1d_state[:b_small].clone()) for _, c in blocks]
+
+  def small_step():
+    x = x_small
+    for (blk, _), cache in zip(blocks, caches_small):
+      x, _ = blk(x, pos_small, cache)
+    return x
+
+  small_ms = {}
+  rows_default = modules.SMALL_ROWS
+  for name, rows in (("library_gemm", 0), ("few_row_kernel", max(rows_default, b_small))):
+    modules.SMALL_ROWS = rows
+    try:
+      gs = torch.cuda.CUDAGraph()
+      with torch.cuda.stream(side):
+        small_step()
+        torch.cuda.synchronize()
+        with torch.cuda.graph(gs, stream=side):
+          small_step()
+      torch.cuda.synchronize()
+      for _ in range(3):
+        gs.replay()
+      torch.cuda.synchronize()
+      small_ms[name] = _time_loop(gs.replay, steps, torch.cuda.current_stream())
+    finally:
+      modules.SMALL_ROWS = rows_default
+  _lib.check_status()
+  small_bytes = n_layers * (3 * e * e * 2 + 2 * 256 * e * 2 + 2 * b_small * 3 * e * 2 +
+                            2 * b_small * e * 4 + 6 * b_small * e * 2)
+
   block_bytes = n_layers * 3 * e * e * 2
   path_bytes = n_layers * (2 * b * e * 2 + b * e * 2 + 2 * b * 3 * e * 2 + 2 * b * e * 4 +
                            2 * 256 * e * 2)
@@ -823,6 +860,13 @@ def decode_leg(dev, steps):
                      "algorithmic_bytes": path_bytes + block_bytes,
                      "GB/s": (path_bytes + block_bytes) / (block_ms * 1e-3) / 1e9,
                      "frac": (path_bytes + block_bytes) / (block_ms * 1e-3) / 1e9 / hbm},
+      "full_block_b16": {"ms": small_ms["few_row_kernel"], "ms_library_gemm": small_ms["library_gemm"],
+                         "what": "the same 26 blocks at batch 16: projections on the few-row "
+                                 "tcgen05 kernel (linear_y | linear_x in one launch) against "
+                                 "library GEMMs, CUDA-graph replay",
+                         "algorithmic_bytes": small_bytes,
+                         "GB/s": small_bytes / (small_ms["few_row_kernel"] * 1e-3) / 1e9,
+                         "frac": small_bytes / (small_ms["few_row_kernel"] * 1e-3) / 1e9 / hbm},
       "roofline": {"bound": "hbm", "algorithmic_bytes": path_bytes,
                    "achieved": path_bytes / (graph_ms * 1e-3) / 1e9, "peak": hbm, "unit": "GB/s",
                    "frac": path_bytes / (graph_ms * 1e-3) / 1e9 / hbm, "peak_source": which},

@@ -28,7 +28,7 @@
 extern "C" {
 #endif
 
-#define RGK_ABI_VERSION 7
+#define RGK_ABI_VERSION 8
 
 #if defined(__GNUC__)
 #define RGK_API __attribute__((visibility("default")))
@@ -221,10 +221,38 @@ RGK_API int rgk_recurrent_path_decode(const void* xb, const void* yb, const void
  * result (torch/modules.py:289-291, 628).  status (optional device int) is raised to RGK_ETIMEOUT if
  * a bounded device-side wait expires.
  * ---------------------------------------------------------------------------------------------- */
-enum { RGK_ACT_NONE = 0, RGK_ACT_GELU_TANH = 1 };
+enum { RGK_ACT_NONE = 0, RGK_ACT_GELU_TANH = 1, RGK_ACT_GEGLU = 2 /* rgk_dense_linear_small only */ };
 RGK_API int rgk_dense_linear(const void* x, const void* weight, const void* bias, int64_t M,
                              int64_t K, int64_t N, int dtype, int act, void* out, int* status,
                              void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * The same torch.nn.Linear for FEW rows (M <= 256: a decode step, where M is the batch)
+ *                                                        torch/modules.py:437-452, 531-548, 626-647
+ *   x [M,K], weight [N,K], bias [N] or NULL, residual [M,N] or NULL
+ *   ->  out [M,N] = act(x weight^T + bias) (+ residual, rounded once more, when given)
+ * The weights are split over all SMs (128 output features x a slice of K per CTA) so that the
+ * call streams them once at HBM speed; the K slices of a feature tile form a thread-block cluster
+ * and add their float32 partial sums in distributed shared memory in a fixed order (the same bits
+ * on every run).  The kernel is launched with programmatic stream serialisation: it may begin
+ * (fetching weights) while the kernel before it in the stream drains, and touches nothing else
+ * before that kernel has completed.  bfloat16 only, K and N multiples of 8; RGK_ESHAPE otherwise
+ * (M > 256 included: rgk_dense_linear covers those).  Roundings as rgk_dense_linear.  status as there.
+ * act RGK_ACT_GEGLU: the up-projection of the MLP block (torch/modules.py:749-752): weight and
+ *   bias are the packed copy rgk_pack_mlp_up writes (N = 2 X rows, X a multiple of 64), out [M, X]
+ *   = gelu_tanh(gate) * value with the roundings of rgk_mlp_block; no residual.
+ * ---------------------------------------------------------------------------------------------- */
+RGK_API int rgk_dense_linear_small(const void* x, const void* weight, const void* bias,
+                                   const void* residual, int64_t M, int64_t K, int64_t N, int dtype,
+                                   int act, void* out, int* status, void* stream);
+/* Two projections of the same x in one launch (linear_y and linear_x of the recurrent block,
+ * torch/modules.py:626-631; proj_k and proj_v of the attention block, torch/modules.py:437-452):
+ *   out_a [M,N_a] = x weight_a^T + bias_a,  out_b [M,N_b] = x weight_b^T + bias_b   (biases or NULL)
+ * N_a a multiple of 128; otherwise as rgk_dense_linear_small with RGK_ACT_NONE. */
+RGK_API int rgk_dense_linear_small_pair(const void* x, const void* weight_a, const void* bias_a,
+                                        const void* weight_b, const void* bias_b, int64_t M,
+                                        int64_t K, int64_t N_a, int64_t N_b, int dtype, void* out_a,
+                                        void* out_b, int* status, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
  * RecurrentBlock.forward, prefill form (cache is None)              torch/modules.py:605-655

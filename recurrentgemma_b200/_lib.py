@@ -21,6 +21,7 @@ RGK_F32, RGK_BF16 = 0, 1
 (RGK_OK, RGK_EINVAL, RGK_ESHAPE, RGK_EALIGN, RGK_EARCH, RGK_ECUDA, RGK_EWORKSPACE,
  RGK_ETIMEOUT, RGK_EBOUNDS) = 0, -1, -2, -3, -4, -5, -6, -7, -8
 RGK_I32, RGK_I64 = 0, 1
+ACT_NONE, ACT_GELU_TANH, ACT_GEGLU = 0, 1, 2
 GATES_AUTO, GATES_SIMT, GATES_TCGEN05, GATES_FUSED, GATES_FUSED_EXACT = 0, 1, 2, 3, 4
 
 _vp, _i64, _int, _sz = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_size_t
@@ -84,6 +85,9 @@ SIGNATURES = {
     "rgk_attention_decode_workspace_bytes": (_sz, [_i64, _int, _int]),
     "rgk_local_attention_decode": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _int, _int, _int, _int,
                                           _int, _vp, _vp, _sz, _vp]),
+    "rgk_dense_linear_small": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _vp, _vp, _vp]),
+    "rgk_dense_linear_small_pair": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _vp,
+                                           _vp, _vp, _vp]),
     "rgk_embed": (_int, [_vp, _int, _vp, _i64, _i64, _i64, ctypes.c_float, _int, _vp, _vp]),
     "rgk_logits": (_int, [_vp, _vp, _i64, _i64, _i64, ctypes.c_float, _int, _vp, _vp, _vp]),
     "rgk_argmax": (_int, [_vp, _i64, _i64, _int, _vp, _vp]),
@@ -121,7 +125,7 @@ def load() -> ctypes.CDLL:
       fn = getattr(lib, name)
       fn.restype = res
       fn.argtypes = args
-    if lib.rgk_abi_version() != 7:
+    if lib.rgk_abi_version() != 8:
       raise RuntimeError("librgk.so has a different ABI version; rebuild it")
     _lib = lib
     return lib

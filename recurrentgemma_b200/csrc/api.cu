@@ -453,6 +453,56 @@ int rgk_dense_linear(const void* x, const void* weight, const void* bias, int64_
   return RGK_OK;
 }
 
+int rgk_dense_linear_small(const void* x, const void* weight, const void* bias, const void* residual,
+                           int64_t M, int64_t K, int64_t N, int dtype, int act, void* out,
+                           int* status, void* stream) {
+  RGK_REQUIRE(dtype == RGK_F32 || dtype == RGK_BF16, RGK_EINVAL, "unknown dtype %d", dtype);
+  RGK_REQUIRE(act == RGK_ACT_NONE || act == RGK_ACT_GELU_TANH || act == RGK_ACT_GEGLU, RGK_EINVAL,
+              "unknown act %d", act);
+  RGK_REQUIRE(M >= 0 && K >= 1 && N >= 1, RGK_EINVAL, "bad size (M=%lld K=%lld N=%lld)",
+              (long long)M, (long long)K, (long long)N);
+  RGK_REQUIRE(x && weight && out, RGK_EINVAL, "NULL pointer argument");
+  RGK_REQUIRE(act != RGK_ACT_GEGLU || (residual == nullptr && bias != nullptr && N % 128 == 0),
+              RGK_ESHAPE, "GeGLU takes the packed up-projection with its bias (N = 2 X with X a "
+              "multiple of 64, N=%lld) and no residual", (long long)N);
+  RGK_REQUIRE(aligned16(x) && aligned16(weight) && aligned16(out) && aligned16(bias) &&
+              aligned16(residual), RGK_EALIGN, "pointers must be 16-byte aligned");
+  RGK_REQUIRE(rgk::dense_small_supported(dtype, M > 0 ? M : 1, K, N), RGK_ESHAPE,
+              "the few-row linear covers bfloat16 with M <= 256 and K and N multiples of 8 "
+              "(dtype %d, M=%lld, K=%lld, N=%lld)", dtype, (long long)M, (long long)K, (long long)N);
+  if (M == 0) return RGK_OK;
+  RGK_CHECK_DEVICE();
+  RGK_CUDA(rgk::launch_dense_small(x, weight, bias, nullptr, nullptr, residual, M, (int)K, (int)N, 0,
+                                   act, out, nullptr, status, static_cast<cudaStream_t>(stream)),
+           "few-row dense linear launch");
+  return RGK_OK;
+}
+
+int rgk_dense_linear_small_pair(const void* x, const void* weight_a, const void* bias_a,
+                                const void* weight_b, const void* bias_b, int64_t M, int64_t K,
+                                int64_t N_a, int64_t N_b, int dtype, void* out_a, void* out_b,
+                                int* status, void* stream) {
+  RGK_REQUIRE(dtype == RGK_F32 || dtype == RGK_BF16, RGK_EINVAL, "unknown dtype %d", dtype);
+  RGK_REQUIRE(M >= 0 && K >= 1 && N_a >= 1 && N_b >= 1, RGK_EINVAL,
+              "bad size (M=%lld K=%lld N_a=%lld N_b=%lld)", (long long)M, (long long)K,
+              (long long)N_a, (long long)N_b);
+  RGK_REQUIRE(x && weight_a && weight_b && out_a && out_b, RGK_EINVAL, "NULL pointer argument");
+  RGK_REQUIRE(aligned16(x) && aligned16(weight_a) && aligned16(weight_b) && aligned16(out_a) &&
+              aligned16(out_b) && aligned16(bias_a) && aligned16(bias_b), RGK_EALIGN,
+              "pointers must be 16-byte aligned");
+  RGK_REQUIRE(rgk::dense_small_supported(dtype, M > 0 ? M : 1, K, N_a + N_b) && N_a % 128 == 0 &&
+              N_b % 8 == 0, RGK_ESHAPE,
+              "the paired few-row linear covers bfloat16 with M <= 256, K and N_b multiples of 8 and "
+              "N_a a multiple of 128 (dtype %d, M=%lld, K=%lld, N_a=%lld, N_b=%lld)", dtype,
+              (long long)M, (long long)K, (long long)N_a, (long long)N_b);
+  if (M == 0) return RGK_OK;
+  RGK_CHECK_DEVICE();
+  RGK_CUDA(rgk::launch_dense_small(x, weight_a, bias_a, weight_b, bias_b, nullptr, M, (int)K, (int)N_a,
+                                   (int)N_b, 0, out_a, out_b, status, static_cast<cudaStream_t>(stream)),
+           "paired few-row dense linear launch");
+  return RGK_OK;
+}
+
 int rgk_embed(const void* tokens, int token_dtype, const void* table, int64_t M, int64_t V,
               int64_t D, float scale, int dtype, void* out, void* stream) {
   RGK_REQUIRE(dtype == RGK_F32 || dtype == RGK_BF16, RGK_EINVAL, "unknown dtype %d", dtype);

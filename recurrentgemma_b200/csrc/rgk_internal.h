@@ -121,6 +121,16 @@ cudaError_t launch_rglru_chan(const void* c, const void* pos, int pos64, const v
 // [M,N] tensor to the rounded result and rounds again (not together with gelu).  cap != 0 (no bias,
 // gelu or residual) is the logits soft cap: tanh(acc / cap) * cap with every rounding of the
 // reference.  status: optional device int raised on a bounded-wait timeout.
+// gemm_small_tc.cu: the same projection for M <= 256 rows, weights split over all SMs (the K
+// slices of a feature tile are a thread-block cluster and add up in distributed shared memory).
+// act 0: bias; 1: gelu_tanh of the rounded result; 2: GeGLU over the packed up-projection of the
+// MLP (w as pack_mlp_up_kernel writes it, N = 2 X rows, out [M, X]).  w2 != nullptr: a second
+// projection of the same x (N2 features, own bias and output) in the same launch; N a multiple of
+// 128 then.
+bool dense_small_supported(int dtype, int64_t M, int64_t K, int64_t N);
+cudaError_t launch_dense_small(const void* x, const void* w, const void* bias, const void* w2,
+                               const void* bias2, const void* residual, int64_t M, int K, int N,
+                               int N2, int act, void* out, void* out2, int* status, cudaStream_t s);
 bool dense_tc_supported(int dtype, int64_t M, int64_t K, int64_t N);
 cudaError_t launch_dense_tc(const void* x, const void* w, const void* bias, const void* residual,
                             int64_t M, int K, int N, int gelu, void* out, int* status,

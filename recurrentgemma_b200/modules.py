@@ -18,8 +18,18 @@ from recurrentgemma_b200 import _lib
 from recurrentgemma_b200 import layers
 
 
-# Fewest rows for which the tensor-core GEMM of the library is used (see MLPBlock._fusable).
+# Fewest rows for which the prefill GEMM of the library is used (see MLPBlock._fusable), and most
+# rows for which the few-row (weight-streaming, split-K) kernel is used; torch's contractions in
+# between.  The few-row kernel takes up to 256 rows, but the exchange of its K-split partial sums
+# grows with the row count: measured on a B200 at 2560 x 2560 it is ahead of the library GEMM up
+# to 32 rows (two projections in one launch: 9.7 against 12.6 us at 16 rows) and behind it from 64.
 SMALL_M = 1024
+SMALL_ROWS = 32
+# The MLP's contractions (2560 -> 2 x 7680 -> 2560) stay on the library below SMALL_M: with 120
+# feature tiles there is nothing to split, and the library's kernel streams those weights faster
+# (15.5 against 21 us).  Raise to SMALL_ROWS to route them through the few-row kernel as well
+# (GeGLU and the residual add then run in its epilogues).
+SMALL_ROWS_MLP = 0
 
 
 class RecurrentBlockCache(NamedTuple):
@@ -109,6 +119,87 @@ def dense_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Ten
   return out
 
 
+@torch.no_grad()
+def small_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
+                 act: int = _lib.ACT_NONE, residual: Optional[torch.Tensor] = None,
+                 bias_ptr: Optional[int] = None) -> torch.Tensor:
+  """The same projection for at most SMALL_ROWS rows (a decode step) on the weight-streaming
+  split-K tcgen05 kernel of librgk.  act: _lib.ACT_NONE, ACT_GELU_TANH (gelu of the rounded result)
+  or ACT_GEGLU (weight = the packed up-projection of the MLP block with its bias at `bias_ptr`;
+  the result has half as many features as the weight has rows).  `residual` is added to the rounded
+  result (its own rounding)."""
+  dev = _lib.require_cuda(x, weight, bias, residual)
+  n, k = weight.shape
+  assert x.shape[-1] == k
+  xc = x.contiguous()
+  m = xc.numel() // k
+  n_out = n // 2 if act == _lib.ACT_GEGLU else n
+  out = torch.empty((*x.shape[:-1], n_out), dtype=x.dtype, device=dev)
+  rc = None if residual is None else residual.contiguous()
+  bc = None if bias is None else bias.contiguous()
+  lib = _lib.load()
+  with torch.cuda.device(dev):
+    _lib.check(lib.rgk_dense_linear_small(
+        xc.data_ptr(), weight.data_ptr(), bias_ptr if bias_ptr is not None else _lib.ptr(bc),
+        _lib.ptr(rc), m, k, n, _lib.dtype_code(x.dtype), act, out.data_ptr(),
+        _lib.status_ptr(dev), _lib.stream_ptr(dev)))
+  return out
+
+
+@torch.no_grad()
+def small_linear_pair(x: torch.Tensor, lin_a: nn.Linear, lin_b: nn.Linear
+                      ) -> Tuple[torch.Tensor, torch.Tensor]:
+  """(lin_a(x), lin_b(x)) for at most SMALL_ROWS rows in ONE launch of the few-row kernel (the two
+  projections share the rows of x); lin_a.out_features a multiple of 128."""
+  dev = _lib.require_cuda(x, lin_a.weight, lin_b.weight)
+  layers._same_dtype(x, lin_a.weight, lin_b.weight,
+                     *[l.bias for l in (lin_a, lin_b) if l.bias is not None])
+  (na, k), (nb, kb) = lin_a.weight.shape, lin_b.weight.shape
+  assert x.shape[-1] == k == kb
+  xc = x.contiguous()
+  m = xc.numel() // k
+  out_a = torch.empty((*x.shape[:-1], na), dtype=x.dtype, device=dev)
+  out_b = torch.empty((*x.shape[:-1], nb), dtype=x.dtype, device=dev)
+  lib = _lib.load()
+  with torch.cuda.device(dev):
+    _lib.check(lib.rgk_dense_linear_small_pair(
+        xc.data_ptr(), lin_a.weight.data_ptr(), _lib.ptr(lin_a.bias), lin_b.weight.data_ptr(),
+        _lib.ptr(lin_b.bias), m, k, na, nb, _lib.dtype_code(x.dtype), out_a.data_ptr(),
+        out_b.data_ptr(), _lib.status_ptr(dev), _lib.stream_ptr(dev)))
+  return out_a, out_b
+
+
+def linear_pair(x: torch.Tensor, lin_a: nn.Linear, lin_b: nn.Linear
+                ) -> Tuple[torch.Tensor, torch.Tensor]:
+  """(lin_a(x), lin_b(x)): one launch of the few-row kernel where it applies, else two `linear`."""
+  rows = x.numel() // x.shape[-1]
+  if (rows < SMALL_M and _small_ok(x, lin_a.weight) and _small_ok(x, lin_b.weight)
+      and lin_a.weight.shape[0] % 128 == 0
+      and all(l.bias is None or l.bias.is_contiguous() for l in (lin_a, lin_b))):
+    return small_linear_pair(x, lin_a, lin_b)
+  return linear(x, lin_a), linear(x, lin_b)
+
+
+def _small_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
+  n, k = weight.shape
+  return (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and weight.is_contiguous()
+          and 1 <= x.numel() // x.shape[-1] <= SMALL_ROWS and k % 8 == 0 and n % 8 == 0)
+
+
+def linear(x: torch.Tensor, lin: nn.Linear, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+  """lin(x) (+ residual): the prefill GEMM from SMALL_M rows on, the few-row kernel up to
+  SMALL_ROWS rows, torch in between and for float32."""
+  rows = x.numel() // x.shape[-1]
+  if x.dtype == torch.bfloat16 and rows >= SMALL_M:
+    y = dense_linear(x, lin.weight, lin.bias)
+  elif _small_ok(x, lin.weight):
+    layers._same_dtype(x, lin.weight, *([lin.bias] if lin.bias is not None else []))
+    return small_linear(x, lin.weight, lin.bias, residual=residual)
+  else:
+    y = lin(x)
+  return y if residual is None else y + residual
+
+
 class RecurrentBlock(nn.Module):
   """Griffin and Hawk's recurrent block."""
 
@@ -159,11 +250,10 @@ class RecurrentBlock(nn.Module):
     dev = _lib.require_cuda(x, segment_pos, self.linear_x.weight)
     if self._fusable(x, cache):
       return self._forward_fused(x, segment_pos, return_cache, dev)
-    yb = self.linear_y(x)
-    xb = self.linear_x(x)
+    yb, xb = linear_pair(x, self.linear_y, self.linear_x)
     z, new_cache = recurrent_path(xb, yb, segment_pos, self.conv_1d, self.rg_lru, cache,
                                   return_cache, inplace=inplace)
-    return self.linear_out(z), new_cache
+    return linear(z, self.linear_out), new_cache
 
   def _forward_fused(self, x, segment_pos, return_cache, dev, norm=None):
     """Prefill of the whole block in one library call: the three projections on the tcgen05 GEMM
@@ -320,6 +410,19 @@ class MLPBlock(nn.Module):
       params.append(pre_norm.scale)
     layers._same_dtype(x, *params)
     assert x.shape[-1] == self.width
+    rows = x.numel() // x.shape[-1]
+    if (x.dtype == torch.bfloat16 and rows <= SMALL_ROWS_MLP and rows < SMALL_M and self.width % 8 == 0
+        and self.expanded_width % 64 == 0 and self.ffw_down.weight.is_contiguous()):
+      # a decode step: both contractions on the few-row kernel, GeGLU and the residual add in
+      # their epilogues
+      xin = x if pre_norm is None else pre_norm(x)
+      packed = self._packed_up()
+      w_bytes = -(-2 * self.expanded_width * self.width * 2 // 256) * 256
+      w_view = self._pack_buf[:2 * self.expanded_width * self.width * 2].view(torch.bfloat16).view(
+          2 * self.expanded_width, self.width)
+      hidden = small_linear(xin, w_view, None, act=_lib.ACT_GEGLU, bias_ptr=packed + w_bytes)
+      res = x if pre_norm is not None else residual
+      return small_linear(hidden, self.ffw_down.weight, self.ffw_down.bias, residual=res)
     if not self._fusable(x):
       xin = x if pre_norm is None else pre_norm(x)
       # ffw_up as two plain contractions (the einsum of layers.Einsum would first make a permuted
@@ -463,9 +566,7 @@ class LocalAttentionBlock(nn.Module):
     torch.nn.init.normal_(w, mean=0.0, std=math.sqrt(self.final_w_init_variance_scale / self.width))
 
   def _linear(self, x: torch.Tensor, lin: nn.Linear) -> torch.Tensor:
-    if x.dtype == torch.bfloat16 and x.numel() // x.shape[-1] >= SMALL_M:
-      return dense_linear(x, lin.weight, lin.bias)
-    return lin(x)
+    return linear(x, lin)
 
   @torch.no_grad()
   def forward(
@@ -483,8 +584,8 @@ class LocalAttentionBlock(nn.Module):
     assert segment_pos.shape == (b, t), segment_pos.shape
     n, hd, w = self.num_heads, self.head_dim, self.window_size
     q = self._linear(x, self.proj_q).view(b, t, n, hd)
-    k = self._linear(x, self.proj_k).view(b, t, 1, hd)
-    v = self._linear(x, self.proj_v).view(b, t, 1, hd)
+    k, v = linear_pair(x, self.proj_k, self.proj_v)
+    k, v = k.view(b, t, 1, hd), v.view(b, t, 1, hd)
     q, k = _rope(q.contiguous(), segment_pos), _rope(k.contiguous(), segment_pos)
     new_cache = None
     if cache is None:

@@ -34,7 +34,7 @@ def test_header_symbols_exported(lib):
 
 
 def test_version_and_error_text(lib):
-  assert lib.rgk_abi_version() == 7
+  assert lib.rgk_abi_version() == 8
   assert isinstance(lib.rgk_last_error(), bytes)
 
 
