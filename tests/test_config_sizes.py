@@ -105,3 +105,44 @@ def test_prefill_workload_slices_vs_oracle(rg, oracle):
       assert_close(h_last[row:row + 1, sl], h_r, TOL[dt], f"final state slice ({row}, {head})")
       mismatch = float((y[row:row + 1, :, sl].cpu() != y_r).float().mean())
       assert mismatch <= max_mismatch, (impl, mismatch)
+
+
+@pytest.mark.parametrize("batch", [256, 130])
+def test_decode_step_at_config_size(rg, oracle, batch):
+  """One decode step of the sub-path at the size of the decode workload (batch 256, 2560 channels,
+  10 heads, bfloat16, cached conv window, float32 state, some rows at a document start): against
+  the oracle, and the in-place form (cache tensors overwritten) against the functional one, bit
+  for bit - every CTA of a head reads the head's whole cache, so the in-place shift has to wait
+  for all of them."""
+  from recurrentgemma_b200 import _lib, modules
+  e, h = 2560, 10
+  dt = torch.bfloat16
+  g = torch.Generator(device="cpu").manual_seed(21 + batch)
+  p = synthetic.rglru_params(e, h, g, dt)
+  conv_w = (torch.randn((4, e), generator=g) * 0.5).to(dt)
+  conv_b = (torch.randn((e,), generator=g) * 0.1).to(dt)
+  xb = torch.randn((batch, 1, e), generator=g).to(dt)
+  yb = torch.randn((batch, 1, e), generator=g).to(dt)
+  h0 = torch.randn((batch, e), generator=g) * 0.5
+  cc = torch.randn((batch, 3, e), generator=g).to(dt)
+  pos = torch.randint(1, 4097, (batch, 1), generator=g)
+  pos[::37] = 0                        # document starts: the state of those rows is dropped
+  conv = rg.Conv1D(e, 4, device=DEV, dtype=dt)
+  conv.load_state_dict({"w": conv_w, "b": conv_b})
+  lru = _lru(rg, p, e, h, dt)
+  cache = modules.RecurrentBlockCache(h0.to(DEV), cc.to(DEV))
+  out, new = rg.recurrent_path(xb.to(DEV), yb.to(DEV), pos.to(DEV), conv, lru, cache)
+  po = {"conv_w": conv_w, "conv_b": conv_b, "a_param": p["a_param"], "gate_x_w": p["input_gate.w"],
+        "gate_x_b": p["input_gate.b"], "gate_a_w": p["a_gate.w"], "gate_a_b": p["a_gate.b"]}
+  out_r, h_r, cc_r = oracle.recurrent_path(xb, yb, pos, po, h0, cc)
+  assert_close(out, out_r, TOL[dt], "decode output")
+  assert_close(new.rg_lru_state, h_r, TOL[dt], "decode state")
+  assert torch.equal(new.conv1d_state.cpu(), cc_r), "shifted conv window"
+  assert torch.equal(cache.conv1d_state.cpu(), cc), "the functional form leaves its input cache alone"
+  own = modules.RecurrentBlockCache(h0.to(DEV), cc.to(DEV))
+  out2, same = rg.recurrent_path(xb.to(DEV), yb.to(DEV), pos.to(DEV), conv, lru, own, inplace=True)
+  assert same.conv1d_state.data_ptr() == own.conv1d_state.data_ptr()
+  assert torch.equal(out2, out), "in-place output"
+  assert torch.equal(own.rg_lru_state, new.rg_lru_state), "in-place state"
+  assert torch.equal(own.conv1d_state, new.conv1d_state), "in-place conv window"
+  _lib.check_status()
