@@ -163,13 +163,16 @@ typedef struct rgk_params {
 } rgk_params;
 
 /* ------------------------------------------------------------------------------------------------
- * K-major copy of the two gate weights for the tcgen05 kernels (bfloat16, head width 256 only):
- * rgk_gate_pack_bytes(H) bytes, written once per weight update and passed as
- * rgk_params.gates_packed afterwards (saves a 2.6 MB repack per call; matters for decode steps).
+ * K-major copy of the two gate weights for the tcgen05 kernels (head width 256 only; for float32
+ * the hi and lo halves of the 3xTF32 split): rgk_gate_pack_bytes_for(H, dtype) bytes
+ * (rgk_gate_pack_bytes(H) = the bfloat16 size), written once per weight update and passed as
+ * rgk_params.gates_packed afterwards, with parameters of the same dtype (saves a repack per call;
+ * matters for decode steps and short sequences).
  * No reference counterpart: the reference keeps only the [H, in, out] layout
  * (torch/layers.py:105-112).
  * ---------------------------------------------------------------------------------------------- */
 RGK_API size_t rgk_gate_pack_bytes(int H);
+RGK_API size_t rgk_gate_pack_bytes_for(int H, int dtype);
 RGK_API int rgk_pack_gate_weights(const rgk_params* p, int H, int bw, int dtype, void* packed_out,
                                   void* stream);
 

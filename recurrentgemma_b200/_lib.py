@@ -61,6 +61,7 @@ SIGNATURES = {
                                          _i64, _i64, _int, _int, _int, _int, _vp, _vp, _vp, _vp,
                                          _sz, _vp]),
     "rgk_gate_pack_bytes": (_sz, [_int]),
+    "rgk_gate_pack_bytes_for": (_sz, [_int, _int]),
     "rgk_pack_gate_weights": (_int, [ctypes.POINTER(RgkParams), _int, _int, _int, _vp, _vp]),
     "rgk_dense_linear": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _vp, _vp, _vp]),
     "rgk_block_workspace_bytes": (_sz, [_i64, _i64, _i64, _i64, _int]),

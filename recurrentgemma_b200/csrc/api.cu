@@ -109,7 +109,9 @@ int run_gates(const void* c, const void* pos, int pos64, const rgk_params* p, in
                             "(dtype %d, head width %d)", dtype, bw);
   if (tf32_ok && gates_impl != RGK_GATES_SIMT) {
     cudaError_t e = rgk::launch_gates_tf32(c, pos, pos64, p->a_param, p->gate_x_w, p->gate_x_b,
-                                           p->gate_a_w, p->gate_a_b, M, H, wpack, a, xn, ws_header, s);
+                                           p->gate_a_w, p->gate_a_b, M, H,
+                                           p->gates_packed ? const_cast<void*>(p->gates_packed) : wpack,
+                                           p->gates_packed != nullptr, a, xn, ws_header, s);
     if (e != cudaSuccess) return cuda_fail(e, "tcgen05 TF32 gates launch");
     return RGK_OK;
   }
@@ -300,15 +302,28 @@ int rgk_linear_scan(const void* x, const void* a, const uint8_t* reset, const fl
 
 size_t rgk_gate_pack_bytes(int H) { return H > 0 ? rgk::gates_tc_packed_bytes(H) : 0; }
 
+size_t rgk_gate_pack_bytes_for(int H, int dtype) {
+  if (H <= 0) return 0;
+  if (dtype == RGK_BF16) return rgk::gates_tc_packed_bytes(H);
+  if (dtype == RGK_F32) return rgk::gates_tf32_packed_bytes(H);
+  return 0;
+}
+
 int rgk_pack_gate_weights(const rgk_params* p, int H, int bw, int dtype, void* packed_out,
                           void* stream) {
   int rc = check_params(p, false);
   if (rc) return rc;
   RGK_REQUIRE(H >= 1 && packed_out != nullptr && aligned16(packed_out), RGK_EINVAL,
               "bad H or packed_out");
-  RGK_REQUIRE(rgk::gates_tc_supported(dtype, bw, 1), RGK_ESHAPE,
-              "packed gate weights exist for bfloat16 with head width 256 only");
+  RGK_REQUIRE(rgk::gates_tc_supported(dtype, bw, 1) || rgk::gates_tf32_supported(dtype, bw, 1),
+              RGK_ESHAPE, "packed gate weights exist for head width 256 only");
   RGK_CHECK_DEVICE();
+  if (dtype == RGK_F32) {
+    RGK_CUDA(rgk::launch_pack_gate_weights_tf32(p->gate_x_w, p->gate_a_w, H, packed_out,
+                                                static_cast<cudaStream_t>(stream)),
+             "pack_gate_weights (TF32 split) launch");
+    return RGK_OK;
+  }
   RGK_CUDA(rgk::launch_pack_gate_weights(p->gate_x_w, p->gate_a_w, H, packed_out,
                                          static_cast<cudaStream_t>(stream)),
            "pack_gate_weights launch");

@@ -290,18 +290,27 @@ bool gates_tf32_supported(int dtype, int bw, int64_t M) {
   return dtype == 0 && bw == kHW && M >= 1 && M < ((int64_t)1 << 31);
 }
 
-cudaError_t launch_gates_tf32(const void* c, const void* pos, int pos64, const void* a_param,
-                              const void* wx, const void* bx, const void* wa, const void* ba,
-                              int64_t M, int H, void* packed_w, void* a_out, void* xn_out,
-                              void* ws_header, cudaStream_t s) {
-  if (M == 0) return cudaSuccess;
-  const int E = H * kHW;
+cudaError_t launch_pack_gate_weights_tf32(const void* wx, const void* wa, int H, void* packed_w,
+                                          cudaStream_t s) {
   float* hi = static_cast<float*>(packed_w);
   float* lo = hi + (size_t)H * 2 * kTN * kHW;
   pack_gate_weights_tf32_kernel<<<dim3(kHW / 32, kTN / 32, 2 * H), dim3(32, 8), 0, s>>>(
       (const float*)wx, (const float*)wa, H, hi, lo);
-  cudaError_t err = cudaGetLastError();
-  if (err != cudaSuccess) return err;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_gates_tf32(const void* c, const void* pos, int pos64, const void* a_param,
+                              const void* wx, const void* bx, const void* wa, const void* ba,
+                              int64_t M, int H, void* packed_w, bool packed_valid, void* a_out,
+                              void* xn_out, void* ws_header, cudaStream_t s) {
+  if (M == 0) return cudaSuccess;
+  const int E = H * kHW;
+  float* hi = static_cast<float*>(packed_w);
+  float* lo = hi + (size_t)H * 2 * kTN * kHW;
+  if (!packed_valid) {
+    cudaError_t err = launch_pack_gate_weights_tf32(wx, wa, H, packed_w, s);
+    if (err != cudaSuccess) return err;
+  }
 
   CUtensorMap map_x, map_wh, map_wl;
   if (!tensor_map_2d(&map_x, c, (uint64_t)M, (uint64_t)E, kTM, kKS, kSw128, 4, !kSw128) ||

@@ -83,9 +83,11 @@ cudaError_t launch_gates_tc(const void* c, const void* pos, int pos64, const voi
 // gates_tf32_packed_bytes(H) bytes of scratch for the split K-major copies of the weights.
 bool gates_tf32_supported(int dtype, int bw, int64_t M);
 size_t gates_tf32_packed_bytes(int H);
+cudaError_t launch_pack_gate_weights_tf32(const void* wx, const void* wa, int H, void* packed_w,
+                                          cudaStream_t s);
 cudaError_t launch_gates_tf32(const void* c, const void* pos, int pos64, const void* a_param,
                               const void* wx, const void* bx, const void* wa, const void* ba,
-                              int64_t M, int H, void* packed_w, void* a_out, void* xn_out,
+                              int64_t M, int H, void* packed_w, bool packed_valid, void* a_out, void* xn_out,
                               void* ws_header, cudaStream_t s);
 
 // Packs the gate weights only (the first step of launch_gates_tc), for callers that keep the

@@ -246,24 +246,26 @@ class RGLRU(nn.Module):
     return super()._apply(fn, *args, **kwargs)
 
   def _packed_gates(self) -> Optional[int]:
-    """Device pointer of the K-major copy of the gate weights the tcgen05 kernels read, rebuilt
+    """Device pointer of the K-major copy of the gate weights the tcgen05 kernels read (bfloat16,
+    or the hi / lo halves of the float32 weights for the 3xTF32 kernel), rebuilt
     whenever either weight tensor is replaced or modified in place (a derived, non-persistent
     buffer: it never enters the state_dict).  Writes through `.data` bypass the version counter:
     call `invalidate_packed()` after them."""
     wx, wa = self.input_gate.w, self.a_gate.w
-    if (not wx.is_cuda or wx.dtype != torch.bfloat16 or self.width // self.num_heads != 256 or
-        self.gates_impl == _lib.GATES_SIMT):
+    if (not wx.is_cuda or wx.dtype not in (torch.bfloat16, torch.float32) or wa.dtype != wx.dtype
+        or self.width // self.num_heads != 256 or self.gates_impl == _lib.GATES_SIMT):
       return None
-    key = (wx.data_ptr(), wx._version, wa.data_ptr(), wa._version)
+    dt = _lib.dtype_code(wx.dtype)
+    key = (wx.data_ptr(), wx._version, wa.data_ptr(), wa._version, dt)
     if getattr(self, "_pack_key", None) != key:
       lib = _lib.load()
-      buf = torch.empty(lib.rgk_gate_pack_bytes(self.num_heads), dtype=torch.uint8,
+      buf = torch.empty(lib.rgk_gate_pack_bytes_for(self.num_heads, dt), dtype=torch.uint8,
                         device=wx.device)
       p = _lib.RgkParams(a_param=self.a_param.data_ptr(), gate_x_w=wx.data_ptr(),
                          gate_x_b=self.input_gate.b.data_ptr(), gate_a_w=wa.data_ptr(),
                          gate_a_b=self.a_gate.b.data_ptr())
       with torch.cuda.device(wx.device):
-        _lib.check(lib.rgk_pack_gate_weights(ctypes.byref(p), self.num_heads, 256, _lib.RGK_BF16,
+        _lib.check(lib.rgk_pack_gate_weights(ctypes.byref(p), self.num_heads, 256, dt,
                                              buf.data_ptr(), _lib.stream_ptr(wx.device)))
       self._pack_buf, self._pack_key = buf, key
     return self._pack_buf.data_ptr()
