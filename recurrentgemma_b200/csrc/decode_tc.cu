@@ -3,14 +3,14 @@
 // (rnn_scan with one token) and the join of torch/modules.py:627-628, 646.
 //
 // The "tokens" of the contraction are the batch rows.  A CTA serves 128 rows x one quarter of a
-// head (64 channels).  The A operand - the conv output of the 128 rows for all 256 channels of the
-// head, computed from the new token and the three cached rows with the reference's bfloat16
-// roundings, in the 128-byte-swizzled K-major layout tcgen05 reads - is built by every CTA for
-// itself (the four CTAs of a head share the cache lines through L2), while TMA brings the CTA's 64
-// x-gate and 64 a-gate weight rows (64 KiB, pre-packed K-major).  Sixteen tcgen05.mma (M 128,
-// N 128, K 16) leave both gates of every channel in TMEM; the epilogue does the gate arithmetic,
-// the state update h = a h + x in float32 (stored unrounded), the join with gelu(y branch), and
-// writes out / state / shifted conv cache.
+// head (64 channels); the four CTAs of a head form a cluster.  The A operand - the conv output of
+// the 128 rows for all 256 channels of the head, computed from the new token and the three cached
+// rows with the reference's bfloat16 roundings, in the 128-byte-swizzled K-major layout tcgen05
+// reads - is built once per cluster: each CTA computes the slice of its own 64 channels and stores it
+// into the shared memory of all four (distributed shared memory), while TMA brings the CTA's 64
+// x-gate and 64 a-gate weight rows (64 KiB, pre-packed K-major).  Sixteen tcgen05.mma (M 128, N 128, K 16) leave both gates of every channel in TMEM;
+// the epilogue does the gate arithmetic, the state update h = a h + x in float32 (stored
+// unrounded), the join with gelu(y branch), and writes out / state / shifted conv cache.
 //
 // Both mbarrier waits are bounded; on expiry WsHeader::status is raised and the CTA leaves.
 #include <cuda.h>
@@ -47,7 +47,7 @@ __device__ __forceinline__ uint4 add4(const uint4& a, const uint4& b) {
   return make_uint4(badd2(a.x, b.x), badd2(a.y, b.y), badd2(a.z, b.z), badd2(a.w, b.w));
 }
 
-template <bool kMul, bool kInPlace>
+template <bool kMul>
 __global__ void __launch_bounds__(kThreadsDec, 1)
 decode_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __nv_bfloat16* __restrict__ xb,
                  const __nv_bfloat16* __restrict__ yb, const void* __restrict__ pos, int pos64,
@@ -138,73 +138,76 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __nv_bfloat16*
   }
 
   // ---- A operand: conv output of 128 rows x the head's 256 channels ------------------------------
-  // Every CTA builds the whole tile itself: the four CTAs of a head read the same cache lines at
-  // about the same time (one HBM read, three L2 hits), the arithmetic is small, and sharing the
-  // slices through distributed shared memory instead cost two cluster barriers and remote stores
-  // that run far below local shared-memory speed.  A thread owns one 16-byte pack of channels
-  // (32 packs = the head's 256 channels) and walks the rows, 16 rows apart.
+  // The four CTAs of a head (a cluster) need the same A tile.  Each computes the K slice of its own
+  // 64 channels and stores it into the shared memory of all four: a quarter of the loads and of the
+  // arithmetic per CTA.
   {
-    const int pack = tid & 31;                    // pack of 8 channels within the head
-    const int slice = pack >> 3, pk = pack & 7;   // K slice of 64 channels, pack within it
-    const int e = head * kHeadW + pack * 8;
+    const int pk = tid & 7;                       // 16-byte pack inside this CTA's slice of channels
+    const int e = chan0 + pk * 8;
     uint4 wv[4];
 #pragma unroll
     for (int k = 0; k < 4; ++k) wv[k] = *reinterpret_cast<const uint4*>(conv_w + (int64_t)k * E + e);
     const uint4 bv = *reinterpret_cast<const uint4*>(conv_b + e);
+    uint32_t a_remote[4];                         // this slice inside each CTA of the cluster
+#pragma unroll
+    for (int d = 0; d < 4; ++d)
+      asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
+                   : "=r"(a_remote[d]) : "r"(s_base + kOffA + quarter * kASlice), "r"(d));
     // Everything above (barriers, TMEM, the per-channel constants) is independent of the kernel
     // before this one on the stream, which in a decode loop is the previous layer: with
     // programmatic dependent launch it overlaps that kernel's tail.  The activations below are its
     // output, so wait for it here, then let the next layer's prologue start in turn.
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    constexpr int kRowStep = kThreadsDec / 32;         // 16 rows per pass
-    constexpr int kBatch = 4;                          // rows in flight per thread
-    const bool own = slice == quarter;                 // this CTA shifts the cache of its own channels
-#pragma unroll 1
-    for (int r0 = tid >> 5; r0 < kRowsM; r0 += kRowStep * kBatch) {
-      uint4 xv[kBatch][4];
+    // two rows per thread, their 8 loads all issued before the first use
+    constexpr int kPer = kRowsM * 8 / kThreadsDec;     // rows per thread: 2
+    constexpr int kRowStep = kThreadsDec / 8;
+    uint4 xv[kPer][4];
 #pragma unroll
-      for (int i = 0; i < kBatch; ++i) {
-        const int r = r0 + kRowStep * i;
-        const int64_t m = min((int64_t)tile * kRowsM + r, (int64_t)M - 1);   // clamped: never out of range
-        const __nv_bfloat16* cr = cache_in + m * 3 * E + e;
-        xv[i][0] = *reinterpret_cast<const uint4*>(cr);
-        xv[i][1] = *reinterpret_cast<const uint4*>(cr + E);
-        xv[i][2] = *reinterpret_cast<const uint4*>(cr + 2 * (int64_t)E);
-        xv[i][3] = *reinterpret_cast<const uint4*>(xb + m * E + e);
-      }
+    for (int i = 0; i < kPer; ++i) {
+      const int r = (tid >> 3) + kRowStep * i;
+      const int64_t m = min((int64_t)tile * kRowsM + r, (int64_t)M - 1);   // clamped: never out of range
+      const __nv_bfloat16* cr = cache_in + m * 3 * E + e;
+      xv[i][0] = *reinterpret_cast<const uint4*>(cr);
+      xv[i][1] = *reinterpret_cast<const uint4*>(cr + E);
+      xv[i][2] = *reinterpret_cast<const uint4*>(cr + 2 * (int64_t)E);
+      xv[i][3] = *reinterpret_cast<const uint4*>(xb + m * E + e);
+    }
+    // every CTA of the cluster is running before its shared memory is written from outside
+    asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
 #pragma unroll
-      for (int i = 0; i < kBatch; ++i) {
-        const int r = r0 + kRowStep * i;
-        const int64_t m = (int64_t)tile * kRowsM + r;
-        // newest tap first (torch/layers.py:491-517 with prompt_len = 3), then the bias
-        uint4 acc = mul4(xv[i][3], wv[3]);
-        acc = add4(acc, mul4(xv[i][2], wv[2]));
-        acc = add4(acc, mul4(xv[i][1], wv[1]));
-        acc = add4(acc, mul4(xv[i][0], wv[0]));
-        acc = add4(acc, bv);
-        if (m < M) {
-          if (!kInPlace && own && cache_out != nullptr) {
-            __nv_bfloat16* co = cache_out + m * 3 * E + e;
-            *reinterpret_cast<uint4*>(co) = xv[i][1];
-            *reinterpret_cast<uint4*>(co + E) = xv[i][2];
-            *reinterpret_cast<uint4*>(co + 2 * (int64_t)E) = xv[i][3];
-          }
-        } else {
-          acc = make_uint4(0u, 0u, 0u, 0u);
+    for (int i = 0; i < kPer; ++i) {
+      const int r = (tid >> 3) + kRowStep * i;
+      const int64_t m = (int64_t)tile * kRowsM + r;
+      // newest tap first (torch/layers.py:491-517 with prompt_len = 3), then the bias
+      uint4 acc = mul4(xv[i][3], wv[3]);
+      acc = add4(acc, mul4(xv[i][2], wv[2]));
+      acc = add4(acc, mul4(xv[i][1], wv[1]));
+      acc = add4(acc, mul4(xv[i][0], wv[0]));
+      acc = add4(acc, bv);
+      if (m < M) {
+        if (cache_out != nullptr) {               // these are this CTA's own channels: shift the cache
+          __nv_bfloat16* co = cache_out + m * 3 * E + e;
+          *reinterpret_cast<uint4*>(co) = xv[i][1];
+          *reinterpret_cast<uint4*>(co + E) = xv[i][2];
+          *reinterpret_cast<uint4*>(co + 2 * (int64_t)E) = xv[i][3];
         }
-        *reinterpret_cast<uint4*>(smem + kOffA + slice * kASlice + r * 128 + ((pk ^ (r & 7)) << 4)) = acc;
+      } else {
+        acc = make_uint4(0u, 0u, 0u, 0u);
       }
+      const uint32_t off = r * 128 + ((pk ^ (r & 7)) << 4);
+#pragma unroll
+      for (int d = 0; d < 4; ++d)
+        asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};"
+                     :: "r"(a_remote[d] + off), "r"(acc.x), "r"(acc.y), "r"(acc.z), "r"(acc.w) : "memory");
     }
   }
-  // The tile is complete when every thread has stored its packs: the generic-proxy writes are
-  // fenced towards the tensor core's (async) proxy before the barrier.
+  // The tile is complete when all four CTAs have stored their slices: the generic-proxy writes are
+  // fenced towards the tensor core's (async) proxy, then released and acquired across the cluster.
   asm volatile("fence.proxy.async;" ::: "memory");
-  __syncthreads();
-  // In place (cache_out == cache_in) the four CTAs of a head, which all read the head's cache rows,
-  // are a cluster: each tells the others here that it has read them, and the shift of a CTA's own
-  // channels waits for all four at the end of the kernel.
-  if constexpr (kInPlace) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 
   // ---- MMA ------------------------------------------------------------------------------------------
   if (tid == 0) {
@@ -290,28 +293,6 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __nv_bfloat16*
     }
   }
 
-  if constexpr (kInPlace) {
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-    // rows 1, 2 and the new token move to rows 0, 1, 2 of this CTA's 64 channels (nobody else
-    // writes them, so they still hold what the conv above read)
-    const int pk = tid & 7;
-    const int e = chan0 + pk * 8;
-#pragma unroll
-    for (int i = 0; i < kRowsM * 8 / kThreadsDec; ++i) {
-      const int r = (tid >> 3) + (kThreadsDec / 8) * i;
-      const int64_t m = (int64_t)tile * kRowsM + r;
-      if (m < M) {
-        __nv_bfloat16* cr = cache_out + m * 3 * E + e;
-        const uint4 r1 = *reinterpret_cast<const uint4*>(cr + E);
-        const uint4 r2 = *reinterpret_cast<const uint4*>(cr + 2 * (int64_t)E);
-        const uint4 xn = *reinterpret_cast<const uint4*>(xb + m * E + e);
-        *reinterpret_cast<uint4*>(cr) = r1;
-        *reinterpret_cast<uint4*>(cr + E) = r2;
-        *reinterpret_cast<uint4*>(cr + 2 * (int64_t)E) = xn;
-      }
-    }
-  }
-
   tc_fence_before();
   __syncthreads();
   if (tid == 0 && *s_abort) atomicExch(&hdr->status, kStatusTimeout);
@@ -339,16 +320,11 @@ cudaError_t launch_path_decode_tc(const void* xb, const void* yb, const void* po
     return cudaErrorInvalidValue;
   static PerDeviceOnce once;
   cudaError_t e0 = once.run([] {
-    cudaError_t e;
-#define RGK_DEC_ATTR(MUL, INPLACE)                                                              \
-    if ((e = cudaFuncSetAttribute(decode_tc_kernel<MUL, INPLACE>,                               \
-                                  cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem)) != cudaSuccess) return e
-    RGK_DEC_ATTR(true, true);
-    RGK_DEC_ATTR(true, false);
-    RGK_DEC_ATTR(false, true);
-    RGK_DEC_ATTR(false, false);
-#undef RGK_DEC_ATTR
-    return cudaSuccess;
+    cudaError_t e = cudaFuncSetAttribute(decode_tc_kernel<true>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(decode_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                kSmem);
   });
   if (e0 != cudaSuccess) return e0;
   const dim3 grid((unsigned)(H * 4), (unsigned)((B + kRowsM - 1) / kRowsM));
@@ -360,26 +336,21 @@ cudaError_t launch_path_decode_tc(const void* xb, const void* yb, const void* po
   cfg.blockDim = dim3(kThreadsDec);
   cfg.dynamicSmemBytes = kSmem;
   cfg.stream = s;
-  // The cache updated in place: the four CTAs of a head, which all read its cache rows, form a
-  // cluster and hold the shift back until all four have read (see the kernel).
-  const bool in_place = cache_out != nullptr && cache_out == cache_in;
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
-  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].id = cudaLaunchAttributeClusterDimension;      // the four channel quarters of a head
   attr[1].val.clusterDim.x = 4;
   attr[1].val.clusterDim.y = 1;
   attr[1].val.clusterDim.z = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = in_place ? 2 : 1;
-#define RGK_DEC(MUL, INPLACE)                                                                      \
-  cudaLaunchKernelEx(&cfg, decode_tc_kernel<MUL, INPLACE>, map_w, (const T_*)xb, (const T_*)yb,    \
-                     pos, pos64, (const T_*)conv_w, (const T_*)conv_b, (const T_*)a_param,         \
-                     (const T_*)bx, (const T_*)ba, h_in, (const T_*)cache_in, packed_w, (int)B, E, \
-                     (T_*)out, h_out, (T_*)cache_out, reinterpret_cast<WsHeader*>(ws_header))
-  cudaError_t lerr;
-  if (in_place) lerr = yb ? RGK_DEC(true, true) : RGK_DEC(false, true);
-  else lerr = yb ? RGK_DEC(true, false) : RGK_DEC(false, false);
+  cfg.numAttrs = 2;
+#define RGK_DEC(MUL)                                                                               \
+  cudaLaunchKernelEx(&cfg, decode_tc_kernel<MUL>, map_w, (const T_*)xb, (const T_*)yb, pos, pos64, \
+                     (const T_*)conv_w, (const T_*)conv_b, (const T_*)a_param, (const T_*)bx,      \
+                     (const T_*)ba, h_in, (const T_*)cache_in, packed_w, (int)B, E, (T_*)out, h_out,         \
+                     (T_*)cache_out, reinterpret_cast<WsHeader*>(ws_header))
+  cudaError_t lerr = yb ? RGK_DEC(true) : RGK_DEC(false);
   if (lerr != cudaSuccess) return lerr;
 #undef RGK_DEC
   return cudaGetLastError();

@@ -112,8 +112,7 @@ def test_decode_step_at_config_size(rg, oracle, batch):
   """One decode step of the sub-path at the size of the decode workload (batch 256, 2560 channels,
   10 heads, bfloat16, cached conv window, float32 state, some rows at a document start): against
   the oracle, and the in-place form (cache tensors overwritten) against the functional one, bit
-  for bit - every CTA of a head reads the head's whole cache, so the in-place shift has to wait
-  for all of them."""
+  for bit."""
   from recurrentgemma_b200 import _lib, modules
   e, h = 2560, 10
   dt = torch.bfloat16
