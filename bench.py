@@ -409,6 +409,15 @@ def run_gpu(args, cfg):
     two_kernel = {"gates_tc_ms": max(t_lru_tc - t_scan_plain, 1e-6), "scan_join_ms": t_scan,
                   "gates_tc_GB/s": (3 * n_el * es + 2 * gw) / max(t_lru_tc - t_scan_plain, 1e-6) / 1e6,
                   "scan_join_GB/s": 4 * n_el * es / t_scan / 1e6}
+    # And the route with the Conv1D inside the RG-LRU kernel (rgk_set_conv_fusion): one kernel, no
+    # conv output in HBM, the same bits; timed for the record, it is the slower one.
+    lib.rgk_set_conv_fusion(1)
+    try:
+      k_path()
+      torch.cuda.synchronize()
+      two_kernel["conv_fused_in_one_kernel_ms"] = _time_loop(k_path, ksteps, stream)
+    finally:
+      lib.rgk_set_conv_fusion(0)
     del a_t, c, y2
 
     # The whole RecurrentBlock at the same shapes: the three projections on the

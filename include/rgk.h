@@ -200,6 +200,15 @@ RGK_API int rgk_recurrent_path_prefill(const void* xb, const void* yb, const voi
                                void* out, float* h_last, void* conv_cache_out, void* workspace,
                                size_t workspace_bytes, void* stream);
 
+/* Process-wide switch: with enabled != 0 the bfloat16 / head-width-256 prefill of the sub-path (and
+ * of the block entry points built on it) computes the Conv1D inside the RG-LRU kernel - two extra
+ * warps per CTA turn the block input into the kernel's conv-output operand, so the conv output
+ * never reaches HBM - instead of running rgk_conv1d_prefill's kernel first.  The results are the
+ * same bits.  Off by default: measured on a B200 the fused form is the slower one (DRAM traffic
+ * falls by a third, but the kernel is bound by instruction issue, not by HBM).  Returns the
+ * previous setting. */
+RGK_API int rgk_set_conv_fusion(int enabled);
+
 /* ------------------------------------------------------------------------------------------------
  * The same sub-path for one decode step (T == 1 with caches)       torch/modules.py:631-646,
  *   xb, yb [B,E]; conv_cache_in [B,W-1,E]; h_in [B,E] float32     torch/layers.py:170-177, 469-474

@@ -44,6 +44,7 @@ SIGNATURES = {
     "rgk_abi_version": (_int, []),
     "rgk_last_error": (ctypes.c_char_p, []),
     "rgk_device_check": (_int, []),
+    "rgk_set_conv_fusion": (_int, [_int]),
     "rgk_conv1d_prefill": (_int, [_vp, _vp, _int, _vp, _vp, _i64, _i64, _i64, _int, _int, _vp, _vp,
                                   _vp]),
     "rgk_conv1d_decode": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _int, _int, _vp, _vp, _vp]),

@@ -2,6 +2,7 @@
 // and the composition of the kernels into the calls the reference's Python methods map to.
 #include <cstdarg>
 #include <cstdio>
+#include <atomic>
 #include <cstring>
 
 #include "../../include/rgk.h"
@@ -129,12 +130,31 @@ int run_gates(const void* c, const void* pos, int pos64, const rgk_params* p, in
   return RGK_OK;
 }
 
+// Whether the prefill path convolves inside the fused RG-LRU kernel (rgk_set_conv_fusion).  Off by
+// default: on a B200 the two conv warps a CTA can afford cannot keep up with its sixteen epilogue
+// warps (the same bits, at about half the speed of the separate conv kernel).
+static std::atomic<int> g_conv_fusion{0};
+static bool conv_fusion_enabled() { return g_conv_fusion.load(std::memory_order_relaxed) != 0; }
+
 // RG-LRU on a conv output c: fused kernel when asked for / possible, else gates then scan.
+// With xb != nullptr the Conv1D is this function's job as well: `c` is then only a buffer for the
+// conv output, which the fused kernel does not need (it convolves xb itself, unless out aliases
+// xb: the units read each other's input rows) and the other routes fill with conv1d_prefill.
 int run_rglru(const void* c, const void* pos, int pos64, const rgk_params* p, const float* h0,
               const void* yb, int y_activated, int64_t B, int64_t T, int64_t E, int H, int dtype,
               int gates_impl, void* wpack, void* a_buf, void* xn_buf, void* scan_ws, void* out,
-              float* h_last, cudaStream_t s) {
+              float* h_last, cudaStream_t s, const void* xb = nullptr, void* conv_cache_out = nullptr) {
   const int bw = (int)(E / H);
+  const bool chan_route = rgk::rglru_chan_supported(dtype, bw, B, T) &&
+                          (gates_impl == RGK_GATES_AUTO || gates_impl >= RGK_GATES_FUSED);
+  const bool fuse_conv = xb != nullptr && chan_route && out != xb && conv_fusion_enabled();
+  if (xb != nullptr) {
+    cudaError_t e = fuse_conv
+        ? rgk::launch_conv1d_cache(xb, pos, pos64, B, T, E, dtype, conv_cache_out, s)
+        : rgk::launch_conv1d_prefill(xb, pos, pos64, p->conv_w, p->conv_b, B, T, E, dtype,
+                                     const_cast<void*>(c), conv_cache_out, s);
+    if (e != cudaSuccess) return cuda_fail(e, "conv1d launch");
+  }
   const bool fused_ok = rgk::rglru_chan_supported(dtype, bw, B, T);
   const bool want_fused = gates_impl >= RGK_GATES_FUSED;
   if (want_fused && !fused_ok)
@@ -148,9 +168,10 @@ int run_rglru(const void* c, const void* pos, int pos64, const rgk_params* p, co
       if (e != cudaSuccess) return cuda_fail(e, "pack_gate_weights launch");
       packed = wpack;
     }
-    cudaError_t e = rgk::launch_rglru_chan(c, pos, pos64, p->a_param, p->gate_x_b, p->gate_a_b,
-                                           packed, h0, yb, y_activated, B, T, H, out, h_last,
-                                           scan_ws, math, s);
+    cudaError_t e = rgk::launch_rglru_chan(fuse_conv ? xb : c, pos, pos64, p->a_param, p->gate_x_b,
+                                           p->gate_a_b, packed, h0, yb, y_activated, B, T, H, out,
+                                           h_last, scan_ws, math, s, fuse_conv ? p->conv_w : nullptr,
+                                           fuse_conv ? p->conv_b : nullptr);
     if (e != cudaSuccess) return cuda_fail(e, "fused RG-LRU launch");
     return RGK_OK;
   }
@@ -225,6 +246,10 @@ int rgk_workspace_status(void* workspace, void* stream) {
                               "cleared; results of the calls on this workspace since then are invalid");
   }
   return RGK_OK;
+}
+
+int rgk_set_conv_fusion(int enabled) {
+  return g_conv_fusion.exchange(enabled != 0 ? 1 : 0, std::memory_order_relaxed);
 }
 
 int rgk_conv1d_prefill(const void* x, const void* segment_pos, int pos_dtype, const void* w,
@@ -440,12 +465,9 @@ int rgk_recurrent_path_prefill(const void* xb, const void* yb, const void* segme
   RGK_CHECK_DEVICE();
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int bw = (int)(E / H);
-  RGK_CUDA(rgk::launch_conv1d_prefill(xb, segment_pos, pos_dtype, p->conv_w, p->conv_b, B, T, E,
-                                      dtype, w.c, conv_cache_out, s),
-           "conv1d_prefill launch");
   (void)bw;
   return run_rglru(w.c, segment_pos, pos_dtype, p, h0, yb, 0, B, T, E, H, dtype, gates_impl,
-                   w.wpack, w.a, w.xn, w.scan, out, h_last, s);
+                   w.wpack, w.a, w.xn, w.scan, out, h_last, s, xb, conv_cache_out);
 }
 
 int rgk_dense_linear(const void* x, const void* weight, const void* bias, int64_t M, int64_t K,
@@ -614,15 +636,18 @@ static int block_prefill_impl(const void* x_in, const void* residual, const void
   RGK_CUDA(rgk::launch_dense_tc(x_in, p->linear_x_w, p->linear_x_b, nullptr, M, (int)D, (int)E, 0, xb,
                                 status, s),
            "linear_x launch");
-  RGK_CUDA(rgk::launch_conv1d_prefill(xb, segment_pos, pos_dtype, p->path.conv_w, p->path.conv_b, B,
-                                      T, E, dtype, w.c, conv_cache_out, s),
-           "conv1d_prefill launch");
-  // the conv has consumed xb: its buffer now receives y * gelu(yb)
+  // Conv1D inside the RG-LRU kernel where that kernel applies (the joined output y * gelu(yb) then
+  // goes to the conv-output buffer, which the fused form does not use), else as its own kernel
+  // (a warp reads its tile of yb before it writes the same tile of the output); with a separate
+  // conv kernel xb has been consumed by then and receives the output
+  const bool fused = rgk::rglru_chan_supported(dtype, (int)(E / H), B, T) && conv_fusion_enabled();
+  char* joined = fused ? yb : xb;
   if ((rc = run_rglru(w.c, segment_pos, pos_dtype, &p->path, nullptr, yb, 1, B, T, E, H, dtype,
-                      RGK_GATES_AUTO, w.wpack, w.a, w.xn, w.scan, xb, h_last, s)))
+                      RGK_GATES_AUTO, w.wpack, w.a, w.xn, w.scan, joined, h_last, s, xb,
+                      conv_cache_out)))
     return rc;
-  RGK_CUDA(rgk::launch_dense_tc(xb, p->linear_out_w, p->linear_out_b, residual, M, (int)E, (int)D, 0,
-                                out, status, s),
+  RGK_CUDA(rgk::launch_dense_tc(joined, p->linear_out_w, p->linear_out_b, residual, M, (int)E, (int)D,
+                                0, out, status, s),
            "linear_out launch");
   return RGK_OK;
 }

@@ -154,6 +154,38 @@ conv1d_prefill_kernel(const T* __restrict__ x, const void* __restrict__ pos, int
   }
 }
 
+// Only the cache a prefill returns (for callers that compute the convolution themselves): rows
+// T-3 .. T-1 of the input, each multiplied by (0 or 1) for the document starts that follow it
+// (torch/layers.py:497-508, 526).
+template <typename T>
+__global__ void __launch_bounds__(kConvThreads)
+conv1d_cache_kernel(const T* __restrict__ x, const void* __restrict__ pos, int pos64, int T_, int E,
+                    T* __restrict__ cache_out) {
+  constexpr int kPack = Traits<T>::kPack;
+  using Ops = PackOps<T>;
+  const int e0 = (blockIdx.x * kConvThreads + threadIdx.x) * kPack;
+  if (e0 >= E) return;
+  const int b = blockIdx.y;
+  const int64_t row0 = (int64_t)b * T_;
+  // n0 / n1: rows T-1 / T-2 start no document
+  const bool n0 = !pos_is_zero(pos, pos64, row0 + T_ - 1);
+  const bool n1 = T_ >= 2 ? !pos_is_zero(pos, pos64, row0 + T_ - 2) : true;
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+  T* c = cache_out + (int64_t)b * 3 * E + e0;
+  uint4 v2 = zero, v1 = zero;
+  if (T_ >= 3) {
+    const uint4 x2 = ld_stream(x + (row0 + T_ - 3) * E + e0);
+    v2 = (n0 && n1) ? x2 : Ops::zero_like(x2);
+  }
+  if (T_ >= 2) {
+    const uint4 x1 = ld_stream(x + (row0 + T_ - 2) * E + e0);
+    v1 = n0 ? x1 : Ops::zero_like(x1);
+  }
+  *reinterpret_cast<uint4*>(c) = v2;
+  *reinterpret_cast<uint4*>(c + E) = v1;
+  *reinterpret_cast<uint4*>(c + 2 * (int64_t)E) = ld_stream(x + (row0 + T_ - 1) * E + e0);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kConvThreads)
 conv1d_decode_kernel(const T* x, const T* cache_in, const T* __restrict__ w,
@@ -204,6 +236,20 @@ cudaError_t launch_conv1d_prefill(const void* x, const void* pos, int pos64, con
         (const float*)x, pos, pos64, (const float*)w, (const float*)b, (int)T, (int)E, (float*)out,
         (float*)cache_out);
   }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_conv1d_cache(const void* x, const void* pos, int pos64, int64_t B, int64_t T,
+                                int64_t E, int dtype, void* cache_out, cudaStream_t s) {
+  if (B == 0 || T == 0 || E == 0 || cache_out == nullptr) return cudaSuccess;
+  const int pack = dtype ? 8 : 4;
+  dim3 grid((unsigned)((E / pack + kConvThreads - 1) / kConvThreads), (unsigned)B);
+  if (dtype)
+    conv1d_cache_kernel<__nv_bfloat16><<<grid, kConvThreads, 0, s>>>(
+        (const __nv_bfloat16*)x, pos, pos64, (int)T, (int)E, (__nv_bfloat16*)cache_out);
+  else
+    conv1d_cache_kernel<float><<<grid, kConvThreads, 0, s>>>((const float*)x, pos, pos64, (int)T,
+                                                            (int)E, (float*)cache_out);
   return cudaGetLastError();
 }
 

@@ -56,6 +56,9 @@ enum { kMathExact = 0, kMathFast = 1 };
 cudaError_t launch_conv1d_prefill(const void* x, const void* pos, int pos64, const void* w,
                                   const void* b, int64_t B, int64_t T, int64_t E, int dtype,
                                   void* out, void* cache_out, cudaStream_t s);
+// the cache a prefill returns, alone (the fused RG-LRU kernel computes the convolution itself)
+cudaError_t launch_conv1d_cache(const void* x, const void* pos, int pos64, int64_t B, int64_t T,
+                                int64_t E, int dtype, void* cache_out, cudaStream_t s);
 cudaError_t launch_conv1d_decode(const void* x, const void* cache_in, const void* w, const void* b,
                                  int64_t B, int64_t E, int dtype, void* out, void* cache_out,
                                  cudaStream_t s);
@@ -115,7 +118,8 @@ size_t rglru_chan_workspace_bytes(int64_t B, int64_t T, int64_t E);
 cudaError_t launch_rglru_chan(const void* c, const void* pos, int pos64, const void* a_param,
                               const void* bx, const void* ba, const void* packed_w, const float* h0,
                               const void* yb, int y_activated, int64_t B, int64_t T, int H,
-                              void* out, float* h_last, void* ws, int math, cudaStream_t s);
+                              void* out, float* h_last, void* ws, int math, cudaStream_t s,
+                              const void* conv_w = nullptr, const void* conv_b = nullptr);
 
 // gemm_tc.cu: out [M,N] = x [M,K] W[N,K]^T + bias (bfloat16, float32 accumulation) on tcgen05;
 // gelu == 1 applies gelu_tanh to the rounded result; gelu == 2 is the GeGLU epilogue of the MLP

@@ -53,6 +53,17 @@ constexpr int kWBytes = 2 * kUC * kKB * 2;     // 32 KiB: x-gate rows then a-gat
 constexpr int kStage = kCBytes + kWBytes;
 constexpr int kEpi = 16;
 constexpr int kThreads = (kEpi + 2) * 32;
+// With the Conv1D fused (kConv): two more warps turn the block input into the conv-output operand.
+// The ring then has two stages; the room of the third holds two staging buffers for the input rows
+// of a K-slice (the unit's 128 tokens and the three before them, 64 channels).
+constexpr int kConvWarps = 2;
+constexpr int kThreadsConv = (kEpi + 2 + kConvWarps) * 32;
+constexpr int kRingConv = 2;
+constexpr int kXRows = kUT + 3;
+constexpr int kXBytes = kXRows * kKB * 2;      // 16768
+constexpr int kXStage = 17 * 1024;
+constexpr int kOffXs = kRingConv * kStage;
+static_assert(kOffXs + 2 * kXStage <= kRing * kStage, "the staging buffers overlap the warp tiles");
 constexpr int kSub = 32;                 // a warp's tile: 32 tokens x 32 channels
 constexpr int kSubBytes = kSub * kSub * 2;
 constexpr int kOffRing = 0;
@@ -61,7 +72,7 @@ constexpr int kOffQmap = kOffTiles + kEpi * 2 * kSubBytes;     // float2 [2 pari
 constexpr int kOffHin = kOffQmap + 2 * 4 * 3 * 32 * 8;         // float  [2 parity][4 chq][32]
 constexpr int kOffKnown = kOffHin + 2 * 4 * 32 * 4;              // int    [2 parity][4 chq]
 constexpr int kOffBar = kOffKnown + 2 * 4 * 4;
-constexpr int kNumBar = 2 * kRing + 4 + 2 * kEpi;
+constexpr int kNumBar = 2 * kRing + 4 + 2 * kEpi + 5;        // + staging full[2], empty[2], conv tiles free
 constexpr int kOffTmem = kOffBar + kNumBar * 8;
 constexpr int kOffAbort = kOffTmem + 4;
 constexpr int kOffLut = (kOffAbort + 4 + 15) & ~15;            // {a, multiplier} by log_a, see tc_common.cuh
@@ -69,6 +80,13 @@ constexpr int kSmem = kOffLut + kLutEntries * 4 + 1024;
 static_assert(kSmem <= 232448, "exceeds the 227 KiB of shared memory a CTA may use");
 constexpr uint32_t kIdesc = tc_idesc_bf16(kUC, kUT);
 constexpr unsigned kLookbackSpins = 1u << 20;
+
+__device__ __forceinline__ uint4 mul4(const uint4& a, const uint4& b) {
+  return make_uint4(bmul2(a.x, b.x), bmul2(a.y, b.y), bmul2(a.z, b.z), bmul2(a.w, b.w));
+}
+__device__ __forceinline__ uint4 add4(const uint4& a, const uint4& b) {
+  return make_uint4(badd2(a.x, b.x), badd2(a.y, b.y), badd2(a.z, b.z), badd2(a.w, b.w));
+}
 
 // An inclusive state travels as one 64-bit word per channel {h, token}: one store, one load, and a
 // reader that finds the token has the value, without a flag or a fence.
@@ -247,15 +265,18 @@ struct UnitStep {
 };
 
 // kJoin 0: out = y, 1: out = y * gelu_tanh(yb), 2: out = y * yb;  kMath: see tc_common.cuh
-template <int kJoin, int kMath>
-__global__ void __launch_bounds__(kThreads, 1)
+// kConv: map_c is a map of the block input xb (boxes of 131 rows x 64 channels, no swizzle) and the
+// kernel computes the Conv1D (conv_w [4, E], conv_b [E]) itself.
+template <int kJoin, int kMath, bool kConv>
+__global__ void __launch_bounds__(kConv ? kThreadsConv : kThreads, 1)
 rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_w,
                   const __grid_constant__ CUtensorMap map_ct, const __grid_constant__ CUtensorMap map_yt,
                   const __grid_constant__ CUtensorMap map_ot, const void* __restrict__ pos, int pos64,
                   const __nv_bfloat16* __restrict__ bias_x, const __nv_bfloat16* __restrict__ bias_a,
                   const __nv_bfloat16* __restrict__ m8sp, const float* __restrict__ h0, int B, int T_,
                   int E, int groups, int n_units, float* __restrict__ h_last, WsHeader* hdr,
-                  unsigned long long* agg, unsigned long long* incl, int use_agg) {
+                  unsigned long long* agg, unsigned long long* incl, int use_agg,
+                  const __nv_bfloat16* __restrict__ conv_w, const __nv_bfloat16* __restrict__ conv_b) {
   extern __shared__ uint8_t smem_raw[];
   // aligned by an offset into the shared array, so that the address space stays known to the
   // compiler (shared-memory load/store instructions instead of generic ones)
@@ -268,6 +289,11 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
   auto bar_acc_empty = [&](int s) { return bar0 + 8u * (2 * kRing + 2 + s); };
   auto bar_ct = [&](int w) { return bar0 + 8u * (2 * kRing + 4 + w); };
   auto bar_yt = [&](int w) { return bar0 + 8u * (2 * kRing + 4 + kEpi + w); };
+  auto bar_xs_full = [&](int s) { return bar0 + 8u * (2 * kRing + 4 + 2 * kEpi + s); };
+  auto bar_xs_empty = [&](int s) { return bar0 + 8u * (2 * kRing + 4 + 2 * kEpi + 2 + s); };
+  const uint32_t bar_cfree = bar0 + 8u * (2 * kRing + 4 + 2 * kEpi + 4);
+  constexpr int kR = kConv ? kRingConv : kRing;          // ring stages in use
+  constexpr int kAllThreads = kConv ? kThreadsConv : kThreads;
   volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(smem + kOffTmem);
   volatile int* s_abort = reinterpret_cast<volatile int*>(smem + kOffAbort);
 
@@ -279,10 +305,14 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
   // a = exp(log_a) and the input multiplier by log_a: computed once per CTA with the very
   // operations the gate arithmetic would use, so that looking them up changes no bit
   uint32_t* s_lut = reinterpret_cast<uint32_t*>(smem + kOffLut);
-  for (int i = threadIdx.x; i < kLutEntries; i += kThreads) s_lut[i] = a_mult_entry(i);
+  for (int i = threadIdx.x; i < kLutEntries; i += kAllThreads) s_lut[i] = a_mult_entry(i);
   if (threadIdx.x == 0) {
     *s_abort = 0;
-    for (int s = 0; s < kRing; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
+    // with the conv fused a stage is full when the weights have landed AND the conv warps have
+    // written their slice
+    for (int s = 0; s < kRing; ++s) { mbar_init(bar_full(s), kConv ? 2 : 1); mbar_init(bar_empty(s), 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(bar_xs_full(s), 1); mbar_init(bar_xs_empty(s), 1); }
+    mbar_init(bar_cfree, kEpi);
     for (int s = 0; s < 2; ++s) { mbar_init(bar_acc_full(s), 1); mbar_init(bar_acc_empty(s), kEpi); }
     for (int w = 0; w < kEpi; ++w) { mbar_init(bar_ct(w), 1); mbar_init(bar_yt(w), 1); }
     mbar_fence_init();
@@ -307,12 +337,26 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
         const int tt = u / per_tt, rem = u - tt * per_tt;
         const int b = rem / groups, grp = rem - b * groups;
         for (int kb = 0; kb < kKBlocks; ++kb, ++it) {
-          const int s = it % kRing;
-          ok = mbar_wait(bar_empty(s), ((it / kRing) & 1) ^ 1, s_abort);
+          if constexpr (kConv) {
+            // the input rows of this K-slice for the conv warps (rows before the sequence and past
+            // its end read as zero: the first coordinate may be negative)
+            const int xs = it & 1;
+            ok = mbar_wait(bar_xs_empty(xs), ((it >> 1) & 1) ^ 1, s_abort);
+            if (!ok) break;
+            mbar_expect_tx(bar_xs_full(xs), kXBytes);
+            tma_load_3d(s_base + kOffXs + xs * kXStage, &map_c, (grp >> 1) * kHW + kb * kKB, tt * kUT - 3,
+                        b, bar_xs_full(xs));
+          }
+          const int s = it % kR;
+          ok = mbar_wait(bar_empty(s), ((it / kR) & 1) ^ 1, s_abort);
           if (!ok) break;
-          mbar_expect_tx(bar_full(s), kStage);
-          tma_load_3d(s_base + kOffRing + s * kStage, &map_c, (grp >> 1) * kHW + kb * kKB, tt * kUT, b,
-                      bar_full(s));
+          if constexpr (kConv) {
+            mbar_expect_tx(bar_full(s), kWBytes);
+          } else {
+            mbar_expect_tx(bar_full(s), kStage);
+            tma_load_3d(s_base + kOffRing + s * kStage, &map_c, (grp >> 1) * kHW + kb * kKB, tt * kUT, b,
+                        bar_full(s));
+          }
           tma_load_2d(s_base + kOffRing + s * kStage + kCBytes, &map_w, kb * kKB, grp * 2 * kUC,
                       bar_full(s));
         }
@@ -329,8 +373,8 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
         if (!ok) break;
         tc_fence_after();
         for (int kb = 0; kb < kKBlocks; ++kb, ++it) {
-          const int s = it % kRing;
-          ok = mbar_wait(bar_full(s), (it / kRing) & 1, s_abort);
+          const int s = it % kR;
+          ok = mbar_wait(bar_full(s), (it / kR) & 1, s_abort);
           if (!ok) break;
           tc_fence_after();
           const uint32_t c0 = s_base + kOffRing + s * kStage, w0 = c0 + kCBytes;
@@ -345,6 +389,110 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
           tc_commit(bar_empty(s));
         }
         if (ok) tc_commit(bar_acc_full(as));
+      }
+    }
+  } else if (kConv && warp >= kEpi + 2) {
+    // ------------------------------ Conv1D (torch/layers.py:447-529) ------------------------------
+    // Per K-slice (64 channels of the head) the 64 threads own one 16-byte pack of channels (8) x
+    // a run of 16 tokens (8 runs): 19 input rows from the staging buffer through a sliding window,
+    // four products and four sums per pack in packed bfloat16 (each rounds where torch does), the
+    // result into the slice of the MMA operand (128-byte swizzle) and, for the 128 channels of
+    // this unit's half head, into the epilogue warps' conv tiles (rows of 64 bytes, 64-byte
+    // swizzle), as the copy engine would have delivered them.
+    const int ctid = (int)threadIdx.x - (kEpi + 2) * 32;
+    const int pk = ctid & 7, tg = ctid >> 3;
+    unsigned it = 0;
+    bool ok = true;
+    for (int t = 0; t < n_my && ok; ++t) {
+      const int u = blockIdx.x + t * gridDim.x;
+      const int tt = u / per_tt, rem = u - tt * per_tt;
+      const int b = rem / groups, grp = rem - b * groups;
+      const int head = grp >> 1, half = grp & 1;
+      // nz bit j: token tt*128 + tg*16 - 2 + j starts no document (tokens outside the sequence
+      // count as set: their rows are zero, so their taps add nothing).  A warp covers 64 tokens
+      // and the two before them: three coalesced loads and ballots, then every thread cuts out
+      // the 18 bits of its run.
+      unsigned nz;
+      {
+        const int wl = ctid >> 5, cl = ctid & 31;
+        const int base = tt * kUT + wl * 64 - 2;
+        unsigned word[3];
+#pragma unroll
+        for (int q = 0; q < 3; ++q) {
+          const int tok = base + q * 32 + cl;
+          const bool inside = tok >= 0 && tok < T_ && (q < 2 || cl < 2);
+          const bool starts = inside && pos_is_zero(pos, pos64, (int64_t)b * T_ + (inside ? tok : 0));
+          word[q] = __ballot_sync(0xffffffffu, !starts);
+        }
+        const int off = (cl >> 3) * 16;               // first bit of this thread's run
+        const unsigned long long lo = (unsigned long long)word[0] | ((unsigned long long)word[1] << 32);
+        unsigned long long v = lo >> off;
+        if (off == 48) v |= (unsigned long long)(word[2] & 3u) << 16;
+        nz = (unsigned)v & 0x3ffffu;
+      }
+      const bool plain = nz == 0x3ffffu;
+      for (int kb = 0; kb < kKBlocks && ok; ++kb, ++it) {
+        const int xs = it & 1, s = it % kR;
+        const bool mine = (kb >> 1) == half;         // a slice of this unit's own 128 channels
+        const int e = head * kHW + kb * kKB + pk * 8;
+        uint4 wv[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) wv[k] = __ldg(reinterpret_cast<const uint4*>(conv_w + (int64_t)k * E + e));
+        const uint4 bv = __ldg(reinterpret_cast<const uint4*>(conv_b + e));
+        ok = mbar_wait(bar_xs_full(xs), (it >> 1) & 1, s_abort);
+        if (ok) ok = mbar_wait(bar_empty(s), ((it / kR) & 1) ^ 1, s_abort);
+        // the epilogue warps have taken the previous unit's conv tiles out of their buffers
+        if (ok && mine && t > 0 && (kb & 1) == 0) ok = mbar_wait(bar_cfree, (t - 1) & 1, s_abort);
+        if (!ok) break;
+        // the staging rows are read with loads the compiler may move across the stores below (the
+        // buffers are disjoint), so that the rows of a run are in flight together
+        uint32_t xrow = s_base + kOffXs + xs * kXStage + (tg * 16) * (kKB * 2) + pk * 16;
+        asm volatile("" : "+r"(xrow) :: "memory");   // the loads below stay behind the waits above
+        auto lds16 = [](uint32_t addr) {
+          uint4 v;
+          asm("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+          return v;
+        };
+        uint8_t* c_op = smem + kOffRing + s * kStage;
+        uint4 x0 = lds16(xrow);
+        uint4 x1 = lds16(xrow + kKB * 2);
+        uint4 x2 = lds16(xrow + 2 * kKB * 2);
+#pragma unroll
+        for (int r = 0; r < 16; ++r) {
+          const uint4 x3 = lds16(xrow + (r + 3) * (kKB * 2));
+          // newest tap first; tap s survives while rows t-s+1 .. t start no document
+          uint4 acc = mul4(x3, wv[3]);
+          if (plain) {
+            acc = add4(acc, mul4(x2, wv[2]));
+            acc = add4(acc, mul4(x1, wv[1]));
+            acc = add4(acc, mul4(x0, wv[0]));
+          } else {
+            const bool n0 = (nz >> (r + 2)) & 1u, n1 = (nz >> (r + 1)) & 1u, n2 = (nz >> r) & 1u;
+            if (n0) acc = add4(acc, mul4(x2, wv[2]));
+            if (n0 && n1) acc = add4(acc, mul4(x1, wv[1]));
+            if (n0 && n1 && n2) acc = add4(acc, mul4(x0, wv[0]));
+          }
+          acc = add4(acc, bv);
+          const int row = tg * 16 + r;               // token of the unit
+          *reinterpret_cast<uint4*>(c_op + row * 128 + ((pk ^ (row & 7)) << 4)) = acc;
+          if (mine) {
+            const int w_dst = (row >> 5) * 4 + (kb & 1) * 2 + (pk >> 2);   // token quarter, channel quarter
+            const int rr = row & 31, piece = pk & 3;
+            *reinterpret_cast<uint4*>(smem + kOffTiles + w_dst * 2 * kSubBytes + rr * 64 +
+                                      ((piece ^ ((rr >> 1) & 3)) << 4)) = acc;
+          }
+          x0 = x1; x1 = x2; x2 = x3;
+        }
+        // the operand slice is read by the tensor core (async proxy), the staging buffer is
+        // overwritten by the copy engine: both after this thread's generic accesses
+        fence_proxy_async();
+        named_bar_sync(5, kConvWarps * 32);
+        if (ctid == 0) {
+          mbar_arrive(bar_full(s));
+          mbar_arrive(bar_xs_empty(xs));
+          if (mine && (kb & 1) == 1)
+            for (int w = 0; w < kEpi; ++w) mbar_arrive(bar_ct(w));
+        }
       }
     }
   } else {
@@ -384,7 +532,7 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
       const int tok = u.tt * kUT + tq * kSub + lane;
       return tok < T_ && pos_is_zero(pos, pos64, (int64_t)u.b * T_ + tok);
     };
-    if (lane == 0 && n_my > 0) {
+    if (!kConv && lane == 0 && n_my > 0) {
       mbar_expect_tx(bar_ct(warp), kSubBytes);
       tma_load_3d(tile_c_s, &map_ct, chan0(cur), cur.tt * kUT + tq * kSub, cur.b, bar_ct(warp));
     }
@@ -468,7 +616,9 @@ rglru_chan_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_consta
           // accesses of every lane are ordered before the copy engine's write)
           fence_proxy_async();
           __syncwarp();
-          if (lane == 0 && t + 1 < n_my) {
+          if constexpr (kConv) {
+            if (lane == 0) mbar_arrive(bar_cfree);   // the conv warps may write the next unit's tile
+          } else if (lane == 0 && t + 1 < n_my) {
             mbar_expect_tx(bar_ct(warp), kSubBytes);
             tma_load_3d(tile_c_s, &map_ct, chan0(nxt), nxt.tt * kUT + tq * kSub, nxt.b, bar_ct(warp));
           }
@@ -652,20 +802,22 @@ ChanLayout chan_layout(int64_t B, int64_t T, int64_t E) {
 
 // The kernel needs more dynamic shared memory than the default limit: the attribute is a property
 // of the function on ONE device, so it is set (and the SM count read) once per device.
-template <int kMath>
+template <int kMath, bool kConv>
 cudaError_t chan_set_smem() {
   cudaError_t e;
-  if ((e = cudaFuncSetAttribute(rglru_chan_kernel<0, kMath>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem)) != cudaSuccess) return e;
-  if ((e = cudaFuncSetAttribute(rglru_chan_kernel<1, kMath>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem)) != cudaSuccess) return e;
-  return cudaFuncSetAttribute(rglru_chan_kernel<2, kMath>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+  if ((e = cudaFuncSetAttribute(rglru_chan_kernel<0, kMath, kConv>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem)) != cudaSuccess) return e;
+  if ((e = cudaFuncSetAttribute(rglru_chan_kernel<1, kMath, kConv>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem)) != cudaSuccess) return e;
+  return cudaFuncSetAttribute(rglru_chan_kernel<2, kMath, kConv>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
 }
 
 cudaError_t chan_device_setup(int* num_sms) {
   static PerDeviceOnce once;
   return once.run([] {
-    cudaError_t e = chan_set_smem<kMathExact>();
-    if (e != cudaSuccess) return e;
-    return chan_set_smem<kMathFast>();
+    cudaError_t e;
+    if ((e = chan_set_smem<kMathExact, false>()) != cudaSuccess) return e;
+    if ((e = chan_set_smem<kMathFast, false>()) != cudaSuccess) return e;
+    if ((e = chan_set_smem<kMathExact, true>()) != cudaSuccess) return e;
+    return chan_set_smem<kMathFast, true>();
   }, num_sms);
 }
 
@@ -683,8 +835,10 @@ size_t rglru_chan_workspace_bytes(int64_t B, int64_t T, int64_t E) {
 cudaError_t launch_rglru_chan(const void* c, const void* pos, int pos64, const void* a_param,
                               const void* bx, const void* ba, const void* packed_w, const float* h0,
                               const void* yb, int y_activated, int64_t B, int64_t T, int H,
-                              void* out, float* h_last, void* ws, int math, cudaStream_t s) {
+                              void* out, float* h_last, void* ws, int math, cudaStream_t s,
+                              const void* conv_w, const void* conv_b) {
   using T_ = __nv_bfloat16;
+  const bool conv = conv_w != nullptr;       // `c` is then the block input, the kernel convolves it
   const int E = H * kHW;
   const ChanLayout L = chan_layout(B, T, E);
   char* base = static_cast<char*>(ws);
@@ -708,18 +862,22 @@ cudaError_t launch_rglru_chan(const void* c, const void* pos, int pos64, const v
 
   CUtensorMap map_c, map_w, map_ct, map_yt, map_ot;
   const uint64_t Bu = (uint64_t)B, Tu = (uint64_t)T, Eu = (uint64_t)E;
-  if (!tensor_map_bte(&map_c, c, Bu, Tu, Eu, kUT, kKB, true) ||
+  if (!(conv ? tensor_map_bte(&map_c, c, Bu, Tu, Eu, kXRows, kKB, false)
+             : tensor_map_bte(&map_c, c, Bu, Tu, Eu, kUT, kKB, true)) ||
       !tensor_map_2d(&map_w, packed_w, (uint64_t)H * 4 * kUC, kHW, 2 * kUC, kKB, true) ||
       !tensor_map_bte_sw64(&map_ct, c, Bu, Tu, Eu, kSub, kSub) ||
       !tensor_map_bte_sw64(&map_ot, out, Bu, Tu, Eu, kSub, kSub) ||
       !tensor_map_bte_sw64(&map_yt, yb != nullptr ? yb : out, Bu, Tu, Eu, kSub, kSub))
     return cudaErrorInvalidValue;
-#define RGK_CHAN(J, M)                                                                           \
-  rglru_chan_kernel<J, M><<<grid, kThreads, kSmem, s>>>(                                         \
+#define RGK_CHAN_C(J, M, C, THREADS)                                                             \
+  rglru_chan_kernel<J, M, C><<<grid, THREADS, kSmem, s>>>(                                       \
       map_c, map_w, map_ct, map_yt, map_ot, pos, pos64, (const T_*)bx, (const T_*)ba, m8sp, h0,  \
       (int)B, (int)T, E, groups, n_units, h_last, reinterpret_cast<WsHeader*>(base),             \
       reinterpret_cast<unsigned long long*>(base + L.agg_off),                                   \
-      reinterpret_cast<unsigned long long*>(base + L.incl_off), use_agg)
+      reinterpret_cast<unsigned long long*>(base + L.incl_off), use_agg, (const T_*)conv_w,      \
+      (const T_*)conv_b)
+#define RGK_CHAN(J, M)                                                                           \
+  do { if (conv) RGK_CHAN_C(J, M, true, kThreadsConv); else RGK_CHAN_C(J, M, false, kThreads); } while (0)
 #define RGK_CHAN_J(M)                                                                            \
   if (join == 0) RGK_CHAN(0, M); else if (join == 1) RGK_CHAN(1, M); else RGK_CHAN(2, M)
   const int join = yb == nullptr ? 0 : (y_activated ? 2 : 1);
@@ -730,6 +888,7 @@ cudaError_t launch_rglru_chan(const void* c, const void* pos, int pos64, const v
   }
 #undef RGK_CHAN_J
 #undef RGK_CHAN
+#undef RGK_CHAN_C
   return cudaGetLastError();
 }
 

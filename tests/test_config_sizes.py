@@ -145,3 +145,53 @@ def test_decode_step_at_config_size(rg, oracle, batch):
   assert torch.equal(own.rg_lru_state, new.rg_lru_state), "in-place state"
   assert torch.equal(own.conv1d_state, new.conv1d_state), "in-place conv window"
   _lib.check_status()
+
+
+@pytest.mark.parametrize("b,t,e,h", [(2, 1000, 512, 2), (1, 131, 256, 1), (3, 4096, 2560, 10), (2, 5, 256, 1),
+                                     (8, 300, 2560, 10)])
+@pytest.mark.parametrize("exact", [False, True])
+def test_conv_fused_in_rglru_kernel_same_bits(rg, b, t, e, h, exact):
+  """With rgk_set_conv_fusion(1) the prefill path convolves inside the RG-LRU kernel (no conv output
+  in HBM); its output, state and conv window must be the very bits of the composition Conv1D kernel -> RG-LRU kernel on the
+  conv output, including partial time tiles, sequences shorter than the window, and documents that
+  start on and around the edges of the 128-token units (bit for bit where the kernel is
+  deterministic, see below)."""
+  from recurrentgemma_b200 import _lib
+  dt = torch.bfloat16
+  g = torch.Generator(device="cpu").manual_seed(b * 1000 + t + e)
+  p = synthetic.rglru_params(e, h, g, dt)
+  conv = rg.Conv1D(e, 4, device=DEV, dtype=dt)
+  conv.load_state_dict({"w": (torch.randn((4, e), generator=g) * 0.5).to(dt),
+                        "b": (torch.randn((e,), generator=g) * 0.1).to(dt)})
+  lru = _lru(rg, p, e, h, dt)
+  lru.gates_impl = _lib.GATES_FUSED_EXACT if exact else _lib.GATES_FUSED
+  xb = torch.randn((b, t, e), generator=g).to(dt).to(DEV)
+  pos = torch.arange(t).repeat(b, 1)
+  for start in (1, 2, 3, 126, 127, 128, 129, 130, 131, 255, 256, 500, t - 2, t - 1):
+    if 0 < start < t:
+      pos[0, start:] = torch.arange(t - start)
+  if b > 1:
+    pos[1] = torch.arange(t) + 7           # a row that continues a document: no reset at all
+  pos = pos.to(DEV)
+  # composition of the two modules (conv output through HBM)
+  c, window_ref = conv(xb, pos)
+  y_ref, h_ref = lru(c, pos)
+  # the path as one kernel (yb = None: the join is the identity)
+  before = _lib.load().rgk_set_conv_fusion(1)
+  try:
+    out, new = rg.recurrent_path(xb, None, pos, conv, lru, None)
+  finally:
+    _lib.load().rgk_set_conv_fusion(before)
+  assert torch.equal(new.conv1d_state, window_ref), "conv window"
+  if b * 2 * h >= torch.cuda.get_device_properties(0).multi_processor_count:
+    # every carry comes from the predecessor's published state: the kernel is deterministic
+    assert torch.equal(out, y_ref), "output"
+    assert torch.equal(new.rg_lru_state, h_ref), "final state"
+  else:
+    # with fewer chains than SMs carries are composed from whichever maps have been published, in
+    # an order that depends on timing: float32 states may differ in the last bit between any two
+    # runs of the kernel, and a bfloat16 output here and there with them
+    assert norm_err(new.rg_lru_state, h_ref) <= 1e-6, "final state"
+    assert float((out != y_ref).float().mean()) <= 1e-3, "output"
+    assert norm_err(out, y_ref) <= 2.0 ** -7, "output"
+  _lib.check_status()
