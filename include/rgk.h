@@ -217,6 +217,10 @@ RGK_API int rgk_set_conv_fusion(int enabled);
  * fused single-kernel step reads and then writes every state element from one and the same
  * thread, so it runs in place as well).
  * segment_pos [B] still selects the reset behaviour of the RG-LRU (a position of 0 drops h_in).
+ * gates_impl: RGK_GATES_AUTO / RGK_GATES_FUSED = the single kernel with the packed-tanh input gate
+ * and gelu and the table for exp(log_a) (as the prefill kernel's default arithmetic);
+ * RGK_GATES_FUSED_EXACT / RGK_GATES_TCGEN05 = the same kernel with every rounding of the reference;
+ * RGK_GATES_SIMT = the CUDA-core kernels.
  * ---------------------------------------------------------------------------------------------- */
 RGK_API int rgk_recurrent_path_decode(const void* xb, const void* yb, const void* segment_pos,
                               int pos_dtype, const rgk_params* p, const float* h_in,

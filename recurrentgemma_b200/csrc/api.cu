@@ -993,7 +993,9 @@ int rgk_recurrent_path_decode(const void* xb, const void* yb, const void* segmen
     RGK_CUDA(rgk::launch_path_decode_tc(xb, yb, segment_pos, pos_dtype, p->conv_w, p->conv_b,
                                         p->a_param, p->gate_x_b, p->gate_a_b, packed, h_in,
                                         conv_cache_in, B, H, out, h_out, conv_cache_out, workspace,
-                                        s),
+                                        s, (gates_impl == RGK_GATES_FUSED_EXACT ||
+                                            gates_impl == RGK_GATES_TCGEN05) ? rgk::kMathExact
+                                                                             : rgk::kMathFast),
              "fused decode launch");
     return RGK_OK;
   }

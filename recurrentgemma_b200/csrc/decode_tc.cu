@@ -35,7 +35,8 @@ constexpr int kOffConst = kOffA + kSlices * kASlice;           // 131072
 constexpr int kOffBar = kOffConst + 3 * (kChanCta / 2) * 4;    // two mbarriers
 constexpr int kOffTmem = kOffBar + 16;
 constexpr int kOffAbort = kOffTmem + 4;
-constexpr int kSmem = kOffAbort + 4 + 1024;
+constexpr int kOffLutDec = (kOffAbort + 4 + 15) & ~15;        // {a, multiplier} by log_a (tc_common.cuh)
+constexpr int kSmem = kOffLutDec + kLutEntries * 4 + 1024;
 constexpr int kThreadsDec = 512;
 constexpr int kEpiCols = kChanCta / (kThreadsDec / 128);   // channels per epilogue thread: 16
 constexpr uint32_t kIdescDec = tc_idesc_bf16(kRowsM, kN);
@@ -47,7 +48,9 @@ __device__ __forceinline__ uint4 add4(const uint4& a, const uint4& b) {
   return make_uint4(badd2(a.x, b.x), badd2(a.y, b.y), badd2(a.z, b.z), badd2(a.w, b.w));
 }
 
-template <bool kMul>
+// kMath: how the gates and the gelu are evaluated (see rgk_internal.h); the fast variant takes
+// a = exp(log_a) and the input multiplier from a shared-memory table, built in the prologue.
+template <bool kMul, int kMath>
 __global__ void __launch_bounds__(kThreadsDec, 1)
 decode_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __nv_bfloat16* __restrict__ xb,
                  const __nv_bfloat16* __restrict__ yb, const void* __restrict__ pos, int pos64,
@@ -72,6 +75,9 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __nv_bfloat16*
   const int tile = blockIdx.y;
   const int chan0 = head * kHeadW + quarter * kChanCta;   // first channel this CTA produces
 
+  uint32_t* s_lut = reinterpret_cast<uint32_t*>(smem + kOffLutDec);
+  if constexpr (kMath == kMathFast)
+    for (int i = tid; i < kLutEntries; i += kThreadsDec) s_lut[i] = a_mult_entry(i);
   if (tid == 0) {
     *s_abort = 0;
     mbar_init(bar_b, 1);
@@ -92,7 +98,9 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __nv_bfloat16*
     else {
       const float s0 = round_bf16(softplus_(__bfloat162float(a_param[e])));
       const float s1 = round_bf16(softplus_(__bfloat162float(a_param[e + 1])));
-      v = pack_bf16x2(-8.0f * s0, -8.0f * s1);
+      // (clamped to the range of the table: beyond it a = exp(log_a) is 0 in float32 either way)
+      v = kMath == kMathFast ? pack_bf16x2(fmaxf(-8.0f * s0, kLogAFloor), fmaxf(-8.0f * s1, kLogAFloor))
+                             : pack_bf16x2(-8.0f * s0, -8.0f * s1);
     }
     s_const[which * (kChanCta / 2) + pair] = v;
   }
@@ -270,9 +278,23 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __nv_bfloat16*
           const int n = j * 8 + p * 2;
           const int pair = (col_grp * kEpiCols + n) >> 1;
           uint32_t a2, xn2;
-          gate_pair(__uint_as_float(zx[n]), __uint_as_float(zx[n + 1]), __uint_as_float(za[n]),
-                    __uint_as_float(za[n + 1]), s_const[pair], s_const[kChanCta / 2 + pair],
-                    s_const[kChanCta + pair], cp[p], is_reset, a2, xn2);
+          if constexpr (kMath == kMathFast) {
+            uint32_t gx2, mult2;
+            const uint32_t bx2 = s_const[pair];
+            gate_tokens<kMathFast, true>(__uint_as_float(zx[n]), __uint_as_float(zx[n + 1]),
+                                         __uint_as_float(za[n]), __uint_as_float(za[n + 1]), bx2,
+                                         s_const[kChanCta / 2 + pair], bmul2(bx2, 0x3f003f00u),
+                                         s_const[kChanCta + pair], a2, gx2, mult2, s_lut);
+            if (is_reset) {
+              mult2 = 0x3f803f80u;
+              a2 = 0u;
+            }
+            xn2 = bmul2(bmul2(cp[p], gx2), mult2);
+          } else {
+            gate_pair(__uint_as_float(zx[n]), __uint_as_float(zx[n + 1]), __uint_as_float(za[n]),
+                      __uint_as_float(za[n + 1]), s_const[pair], s_const[kChanCta / 2 + pair],
+                      s_const[kChanCta + pair], cp[p], is_reset, a2, xn2);
+          }
           const float h0v = (p & 1) ? hv[2 * j + (p >> 1)].z : hv[2 * j + (p >> 1)].x;
           const float h1v = (p & 1) ? hv[2 * j + (p >> 1)].w : hv[2 * j + (p >> 1)].y;
           // h = a h + x in float32; the state keeps the unrounded value (torch/layers.py:176-177)
@@ -280,8 +302,12 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __nv_bfloat16*
           hn[2 * p + 1] = fmaf(bf16_hi(a2), h1v, bf16_hi(xn2));
           op[p] = pack_bf16x2(hn[2 * p], hn[2 * p + 1]);
           if constexpr (kMul) {
-            const float g0 = gelu_tanh_<true>(bf16_lo(yp[p])), g1 = gelu_tanh_<true>(bf16_hi(yp[p]));
-            op[p] = bmul2(op[p], pack_bf16x2(g0, g1));
+            if constexpr (kMath == kMathFast) {
+              op[p] = join_gelu2<kMathFast>(op[p], yp[p]);
+            } else {
+              const float g0 = gelu_tanh_<true>(bf16_lo(yp[p])), g1 = gelu_tanh_<true>(bf16_hi(yp[p]));
+              op[p] = bmul2(op[p], pack_bf16x2(g0, g1));
+            }
           }
         }
         if (row_ok) {
@@ -312,7 +338,7 @@ cudaError_t launch_path_decode_tc(const void* xb, const void* yb, const void* po
                                   const void* bx, const void* ba, const void* packed_w,
                                   const float* h_in, const void* cache_in, int64_t B, int H,
                                   void* out, float* h_out, void* cache_out, void* ws_header,
-                                  cudaStream_t s) {
+                                  cudaStream_t s, int math) {
   if (B == 0) return cudaSuccess;
   using T_ = __nv_bfloat16;
   CUtensorMap map_w;
@@ -320,11 +346,16 @@ cudaError_t launch_path_decode_tc(const void* xb, const void* yb, const void* po
     return cudaErrorInvalidValue;
   static PerDeviceOnce once;
   cudaError_t e0 = once.run([] {
-    cudaError_t e = cudaFuncSetAttribute(decode_tc_kernel<true>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
-    if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(decode_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                kSmem);
+    cudaError_t e;
+#define RGK_DEC_ATTR(MUL, MATH)                                                                 \
+    if ((e = cudaFuncSetAttribute(decode_tc_kernel<MUL, MATH>,                                  \
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem)) != cudaSuccess) return e
+    RGK_DEC_ATTR(true, kMathExact);
+    RGK_DEC_ATTR(true, kMathFast);
+    RGK_DEC_ATTR(false, kMathExact);
+    RGK_DEC_ATTR(false, kMathFast);
+#undef RGK_DEC_ATTR
+    return cudaSuccess;
   });
   if (e0 != cudaSuccess) return e0;
   const dim3 grid((unsigned)(H * 4), (unsigned)((B + kRowsM - 1) / kRowsM));
@@ -345,12 +376,14 @@ cudaError_t launch_path_decode_tc(const void* xb, const void* yb, const void* po
   attr[1].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 2;
-#define RGK_DEC(MUL)                                                                               \
-  cudaLaunchKernelEx(&cfg, decode_tc_kernel<MUL>, map_w, (const T_*)xb, (const T_*)yb, pos, pos64, \
-                     (const T_*)conv_w, (const T_*)conv_b, (const T_*)a_param, (const T_*)bx,      \
-                     (const T_*)ba, h_in, (const T_*)cache_in, packed_w, (int)B, E, (T_*)out, h_out,         \
-                     (T_*)cache_out, reinterpret_cast<WsHeader*>(ws_header))
-  cudaError_t lerr = yb ? RGK_DEC(true) : RGK_DEC(false);
+#define RGK_DEC(MUL, MATH)                                                                         \
+  cudaLaunchKernelEx(&cfg, decode_tc_kernel<MUL, MATH>, map_w, (const T_*)xb, (const T_*)yb, pos,  \
+                     pos64, (const T_*)conv_w, (const T_*)conv_b, (const T_*)a_param, (const T_*)bx, \
+                     (const T_*)ba, h_in, (const T_*)cache_in, packed_w, (int)B, E, (T_*)out,      \
+                     h_out, (T_*)cache_out, reinterpret_cast<WsHeader*>(ws_header))
+  cudaError_t lerr;
+  if (math == kMathExact) lerr = yb ? RGK_DEC(true, kMathExact) : RGK_DEC(false, kMathExact);
+  else lerr = yb ? RGK_DEC(true, kMathFast) : RGK_DEC(false, kMathFast);
   if (lerr != cudaSuccess) return lerr;
 #undef RGK_DEC
   return cudaGetLastError();

@@ -106,7 +106,7 @@ cudaError_t launch_path_decode_tc(const void* xb, const void* yb, const void* po
                                   const void* bx, const void* ba, const void* packed_w,
                                   const float* h_in, const void* cache_in, int64_t B, int H,
                                   void* out, float* h_out, void* cache_out, void* ws_header,
-                                  cudaStream_t s);
+                                  cudaStream_t s, int math);
 
 // rglru_chan_tc.cu: gate projections + gate arithmetic + scan (+ join) in one kernel with
 // channel-major accumulators (TMEM lane = channel), so that gate arithmetic, recurrence and join

@@ -374,14 +374,21 @@ def test_fused_decode_step_matches_unfused_and_oracle(rg, oracle, shape):
   cc = C.normal(case.name, "cc", (b, 3, e), 1.0, dt)
   pos = torch.randint(0, 3, (b, 1), generator=torch.Generator().manual_seed(3))
   cache = rg.RecurrentBlockCache(rg_lru_state=h0.to(DEV), conv1d_state=cc.to(DEV))
-  lru.gates_impl = _lib.GATES_AUTO
-  o_f, c_f = rg.recurrent_path(xb.to(DEV), yb.to(DEV), pos.to(DEV), conv, lru, cache)
-  _lib.workspace_status(_lib.workspace(torch.device(DEV), 1))
   lru.gates_impl = _lib.GATES_SIMT
   o_u, c_u = rg.recurrent_path(xb.to(DEV), yb.to(DEV), pos.to(DEV), conv, lru, cache)
   tol = TOL[dt]
-  assert_close(o_f, o_u, 5e-3, "fused vs unfused out")
-  assert_close(c_f.rg_lru_state, c_u.rg_lru_state, 5e-3, "fused vs unfused state")
+  # the variant with every rounding of the reference agrees closely with the CUDA-core kernels;
+  # the default one (packed-tanh input gate and gelu, table for exp(log_a)) within the parity bar
+  lru.gates_impl = _lib.GATES_FUSED_EXACT
+  o_e, c_e = rg.recurrent_path(xb.to(DEV), yb.to(DEV), pos.to(DEV), conv, lru, cache)
+  assert_close(o_e, o_u, 5e-3, "fused (exact) vs unfused out")
+  assert_close(c_e.rg_lru_state, c_u.rg_lru_state, 5e-3, "fused (exact) vs unfused state")
+  assert torch.equal(c_e.conv1d_state, c_u.conv1d_state)
+  lru.gates_impl = _lib.GATES_AUTO
+  o_f, c_f = rg.recurrent_path(xb.to(DEV), yb.to(DEV), pos.to(DEV), conv, lru, cache)
+  _lib.workspace_status(_lib.workspace(torch.device(DEV), 1))
+  assert_close(o_f, o_u, tol, "fused vs unfused out")
+  assert_close(c_f.rg_lru_state, c_u.rg_lru_state, tol, "fused vs unfused state")
   assert torch.equal(c_f.conv1d_state, c_u.conv1d_state)
   op = {"conv_w": p["conv_1d.w"], "conv_b": p["conv_1d.b"], "a_param": p["rg_lru.a_param"],
         "gate_x_w": p["rg_lru.input_gate.w"], "gate_x_b": p["rg_lru.input_gate.b"],
