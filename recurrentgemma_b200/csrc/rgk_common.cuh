@@ -153,13 +153,8 @@ template <bool kBf16>
 __device__ __forceinline__ void gate_math(float c, float zx, float za, float bx, float ba, float sp,
                                           bool is_reset, float& a_out, float& xn_out) {
   constexpr bool kFast = kBf16;
-  // The sigmoids use the hardware exponential in float32 as well: its relative error (2^-22, plus
-  // 2^-24 |z| from the scaled argument) reaches the recurrence only through log_a = -8 gate_a sp,
-  // i.e. as an absolute error 2e-7 |log_a| in the exponent of a, which a channel remembers for
-  // about 1 / |log_a| steps - a few 1e-7 of the state however slow the channel is.  exp(log_a)
-  // and exp(2 log_a) below stay on the accurate expf: their rounding enters 1 - a^2 directly.
-  const float gate_x = rnd<kBf16>(sigmoid_<true>(rnd<kBf16>(rnd<kBf16>(zx) + bx)));
-  const float gate_a = rnd<kBf16>(sigmoid_<true>(rnd<kBf16>(rnd<kBf16>(za) + ba)));
+  const float gate_x = rnd<kBf16>(sigmoid_<kFast>(rnd<kBf16>(rnd<kBf16>(zx) + bx)));
+  const float gate_a = rnd<kBf16>(sigmoid_<kFast>(rnd<kBf16>(rnd<kBf16>(za) + ba)));
   const float log_a = rnd<kBf16>((-8.0f * gate_a) * sp);
   const float e = exp_<kFast>(log_a);
   const float a = rnd<kBf16>(e);
