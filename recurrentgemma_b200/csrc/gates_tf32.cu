@@ -196,17 +196,23 @@ gates_tf32_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     const int64_t row = row0 + lane;
     const bool is_reset = row < M && pos_is_zero(pos, pos64, row);
     const int e0 = chan0 + cq * 32;
-    if (ok) ok = mbar_wait(bar_acc, 0, s_abort);             // every MMA has read the ring by now
-    tc_fence_after();
     uint8_t* blk_a = smem + warp * 8192;                     // conv values in, a out
     uint8_t* blk_x = blk_a + 4096;                           // normalised input out
     const int cr = lane >> 3, cp = lane & 7;                 // copy pattern: row cr + 4 k, piece cp
+    // the conv values of the warp's block are asked for while the last MMAs run
+    float4 cin[8];
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
       const int r = cr + 4 * k;
-      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (row0 + r < M) v = *reinterpret_cast<const float4*>(x + (row0 + r) * E + e0 + cp * 4);
-      *reinterpret_cast<float4*>(blk_a + r * 128 + ((cp ^ (r & 7)) << 4)) = v;
+      cin[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (row0 + r < M) cin[k] = __ldg(reinterpret_cast<const float4*>(x + (row0 + r) * E + e0 + cp * 4));
+    }
+    if (ok) ok = mbar_wait(bar_acc, 0, s_abort);             // every MMA has read the ring by now
+    tc_fence_after();
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int r = cr + 4 * k;
+      *reinterpret_cast<float4*>(blk_a + r * 128 + ((cp ^ (r & 7)) << 4)) = cin[k];
     }
     __syncwarp();
     const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lane_base) << 16) + cq * 32;
