@@ -47,8 +47,8 @@ __device__ __forceinline__ uint64_t tf32_desc(uint32_t addr) {
 }
 constexpr int kEpi = 16;
 constexpr int kThreadsF = (kEpi + 2) * 32;
-constexpr int kOffSp = kStages * kStageBytes;               // float [128]: softplus(a_param)
-constexpr int kOffBarF = kOffSp + kHalf * 4;                // full[2] lo_full[2] empty[2] acc_full
+constexpr int kOffSp = kStages * kStageBytes;               // float [3][128]: softplus(a_param), gate biases
+constexpr int kOffBarF = kOffSp + 3 * kHalf * 4;                // full[2] lo_full[2] empty[2] acc_full
 constexpr int kNumBarF = 3 * kStages + 1;
 constexpr int kOffTmemF = kOffBarF + kNumBarF * 8;
 constexpr int kOffAbortF = kOffTmemF + 4;
@@ -114,7 +114,11 @@ gates_tf32_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                  :: "r"(s_base + kOffTmemF), "r"(256) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
-  if (threadIdx.x < kHalf) s_sp[threadIdx.x] = softplus_(a_param[chan0 + threadIdx.x]);
+  if (threadIdx.x < kHalf) {
+    s_sp[threadIdx.x] = softplus_(a_param[chan0 + threadIdx.x]);
+    s_sp[kHalf + threadIdx.x] = bias_x[chan0 + threadIdx.x];
+    s_sp[2 * kHalf + threadIdx.x] = bias_a[chan0 + threadIdx.x];
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -222,7 +226,6 @@ gates_tf32_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
       tc_ld_32x16(t_row + cc * 16, zx);
       tc_ld_32x16(t_row + kHalf + cc * 16, za);
       tc_wait_ld();
-      const int e = e0 + cc * 16;
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
         const int piece = (cc * 4 + q) ^ (lane & 7);
@@ -232,8 +235,9 @@ gates_tf32_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const int n = q * 4 + j;
-          gate_math<false>(cvv[j], __uint_as_float(zx[n]), __uint_as_float(za[n]), bias_x[e + n],
-                           bias_a[e + n], s_sp[cq * 32 + cc * 16 + n], is_reset, av[j], xv[j]);
+          const int ch = cq * 32 + cc * 16 + n;            // channel within the half
+          gate_math<false, true>(cvv[j], __uint_as_float(zx[n]), __uint_as_float(za[n]), s_sp[kHalf + ch],
+                           s_sp[2 * kHalf + ch], s_sp[ch], is_reset, av[j], xv[j]);
         }
         *reinterpret_cast<float4*>(blk_a + lane * 128 + (piece << 4)) = make_float4(av[0], av[1], av[2], av[3]);
         *reinterpret_cast<float4*>(blk_x + lane * 128 + (piece << 4)) = make_float4(xv[0], xv[1], xv[2], xv[3]);

@@ -149,23 +149,31 @@ template <bool kFast> __device__ __forceinline__ float gelu_tanh_(float z) {
 // Returns a (already multiplied by !reset, torch/layers.py:168) and the normalised input.
 // In bfloat16 mode every tensor-level result is rounded exactly where torch rounds it.
 // ------------------------------------------------------------------------------------------------
-template <bool kBf16>
+// kQuickF32 (float32 only): the sigmoids on the hardware exponential, a^2 as a * a and the
+// hardware square root - a few 1e-7 of normalised error (measured 1.6e-6 -> 1.9e-6 at B2 T1024
+// behind the 3xTF32 contraction, whose own error dominates), for the kernel whose epilogue this
+// arithmetic bounds.  exp(log_a) itself stays on the accurate expf: a slow channel multiplies a
+// into its state a thousand times.
+template <bool kBf16, bool kQuickF32 = false>
 __device__ __forceinline__ void gate_math(float c, float zx, float za, float bx, float ba, float sp,
                                           bool is_reset, float& a_out, float& xn_out) {
   constexpr bool kFast = kBf16;
-  const float gate_x = rnd<kBf16>(sigmoid_<kFast>(rnd<kBf16>(rnd<kBf16>(zx) + bx)));
-  const float gate_a = rnd<kBf16>(sigmoid_<kFast>(rnd<kBf16>(rnd<kBf16>(za) + ba)));
+  constexpr bool kFastAux = kBf16 || kQuickF32;
+  const float gate_x = rnd<kBf16>(sigmoid_<kFastAux>(rnd<kBf16>(rnd<kBf16>(zx) + bx)));
+  const float gate_a = rnd<kBf16>(sigmoid_<kFastAux>(rnd<kBf16>(rnd<kBf16>(za) + ba)));
   const float log_a = rnd<kBf16>((-8.0f * gate_a) * sp);
   const float e = exp_<kFast>(log_a);
   const float a = rnd<kBf16>(e);
   float a_square;
   if constexpr (kBf16) {
     a_square = round_bf16(e * e);          // exp(2 log_a) up to float32 rounding
+  } else if constexpr (kQuickF32) {
+    a_square = e * e;
   } else {
     a_square = expf(2.0f * log_a);
   }
   const float gated_x = rnd<kBf16>(c * gate_x);
-  float mult = rnd<kBf16>(sqrt_<kFast>(rnd<kBf16>(1.0f - a_square)));
+  float mult = rnd<kBf16>(sqrt_<kFastAux>(rnd<kBf16>(1.0f - a_square)));
   if (is_reset) mult = 1.0f;
   a_out = is_reset ? 0.0f : a;
   xn_out = rnd<kBf16>(gated_x * mult);
