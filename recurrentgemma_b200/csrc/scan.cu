@@ -3,8 +3,8 @@
 //
 // Decomposition.  The [B, T, E] problem is cut into tiles of kRows time steps x 64 channels.
 // The x and a tiles are brought into shared memory by TMA (two cp.async.bulk.tensor copies per
-// tile, asked for by one thread), so a tile in flight costs no registers and four tiles per SM are
-// resident.  Inside a tile every thread owns 4 consecutive time steps of one 16-byte pack of
+// tile, asked for by one thread), so a tile in flight costs no registers and four tiles per SM (three
+// in float32) are resident.  Inside a tile every thread owns 4 (8) consecutive time steps of one 16-byte pack of
 // channels and runs them sequentially: pass 1 reduces its steps to the pair (P, H) of the affine
 // map h -> P h + H, the pairs of the tile's sub-chunks are chained through shared memory, and
 // pass 2 replays the same steps from shared memory starting from the now known incoming state.
@@ -29,14 +29,16 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int kChan = 64;        // channels per tile
-constexpr int kRowsPerThread = 4;
 constexpr unsigned kSpinLimit = 1u << 21;
 
 template <typename T> struct ScanCfg {
   static constexpr int kPack = Traits<T>::kPack;
+  // rows a thread scans: 4 (bfloat16), 8 (float32) - a tile is 128 time steps either way, so the
+  // chain of tiles a carry travels along is no longer for float32 than for bfloat16
+  static constexpr int kRowsPerThread = sizeof(T) == 4 ? 8 : 4;
   static constexpr int kLanesPerRow = kChan / kPack;          // 8 (bf16) or 16 (f32)
   static constexpr int kSubs = kThreads / kLanesPerRow;       // 32 or 16 sub-chunks
-  static constexpr int kRows = kSubs * kRowsPerThread;        // 128 or 64 time steps per tile
+  static constexpr int kRows = kSubs * kRowsPerThread;        // 128 time steps per tile
 };
 
 __device__ __forceinline__ unsigned ld_acquire(const unsigned* p) {
@@ -96,7 +98,7 @@ template <typename T> struct ScanSmem {
 };
 
 template <typename T, int kJoin>   // 0: no join, 1: y * gelu_tanh(y_mul), 2: y * y_mul
-__global__ void __launch_bounds__(kThreads, 4)
+__global__ void __launch_bounds__(kThreads, sizeof(T) == 4 ? 3 : 4)
 scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_a,
             const uint8_t* __restrict__ reset, const void* __restrict__ pos, int pos64,
             const float* __restrict__ h0, const T* __restrict__ y_mul, int B, int T_, int E,
@@ -150,21 +152,21 @@ scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
   const int sub = tid / Cfg::kLanesPerRow;
   const int e0 = g * kChan + lane_in_row * kPack;
   const bool chan_ok = e0 < E;
-  const int t0 = tt * Cfg::kRows + sub * kRowsPerThread;
+  const int t0 = tt * Cfg::kRows + sub * Cfg::kRowsPerThread;
   const int64_t row0 = (int64_t)b * T_;
   unsigned valid = 0, rst = 0;
 #pragma unroll
-  for (int r = 0; r < kRowsPerThread; ++r)
+  for (int r = 0; r < Cfg::kRowsPerThread; ++r)
     if (chan_ok && t0 + r < T_) valid |= 1u << r;
   if (reset != nullptr || pos != nullptr) {
-    bool rs[kRowsPerThread];
+    bool rs[Cfg::kRowsPerThread];
 #pragma unroll
-    for (int r = 0; r < kRowsPerThread; ++r) {
+    for (int r = 0; r < Cfg::kRowsPerThread; ++r) {
       const int64_t row = row0 + min(t0 + r, T_ - 1);
       rs[r] = (reset != nullptr) ? (reset[row] != 0) : pos_is_zero(pos, pos64, row);
     }
 #pragma unroll
-    for (int r = 0; r < kRowsPerThread; ++r) rst |= rs[r] ? (1u << r) : 0u;
+    for (int r = 0; r < Cfg::kRowsPerThread; ++r) rst |= rs[r] ? (1u << r) : 0u;
   }
   // a_t * !reset_t (torch/layers.py:168) and rows past the end (identity map) in one mask.
   const unsigned live = valid & ~rst;
@@ -180,8 +182,8 @@ scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
       valid = 0;   // compute nothing from a tile that never arrived; the carries still link up
     }
   }
-  const uint8_t* sx = smem + Sm::kOffX + (sub * kRowsPerThread) * kRowBytes + lane_in_row * 16;
-  const uint8_t* sa = smem + Sm::kOffA + (sub * kRowsPerThread) * kRowBytes + lane_in_row * 16;
+  const uint8_t* sx = smem + Sm::kOffX + (sub * Cfg::kRowsPerThread) * kRowBytes + lane_in_row * 16;
+  const uint8_t* sa = smem + Sm::kOffA + (sub * Cfg::kRowsPerThread) * kRowBytes + lane_in_row * 16;
 
   // ---- pass 1: this thread's steps as an affine map ----------------------------------------------
   {
@@ -189,7 +191,7 @@ scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
 #pragma unroll
     for (int i = 0; i < kPack; ++i) { P[i] = 1.0f; Hh[i] = 0.0f; }
 #pragma unroll
-    for (int r = 0; r < kRowsPerThread; ++r) {
+    for (int r = 0; r < Cfg::kRowsPerThread; ++r) {
       if (valid & (1u << r)) {
         float av[kPack], xv[kPack];
         unpack<T>(*reinterpret_cast<const uint4*>(sx + r * kRowBytes), xv);
@@ -211,11 +213,11 @@ scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
   }
   // The other branch's tile is needed once, in pass 2: it goes straight to registers, and its
   // latency hides behind the carry resolution below.
-  uint4 mraw[kRowsPerThread];
+  uint4 mraw[Cfg::kRowsPerThread];
   if constexpr (kMul) {
     const int e_ld = chan_ok ? e0 : 0;
 #pragma unroll
-    for (int r = 0; r < kRowsPerThread; ++r)
+    for (int r = 0; r < Cfg::kRowsPerThread; ++r)
       mraw[r] = ld_stream(y_mul + (row0 + min(t0 + r, T_ - 1)) * E + e_ld);
   }
   __syncthreads();
@@ -305,7 +307,7 @@ scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
   // warp 0 resolves the carry do most of pass 2's arithmetic in that time ---------------------------
   if constexpr (kJoin == 1) {
 #pragma unroll
-    for (int r = 0; r < kRowsPerThread; ++r) {
+    for (int r = 0; r < Cfg::kRowsPerThread; ++r) {
       float mv[kPack];
       unpack<T>(mraw[r], mv);
       if constexpr (kBf16) {
@@ -342,7 +344,7 @@ scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
 #pragma unroll
   for (int i = 0; i < kPack; ++i) h[i] = s_sub[sub][lane_in_row * kPack + i].y;
 #pragma unroll
-  for (int r = 0; r < kRowsPerThread; ++r) {
+  for (int r = 0; r < Cfg::kRowsPerThread; ++r) {
     if (valid & (1u << r)) {
       float av[kPack], xv[kPack];
       unpack<T>(*reinterpret_cast<const uint4*>(sx + r * kRowBytes), xv);
